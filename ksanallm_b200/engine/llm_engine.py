@@ -1,0 +1,520 @@
+"""The serving engine: request intake, the step loop, output delivery.
+
+Rank 0 owns the native scheduler (C++), plans every step, broadcasts the packed plan to the other
+tensor-parallel ranks (one int32 buffer over the CPU process group), runs its shard of the model and
+samples. Other ranks run :meth:`LLMEngine.follow`. Reference counterparts: InferenceEngine
+(src/ksana_llm/service/inference_engine.cpp:56-370, 418-561), BatchManager::MainProcess
+(batch_manager/batch_manager.cpp:119-214), LlmRuntime::StepOnChief (runtime/llm_runtime.cpp:290-338).
+"""
+from __future__ import annotations
+
+import itertools
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .. import host as _host
+from ..config.model_config import ModelConfig
+from ..config.schema import ServingConfig
+from ..models.transformer import TransformerModel
+from ..parallel.comm import TPGroup
+from .model_runner import ModelRunner
+from .sampler import SampleRow
+from .sampling_params import SamplingParams
+
+FINISH_NAMES = {
+    _host.FINISH_NONE: None, _host.FINISH_EOS: "stop", _host.FINISH_STOP_TOKEN: "stop", _host.FINISH_LENGTH: "length",
+    _host.FINISH_ABORTED: "abort", _host.FINISH_TIMEOUT: "timeout", _host.FINISH_STOP_STRING: "stop",
+    _host.FINISH_ERROR: "error",
+}
+
+
+class EngineError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(message)
+        self.code = code
+
+
+@dataclass
+class SequenceOutput:
+    seq_id: int
+    output_tokens: List[int] = field(default_factory=list)
+    logprobs: List[Any] = field(default_factory=list)
+    finished: bool = False
+    finish_reason: Optional[str] = None
+    cum_logprob: float = 0.0
+    text_checked: int = 0  # number of output tokens already scanned for stop strings
+
+
+class Request:
+    """One user request = one or more output sequences (parallel sampling / beams)."""
+
+    def __init__(self, req_id: int, prompt_tokens: List[int], params: SamplingParams, arrival: float):
+        self.req_id = req_id
+        self.prompt_tokens = prompt_tokens
+        self.params = params
+        self.arrival = arrival
+        self.first_token_time: Optional[float] = None
+        self.finish_time: Optional[float] = None
+        self.token_times: List[float] = []
+        self.seqs: List[SequenceOutput] = []
+        self.finished = False
+        self.error: Optional[EngineError] = None
+        self.cond = threading.Condition()
+        self.version = 0
+        self.aborted = False
+        self.refit = None
+        self.grammar = None
+        self.probe = None  # /forward request targets
+        self.probe_result = None
+        self.generators: Dict[int, torch.Generator] = {}
+        self.tries: Dict[int, Any] = {}
+        self.beam = None
+
+    def notify(self) -> None:
+        with self.cond:
+            self.version += 1
+            self.cond.notify_all()
+
+    def wait(self, last_version: int, timeout: Optional[float] = None) -> int:
+        with self.cond:
+            if self.version == last_version and not self.finished:
+                self.cond.wait(timeout)
+            return self.version
+
+    @property
+    def output_token_ids(self) -> List[List[int]]:
+        return [list(s.output_tokens) for s in self.seqs]
+
+
+class LLMEngine:
+    def __init__(self, model: TransformerModel, serving: ServingConfig, tp: Optional[TPGroup] = None,
+                 num_blocks: Optional[int] = None, num_host_blocks: Optional[int] = None,
+                 detokenize: Optional[Callable[[List[int]], str]] = None, seed: int = 0,
+                 kv_dtype: Optional[torch.dtype] = None):
+        self.model = model
+        self.cfg: ModelConfig = model.cfg
+        self.serving = serving
+        self.tp = tp or model.tp
+        self.detokenize = detokenize
+        bs_cfg, bm_cfg = serving.setting.batch_scheduler, serving.setting.block_manager
+        self.block_size = 64 if self.cfg.use_mla and bm_cfg.block_token_num == 16 else bm_cfg.block_token_num
+        if num_blocks is None:
+            num_blocks = self._derive_num_blocks(kv_dtype)
+        if num_host_blocks is None:
+            num_host_blocks = int(num_blocks * bm_cfg.block_host_memory_factor) if bs_cfg.preempt_mode == 0 else 0
+            num_host_blocks = min(num_host_blocks, self._host_block_cap(kv_dtype))
+        self.num_blocks = num_blocks
+        max_blocks_per_seq = (bs_cfg.max_token_len + self.block_size - 1) // self.block_size + 1
+        self.runner = ModelRunner(model, num_blocks, self.block_size, num_host_blocks, bs_cfg.max_step_tokens,
+                                  bs_cfg.max_batch_size, max_blocks_per_seq, kv_dtype, seed)
+        self.is_driver = self.tp.rank == 0
+        self.mtp_steps = bs_cfg.mtp_step_num if (bs_cfg.enable_speculative_decoding or bs_cfg.mtp_step_num) and \
+            model.mtp_layers else 0
+        self.trie_drafts = 3 if (bs_cfg.enable_speculative_decoding and not model.mtp_layers) else 0
+        sc = _host.SchedulerConfig()
+        sc.block_size = self.block_size
+        sc.max_batch_size = bs_cfg.max_batch_size
+        sc.max_step_tokens = bs_cfg.max_step_tokens
+        sc.max_token_len = bs_cfg.max_token_len
+        sc.max_waiting_queue_len = bs_cfg.max_waiting_queue_len
+        sc.waiting_timeout_ms = bs_cfg.waiting_timeout_in_ms
+        sc.split_fuse_token_num = bs_cfg.split_fuse_token_num
+        sc.preempt_mode = bs_cfg.preempt_mode if num_host_blocks > 0 else 1
+        sc.launch_block_threshold = bs_cfg.launch_block_threshold
+        sc.swapin_block_threshold = bs_cfg.swapin_block_threshold
+        sc.max_draft_tokens = max(self.mtp_steps, self.trie_drafts)
+        sc.decode_token_threshold = 1 + sc.max_draft_tokens
+        self.cache = _host.KVCacheManager(num_blocks, num_host_blocks, self.block_size,
+                                          bool(bs_cfg.enable_auto_prefix_cache))
+        self.sched = _host.Scheduler(sc, self.cache)
+        self.sched_cfg = sc
+        self._ids = itertools.count(1)
+        self._seq_ids = itertools.count(1)
+        self.requests: Dict[int, Request] = {}
+        self.seq_owner: Dict[int, Tuple[Request, SequenceOutput]] = {}
+        self.lock = threading.RLock()
+        self._loop_thread: Optional[threading.Thread] = None
+        self._stop = threading.Event()
+        self._wake = threading.Event()
+        self.step_count = 0
+        self.metrics = None  # utils.metrics.Metrics, attached by the server
+        self.tracer = None
+        self._ctl = None  # CPU process group for plan broadcast
+        self._hdr = np.zeros(64, dtype=np.int32)
+        self.stats = {"generated_tokens": 0, "prompt_tokens": 0, "steps": 0, "forward_time": 0.0, "schedule_time": 0.0}
+        self.on_step: Optional[Callable[[Dict[str, Any]], None]] = None
+
+    # ---- sizing ----------------------------------------------------------------------------------------
+    def _derive_num_blocks(self, kv_dtype) -> int:
+        bm = self.serving.setting.block_manager
+        per_block = self.model.kv_block_bytes(self.block_size, kv_dtype)
+        if self.model.device.type == "cuda":
+            free, total = torch.cuda.mem_get_info(self.model.device)
+            budget = free - int(total * bm.reserved_device_memory_ratio) - (2 << 30)
+            if bm.block_device_memory_ratio > 0:
+                budget = min(budget, int(total * bm.block_device_memory_ratio))
+            n = max(int(budget // per_block), 16)
+        else:
+            n = 512
+        if self.tp.size > 1:
+            t = torch.tensor([n], dtype=torch.int64, device=self.model.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.tp.group)
+            n = int(t.item())
+        cap = self.serving.setting.batch_scheduler
+        need = (cap.max_token_len // self.block_size + 2) * max(cap.max_batch_size, 1) * 4
+        return int(min(n, max(need, 64)))
+
+    def _host_block_cap(self, kv_dtype) -> int:
+        per_block = self.model.kv_block_bytes(self.block_size, kv_dtype)
+        return max(int((8 << 30) // max(per_block, 1)), 0)
+
+    # ---- request intake --------------------------------------------------------------------------------
+    def add_request(self, prompt_tokens: Sequence[int], params: Optional[SamplingParams] = None,
+                    refit=None, grammar=None, probe=None) -> Request:
+        params = params or SamplingParams()
+        params.verify()
+        now = time.time()
+        req = Request(next(self._ids), list(int(t) for t in prompt_tokens), params, now)
+        req.refit, req.grammar, req.probe = refit, grammar, probe
+        n_out = max(params.num_beams, params.num_return_sequences, 1)
+        with self.lock:
+            first = self._enqueue_seq(req, req.prompt_tokens)
+            if params.num_beams > 1:
+                from .beam_search import BeamState
+                req.beam = BeamState(params.num_beams, params.num_return_sequences, params.length_penalty,
+                                     params.max_new_tokens)
+            req._pending_fanout = n_out - 1 if params.num_beams <= 1 else 0
+            self.requests[req.req_id] = req
+            self.stats["prompt_tokens"] += len(req.prompt_tokens)
+        self._wake.set()
+        return req
+
+    def _enqueue_seq(self, req: Request, tokens: List[int]) -> SequenceOutput:
+        sid = next(self._seq_ids)
+        p = req.params
+        eos = list(self.cfg.eos_token_ids)
+        code = self.sched.enqueue(sid, tokens, p.max_new_tokens, p.ignore_eos, eos, list(p.stop_token_ids),
+                                  int(req.arrival * 1000), req.req_id)
+        if code != _host.RET_SUCCESS:
+            msg = {_host.RET_EXCEED_CAPACITY: "waiting queue is full",
+                   _host.RET_INPUT_LENGTH_EXCEEDED: "input length exceeds max_token_len",
+                   _host.RET_OUT_OF_MEMORY: "request can never fit in the KV cache",
+                   _host.RET_INVALID_ARGUMENT: "invalid request"}.get(code, "rejected")
+            raise EngineError(code, msg)
+        so = SequenceOutput(sid)
+        req.seqs.append(so)
+        self.seq_owner[sid] = (req, so)
+        if p.seed is not None:
+            g = torch.Generator(device=self.runner.device)
+            g.manual_seed(p.seed + len(req.seqs) - 1)
+            req.generators[sid] = g
+        if self.trie_drafts:
+            trie = _host.DraftTrie()
+            trie.feed(tokens)
+            req.tries[sid] = trie
+        return so
+
+    def abort(self, req: Request) -> None:
+        with self.lock:
+            req.aborted = True
+            for s in req.seqs:
+                if not s.finished:
+                    self.sched.abort(s.seq_id)
+        self._wake.set()
+
+    def has_unfinished(self) -> bool:
+        return self.sched.has_unfinished()
+
+    # ---- one step ----------------------------------------------------------------------------------------
+    def step(self) -> int:
+        """Schedules and runs one step. Returns the number of tokens generated."""
+        t0 = time.perf_counter()
+        with self.lock:
+            plan = self.sched.schedule(int(time.time() * 1000))
+            for sid, reason in plan.dropped:
+                self._finish_seq(sid, reason)
+            if plan.empty():
+                if self.tp.size > 1 and len(plan.swap_out) + len(plan.swap_in) + len(plan.block_copies) > 0:
+                    pass
+                return 0
+            layout = self.sched.pack(plan, self.runner.staging.host_np, self.runner.max_blocks_per_seq)
+            rows, greedy, refit = self._sample_rows(plan)
+        t1 = time.perf_counter()
+        if self.tp.size > 1:
+            self._broadcast_plan(layout, plan, greedy)
+        self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
+        meta = self.runner.upload(layout)
+        hidden = self.runner.forward(meta, refit)
+        self._run_probes(plan, meta, hidden)
+        out = self.runner.sample(hidden, meta, rows, greedy)
+        t2 = time.perf_counter()
+        with self.lock:
+            n_new = self._apply_results(plan, out, meta, hidden)
+        self.step_count += 1
+        self.stats["steps"] += 1
+        self.stats["schedule_time"] += t1 - t0
+        self.stats["forward_time"] += t2 - t1
+        if self.on_step is not None:
+            self.on_step({"tokens": meta.total_tokens, "seqs": meta.num_seqs, "new_tokens": n_new,
+                          "schedule_s": t1 - t0, "forward_s": t2 - t1, "prefill": meta.num_prefill,
+                          "decode": meta.num_decode})
+        return n_new
+
+    def _sample_rows(self, plan):
+        rows: List[SampleRow] = []
+        refit = None
+        for e in plan.entries:
+            req, so = self.seq_owner[e.seq_id]
+            if req.refit is not None and e.q_start == 0:
+                refit = (refit or []) + [(pos + 0, emb) for pos, emb in req.refit]
+            for j in range(e.num_logits):
+                bm = None
+                if req.grammar is not None and j == 0:
+                    bm = req.grammar.next_bitmask(so.seq_id)
+                rows.append(SampleRow(req.params, req.prompt_tokens, so.output_tokens, bm,
+                                      req.generators.get(e.seq_id)))
+        from .sampler import Sampler
+        greedy = Sampler.all_greedy(rows)
+        return rows, greedy, refit
+
+    def _apply_results(self, plan, out, meta, hidden) -> int:
+        now = time.time()
+        sampled = out.tokens
+        # beam search rewrites the sampled tokens from the top-2k log-probs before the scheduler sees them
+        results = self.sched.update(plan, sampled, int(now * 1000))
+        row = 0
+        row_of = {}
+        for e in plan.entries:
+            row_of[e.seq_id] = row
+            row += e.num_logits
+        n_new = 0
+        touched = set()
+        for r in results:
+            req, so = self.seq_owner.get(r.seq_id, (None, None))
+            if req is None:
+                continue
+            base = row_of[r.seq_id]
+            for j, tok in enumerate(r.new_tokens):
+                so.output_tokens.append(int(tok))
+                if out.logprobs and out.logprobs[base + j] is not None:
+                    so.logprobs.append({"token": int(tok), "logprob": out.chosen_logprob[base + j],
+                                        "top": out.logprobs[base + j]})
+                    so.cum_logprob += out.chosen_logprob[base + j] or 0.0
+                if req.grammar is not None:
+                    req.grammar.accept(so.seq_id, int(tok))
+                trie = req.tries.get(r.seq_id)
+                if trie is not None:
+                    trie.feed_one(int(tok))
+            n_new += len(r.new_tokens)
+            if req.first_token_time is None and r.new_tokens:
+                req.first_token_time = now
+            req.token_times.extend([now] * len(r.new_tokens))
+            reason = r.finish_reason
+            if reason == _host.FINISH_NONE and req.params.stop_strings and self.detokenize is not None:
+                if self._hit_stop_string(req, so):
+                    self.sched.finish(r.seq_id, _host.FINISH_STOP_STRING)
+                    reason = _host.FINISH_STOP_STRING
+            if reason == _host.FINISH_NONE and req.grammar is not None and req.grammar.is_terminated(so.seq_id):
+                self.sched.finish(r.seq_id, _host.FINISH_EOS)
+                reason = _host.FINISH_EOS
+            if reason != _host.FINISH_NONE:
+                self._finish_seq(r.seq_id, reason, notify=False)
+            else:
+                trie = req.tries.get(r.seq_id)
+                if trie is not None:
+                    d = trie.propose(self.trie_drafts)
+                    if d:
+                        self.sched.set_drafts(r.seq_id, d)
+            # fan-out of parallel samples once the prompt's blocks are cached
+            if getattr(req, "_pending_fanout", 0) and r.new_tokens:
+                k = req._pending_fanout
+                req._pending_fanout = 0
+                for _ in range(k):
+                    try:
+                        self._enqueue_seq(req, req.prompt_tokens)
+                    except EngineError as ex:
+                        req.error = ex
+            touched.add(req.req_id)
+        self.stats["generated_tokens"] += n_new
+        for rid in touched:
+            req = self.requests.get(rid)
+            if req is not None:
+                self._check_request_done(req)
+                req.notify()
+        return n_new
+
+    def _hit_stop_string(self, req: Request, so: SequenceOutput) -> bool:
+        window = so.output_tokens[max(0, so.text_checked - 16):]
+        text = self.detokenize(window)
+        so.text_checked = len(so.output_tokens)
+        return any(s and s in text for s in req.params.stop_strings)
+
+    def _finish_seq(self, sid: int, reason: int, notify: bool = True) -> None:
+        owner = self.seq_owner.pop(sid, None)
+        self.sched.forget(sid)
+        if owner is None:
+            return
+        req, so = owner
+        so.finished = True
+        so.finish_reason = FINISH_NAMES.get(reason, "stop")
+        if reason == _host.FINISH_TIMEOUT and req.error is None:
+            req.error = EngineError(_host.RET_REQUEST_TIMEOUT if hasattr(_host, "RET_REQUEST_TIMEOUT") else 4,
+                                    "request timed out in queue")
+        if notify:
+            self._check_request_done(req)
+            req.notify()
+
+    def _check_request_done(self, req: Request) -> None:
+        if req.finished:
+            return
+        if all(s.finished for s in req.seqs) and not getattr(req, "_pending_fanout", 0):
+            req.finished = True
+            req.finish_time = time.time()
+            self.requests.pop(req.req_id, None)
+            if self.metrics is not None:
+                self.metrics.observe_request(req)
+
+    def _run_probes(self, plan, meta, hidden) -> None:
+        for e in plan.entries:
+            owner = self.seq_owner.get(e.seq_id)
+            if owner is None or owner[0].probe is None:
+                continue
+            from .forward_probe import run_probe
+            b = [x.seq_id for x in plan.entries].index(e.seq_id)
+            lo, hi = int(meta.cu_q_host[b]), int(meta.cu_q_host[b + 1])
+            owner[0].probe_result = run_probe(self.model, owner[0].probe, hidden[lo:hi],
+                                              self.model.last_residual[lo:hi], owner[0].prompt_tokens)
+
+    # ---- multi-rank plan distribution ---------------------------------------------------------------------
+    def attach_control_group(self, group) -> None:
+        self._ctl = group
+
+    def _broadcast_plan(self, layout, plan, greedy: bool, stop: bool = False) -> None:
+        keys = ["num_seqs", "num_prefill", "num_decode", "total_tokens", "total_logits", "max_q_len", "max_kv_len",
+                "max_blocks", "input_ids", "positions", "slot_mapping", "seq_of_token", "cu_q", "kv_lens", "q_starts",
+                "logits_idx", "block_tables", "total_words"]
+        h = self._hdr
+        h[:] = 0
+        h[0] = 2 if stop else 1
+        if not stop:
+            for i, k in enumerate(keys):
+                h[1 + i] = layout[k]
+            h[30] = 1 if greedy else 0
+            so, si, bc = plan.swap_out, plan.swap_in, plan.block_copies
+            h[31], h[32], h[33] = len(so), len(si), len(bc)
+        hdr = torch.from_numpy(h)
+        dist.broadcast(hdr, src=0, group=self._ctl)
+        if stop:
+            return
+        n = int(h[18])
+        dist.broadcast(self.runner.staging.host[:n], src=0, group=self._ctl)
+        extra = int(h[31] + h[32] + h[33])
+        if extra:
+            arr = np.concatenate([np.asarray(a, dtype=np.int32).reshape(-1, 2) for a in (so, si, bc)], 0)
+            dist.broadcast(torch.from_numpy(np.ascontiguousarray(arr)), src=0, group=self._ctl)
+
+    def follow(self) -> None:
+        """Step loop of a non-driver rank: receive plan, run the shard, join the collectives."""
+        keys = ["num_seqs", "num_prefill", "num_decode", "total_tokens", "total_logits", "max_q_len", "max_kv_len",
+                "max_blocks", "input_ids", "positions", "slot_mapping", "seq_of_token", "cu_q", "kv_lens", "q_starts",
+                "logits_idx", "block_tables", "total_words"]
+        hdr = torch.zeros(64, dtype=torch.int32)
+        while True:
+            dist.broadcast(hdr, src=0, group=self._ctl)
+            h = hdr.numpy()
+            if h[0] == 2:
+                return
+            layout = {k: int(h[1 + i]) for i, k in enumerate(keys)}
+            n = layout["total_words"]
+            dist.broadcast(self.runner.staging.host[:n], src=0, group=self._ctl)
+            nso, nsi, nbc = int(h[31]), int(h[32]), int(h[33])
+            so = si = bc = np.zeros((0, 2), dtype=np.int32)
+            if nso + nsi + nbc:
+                arr = torch.zeros(nso + nsi + nbc, 2, dtype=torch.int32)
+                dist.broadcast(arr, src=0, group=self._ctl)
+                a = arr.numpy()
+                so, si, bc = a[:nso], a[nso:nso + nsi], a[nso + nsi:]
+            self.runner.apply_block_ops(so, si, bc)
+            meta = self.runner.upload(layout)
+            hidden = self.runner.forward(meta)
+            self.runner.sample(hidden, meta, None, bool(h[30]))
+
+    def shutdown_followers(self) -> None:
+        if self.tp.size > 1 and self.is_driver and self._ctl is not None:
+            self._broadcast_plan(None, None, True, stop=True)
+
+    # ---- loops ----------------------------------------------------------------------------------------------
+    def run_until_done(self, max_steps: Optional[int] = None) -> int:
+        steps = 0
+        while self.has_unfinished():
+            self.step()
+            steps += 1
+            if max_steps is not None and steps >= max_steps:
+                break
+        return steps
+
+    def start(self) -> None:
+        """Background step loop (serving mode)."""
+        if self._loop_thread is not None:
+            return
+        self._stop.clear()
+
+        def loop():
+            while not self._stop.is_set():
+                if self.has_unfinished():
+                    try:
+                        self.step()
+                    except Exception as ex:  # fail in-flight requests, keep serving
+                        self._fail_all(ex)
+                else:
+                    self._wake.wait(0.05)
+                    self._wake.clear()
+
+        self._loop_thread = threading.Thread(target=loop, name="ksana-step-loop", daemon=True)
+        self._loop_thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        self._wake.set()
+        if self._loop_thread is not None:
+            self._loop_thread.join(timeout=10)
+            self._loop_thread = None
+        self.shutdown_followers()
+
+    def _fail_all(self, ex: Exception) -> None:
+        with self.lock:
+            for req in list(self.requests.values()):
+                req.error = EngineError(_host.FINISH_ERROR, f"engine step failed: {ex}")
+                for s in req.seqs:
+                    if not s.finished:
+                        self.sched.finish(s.seq_id, _host.FINISH_ERROR)
+                        self.seq_owner.pop(s.seq_id, None)
+                        self.sched.forget(s.seq_id)
+                        s.finished, s.finish_reason = True, "error"
+                req.finished = True
+                req.notify()
+            self.requests.clear()
+
+    # ---- convenience ------------------------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[Sequence[SamplingParams]] = None
+                 ) -> List[Request]:
+        """Synchronous batch generation (offline use, tests, benchmarks)."""
+        if params is None:
+            params = [SamplingParams() for _ in prompts]
+        elif isinstance(params, SamplingParams):
+            params = [params for _ in prompts]
+        reqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        if self._loop_thread is None:
+            self.run_until_done()
+        else:
+            for r in reqs:
+                v = -1
+                while not r.finished:
+                    v = r.wait(v, 1.0)
+        return reqs

@@ -1,0 +1,102 @@
+"""Executes one scheduled step on this rank's device.
+
+Owns the model, the per-layer KV block pools, the host swap pool and the step staging buffer. The
+reference splits this between LlmRuntime::Step / Worker threads / CommonModel::Forward / LmHead
+(src/ksana_llm/runtime/llm_runtime.cpp:76-145, 290-338; models/common/common_model.cpp:424-639); with
+one process per GPU it collapses into a single object per rank.
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..models.transformer import TransformerModel
+from .sampler import SampleOutput, SampleRow, Sampler
+from .step_input import StepInput, StepStaging
+
+
+class ModelRunner:
+    def __init__(self, model: TransformerModel, num_blocks: int, block_size: int, num_host_blocks: int = 0,
+                 max_step_tokens: int = 4096, max_batch_size: int = 128, max_blocks_per_seq: int = 128,
+                 kv_dtype: Optional[torch.dtype] = None, seed: int = 0):
+        self.model = model
+        self.device = model.device
+        self.block_size = block_size
+        self.num_blocks = num_blocks
+        self.kv_caches = model.allocate_kv_cache(num_blocks, block_size, kv_dtype)
+        self.host_caches = None
+        if num_host_blocks > 0:
+            pin = self.device.type == "cuda"
+            self.host_caches = [torch.empty((num_host_blocks,) + tuple(c.shape[1:]), dtype=c.dtype, pin_memory=pin)
+                                for c in self.kv_caches]
+        self.max_blocks_per_seq = max_blocks_per_seq
+        words = 8 * (max_step_tokens + 64) + 8 * (max_batch_size + 64) + max_batch_size * (max_blocks_per_seq + 32) + 4096
+        self.staging = StepStaging(words, self.device)
+        self.sampler = Sampler(model.cfg.vocab_size, self.device, seed)
+        self.copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.last_hidden: Optional[torch.Tensor] = None
+
+    # ---- block movement -------------------------------------------------------------------------------
+    def apply_block_ops(self, swap_out: np.ndarray, swap_in: np.ndarray, copies: np.ndarray) -> None:
+        """Swap-out (device->host) must land before the step overwrites the freed blocks, swap-in and
+        fork copies before attention reads them: all are issued on the compute stream ahead of the forward."""
+        if len(swap_out):
+            src = torch.from_numpy(np.ascontiguousarray(swap_out[:, 0])).long()
+            dst = torch.from_numpy(np.ascontiguousarray(swap_out[:, 1])).long()
+            for dev, host in zip(self.kv_caches, self.host_caches):
+                host[dst] = dev[src.to(self.device)].to("cpu")
+        if len(swap_in):
+            src = torch.from_numpy(np.ascontiguousarray(swap_in[:, 0])).long()
+            dst = torch.from_numpy(np.ascontiguousarray(swap_in[:, 1])).long().to(self.device)
+            for dev, host in zip(self.kv_caches, self.host_caches):
+                dev[dst] = host[src].to(self.device, non_blocking=True)
+        if len(copies):
+            src = torch.from_numpy(np.ascontiguousarray(copies[:, 0])).long().to(self.device)
+            dst = torch.from_numpy(np.ascontiguousarray(copies[:, 1])).long().to(self.device)
+            for dev in self.kv_caches:
+                dev[dst] = dev[src]
+
+    # ---- forward ---------------------------------------------------------------------------------------
+    def upload(self, layout: Dict[str, int]) -> StepInput:
+        meta = self.staging.upload(layout)
+        self.h2d_bytes += meta.h2d_bytes
+        return meta
+
+    @torch.inference_mode()
+    def forward(self, meta: StepInput, refit=None) -> torch.Tensor:
+        hidden = self.model.forward(meta, self.kv_caches, refit)
+        self.last_hidden = hidden
+        return hidden
+
+    @torch.inference_mode()
+    def sample(self, hidden: torch.Tensor, meta: StepInput, rows: Optional[Sequence[SampleRow]],
+               greedy: Optional[bool] = None) -> SampleOutput:
+        """rows is None on ranks that do not own the sampler: they still join the collectives of the
+        path (greedy pair exchange, or full logits gather) chosen by the driving rank via ``greedy``."""
+        if meta.total_logits == 0:
+            return SampleOutput(tokens=[])
+        if greedy is None:
+            greedy = rows is None or Sampler.all_greedy(rows)
+        if greedy:
+            toks = self.model.greedy_tokens(hidden, meta.logits_idx)
+            if rows is None:
+                return SampleOutput(tokens=[])
+            host = toks.to("cpu", non_blocking=False)
+            self.d2h_bytes += host.numel() * host.element_size()
+            n = len(rows)
+            return SampleOutput(tokens=host.tolist(), logprobs=[None] * n, chosen_logprob=[None] * n)
+        logits = self.model.compute_logits(hidden, meta.logits_idx)
+        if rows is None:
+            return SampleOutput(tokens=[])
+        out = self.sampler.sample(logits, rows)
+        self.d2h_bytes += 4 * len(out.tokens)
+        return out
+
+    @torch.inference_mode()
+    def logits(self, hidden: torch.Tensor, meta: StepInput) -> torch.Tensor:
+        return self.model.compute_logits(hidden, meta.logits_idx)

@@ -1,0 +1,203 @@
+"""Building blocks shared by every architecture: (quantised) linear holders, attention flavours
+(MHA/GQA with RoPE / ALiBi / learned positions, MLA with weight absorption), FFN flavours (gated,
+plain, MoE with shared experts) over the paged KV cache.
+
+Reference counterparts: src/ksana_llm/modules/basic/linear.cpp:44, modules/attention/
+common_attention.cpp:33-75, multihead_latent_attention.cpp:155-456, modules/ffn/two_layered_ffn.cpp:22-118,
+layers/nvidia/moe_layer.cpp:208-377.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops
+from ..config.model_config import ModelConfig
+from ..ops import reference as ref
+from ..parallel.comm import TPGroup
+
+
+class LinearW:
+    """y = x @ W^T (+ b). W is stored [N, K] (K contiguous), which is exactly the K-major B operand the
+    tcgen05 kernels want. Quantised variants keep the checkpoint's format:
+    fp8 block-scaled (``weight`` e4m3 + ``weight_scale_inv`` fp32 per 128x128) and int4 group-quantised
+    (``qweight`` packed + ``scales`` + ``zeros``)."""
+
+    def __init__(self, weights: Dict[str, torch.Tensor], prefix: str):
+        self.prefix = prefix
+        self.weight = weights.get(prefix + ".weight")
+        self.bias = weights.get(prefix + ".bias")
+        self.scale_inv = weights.get(prefix + ".weight_scale_inv")
+        self.qweight = weights.get(prefix + ".qweight")
+        self.scales = weights.get(prefix + ".scales")
+        self.zeros = weights.get(prefix + ".zeros")
+        self.group = 128
+        if self.qweight is not None:
+            self.kind = "int4"
+            self.group = self.qweight.shape[1] * 8 // self.scales.shape[1]
+        elif self.scale_inv is not None:
+            self.kind = "fp8_block"
+        elif self.weight is not None:
+            self.kind = "dense"
+        else:
+            raise KeyError(f"missing weight for {prefix}")
+
+    @property
+    def out_features(self) -> int:
+        return (self.qweight if self.kind == "int4" else self.weight).shape[0]
+
+    @property
+    def in_features(self) -> int:
+        return self.qweight.shape[1] * 8 if self.kind == "int4" else self.weight.shape[1]
+
+    def __call__(self, x: torch.Tensor, add_bias: bool = True) -> torch.Tensor:
+        b = self.bias if add_bias else None
+        if self.kind == "dense":
+            return ops.linear(x, self.weight, b)
+        if self.kind == "fp8_block":
+            return ops.linear_fp8_block(x, self.weight, self.scale_inv, b)
+        return ops.linear_int4(x, self.qweight, self.scales, self.zeros, b, self.group)
+
+
+class Attention:
+    """MHA / GQA over the paged cache. Heads are sharded over the TP group; o_proj is row-parallel."""
+
+    def __init__(self, cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str, layer_idx: int, tp: TPGroup,
+                 rope_cache: Optional[torch.Tensor]):
+        self.cfg = cfg
+        self.tp = tp
+        self.layer_idx = layer_idx
+        self.h = cfg.num_heads // tp.size
+        self.hk = max(cfg.num_kv_heads // tp.size, 1)
+        self.d = cfg.head_dim
+        self.qkv = LinearW(w, prefix + ".query_key_value")
+        self.o_proj = LinearW(w, prefix + ".o_proj")
+        self.q_norm = w.get(prefix + ".query_layernorm.weight")
+        self.k_norm = w.get(prefix + ".key_layernorm.weight")
+        self.rope_cache = rope_cache
+        self.scale = 1.0 / math.sqrt(self.d)
+        self.alibi = None
+        if cfg.position_encoding == "alibi":
+            full = ref.alibi_slopes(cfg.num_heads)
+            self.alibi = full[tp.rank * self.h:(tp.rank + 1) * self.h].to(self.o_proj.weight.device)
+
+    def core(self, h: torch.Tensor, meta, kv_cache: torch.Tensor) -> torch.Tensor:
+        T = h.shape[0]
+        qkv = self.qkv(h)
+        nq, nk = self.h * self.d, self.hk * self.d
+        q = qkv[:, :nq].view(T, self.h, self.d)
+        k = qkv[:, nq:nq + nk].view(T, self.hk, self.d)
+        v = qkv[:, nq + nk:].view(T, self.hk, self.d)
+        ops.rope_qknorm_cache(q, k, v, meta.positions, self.rope_cache, meta.slot_mapping, kv_cache,
+                              self.q_norm, self.k_norm, self.cfg.rms_norm_eps, self.cfg.rope_interleaved,
+                              self.cfg.rotary_dim)
+        o = ops.paged_attention(q, kv_cache, meta, self.scale, self.alibi)
+        return o.reshape(T, nq)
+
+
+class MLAttention:
+    """Multi-head latent attention with absorbed up-projections: the cache holds one
+    ``kv_lora_rank + rope`` vector per token, scores and outputs are computed in latent space."""
+
+    def __init__(self, cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str, layer_idx: int, tp: TPGroup,
+                 rope_cache: torch.Tensor):
+        self.cfg = cfg
+        self.tp = tp
+        self.h = cfg.num_heads // tp.size
+        self.r, self.dr, self.dn, self.dv = cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.qk_nope_head_dim, cfg.v_head_dim
+        self.q_lora = cfg.q_lora_rank
+        self.fused_a = LinearW(w, prefix + ".fused_lora_a_proj")  # [q_lora + r + dr, H] (or [r + dr, H])
+        self.q_a_norm = w.get(prefix + ".q_a_layernorm.weight")
+        self.kv_a_norm = w[prefix + ".kv_a_layernorm.weight"]
+        self.q_b = LinearW(w, prefix + (".q_b_nope_rope_proj" if self.q_lora else ".q_proj"))
+        self.w_uk = w[prefix + ".w_uk_t"]  # [h, dn, r]
+        self.w_uv = w[prefix + ".w_uv"]    # [h, r, dv]
+        self.o_proj = LinearW(w, prefix + ".o_proj")
+        self.rope_cache = rope_cache
+        self.scale = 1.0 / math.sqrt(self.dn + self.dr)
+        rs = cfg.rope_scaling
+        if rs.type == "yarn" and rs.mscale_all_dim:
+            m = ref.yarn_mscale(rs.factor, rs.mscale_all_dim)
+            self.scale *= m * m
+
+    def core(self, h: torch.Tensor, meta, cache: torch.Tensor) -> torch.Tensor:
+        T = h.shape[0]
+        eps = self.cfg.rms_norm_eps
+        a = self.fused_a(h)
+        if self.q_lora:
+            q_a = ops.rms_norm(a[:, :self.q_lora].contiguous(), self.q_a_norm, eps)
+            q = self.q_b(q_a)
+            rest = a[:, self.q_lora:]
+        else:
+            q = self.q_b(h)
+            rest = a
+        latent = ops.rms_norm(rest[:, :self.r].contiguous(), self.kv_a_norm, eps)
+        k_rope = rest[:, self.r:].contiguous()
+        q = q.view(T, self.h, self.dn + self.dr)
+        q_nope, q_rope = q[..., :self.dn], q[..., self.dn:].contiguous()
+        cs = self.rope_cache[meta.positions.long()]
+        cos, sin = cs[:, :self.dr // 2], cs[:, self.dr // 2:]
+        q_rope = ref.apply_rope(q_rope, cos, sin, True, self.dr)
+        k_rope = ref.apply_rope(k_rope.view(T, 1, self.dr), cos, sin, True, self.dr).view(T, self.dr)
+        ops.mla_cache_append(latent, k_rope, meta.slot_mapping, cache)
+        q_lat = torch.einsum("thd,hdr->thr", q_nope.to(self.w_uk.dtype), self.w_uk)
+        o_lat = ops.mla_paged_attention(q_lat.contiguous(), q_rope, cache, meta, self.scale)
+        o = torch.einsum("thr,hrd->thd", o_lat.to(self.w_uv.dtype), self.w_uv)
+        return o.reshape(T, self.h * self.dv)
+
+
+class DenseFFN:
+    """Gated (SwiGLU / GeGLU) or plain two-layer FFN; up projections column-parallel, down row-parallel."""
+
+    def __init__(self, cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str, tp: TPGroup):
+        self.cfg = cfg
+        self.tp = tp
+        self.gated = cfg.gated_mlp
+        self.up = LinearW(w, prefix + (".gate_up_proj" if self.gated else ".up_proj"))
+        self.down = LinearW(w, prefix + ".down_proj")
+        self.act = cfg.hidden_act
+
+    def core(self, h: torch.Tensor) -> torch.Tensor:
+        u = self.up(h)
+        if self.gated:
+            if self.act in ("silu", "swish"):
+                return ops.silu_and_mul(u)
+            return ref.gelu_and_mul(u)
+        return ops.activation(u, self.act)
+
+
+class MoEFFN:
+    """Routed experts (+ optional shared expert). Experts are sharded over the expert-parallel group
+    (here: the TP group); every rank sees all tokens, computes its local experts and the partial sums are
+    combined by the all-reduce that follows (or by the fused dispatch/combine kernel when attached)."""
+
+    def __init__(self, cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str, tp: TPGroup):
+        self.cfg = cfg
+        self.tp = tp
+        self.gate_w = w[prefix + ".gate.weight"]
+        self.bias = w.get(prefix + ".gate.e_score_correction_bias")
+        self.w_gate_up = w[prefix + ".experts.up_gate_proj.weight"]  # [E_local, 2I, H]
+        self.w_down = w[prefix + ".experts.down_proj.weight"]        # [E_local, H, I]
+        self.e_local = self.w_gate_up.shape[0]
+        self.expert_offset = tp.rank * self.e_local if self.e_local < cfg.num_experts else 0
+        self.shared = None
+        if cfg.num_shared_experts:
+            self.shared = DenseFFN(cfg, w, prefix + ".shared_expert", tp)
+            self.shared_gate = w.get(prefix + ".shared_expert_gate.weight")
+
+    def partial(self, h: torch.Tensor) -> torch.Tensor:
+        """Per-rank partial sum of the block output (needs a cross-rank sum when size > 1)."""
+        c = self.cfg
+        logits = ops.linear(h.float() if self.gate_w.dtype == torch.float32 else h, self.gate_w)
+        ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
+                                 c.topk_group, c.routed_scaling_factor, self.bias)
+        y = ops.moe_experts(h, ids, wts, self.w_gate_up, self.w_down, self.expert_offset)
+        if self.shared is not None:
+            s = self.shared.down(self.shared.core(h), add_bias=self.tp.rank == 0)
+            if self.shared_gate is not None:
+                g = torch.sigmoid(ops.linear(h, self.shared_gate).float()).to(s.dtype)
+                s = s * g
+            y = y + s
+        return y

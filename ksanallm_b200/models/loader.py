@@ -1,0 +1,576 @@
+"""Checkpoint -> per-rank canonical weights.
+
+Input: an iterator of ``(hf_name, tensor)`` pairs from ``*.safetensors`` (mmap), ``pytorch_model*.bin``
+or a synthetic generator. Output: a dict with the canonical internal names
+(``model.layers.N.self_attn.query_key_value.weight`` fused per rank, ``...mlp.gate_up_proj.weight``,
+``...mlp.experts.up_gate_proj.weight`` stacked, MLA ``fused_lora_a_proj / w_uk_t / w_uv`` ...),
+tensor-parallel slices taken, expert-parallel experts selected and optional load-time quantisation
+(bf16 -> fp8 128x128 block-scaled, bf16 -> int4 group-128) applied.
+
+Reference: model_weight_loader.cpp:25-120, llama_model_weight_loader.cpp:91-280 (TP slicing, fused qkv),
+new_deepseek_v3_weight_loader.cpp:154-186, 268-320, 383-497 (fp8 scale_inv, lora-a fusion, kv_b split for
+absorption, expert stacking), python/weight_map/*.json (regex renames to Llama names).
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+import re
+from collections import defaultdict
+from typing import Dict, Iterable, Iterator, List, Optional, Tuple
+
+import torch
+
+from ..config.model_config import ModelConfig
+from ..ops import reference as ref
+
+# ---------------------------------------------------------------------------------------------------
+# name normalisation: architecture-specific HF names -> Llama-style names
+# ---------------------------------------------------------------------------------------------------
+
+_RENAMES: Dict[str, List[Tuple[str, str]]] = {
+    "qwen3": [(r"\.q_norm\.", ".query_layernorm."), (r"\.k_norm\.", ".key_layernorm.")],
+    "qwen3_moe": [(r"\.q_norm\.", ".query_layernorm."), (r"\.k_norm\.", ".key_layernorm.")],
+    "mixtral": [(r"\.block_sparse_moe\.", ".mlp."), (r"\.w1\.", ".gate_proj."), (r"\.w2\.", ".down_proj."),
+                (r"\.w3\.", ".up_proj.")],
+    "deepseek_v2": [(r"\.shared_experts\.", ".shared_expert.")],
+    "deepseek_v3": [(r"\.shared_experts\.", ".shared_expert.")],
+    "kimi_k2": [(r"\.shared_experts\.", ".shared_expert.")],
+    "qwen2_moe": [],
+    "internlm2": [(r"^model\.tok_embeddings\.", "model.embed_tokens."), (r"^output\.", "lm_head."),
+                  (r"\.attention\.wqkv\.", ".self_attn.wqkv."), (r"\.attention\.wo\.", ".self_attn.o_proj."),
+                  (r"\.feed_forward\.w1\.", ".mlp.gate_proj."), (r"\.feed_forward\.w3\.", ".mlp.up_proj."),
+                  (r"\.feed_forward\.w2\.", ".mlp.down_proj."), (r"\.attention_norm\.", ".input_layernorm."),
+                  (r"\.ffn_norm\.", ".post_attention_layernorm.")],
+    "baichuan": [(r"\.W_pack\.", ".wpack.")],
+    "chatglm": [(r"^transformer\.embedding\.word_embeddings\.", "model.embed_tokens."),
+                (r"^transformer\.encoder\.layers\.", "model.layers."),
+                (r"^transformer\.encoder\.final_layernorm\.", "model.norm."),
+                (r"^transformer\.output_layer\.", "lm_head."),
+                (r"\.self_attention\.query_key_value\.", ".self_attn.wpack."),
+                (r"\.self_attention\.dense\.", ".self_attn.o_proj."),
+                (r"\.mlp\.dense_h_to_4h\.", ".mlp.gate_up_proj."), (r"\.mlp\.dense_4h_to_h\.", ".mlp.down_proj.")],
+    "gpt2": [(r"^(transformer\.)?wte\.", "model.embed_tokens."), (r"^(transformer\.)?wpe\.", "model.embed_positions."),
+             (r"^(transformer\.)?h\.", "model.layers."), (r"^(transformer\.)?ln_f\.", "model.norm."),
+             (r"\.ln_1\.", ".input_layernorm."), (r"\.ln_2\.", ".post_attention_layernorm."),
+             (r"\.attn\.c_attn\.", ".self_attn.wpack_t."), (r"\.attn\.c_proj\.", ".self_attn.o_proj_t."),
+             (r"\.mlp\.c_fc\.", ".mlp.up_proj_t."), (r"\.mlp\.c_proj\.", ".mlp.down_proj_t.")],
+    "hunyuan": [(r"\.mlp\.shared_mlp\.", ".mlp.shared_expert."), (r"\.query_layernorm\.", ".query_layernorm."),
+                (r"\.mlp\.gate\.wg\.", ".mlp.gate.")],
+}
+_RENAMES["qwen2_vl"] = []
+_RENAMES["internvl_chat"] = [(r"^language_model\.", "")] + _RENAMES["internlm2"]
+_RENAMES["internlmxcomposer2"] = _RENAMES["internlm2"]
+_RENAMES["llama4"] = [(r"^language_model\.", ""), (r"\.feed_forward\.", ".mlp."), (r"\.router\.", ".gate.")]
+
+
+def load_weight_map(model_dir: str, model_type: str) -> List[Tuple[str, str]]:
+    """Optional ``<model_type>_weight_map.json`` in the model directory: {regex: replacement}."""
+    path = os.path.join(model_dir or "", f"{model_type}_weight_map.json")
+    if model_dir and os.path.isfile(path):
+        with open(path, "r", encoding="utf-8") as f:
+            return [(k, v) for k, v in json.load(f).items()]
+    return []
+
+
+def normalise_name(name: str, rules: List[Tuple[str, str]]) -> str:
+    for pat, rep in rules:
+        name = re.sub(pat, rep, name)
+    return name
+
+
+# ---------------------------------------------------------------------------------------------------
+# checkpoint readers
+# ---------------------------------------------------------------------------------------------------
+
+def iter_checkpoint(model_dir: str) -> Iterator[Tuple[str, torch.Tensor]]:
+    st = sorted(glob.glob(os.path.join(model_dir, "*.safetensors")))
+    if st:
+        from safetensors import safe_open
+        for path in st:
+            with safe_open(path, framework="pt", device="cpu") as f:
+                for k in f.keys():
+                    yield k, f.get_tensor(k)
+        return
+    bins = sorted(glob.glob(os.path.join(model_dir, "pytorch_model*.bin"))) or \
+        sorted(glob.glob(os.path.join(model_dir, "*.bin"))) or sorted(glob.glob(os.path.join(model_dir, "*.pt")))
+    if bins:
+        for path in bins:
+            sd = torch.load(path, map_location="cpu", weights_only=True, mmap=True)
+            for k, v in sd.items():
+                yield k, v
+        return
+    ggufs = sorted(glob.glob(os.path.join(model_dir, "*.gguf")))
+    if ggufs:
+        from .gguf_reader import iter_gguf
+        for path in ggufs:
+            yield from iter_gguf(path)
+        return
+    raise FileNotFoundError(f"no *.safetensors / *.bin / *.gguf under {model_dir}")
+
+
+def synthetic_checkpoint(cfg: ModelConfig, seed: int = 0, std: float = 0.02, device="cpu",
+                         dtype: Optional[torch.dtype] = None) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Random-init N(0, std) weights under plain HF Llama-style names (norm weights = 1). Every rank
+    that iterates with the same seed sees identical tensors, so TP slices are consistent."""
+    dtype = dtype or getattr(torch, cfg.torch_dtype, torch.bfloat16)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+
+    def rnd(*shape):
+        return (torch.randn(*shape, generator=gen, device=device, dtype=torch.float32) * std).to(dtype)
+
+    def ones(n):
+        return torch.ones(n, device=device, dtype=dtype)
+
+    H, d = cfg.hidden_size, cfg.head_dim
+    yield "model.embed_tokens.weight", rnd(cfg.vocab_size, H)
+    n_total = cfg.num_layers + cfg.num_nextn_predict_layers
+    for i in range(n_total):
+        p = f"model.layers.{i}"
+        yield p + ".input_layernorm.weight", ones(H)
+        yield p + ".post_attention_layernorm.weight", ones(H)
+        a = p + ".self_attn"
+        if cfg.use_mla:
+            if cfg.q_lora_rank:
+                yield a + ".q_a_proj.weight", rnd(cfg.q_lora_rank, H)
+                yield a + ".q_a_layernorm.weight", ones(cfg.q_lora_rank)
+                yield a + ".q_b_proj.weight", rnd(cfg.num_heads * cfg.q_head_dim, cfg.q_lora_rank)
+            else:
+                yield a + ".q_proj.weight", rnd(cfg.num_heads * cfg.q_head_dim, H)
+            yield a + ".kv_a_proj_with_mqa.weight", rnd(cfg.kv_lora_rank + cfg.qk_rope_head_dim, H)
+            yield a + ".kv_a_layernorm.weight", ones(cfg.kv_lora_rank)
+            yield a + ".kv_b_proj.weight", rnd(cfg.num_heads * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank)
+            yield a + ".o_proj.weight", rnd(H, cfg.num_heads * cfg.v_head_dim)
+        else:
+            yield a + ".q_proj.weight", rnd(cfg.num_heads * d, H)
+            yield a + ".k_proj.weight", rnd(cfg.num_kv_heads * d, H)
+            yield a + ".v_proj.weight", rnd(cfg.num_kv_heads * d, H)
+            if cfg.qkv_bias:
+                yield a + ".q_proj.bias", rnd(cfg.num_heads * d)
+                yield a + ".k_proj.bias", rnd(cfg.num_kv_heads * d)
+                yield a + ".v_proj.bias", rnd(cfg.num_kv_heads * d)
+            if cfg.qk_norm:
+                yield a + ".query_layernorm.weight", ones(d)
+                yield a + ".key_layernorm.weight", ones(d)
+            yield a + ".o_proj.weight", rnd(H, cfg.num_heads * d)
+        m = p + ".mlp"
+        if cfg.is_moe_layer(i) or (cfg.is_moe and i >= cfg.num_layers):
+            I = cfg.moe_intermediate_size
+            yield m + ".gate.weight", rnd(cfg.num_experts, H).float() if cfg.scoring_func == "sigmoid" else rnd(cfg.num_experts, H)
+            if cfg.topk_method == "noaux_tc":
+                yield m + ".gate.e_score_correction_bias", torch.zeros(cfg.num_experts, device=device, dtype=torch.float32)
+            for e in range(cfg.num_experts):
+                yield f"{m}.experts.{e}.gate_proj.weight", rnd(I, H)
+                yield f"{m}.experts.{e}.up_proj.weight", rnd(I, H)
+                yield f"{m}.experts.{e}.down_proj.weight", rnd(H, I)
+            if cfg.num_shared_experts:
+                S = cfg.shared_expert_intermediate_size
+                yield m + ".shared_expert.gate_proj.weight", rnd(S, H)
+                yield m + ".shared_expert.up_proj.weight", rnd(S, H)
+                yield m + ".shared_expert.down_proj.weight", rnd(H, S)
+                if cfg.shared_expert_gate:
+                    yield m + ".shared_expert_gate.weight", rnd(1, H)
+        else:
+            I = cfg.intermediate_size
+            if cfg.gated_mlp:
+                yield m + ".gate_proj.weight", rnd(I, H)
+            yield m + ".up_proj.weight", rnd(I, H)
+            yield m + ".down_proj.weight", rnd(H, I)
+        if i >= cfg.num_layers:
+            yield p + ".enorm.weight", ones(H)
+            yield p + ".hnorm.weight", ones(H)
+            yield p + ".eh_proj.weight", rnd(H, 2 * H)
+            yield p + ".shared_head.norm.weight", ones(H)
+    yield "model.norm.weight", ones(H)
+    if not cfg.tie_word_embeddings:
+        yield "lm_head.weight", rnd(cfg.vocab_size, H)
+
+
+# ---------------------------------------------------------------------------------------------------
+# sharding helpers
+# ---------------------------------------------------------------------------------------------------
+
+def _rows(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    n = t.shape[0] // size
+    return t[rank * n:(rank + 1) * n]
+
+
+def _cols(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    n = t.shape[1] // size
+    return t[:, rank * n:(rank + 1) * n]
+
+
+def _kv_rows(t: torch.Tensor, rank: int, size: int, num_kv_heads: int, d: int) -> torch.Tensor:
+    """KV heads are split across ranks; with fewer KV heads than ranks each head is replicated."""
+    if num_kv_heads >= size:
+        return _rows(t, rank, size)
+    rep = size // num_kv_heads
+    hidx = rank // rep
+    return t[hidx * d:(hidx + 1) * d]
+
+
+class WeightLoader:
+    def __init__(self, cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, device="cpu",
+                 dtype: Optional[torch.dtype] = None, quantize: Optional[str] = None,
+                 ep_rank: Optional[int] = None, ep_size: Optional[int] = None, model_dir: str = "",
+                 layer_range: Optional[range] = None):
+        self.cfg = cfg
+        self.rank, self.size = tp_rank, tp_size
+        self.ep_rank = tp_rank if ep_rank is None else ep_rank
+        self.ep_size = tp_size if ep_size is None else ep_size
+        self.device = torch.device(device)
+        self.dtype = dtype or getattr(torch, cfg.torch_dtype, torch.bfloat16)
+        self.quantize = quantize  # None | "fp8_block" | "int4"
+        self.rules = load_weight_map(model_dir, cfg.model_type) + _RENAMES.get(cfg.model_type, [])
+        self.layer_range = layer_range
+        self.out: Dict[str, torch.Tensor] = {}
+        self._pending: Dict[str, Dict[str, torch.Tensor]] = defaultdict(dict)
+        self._experts: Dict[str, Dict[Tuple[int, str], torch.Tensor]] = defaultdict(dict)
+
+    # ---- placement --------------------------------------------------------------------------------
+    def _own(self, t: torch.Tensor) -> torch.Tensor:
+        """Device-resident, contiguous and not a view into a larger storage (a TP slice must not keep
+        the full tensor alive)."""
+        t = t.to(self.device).contiguous()
+        if t.untyped_storage().nbytes() > t.numel() * t.element_size():
+            t = t.clone()
+        return t
+
+    def _put(self, name: str, t: torch.Tensor, keep_dtype: bool = False) -> None:
+        if not keep_dtype and t.is_floating_point() and t.dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
+            t = t.to(self.dtype)
+        self.out[name] = self._own(t)
+
+    def _put_linear(self, prefix: str, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None) -> None:
+        """Stores a linear weight, quantising at load time when requested. Norms, embeddings, the router
+        and lm_head stay in the model dtype."""
+        if scale_inv is not None:
+            self.out[prefix + ".weight"] = self._own(w)
+            self.out[prefix + ".weight_scale_inv"] = self._own(scale_inv.float())
+            return
+        if self.quantize == "fp8_block" and w.dim() == 2 and w.shape[1] % 128 == 0:
+            q, s = ref.quant_fp8_block_weight(w.to(self.device).float())
+            self.out[prefix + ".weight"] = q.contiguous()
+            self.out[prefix + ".weight_scale_inv"] = s.contiguous()
+            return
+        if self.quantize == "int4" and w.dim() == 2 and w.shape[1] % 128 == 0:
+            p, s, z = ref.quant_int4_group(w.to(self.device).float())
+            self.out[prefix + ".qweight"] = p.contiguous()
+            self.out[prefix + ".scales"] = s.to(self.dtype).contiguous()
+            self.out[prefix + ".zeros"] = z.to(self.dtype).contiguous()
+            return
+        self._put(prefix + ".weight", w)
+
+    def _layer_of(self, name: str) -> Optional[int]:
+        m = re.match(r"model\.layers\.(\d+)\.", name)
+        return int(m.group(1)) if m else None
+
+    # ---- main entry -------------------------------------------------------------------------------
+    def load(self, tensors: Iterable[Tuple[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
+        for raw_name, t in tensors:
+            name = normalise_name(raw_name, self.rules)
+            li = self._layer_of(name)
+            if li is not None and self.layer_range is not None and li not in self.layer_range \
+                    and li < self.cfg.num_layers:
+                continue
+            self._consume(name, t)
+        self._finish()
+        return self.out
+
+    def _consume(self, name: str, t: torch.Tensor) -> None:
+        cfg, r, n = self.cfg, self.rank, self.size
+        d = cfg.head_dim
+        if name.endswith("rotary_emb.inv_freq"):
+            return
+        if name == "model.embed_tokens.weight":
+            self._put(name, t)  # replicated: no collective on the embedding path
+            return
+        if name == "model.embed_positions.weight":
+            self._put(name, t)
+            return
+        if name == "lm_head.weight":
+            V = t.shape[0]
+            if n > 1:
+                pad = (-V) % n
+                if pad:
+                    t = torch.cat((t, torch.zeros(pad, t.shape[1], dtype=t.dtype, device=t.device)), 0)
+                t = _rows(t, r, n)
+            self._put(name, t)
+            return
+        if name.startswith("model.norm.") or "layernorm" in name or name.endswith("norm.weight") \
+                or name.endswith("norm.bias") or ".enorm." in name or ".hnorm." in name:
+            self._put(name, t)
+            return
+        m = re.match(r"(model\.layers\.\d+)\.(self_attn|mlp)\.(.*)$", name)
+        if not m:
+            mm = re.match(r"(model\.layers\.\d+)\.(eh_proj)\.(weight|weight_scale_inv)$", name)
+            if mm:
+                self._pending[mm.group(1) + ".eh_proj"][mm.group(3)] = t
+            else:
+                self._put(name, t)
+            return
+        layer, block, rest = m.groups()
+        key = f"{layer}.{block}"
+        # expert weights: experts.E.{gate,up,down}_proj.(weight|weight_scale_inv)
+        em = re.match(r"experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv)$", rest)
+        if em:
+            e = int(em.group(1))
+            per = max(cfg.num_experts // self.ep_size, 1)
+            if self.ep_size > 1 and not (self.ep_rank * per <= e < (self.ep_rank + 1) * per):
+                return
+            self._experts[key][(e, em.group(2) + "." + em.group(3))] = t
+            self._maybe_flush_experts(key)
+            return
+        self._pending[key][rest] = t
+        self._maybe_flush(key)
+
+    # ---- streaming: a block is assembled as soon as all of its parts have arrived ----------------------
+    @staticmethod
+    def _fp8(t: torch.Tensor) -> bool:
+        return t.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
+
+    def _have(self, p: Dict[str, torch.Tensor], stem: str, bias: bool = False) -> bool:
+        w = p.get(stem + ".weight")
+        if w is None:
+            return False
+        if self._fp8(w) and (stem + ".weight_scale_inv") not in p:
+            return False
+        if bias and (stem + ".bias") not in p:
+            return False
+        return True
+
+    def _maybe_flush(self, key: str) -> None:
+        cfg = self.cfg
+        p = self._pending[key]
+        if key.endswith(".self_attn"):
+            if cfg.use_mla:
+                ok = self._have(p, "kv_a_proj_with_mqa") and "kv_a_layernorm.weight" in p and \
+                    self._have(p, "kv_b_proj") and self._have(p, "o_proj")
+                if cfg.q_lora_rank:
+                    ok = ok and self._have(p, "q_a_proj") and "q_a_layernorm.weight" in p and self._have(p, "q_b_proj")
+                else:
+                    ok = ok and self._have(p, "q_proj")
+                if ok:
+                    self._finish_mla(key, self._pending.pop(key))
+                return
+            b = cfg.qkv_bias
+            qkv = (self._have(p, "q_proj", b) and self._have(p, "k_proj", b) and self._have(p, "v_proj", b)) or \
+                self._have(p, "wpack", b) or self._have(p, "wpack_t", b) or self._have(p, "wqkv", b)
+            o = self._have(p, "o_proj", cfg.o_bias) or self._have(p, "o_proj_t", cfg.o_bias)
+            nrm = (not cfg.qk_norm) or ("query_layernorm.weight" in p and "key_layernorm.weight" in p)
+            if qkv and o and nrm:
+                self._finish_attn(key, self._pending.pop(key))
+            return
+        if key.endswith(".mlp"):
+            li = self._layer_of(key + ".")
+            moe = cfg.is_moe_layer(li) or (cfg.is_moe and li >= cfg.num_layers)
+            b = cfg.mlp_bias
+
+            def ffn_ok(pre):
+                return (self._have(p, pre + "gate_proj") and self._have(p, pre + "up_proj") and
+                        self._have(p, pre + "down_proj")) or \
+                    (self._have(p, pre + "gate_up_proj") and self._have(p, pre + "down_proj")) or \
+                    (not cfg.gated_mlp and ((self._have(p, pre + "up_proj", b) and self._have(p, pre + "down_proj", b)) or
+                                            (self._have(p, pre + "up_proj_t", b) and self._have(p, pre + "down_proj_t", b))))
+            if moe:
+                ok = "gate.weight" in p
+                if cfg.topk_method == "noaux_tc":
+                    ok = ok and "gate.e_score_correction_bias" in p
+                if cfg.num_shared_experts:
+                    ok = ok and ffn_ok("shared_expert.")
+                    if cfg.shared_expert_gate:
+                        ok = ok and "shared_expert_gate.weight" in p
+            else:
+                ok = ffn_ok("")
+            if ok:
+                self._finish_mlp(key, self._pending.pop(key))
+
+    def _maybe_flush_experts(self, key: str) -> None:
+        ex = self._experts[key]
+        per = max(self.cfg.num_experts // max(self.ep_size, 1), 1) if self.ep_size > 1 else self.cfg.num_experts
+        first = next(iter(ex.values()))
+        want = per * 3 * (2 if any(self._fp8(t) for t in ex.values()) else 1)
+        if len(ex) >= want:
+            self._finish_experts(key, self._experts.pop(key))
+
+    # ---- assembling fused tensors --------------------------------------------------------------------
+    def _finish(self) -> None:
+        cfg, r, n = self.cfg, self.rank, self.size
+        d = cfg.head_dim
+        for key, parts in list(self._pending.items()):
+            if key.endswith(".eh_proj"):
+                self._put_linear(key, parts["weight"], parts.get("weight_scale_inv"))
+            elif key.endswith(".self_attn"):
+                if cfg.use_mla:
+                    self._finish_mla(key, parts)
+                else:
+                    self._finish_attn(key, parts)
+            else:
+                self._finish_mlp(key, parts)
+        for key, ex in list(self._experts.items()):
+            self._finish_experts(key, ex)
+        self._pending.clear()
+        self._experts.clear()
+
+    def _finish_attn(self, key: str, p: Dict[str, torch.Tensor]) -> None:
+        cfg, r, n = self.cfg, self.rank, self.size
+        d, hq, hk = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+        for suffix in ("weight", "bias", "weight_scale_inv"):
+            q = k = v = None
+            if f"q_proj.{suffix}" in p:
+                q, k, v = p[f"q_proj.{suffix}"], p[f"k_proj.{suffix}"], p[f"v_proj.{suffix}"]
+            elif f"wpack.{suffix}" in p:  # [q | k | v] stacked rows (Baichuan W_pack, ChatGLM)
+                w = p[f"wpack.{suffix}"]
+                q, k, v = w[:hq * d], w[hq * d:(hq + hk) * d], w[(hq + hk) * d:]
+            elif f"wpack_t.{suffix}" in p:  # GPT-2 Conv1D: [in, out]
+                w = p[f"wpack_t.{suffix}"]
+                w = w.t() if w.dim() == 2 else w
+                q, k, v = w[:hq * d], w[hq * d:(hq + hk) * d], w[(hq + hk) * d:]
+            elif f"wqkv.{suffix}" in p:  # InternLM2: per KV group [q*g | k | v]
+                w = p[f"wqkv.{suffix}"]
+                g = hq // hk
+                w = w.view(hk, g + 2, d, *w.shape[1:])
+                q = w[:, :g].reshape(hq * d, *w.shape[3:])
+                k = w[:, g].reshape(hk * d, *w.shape[3:])
+                v = w[:, g + 1].reshape(hk * d, *w.shape[3:])
+            if q is None:
+                continue
+            if suffix == "weight_scale_inv":
+                # block-scaled fp8 qkv: slice in units of 128 rows
+                qs, ks, vs = _rows(q, r, n), _kv_rows(k, r, n, hk, max(d // 128, 1)), _kv_rows(v, r, n, hk, max(d // 128, 1))
+                self.out[f"{key}.query_key_value.weight_scale_inv"] = torch.cat((qs, ks, vs), 0).float().to(self.device)
+                continue
+            fused = torch.cat((_rows(q, r, n), _kv_rows(k, r, n, hk, d), _kv_rows(v, r, n, hk, d)), 0)
+            if suffix == "bias":
+                self._put(f"{key}.query_key_value.bias", fused)
+            elif fused.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+                self.out[f"{key}.query_key_value.weight"] = fused.to(self.device).contiguous()
+            else:
+                self._put_linear(f"{key}.query_key_value", fused)
+        o_w = p.get("o_proj.weight")
+        if o_w is None and "o_proj_t.weight" in p:
+            o_w = p["o_proj_t.weight"].t()
+        if o_w is not None:
+            s = p.get("o_proj.weight_scale_inv")
+            self._put_linear(f"{key}.o_proj", _cols(o_w, r, n), None if s is None else _cols(s, r, n))
+        ob = p.get("o_proj.bias", p.get("o_proj_t.bias"))
+        if ob is not None:
+            self._put(f"{key}.o_proj.bias", ob)
+        for nm in ("query_layernorm.weight", "key_layernorm.weight"):
+            if nm in p:
+                self._put(f"{key}.{nm}", p[nm])
+
+    def _finish_mla(self, key: str, p: Dict[str, torch.Tensor]) -> None:
+        cfg, r, n = self.cfg, self.rank, self.size
+        h = cfg.num_heads
+        dn, dr, dv, rk = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+
+        def deq(nm):
+            w = p[nm + ".weight"]
+            s = p.get(nm + ".weight_scale_inv")
+            if s is not None:
+                w = ref.dequant_fp8_block_weight(w.to(self.device), s.to(self.device))
+            return w
+
+        kv_a = p["kv_a_proj_with_mqa.weight"]
+        kv_a_s = p.get("kv_a_proj_with_mqa.weight_scale_inv")
+        if cfg.q_lora_rank:
+            q_a, q_a_s = p["q_a_proj.weight"], p.get("q_a_proj.weight_scale_inv")
+            fused = torch.cat((q_a, kv_a), 0)
+            fs = None
+            if q_a_s is not None and kv_a_s is not None and q_a.shape[0] % 128 == 0:
+                fs = torch.cat((q_a_s, kv_a_s), 0)
+            elif q_a_s is not None:
+                fused = torch.cat((deq("q_a_proj"), deq("kv_a_proj_with_mqa")), 0)
+            self._put_linear(f"{key}.fused_lora_a_proj", fused, fs)
+            self._put(f"{key}.q_a_layernorm.weight", p["q_a_layernorm.weight"])
+            qb, qbs = p["q_b_proj.weight"], p.get("q_b_proj.weight_scale_inv")
+            self._put_linear(f"{key}.q_b_nope_rope_proj", _rows(qb, r, n), None if qbs is None else _rows(qbs, r, n))
+        else:
+            self._put_linear(f"{key}.fused_lora_a_proj", kv_a, kv_a_s)
+            qp, qps = p["q_proj.weight"], p.get("q_proj.weight_scale_inv")
+            self._put_linear(f"{key}.q_proj", _rows(qp, r, n), None if qps is None else _rows(qps, r, n))
+        self._put(f"{key}.kv_a_layernorm.weight", p["kv_a_layernorm.weight"])
+        # kv_b: [h * (dn + dv), rk] -> absorbed w_uk_t [h, dn, rk] and w_uv [h, rk, dv] (always dequantised)
+        kvb = deq("kv_b_proj").to(self.device).float().view(h, dn + dv, rk)
+        hl = h // n
+        kvb = kvb[r * hl:(r + 1) * hl]
+        self._put(f"{key}.w_uk_t", kvb[:, :dn, :].contiguous())
+        self._put(f"{key}.w_uv", kvb[:, dn:, :].transpose(1, 2).contiguous())
+        ow, ows = p["o_proj.weight"], p.get("o_proj.weight_scale_inv")
+        self._put_linear(f"{key}.o_proj", _cols(ow, r, n), None if ows is None else _cols(ows, r, n))
+
+    def _finish_mlp(self, key: str, p: Dict[str, torch.Tensor]) -> None:
+        cfg, r, n = self.cfg, self.rank, self.size
+        for pre in ("", "shared_expert."):
+            gate, up, down = p.get(pre + "gate_proj.weight"), p.get(pre + "up_proj.weight"), p.get(pre + "down_proj.weight")
+            if up is None and pre + "up_proj_t.weight" in p:
+                up, down = p[pre + "up_proj_t.weight"].t(), p[pre + "down_proj_t.weight"].t()
+            if pre + "gate_up_proj.weight" in p:  # already fused [gate | up] rows (ChatGLM, Phi-3 style)
+                gu = p[pre + "gate_up_proj.weight"]
+                half = gu.shape[0] // 2
+                gate, up = gu[:half], gu[half:]
+            if up is None:
+                continue
+            gs, us, ds = (p.get(pre + f"{x}_proj.weight_scale_inv") for x in ("gate", "up", "down"))
+            if gate is not None:
+                fused = torch.cat((_rows(gate, r, n), _rows(up, r, n)), 0)
+                fs = None if gs is None else torch.cat((_rows(gs, r, n), _rows(us, r, n)), 0)
+                self._put_linear(f"{key}.{pre}gate_up_proj", fused, fs)
+            else:
+                self._put_linear(f"{key}.{pre}up_proj", _rows(up, r, n), None if us is None else _rows(us, r, n))
+            self._put_linear(f"{key}.{pre}down_proj", _cols(down, r, n), None if ds is None else _cols(ds, r, n))
+            for b in ("up_proj", "up_proj_t"):
+                if pre + b + ".bias" in p:
+                    self._put(f"{key}.{pre}up_proj.bias", _rows(p[pre + b + ".bias"], r, n))
+            for b in ("down_proj", "down_proj_t"):
+                if pre + b + ".bias" in p:
+                    self._put(f"{key}.{pre}down_proj.bias", p[pre + b + ".bias"])
+        if "gate.weight" in p:
+            self._put(f"{key}.gate.weight", p["gate.weight"], keep_dtype=p["gate.weight"].dtype == torch.float32)
+        if "gate.e_score_correction_bias" in p:
+            self._put(f"{key}.gate.e_score_correction_bias", p["gate.e_score_correction_bias"].float(), keep_dtype=True)
+        if "shared_expert_gate.weight" in p:
+            self._put(f"{key}.shared_expert_gate.weight", p["shared_expert_gate.weight"])
+
+    def _finish_experts(self, key: str, ex: Dict[Tuple[int, str], torch.Tensor]) -> None:
+        ids = sorted({e for e, _ in ex})
+        has_scale = (ids[0], "gate_proj.weight_scale_inv") in ex
+        gu = torch.stack([torch.cat((ex[(e, "gate_proj.weight")], ex[(e, "up_proj.weight")]), 0) for e in ids])
+        dn = torch.stack([ex[(e, "down_proj.weight")] for e in ids])
+        if has_scale:
+            self.out[f"{key}.experts.up_gate_proj.weight"] = gu.to(self.device).contiguous()
+            self.out[f"{key}.experts.down_proj.weight"] = dn.to(self.device).contiguous()
+            self.out[f"{key}.experts.up_gate_proj.weight_scale_inv"] = torch.stack(
+                [torch.cat((ex[(e, "gate_proj.weight_scale_inv")], ex[(e, "up_proj.weight_scale_inv")]), 0)
+                 for e in ids]).float().to(self.device).contiguous()
+            self.out[f"{key}.experts.down_proj.weight_scale_inv"] = torch.stack(
+                [ex[(e, "down_proj.weight_scale_inv")] for e in ids]).float().to(self.device).contiguous()
+        elif self.quantize == "fp8_block":
+            E = gu.shape[0]
+            q1, s1, q2, s2 = [], [], [], []
+            for e in range(E):
+                a, b = ref.quant_fp8_block_weight(gu[e].to(self.device).float())
+                c, dd = ref.quant_fp8_block_weight(dn[e].to(self.device).float())
+                q1.append(a); s1.append(b); q2.append(c); s2.append(dd)
+            self.out[f"{key}.experts.up_gate_proj.weight"] = torch.stack(q1)
+            self.out[f"{key}.experts.up_gate_proj.weight_scale_inv"] = torch.stack(s1)
+            self.out[f"{key}.experts.down_proj.weight"] = torch.stack(q2)
+            self.out[f"{key}.experts.down_proj.weight_scale_inv"] = torch.stack(s2)
+        else:
+            self._put(f"{key}.experts.up_gate_proj.weight", gu)
+            self._put(f"{key}.experts.down_proj.weight", dn)
+
+
+def load_model_weights(cfg: ModelConfig, model_dir: str = "", tp_rank: int = 0, tp_size: int = 1, device="cpu",
+                       dtype: Optional[torch.dtype] = None, quantize: Optional[str] = None,
+                       synthetic_seed: Optional[int] = None, synthetic_std: float = 0.02,
+                       layer_range: Optional[range] = None) -> Dict[str, torch.Tensor]:
+    loader = WeightLoader(cfg, tp_rank, tp_size, device, dtype, quantize, model_dir=model_dir, layer_range=layer_range)
+    if synthetic_seed is not None or not model_dir:
+        src = synthetic_checkpoint(cfg, synthetic_seed or 0, synthetic_std, device=device, dtype=dtype)
+    else:
+        src = iter_checkpoint(model_dir)
+    return loader.load(src)
