@@ -1,0 +1,83 @@
+"""Paged attention kernels (tcgen05 prefill, split-KV decode) against the fp32 reference."""
+import pytest
+import torch
+
+from ksanallm_b200.engine.step_input import make_step_input
+from ksanallm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(q_lens, kv_lens, h, hk, d=128, bs=16, seed=0):
+    """Random cache + block tables for sequences with the given new-token and context lengths."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    B = len(q_lens)
+    nblk = [(L + bs - 1) // bs for L in kv_lens]
+    total = sum(nblk) + 3
+    cache = (torch.randn(total, 2, hk, bs, d, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    perm = torch.randperm(total, device="cuda", generator=g).tolist()
+    maxb = max(nblk) + 2
+    bt = torch.zeros(B, maxb, dtype=torch.int32)
+    it = iter(perm)
+    for b in range(B):
+        for j in range(nblk[b]):
+            bt[b, j] = next(it)
+    T = sum(q_lens)
+    q = (torch.randn(T, h, d, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    return q, cache, bt, cu
+
+
+def _run(q_lens, kv_lens, h, hk, num_prefill, seed=0, tol=2e-2):
+    from ksanallm_b200.ops import cuda
+    q, cache, bt, cu = _setup(q_lens, kv_lens, h, hk, seed=seed)
+    T = q.shape[0]
+    meta = make_step_input([0] * T, [0] * T, [0] * T, cu, kv_lens, bt, num_prefill=num_prefill, device="cuda")
+    scale = 1.0 / (128 ** 0.5)
+    out = cuda.paged_attention(q, cache, meta, scale)
+    torch.cuda.synchronize()
+    assert cuda.read_error() == 0
+    want = ref.paged_attention(q, cache, meta.block_tables, meta.cu_q, meta.kv_lens, scale)
+    err = (out.float() - want.float()).abs().max().item()
+    assert err < tol, f"max err {err}"
+
+
+def test_decode_mha():
+    _run([1, 1, 1, 1, 1], [1, 17, 160, 1000, 33], h=8, hk=8, num_prefill=0)
+
+
+def test_decode_gqa():
+    _run([1, 1, 1], [300, 5, 2049], h=16, hk=2, num_prefill=0)
+
+
+def test_decode_multi_token_queries():
+    _run([2, 2, 2], [50, 700, 3], h=8, hk=1, num_prefill=0)
+    _run([3, 1], [130, 64], h=4, hk=4, num_prefill=0)
+
+
+def test_decode_long_context_split_kv():
+    _run([1], [8000], h=8, hk=8, num_prefill=0)
+
+
+def test_prefill_single_tile():
+    _run([100], [100], h=4, hk=4, num_prefill=1)
+
+
+def test_prefill_multi_tile_causal():
+    _run([300], [300], h=2, hk=2, num_prefill=1)
+    _run([513], [513], h=2, hk=1, num_prefill=1)
+
+
+def test_prefill_with_cached_prefix():
+    _run([70], [70 + 256], h=4, hk=2, num_prefill=1)
+    _run([200], [200 + 48], h=4, hk=4, num_prefill=1)
+
+
+def test_prefill_batch_ragged():
+    _run([129, 16, 250, 5], [129, 16 + 32, 250, 5 + 400], h=8, hk=2, num_prefill=4)
+
+
+def test_mixed_prefill_and_decode():
+    _run([150, 40, 1, 1, 1], [150, 40 + 64, 77, 1300, 16], h=8, hk=4, num_prefill=2)

@@ -1,0 +1,61 @@
+"""tcgen05 bf16 GEMM against an fp32 PyTorch reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(M, N, K, bias=False, out_fp32=False, bn=0, splits=0, strided=False):
+    from ksanallm_b200.ops import cuda
+    torch.manual_seed(M * 131 + N * 7 + K)
+    dev = "cuda"
+    if strided:
+        xbuf = torch.randn(M, K + 64, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        x = xbuf[:, 32:32 + K]
+    else:
+        x = torch.randn(M, K, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev, dtype=torch.float32) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, device=dev).to(torch.bfloat16) if bias else None
+    y = cuda.gemm_bf16(x, w, b, out_dtype=torch.float32 if out_fp32 else None, bn=bn, splits=splits)
+    torch.cuda.synchronize()
+    assert cuda.read_error() == 0
+    ref = x.float() @ w.float().t()
+    if bias:
+        ref = ref + b.float()
+    err = (y.float() - ref).abs().max().item()
+    tol = 2e-2 * max(1.0, ref.abs().max().item()) if not out_fp32 else 1e-3 * max(1.0, ref.abs().max().item())
+    assert err <= tol, f"M={M} N={N} K={K} bn={bn} splits={splits}: max err {err} > {tol}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (256, 512, 256), (77, 1024, 512),
+                                   (300, 1536, 4096), (1, 4096, 4096), (17, 4096, 11008), (1000, 256, 128)])
+def test_gemm_shapes(M, N, K):
+    _check(M, N, K)
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_tile_widths(bn):
+    _check(260, 768, 512, bn=bn)
+    _check(260, 776, 520, bn=bn)  # ragged N and K tails
+
+
+@pytest.mark.parametrize("splits", [2, 3, 4, 8])
+def test_gemm_split_k(splits):
+    _check(48, 512, 4096, splits=splits)
+    _check(48, 512, 4096, splits=splits, bias=True)
+
+
+def test_gemm_bias_fp32_out_and_strided_input():
+    _check(200, 640, 768, bias=True)
+    _check(200, 640, 768, out_fp32=True)
+    _check(200, 640, 768, strided=True)
+
+
+def test_gemm_deterministic():
+    from ksanallm_b200.ops import cuda
+    x = torch.randn(64, 4096, device="cuda").to(torch.bfloat16)
+    w = torch.randn(4096, 4096, device="cuda").to(torch.bfloat16)
+    a = cuda.gemm_bf16(x, w)
+    b = cuda.gemm_bf16(x, w)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
