@@ -275,9 +275,10 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tc_fence_after();
   }
 
-  if (!bad && valid) {
+  if (!bad) {
+    // tcgen05.ld is warp-collective: all lanes load, only rows inside the sequence store
     const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-    __nv_bfloat16* orow = out + static_cast<size_t>(q0 + q_idx) * ldo + head * D;
+    __nv_bfloat16* orow = out + static_cast<size_t>(q0 + (valid ? q_idx : 0)) * ldo + head * D;
 #pragma unroll 1
     for (int c = 0; c < D / 32; ++c) {
       uint32_t r[32];
@@ -290,11 +291,9 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         o.y = pack_bf16(__uint_as_float(r[j + 2]) * inv, __uint_as_float(r[j + 3]) * inv);
         o.z = pack_bf16(__uint_as_float(r[j + 4]) * inv, __uint_as_float(r[j + 5]) * inv);
         o.w = pack_bf16(__uint_as_float(r[j + 6]) * inv, __uint_as_float(r[j + 7]) * inv);
-        *reinterpret_cast<uint4*>(orow + c * 32 + j) = o;
+        if (valid) *reinterpret_cast<uint4*>(orow + c * 32 + j) = o;
       }
     }
-  } else if (!bad) {
-    // rows outside the sequence still have to drain their TMEM loads? no: nothing outstanding.
   }
   tc_fence_before();
   __syncthreads();

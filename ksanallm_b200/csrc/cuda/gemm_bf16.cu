@@ -206,8 +206,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         reduce_here = (*last_flag != 0);
         __threadfence();
       }
-      if (reduce_here && row < M) {
-        OutT* crow = C + static_cast<size_t>(row) * ldc;
+      // tcgen05.ld is warp-collective (.sync.aligned): every lane executes the loads, only the global
+      // stores are predicated on the row being inside the matrix.
+      const bool row_ok = row < M;
+      if (reduce_here) {
+        OutT* crow = C + static_cast<size_t>(row_ok ? row : 0) * ldc;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           float v[32];
@@ -215,10 +218,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.f;
             for (int s = 0; s < splits; ++s) {
-              const float* wrow = ws + (static_cast<size_t>(s) * M + row) * N + n_idx * BN + c * 32;
+              const float* wrow = ws + (static_cast<size_t>(s) * M + (row_ok ? row : 0)) * N + n_idx * BN + c * 32;
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
-                if (n_idx * BN + c * 32 + j < N) {
+                if (row_ok && n_idx * BN + c * 32 + j < N) {
                   float4 p = __ldcg(reinterpret_cast<const float4*>(wrow + j));
                   v[j] += p.x;
                   v[j + 1] += p.y;
@@ -243,7 +246,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
-              if (col0 + j < N) {
+              if (row_ok && col0 + j < N) {
                 uint4 o;
                 o.x = pack_bf16(v[j], v[j + 1]);
                 o.y = pack_bf16(v[j + 2], v[j + 3]);
@@ -255,7 +258,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              if (col0 + j < N) {
+              if (row_ok && col0 + j < N) {
                 *reinterpret_cast<float4*>(crow + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
               }
             }
