@@ -156,7 +156,7 @@ class LLMEngine:
         per_block = self.model.kv_block_bytes(self.block_size, kv_dtype)
         if self.model.device.type == "cuda":
             free, total = torch.cuda.mem_get_info(self.model.device)
-            budget = free - int(total * bm.reserved_device_memory_ratio) - (2 << 30)
+            budget = free - int(total * bm.reserved_device_memory_ratio) - (8 << 30)
             if bm.block_device_memory_ratio > 0:
                 budget = min(budget, int(total * bm.block_device_memory_ratio))
             n = max(int(budget // per_block), 16)
