@@ -306,3 +306,112 @@ KSANA_API int ksana_paged_decode(const void* q, int ldq, const void* cache, int 
   }
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Decode attention that allocates nothing (see attention_decode.h for who needs it and why).
+//
+// The split-KV partial results live in a fixed array that is part of the loaded library image instead of a
+// caller-provided workspace. In host code `g_decode_static_scratch` is only a handle for the runtime, not a
+// device address, so the address is resolved once per device with cudaGetSymbolAddress (on the first call made
+// while that device is current) and handed to the kernels as an ordinary pointer.
+// ---------------------------------------------------------------------------------------------------------------
+namespace ksana {
+constexpr long long kDecodeStaticScratchFloats = 2ll << 20;  // 8 MiB, held by every GPU that loads the library
+static __device__ __align__(256) float g_decode_static_scratch[kDecodeStaticScratchFloats];
+static float* g_decode_static_scratch_ptr[64] = {nullptr};
+}  // namespace ksana
+
+KSANA_API long long ksana_paged_decode_static_scratch_floats() { return ksana::kDecodeStaticScratchFloats; }
+
+KSANA_API const char* ksana_paged_decode_static_error(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -1: return "unsupported shape: needs head_dim 128, block_size 16 and h divisible by hk";
+    case -5: return "kernel launch failed";
+    case -7: return "problem too large for the built-in scratch array: num_seqs * max_q_len * h * kv_splits * 129 "
+                    "floats exceed ksana_paged_decode_static_scratch_floats(); use ksana_paged_decode with a "
+                    "caller-provided workspace instead";
+    case -8: return "could not resolve the device address of the built-in scratch array (cudaGetSymbolAddress)";
+    case -9: return "device index out of range";
+    default: return "unknown error";
+  }
+}
+
+KSANA_API int ksana_paged_decode_static(const void* q, int ldq, const void* cache, int cache_kind,
+                                        const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens,
+                                        int seq_base, int num_seqs, int max_q_len, int max_kv_len, int h, int hk, int d,
+                                        int block_size, float scale, const float* alibi, float k_scale, float v_scale,
+                                        void* out, int ldo, cudaStream_t stream) {
+  using namespace ksana;
+  if (num_seqs <= 0) return 0;
+  if (d != 128 || block_size != 16 || hk <= 0 || h % hk != 0) return -1;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -9;
+  if (g_decode_static_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_decode_static_scratch) != cudaSuccess || p == nullptr)
+      return -8;
+    g_decode_static_scratch_ptr[dev] = p;
+  }
+  float* scratch = g_decode_static_scratch_ptr[dev];
+  // same KV split policy as ksana_paged_decode
+  const int n_pages = (max_kv_len + block_size - 1) / block_size;
+  int sms = 148;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  int splits = 1;
+  const int base_ctas = num_seqs * hk;
+  if (base_ctas < 4 * sms) {
+    splits = (4 * sms + base_ctas - 1) / base_ctas;
+    const int max_splits = (n_pages + 2 * DEC_WARPS - 1) / (2 * DEC_WARPS);
+    if (splits > max_splits) splits = max_splits;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+  }
+  int pages_per_split = (n_pages + splits - 1) / splits;
+  if (pages_per_split < 1) pages_per_split = 1;
+  splits = (n_pages + pages_per_split - 1) / pages_per_split;
+  if (splits < 1) splits = 1;
+  const int max_rows = max_q_len * h;
+  float* part_o = nullptr;
+  float* part_lse = nullptr;
+  if (splits > 1) {
+    const long long rows = static_cast<long long>(num_seqs) * max_rows * splits;
+    if (rows * (d + 1) > kDecodeStaticScratchFloats) return -7;
+    part_o = scratch;
+    part_lse = scratch + rows * d;
+  }
+  dim3 grid(num_seqs, hk, splits);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  auto Q = reinterpret_cast<const __nv_bfloat16*>(q);
+  auto O = reinterpret_cast<__nv_bfloat16*>(out);
+  const int rows_per_cta = max_q_len * (h / hk);
+#define KSANA_DECODE_STATIC_LAUNCH(RM, CT)                                                                          \
+  {                                                                                                                  \
+    auto kern = paged_decode_kernel<128, 16, RM, CT>;                                                                \
+    const size_t smem = (RM * 128 + DEC_WARPS * RM * 128 + 2 * DEC_WARPS * RM) * sizeof(float);                      \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));                 \
+    kern<<<grid, DEC_WARPS * 32, smem, stream>>>(Q, ldq, reinterpret_cast<const CT*>(cache), block_tables,           \
+                                                 max_blocks, cu_q, kv_lens, seq_base, h, hk, scale_log2, alibi,      \
+                                                 k_scale, v_scale, O, ldo, part_o, part_lse, splits,                 \
+                                                 pages_per_split, max_rows);                                         \
+  }
+  if (cache_kind == 0) {
+    if (rows_per_cta <= 1) KSANA_DECODE_STATIC_LAUNCH(1, __nv_bfloat16)
+    else if (rows_per_cta <= 4) KSANA_DECODE_STATIC_LAUNCH(4, __nv_bfloat16)
+    else if (rows_per_cta <= 8) KSANA_DECODE_STATIC_LAUNCH(8, __nv_bfloat16)
+    else KSANA_DECODE_STATIC_LAUNCH(16, __nv_bfloat16)
+  } else {
+    if (rows_per_cta <= 1) KSANA_DECODE_STATIC_LAUNCH(1, __nv_fp8_e4m3)
+    else if (rows_per_cta <= 4) KSANA_DECODE_STATIC_LAUNCH(4, __nv_fp8_e4m3)
+    else if (rows_per_cta <= 8) KSANA_DECODE_STATIC_LAUNCH(8, __nv_fp8_e4m3)
+    else KSANA_DECODE_STATIC_LAUNCH(16, __nv_fp8_e4m3)
+  }
+#undef KSANA_DECODE_STATIC_LAUNCH
+  if (cudaGetLastError() != cudaSuccess) return -5;
+  if (splits > 1) {
+    dim3 cgrid(num_seqs, (max_rows + 3) / 4);
+    decode_combine_kernel<128><<<cgrid, 128, 0, stream>>>(part_o, part_lse, cu_q, seq_base, h, splits, max_rows, O, ldo);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+  }
+  return 0;
+}
