@@ -156,6 +156,7 @@ def main():
         cfg.num_layers = args.layers
     weights = load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.02, tp_rank=rank, tp_size=world, device=dev,
                                  dtype=torch.bfloat16)
+    tp.init_fused(cfg.hidden_size, args.max_step_tokens)
     model = TransformerModel(cfg, weights, tp, max_positions=4096)
     serving = parse_serving_config({"setting": {
         "global": {"tensor_para_size": world, "enable_cuda_graph": not args.no_cuda_graph},
@@ -167,7 +168,6 @@ def main():
     ctl = dist.new_group(backend="gloo") if world > 1 else None
     if world > 1:
         eng.attach_control_group(ctl)
-        tp.init_fused_if_enabled()
 
     result = None
     if rank == 0:

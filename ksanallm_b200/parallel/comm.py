@@ -31,6 +31,15 @@ class TPGroup:
         self.fused = None  # parallel.fused.FusedComm, attached by init_fused()
         self.stats = {"all_reduce": 0, "all_gather": 0, "fused": 0}
 
+    def init_fused(self, hidden: int, max_tokens: int, use_multicast: Optional[bool] = None) -> bool:
+        """Collective: allocates the symmetric heap and attaches the fused kernels. No-op for size 1, on CPU
+        or when fused kernels were disabled for this group (library-collective baseline)."""
+        if self.size == 1 or not self.use_fused or self.device is None or self.device.type != "cuda":
+            return False
+        from .fused import FusedComm
+        self.fused = FusedComm(self.group, self.rank, self.size, self.device, hidden, max_tokens, use_multicast)
+        return True
+
     # ---- plain collectives ------------------------------------------------------------------------
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.size == 1:

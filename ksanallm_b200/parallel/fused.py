@@ -1,0 +1,109 @@
+"""Symmetric-memory heap and the fused tensor-parallel kernels built on it.
+
+Every rank allocates the same three buffers with ``torch.distributed._symmetric_memory`` (CUDA VMM allocations
+mapped into every peer's address space, plus an NVLS multicast mapping when the fabric offers one):
+
+* ``partial``  [max_tokens, H] bf16 - where this rank's row-parallel GEMM writes its un-reduced output,
+* ``hbuf``     [max_tokens, H] bf16 - where the owners of each row deposit the reduced + normalised activations,
+* ``sig``      uint32 flag words for the epoch-stamped cross-rank barriers.
+
+The kernels (csrc/cuda/comm_fused.cu) issue the NVLink traffic themselves (``multimem.ld_reduce`` / ``multimem.st``
+or plain peer loads/stores); NCCL is only the bootstrap and the measured baseline. Reference counterparts:
+NVLS setup in src/ksana_llm/utils/nvidia/cuda_utils.cpp:89-254 and the custom all-reduce buffers registered in
+src/ksana_llm/layers/nvidia/custom_all_reduce_sum_layer.cpp:19-104.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import cuda as kcuda
+
+
+class FusedComm:
+    def __init__(self, group, rank: int, size: int, device: torch.device, hidden: int, max_tokens: int,
+                 use_multicast: Optional[bool] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rank, self.size, self.device = rank, size, device
+        self.hidden, self.max_tokens = hidden, max_tokens
+        self.group = group
+        gname = group.group_name if hasattr(group, "group_name") else group
+        self.partial = symm_mem.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
+        self.hbuf = symm_mem.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
+        self.sig = symm_mem.empty(8192, dtype=torch.int32, device=device)
+        self.sig.zero_()
+        self.partial.zero_()
+        self.hbuf.zero_()
+        torch.cuda.synchronize(device)
+        self._h_partial = symm_mem.rendezvous(self.partial, gname)
+        self._h_hbuf = symm_mem.rendezvous(self.hbuf, gname)
+        self._h_sig = symm_mem.rendezvous(self.sig, gname)
+        if use_multicast is None:
+            use_multicast = os.environ.get("KSANA_DISABLE_MULTIMEM", "0") != "1"
+        mc_ok = bool(use_multicast)
+        self.partial_mc = int(self._h_partial.multicast_ptr) if mc_ok and self._h_partial.multicast_ptr else 0
+        self.hbuf_mc = int(self._h_hbuf.multicast_ptr) if mc_ok and self._h_hbuf.multicast_ptr else 0
+        if not (self.partial_mc and self.hbuf_mc):
+            self.partial_mc = self.hbuf_mc = 0
+        arr = ctypes.c_void_p * size
+        self._partial_ptrs = arr(*[int(p) for p in self._h_partial.buffer_ptrs])
+        self._hbuf_ptrs = arr(*[int(p) for p in self._h_hbuf.buffer_ptrs])
+        self._sig_ptrs = arr(*[int(p) for p in self._h_sig.buffer_ptrs])
+        self.epoch = 0
+        lib = kcuda.lib()
+        lib.ksana_rs_norm_ag.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                         ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
+                                         ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        lib.ksana_rs_norm_ag.restype = ctypes.c_int
+        self._lib = lib
+        dist.barrier(group=group)
+
+    @property
+    def multicast(self) -> bool:
+        return bool(self.partial_mc)
+
+    # ---- capability checks used by TPGroup -----------------------------------------------------------------
+    def can_all_reduce(self, x: torch.Tensor) -> bool:
+        return (x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.hidden and
+                x.shape[0] <= self.max_tokens)
+
+    def can_linear_reduce_norm(self, x: torch.Tensor, lin) -> bool:
+        return x.dtype == torch.bfloat16 and lin.out_features == self.hidden and x.shape[0] <= self.max_tokens
+
+    # ---- kernels ------------------------------------------------------------------------------------------------
+    def _launch(self, T: int, residual: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+        self.epoch += 1
+        mode = (1 if norm_w is not None else 0) | (2 if residual is not None else 0)
+        code = self._lib.ksana_rs_norm_ag(self.rank, self.size, self._partial_ptrs, self._hbuf_ptrs, self._sig_ptrs,
+                                          self.partial_mc or None, self.hbuf_mc or None, T, self.hidden,
+                                          residual.data_ptr() if residual is not None else None,
+                                          norm_w.data_ptr() if norm_w is not None else None, float(eps),
+                                          self.epoch & 0x7FFFFFFF, mode, 0, torch.cuda.current_stream().cuda_stream)
+        kcuda._check(code, "rs_norm_ag")
+        return self.hbuf[:T]
+
+    def linear_reduce_add_norm(self, x, lin, residual, norm_w, eps) -> torch.Tensor:
+        """GEMM straight into the symmetric ``partial`` buffer, then the fused reduce/add/norm/gather kernel.
+        The returned tensor is a view of ``hbuf`` (valid until the next fused call)."""
+        T = x.shape[0]
+        if lin.kind == "dense" and (lin.bias is None or self.rank != 0):
+            kcuda.gemm_bf16(x, lin.weight, None, out=self.partial[:T])
+        else:
+            self.partial[:T].copy_(lin(x, add_bias=self.rank == 0))
+        return self._launch(T, residual, norm_w, eps)
+
+    def reduce_add_norm(self, y, residual, norm_w, eps) -> torch.Tensor:
+        T = y.shape[0]
+        self.partial[:T].copy_(y)
+        return self._launch(T, residual, norm_w, eps)
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        T = x.shape[0]
+        self.partial[:T].copy_(x)
+        out = self._launch(T, None, None, 0.0)
+        return out.clone()

@@ -92,3 +92,26 @@ def test_argmax_and_sampling():
     # k = 1 is greedy
     got = cuda.sample(logits, temp, torch.ones_like(topk), topp, u)
     assert torch.equal(got.long(), logits.argmax(-1))
+
+
+def test_bounded_flag_wait_times_out_cleanly():
+    """A wait on a flag that nobody sets must give up by itself, report KERR_PEER_TIMEOUT in the status word and
+    leave the context usable (no trap, no hang)."""
+    import ctypes
+    from ksanallm_b200.ops import cuda
+    lib = cuda.lib()
+    lib.ksana_flag_timeout_probe.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p]
+    lib.ksana_flag_timeout_probe.restype = ctypes.c_int
+    cuda.read_error()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    result = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    assert lib.ksana_flag_timeout_probe(flag.data_ptr(), 5, result.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert result.item() == 0
+    assert cuda.read_error() & 8  # KERR_PEER_TIMEOUT
+    # satisfied flag: returns immediately with success, context still fine
+    flag.fill_(7)
+    lib.ksana_flag_timeout_probe(flag.data_ptr(), 5, result.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert result.item() == 1 and cuda.read_error() == 0

@@ -1,0 +1,107 @@
+"""Multi-GPU tests (2 ranks, one process per GPU): fused reduce + residual + RMSNorm + gather kernel over
+symmetric memory, with and without the NVLS multicast path, and a tensor-parallel model forward."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, use_mc, q):
+    import torch.distributed as dist
+    from ksanallm_b200.config.model_config import model_config_from_dict
+    from ksanallm_b200.engine.step_input import make_step_input
+    from ksanallm_b200.models.loader import load_model_weights
+    from ksanallm_b200.models.transformer import TransformerModel
+    from ksanallm_b200.ops import cuda
+    from ksanallm_b200.ops import reference as ref
+    from ksanallm_b200.parallel.comm import TPGroup, init_distributed
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    tp = init_distributed("cuda")
+    dev = tp.device
+    H = 1024
+    tp.init_fused(H, 512, use_multicast=use_mc)
+    fc = tp.fused
+    report = {"multicast": fc.multicast}
+    errs = []
+    for T in (1, 7, 64, 300):
+        g = torch.Generator(device=dev).manual_seed(100 + T)
+        parts = [torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16) for _ in range(world)]
+        res0 = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(H, device=dev, generator=g)).to(torch.bfloat16)
+        total = sum(p.float() for p in parts)
+        res_ref = (total + res0.float()).to(torch.bfloat16)
+        want = ref.rms_norm(res_ref, w, 1e-6)
+        residual = res0.clone()
+        out = fc.reduce_add_norm(parts[rank], residual, w, 1e-6).clone()
+        torch.cuda.synchronize()
+        rows_per = (T + world - 1) // world
+        lo, hi = rank * rows_per, min(T, (rank + 1) * rows_per)
+        e1 = (out.float() - want.float()).abs().max().item()
+        e2 = (residual[lo:hi].float() - res_ref[lo:hi].float()).abs().max().item() if hi > lo else 0.0
+        errs.append((T, e1, e2))
+        ar = fc.all_reduce(parts[rank])
+        torch.cuda.synchronize()
+        errs.append((T, (ar.float() - total).abs().max().item() / max(1.0, total.abs().max().item()), 0.0))
+    report["errs"] = errs
+    report["kernel_error"] = cuda.read_error()
+
+    # tensor-parallel forward vs the single-rank forward of the same weights
+    cfg = model_config_from_dict(dict(model_type="llama", hidden_size=H, num_hidden_layers=2, num_attention_heads=8,
+                                      num_key_value_heads=4, intermediate_size=2816, vocab_size=1000,
+                                      torch_dtype="bfloat16"))
+    w_tp = load_model_weights(cfg, synthetic_seed=3, tp_rank=rank, tp_size=world, device=dev, dtype=torch.bfloat16)
+    m_tp = TransformerModel(cfg, w_tp, tp, max_positions=512)
+    T = 40
+    ids = list(range(5, 5 + T))
+    meta = make_step_input(ids, list(range(T)), list(range(T)), [0, T], [T], [[0, 1, 2, 3]], device=dev)
+    kv = m_tp.allocate_kv_cache(8, 16)
+    h_tp = m_tp.forward(meta, kv).clone()
+    torch.cuda.synchronize()
+    if rank == 0:
+        w_1 = load_model_weights(cfg, synthetic_seed=3, device=dev, dtype=torch.bfloat16)
+        m_1 = TransformerModel(cfg, w_1, TPGroup(), max_positions=512)
+        kv1 = m_1.allocate_kv_cache(8, 16)
+        h_1 = m_1.forward(meta, kv1)
+        torch.cuda.synchronize()
+        report["model_err"] = (h_tp.float() - h_1.float()).abs().max().item()
+        report["model_ref_max"] = h_1.float().abs().max().item()
+    dist.barrier()
+    report["kernel_error2"] = cuda.read_error()
+    if rank == 0:
+        q.put(report)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("use_mc", [False, True])
+def test_fused_reduce_norm_two_ranks(use_mc):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, use_mc, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    rep = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    print(rep)
+    assert rep["kernel_error"] == 0 and rep["kernel_error2"] == 0
+    for T, e1, e2 in rep["errs"]:
+        assert e1 < 6e-2 and e2 < 6e-2, (T, e1, e2)
+    assert rep["model_err"] < 0.05 * max(1.0, rep["model_ref_max"])

@@ -1,0 +1,69 @@
+"""Tensor-parallel engine on CPU (gloo, 2 ranks): the driver rank schedules and broadcasts step plans, the
+follower executes its weight shard; generated tokens must equal the single-rank run."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ksanallm_b200.config.model_config import model_config_from_dict
+from ksanallm_b200.config.schema import parse_serving_config
+from ksanallm_b200.engine.llm_engine import LLMEngine
+from ksanallm_b200.engine.sampling_params import SamplingParams
+from ksanallm_b200.models.loader import load_model_weights
+from ksanallm_b200.models.transformer import TransformerModel
+from ksanallm_b200.parallel.comm import TPGroup
+
+
+def _cfg():
+    return model_config_from_dict(dict(model_type="llama", hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                       num_key_value_heads=2, intermediate_size=256, vocab_size=500,
+                                       torch_dtype="float32", eos_token_id=2))
+
+
+def _serving():
+    return parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 64,
+                                                                 "max_token_len": 128}}})
+
+
+PROMPTS = [[5, 9, 77, 120, 33, 4, 8], [400, 3, 3, 19, 250, 7, 7, 7, 91, 12, 13], [8, 6, 4]]
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    tp = TPGroup(rank, world, dist.group.WORLD, torch.device("cpu"))
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=1, tp_rank=rank, tp_size=world, dtype=torch.float32)
+    model = TransformerModel(cfg, w, tp)
+    eng = LLMEngine(model, _serving(), tp, num_blocks=64, num_host_blocks=0)
+    eng.attach_control_group(dist.group.WORLD)
+    if rank == 0:
+        reqs = eng.generate(PROMPTS, SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True))
+        eng.shutdown_followers()
+        out.put([r.output_token_ids[0] for r in reqs])
+    else:
+        eng.follow()
+    dist.destroy_process_group()
+
+
+def test_tp2_matches_single_rank():
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32)
+    eng = LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=64, num_host_blocks=0)
+    want = [r.output_token_ids[0] for r in eng.generate(PROMPTS, SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True))]
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == want
