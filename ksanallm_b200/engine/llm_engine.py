@@ -183,12 +183,15 @@ class LLMEngine:
         req = Request(next(self._ids), list(int(t) for t in prompt_tokens), params, now)
         req.refit, req.grammar, req.probe = refit, grammar, probe
         n_out = max(params.num_beams, params.num_return_sequences, 1)
+        if params.num_beams > 1:
+            import dataclasses
+            from .beam_search import BeamState
+            req.beam = BeamState(params.num_beams, params.num_return_sequences, params.length_penalty,
+                                 params.max_new_tokens)
+            req.row_params = dataclasses.replace(params, topk=1, do_sample=False, num_beams=1,
+                                                 logprobs=max(params.logprobs, 2 * params.num_beams))
         with self.lock:
             first = self._enqueue_seq(req, req.prompt_tokens)
-            if params.num_beams > 1:
-                from .beam_search import BeamState
-                req.beam = BeamState(params.num_beams, params.num_return_sequences, params.length_penalty,
-                                     params.max_new_tokens)
             req._pending_fanout = n_out - 1 if params.num_beams <= 1 else 0
             self.requests[req.req_id] = req
             self.stats["prompt_tokens"] += len(req.prompt_tokens)
@@ -199,8 +202,13 @@ class LLMEngine:
         sid = next(self._seq_ids)
         p = req.params
         eos = list(self.cfg.eos_token_ids)
-        code = self.sched.enqueue(sid, tokens, p.max_new_tokens, p.ignore_eos, eos, list(p.stop_token_ids),
-                                  int(req.arrival * 1000), req.req_id)
+        if req.beam is not None:
+            # the beam state applies EOS / length rules itself (a finished hypothesis is not a finished request)
+            code = self.sched.enqueue(sid, tokens, p.max_new_tokens + 1, True, [], [], int(req.arrival * 1000),
+                                      req.req_id)
+        else:
+            code = self.sched.enqueue(sid, tokens, p.max_new_tokens, p.ignore_eos, eos, list(p.stop_token_ids),
+                                      int(req.arrival * 1000), req.req_id)
         if code != _host.RET_SUCCESS:
             msg = {_host.RET_EXCEED_CAPACITY: "waiting queue is full",
                    _host.RET_INPUT_LENGTH_EXCEEDED: "input length exceeds max_token_len",
@@ -218,6 +226,19 @@ class LLMEngine:
             trie = _host.DraftTrie()
             trie.feed(tokens)
             req.tries[sid] = trie
+        return so
+
+    def _fork_seq(self, req: Request, parent_sid: int) -> Optional[SequenceOutput]:
+        """Copy-on-write fork of a running sequence (beam search)."""
+        import copy
+        child_id = next(self._seq_ids)
+        if not self.sched.fork(parent_sid, child_id):
+            return None
+        parent = self.seq_owner[parent_sid][1]
+        so = SequenceOutput(child_id, list(parent.output_tokens), copy.copy(parent.logprobs))
+        so.cum_logprob = parent.cum_logprob
+        req.seqs.append(so)
+        self.seq_owner[child_id] = (req, so)
         return so
 
     def abort(self, req: Request) -> None:
@@ -277,7 +298,7 @@ class LLMEngine:
                 bm = None
                 if req.grammar is not None and j == 0:
                     bm = req.grammar.next_bitmask(so.seq_id)
-                rows.append(SampleRow(req.params, req.prompt_tokens, so.output_tokens, bm,
+                rows.append(SampleRow(getattr(req, "row_params", req.params), req.prompt_tokens, so.output_tokens, bm,
                                       req.generators.get(e.seq_id)))
         from .sampler import Sampler
         greedy = Sampler.all_greedy(rows)
@@ -342,6 +363,20 @@ class LLMEngine:
                         req.error = ex
             touched.add(req.req_id)
         self.stats["generated_tokens"] += n_new
+        # ---- beam search: re-rank and fork/prune the beams of every request that advanced ----
+        for rid in touched:
+            req = self.requests.get(rid)
+            if req is None or req.beam is None or req.beam.done:
+                continue
+            rows = {}
+            for r in results:
+                owner = self.seq_owner.get(r.seq_id)
+                if owner is None or owner[0] is not req or not r.new_tokens:
+                    continue
+                top = out.logprobs[row_of[r.seq_id]] or []
+                rows[r.seq_id] = (list(owner[1].output_tokens[:-1]), top)
+            if rows:
+                req.beam.step(self, req, rows, set(self.cfg.eos_token_ids) | set(req.params.stop_token_ids))
         for rid in touched:
             req = self.requests.get(rid)
             if req is not None:

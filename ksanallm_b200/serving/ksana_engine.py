@@ -1,0 +1,366 @@
+"""Public Python engine API: ``KsanaLLMEngine`` (from_engine_args / initialize / generate / forward).
+
+Same surface as the reference's Python wrapper (src/ksana_llm/python/ksana_llm/ksana_engine.py:91-473 and
+arg_utils.py:36-254): a request dictionary with ``prompt`` | ``input_tokens`` | ``messages``, ``sampling_config``,
+``stream`` ... goes in, a status plus an output object (or an async iterator of outputs when streaming) comes out.
+Underneath it drives :class:`ksanallm_b200.engine.llm_engine.LLMEngine` instead of a pybind module.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import base64
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, AsyncIterator, Dict, List, Optional, Tuple
+
+import torch
+
+from ..config.model_config import ModelConfig, load_model_config, NAMED_CONFIGS
+from ..config.schema import ServingConfig, load_serving_config, parse_serving_config
+from ..engine.llm_engine import EngineError, LLMEngine, Request
+from ..engine.sampling_params import SamplingParams
+from ..engine.forward_probe import validate_targets
+from .tokenizer import TokenizerProcessor
+
+
+# ---- status object -------------------------------------------------------------------------------------
+class RetCode:
+    RET_SUCCESS = 0
+    RET_EXCEED_CAPACITY = 1
+    RET_INPUT_LENGTH_EXCEEDED = 2
+    RET_INVALID_ARGUMENT = 3
+    RET_REQUEST_TIMEOUT = 4
+    RET_REQUEST_TERMINATED = 5
+    RET_OUT_OF_MEMORY = 6
+    RET_INTERNAL_ERROR = 7
+
+
+class _Code(int):
+    @property
+    def value(self) -> int:
+        return int(self)
+
+
+class Status:
+    def __init__(self, code: int = 0, message: str = ""):
+        self._code, self._msg = code, message
+
+    def OK(self) -> bool:  # noqa: N802  (name kept for API compatibility)
+        return self._code == 0
+
+    def GetMessage(self) -> str:  # noqa: N802
+        return self._msg
+
+    def GetCode(self):  # noqa: N802
+        return _Code(self._code)
+
+    def __repr__(self):
+        return f"Status(code={self._code}, message={self._msg!r})"
+
+
+@dataclass
+class KsanaPythonOutput:
+    input_tokens: List[int] = field(default_factory=list)
+    output_tokens: List[List[int]] = field(default_factory=list)
+    logprobs: List[Any] = field(default_factory=list)
+    finish_status: Status = field(default_factory=Status)
+    finish_reasons: List[Optional[str]] = field(default_factory=list)
+    finished: bool = False
+
+
+@dataclass
+class EngineArgs:
+    config_file: str = ""
+    model_dir: str = ""
+    tokenizer_path: str = ""
+    model_type: str = ""
+    host: str = "0.0.0.0"
+    port: int = 8080
+    endpoint: str = "python"
+    access_log: bool = True
+    ssl_keyfile: Optional[str] = None
+    ssl_certfile: Optional[str] = None
+    root_path: Optional[str] = None
+    tool_call_parser: Optional[str] = None
+    reasoning_parser: Optional[str] = None
+    enable_auto_tool_choice: bool = False
+    tool_parser_plugin: str = ""
+    chat_template: Optional[str] = None
+    chat_template_content_format: str = "auto"
+    synthetic_model: Optional[str] = None  # one of NAMED_CONFIGS: random weights, no checkpoint files needed
+    device: Optional[str] = None
+    serving: Optional[ServingConfig] = None
+    max_token_len: int = 0
+
+    @classmethod
+    def from_config_file(cls, config_file: str, **overrides) -> "EngineArgs":
+        serving = load_serving_config(config_file)
+        a = cls(config_file=config_file, serving=serving, model_dir=serving.model_spec.model_dir)
+        a.endpoint = serving.setting.endpoint_type or "python"
+        a.max_token_len = serving.setting.batch_scheduler.max_token_len
+        for k, v in overrides.items():
+            if v is not None and hasattr(a, k):
+                setattr(a, k, v)
+        if not a.tokenizer_path:
+            a.tokenizer_path = a.model_dir
+        cfg_path = os.path.join(a.model_dir or "", "config.json")
+        if os.path.isfile(cfg_path):
+            with open(cfg_path, "r", encoding="utf-8") as f:
+                a.model_type = str(json.load(f).get("model_type", ""))
+        return a
+
+    @classmethod
+    def add_cli_args(cls, p: argparse.ArgumentParser) -> argparse.ArgumentParser:
+        p.add_argument("--config_file", type=str, default="examples/ksana_llm.yaml", help="serving config file")
+        p.add_argument("--tokenizer_path", type=str, default=None)
+        p.add_argument("--host", type=str, default="0.0.0.0")
+        p.add_argument("--port", type=int, default=8080)
+        p.add_argument("--endpoint", type=str, default=None)
+        p.add_argument("--access_log", action="store_true", default=False)
+        p.add_argument("--ssl_keyfile", type=str, default=None)
+        p.add_argument("--ssl_certfile", type=str, default=None)
+        p.add_argument("--root_path", type=str, default=None)
+        p.add_argument("--tool-call-parser", dest="tool_call_parser", type=str, default=None)
+        p.add_argument("--reasoning-parser", dest="reasoning_parser", type=str, default=None)
+        p.add_argument("--enable-auto-tool-choice", dest="enable_auto_tool_choice", action="store_true")
+        p.add_argument("--tool-parser-plugin", dest="tool_parser_plugin", type=str, default="")
+        p.add_argument("--chat-template", dest="chat_template", type=str, default=None)
+        p.add_argument("--chat-template-content-format", dest="chat_template_content_format", type=str, default="auto",
+                       choices=["auto", "string", "openai"])
+        p.add_argument("--synthetic-model", dest="synthetic_model", type=str, default=None,
+                       help="serve random-init weights of a named architecture: " + ", ".join(NAMED_CONFIGS))
+        p.add_argument("--device", type=str, default=None)
+        return p
+
+    @classmethod
+    def from_command_line(cls, argv: Optional[List[str]] = None) -> "EngineArgs":
+        p = cls.add_cli_args(argparse.ArgumentParser(description="ksanallm_b200 serving server"))
+        ns = p.parse_args(argv)
+        d = vars(ns)
+        cfg_file = d.pop("config_file")
+        return cls.from_config_file(cfg_file, **d)
+
+
+class PyAsyncStreamingIterator:
+    """Async iterator over the growing output of one request; each item carries the FULL output so far
+    (reference streaming contract). Dropping the iterator aborts the request (client disconnect)."""
+
+    def __init__(self, engine: "KsanaLLMEngine", req: Request):
+        self.engine, self.req = engine, req
+        self.version = -1
+        self.done = False
+
+    def __aiter__(self):
+        return self
+
+    async def __anext__(self) -> KsanaPythonOutput:
+        if self.done:
+            raise StopAsyncIteration
+        loop = asyncio.get_running_loop()
+        self.version = await loop.run_in_executor(None, self.req.wait, self.version, 1.0)
+        out = self.engine._snapshot(self.req)
+        if self.req.finished:
+            self.done = True
+        return out
+
+    def abort(self) -> None:
+        if not self.req.finished:
+            self.engine.llm.abort(self.req)
+
+    def __del__(self):
+        try:
+            self.abort()
+        except Exception:
+            pass
+
+
+class KsanaLLMEngine:
+    def __init__(self, args: EngineArgs):
+        self.args = args
+        self.serving: ServingConfig = args.serving or parse_serving_config({})
+        self.llm: Optional[LLMEngine] = None
+        self.tokenizer: Optional[TokenizerProcessor] = None
+        self.model_config: Optional[ModelConfig] = None
+        self.plugin = None
+        self.think_end_token_id: Optional[int] = None
+
+    @classmethod
+    def from_engine_args(cls, args: EngineArgs) -> "KsanaLLMEngine":
+        return cls(args)
+
+    # ---- bootstrap ---------------------------------------------------------------------------------------
+    def initialize(self, tp=None) -> None:
+        """Loads config, weights and the model on this rank and starts the step loop (rank 0 only)."""
+        from ..models.loader import load_model_weights
+        from ..models.transformer import TransformerModel
+        from ..parallel.comm import TPGroup, init_distributed, world_group
+
+        a = self.args
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        want_cuda = (a.device or ("cuda" if torch.cuda.is_available() else "cpu")).startswith("cuda")
+        if tp is None:
+            tp = init_distributed("cuda" if want_cuda else "cpu") if (world > 1 or want_cuda) else TPGroup()
+        device = tp.device if tp.device is not None else torch.device(a.device or "cpu")
+        if a.synthetic_model:
+            cfg = NAMED_CONFIGS[a.synthetic_model]()
+        else:
+            cfg = load_model_config(a.model_dir)
+        self.model_config = cfg
+        dtype = torch.float32 if device.type == "cpu" and cfg.torch_dtype == "float32" else \
+            (torch.bfloat16 if device.type == "cuda" else getattr(torch, cfg.torch_dtype, torch.float32))
+        qmethod = self.serving.setting.quantization_config.weight.quant_method
+        quantize = {"fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "int4": "int4"}.get(qmethod)
+        weights = load_model_weights(cfg, "" if a.synthetic_model else a.model_dir, tp.rank, tp.size, device, dtype,
+                                     quantize, synthetic_seed=0 if a.synthetic_model else None)
+        bs = self.serving.setting.batch_scheduler
+        if tp.size > 1 and device.type == "cuda":
+            tp.init_fused(cfg.hidden_size, bs.max_step_tokens)
+        model = TransformerModel(cfg, weights, tp, max_positions=max(bs.max_token_len, 2048))
+        self.tokenizer = TokenizerProcessor(a.tokenizer_path or a.model_dir, cfg.vocab_size,
+                                            self.serving.setting.tokenization.add_special_tokens,
+                                            self.serving.setting.tokenization.skip_special_tokens, a.chat_template)
+        kvd = self.serving.setting.quantization_config.kv_cache.dtype
+        kv_dtype = torch.float8_e4m3fn if kvd == "fp8_e4m3" else (torch.float8_e5m2 if kvd == "fp8_e5m2" else None)
+        self.llm = LLMEngine(model, self.serving, tp, detokenize=lambda ids: self.tokenizer.decode(ids),
+                             kv_dtype=kv_dtype)
+        if tp.size > 1:
+            import torch.distributed as dist
+            self.llm.attach_control_group(dist.new_group(backend="gloo"))
+        self._load_plugin()
+        if tp.rank == 0:
+            self.llm.start()
+
+    def serve_follower(self) -> None:
+        """Blocks in the follower loop (ranks > 0)."""
+        self.llm.follow()
+
+    def shutdown(self) -> None:
+        if self.llm is not None:
+            self.llm.stop()
+
+    def _load_plugin(self) -> None:
+        from .plugin import load_plugin
+        self.plugin = load_plugin(self.args.model_dir, self.serving.model_spec.plugin_model, self)
+
+    # ---- request construction --------------------------------------------------------------------------------
+    def _build_sampling(self, request_dict: Dict[str, Any]) -> SamplingParams:
+        sc = dict(request_dict.get("sampling_config") or {})
+        for k in ("structured_output_regex",):
+            if k in request_dict and k not in sc:
+                sc[k] = request_dict[k]
+        if "max_new_tokens" not in sc:
+            sc["max_new_tokens"] = max(self.serving.setting.batch_scheduler.max_token_len // 2, 1)
+        return SamplingParams.from_dict(sc)
+
+    def _build_tokens(self, request_dict: Dict[str, Any]) -> Tuple[List[int], Any]:
+        refit = None
+        if request_dict.get("input_tokens") is not None:
+            tokens = [int(t) for t in request_dict["input_tokens"]]
+        elif request_dict.get("messages") is not None:
+            msgs = request_dict["messages"]
+            kw = {}
+            if request_dict.get("sampling_config", {}).get("enable_thinking") is not None:
+                kw["enable_thinking"] = bool(request_dict["sampling_config"]["enable_thinking"])
+            text = self.tokenizer.apply_chat_template(msgs, True, request_dict.get("tools"), **kw)
+            tokens = self.tokenizer.encode(text, add_special_tokens=False)
+        else:
+            prompt = request_dict.get("prompt")
+            if prompt is None:
+                raise ValueError("one of prompt, input_tokens, messages is required")
+            if request_dict.get("use_chat_template"):
+                prompt = self.tokenizer.apply_chat_template([{"role": "user", "content": prompt}])
+                tokens = self.tokenizer.encode(prompt, add_special_tokens=False)
+            else:
+                tokens = self.tokenizer.encode(prompt)
+        emb = request_dict.get("input_refit_embedding") or {}
+        pos = emb.get("pos", request_dict.get("pos"))
+        vals = emb.get("embeddings", request_dict.get("embeddings"))
+        if pos and vals:
+            refit = []
+            for p, e in zip(pos, vals):
+                t = torch.as_tensor(e, dtype=torch.float32)
+                refit.append((int(p), t.view(-1, self.model_config.hidden_size)))
+        if self.plugin is not None:
+            extra = self.plugin.preprocess(request_dict, tokens)
+            if extra:
+                tokens = extra.get("input_tokens", tokens)
+                refit = extra.get("refit", refit)
+        return tokens, refit
+
+    def _grammar_for(self, sp: SamplingParams):
+        if not (sp.enable_structured_output or sp.json_schema or sp.structured_output_regex):
+            return None
+        from ..engine.structured import build_grammar
+        return build_grammar(sp, self.tokenizer, self.model_config.vocab_size, self.think_end_token_id)
+
+    def _snapshot(self, req: Request) -> KsanaPythonOutput:
+        out = KsanaPythonOutput(input_tokens=list(req.prompt_tokens))
+        seqs = req.seqs
+        if req.beam is not None and req.finished:
+            seqs = req.beam.best(req)
+        elif req.params.num_return_sequences < len(seqs) and req.finished:
+            seqs = seqs[:req.params.num_return_sequences]
+        out.output_tokens = [list(s.output_tokens) for s in seqs]
+        out.logprobs = [s.logprobs for s in seqs] if req.params.logprobs else []
+        out.finish_reasons = [s.finish_reason for s in seqs]
+        out.finished = req.finished
+        if req.error is not None:
+            out.finish_status = Status(req.error.code, str(req.error))
+        return out
+
+    # ---- public calls --------------------------------------------------------------------------------------------
+    async def generate(self, request_dict: Dict[str, Any], streamer: Optional[bool] = None,
+                       req_ctx: Optional[Dict[str, str]] = None):
+        """Returns (Status, KsanaPythonOutput) or (Status, async iterator of KsanaPythonOutput) when streaming."""
+        try:
+            sp = self._build_sampling(request_dict)
+            tokens, refit = self._build_tokens(request_dict)
+            grammar = self._grammar_for(sp)
+            req = self.llm.add_request(tokens, sp, refit=refit, grammar=grammar)
+            req.ctx = req_ctx or {}
+        except EngineError as ex:
+            return Status(ex.code, str(ex)), None
+        except (ValueError, KeyError, TypeError) as ex:
+            return Status(RetCode.RET_INVALID_ARGUMENT, str(ex)), None
+        if streamer:
+            return Status(), PyAsyncStreamingIterator(self, req)
+        loop = asyncio.get_running_loop()
+        v = -1
+        while not req.finished:
+            v = await loop.run_in_executor(None, req.wait, v, 1.0)
+        out = self._snapshot(req)
+        if self.plugin is not None:
+            self.plugin.postprocess(request_dict, out)
+        return out.finish_status, out
+
+    def generate_sync(self, request_dict: Dict[str, Any]) -> Tuple[Status, Optional[KsanaPythonOutput]]:
+        return asyncio.run(self.generate(request_dict, streamer=False))
+
+    async def forward(self, request_bytes: bytes, req_ctx: Optional[Dict[str, str]] = None):
+        """msgpack (or JSON when Content-Type says so) batch of single-prefill probes -> packed responses."""
+        import msgpack
+        is_json = bool(req_ctx) and "json" in (req_ctx.get("Content-Type", "") or "").lower()
+        try:
+            body = json.loads(request_bytes) if is_json else msgpack.unpackb(request_bytes, raw=False)
+            reqs = []
+            for r in body.get("requests", []):
+                tokens, refit = self._build_tokens(r)
+                targets = r.get("request_target") or []
+                validate_targets(targets, len(tokens))
+                sp = SamplingParams(topk=1, max_new_tokens=1, ignore_eos=True)
+                reqs.append(self.llm.add_request(tokens, sp, refit=refit, probe=targets))
+        except EngineError as ex:
+            return Status(ex.code, str(ex)), None
+        except Exception as ex:
+            return Status(RetCode.RET_INVALID_ARGUMENT, str(ex)), None
+        loop = asyncio.get_running_loop()
+        for q in reqs:
+            v = -1
+            while not q.finished:
+                v = await loop.run_in_executor(None, q.wait, v, 1.0)
+        responses = [{"input_token_ids": list(q.prompt_tokens), "response": q.probe_result or []} for q in reqs]
+        payload = {"responses": responses}
+        data = json.dumps(payload).encode() if is_json else msgpack.packb(payload, use_bin_type=True)
+        return Status(), data
