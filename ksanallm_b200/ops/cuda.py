@@ -41,6 +41,11 @@ class _Sig:
     ksana_read_error = ([I], ctypes.c_uint)
     ksana_sm_count = ([], I)
     ksana_gemm_bf16 = ([P, P, P, P, I, I, I, I, I, I, I, I, I, P, LL, P, I, P], I)
+    ksana_gemm_fp8_block = ([P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, LL, P, I, P], I)
+    ksana_moe_route = ([P, I, P, I, I, I, I, I, I, I, F, P, P, P], I)
+    ksana_moe_permute = ([P, I, P, I, I, I, I, I, P, P, P, P, P], I)
+    ksana_moe_grouped_gemm = ([P, P, P, P, I, I, I, I, P], I)
+    ksana_moe_combine = ([P, P, P, I, I, I, P, P], I)
     ksana_rms_norm = ([P, I, P, I, P, P, I, I, I, F, P], I)
     ksana_silu_mul = ([P, I, P, I, I, I, P], I)
     ksana_embedding = ([P, P, P, I, I, I, F, P], I)
@@ -128,6 +133,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     else:
         y = gemm_bf16(x2, weight, bias)
     return y.view(*lead, N)
+
+
+def gemm_fp8_block(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws_inv: torch.Tensor,
+                   bias: Optional[torch.Tensor] = None, out_dtype=None, splits: int = 0,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Block-scaled fp8 GEMM: xq [M, K] e4m3 + xs [M, K/128]; wq [N, K] e4m3 + ws_inv [ceil(N/128), K/128]."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=xq.device)
+    if M == 0:
+        return out
+    w = workspace(xq.device)
+    code = lib().ksana_gemm_fp8_block(_ptr(xq), _ptr(xs), _ptr(wq), _ptr(ws_inv), _ptr(out), _ptr(bias), M, N, K,
+                                      xq.stride(0), wq.stride(0), out.stride(0),
+                                      1 if out.dtype == torch.float32 else 0, splits, _ptr(w.gemm_ws),
+                                      w.gemm_ws.numel(), _ptr(w.gemm_counters), w.gemm_counters.numel(), _stream())
+    _check(code, f"gemm_fp8_block M={M} N={N} K={K}")
+    return out
 
 
 def linear_fp8_block(x, wq, w_scale_inv, bias=None):

@@ -1,9 +1,6 @@
-"""fp8 block-scaled linear: per-token 1x128 activation quantisation kernel + GEMM.
-
-The GEMM currently dequantises the 128x128 block-scaled weight to bf16 and runs the bf16 tcgen05 kernel;
-activations go through the same quantise/dequantise round trip as the block-scaled kernel would apply, so the
-numerics match the fp32 reference of the format.
-"""
+"""fp8 block-scaled linear: per-token 1 x 128 activation quantisation kernel + block-scaled tcgen05 GEMM
+(csrc/cuda/gemm_fp8_block.cu). Shapes the kernel does not take (K not a multiple of 128, N not a multiple of 8)
+are dequantised and sent through the bf16 GEMM."""
 from __future__ import annotations
 
 import torch
@@ -14,13 +11,15 @@ from . import reference as ref
 def linear_fp8_block(x, wq, w_scale_inv, bias=None):
     from . import cuda
     lead = x.shape[:-1]
-    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
     T, K = x2.shape
-    if K % 128 == 0 and x2.dtype == torch.bfloat16:
+    N = wq.shape[0]
+    if K % 128 == 0 and N % 8 == 0 and x2.dtype == torch.bfloat16 and wq.stride(1) == 1 and wq.stride(0) % 16 == 0:
         xq, xs = cuda.quant_fp8_group(x2)
-        xd = (xq.float().view(T, K // 128, 128) * xs.unsqueeze(-1)).view(T, K).to(torch.bfloat16)
-    else:
-        xd = x2
+        y = cuda.gemm_fp8_block(xq, xs, wq, w_scale_inv.contiguous(), bias)
+        return y.view(*lead, N)
     w = ref.dequant_fp8_block_weight(wq, w_scale_inv).to(torch.bfloat16)
-    y = cuda.gemm_bf16(xd, w, bias)
-    return y.view(*lead, w.shape[0])
+    y = cuda.gemm_bf16(x2.contiguous().to(torch.bfloat16), w, bias)
+    return y.view(*lead, N)

@@ -1,38 +1,70 @@
-"""MoE routing and expert computation on the GPU."""
+"""MoE on the GPU: router kernel, device-side counting sort by expert, grouped tcgen05 expert GEMMs, combine.
+No host synchronisation: expert row offsets stay on the device and the grouped GEMM walks them itself."""
 from __future__ import annotations
+
+from typing import Dict
 
 import torch
 
 from . import reference as ref
 
+_meta: Dict[tuple, torch.Tensor] = {}
+
 
 def moe_route(logits, top_k, scoring="softmax", norm_topk=False, n_group=1, topk_group=1, routed_scale=1.0,
               correction_bias=None):
-    return ref.moe_route(logits, top_k, scoring, norm_topk, n_group, topk_group, routed_scale, correction_bias)
+    from . import cuda
+    T, E = logits.shape
+    if E > 512 or top_k > 16 or n_group > 32 or E % max(n_group, 1):
+        return ref.moe_route(logits, top_k, scoring, norm_topk, n_group, topk_group, routed_scale, correction_bias)
+    x = logits if logits.dtype == torch.float32 else logits.float()
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    b = None if correction_bias is None else correction_bias.float().contiguous()
+    code = cuda.lib().ksana_moe_route(cuda._ptr(x), x.stride(0), cuda._ptr(b), T, E, top_k,
+                                      1 if scoring == "sigmoid" else 0, 1 if norm_topk else 0, n_group, topk_group,
+                                      float(routed_scale), cuda._ptr(ids), cuda._ptr(w), cuda._stream())
+    cuda._check(code, "moe_route")
+    return ids, w
 
 
 def moe_experts(x, ids, weights, w_gate_up, w_down, expert_offset=0):
-    """Tokens are sorted by expert once; each local expert with work runs two tcgen05 GEMMs on its slice."""
+    """x [T, H] bf16; ids/weights [T, k]; w_gate_up [E_local, 2I, H]; w_down [E_local, H, I] (bf16, contiguous)."""
     from . import cuda
     T, H = x.shape
-    E_local = w_gate_up.shape[0]
     k = ids.shape[1]
-    flat = ids.reshape(-1).long() - expert_offset
-    local = (flat >= 0) & (flat < E_local)
-    order = torch.argsort(torch.where(local, flat, torch.full_like(flat, E_local)), stable=True)
-    counts = torch.bincount(flat[local], minlength=E_local).tolist()
-    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
-    tok_of = order // k
-    wflat = weights.reshape(-1)
-    start = 0
-    for e, n in enumerate(counts):
-        if n == 0:
-            continue
-        sel = order[start:start + n]
-        tok = tok_of[start:start + n]
-        start += n
-        h = cuda.gemm_bf16(x.index_select(0, tok), w_gate_up[e])
-        a = cuda.silu_and_mul(h)
-        y = cuda.gemm_bf16(a, w_down[e]).float()
-        out.index_add_(0, tok, y * wflat[sel].unsqueeze(-1))
-    return out.to(x.dtype)
+    E_local, two_i, _ = w_gate_up.shape
+    I_ = two_i // 2
+    if (x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16 or two_i % 128 or H % 128 or I_ % 8 or
+            not w_gate_up.is_contiguous() or not w_down.is_contiguous()):
+        return ref.moe_experts(x, ids, weights, w_gate_up, w_down, expert_offset)
+    dev = x.device
+    key = (dev.index, E_local)
+    meta = _meta.get(key)
+    if meta is None:
+        meta = _meta[key] = torch.zeros(3 * E_local + 2, dtype=torch.int32, device=dev)
+    n = T * k
+    pos = torch.empty(n, dtype=torch.int32, device=dev)
+    row_src = torch.empty(n, dtype=torch.int32, device=dev)
+    xs = torch.empty(n, H, dtype=torch.bfloat16, device=dev)
+    lib = cuda.lib()
+    st = cuda._stream()
+    idc = ids if ids.is_contiguous() else ids.contiguous()
+    cuda._check(lib.ksana_moe_permute(cuda._ptr(x), x.stride(0), cuda._ptr(idc), T, k, H, expert_offset, E_local,
+                                      cuda._ptr(meta), cuda._ptr(pos), cuda._ptr(row_src), cuda._ptr(xs), st),
+                "moe_permute")
+    offsets = meta[E_local:2 * E_local + 1]
+    h1 = torch.empty(n, two_i, dtype=torch.bfloat16, device=dev)
+    cuda._check(lib.ksana_moe_grouped_gemm(cuda._ptr(xs), cuda._ptr(w_gate_up), cuda._ptr(h1), cuda._ptr(offsets),
+                                           E_local, n, two_i, H, st), "moe_grouped_gemm(gate_up)")
+    a = cuda.silu_and_mul(h1)
+    y = torch.empty(n, H, dtype=torch.bfloat16, device=dev)
+    cuda._check(lib.ksana_moe_grouped_gemm(cuda._ptr(a), cuda._ptr(w_down), cuda._ptr(y), cuda._ptr(offsets), E_local,
+                                           n, H, I_, st), "moe_grouped_gemm(down)")
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    wc = weights if weights.dtype == torch.float32 and weights.is_contiguous() else weights.float().contiguous()
+    cuda._check(lib.ksana_moe_combine(cuda._ptr(y), cuda._ptr(pos), cuda._ptr(wc), T, k, H, cuda._ptr(out), st),
+                "moe_combine")
+    return out
