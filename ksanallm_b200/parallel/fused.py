@@ -35,6 +35,9 @@ class FusedComm:
         self.partial = symm_mem.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
         self.hbuf = symm_mem.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
         self.sig = symm_mem.empty(8192, dtype=torch.int32, device=device)
+        self.rows_cap = (max_tokens + size - 1) // size
+        self.recv = symm_mem.empty(size * self.rows_cap, hidden, dtype=torch.bfloat16, device=device)
+        self.recv.zero_()
         self.sig.zero_()
         self.partial.zero_()
         self.hbuf.zero_()
@@ -42,6 +45,7 @@ class FusedComm:
         self._h_partial = symm_mem.rendezvous(self.partial, gname)
         self._h_hbuf = symm_mem.rendezvous(self.hbuf, gname)
         self._h_sig = symm_mem.rendezvous(self.sig, gname)
+        self._h_recv = symm_mem.rendezvous(self.recv, gname)
         if use_multicast is None:
             use_multicast = os.environ.get("KSANA_DISABLE_MULTIMEM", "0") != "1"
         mc_ok = bool(use_multicast)
@@ -53,6 +57,9 @@ class FusedComm:
         self._partial_ptrs = arr(*[int(p) for p in self._h_partial.buffer_ptrs])
         self._hbuf_ptrs = arr(*[int(p) for p in self._h_hbuf.buffer_ptrs])
         self._sig_ptrs = arr(*[int(p) for p in self._h_sig.buffer_ptrs])
+        self._recv_ptrs = arr(*[int(p) for p in self._h_recv.buffer_ptrs])
+        self.single_kernel = os.environ.get("KSANA_DISABLE_FUSED_GEMM_RS", "0") != "1"
+        self.comm_ctas = int(os.environ.get("KSANA_FUSED_COMM_CTAS", "16"))
         self.epoch = 0
         lib = kcuda.lib()
         lib.ksana_rs_norm_ag.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
@@ -60,7 +67,18 @@ class FusedComm:
                                          ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
                                          ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         lib.ksana_rs_norm_ag.restype = ctypes.c_int
+        lib.ksana_gemm_rs_norm_ag.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                              ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
+                                              ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        lib.ksana_gemm_rs_norm_ag.restype = ctypes.c_int
         self._lib = lib
+        dist.barrier(group=group)
+        # warm-up: lazy module loading and first-launch costs happen here, under a barrier, not inside a step
+        z = torch.zeros(8, hidden, dtype=torch.bfloat16, device=device)
+        self.all_reduce(z)
+        torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
     @property
@@ -91,11 +109,32 @@ class FusedComm:
         """GEMM straight into the symmetric ``partial`` buffer, then the fused reduce/add/norm/gather kernel.
         The returned tensor is a view of ``hbuf`` (valid until the next fused call)."""
         T = x.shape[0]
+        if (self.single_kernel and lin.kind == "dense" and lin.bias is None and self.hidden % 128 == 0 and
+                self.hidden <= 9216 and T <= 8192 and x.dim() == 2 and residual is not None and
+                residual.is_contiguous()):
+            return self.gemm_reduce_add_norm(x, lin.weight, residual, norm_w, eps)
         if lin.kind == "dense" and (lin.bias is None or self.rank != 0):
             kcuda.gemm_bf16(x, lin.weight, None, out=self.partial[:T])
         else:
             self.partial[:T].copy_(lin(x, add_bias=self.rank == 0))
         return self._launch(T, residual, norm_w, eps)
+
+    def gemm_reduce_add_norm(self, x, weight, residual, norm_w, eps) -> torch.Tensor:
+        """The single-kernel path: tcgen05 GEMM whose epilogue pushes tiles to the row owners over NVLink while
+        communication CTAs reduce, normalise and broadcast finished row bands (csrc/cuda/gemm_fused_rs.cu)."""
+        T, K = x.shape
+        if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+            x = x.contiguous()
+        self.epoch += 1
+        mode = (1 if norm_w is not None else 0) | (2 if residual is not None else 0)
+        code = self._lib.ksana_gemm_rs_norm_ag(
+            x.data_ptr(), weight.data_ptr(), T, self.hidden, K, x.stride(0), weight.stride(0), self.rank, self.size,
+            self._recv_ptrs, self._hbuf_ptrs, self._sig_ptrs, self.hbuf_mc or None, self.rows_cap,
+            residual.data_ptr() if residual is not None else None,
+            norm_w.data_ptr() if norm_w is not None else None, float(eps), self.epoch & 0x7FFFFFFF, mode,
+            self.comm_ctas, torch.cuda.current_stream().cuda_stream)
+        kcuda._check(code, "gemm_rs_norm_ag")
+        return self.hbuf[:T]
 
     def reduce_add_norm(self, y, residual, norm_w, eps) -> torch.Tensor:
         T = y.shape[0]

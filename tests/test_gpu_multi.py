@@ -55,6 +55,29 @@ def _worker(rank, world, port, use_mc, q):
         ar = fc.all_reduce(parts[rank])
         torch.cuda.synchronize()
         errs.append((T, (ar.float() - total).abs().max().item() / max(1.0, total.abs().max().item()), 0.0))
+    # single-kernel GEMM + reduce-scatter + norm + all-gather vs (local GEMMs summed in fp32 -> reference norm)
+    ferrs = []
+    for T, K in ((1, 256), (64, 512), (300, 1024), (500, 384)):
+        g = torch.Generator(device=dev).manual_seed(7 * T + K)
+        xs = [(torch.randn(T, K, device=dev, generator=g) * 0.5).to(torch.bfloat16) for _ in range(world)]
+        wsl = [(torch.randn(H, K, device=dev, generator=g) * 0.05).to(torch.bfloat16) for _ in range(world)]
+        res0 = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(H, device=dev, generator=g)).to(torch.bfloat16)
+        total = sum((x.float() @ ww.float().t()).to(torch.bfloat16).float() for x, ww in zip(xs, wsl))
+        res_ref = (total + res0.float()).to(torch.bfloat16)
+        want = ref.rms_norm(res_ref, w, 1e-6)
+        residual = res0.clone()
+        out = fc.gemm_reduce_add_norm(xs[rank], wsl[rank], residual, w, 1e-6).clone()
+        torch.cuda.synchronize()
+        rows_per = (T + world - 1) // world
+        lo, hi = rank * rows_per, min(T, (rank + 1) * rows_per)
+        e1 = (out.float() - want.float()).abs().max().item()
+        e2 = (residual[lo:hi].float() - res_ref[lo:hi].float()).abs().max().item() if hi > lo else 0.0
+        ferrs.append((T, K, e1, e2))
+        out2 = fc.gemm_reduce_add_norm(xs[rank], wsl[rank], res0.clone(), w, 1e-6).clone()
+        torch.cuda.synchronize()
+        ferrs.append((T, K, 0.0 if torch.equal(out, out2) else 1.0, 0.0))  # deterministic
+    report["ferrs"] = ferrs
     report["errs"] = errs
     report["kernel_error"] = cuda.read_error()
 
@@ -104,4 +127,6 @@ def test_fused_reduce_norm_two_ranks(use_mc):
     assert rep["kernel_error"] == 0 and rep["kernel_error2"] == 0
     for T, e1, e2 in rep["errs"]:
         assert e1 < 6e-2 and e2 < 6e-2, (T, e1, e2)
+    for T, K, e1, e2 in rep["ferrs"]:
+        assert e1 < 8e-2 and e2 < 8e-2, (T, K, e1, e2)
     assert rep["model_err"] < 0.05 * max(1.0, rep["model_ref_max"])
