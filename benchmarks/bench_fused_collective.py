@@ -1,0 +1,102 @@
+#!/usr/bin/env python
+"""Micro-benchmark of the row-parallel "GEMM -> all-reduce -> residual add -> RMSNorm" block under tensor parallelism.
+
+Three implementations of the same math, timed on the device (CUDA events, max over ranks, L2 flushed between
+iterations by cycling through distinct weight copies larger than L2):
+  fused1   one kernel: tcgen05 GEMM whose epilogue pushes tiles to the row owners + communication CTAs
+           (csrc/cuda/gemm_fused_rs.cu)
+  fused2   tcgen05 GEMM into symmetric memory, then the reduce/add/norm/gather kernel (csrc/cuda/comm_fused.cu)
+  nccl     cuBLAS GEMM -> NCCL all-reduce -> add + RMSNorm kernel (the library baseline)
+Roofline per call = max(2*M*N*K / measured bf16 GEMM peak, bytes over NVLink / link bandwidth) with bytes =
+(ws-1)/ws * M*N*2 out (reduce-scatter) and the same in (all-gather) per GPU, one per direction; `roofline_hbm_us`
+additionally counts the time to stream this rank's weight slice once from HBM (the real bound for small M).
+Peaks come from MEASURED_PEAKS.json when present (else 1590 TFLOP/s, 6650 GB/s, 770 GB/s per direction).
+
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/bench_fused_collective.py
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from ksanallm_b200.ops import cuda  # noqa: E402
+from ksanallm_b200.parallel.comm import init_distributed  # noqa: E402
+
+
+def main():
+    tp = init_distributed("cuda")
+    rank, ws, dev = tp.rank, tp.size, tp.device
+    H = int(os.environ.get("BENCH_HIDDEN", "8192"))
+    Kfull = int(os.environ.get("BENCH_K", "28672"))
+    K = Kfull // ws
+    Ms = [int(x) for x in os.environ.get("BENCH_M", "16,64,256,2048,8192").split(",")]
+    tp.init_fused(H, max(Ms))
+    fc = tp.fused
+    peaks = {"bf16_tflops": 1590.0, "nvlink_gbs": 770.0, "hbm_gbs": 6650.0}
+    pk = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        mp = json.load(open(pk))
+        peaks["bf16_tflops"] = float(mp.get("bf16_tflops", 1590.0))
+        peaks["hbm_gbs"] = float(mp.get("hbm_gbs", 6650.0))
+    ncopies = max(2, int(256e6 // (H * K * 2)) + 1)  # cycle through > L2 worth of weights
+    ws_list = [(torch.randn(H, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(ncopies)]
+    norm_w = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    rows = []
+    for M in Ms:
+        x = (torch.randn(M, K, device=dev) * 0.5).to(torch.bfloat16)
+        residual = torch.zeros(M, H, device=dev, dtype=torch.bfloat16)
+
+        def run_fused1(i):
+            fc.gemm_reduce_add_norm(x, ws_list[i % ncopies], residual, norm_w, 1e-6)
+
+        def run_fused2(i):
+            cuda.gemm_bf16(x, ws_list[i % ncopies], None, out=fc.partial[:M])
+            fc._launch(M, residual, norm_w, 1e-6)
+
+        def run_nccl(i):
+            y = torch.nn.functional.linear(x, ws_list[i % ncopies])
+            dist.all_reduce(y)
+            cuda.rms_norm(y, norm_w, 1e-6, residual)
+
+        res = {}
+        for name, fn in (("fused1", run_fused1), ("fused2", run_fused2), ("nccl", run_nccl)):
+            for i in range(5):
+                fn(i)
+            torch.cuda.synchronize()
+            dist.barrier()
+            iters = 30
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(iters):
+                fn(i)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], device=dev)  # us
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[name] = float(t.item())
+            dist.barrier()
+        flops = 2.0 * M * H * K
+        t_gemm = flops / (peaks["bf16_tflops"] * 1e12) * 1e6
+        link_bytes = (ws - 1) / ws * M * H * 2
+        t_link = link_bytes / (peaks["nvlink_gbs"] * 1e9) * 1e6  # RS out and AG in run in opposite directions
+        roof = max(t_gemm, t_link)
+        t_hbm = (H * K * 2 + M * K * 2) / (peaks["hbm_gbs"] * 1e9) * 1e6
+        rows.append(dict(M=M, N=H, K=K, ws=ws, roofline_us=round(roof, 2), roofline_hbm_us=round(max(roof, t_hbm), 2),
+                         gemm_us=round(t_gemm, 2),
+                         link_us=round(t_link, 2), **{k: round(v, 2) for k, v in res.items()},
+                         fused1_frac=round(roof / res["fused1"], 3), fused2_frac=round(roof / res["fused2"], 3),
+                         nccl_frac=round(roof / res["nccl"], 3)))
+    if rank == 0:
+        print(json.dumps({"multicast": fc.multicast, "kernel_error": cuda.read_error(), "rows": rows}, indent=1))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -52,12 +52,12 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // records KERR_PEER_TIMEOUT on expiry, so a missing peer can never hang the GPU.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, unsigned int* err,
                                              unsigned long long timeout_ns = KSANA_PEER_TIMEOUT_NS) {
-  for (int it = 0; it < 2048; ++it)
+  for (int it = 0; it < 64; ++it)
     if (static_cast<int32_t>(ld_acquire_sys(p) - want) >= 0) return true;
   const unsigned long long t0 = global_timer_ns();
   while (true) {
     if (static_cast<int32_t>(ld_acquire_sys(p) - want) >= 0) return true;
-    __nanosleep(200);
+    __nanosleep(400);
     if (global_timer_ns() - t0 > timeout_ns) break;
   }
   if (err) atomicOr(err, KERR_PEER_TIMEOUT);

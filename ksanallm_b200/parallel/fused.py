@@ -71,7 +71,8 @@ class FusedComm:
                                               ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                               ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                               ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
-                                              ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+                                              ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_void_p]
         lib.ksana_gemm_rs_norm_ag.restype = ctypes.c_int
         self._lib = lib
         dist.barrier(group=group)
@@ -109,7 +110,7 @@ class FusedComm:
         """GEMM straight into the symmetric ``partial`` buffer, then the fused reduce/add/norm/gather kernel.
         The returned tensor is a view of ``hbuf`` (valid until the next fused call)."""
         T = x.shape[0]
-        if (self.single_kernel and lin.kind == "dense" and lin.bias is None and self.hidden % 128 == 0 and
+        if (self.single_kernel and lin.kind == "dense" and lin.bias is None and self.hidden % 256 == 0 and
                 self.hidden <= 9216 and T <= 8192 and x.dim() == 2 and residual is not None and
                 residual.is_contiguous()):
             return self.gemm_reduce_add_norm(x, lin.weight, residual, norm_w, eps)
@@ -132,7 +133,7 @@ class FusedComm:
             self._recv_ptrs, self._hbuf_ptrs, self._sig_ptrs, self.hbuf_mc or None, self.rows_cap,
             residual.data_ptr() if residual is not None else None,
             norm_w.data_ptr() if norm_w is not None else None, float(eps), self.epoch & 0x7FFFFFFF, mode,
-            self.comm_ctas, torch.cuda.current_stream().cuda_stream)
+            self.comm_ctas, 0, torch.cuda.current_stream().cuda_stream)
         kcuda._check(code, "gemm_rs_norm_ag")
         return self.hbuf[:T]
 
