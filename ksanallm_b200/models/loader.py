@@ -346,10 +346,10 @@ class WeightLoader:
         p = self._pending[key]
         if key.endswith(".self_attn"):
             if cfg.use_mla:
-                ok = self._have(p, "kv_a_proj_with_mqa") and "kv_a_layernorm.weight" in p and \
-                    self._have(p, "kv_b_proj") and self._have(p, "o_proj")
+                # (the *_layernorm weights never enter the pending set: norm tensors are placed directly)
+                ok = self._have(p, "kv_a_proj_with_mqa") and self._have(p, "kv_b_proj") and self._have(p, "o_proj")
                 if cfg.q_lora_rank:
-                    ok = ok and self._have(p, "q_a_proj") and "q_a_layernorm.weight" in p and self._have(p, "q_b_proj")
+                    ok = ok and self._have(p, "q_a_proj") and self._have(p, "q_b_proj")
                 else:
                     ok = ok and self._have(p, "q_proj")
                 if ok:
@@ -359,8 +359,7 @@ class WeightLoader:
             qkv = (self._have(p, "q_proj", b) and self._have(p, "k_proj", b) and self._have(p, "v_proj", b)) or \
                 self._have(p, "wpack", b) or self._have(p, "wpack_t", b) or self._have(p, "wqkv", b)
             o = self._have(p, "o_proj", cfg.o_bias) or self._have(p, "o_proj_t", cfg.o_bias)
-            nrm = (not cfg.qk_norm) or ("query_layernorm.weight" in p and "key_layernorm.weight" in p)
-            if qkv and o and nrm:
+            if qkv and o:
                 self._finish_attn(key, self._pending.pop(key))
             return
         if key.endswith(".mlp"):
@@ -458,9 +457,6 @@ class WeightLoader:
         ob = p.get("o_proj.bias", p.get("o_proj_t.bias"))
         if ob is not None:
             self._put(f"{key}.o_proj.bias", ob)
-        for nm in ("query_layernorm.weight", "key_layernorm.weight"):
-            if nm in p:
-                self._put(f"{key}.{nm}", p[nm])
 
     def _finish_mla(self, key: str, p: Dict[str, torch.Tensor]) -> None:
         cfg, r, n = self.cfg, self.rank, self.size
@@ -485,14 +481,12 @@ class WeightLoader:
             elif q_a_s is not None:
                 fused = torch.cat((deq("q_a_proj"), deq("kv_a_proj_with_mqa")), 0)
             self._put_linear(f"{key}.fused_lora_a_proj", fused, fs)
-            self._put(f"{key}.q_a_layernorm.weight", p["q_a_layernorm.weight"])
             qb, qbs = p["q_b_proj.weight"], p.get("q_b_proj.weight_scale_inv")
             self._put_linear(f"{key}.q_b_nope_rope_proj", _rows(qb, r, n), None if qbs is None else _rows(qbs, r, n))
         else:
             self._put_linear(f"{key}.fused_lora_a_proj", kv_a, kv_a_s)
             qp, qps = p["q_proj.weight"], p.get("q_proj.weight_scale_inv")
             self._put_linear(f"{key}.q_proj", _rows(qp, r, n), None if qps is None else _rows(qps, r, n))
-        self._put(f"{key}.kv_a_layernorm.weight", p["kv_a_layernorm.weight"])
         # kv_b: [h * (dn + dv), rk] -> absorbed w_uk_t [h, dn, rk] and w_uv [h, rk, dv] (always dequantised)
         kvb = deq("kv_b_proj").to(self.device).float().view(h, dn + dv, rk)
         hl = h // n
