@@ -35,8 +35,19 @@ template <int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ C,
                  const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc, int splits,
-                 float* __restrict__ ws, unsigned int* __restrict__ counters, unsigned int* err) {
+                 float* __restrict__ ws, unsigned int* __restrict__ counters, unsigned int* err,
+                 unsigned long long* trace) {
   using L = GemmSmem<BN, STAGES>;
+  // optional timeline of CTA 0 (nanoseconds of the global timer): [0] entry, [1] set-up done, [2] first operands
+  // landed, [3] last MMA committed, [4] accumulator visible to the epilogue, [5] epilogue done
+  auto stamp = [&](int i) {
+    if (trace != nullptr && blockIdx.x == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      trace[i] = t;
+    }
+  };
+  if (threadIdx.x == 0) stamp(0);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -76,6 +87,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  if (threadIdx.x == 0) stamp(1);
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -130,6 +142,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             break;
           }
           tc_fence_after();
+          if (it == 0 && kb == kb0) stamp(2);
           const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
           const uint64_t da = umma_desc_k128(sa);
           const uint64_t db = umma_desc_k128(sa + L::A_BYTES);
@@ -144,6 +157,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
         if (ok) umma_commit(&acc_full[as]);
+        if (it == 0) stamp(3);
       }
     }
   } else {
@@ -170,6 +184,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok_all) break;
       }
       tc_fence_after();
+      if (it == 0 && threadIdx.x == 64) stamp(4);
       const int row = m_idx * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
       bool reduce_here = true;
@@ -267,6 +282,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[as]);
+      if (it == 0 && threadIdx.x == 64) stamp(5);
     }
   }
 
@@ -276,11 +292,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN);
   }
+  if (threadIdx.x == 0) stamp(6);
 }
 
 template <int BN, int STAGES, typename OutT>
 static int launch_gemm(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda, int ldw,
-                       int ldc, int splits, float* ws, unsigned int* counters, int max_ctas, cudaStream_t stream) {
+                       int ldc, int splits, float* ws, unsigned int* counters, int max_ctas, cudaStream_t stream,
+                       unsigned long long* trace = nullptr) {
   using L = GemmSmem<BN, STAGES>;
   CUtensorMap tmA, tmB;
   if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B)) return -2;
@@ -296,11 +314,15 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
   if (grid > max_ctas) grid = max_ctas;
   kern<<<grid, 192, L::TOTAL, stream>>>(tmA, tmB, reinterpret_cast<OutT*>(C),
                                         reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, splits, ws, counters,
-                                        error_word());
+                                        error_word(), trace);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 }  // namespace ksana
+
+static unsigned long long* g_gemm_trace = nullptr;
+// Debug aid: device buffer of 8 uint64 that receives the timeline of CTA 0 of subsequent GEMM launches (nullptr: off).
+KSANA_API void ksana_gemm_set_trace(void* buf) { g_gemm_trace = reinterpret_cast<unsigned long long*>(buf); }
 
 // C[M, N] = A[M, K] * W[N, K]^T (+ bias[N]). A, W bf16 with row pitches lda / ldw (elements, multiples of 8,
 // base pointers 16-byte aligned); C bf16 (out_fp32 = 0) or fp32 (out_fp32 = 1) with row pitch ldc; N % 8 == 0.
@@ -341,9 +363,9 @@ KSANA_API int ksana_gemm_bf16(const void* A, const void* W, void* C, const void*
     splits = 1;
 #define KSANA_GEMM_CASE(BN_, ST_)                                                                                   \
   return out_fp32 ? launch_gemm<BN_, ST_, float>(A, W, C, bias, M, N, K, lda, ldw, ldc, splits, ws, counters, sms, \
-                                                 stream)                                                            \
+                                                 stream, g_gemm_trace)                                              \
                   : launch_gemm<BN_, ST_, __nv_bfloat16>(A, W, C, bias, M, N, K, lda, ldw, ldc, splits, ws,        \
-                                                         counters, sms, stream)
+                                                         counters, sms, stream, g_gemm_trace)
   if (bn == 64) { KSANA_GEMM_CASE(64, 8); }
   if (bn == 256) { KSANA_GEMM_CASE(256, 4); }
   KSANA_GEMM_CASE(128, 6);
