@@ -320,6 +320,11 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
 
 }  // namespace ksana
 
+namespace ksana {
+int gemm_bf16_cluster_splitk(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda,
+                             int ldw, int ldc, int out_fp32, int splits, cudaStream_t stream);
+}
+
 static unsigned long long* g_gemm_trace = nullptr;
 // Debug aid: device buffer of 8 uint64 that receives the timeline of CTA 0 of subsequent GEMM launches (nullptr: off).
 KSANA_API void ksana_gemm_set_trace(void* buf) { g_gemm_trace = reinterpret_cast<unsigned long long*>(buf); }
@@ -338,24 +343,36 @@ KSANA_API int ksana_gemm_bf16(const void* A, const void* W, void* C, const void*
   const int sms = sm_count();
   const int tiles_m = (M + BM - 1) / BM;
   if (bn == 0) {
+    // A CTA's K loop is latency-bound (~0.3 us per 64-wide k-block whatever the tile width), so the cost of a
+    // launch is (number of waves) x (k-blocks) with a ~15 % surcharge for the wider tile: pick the cheaper one.
     const int t256 = tiles_m * ((N + 255) / 256);
     const int t128 = tiles_m * ((N + 127) / 128);
-    if (t256 >= 2 * sms) bn = 256;
-    else if (t128 >= sms || N < 128) bn = 128;
-    else bn = 128;
+    const float c128 = static_cast<float>((t128 + sms - 1) / sms);
+    const float c256 = 1.15f * static_cast<float>((t256 + sms - 1) / sms);
+    bn = (c256 < c128) ? 256 : 128;
+    if (t128 * 2 <= sms) bn = 128;  // few tiles: the cluster split-K path below takes over
     if (N <= 64) bn = 64;
   }
-  const int tiles = tiles_m * ((N + bn - 1) / bn);
   const int num_kb = (K + BK - 1) / BK;
-  int splits = 1;
-  if (force_splits > 0) {
-    splits = force_splits;
-  } else if (tiles * 2 <= sms && num_kb >= 8) {
-    splits = sms / tiles;
-    if (splits > 8) splits = 8;
-    if (splits > num_kb / 4) splits = num_kb / 4;
-    if (splits < 1) splits = 1;
+  // ---- small M: K-splits of a tile run as one thread-block cluster and reduce through distributed shared memory.
+  // force_splits > 0 requests that many splits (2 / 4 / 8 take the cluster path), force_splits < 0 requests
+  // |force_splits| splits through the global-workspace reduction below.
+  {
+    const int tiles128 = tiles_m * ((N + 127) / 128);
+    int cs = 0;
+    if (force_splits == 2 || force_splits == 4 || force_splits == 8) {
+      cs = force_splits;
+    } else if (force_splits == 0 && (bn == 128 || bn == 64) && tiles128 * 2 <= sms && num_kb >= 8) {
+      cs = 8;
+      while (cs > 1 && (cs * tiles128 > sms + tiles128 / 2 || num_kb / cs < 4)) cs >>= 1;
+    }
+    if (cs >= 2 && (bn == 0 || bn == 128 || force_splits == 0) && ((num_kb + cs - 1) / cs) * (cs - 1) < num_kb &&
+        cs <= sms)
+      return gemm_bf16_cluster_splitk(A, W, C, bias, M, N, K, lda, ldw, ldc, out_fp32, cs, stream);
   }
+  if (force_splits < 0) force_splits = -force_splits;
+  const int tiles = tiles_m * ((N + bn - 1) / bn);
+  int splits = 1;
   // every split must own at least one k-block
   while (splits > 1 && ((num_kb + splits - 1) / splits) * (splits - 1) >= num_kb) --splits;
   if (splits > 1 && (ws == nullptr || counters == nullptr || static_cast<long long>(splits) * M * N > ws_floats ||

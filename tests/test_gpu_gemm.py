@@ -39,10 +39,13 @@ def test_gemm_tile_widths(bn):
     _check(260, 776, 520, bn=bn)  # ragged N and K tails
 
 
-@pytest.mark.parametrize("splits", [2, 3, 4, 8])
+@pytest.mark.parametrize("splits", [2, 3, 4, 8, -2, -4])
 def test_gemm_split_k(splits):
+    """2 / 4 / 8: thread-block-cluster reduction through distributed shared memory; 3 and negative values: the
+    global-workspace reduction."""
     _check(48, 512, 4096, splits=splits)
     _check(48, 512, 4096, splits=splits, bias=True)
+    _check(200, 384, 2048, splits=splits, out_fp32=True)
 
 
 def test_gemm_bias_fp32_out_and_strided_input():
