@@ -46,6 +46,8 @@ class _Sig:
     ksana_moe_permute = ([P, I, P, I, I, I, I, I, P, P, P, P, P], I)
     ksana_moe_grouped_gemm = ([P, P, P, P, I, I, I, I, P], I)
     ksana_moe_combine = ([P, P, P, I, I, I, P, P], I)
+    ksana_mla_decode = ([P, I, P, I, P, I, P, P, I, I, I, I, I, F, P, P, LL, P], I)
+    ksana_mla_cache_append = ([P, I, P, I, P, P, I, I, I, P], I)
     ksana_rms_norm = ([P, I, P, I, P, P, I, I, I, F, P], I)
     ksana_silu_mul = ([P, I, P, I, I, I, P], I)
     ksana_embedding = ([P, P, P, I, I, I, F, P], I)
