@@ -7,6 +7,7 @@ each case is small (at most a few GB on the device) and launches its kernel a ha
     python benchmarks/kernel_cases.py gemm_fp8 [M N K]        # block-scaled fp8 GEMM
     python benchmarks/kernel_cases.py decode [B ctx h hk]     # paged split-KV decode attention
     python benchmarks/kernel_cases.py prefill [T h hk]        # tcgen05 paged prefill attention
+    python benchmarks/kernel_cases.py mla [B ctx h q_len]     # tcgen05 absorbed-MLA decode over the latent cache
     python benchmarks/kernel_cases.py rmsnorm [T H]
     python benchmarks/kernel_cases.py moe [T E k H I]
     python benchmarks/kernel_cases.py all
@@ -126,6 +127,27 @@ def case_prefill():
                 frac_of_measured_bf16=round(fl / us / 1e6 / p["bf16_tflops"], 3))
 
 
+def case_mla():
+    from ksanallm_b200.ops import cuda_mla
+    B, ctx, h, ql = args_or([64, 4096, 128, 1])
+    bs = 64
+    nb = (ctx + bs - 1) // bs
+    cache = (torch.randn(B * nb + 1, bs, 576, device=DEV) * 0.3).to(torch.bfloat16)
+    bt = torch.arange(B * nb, dtype=torch.int32).reshape(B, nb)
+    cu = [i * ql for i in range(B + 1)]
+    T = B * ql
+    q_lat = (torch.randn(T, h, 512, device=DEV) * 0.3).to(torch.bfloat16)
+    q_rope = (torch.randn(T, h, 64, device=DEV) * 0.3).to(torch.bfloat16)
+    meta = make_step_input([0] * T, [0] * T, [0] * T, cu, [ctx] * B, bt, num_prefill=0, device=DEV)
+    us = timeit(lambda i: cuda_mla.mla_paged_attention(q_lat, q_rope, cache, meta, 0.1147))
+    by = B * ctx * 576 * 2
+    fl = 2.0 * T * h * ctx * (576 + 512)
+    p = peaks()
+    return dict(kernel="mla_decode", B=B, ctx=ctx, h=h, q_len=ql, us=round(us, 1), kv_gb=round(by / 1e9, 3),
+                gbs=round(by / us / 1e3, 1), frac_of_measured_hbm=round(by / us / 1e3 / p["hbm_gbs"], 3),
+                tflops=round(fl / us / 1e6, 1), frac_of_measured_bf16=round(fl / us / 1e6 / p["bf16_tflops"], 3))
+
+
 def case_rmsnorm():
     T, H = args_or([16384, 8192])
     xs = [torch.randn(T, H, device=DEV).to(torch.bfloat16) for _ in range(2)]
@@ -151,7 +173,7 @@ def case_moe():
                 tflops=round(fl / us / 1e6, 1), frac_of_measured_bf16=round(fl / us / 1e6 / p["bf16_tflops"], 3))
 
 
-CASES = dict(gemm=case_gemm, gemm_fp8=case_gemm_fp8, decode=case_decode, prefill=case_prefill, rmsnorm=case_rmsnorm,
+CASES = dict(gemm=case_gemm, gemm_fp8=case_gemm_fp8, decode=case_decode, prefill=case_prefill, mla=case_mla, rmsnorm=case_rmsnorm,
              moe=case_moe)
 
 if __name__ == "__main__":

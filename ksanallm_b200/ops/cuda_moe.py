@@ -30,16 +30,14 @@ def moe_route(logits, top_k, scoring="softmax", norm_topk=False, n_group=1, topk
     return ids, w
 
 
-def moe_experts(x, ids, weights, w_gate_up, w_down, expert_offset=0):
-    """x [T, H] bf16; ids/weights [T, k]; w_gate_up [E_local, 2I, H]; w_down [E_local, H, I] (bf16, contiguous)."""
+def expert_pipeline(x, ids, w_gate_up, w_down, expert_offset=0):
+    """Sort the (token, slot) pairs by local expert and run gate_up -> SiLU*mul -> down on the sorted rows.
+    Returns (y [T*k, H] sorted expert outputs, pos [T*k] sorted row of each pair or -1 for non-local experts)."""
     from . import cuda
     T, H = x.shape
     k = ids.shape[1]
     E_local, two_i, _ = w_gate_up.shape
     I_ = two_i // 2
-    if (x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16 or two_i % 128 or H % 128 or I_ % 8 or
-            not w_gate_up.is_contiguous() or not w_down.is_contiguous()):
-        return ref.moe_experts(x, ids, weights, w_gate_up, w_down, expert_offset)
     dev = x.device
     key = (dev.index, E_local)
     meta = _meta.get(key)
@@ -63,8 +61,25 @@ def moe_experts(x, ids, weights, w_gate_up, w_down, expert_offset=0):
     y = torch.empty(n, H, dtype=torch.bfloat16, device=dev)
     cuda._check(lib.ksana_moe_grouped_gemm(cuda._ptr(a), cuda._ptr(w_down), cuda._ptr(y), cuda._ptr(offsets), E_local,
                                            n, H, I_, st), "moe_grouped_gemm(down)")
-    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    return y, pos
+
+
+def supports(x, w_gate_up, w_down) -> bool:
+    two_i, H = w_gate_up.shape[1], x.shape[1]
+    return (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and two_i % 128 == 0 and H % 128 == 0 and
+            (two_i // 2) % 8 == 0 and w_gate_up.is_contiguous() and w_down.is_contiguous())
+
+
+def moe_experts(x, ids, weights, w_gate_up, w_down, expert_offset=0):
+    """x [T, H] bf16; ids/weights [T, k]; w_gate_up [E_local, 2I, H]; w_down [E_local, H, I] (bf16, contiguous)."""
+    from . import cuda
+    if not supports(x, w_gate_up, w_down):
+        return ref.moe_experts(x, ids, weights, w_gate_up, w_down, expert_offset)
+    T, H = x.shape
+    k = ids.shape[1]
+    y, pos = expert_pipeline(x, ids, w_gate_up, w_down, expert_offset)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
     wc = weights if weights.dtype == torch.float32 and weights.is_contiguous() else weights.float().contiguous()
-    cuda._check(lib.ksana_moe_combine(cuda._ptr(y), cuda._ptr(pos), cuda._ptr(wc), T, k, H, cuda._ptr(out), st),
-                "moe_combine")
+    cuda._check(cuda.lib().ksana_moe_combine(cuda._ptr(y), cuda._ptr(pos), cuda._ptr(wc), T, k, H, cuda._ptr(out),
+                                             cuda._stream()), "moe_combine")
     return out

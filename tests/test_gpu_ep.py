@@ -1,0 +1,85 @@
+"""Expert-parallel dispatch / combine over peer memory (one process per GPU) against the fp32 reference MoE."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    from ksanallm_b200.ops import cuda
+    from ksanallm_b200.ops import reference as ref
+    from ksanallm_b200.parallel.comm import init_distributed
+    from ksanallm_b200.parallel.ep import EPExchange
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    tp = init_distributed("cuda", use_fused=False)
+    dev = tp.device
+    E, k, H, I = 16, 4, 512, 256
+    g = torch.Generator(device=dev).manual_seed(11)  # same weights on every rank
+    w1 = (torch.randn(E, 2 * I, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    el = E // world
+    w1_l, w2_l = w1[rank * el:(rank + 1) * el].contiguous(), w2[rank * el:(rank + 1) * el].contiguous()
+    ex = EPExchange(tp.group, rank, world, dev, H, k, E, max_tokens_per_rank=128)
+    errs = []
+    for it, (t_stride, t_of) in enumerate(((64, lambda r: 37 + 9 * r), (8, lambda r: 1 + (r % 2)), (128, lambda r: 128),
+                                            (16, lambda r: 0 if r == 1 else 16), (64, lambda r: 64 - r))):
+        T = min(t_of(rank), t_stride)
+        gl = torch.Generator(device=dev).manual_seed(1000 * it + rank)
+        x = (torch.randn(T, H, device=dev, generator=gl) * 0.5).to(torch.bfloat16)
+        logits = torch.randn(T, E, device=dev, generator=gl)
+        ids, w = ref.moe_route(logits, k, "softmax", True)
+        add = (torch.randn(T, H, device=dev, generator=gl) * 0.1).to(torch.bfloat16) if it % 2 else None
+        out = ex.moe(x, ids, w, w1_l, w2_l, t_stride, add)
+        torch.cuda.synchronize()
+        if T:
+            want = ref.moe_experts(x, ids, w, w1, w2, 0).float()
+            if add is not None:
+                want = want + add.float()
+            errs.append((it, T, (out.float() - want).abs().max().item(), want.abs().max().item()))
+    dist.barrier()
+    allerrs = [None] * world
+    dist.all_gather_object(allerrs, (errs, cuda.read_error()))
+    if rank == 0:
+        q.put(allerrs)
+    dist.destroy_process_group()
+
+
+def _worlds():
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return sorted({w for w in (2, 4, 8) if w <= n})
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ep_dispatch_combine(world):
+    if world not in _worlds():
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    rep = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    print(rep)
+    for errs, kerr in rep:
+        assert kerr == 0
+        for it, T, e, m in errs:
+            assert e < 3e-2 * max(1.0, m), (it, T, e, m)

@@ -1,4 +1,4 @@
-"""Multi-GPU tests (2 ranks, one process per GPU): fused reduce + residual + RMSNorm + gather kernel over
+"""Multi-GPU tests (2, 4 or 8 ranks, one process per GPU): fused reduce + residual + RMSNorm + gather kernel over
 symmetric memory, with and without the NVLS multicast path, and a tensor-parallel model forward."""
 import os
 import socket
@@ -83,7 +83,7 @@ def _worker(rank, world, port, use_mc, q):
 
     # tensor-parallel forward vs the single-rank forward of the same weights
     cfg = model_config_from_dict(dict(model_type="llama", hidden_size=H, num_hidden_layers=2, num_attention_heads=8,
-                                      num_key_value_heads=4, intermediate_size=2816, vocab_size=1000,
+                                      num_key_value_heads=8, intermediate_size=2816, vocab_size=1000,
                                       torch_dtype="bfloat16"))
     w_tp = load_model_weights(cfg, synthetic_seed=3, tp_rank=rank, tp_size=world, device=dev, dtype=torch.bfloat16)
     m_tp = TransformerModel(cfg, w_tp, tp, max_positions=512)
@@ -108,15 +108,16 @@ def _worker(rank, world, port, use_mc, q):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("use_mc", [False, True])
-def test_fused_reduce_norm_two_ranks(use_mc):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+def test_fused_reduce_norm_ranks(use_mc, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, use_mc, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, use_mc, q)) for r in range(world)]
     for p in procs:
         p.start()
     rep = q.get(timeout=240)
