@@ -29,6 +29,99 @@ from ksanallm_b200.ops import cuda  # noqa: E402
 from ksanallm_b200.parallel.comm import init_distributed  # noqa: E402
 
 
+def _time(fn, dev, iters=20, warm=4):
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    return float(t.item())
+
+
+def bench_allgather_gemm(tp, fc, peaks, Ms, H):
+    """Column-parallel GEMM on a row-sharded activation: C[M, N/ws] = all_gather(A_r)[M, H] * W_r^T.
+    fused = one kernel reading A tiles from the owners over NVLink; nccl = all_gather + cuBLAS."""
+    rank, ws, dev = tp.rank, tp.size, tp.device
+    N = int(os.environ.get("BENCH_AG_N", "28672")) // ws
+    ncopies = max(2, int(256e6 // (H * N * 2)) + 1)
+    wl = [(torch.randn(N, H, device=dev) * 0.02).to(torch.bfloat16) for _ in range(ncopies)]
+    out = []
+    for M in Ms:
+        rows_per = (M + ws - 1) // ws
+        if rows_per > fc.rows_cap:
+            continue
+        mine = (torch.randn(rows_per, H, device=dev) * 0.5).to(torch.bfloat16)
+        gathered = torch.empty(ws * rows_per, H, device=dev, dtype=torch.bfloat16)
+
+        def run_fused(i):
+            fc.ag_rows(rows_per).copy_(mine)
+            fc.gemm_allgather(rows_per, M, wl[i % ncopies])
+
+        def run_nccl(i):
+            dist.all_gather_into_tensor(gathered, mine)
+            torch.nn.functional.linear(gathered[:M], wl[i % ncopies])
+
+        tf, tn = _time(run_fused, dev), _time(run_nccl, dev)
+        t_gemm = 2.0 * M * N * H / (peaks["bf16_tflops"] * 1e12) * 1e6
+        t_link = (ws - 1) / ws * M * H * 2 / (peaks["nvlink_gbs"] * 1e9) * 1e6
+        roof = max(t_gemm, t_link)
+        out.append(dict(M=M, N=N, K=H, ws=ws, roofline_us=round(roof, 2), fused_us=round(tf, 2), nccl_us=round(tn, 2),
+                        fused_frac=round(roof / tf, 3), nccl_frac=round(roof / tn, 3)))
+    return out
+
+
+def bench_ep(tp, peaks):
+    """MoE block under expert parallelism, each rank owning T/ws tokens: peer-memory dispatch/combine kernels vs
+    the replicated-token formulation (all_gather tokens, every rank runs its experts on all of them, reduce_scatter)."""
+    from ksanallm_b200.ops import cuda_moe
+    from ksanallm_b200.ops import reference as ref
+    from ksanallm_b200.parallel.ep import EPExchange
+    rank, ws, dev = tp.rank, tp.size, tp.device
+    E, k = int(os.environ.get("BENCH_EP_E", "64")), 8
+    H, I = int(os.environ.get("BENCH_EP_H", "4096")), int(os.environ.get("BENCH_EP_I", "1024"))
+    el = E // ws
+    w1 = (torch.randn(el, 2 * I, H, device=dev) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(el, H, I, device=dev) * 0.02).to(torch.bfloat16)
+    Ts = [int(x) for x in os.environ.get("BENCH_EP_T", "16,128,1024").split(",")]
+    ex = EPExchange(tp.group, rank, ws, dev, H, k, E, max(Ts))
+    out = []
+    for Tl in Ts:
+        x = (torch.randn(Tl, H, device=dev) * 0.5).to(torch.bfloat16)
+        ids, w = ref.moe_route(torch.randn(Tl, E, device=dev), k, "softmax", True)
+        ids = ids.to(torch.int32)
+        xg = torch.empty(ws * Tl, H, device=dev, dtype=torch.bfloat16)
+        idg = torch.empty(ws * Tl, k, device=dev, dtype=torch.int32)
+        wg = torch.empty(ws * Tl, k, device=dev, dtype=torch.float32)
+        ys = torch.empty(Tl, H, device=dev, dtype=torch.bfloat16)
+
+        def run_ep(i):
+            ex.moe(x, ids, w, w1, w2, Tl)
+
+        def run_repl(i):
+            dist.all_gather_into_tensor(xg, x)
+            dist.all_gather_into_tensor(idg, ids)
+            dist.all_gather_into_tensor(wg, w)
+            y = cuda_moe.moe_experts(xg, idg, wg, w1, w2, rank * el)
+            dist.reduce_scatter_tensor(ys, y)
+
+        te, tr = _time(run_ep, dev), _time(run_repl, dev)
+        flops = 2.0 * Tl * k * 3 * H * I  # per rank on average
+        link = 2.0 * Tl * min(k, ws - 1) * (ws - 1) / ws * H * 2 / 2  # out + back, one per direction (upper bound)
+        roof = max(flops / (peaks["bf16_tflops"] * 1e12), link / (peaks["nvlink_gbs"] * 1e9),
+                   3 * el * H * I * 2 / (peaks["hbm_gbs"] * 1e9)) * 1e6
+        out.append(dict(tokens_per_rank=Tl, E=E, k=k, H=H, I=I, ws=ws, roofline_us=round(roof, 2),
+                        ep_dispatch_us=round(te, 2), replicated_nccl_us=round(tr, 2)))
+    return out
+
+
 def main():
     tp = init_distributed("cuda")
     rank, ws, dev = tp.rank, tp.size, tp.device
@@ -92,8 +185,11 @@ def main():
                          link_us=round(t_link, 2), **{k: round(v, 2) for k, v in res.items()},
                          fused1_frac=round(roof / res["fused1"], 3), fused2_frac=round(roof / res["fused2"], 3),
                          nccl_frac=round(roof / res["nccl"], 3)))
+    ag_rows = bench_allgather_gemm(tp, fc, peaks, Ms, H) if os.environ.get("BENCH_AG", "1") == "1" else []
+    ep_rows = bench_ep(tp, peaks) if os.environ.get("BENCH_EP", "1") == "1" else []
     if rank == 0:
-        print(json.dumps({"multicast": fc.multicast, "kernel_error": cuda.read_error(), "rows": rows}, indent=1))
+        print(json.dumps({"multicast": fc.multicast, "kernel_error": cuda.read_error(), "rows": rows,
+                          "allgather_gemm": ag_rows, "ep_moe": ep_rows}, indent=1))
     dist.barrier()
     dist.destroy_process_group()
 

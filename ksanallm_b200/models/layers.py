@@ -190,6 +190,10 @@ class MoEFFN:
     def partial(self, h: torch.Tensor) -> torch.Tensor:
         """Per-rank partial sum of the block output (needs a cross-rank sum when size > 1)."""
         c = self.cfg
+        ep = self.tp.ep
+        if (ep is not None and h.is_cuda and h.dtype == torch.bfloat16 and self.e_local < c.num_experts and
+                h.shape[0] <= ep.t_cap * ep.size):
+            return self._partial_dispatch(h, ep)
         logits = ops.linear(h.float() if self.gate_w.dtype == torch.float32 else h, self.gate_w)
         ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
                                  c.topk_group, c.routed_scaling_factor, self.bias)
@@ -200,4 +204,27 @@ class MoEFFN:
                 g = torch.sigmoid(ops.linear(h, self.shared_gate).float()).to(s.dtype)
                 s = s * g
             y = y + s
+        return y
+
+    def _partial_dispatch(self, h: torch.Tensor, ep) -> torch.Tensor:
+        """Expert-parallel path: this rank routes only its own slice of the tokens, sends each row to the ranks
+        hosting its experts and gets the weighted outputs back. The result keeps the "partial sum" contract of
+        ``partial`` (rows owned by other ranks are zero here), so the reduce that follows is unchanged."""
+        c = self.cfg
+        T = h.shape[0]
+        per = (T + ep.size - 1) // ep.size
+        lo, hi = min(T, ep.rank * per), min(T, (ep.rank + 1) * per)
+        mine = h[lo:hi]
+        logits = ops.linear(mine.float() if self.gate_w.dtype == torch.float32 else mine, self.gate_w)
+        ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
+                                 c.topk_group, c.routed_scaling_factor, self.bias)
+        y = torch.zeros_like(h)
+        if self.shared is not None:
+            s = self.shared.down(self.shared.core(h), add_bias=self.tp.rank == 0)
+            if self.shared_gate is not None:
+                s = s * torch.sigmoid(ops.linear(h, self.shared_gate).float()).to(s.dtype)
+            y = s
+        out = ep.moe(mine, ids, wts, self.w_gate_up, self.w_down, per, add=y[lo:hi] if hi > lo else None)
+        if hi > lo:
+            y[lo:hi] = out
         return y

@@ -29,6 +29,7 @@ class TPGroup:
         self.device = device
         self.use_fused = use_fused and size > 1
         self.fused = None  # parallel.fused.FusedComm, attached by init_fused()
+        self.ep = None     # parallel.ep.EPExchange, attached by init_ep()
         self.stats = {"all_reduce": 0, "all_gather": 0, "fused": 0}
 
     def init_fused(self, hidden: int, max_tokens: int, use_multicast: Optional[bool] = None) -> bool:
@@ -41,6 +42,18 @@ class TPGroup:
         return True
 
     # ---- plain collectives ------------------------------------------------------------------------
+    def init_ep(self, hidden: int, top_k: int, num_experts: int, max_tokens: int) -> bool:
+        """Attaches the peer-memory expert-parallel exchange (token dispatch / combine instead of running every
+        local expert over every token). Only for CUDA groups of 2..8 ranks with experts divisible by the size."""
+        if self.size < 2 or self.size > 8 or self.device is None or self.device.type != "cuda":
+            return False
+        if num_experts % self.size:
+            return False
+        from .ep import EPExchange
+        per_rank = (max_tokens + self.size - 1) // self.size
+        self.ep = EPExchange(self.group, self.rank, self.size, self.device, hidden, top_k, num_experts, per_rank)
+        return True
+
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.size == 1:
             return x

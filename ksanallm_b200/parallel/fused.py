@@ -37,6 +37,11 @@ class FusedComm:
         self.sig = symm_mem.empty(8192, dtype=torch.int32, device=device)
         self.rows_cap = (max_tokens + size - 1) // size
         self.recv = symm_mem.empty(size * self.rows_cap, hidden, dtype=torch.bfloat16, device=device)
+        self.agbuf = symm_mem.empty(self.rows_cap, hidden, dtype=torch.bfloat16, device=device)
+        self.agflags = symm_mem.empty(1024, dtype=torch.int32, device=device)
+        self.ag_staged = torch.empty(size * self.rows_cap, hidden, dtype=torch.bfloat16, device=device)
+        self.agbuf.zero_()
+        self.agflags.zero_()
         self.recv.zero_()
         self.sig.zero_()
         self.partial.zero_()
@@ -46,6 +51,8 @@ class FusedComm:
         self._h_hbuf = symm_mem.rendezvous(self.hbuf, gname)
         self._h_sig = symm_mem.rendezvous(self.sig, gname)
         self._h_recv = symm_mem.rendezvous(self.recv, gname)
+        self._h_agbuf = symm_mem.rendezvous(self.agbuf, gname)
+        self._h_agflags = symm_mem.rendezvous(self.agflags, gname)
         if use_multicast is None:
             use_multicast = os.environ.get("KSANA_DISABLE_MULTIMEM", "0") != "1"
         mc_ok = bool(use_multicast)
@@ -58,6 +65,9 @@ class FusedComm:
         self._hbuf_ptrs = arr(*[int(p) for p in self._h_hbuf.buffer_ptrs])
         self._sig_ptrs = arr(*[int(p) for p in self._h_sig.buffer_ptrs])
         self._recv_ptrs = arr(*[int(p) for p in self._h_recv.buffer_ptrs])
+        self._agbuf_ptrs = arr(*[int(p) for p in self._h_agbuf.buffer_ptrs])
+        self._agflag_ptrs = arr(*[int(p) for p in self._h_agflags.buffer_ptrs])
+        self.ag_epoch = 0
         self.single_kernel = os.environ.get("KSANA_DISABLE_FUSED_GEMM_RS", "0") != "1"
         self.comm_ctas = int(os.environ.get("KSANA_FUSED_COMM_CTAS", "16"))
         self.epoch = 0
@@ -74,6 +84,13 @@ class FusedComm:
                                               ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                               ctypes.c_void_p]
         lib.ksana_gemm_rs_norm_ag.restype = ctypes.c_int
+        lib.ksana_ag_wait_readers.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_uint,
+                                              ctypes.c_void_p]
+        lib.ksana_ag_wait_readers.restype = ctypes.c_int
+        lib.ksana_gemm_allgather.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 7 + [
+                                                 ctypes.c_uint, ctypes.c_void_p]
+        lib.ksana_gemm_allgather.restype = ctypes.c_int
         self._lib = lib
         dist.barrier(group=group)
         # warm-up: lazy module loading and first-launch costs happen here, under a barrier, not inside a step
@@ -136,6 +153,34 @@ class FusedComm:
             self.comm_ctas, 0, torch.cuda.current_stream().cuda_stream)
         kcuda._check(code, "gemm_rs_norm_ag")
         return self.hbuf[:T]
+
+    # ---- all-gather -> GEMM -------------------------------------------------------------------------------------
+    def ag_rows(self, rows: int) -> torch.Tensor:
+        """This rank's slice of the row-sharded activation ([rows, hidden] view of the symmetric buffer) for the next
+        ``gemm_allgather``. The stream first waits until every peer has finished reading the previous contents."""
+        assert rows <= self.rows_cap
+        if self.ag_epoch:
+            code = self._lib.ksana_ag_wait_readers(self.rank, self.size, self._agflag_ptrs,
+                                                   self.ag_epoch & 0x7FFFFFFF, torch.cuda.current_stream().cuda_stream)
+            kcuda._check(code, "ag_wait_readers")
+        return self.agbuf[:rows]
+
+    def gemm_allgather(self, rows_per: int, total_rows: int, weight: torch.Tensor,
+                       bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """C[total_rows, N] = concat over ranks of their ``ag_rows(rows_per)`` contents times weight^T; every rank
+        gets the full C. One kernel: A tiles are TMA-loaded from the owning rank's memory (csrc/cuda/
+        gemm_allgather.cu)."""
+        N = weight.shape[0]
+        out = torch.empty(total_rows, N, dtype=torch.bfloat16, device=self.device)
+        self.ag_epoch += 1
+        code = self._lib.ksana_gemm_allgather(self.rank, self.size, self._agbuf_ptrs, self._agflag_ptrs,
+                                              self.ag_staged.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                              out.data_ptr(), rows_per, total_rows, N, self.hidden, self.hidden,
+                                              weight.stride(0), N, self.ag_epoch & 0x7FFFFFFF,
+                                              torch.cuda.current_stream().cuda_stream)
+        kcuda._check(code, "gemm_allgather")
+        kcuda.launch_count += 2
+        return out
 
     def reduce_add_norm(self, y, residual, norm_w, eps) -> torch.Tensor:
         T = y.shape[0]

@@ -50,6 +50,26 @@ def _worker(rank, world, port, q):
             if add is not None:
                 want = want + add.float()
             errs.append((it, T, (out.float() - want).abs().max().item(), want.abs().max().item()))
+    # a 2-layer MoE model: MoE blocks through the exchange vs the replicated-token formulation on the same ranks
+    # (same inputs, so the routing decisions agree; a comparison across TP degrees could flip near-tied experts)
+    from ksanallm_b200.config.model_config import model_config_from_dict
+    from ksanallm_b200.engine.step_input import make_step_input
+    from ksanallm_b200.models.loader import load_model_weights
+    from ksanallm_b200.models.transformer import TransformerModel
+    cfg = model_config_from_dict(dict(model_type="mixtral", hidden_size=1024, num_hidden_layers=2,
+                                      num_attention_heads=8, num_key_value_heads=8, intermediate_size=256,
+                                      num_local_experts=8, num_experts_per_tok=2, vocab_size=1000,
+                                      torch_dtype="bfloat16"))
+    w_tp = load_model_weights(cfg, synthetic_seed=5, tp_rank=rank, tp_size=world, device=dev, dtype=torch.bfloat16)
+    m_tp = TransformerModel(cfg, w_tp, tp, max_positions=256)
+    T = 45
+    meta = make_step_input(list(range(7, 7 + T)), list(range(T)), list(range(T)), [0, T], [T], [[0, 1, 2]], device=dev)
+    h_rep = m_tp.forward(meta, m_tp.allocate_kv_cache(4, 16)).clone()
+    assert tp.init_ep(cfg.hidden_size, cfg.num_experts_per_tok, cfg.num_experts, 64)
+    h_ep = m_tp.forward(meta, m_tp.allocate_kv_cache(4, 16)).clone()
+    torch.cuda.synchronize()
+    d = (h_ep.float() - h_rep.float()).abs()
+    errs.append((99, T, d.mean().item() * 3, h_rep.float().abs().max().item()))
     dist.barrier()
     allerrs = [None] * world
     dist.all_gather_object(allerrs, (errs, cuda.read_error()))

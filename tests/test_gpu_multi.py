@@ -78,6 +78,20 @@ def _worker(rank, world, port, use_mc, q):
         torch.cuda.synchronize()
         ferrs.append((T, K, 0.0 if torch.equal(out, out2) else 1.0, 0.0))  # deterministic
     report["ferrs"] = ferrs
+    # all-gather -> GEMM: every rank contributes rows_per rows, all ranks get the full product
+    aerrs = []
+    for it, (rows_per, T_total, N) in enumerate(((5, 5 * world - 2, 512), (128, 128 * world, 768), (200, 200 * world - 77, 256),
+                                                 (fc.rows_cap, fc.rows_cap * world, 1024))):
+        g = torch.Generator(device=dev).manual_seed(900 + it)
+        full = (torch.randn(world * rows_per, H, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+        wt = (torch.randn(N, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        mine = fc.ag_rows(rows_per)
+        mine.copy_(full[rank * rows_per:(rank + 1) * rows_per])
+        got = fc.gemm_allgather(rows_per, T_total, wt)
+        torch.cuda.synchronize()
+        want = full[:T_total].float() @ wt.float().t()
+        aerrs.append((rows_per, N, (got.float() - want).abs().max().item(), want.abs().max().item()))
+    report["aerrs"] = aerrs
     report["errs"] = errs
     report["kernel_error"] = cuda.read_error()
 
@@ -130,4 +144,6 @@ def test_fused_reduce_norm_ranks(use_mc, world):
         assert e1 < 6e-2 and e2 < 6e-2, (T, e1, e2)
     for T, K, e1, e2 in rep["ferrs"]:
         assert e1 < 8e-2 and e2 < 8e-2, (T, K, e1, e2)
+    for rows_per, N, e, m in rep["aerrs"]:
+        assert e < 2e-2 * max(1.0, m), (rows_per, N, e, m)
     assert rep["model_err"] < 0.05 * max(1.0, rep["model_ref_max"])
