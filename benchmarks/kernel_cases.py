@@ -5,6 +5,7 @@ each case is small (at most a few GB on the device) and launches its kernel a ha
 
     python benchmarks/kernel_cases.py gemm [M N K]            # tcgen05 bf16 GEMM
     python benchmarks/kernel_cases.py gemm_fp8 [M N K]        # block-scaled fp8 GEMM
+    python benchmarks/kernel_cases.py gemm_int4 [M N K]       # int4 weight-only GEMM (in-pipeline dequant)
     python benchmarks/kernel_cases.py decode [B ctx h hk]     # paged split-KV decode attention
     python benchmarks/kernel_cases.py prefill [T h hk]        # tcgen05 paged prefill attention
     python benchmarks/kernel_cases.py mla [B ctx h q_len]     # tcgen05 absorbed-MLA decode over the latent cache
@@ -85,6 +86,22 @@ def case_gemm_fp8():
     return dict(kernel="gemm_fp8_block", M=M, N=N, K=K, us=round(us, 1), tflops=round(fl / us / 1e6, 1),
                 gbs=round(by / us / 1e3, 1), frac_of_measured_hbm=round(by / us / 1e3 / p["hbm_gbs"], 3),
                 frac_of_2x_measured_bf16=round(fl / us / 1e6 / (2 * p["bf16_tflops"]), 3))
+
+
+def case_gemm_int4():
+    from ksanallm_b200.ops import cuda_int4
+    M, N, K = args_or([16, 8192, 8192])
+    nw = max(2, int(300e6 // (N * K // 2)) + 1)
+    qs = [ref.quant_int4_group(torch.randn(N, K, device=DEV) * 0.05, 128) for _ in range(nw)]
+    qs = [(ref.tile_int4(p), s, z, cuda_int4.pack_scale_zero(s, z)) for p, s, z in qs]
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    us = timeit(lambda i: cuda_int4.linear_int4(x, *qs[i % nw][:3], None, 128, sz=qs[i % nw][3]))
+    by = N * K / 2 + N * (K // 128) * 8 + M * K * 2 + M * N * 2
+    fl = 2.0 * M * N * K
+    p = peaks()
+    return dict(kernel="gemm_int4", M=M, N=N, K=K, us=round(us, 1), gbs=round(by / us / 1e3, 1),
+                frac_of_measured_hbm=round(by / us / 1e3 / p["hbm_gbs"], 3), tflops=round(fl / us / 1e6, 1),
+                frac_of_measured_bf16=round(fl / us / 1e6 / p["bf16_tflops"], 3))
 
 
 def _attn_setup(q_lens, kv_lens, h, hk):
@@ -173,7 +190,7 @@ def case_moe():
                 tflops=round(fl / us / 1e6, 1), frac_of_measured_bf16=round(fl / us / 1e6 / p["bf16_tflops"], 3))
 
 
-CASES = dict(gemm=case_gemm, gemm_fp8=case_gemm_fp8, decode=case_decode, prefill=case_prefill, mla=case_mla, rmsnorm=case_rmsnorm,
+CASES = dict(gemm=case_gemm, gemm_fp8=case_gemm_fp8, gemm_int4=case_gemm_int4, decode=case_decode, prefill=case_prefill, mla=case_mla, rmsnorm=case_rmsnorm,
              moe=case_moe)
 
 if __name__ == "__main__":

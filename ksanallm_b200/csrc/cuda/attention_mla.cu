@@ -116,7 +116,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     for (int c = 0; c < MLA_CHUNKS; ++c) mbar_init(&kv_full[c], 1);
     mbar_init(s_done, 1);
     mbar_init(o_done, 1);
-    mbar_init(p_ready, 256);
+    mbar_init(p_ready, 8);
     *abort_flag = 0;
     bad_vote[0] = bad_vote[1] = bad_vote[2] = bad_vote[3] = 0;
     fence_mbar_init();
@@ -311,7 +311,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tmem_wait_st();
       }
       tc_fence_before();
-      mbar_arrive(p_ready);
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(p_ready);  // one arrival per warp
       MLA_TRACE(6, 0)
     }
     // every softmax thread leaves the loop at the same iteration (uniform votes), so the named barrier stays balanced

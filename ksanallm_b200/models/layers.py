@@ -34,9 +34,17 @@ class LinearW:
         self.scales = weights.get(prefix + ".scales")
         self.zeros = weights.get(prefix + ".zeros")
         self.group = 128
+        self.sz = None
         if self.qweight is not None:
             self.kind = "int4"
             self.group = self.qweight.shape[1] * 8 // self.scales.shape[1]
+            self._n, self._k = self.qweight.shape[0], self.qweight.shape[1] * 8
+            from ..ops import cuda_int4
+            if self.qweight.is_cuda and cuda_int4.supports(self._k, self._n, self.group):
+                # the CUDA GEMM streams 4 KB (128 rows x 64 weights) blocks: re-tile once, drop the row-major copy
+                self.qweight = ref.tile_int4(self.qweight)
+                weights[prefix + ".qweight"] = self.qweight
+                self.sz = cuda_int4.pack_scale_zero(self.scales, self.zeros)
         elif self.scale_inv is not None:
             self.kind = "fp8_block"
         elif self.weight is not None:
@@ -46,11 +54,11 @@ class LinearW:
 
     @property
     def out_features(self) -> int:
-        return (self.qweight if self.kind == "int4" else self.weight).shape[0]
+        return self._n if self.kind == "int4" else self.weight.shape[0]
 
     @property
     def in_features(self) -> int:
-        return self.qweight.shape[1] * 8 if self.kind == "int4" else self.weight.shape[1]
+        return self._k if self.kind == "int4" else self.weight.shape[1]
 
     def __call__(self, x: torch.Tensor, add_bias: bool = True) -> torch.Tensor:
         b = self.bias if add_bias else None
@@ -58,7 +66,7 @@ class LinearW:
             return ops.linear(x, self.weight, b)
         if self.kind == "fp8_block":
             return ops.linear_fp8_block(x, self.weight, self.scale_inv, b)
-        return ops.linear_int4(x, self.qweight, self.scales, self.zeros, b, self.group)
+        return ops.linear_int4(x, self.qweight, self.scales, self.zeros, b, self.group, self.sz)
 
 
 class Attention:

@@ -49,9 +49,9 @@ def linear_fp8_block(x, wq, w_scale_inv, bias=None):
     return ref.linear_fp8_block(x, wq, w_scale_inv, bias)
 
 
-def linear_int4(x, packed, scales, zeros, bias=None, group=128):
+def linear_int4(x, packed, scales, zeros, bias=None, group=128, sz=None):
     if x.is_cuda:
-        return _cuda().linear_int4(x, packed, scales, zeros, bias, group)
+        return _cuda().linear_int4(x, packed, scales, zeros, bias, group, sz=sz)
     return ref.linear_int4(x, packed, scales, zeros, bias, group)
 
 

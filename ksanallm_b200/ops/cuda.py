@@ -46,6 +46,8 @@ class _Sig:
     ksana_moe_permute = ([P, I, P, I, I, I, I, I, P, P, P, P, P], I)
     ksana_moe_grouped_gemm = ([P, P, P, P, I, I, I, I, P], I)
     ksana_moe_combine = ([P, P, P, I, I, I, P, P], I)
+    ksana_gemm_int4_small = ([P, P, P, P, P, I, I, I, I, I, I, P, LL, P, I, I, P], I)
+    ksana_gemm_int4 = ([P, P, P, P, P, I, I, I, I, I, I, P, LL, P, I, P], I)
     ksana_mla_decode = ([P, I, P, I, P, I, P, P, I, I, I, I, I, F, P, P, LL, P], I)
     ksana_mla_cache_append = ([P, I, P, I, P, P, I, I, I, P], I)
     ksana_rms_norm = ([P, I, P, I, P, P, I, I, I, F, P], I)
@@ -161,9 +163,9 @@ def linear_fp8_block(x, wq, w_scale_inv, bias=None):
     return cuda_quant.linear_fp8_block(x, wq, w_scale_inv, bias)
 
 
-def linear_int4(x, packed, scales, zeros, bias=None, group=128):
-    from . import cuda_quant
-    return cuda_quant.linear_int4(x, packed, scales, zeros, bias, group)
+def linear_int4(x, packed, scales, zeros, bias=None, group=128, sz=None):
+    from . import cuda_int4
+    return cuda_int4.linear_int4(x, packed, scales, zeros, bias, group, sz=sz)
 
 
 # ---- elementwise -------------------------------------------------------------------------------------------

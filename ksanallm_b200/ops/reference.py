@@ -154,6 +154,25 @@ def unpack_int4(packed: torch.Tensor) -> torch.Tensor:
     return torch.stack(cols, dim=-1).view(N, K8 * 8).to(torch.int32)
 
 
+def tile_int4(packed: torch.Tensor) -> torch.Tensor:
+    """[N, K/8] packed words -> [K/64, ceil(N/128), 128, 8]: each (128 rows x 64 weights) block contiguous, rows
+    past N zero, blocks of one k-step next to each other. This is the layout the CUDA int4 GEMM streams (one 4 KB
+    block per pipeline stage; CTAs working on neighbouring row tiles read neighbouring blocks, which keeps their
+    concurrent streams spread over all memory channels)."""
+    N, K8 = packed.shape
+    assert K8 % 8 == 0
+    nt = (N + 127) // 128
+    p = packed
+    if nt * 128 != N:
+        p = torch.cat((p, torch.zeros(nt * 128 - N, K8, dtype=p.dtype, device=p.device)), dim=0)
+    return p.view(nt, 128, K8 // 8, 8).permute(2, 0, 1, 3).contiguous()
+
+
+def untile_int4(tiled: torch.Tensor, n_rows: int) -> torch.Tensor:
+    kb, nt, _, _ = tiled.shape
+    return tiled.permute(1, 2, 0, 3).reshape(nt * 128, kb * 8)[:n_rows].contiguous()
+
+
 def quant_int4_group(w: torch.Tensor, group: int = 128) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Asymmetric 4-bit group quantisation along K: (packed[N, K/8] i32, scales[N, K/g], zeros[N, K/g])
     with w ~= (q - zero) * scale."""
@@ -175,6 +194,8 @@ def dequant_int4_group(packed: torch.Tensor, scales: torch.Tensor, zeros: torch.
 
 def linear_int4(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
                 bias: Optional[torch.Tensor] = None, group: int = 128) -> torch.Tensor:
+    if packed.dim() == 4:
+        packed = untile_int4(packed, scales.shape[0])
     w = dequant_int4_group(packed, scales, zeros, group).to(x.dtype)
     return linear(x, w, bias)
 
