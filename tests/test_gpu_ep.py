@@ -94,7 +94,22 @@ def test_ep_dispatch_combine(world):
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    rep = q.get(timeout=240)
+    rep = None
+    import queue
+    import time
+    deadline = time.time() + 240
+    while rep is None and time.time() < deadline:
+        try:
+            rep = q.get(timeout=2)
+        except queue.Empty:
+            # a rank that died (assertion, CUDA error) never reports: stop waiting for it
+            if any(p.exitcode not in (None, 0) for p in procs):
+                break
+    if rep is None:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        pytest.fail("a rank exited without reporting: " + str([p.exitcode for p in procs]))
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
