@@ -1,0 +1,71 @@
+// Native forward pass of the dense decoder stack (Llama / Qwen family blocks: RMSNorm, fused-QKV attention with RoPE
+// over the paged cache, gated FFN), driven from ONE call per step. Declared here so that the Python side can mirror
+// the structs with ctypes.
+#pragma once
+#include <cuda_runtime.h>
+
+extern "C" {
+
+struct KsanaDenseLayer {
+  const void* wqkv;     // [(h + 2 hk) d, H] bf16
+  const void* bqkv;     // optional bias [(h + 2 hk) d]
+  const void* wo;       // [H, h d]
+  const void* ln2;      // post-attention RMSNorm weight [H]
+  const void* wgu;      // [2 I, H] gate rows then up rows
+  const void* wdown;    // [H, I]
+  const void* next_ln;  // the norm applied after this layer's FFN: next layer's input norm, or the final norm
+  const void* q_norm;   // optional per-head RMSNorm weights [d]
+  const void* k_norm;
+  void* kv_cache;       // [num_blocks, 2, hk, block_size, d]
+};
+
+struct KsanaDenseModel {
+  int hidden, heads, kv_heads, head_dim, inter;  // per-rank heads and FFN width
+  int n_layers;
+  float eps;
+  int rotary_dim, rope_interleaved;
+  int block_size, num_blocks, kv_kind;  // kv_kind 0 bf16, 1 fp8 e4m3
+  float attn_scale, k_scale, v_scale;
+  const float* rope_cache;  // [max_pos, rotary_dim] cos | sin, or null
+  // tensor parallel (ws == 1: everything below up to comm_ctas is ignored)
+  int rank, ws, rows_cap, comm_ctas;
+  void* const* recv;
+  void* const* hbuf;
+  void* const* sig;
+  void* hbuf_mc;
+  // scratch, all sized for max_tokens rows
+  void* qkv_buf;   // [T, (h + 2 hk) d]
+  void* attn_buf;  // [T, h d]
+  void* gu_buf;    // [T, 2 I]
+  void* act_buf;   // [T, I]
+  void* proj_buf;  // [T, H]   (ws == 1)
+  void* h_buf[2];  // [T, H]   (ws == 1) normalised activations, ping-pong
+  float* gemm_ws;
+  long long gemm_ws_floats;
+  unsigned int* gemm_counters;
+  int n_counters;
+  float* attn_ws;
+  long long attn_ws_floats;
+  const KsanaDenseLayer* layers;
+};
+
+struct KsanaDenseStep {
+  const int* positions;
+  const int* slot_mapping;
+  const int* block_tables;
+  const int* cu_q;
+  const int* kv_lens;
+  int total_tokens, num_prefill, num_decode, max_blocks;
+  int max_q_prefill, max_q_decode, max_kv_decode;
+};
+
+// h: normalised input of layer `first` ([T, H] bf16; for ws > 1 it may be any buffer), residual: [T, H] running
+// residual stream (updated in place; row-sharded across ranks when ws > 1). Runs layers [first, last). epoch: first
+// collective epoch to use (ws > 1), two are consumed per layer. *out_h receives the pointer of the normalised output
+// (one of the scratch buffers or this rank's hbuf). Returns 0, or (layer + 1) * 100 + step on failure with
+// *fail_code holding the failing call's code. Has no counterpart in the reference (its per-layer C++ forward is
+// CommonModel::LayerForward, src/ksana_llm/models/common/common_model.cpp).
+int ksana_dense_forward(const KsanaDenseModel* m, const KsanaDenseStep* s, const void* h, void* residual, int first,
+                        int last, unsigned int epoch, void** out_h, int* fail_code, int* launches,
+                        cudaStream_t stream);
+}

@@ -1,0 +1,205 @@
+"""Binding of the native dense-layer executor (csrc/cuda/dense_executor.cu): the whole decoder stack of a step is
+launched by one C call instead of ~8 Python-level kernel wrappers per layer.
+
+Eligible models: dense (no MoE / MLA) RMSNorm + RoPE decoders with a gated SiLU FFN, bf16 weights, head_dim 128 and
+the 16-token KV block, on one GPU or tensor-parallel with the single-kernel fused GEMM + reduce-scatter path. Anything
+else keeps the Python layer code in models/transformer.py (same kernels, launched one by one).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..ops import cuda as kcuda
+
+P, I, F, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+class _Layer(ctypes.Structure):
+    _fields_ = [(n, P) for n in ("wqkv", "bqkv", "wo", "ln2", "wgu", "wdown", "next_ln", "q_norm", "k_norm",
+                                 "kv_cache")]
+
+
+class _Model(ctypes.Structure):
+    _fields_ = [("hidden", I), ("heads", I), ("kv_heads", I), ("head_dim", I), ("inter", I), ("n_layers", I),
+                ("eps", F), ("rotary_dim", I), ("rope_interleaved", I), ("block_size", I), ("num_blocks", I),
+                ("kv_kind", I), ("attn_scale", F), ("k_scale", F), ("v_scale", F), ("rope_cache", P),
+                ("rank", I), ("ws", I), ("rows_cap", I), ("comm_ctas", I), ("recv", P), ("hbuf", P), ("sig", P),
+                ("hbuf_mc", P), ("qkv_buf", P), ("attn_buf", P), ("gu_buf", P), ("act_buf", P), ("proj_buf", P),
+                ("h_buf", P * 2), ("gemm_ws", P), ("gemm_ws_floats", LL), ("gemm_counters", P), ("n_counters", I),
+                ("attn_ws", P), ("attn_ws_floats", LL), ("layers", P)]
+
+
+class _Step(ctypes.Structure):
+    _fields_ = [("positions", P), ("slot_mapping", P), ("block_tables", P), ("cu_q", P), ("kv_lens", P),
+                ("total_tokens", I), ("num_prefill", I), ("num_decode", I), ("max_blocks", I), ("max_q_prefill", I),
+                ("max_q_decode", I), ("max_kv_decode", I)]
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+class DenseExecutor:
+    @staticmethod
+    def eligible(model) -> bool:
+        cfg, tp = model.cfg, model.tp
+        if os.environ.get("KSANA_DISABLE_NATIVE_EXECUTOR", "0") == "1" or os.environ.get("KSANA_LIBRARY_BASELINE") == "1":
+            return False
+        if model.device.type != "cuda" or model.dtype != torch.bfloat16 or not model.layers:
+            return False
+        if getattr(model, "num_cache_layers", len(model.layers)) != len(model.layers):
+            return False  # cross-layer KV sharing
+        if (cfg.use_mla or cfg.norm_type != "rmsnorm" or cfg.residual_scale != 1.0 or cfg.head_dim != 128 or
+                cfg.position_encoding not in ("rope", "none") or not cfg.gated_mlp or
+                cfg.hidden_act not in ("silu", "swish") or getattr(cfg, "sliding_window", 0)):
+            return False
+        for layer in model.layers:
+            if layer.is_moe or not hasattr(layer.attn, "qkv"):
+                return False
+            lins = (layer.attn.qkv, layer.attn.o_proj, layer.ffn.up, layer.ffn.down)
+            if any(l.kind != "dense" for l in lins) or layer.attn.o_proj.bias is not None:
+                return False
+            if layer.ffn.up.bias is not None or layer.ffn.down.bias is not None or layer.attn.alibi is not None:
+                return False
+            if layer.ln2 is None or getattr(layer, "ln2_b", None) is not None:
+                return False
+        if tp.size > 1:
+            fc = tp.fused
+            if fc is None or not fc.single_kernel or fc.hidden % 256 or fc.hidden > 9216 or fc.hidden != cfg.hidden_size:
+                return False
+        return True
+
+    def __init__(self, model):
+        self.model = model
+        cfg, tp = model.cfg, model.tp
+        self.tp = tp
+        self.H = cfg.hidden_size
+        a0 = model.layers[0].attn
+        self.h, self.hk, self.d = a0.h, a0.hk, a0.d
+        self.inter = model.layers[0].ffn.down.weight.shape[1]
+        n = len(model.layers)
+        self._layers = (_Layer * n)()
+        for i, layer in enumerate(model.layers):
+            L = self._layers[i]
+            nxt = model.layers[i + 1].ln1 if i + 1 < n else model.norm_w
+            L.wqkv, L.bqkv = _p(layer.attn.qkv.weight), _p(layer.attn.qkv.bias)
+            L.wo, L.ln2 = _p(layer.attn.o_proj.weight), _p(layer.ln2)
+            L.wgu, L.wdown = _p(layer.ffn.up.weight), _p(layer.ffn.down.weight)
+            L.next_ln = _p(nxt)
+            L.q_norm, L.k_norm = _p(layer.attn.q_norm), _p(layer.attn.k_norm)
+            L.kv_cache = None
+        m = self._m = _Model()
+        m.hidden, m.heads, m.kv_heads, m.head_dim, m.inter, m.n_layers = self.H, self.h, self.hk, self.d, self.inter, n
+        m.eps = float(cfg.rms_norm_eps)
+        m.rotary_dim = int(cfg.rotary_dim or cfg.head_dim)
+        m.rope_interleaved = 1 if cfg.rope_interleaved else 0
+        m.attn_scale = float(a0.scale)
+        m.k_scale = m.v_scale = 1.0
+        m.rope_cache = _p(model.rope_cache)
+        m.rank, m.ws = tp.rank, tp.size
+        if tp.size > 1:
+            fc = tp.fused
+            m.rows_cap, m.comm_ctas = fc.rows_cap, fc.comm_ctas
+            m.recv = ctypes.cast(fc._recv_ptrs, P)
+            m.hbuf = ctypes.cast(fc._hbuf_ptrs, P)
+            m.sig = ctypes.cast(fc._sig_ptrs, P)
+            m.hbuf_mc = fc.hbuf_mc or None
+        ws = kcuda.workspace(model.device)
+        self._ws = ws
+        m.gemm_ws, m.gemm_ws_floats = _p(ws.gemm_ws), ws.gemm_ws.numel()
+        m.gemm_counters, m.n_counters = _p(ws.gemm_counters), ws.gemm_counters.numel()
+        m.attn_ws, m.attn_ws_floats = _p(ws.attn_ws), ws.attn_ws.numel()
+        m.layers = ctypes.cast(self._layers, P)
+        self.cap = 0
+        self._bufs: List[torch.Tensor] = []
+        self._kv_key = None
+        self._step = _Step()
+        lib = kcuda.lib()
+        lib.ksana_dense_forward.argtypes = [P, P, P, P, I, I, ctypes.c_uint, P, P, P, P]
+        lib.ksana_dense_forward.restype = I
+        self._fn = lib.ksana_dense_forward
+        self._out = P()
+        self._fail = I()
+        self._launches = I()
+
+    def _ensure(self, T: int) -> None:
+        if T <= self.cap:
+            return
+        cap = (max(T, 1024) + 1023) // 1024 * 1024
+        dev, bf = self.model.device, torch.bfloat16
+        nqkv = (self.h + 2 * self.hk) * self.d
+        mk = lambda cols: torch.empty(cap, cols, dtype=bf, device=dev)  # noqa: E731
+        qkv, attn, gu, act = mk(nqkv), mk(self.h * self.d), mk(2 * self.inter), mk(self.inter)
+        self._bufs = [qkv, attn, gu, act]
+        m = self._m
+        m.qkv_buf, m.attn_buf, m.gu_buf, m.act_buf = _p(qkv), _p(attn), _p(gu), _p(act)
+        if self.tp.size == 1:
+            proj, h0, h1 = mk(self.H), mk(self.H), mk(self.H)
+            self._bufs += [proj, h0, h1]
+            m.proj_buf = _p(proj)
+            m.h_buf[0], m.h_buf[1] = _p(h0), _p(h1)
+            self._h = (h0, h1)
+        self.cap = cap
+
+    def _bind_kv(self, kv_caches) -> None:
+        key = (kv_caches[0].data_ptr(), len(kv_caches))
+        if key == self._kv_key:
+            return
+        for i in range(len(self.model.layers)):
+            self._layers[i].kv_cache = kv_caches[i].data_ptr()
+        c = kv_caches[0]
+        m = self._m
+        m.num_blocks, m.block_size = c.shape[0], c.shape[3]
+        m.kv_kind = 0 if c.dtype == torch.bfloat16 else 1
+        self._kv_key = key
+
+    def can_run(self, meta, kv_caches, n_layers: int) -> bool:
+        T = meta.total_tokens
+        if T == 0 or n_layers == 0 or kv_caches[0].dim() != 5 or kv_caches[0].shape[3] != 16:
+            return False
+        if kv_caches[0].dtype != torch.bfloat16 and meta.num_prefill:
+            return False  # fp8 cache prefill chunks take the dequantising path
+        if self.tp.size > 1:
+            fc = self.tp.fused
+            return T <= min(8192, fc.max_tokens)
+        return True
+
+    def forward(self, meta, kv_caches, h: torch.Tensor, residual: torch.Tensor, n_layers: int) -> torch.Tensor:
+        """h: normalised input of layer 0, residual: the residual stream (both [T, H], contiguous); returns the
+        normalised output of layer ``n_layers - 1`` (a view of an internal buffer, valid until the next call)."""
+        T = meta.total_tokens
+        self._ensure(T)
+        self._bind_kv(kv_caches)
+        s = self._step
+        s.positions, s.slot_mapping = meta.positions.data_ptr(), meta.slot_mapping.data_ptr()
+        s.block_tables, s.cu_q, s.kv_lens = meta.block_tables.data_ptr(), meta.cu_q.data_ptr(), meta.kv_lens.data_ptr()
+        n_pre, n_dec = meta.num_prefill, meta.num_decode
+        s.total_tokens, s.num_prefill, s.num_decode, s.max_blocks = T, n_pre, n_dec, meta.max_blocks
+        cu, kl = meta.cu_q_host, meta.kv_lens_host
+        s.max_q_prefill = int((cu[1:n_pre + 1] - cu[:n_pre]).max()) if n_pre else 0
+        if n_dec:
+            s.max_q_decode = int((cu[n_pre + 1:n_pre + n_dec + 1] - cu[n_pre:n_pre + n_dec]).max())
+            s.max_kv_decode = int(kl[n_pre:n_pre + n_dec].max())
+        else:
+            s.max_q_decode = s.max_kv_decode = 0
+        epoch = 0
+        fc = self.tp.fused if self.tp.size > 1 else None
+        if fc is not None:
+            epoch = (fc.epoch + 1) & 0x7FFFFFFF
+            fc.epoch += 2 * n_layers
+        rc = self._fn(ctypes.byref(self._m), ctypes.byref(s), h.data_ptr(), residual.data_ptr(), 0, n_layers, epoch,
+                      ctypes.byref(self._out), ctypes.byref(self._fail), ctypes.byref(self._launches),
+                      torch.cuda.current_stream().cuda_stream)
+        kcuda.launch_count += self._launches.value
+        if rc != 0:
+            raise RuntimeError(f"native dense forward failed at layer {rc // 100 - 1}, step {rc % 100}, "
+                               f"code {self._fail.value}")
+        if fc is not None:
+            return fc.hbuf[:T]
+        out = self._out.value
+        return (self._h[0] if out == self._h[0].data_ptr() else self._h[1])[:T]

@@ -162,12 +162,28 @@ class TransformerModel:
         h = first._norm(x, first.ln1, first.ln1_b, None)
         if h.data_ptr() == residual.data_ptr():
             residual = x.clone()
+        native = self._native_executor()
+        if native is not None and cutoff_layer is None and native.can_run(meta, kv_caches, len(layers)):
+            if not residual.is_contiguous():
+                residual = residual.contiguous()
+            h = native.forward(meta, kv_caches, h.contiguous(), residual, len(layers))
+            self.last_residual = residual
+            return h
         for li, layer in enumerate(layers):
             nxt = layers[li + 1] if li + 1 < len(layers) else None
             nw, nb = (nxt.ln1, nxt.ln1_b) if nxt is not None else (self.norm_w, self.norm_b)
             h = layer.forward(h, residual, meta, kv_caches[li], nw, nb)
         self.last_residual = residual
         return h
+
+    def _native_executor(self):
+        """The one-call-per-step C++ executor for eligible dense models (models/native_executor.py), created on
+        first use; None when the model or the environment rules it out."""
+        ex = getattr(self, "_native", False)
+        if ex is False:
+            from .native_executor import DenseExecutor
+            ex = self._native = DenseExecutor(self) if DenseExecutor.eligible(self) else None
+        return ex
 
     def _final_norm_only(self, x):
         if self.norm_w is None:

@@ -1,0 +1,70 @@
+"""The one-call-per-step native executor must reproduce the per-layer Python path exactly (same kernels, same order)."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(model_type="llama", **over):
+    from ksanallm_b200.config.model_config import model_config_from_dict
+    from ksanallm_b200.models.loader import load_model_weights
+    from ksanallm_b200.models.transformer import TransformerModel
+    d = dict(model_type=model_type, hidden_size=1024, num_hidden_layers=3, num_attention_heads=8,
+             num_key_value_heads=4, intermediate_size=2816, vocab_size=1000, torch_dtype="bfloat16")
+    d.update(over)
+    cfg = model_config_from_dict(d)
+    w = load_model_weights(cfg, synthetic_seed=4, device="cuda", dtype=torch.bfloat16)
+    return TransformerModel(cfg, w, max_positions=512)
+
+
+def _mixed_meta():
+    from ksanallm_b200.engine.step_input import make_step_input
+    # one prefill of 37 tokens, one chunk continuing at position 20 (9 new tokens), three decodes
+    q_lens = [37, 9, 1, 1, 1]
+    kv_lens = [37, 29, 50, 17, 64]
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    bt = torch.zeros(5, 4, dtype=torch.int32)
+    nxt = 0
+    pos, slots = [], []
+    for b, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        nb = (kl + 15) // 16
+        bt[b, :nb] = torch.arange(nxt, nxt + nb, dtype=torch.int32)
+        for p in range(kl - ql, kl):
+            pos.append(p)
+            slots.append(int(bt[b, p // 16]) * 16 + p % 16)
+        nxt += nb
+    ids = [(7 * i + 3) % 1000 for i in range(cu[-1])]
+    return make_step_input(ids, pos, slots, cu, kv_lens, bt, num_prefill=2, device="cuda"), nxt
+
+
+@pytest.mark.parametrize("model_type,extra", [("llama", {}), ("qwen3", {"head_dim": 128}), ("qwen2", {})])
+def test_native_matches_python_path(model_type, extra):
+    from ksanallm_b200.ops import cuda
+    m = _build(model_type, **extra)
+    meta, nblocks = _mixed_meta()
+    assert m._native_executor() is not None
+    kv_a = m.allocate_kv_cache(nblocks + 1, 16)
+    for c in kv_a:
+        c.normal_(0, 0.3)
+    kv_b = [c.clone() for c in kv_a]
+    base = cuda.launch_count
+    out_native = m.forward(meta, kv_a).clone()
+    native_launches = cuda.launch_count - base
+    m._native = None  # per-layer Python path
+    out_python = m.forward(meta, kv_b).clone()
+    torch.cuda.synchronize()
+    assert cuda.read_error() == 0
+    assert torch.equal(out_native, out_python)
+    for a, b in zip(kv_a, kv_b):
+        assert torch.equal(a, b)
+    assert native_launches >= 8 * 3
+
+
+def test_native_declines_unsupported():
+    m = _build("llama", num_hidden_layers=1, hidden_size=512, num_attention_heads=8, num_key_value_heads=8,
+               intermediate_size=1024)  # head_dim 64
+    assert m._native_executor() is None
