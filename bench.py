@@ -222,7 +222,10 @@ def main():
         for r in all_reqs:
             if r.finished and len(r.token_times) > 1:
                 tpot.append((r.token_times[-1] - r.token_times[0]) / (len(r.token_times) - 1))
-        result = dict(toks_a=toks_a, ms_a=ms_a, toks_b=toks_b, wall_b=wall_b, launches=launches, clocks=clocks,
+        st = eng.stats
+        host_ms = {k: round(1e3 * st[k] / max(st["steps"], 1), 3) for k in
+                   ("schedule_time", "t_broadcast", "t_launch", "t_sample_sync", "t_apply")}
+        result = dict(host_ms=host_ms, toks_a=toks_a, ms_a=ms_a, toks_b=toks_b, wall_b=wall_b, launches=launches, clocks=clocks,
                       h2d=h2d, d2h=d2h, ttft=ttft, tpot=tpot, err=cuda.read_error())
         eng.shutdown_followers()
     else:
@@ -255,6 +258,7 @@ def main():
             "p50_ttft_s": round(statistics.median(result["ttft"]), 4) if result["ttft"] else None,
             "p50_tpot_s": round(statistics.median(result["tpot"]), 5) if result["tpot"] else None,
             "kernel_error_word": result["err"],
+            "host_ms_per_step": result["host_ms"],
         }
         print(json.dumps(line))
     if world > 1:

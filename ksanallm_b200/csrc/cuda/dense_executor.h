@@ -33,6 +33,9 @@ struct KsanaDenseModel {
   void* const* hbuf;
   void* const* sig;
   void* hbuf_mc;
+  void* const* partial;  // two-kernel path: GEMM into this rank's symmetric `partial`, then the reduce/norm/gather kernel
+  void* partial_mc;
+  int two_kernel_max_tokens;  // steps with at most this many tokens take the two-kernel path (0: never)
   // scratch, all sized for max_tokens rows
   void* qkv_buf;   // [T, (h + 2 hk) d]
   void* attn_buf;  // [T, h d]

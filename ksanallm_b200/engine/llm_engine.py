@@ -147,7 +147,8 @@ class LLMEngine:
         self.tracer = None
         self._ctl = None  # CPU process group for plan broadcast
         self._hdr = np.zeros(64, dtype=np.int32)
-        self.stats = {"generated_tokens": 0, "prompt_tokens": 0, "steps": 0, "forward_time": 0.0, "schedule_time": 0.0}
+        self.stats = {"generated_tokens": 0, "prompt_tokens": 0, "steps": 0, "forward_time": 0.0, "schedule_time": 0.0,
+                      "t_broadcast": 0.0, "t_launch": 0.0, "t_sample_sync": 0.0, "t_apply": 0.0}
         self.on_step: Optional[Callable[[Dict[str, Any]], None]] = None
 
     # ---- sizing ----------------------------------------------------------------------------------------
@@ -269,18 +270,27 @@ class LLMEngine:
         t1 = time.perf_counter()
         if self.tp.size > 1:
             self._broadcast_plan(layout, plan, greedy)
+        ta = time.perf_counter()
         self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
         meta = self.runner.upload(layout)
         hidden = self.runner.forward(meta, refit)
         self._run_probes(plan, meta, hidden)
+        tb = time.perf_counter()
         out = self.runner.sample(hidden, meta, rows, greedy)
         t2 = time.perf_counter()
         with self.lock:
             n_new = self._apply_results(plan, out, meta, hidden)
+        t3 = time.perf_counter()
         self.step_count += 1
-        self.stats["steps"] += 1
-        self.stats["schedule_time"] += t1 - t0
-        self.stats["forward_time"] += t2 - t1
+        st = self.stats
+        st["steps"] += 1
+        st["schedule_time"] += t1 - t0
+        st["forward_time"] += t2 - t1
+        # host-side phase clocks (seconds, cumulative): where a step's wall time goes on the driving rank
+        st["t_broadcast"] += ta - t1
+        st["t_launch"] += tb - ta
+        st["t_sample_sync"] += t2 - tb
+        st["t_apply"] += t3 - t2
         if self.on_step is not None:
             self.on_step({"tokens": meta.total_tokens, "seqs": meta.num_seqs, "new_tokens": n_new,
                           "schedule_s": t1 - t0, "forward_s": t2 - t1, "prefill": meta.num_prefill,

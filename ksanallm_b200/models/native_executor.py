@@ -29,7 +29,7 @@ class _Model(ctypes.Structure):
                 ("eps", F), ("rotary_dim", I), ("rope_interleaved", I), ("block_size", I), ("num_blocks", I),
                 ("kv_kind", I), ("attn_scale", F), ("k_scale", F), ("v_scale", F), ("rope_cache", P),
                 ("rank", I), ("ws", I), ("rows_cap", I), ("comm_ctas", I), ("recv", P), ("hbuf", P), ("sig", P),
-                ("hbuf_mc", P), ("qkv_buf", P), ("attn_buf", P), ("gu_buf", P), ("act_buf", P), ("proj_buf", P),
+                ("hbuf_mc", P), ("partial", P), ("partial_mc", P), ("two_kernel_max_tokens", I), ("qkv_buf", P), ("attn_buf", P), ("gu_buf", P), ("act_buf", P), ("proj_buf", P),
                 ("h_buf", P * 2), ("gemm_ws", P), ("gemm_ws_floats", LL), ("gemm_counters", P), ("n_counters", I),
                 ("attn_ws", P), ("attn_ws_floats", LL), ("layers", P)]
 
@@ -109,6 +109,9 @@ class DenseExecutor:
             m.hbuf = ctypes.cast(fc._hbuf_ptrs, P)
             m.sig = ctypes.cast(fc._sig_ptrs, P)
             m.hbuf_mc = fc.hbuf_mc or None
+            m.partial = ctypes.cast(fc._partial_ptrs, P)
+            m.partial_mc = fc.partial_mc or None
+            m.two_kernel_max_tokens = fc.two_kernel_max_tokens
         ws = kcuda.workspace(model.device)
         self._ws = ws
         m.gemm_ws, m.gemm_ws_floats = _p(ws.gemm_ws), ws.gemm_ws.numel()
@@ -192,6 +195,7 @@ class DenseExecutor:
         if fc is not None:
             epoch = (fc.epoch + 1) & 0x7FFFFFFF
             fc.epoch += 2 * n_layers
+            self._m.two_kernel_max_tokens = fc.two_kernel_max_tokens
         rc = self._fn(ctypes.byref(self._m), ctypes.byref(s), h.data_ptr(), residual.data_ptr(), 0, n_layers, epoch,
                       ctypes.byref(self._out), ctypes.byref(self._fail), ctypes.byref(self._launches),
                       torch.cuda.current_stream().cuda_stream)

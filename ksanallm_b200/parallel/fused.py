@@ -70,6 +70,8 @@ class FusedComm:
         self.ag_epoch = 0
         self.single_kernel = os.environ.get("KSANA_DISABLE_FUSED_GEMM_RS", "0") != "1"
         self.comm_ctas = int(os.environ.get("KSANA_FUSED_COMM_CTAS", "16"))
+        # latency-bound steps (few tokens, many ranks): GEMM + reduce/norm/gather kernel instead of the single kernel
+        self.two_kernel_max_tokens = int(os.environ.get("KSANA_TWO_KERNEL_MAX_TOKENS", "256" if size >= 4 else "0"))
         self.epoch = 0
         lib = kcuda.lib()
         lib.ksana_rs_norm_ag.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
@@ -127,9 +129,9 @@ class FusedComm:
         """GEMM straight into the symmetric ``partial`` buffer, then the fused reduce/add/norm/gather kernel.
         The returned tensor is a view of ``hbuf`` (valid until the next fused call)."""
         T = x.shape[0]
-        if (self.single_kernel and lin.kind == "dense" and lin.bias is None and self.hidden % 256 == 0 and
-                self.hidden <= 9216 and T <= 8192 and x.dim() == 2 and residual is not None and
-                residual.is_contiguous()):
+        if (self.single_kernel and T > self.two_kernel_max_tokens and lin.kind == "dense" and lin.bias is None and
+                self.hidden % 256 == 0 and self.hidden <= 9216 and T <= 8192 and x.dim() == 2 and
+                residual is not None and residual.is_contiguous()):
             return self.gemm_reduce_add_norm(x, lin.weight, residual, norm_w, eps)
         if lin.kind == "dense" and (lin.bias is None or self.rank != 0):
             kcuda.gemm_bf16(x, lin.weight, None, out=self.partial[:T])

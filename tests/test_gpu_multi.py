@@ -109,6 +109,14 @@ def _worker(rank, world, port, use_mc, q):
     kv = m_tp.allocate_kv_cache(8, 16)
     h_tp = m_tp.forward(meta, kv).clone()
     torch.cuda.synchronize()
+    report["native"] = m_tp._native_executor() is not None
+    # the other row-parallel strategy (single fused kernel <-> GEMM + reduce kernel) must agree
+    old = fc.two_kernel_max_tokens
+    fc.two_kernel_max_tokens = 0 if old else 4096
+    h_alt = m_tp.forward(meta, m_tp.allocate_kv_cache(8, 16)).clone()
+    fc.two_kernel_max_tokens = old
+    torch.cuda.synchronize()
+    report["alt_err"] = (h_alt.float() - h_tp.float()).abs().max().item()
     if rank == 0:
         w_1 = load_model_weights(cfg, synthetic_seed=3, device=dev, dtype=torch.bfloat16)
         m_1 = TransformerModel(cfg, w_1, TPGroup(), max_positions=512)
@@ -163,4 +171,6 @@ def test_fused_reduce_norm_ranks(use_mc, world):
         assert e1 < 8e-2 and e2 < 8e-2, (T, K, e1, e2)
     for rows_per, N, e, m in rep["aerrs"]:
         assert e < 2e-2 * max(1.0, m), (rows_per, N, e, m)
+    assert rep["native"]
+    assert rep["alt_err"] < 0.05 * max(1.0, rep["model_ref_max"])
     assert rep["model_err"] < 0.05 * max(1.0, rep["model_ref_max"])
