@@ -157,8 +157,23 @@ def main():
             dist.all_reduce(y)
             cuda.rms_norm(y, norm_w, 1e-6, residual)
 
+        ybuf = torch.empty(M, H, device=dev, dtype=torch.bfloat16)
+
+        def run_gemm_only(i):
+            cuda.gemm_bf16(x, ws_list[i % ncopies], None, out=fc.partial[:M])
+
+        def run_reduce_only(i):
+            fc._launch(M, residual, norm_w, 1e-6)
+
+        def run_nccl_ar_only(i):
+            dist.all_reduce(ybuf)
+
         res = {}
-        for name, fn in (("fused1", run_fused1), ("fused2", run_fused2), ("nccl", run_nccl)):
+        parts = (("fused1", run_fused1), ("fused2", run_fused2), ("nccl", run_nccl))
+        if os.environ.get("BENCH_PARTS", "0") == "1":
+            parts += (("gemm_only", run_gemm_only), ("reduce_norm_gather_only", run_reduce_only),
+                      ("nccl_allreduce_only", run_nccl_ar_only))
+        for name, fn in parts:
             for i in range(5):
                 fn(i)
             torch.cuda.synchronize()

@@ -70,8 +70,11 @@ class FusedComm:
         self.ag_epoch = 0
         self.single_kernel = os.environ.get("KSANA_DISABLE_FUSED_GEMM_RS", "0") != "1"
         self.comm_ctas = int(os.environ.get("KSANA_FUSED_COMM_CTAS", "16"))
-        # latency-bound steps (few tokens, many ranks): GEMM + reduce/norm/gather kernel instead of the single kernel
-        self.two_kernel_max_tokens = int(os.environ.get("KSANA_TWO_KERNEL_MAX_TOKENS", "256" if size >= 4 else "0"))
+        # Row-parallel GEMM + collective: ONE kernel (GEMM epilogue pushes tiles, communication warps reduce) or the
+        # plain GEMM into symmetric memory followed by the reduce/norm/gather kernel. Measured (Llama-7B shapes,
+        # 730 tokens): 2 ranks 1-kernel wins; 4 ranks 72 us vs 58 us and 8 ranks 81 us vs 48 us (64 tokens) for the
+        # 2-kernel form at every size tried, so 4+ ranks always take it.
+        self.two_kernel_max_tokens = int(os.environ.get("KSANA_TWO_KERNEL_MAX_TOKENS", "1048576" if size >= 4 else "0"))
         self.epoch = 0
         lib = kcuda.lib()
         lib.ksana_rs_norm_ag.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,

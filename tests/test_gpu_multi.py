@@ -165,8 +165,10 @@ def test_fused_reduce_norm_ranks(use_mc, world):
         assert p.exitcode == 0
     print(rep)
     assert rep["kernel_error"] == 0 and rep["kernel_error2"] == 0
+    # sums of `world` unit-variance terms: one bf16 ulp grows with the magnitude of the sum
+    tol = 6e-2 * max(1.0, (world / 2) ** 0.5)
     for T, e1, e2 in rep["errs"]:
-        assert e1 < 6e-2 and e2 < 6e-2, (T, e1, e2)
+        assert e1 < tol and e2 < tol, (T, e1, e2)
     for T, K, e1, e2 in rep["ferrs"]:
         assert e1 < 8e-2 and e2 < 8e-2, (T, K, e1, e2)
     for rows_per, N, e, m in rep["aerrs"]:
