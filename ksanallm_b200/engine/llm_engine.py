@@ -113,7 +113,7 @@ class LLMEngine:
         max_blocks_per_seq = (bs_cfg.max_token_len + self.block_size - 1) // self.block_size + 1
         self.runner = ModelRunner(model, num_blocks, self.block_size, num_host_blocks, bs_cfg.max_step_tokens,
                                   bs_cfg.max_batch_size, max_blocks_per_seq, kv_dtype, seed)
-        self.is_driver = self.tp.rank == 0
+        self.is_driver = self.tp.rank == 0  # with pipeline stages: re-set by attach_pipeline (global rank 0 drives)
         self.mtp_steps = bs_cfg.mtp_step_num if (bs_cfg.enable_speculative_decoding or bs_cfg.mtp_step_num) and \
             model.mtp_layers else 0
         self.trie_drafts = 3 if (bs_cfg.enable_speculative_decoding and not model.mtp_layers) else 0
@@ -150,6 +150,7 @@ class LLMEngine:
         self.stats = {"generated_tokens": 0, "prompt_tokens": 0, "steps": 0, "forward_time": 0.0, "schedule_time": 0.0,
                       "t_broadcast": 0.0, "t_launch": 0.0, "t_sample_sync": 0.0, "t_apply": 0.0}
         self.on_step: Optional[Callable[[Dict[str, Any]], None]] = None
+        self.pipeline = None  # parallel.pipeline.PipelineStage when the model is split over stages
 
     # ---- sizing ----------------------------------------------------------------------------------------
     def _derive_num_blocks(self, kv_dtype) -> int:
@@ -268,15 +269,19 @@ class LLMEngine:
             layout = self.sched.pack(plan, self.runner.staging.host_np, self.runner.max_blocks_per_seq)
             rows, greedy, refit = self._sample_rows(plan)
         t1 = time.perf_counter()
-        if self.tp.size > 1:
+        if self._has_followers():
             self._broadcast_plan(layout, plan, greedy)
         ta = time.perf_counter()
         self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
         meta = self.runner.upload(layout)
-        hidden = self.runner.forward(meta, refit)
-        self._run_probes(plan, meta, hidden)
-        tb = time.perf_counter()
-        out = self.runner.sample(hidden, meta, rows, greedy)
+        if self.pipeline is not None and self.pipeline.topo.num_stages > 1:
+            out, hidden = self._pipeline_step_driver(meta, refit, rows, greedy)
+            tb = time.perf_counter()
+        else:
+            hidden = self.runner.forward(meta, refit)
+            self._run_probes(plan, meta, hidden)
+            tb = time.perf_counter()
+            out = self.runner.sample(hidden, meta, rows, greedy)
         t2 = time.perf_counter()
         with self.lock:
             n_new = self._apply_results(plan, out, meta, hidden)
@@ -440,6 +445,10 @@ class LLMEngine:
     def attach_control_group(self, group) -> None:
         self._ctl = group
 
+    def _has_followers(self) -> bool:
+        """Other ranks execute this engine's plans: tensor-parallel peers and / or later pipeline stages."""
+        return self.tp.size > 1 or (self.pipeline is not None and self.pipeline.topo.num_stages > 1)
+
     def _broadcast_plan(self, layout, plan, greedy: bool, stop: bool = False) -> None:
         keys = ["num_seqs", "num_prefill", "num_decode", "total_tokens", "total_logits", "max_q_len", "max_kv_len",
                 "max_blocks", "input_ids", "positions", "slot_mapping", "seq_of_token", "cu_q", "kv_lens", "q_starts",
@@ -487,11 +496,47 @@ class LLMEngine:
                 so, si, bc = a[:nso], a[nso:nso + nsi], a[nso + nsi:]
             self.runner.apply_block_ops(so, si, bc)
             meta = self.runner.upload(layout)
+            if self.pipeline is not None and self.pipeline.topo.num_stages > 1:
+                self._pipeline_step_follower(meta)
+                continue
             hidden = self.runner.forward(meta)
             self.runner.sample(hidden, meta, None, bool(h[30]))
 
+    # ---- pipeline parallelism ---------------------------------------------------------------------------------
+    def attach_pipeline(self, stage) -> None:
+        """``stage``: parallel.pipeline.PipelineStage of this rank. The driver is rank 0 (first stage); the last
+        stage computes the tokens and returns them to the driver."""
+        self.pipeline = stage
+        self.is_driver = stage.topo.rank == 0
+
+    def _pipeline_step_driver(self, meta, refit, rows, greedy):
+        from .sampler import SampleOutput
+        if not greedy:
+            raise NotImplementedError("pipeline-parallel serving samples greedily (top-k/top-p state lives on the "
+                                      "driver, the logits on the last stage)")
+        pl = self.pipeline
+        hidden = pl.run(meta, self.runner.kv_caches, refit)
+        n = meta.total_logits
+        if n == 0:
+            return SampleOutput(tokens=[]), hidden
+        if pl.topo.is_last:
+            toks = self.model.greedy_tokens(hidden, meta.logits_idx)
+        else:
+            toks = pl.channel.recv_tokens(n, pl.topo.num_stages * pl.topo.tp_size - pl.topo.tp_size)
+        host = toks.to("cpu").tolist()
+        self.runner.d2h_bytes += 4 * n
+        return SampleOutput(tokens=host, logprobs=[None] * n, chosen_logprob=[None] * n), hidden
+
+    def _pipeline_step_follower(self, meta) -> None:
+        pl = self.pipeline
+        hidden = pl.run(meta, self.runner.kv_caches)
+        if pl.topo.is_last and meta.total_logits:
+            toks = self.model.greedy_tokens(hidden, meta.logits_idx)
+            if pl.topo.tp_rank == 0:
+                pl.channel.send_tokens(toks, 0)
+
     def shutdown_followers(self) -> None:
-        if self.tp.size > 1 and self.is_driver and self._ctl is not None:
+        if self._has_followers() and self.is_driver and self._ctl is not None:
             self._broadcast_plan(None, None, True, stop=True)
 
     # ---- loops ----------------------------------------------------------------------------------------------

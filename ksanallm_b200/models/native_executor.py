@@ -50,7 +50,7 @@ class DenseExecutor:
         cfg, tp = model.cfg, model.tp
         if os.environ.get("KSANA_DISABLE_NATIVE_EXECUTOR", "0") == "1" or os.environ.get("KSANA_LIBRARY_BASELINE") == "1":
             return False
-        if model.device.type != "cuda" or model.dtype != torch.bfloat16 or not model.layers:
+        if model.device.type != "cuda" or model.dtype != torch.bfloat16 or not model.layers or model.norm_w is None:
             return False
         if getattr(model, "num_cache_layers", len(model.layers)) != len(model.layers):
             return False  # cross-layer KV sharing

@@ -149,10 +149,15 @@ class TransformerModel:
                 x[pos:pos + emb.shape[0]] = emb.to(x.dtype)
         return x
 
-    def forward(self, meta, kv_caches, refit=None, cutoff_layer: Optional[int] = None) -> torch.Tensor:
+    def forward(self, meta, kv_caches, refit=None, cutoff_layer: Optional[int] = None,
+                hidden_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Returns the final normalised hidden states [T, H]. ``self.last_residual`` then holds the
-        un-normalised residual stream (the "transformer" probe target)."""
-        x = self.embed_tokens(meta, refit)
+        un-normalised residual stream (the "transformer" probe target).
+
+        Pipeline stages: ``hidden_in`` is the residual stream received from the previous stage (no embedding
+        lookup); a stage built without ``model.norm.weight`` (not the last one) returns the un-normalised residual
+        stream for the next stage."""
+        x = self.embed_tokens(meta, refit) if hidden_in is None else hidden_in
         layers = self.layers if cutoff_layer is None else self.layers[:cutoff_layer]
         residual = x
         if not layers:

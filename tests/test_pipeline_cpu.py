@@ -1,0 +1,103 @@
+"""Pipeline parallelism on CPU (gloo): layer split, micro-batch controller, and a 2-stage engine whose greedy
+output must equal the single-process run."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ksanallm_b200.config.model_config import model_config_from_dict
+from ksanallm_b200.config.schema import parse_serving_config
+from ksanallm_b200.engine.llm_engine import LLMEngine
+from ksanallm_b200.engine.sampling_params import SamplingParams
+from ksanallm_b200.models.loader import load_model_weights
+from ksanallm_b200.models.transformer import TransformerModel
+from ksanallm_b200.parallel.comm import TPGroup
+from ksanallm_b200.parallel.pipeline import (BatchState, HiddenChannel, MultiBatchController, PipelineStage,
+                                             StageTopology, split_layers)
+
+
+def test_split_layers():
+    assert [list(r) for r in split_layers(5, 2)] == [[0, 1, 2], [3, 4]]
+    assert [len(r) for r in split_layers(61, 4)] == [16, 15, 15, 15]
+    assert [len(r) for r in split_layers(8, 2, first_stage_offload=2)] == [2, 6]
+    r = split_layers(32, 8)
+    assert r[0].start == 0 and r[-1].stop == 32 and all(a.stop == b.start for a, b in zip(r, r[1:]))
+
+
+def test_multi_batch_controller_orders_micro_batches():
+    c = MultiBatchController(3)
+    assert c.next_runnable() is None
+    c.ready(1)
+    c.ready(0)
+    assert c.next_runnable() == 1
+    c.start(1)
+    assert c.next_runnable() is None  # one micro-batch owns the device
+    c.done(1)
+    assert c.state[1] == BatchState.FINISHED and c.next_runnable() == 0
+    c.start(0)
+    c.collected(1)
+    c.ready(1)  # re-scheduled while 0 runs
+    c.done(0)
+    assert c.wait_turn(1, timeout=1.0)
+    c.done(1)
+    assert c.history == [1, 0, 1]
+
+
+def _cfg():
+    return model_config_from_dict(dict(model_type="llama", hidden_size=128, num_hidden_layers=4, num_attention_heads=4,
+                                       num_key_value_heads=2, intermediate_size=256, vocab_size=500,
+                                       torch_dtype="float32", eos_token_id=2))
+
+
+def _serving():
+    return parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 64,
+                                                                 "max_token_len": 128}}})
+
+
+PROMPTS = [[5, 9, 77, 120, 33, 4, 8], [400, 3, 3, 19, 250, 7, 7, 7, 91, 12, 13], [8, 6, 4]]
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    topo = StageTopology(world, 1, rank)
+    cfg = _cfg()
+    ranges = split_layers(cfg.num_layers, topo.num_stages)
+    w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32, layer_range=ranges[topo.stage])
+    model = TransformerModel(cfg, w, TPGroup(), layer_range=ranges[topo.stage])
+    if not topo.is_last:
+        model.norm_w = None  # the next stage normalises
+    eng = LLMEngine(model, _serving(), num_blocks=64, num_host_blocks=0)
+    eng.attach_control_group(dist.group.WORLD)
+    eng.attach_pipeline(PipelineStage(model, topo, HiddenChannel(topo, cfg.hidden_size, torch.float32,
+                                                                 torch.device("cpu"))))
+    if rank == 0:
+        reqs = eng.generate(PROMPTS, SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True))
+        eng.shutdown_followers()
+        out.put([r.output_token_ids[0] for r in reqs])
+    else:
+        eng.follow()
+    dist.destroy_process_group()
+
+
+def test_pp2_matches_single_process():
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32)
+    eng = LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=64, num_host_blocks=0)
+    want = [r.output_token_ids[0] for r in eng.generate(PROMPTS, SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True))]
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    assert got == want
