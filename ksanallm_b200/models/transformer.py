@@ -93,6 +93,7 @@ class TransformerModel:
         if cfg.position_encoding == "rope":
             rd = cfg.qk_rope_head_dim if cfg.use_mla else (cfg.rotary_dim or cfg.head_dim)
             self.rope_cache = ref.build_rope_cache(rd, maxp, cfg.rope_theta, cfg.rope_scaling, self.device)
+        self.progress = None  # optional per-layer completion tracker (prefill/decode disaggregation)
         self.layer_ids = list(layer_range) if layer_range is not None else list(range(cfg.num_layers))
         self.layers: List[DecoderLayer] = [DecoderLayer(cfg, weights, i, self.tp, self.rope_cache)
                                            for i in self.layer_ids]
@@ -173,11 +174,15 @@ class TransformerModel:
                 residual = residual.contiguous()
             h = native.forward(meta, kv_caches, h.contiguous(), residual, len(layers))
             self.last_residual = residual
+            if self.progress is not None:
+                self.progress.record(len(layers) - 1)  # one launch covers the stack: every layer reports together
             return h
         for li, layer in enumerate(layers):
             nxt = layers[li + 1] if li + 1 < len(layers) else None
             nw, nb = (nxt.ln1, nxt.ln1_b) if nxt is not None else (self.norm_w, self.norm_b)
             h = layer.forward(h, residual, meta, kv_caches[li], nw, nb)
+            if self.progress is not None:
+                self.progress.record(li)  # parallel.transfer.LayerProgressTracker: KV of layer li may leave now
         self.last_residual = residual
         return h
 

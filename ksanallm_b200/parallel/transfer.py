@@ -1,0 +1,232 @@
+"""Prefill / decode disaggregation: moving a request's KV blocks (and its first token) from the prefill instance to
+the decode instance, layer by layer as the layers finish.
+
+Reference: TransferEngine (src/ksana_llm/transfer/transfer_engine.h:63-190) is driven by LayerProgressTracker
+(runtime/layer_progress_tracker.{h,cpp}: one CUDA event per layer, a monitor thread, a callback that pushes the
+layer's blocks) over the connector's NCCL / ZMQ / TCP communicators (connector/communicator/**); the first token and
+draft tokens follow the blocks (runtime/llm_runtime.cpp:253-279).
+
+Both sides go through the prefix tree of their KV cache manager: the exporter pins the request's full blocks by
+matching its tokens, the importer allocates blocks for the same tokens, receives into them and commits them, after
+which the ordinary admission path finds them as a cached prefix and only recomputes the unfinished tail block.
+"""
+from __future__ import annotations
+
+import socket
+import struct
+import threading
+import time
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+class LayerProgressTracker:
+    """Per-layer completion events. ``record(layer)`` is called right after a layer's kernels were launched; a
+    monitor thread fires the callbacks in layer order once the device has actually finished them (CUDA events), or
+    immediately on CPU. Recording layer L implies every layer below it was launched before."""
+
+    def __init__(self, num_layers: int, device: torch.device):
+        self.num_layers, self.device = num_layers, torch.device(device)
+        self._callbacks: List[Callable[[int], None]] = []
+        self._events: Dict[int, "torch.cuda.Event"] = {}
+        self._lock = threading.Condition()
+        self._next = 0          # next layer whose completion has not been reported
+        self._recorded = -1     # highest layer recorded in this pass
+        self._stop = False
+        self._thread: Optional[threading.Thread] = None
+
+    def register_callback(self, fn: Callable[[int], None]) -> None:
+        self._callbacks.append(fn)
+
+    def reset(self) -> None:
+        with self._lock:
+            self._events.clear()
+            self._next, self._recorded = 0, -1
+
+    def record(self, layer: int) -> None:
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            with self._lock:
+                self._events[layer] = ev
+                self._recorded = max(self._recorded, layer)
+                self._lock.notify_all()
+            if self._thread is None:
+                self._thread = threading.Thread(target=self._monitor, daemon=True)
+                self._thread.start()
+        else:
+            with self._lock:
+                self._recorded = max(self._recorded, layer)
+            self._drain(layer)
+
+    def _drain(self, upto: int) -> None:
+        while self._next <= upto:
+            for fn in self._callbacks:
+                fn(self._next)
+            self._next += 1
+
+    def _monitor(self) -> None:
+        while True:
+            with self._lock:
+                self._lock.wait_for(lambda: self._stop or any(l >= self._next for l in self._events), timeout=0.5)
+                if self._stop:
+                    return
+                ready = sorted(l for l in self._events if l >= self._next)
+            for layer in ready:
+                self._events[layer].synchronize()
+                self._drain(layer)
+
+    def wait_all(self, timeout: float = 30.0) -> bool:
+        t0 = time.time()
+        while self._next <= self._recorded:
+            if time.time() - t0 > timeout:
+                return False
+            time.sleep(0.0005)
+        return True
+
+    def close(self) -> None:
+        with self._lock:
+            self._stop = True
+            self._lock.notify_all()
+
+
+# ---- transports -----------------------------------------------------------------------------------------------------
+class DistTransport:
+    """torch.distributed point-to-point (NCCL between GPUs, gloo on CPU)."""
+
+    def __init__(self, group=None):
+        self.group = group
+
+    def send(self, t: torch.Tensor, peer: int) -> None:
+        dist.send(t.contiguous(), dst=peer, group=self.group)
+
+    def recv(self, t: torch.Tensor, peer: int) -> None:
+        dist.recv(t, src=peer, group=self.group)
+
+
+class TcpTransport:
+    """Host-staged TCP stream for instances that share no process group (the reference's TCP communicator)."""
+
+    def __init__(self, sock: socket.socket):
+        self.sock = sock
+        self.sock.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+
+    @staticmethod
+    def listen(host: str, port: int) -> "TcpTransport":
+        srv = socket.socket()
+        srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        srv.bind((host, port))
+        srv.listen(1)
+        conn, _ = srv.accept()
+        srv.close()
+        return TcpTransport(conn)
+
+    @staticmethod
+    def connect(host: str, port: int, retries: int = 100) -> "TcpTransport":
+        for _ in range(retries):
+            try:
+                return TcpTransport(socket.create_connection((host, port)))
+            except OSError:
+                time.sleep(0.05)
+        raise ConnectionError(f"cannot reach {host}:{port}")
+
+    def send(self, t: torch.Tensor, peer: int = 0) -> None:
+        raw = t.detach().to("cpu").contiguous().view(torch.uint8).numpy().tobytes()
+        self.sock.sendall(struct.pack("<q", len(raw)) + raw)
+
+    def recv(self, t: torch.Tensor, peer: int = 0) -> None:
+        n = struct.unpack("<q", self._read(8))[0]
+        buf = torch.frombuffer(bytearray(self._read(n)), dtype=torch.uint8)
+        t.copy_(buf.view(t.dtype).view(t.shape))
+
+    def _read(self, n: int) -> bytes:
+        chunks = []
+        while n:
+            c = self.sock.recv(min(n, 1 << 20))
+            if not c:
+                raise ConnectionError("peer closed")
+            chunks.append(c)
+            n -= len(c)
+        return b"".join(chunks)
+
+
+# ---- engine ------------------------------------------------------------------------------------------------------------
+class TransferEngine:
+    def __init__(self, kv_caches: Sequence[torch.Tensor], cache_manager, transport, block_size: int):
+        self.kv, self.cache, self.tr, self.block_size = list(kv_caches), cache_manager, transport, block_size
+        self._tmp_ids = iter(range(-2, -(1 << 40), -1))
+        self.sent_blocks = self.recv_blocks = 0
+
+    def _hdr(self) -> torch.Tensor:
+        return torch.zeros(4, dtype=torch.int64)
+
+    def export_request(self, tokens: Sequence[int], first_tokens: Sequence[int], peer: int,
+                       tracker: Optional[LayerProgressTracker] = None) -> int:
+        """Sends the KV of every FULL block of ``tokens`` (they must still be in the prefix tree: the request was
+        just prefilled with prefix caching on) followed by the tokens generated so far. Returns blocks sent."""
+        toks = [int(t) for t in tokens]
+        tmp = next(self._tmp_ids)
+        hit = self.cache.create_seq(tmp, toks + [0])  # + 1: matching never covers the whole sequence
+        n_blocks = hit // self.block_size
+        blocks = list(self.cache.block_table(tmp))[:n_blocks]
+        try:
+            h = self._hdr()
+            h[0], h[1], h[2], h[3] = len(toks), n_blocks, len(first_tokens), len(self.kv)
+            self.tr.send(h, peer)
+            self.tr.send(torch.tensor(toks + [int(t) for t in first_tokens], dtype=torch.int32), peer)
+            if n_blocks:
+                idx = torch.tensor(blocks, dtype=torch.long, device=self.kv[0].device)
+                send_layer = lambda l: self.tr.send(self.kv[l].index_select(0, idx), peer)  # noqa: E731
+                if tracker is not None:
+                    # layers are pushed as the device finishes them
+                    done = threading.Event()
+
+                    def cb(layer, _n=len(self.kv)):
+                        send_layer(layer)
+                        if layer == _n - 1:
+                            done.set()
+                    tracker.register_callback(cb)
+                    done.wait(60.0)
+                else:
+                    for l in range(len(self.kv)):
+                        send_layer(l)
+            self.sent_blocks += n_blocks
+        finally:
+            self.cache.free_seq(tmp)
+        return n_blocks
+
+    def import_request(self, peer: int) -> Tuple[List[int], List[int], int]:
+        """Receives one exported request. Returns (prompt tokens, tokens already generated, blocks placed in the
+        prefix tree)."""
+        h = self._hdr()
+        self.tr.recv(h, peer)
+        n_tok, n_blocks, n_first, n_layers = (int(x) for x in h)
+        assert n_layers == len(self.kv), "both instances must hold the same layers"
+        tt = torch.zeros(n_tok + n_first, dtype=torch.int32)
+        self.tr.recv(tt, peer)
+        toks, first = tt[:n_tok].tolist(), tt[n_tok:].tolist()
+        if n_blocks == 0:
+            return toks, first, 0
+        tmp = next(self._tmp_ids)
+        covered = n_blocks * self.block_size
+        hit = self.cache.create_seq(tmp, toks[:covered] + [0])
+        have = hit // self.block_size
+        ok = self.cache.ensure_capacity(tmp, covered)
+        table = list(self.cache.block_table(tmp)) if ok else []
+        dev = self.kv[0].device
+        for l in range(n_layers):
+            buf = torch.empty((n_blocks,) + tuple(self.kv[l].shape[1:]), dtype=self.kv[l].dtype, device=dev)
+            self.tr.recv(buf, peer)
+            if ok and have < n_blocks:
+                idx = torch.tensor(table[have:n_blocks], dtype=torch.long, device=dev)
+                self.kv[l].index_copy_(0, idx, buf[have:])
+        placed = 0
+        if ok:
+            self.cache.commit_filled(tmp, toks[:covered] + [0], covered)
+            placed = n_blocks - have
+        self.cache.free_seq(tmp)
+        self.recv_blocks += placed
+        return toks, first, placed
