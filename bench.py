@@ -43,6 +43,7 @@ def parse_args():
     ap.add_argument("--max-step-tokens", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncates the model (result marked invalid)")
     ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--no-async", action="store_true", help="synchronous scheduling (host waits for every step)")
     return ap.parse_args()
 
 
@@ -162,6 +163,7 @@ def main():
         "global": {"tensor_para_size": world, "enable_cuda_graph": not args.no_cuda_graph},
         "batch_scheduler": {"max_batch_size": args.max_batch, "max_step_tokens": args.max_step_tokens,
                             "max_token_len": 3200, "max_waiting_queue_len": 100000, "preempt_mode": 1,
+                            "enable_async": not args.no_async,
                             "enable_auto_prefix_cache": False},
         "block_manager": {"block_token_num": 16}}})
     eng = LLMEngine(model, serving, tp)
@@ -249,6 +251,7 @@ def main():
                        "global_batch": args.max_batch, "seq_len": "prompt lognormal(200,1.0)[4,2048] + "
                        "output lognormal(180,1.0)[4,1024]", "parallelism": f"tp{world}",
                        "max_step_tokens": args.max_step_tokens, "requests": args.requests,
+                       "scheduling": "sync" if args.no_async else "async (host one step behind the device)",
                        "l2": "weights (13.5 GB) and KV cache far exceed the 126 MB L2: no explicit flush",
                        "weights": "random N(0, 0.02), seed 0"},
             "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": int(result["h2d"]),

@@ -520,6 +520,44 @@ class Scheduler {
     return out;
   }
 
+  // Asynchronous scheduling: Update() may be called with PLACEHOLDER tokens (negative values, -(1 + row) where row
+  // is the token's position in the step's sampled vector) before the device has produced the real ones, so that the
+  // next step can be planned while this one runs. Placeholders never match a stop token; length limits still apply.
+  // Resolve() later patches the real tokens in and reports the sequences that turn out to have finished on an EOS /
+  // stop token. Such a sequence may already be part of the following in-flight step: Update() of that step skips it
+  // (it is no longer running) and its blocks were released here; the stray KV write of the in-flight step lands
+  // before any later step can reuse the blocks (same stream).
+  // Requires one logit per entry (no draft tokens). Returns (seq_id, real token, finish_reason) per sampled row.
+  std::vector<StepResult> Resolve(const StepPlan& plan, const std::vector<int32_t>& real) {
+    std::vector<StepResult> out;
+    size_t cursor = 0;
+    for (auto& e : plan.entries) {
+      size_t base = cursor;
+      cursor += e.num_logits;
+      if (e.num_logits == 0) continue;
+      auto it = seqs_.find(e.seq_id);
+      if (it == seqs_.end()) continue;
+      Sequence& s = *it->second;
+      const int32_t want = -(1 + static_cast<int32_t>(base));
+      // the placeholder is the last token of the sequence (nothing was appended since)
+      if (s.tokens.empty() || s.tokens.back() != want) continue;
+      const int32_t tok = real[base];
+      s.tokens.back() = tok;
+      StepResult r{e.seq_id, {tok}, 0, s.state == SEQ_FINISHED ? s.finish_reason : FINISH_NONE};
+      if (s.state != SEQ_FINISHED && IsStop(s, tok)) {
+        int reason = FINISH_STOP_TOKEN;
+        if (!s.ignore_eos)
+          for (auto x : s.eos_ids)
+            if (x == tok) reason = FINISH_EOS;
+        RemoveFromQueues(s.id);
+        Retire(s, reason);
+        r.finish_reason = reason;
+      }
+      out.push_back(std::move(r));
+    }
+    return out;
+  }
+
  private:
   int64_t ComputeLayout(const StepPlan& plan, int max_blocks, PackedLayout* l) const {
     auto align = [](int64_t x) { return (x + 31) / 32 * 32; };

@@ -151,6 +151,11 @@ class LLMEngine:
                       "t_broadcast": 0.0, "t_launch": 0.0, "t_sample_sync": 0.0, "t_apply": 0.0}
         self.on_step: Optional[Callable[[Dict[str, Any]], None]] = None
         self.pipeline = None  # parallel.pipeline.PipelineStage when the model is split over stages
+        # asynchronous scheduling (setting.batch_scheduler.enable_async): step N + 1 is planned and launched while
+        # step N still runs; its tokens reach the host one step late
+        self.async_mode = bool(bs_cfg.enable_async) and not self.mtp_steps and not self.trie_drafts
+        self._inflight = None       # (plan, token handle) of the step whose tokens are not on the host yet
+        self._complex_requests = 0  # live requests that need per-token host state (grammar, beams, penalties, ...)
 
     # ---- sizing ----------------------------------------------------------------------------------------
     def _derive_num_blocks(self, kv_dtype) -> int:
@@ -196,6 +201,8 @@ class LLMEngine:
             first = self._enqueue_seq(req, req.prompt_tokens)
             req._pending_fanout = n_out - 1 if params.num_beams <= 1 else 0
             self.requests[req.req_id] = req
+            req._complex = self._needs_host_tokens(params, req) or n_out > 1
+            self._complex_requests += 1 if req._complex else 0
             self.stats["prompt_tokens"] += len(req.prompt_tokens)
         self._wake.set()
         return req
@@ -252,11 +259,19 @@ class LLMEngine:
         self._wake.set()
 
     def has_unfinished(self) -> bool:
-        return self.sched.has_unfinished()
+        return self.sched.has_unfinished() or self._inflight is not None
 
     # ---- one step ----------------------------------------------------------------------------------------
     def step(self) -> int:
         """Schedules and runs one step. Returns the number of tokens generated."""
+        if self.async_mode and self.is_driver:
+            if self._complex_requests == 0 and (self.pipeline is None or self.pipeline.topo.num_stages == 1):
+                return self._step_async()
+            drained = self._drain_inflight()
+            return drained + self._step_sync()
+        return self._step_sync()
+
+    def _step_sync(self) -> int:
         t0 = time.perf_counter()
         with self.lock:
             plan = self.sched.schedule(int(time.time() * 1000))
@@ -302,6 +317,74 @@ class LLMEngine:
                           "decode": meta.num_decode})
         return n_new
 
+    # ---- asynchronous scheduling ---------------------------------------------------------------------------------
+    @staticmethod
+    def _needs_host_tokens(params, req) -> bool:
+        """True when sampling this request depends on host-side per-token state, which lags one step in async mode."""
+        p = params
+        greedy = p.do_sample is False or p.topk == 1
+        return (not greedy or p.logprobs > 0 or p.repetition_penalty != 1.0 or p.no_repeat_ngram_size > 0 or
+                p.encoder_no_repeat_ngram_size > 0 or p.decoder_no_repeat_ngram_size > 0 or p.num_beams > 1 or
+                bool(p.stop_strings) or req.grammar is not None or req.probe is not None or req.refit is not None)
+
+    def _drain_inflight(self) -> int:
+        """Brings the tokens of the in-flight step to the host and applies them."""
+        inf, self._inflight = self._inflight, None
+        if inf is None:
+            return 0
+        from .sampler import SampleOutput
+        plan, handle = inf
+        toks = self.runner.wait_tokens(handle)
+        n = len(toks)
+        with self.lock:
+            results = self.sched.resolve(plan, toks)
+            return self._apply_results(plan, SampleOutput(tokens=toks, logprobs=[None] * n, chosen_logprob=[None] * n),
+                                       None, None, results=results)
+
+    def _step_async(self) -> int:
+        """One step with the host one token behind the device (reference: the async mode of ScheduleProcessor,
+        src/ksana_llm/batch_manager/schedule_processor.cpp:118-199, which plans on estimated generation results).
+        The plan is built from placeholder tokens; the device substitutes the real ones from the previous step's
+        token vector (ModelRunner.fixup_inputs)."""
+        t0 = time.perf_counter()
+        with self.lock:
+            plan = self.sched.schedule(int(time.time() * 1000))
+            for sid, reason in plan.dropped:
+                self._finish_seq(sid, reason)
+            if plan.empty():
+                return self._drain_inflight()
+            self.runner.staging.flip()
+            layout = self.sched.pack(plan, self.runner.staging.host_np, self.runner.max_blocks_per_seq)
+        t1 = time.perf_counter()
+        fix = self._inflight is not None
+        if self._has_followers():
+            self._broadcast_plan(layout, plan, True, fixup=fix)
+        ta = time.perf_counter()
+        self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
+        meta = self.runner.upload(layout)
+        if fix:
+            self.runner.fixup_inputs(meta)
+        hidden = self.runner.forward(meta, None)
+        handle = self.runner.sample_greedy_async(hidden, meta)
+        tb = time.perf_counter()
+        n_new = self._drain_inflight()  # the PREVIOUS step: its tokens were produced before this one started
+        t2 = time.perf_counter()
+        with self.lock:
+            placeholders = [-(1 + i) for i in range(plan.total_logits)]
+            self.sched.update(plan, placeholders, int(time.time() * 1000))
+        self._inflight = (plan, handle)
+        t3 = time.perf_counter()
+        self.step_count += 1
+        st = self.stats
+        st["steps"] += 1
+        st["schedule_time"] += t1 - t0
+        st["forward_time"] += t2 - t1
+        st["t_broadcast"] += ta - t1
+        st["t_launch"] += tb - ta
+        st["t_sample_sync"] += t2 - tb
+        st["t_apply"] += t3 - t2
+        return n_new
+
     def _sample_rows(self, plan):
         rows: List[SampleRow] = []
         refit = None
@@ -319,11 +402,12 @@ class LLMEngine:
         greedy = Sampler.all_greedy(rows)
         return rows, greedy, refit
 
-    def _apply_results(self, plan, out, meta, hidden) -> int:
+    def _apply_results(self, plan, out, meta, hidden, results=None) -> int:
         now = time.time()
         sampled = out.tokens
         # beam search rewrites the sampled tokens from the top-2k log-probs before the scheduler sees them
-        results = self.sched.update(plan, sampled, int(now * 1000))
+        if results is None:
+            results = self.sched.update(plan, sampled, int(now * 1000))
         row = 0
         row_of = {}
         for e in plan.entries:
@@ -427,6 +511,9 @@ class LLMEngine:
             req.finished = True
             req.finish_time = time.time()
             self.requests.pop(req.req_id, None)
+            if getattr(req, "_complex", False):
+                req._complex = False
+                self._complex_requests -= 1
             if self.metrics is not None:
                 self.metrics.observe_request(req)
 
@@ -449,7 +536,7 @@ class LLMEngine:
         """Other ranks execute this engine's plans: tensor-parallel peers and / or later pipeline stages."""
         return self.tp.size > 1 or (self.pipeline is not None and self.pipeline.topo.num_stages > 1)
 
-    def _broadcast_plan(self, layout, plan, greedy: bool, stop: bool = False) -> None:
+    def _broadcast_plan(self, layout, plan, greedy: bool, stop: bool = False, fixup: bool = False) -> None:
         keys = ["num_seqs", "num_prefill", "num_decode", "total_tokens", "total_logits", "max_q_len", "max_kv_len",
                 "max_blocks", "input_ids", "positions", "slot_mapping", "seq_of_token", "cu_q", "kv_lens", "q_starts",
                 "logits_idx", "block_tables", "total_words"]
@@ -460,6 +547,7 @@ class LLMEngine:
             for i, k in enumerate(keys):
                 h[1 + i] = layout[k]
             h[30] = 1 if greedy else 0
+            h[34] = 1 if fixup else 0
             so, si, bc = plan.swap_out, plan.swap_in, plan.block_copies
             h[31], h[32], h[33] = len(so), len(si), len(bc)
         hdr = torch.from_numpy(h)
@@ -486,6 +574,7 @@ class LLMEngine:
                 return
             layout = {k: int(h[1 + i]) for i, k in enumerate(keys)}
             n = layout["total_words"]
+            self.runner.staging.flip()  # the previous step's host-to-device copy may still be pending
             dist.broadcast(self.runner.staging.host[:n], src=0, group=self._ctl)
             nso, nsi, nbc = int(h[31]), int(h[32]), int(h[33])
             so = si = bc = np.zeros((0, 2), dtype=np.int32)
@@ -496,6 +585,8 @@ class LLMEngine:
                 so, si, bc = a[:nso], a[nso:nso + nsi], a[nso + nsi:]
             self.runner.apply_block_ops(so, si, bc)
             meta = self.runner.upload(layout)
+            if h[34]:
+                self.runner.fixup_inputs(meta)
             if self.pipeline is not None and self.pipeline.topo.num_stages > 1:
                 self._pipeline_step_follower(meta)
                 continue

@@ -40,6 +40,7 @@ class ModelRunner:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.last_hidden: Optional[torch.Tensor] = None
+        self.prev_tokens: Optional[torch.Tensor] = None  # device copy of the last step's greedy tokens
 
     # ---- block movement -------------------------------------------------------------------------------
     def apply_block_ops(self, swap_out: np.ndarray, swap_in: np.ndarray, copies: np.ndarray) -> None:
@@ -84,6 +85,7 @@ class ModelRunner:
             greedy = rows is None or Sampler.all_greedy(rows)
         if greedy:
             toks = self.model.greedy_tokens(hidden, meta.logits_idx)
+            self.prev_tokens = toks
             if rows is None:
                 return SampleOutput(tokens=[])
             host = toks.to("cpu", non_blocking=False)
@@ -96,6 +98,43 @@ class ModelRunner:
         out = self.sampler.sample(logits, rows)
         self.d2h_bytes += 4 * len(out.tokens)
         return out
+
+    # ---- asynchronous scheduling support ------------------------------------------------------------------------
+    @torch.inference_mode()
+    def fixup_inputs(self, meta: StepInput) -> None:
+        """Input ids planned before the previous step's tokens reached the host are placeholders -(1 + row): they
+        are replaced on the device by row ``row`` of the previous step's token vector."""
+        if self.prev_tokens is None or meta.total_tokens == 0:
+            return
+        ids = meta.input_ids
+        src = (-ids - 1).clamp_(min=0, max=self.prev_tokens.numel() - 1).long()
+        ids.copy_(torch.where(ids < 0, self.prev_tokens.to(torch.int32).index_select(0, src), ids))
+
+    @torch.inference_mode()
+    def sample_greedy_async(self, hidden: torch.Tensor, meta: StepInput):
+        """Greedy tokens stay on the device (for ``fixup_inputs`` of the next step); the host copy is started
+        without waiting. Returns a handle for ``wait_tokens`` (None when the step has no logits)."""
+        if meta.total_logits == 0:
+            return None
+        toks = self.model.greedy_tokens(hidden, meta.logits_idx).to(torch.int32)
+        self.prev_tokens = toks
+        if toks.device.type != "cuda":
+            return (toks.clone(), None)
+        host = torch.empty(toks.shape, dtype=torch.int32, pin_memory=True)
+        host.copy_(toks, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.d2h_bytes += host.numel() * 4
+        return (host, ev)
+
+    @staticmethod
+    def wait_tokens(handle) -> List[int]:
+        if handle is None:
+            return []
+        host, ev = handle
+        if ev is not None:
+            ev.synchronize()
+        return host.tolist()
 
     @torch.inference_mode()
     def logits(self, hidden: torch.Tensor, meta: StepInput) -> torch.Tensor:

@@ -56,10 +56,21 @@ class StepStaging:
     def __init__(self, capacity_words: int, device: torch.device):
         self.device = torch.device(device)
         pin = self.device.type == "cuda"
-        self.host = torch.empty(capacity_words, dtype=torch.int32, pin_memory=pin)
+        # two host buffers: with asynchronous scheduling the next step is packed while the previous step's
+        # host-to-device copy may not have run yet
+        self._hosts = [torch.empty(capacity_words, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self._cur = 0
+        self.host = self._hosts[0]
         self.host_np = self.host.numpy()
         self.dev = self.host if self.device.type == "cpu" else torch.empty(
             capacity_words, dtype=torch.int32, device=self.device)
+
+    def flip(self) -> None:
+        if self.dev is self.host:
+            return  # CPU: the "device" view IS the host buffer and steps run synchronously
+        self._cur ^= 1
+        self.host = self._hosts[self._cur]
+        self.host_np = self.host.numpy()
 
     def upload(self, layout: Dict[str, int]) -> StepInput:
         n = layout["total_words"]

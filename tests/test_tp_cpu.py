@@ -22,22 +22,23 @@ def _cfg():
                                        torch_dtype="float32", eos_token_id=2))
 
 
-def _serving():
+def _serving(enable_async=False):
     return parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 64,
-                                                                 "max_token_len": 128}}})
+                                                                 "max_token_len": 128,
+                                                                 "enable_async": enable_async}}})
 
 
 PROMPTS = [[5, 9, 77, 120, 33, 4, 8], [400, 3, 3, 19, 250, 7, 7, 7, 91, 12, 13], [8, 6, 4]]
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, enable_async=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     tp = TPGroup(rank, world, dist.group.WORLD, torch.device("cpu"))
     cfg = _cfg()
     w = load_model_weights(cfg, synthetic_seed=1, tp_rank=rank, tp_size=world, dtype=torch.float32)
     model = TransformerModel(cfg, w, tp)
-    eng = LLMEngine(model, _serving(), tp, num_blocks=64, num_host_blocks=0)
+    eng = LLMEngine(model, _serving(enable_async), tp, num_blocks=64, num_host_blocks=0)
     eng.attach_control_group(dist.group.WORLD)
     if rank == 0:
         reqs = eng.generate(PROMPTS, SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True))
@@ -48,7 +49,11 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_tp2_matches_single_rank():
+import pytest
+
+
+@pytest.mark.parametrize("enable_async", [False, True])
+def test_tp2_matches_single_rank(enable_async):
     cfg = _cfg()
     w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32)
     eng = LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=64, num_host_blocks=0)
@@ -59,7 +64,7 @@ def test_tp2_matches_single_rank():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, enable_async)) for r in range(2)]
     for p in procs:
         p.start()
     got = q.get(timeout=120)
