@@ -156,6 +156,8 @@ class LLMEngine:
         self.async_mode = bool(bs_cfg.enable_async) and not self.mtp_steps and not self.trie_drafts
         self._inflight = None       # (plan, token handle) of the step whose tokens are not on the host yet
         self._complex_requests = 0  # live requests that need per-token host state (grammar, beams, penalties, ...)
+        self.dp = None              # parallel.attn_dp.DPCoordinator under attention data parallelism
+        self.dp_any_work = True
 
     # ---- sizing ----------------------------------------------------------------------------------------
     def _derive_num_blocks(self, kv_dtype) -> int:
@@ -277,6 +279,17 @@ class LLMEngine:
             plan = self.sched.schedule(int(time.time() * 1000))
             for sid, reason in plan.dropped:
                 self._finish_seq(sid, reason)
+            if self.dp is not None:
+                # attention data parallelism: all ranks step together; a rank without work runs a mock step
+                stride, anybody = self.dp.sync(plan.total_tokens, self.sched.has_unfinished())
+                self.dp_any_work = anybody
+                if self.tp.ep is not None:
+                    self.tp.ep.step_stride = max(stride, 1)
+                if plan.empty():
+                    if stride > 0:
+                        self.runner.mock_forward()
+                        self.stats["mock_steps"] = self.stats.get("mock_steps", 0) + 1
+                    return 0
             if plan.empty():
                 if self.tp.size > 1 and len(plan.swap_out) + len(plan.swap_in) + len(plan.block_copies) > 0:
                     pass
@@ -592,6 +605,24 @@ class LLMEngine:
                 continue
             hidden = self.runner.forward(meta)
             self.runner.sample(hidden, meta, None, bool(h[30]))
+
+    # ---- attention data parallelism ------------------------------------------------------------------------------
+    def attach_dp(self, coordinator) -> None:
+        """This engine is one DP rank: its own requests, scheduler and KV cache; MoE blocks exchange tokens with the
+        other ranks, so every rank steps in lock-step (``run_dp``)."""
+        self.dp = coordinator
+        self.async_mode = False
+        self.tp.ep_dp = True
+
+    def run_dp(self, max_steps: int = 1 << 30) -> int:
+        """Steps until NO rank has unfinished work (a rank whose own requests are done keeps running mock steps)."""
+        steps = 0
+        while steps < max_steps:
+            self._step_sync()
+            steps += 1
+            if not self.dp_any_work:
+                break
+        return steps
 
     # ---- pipeline parallelism ---------------------------------------------------------------------------------
     def attach_pipeline(self, stage) -> None:

@@ -75,6 +75,15 @@ class ModelRunner:
         return hidden
 
     @torch.inference_mode()
+    def mock_forward(self) -> None:
+        """A step with zero tokens: only the collectives inside the layers matter (expert-parallel exchanges of
+        the MoE blocks when other data-parallel ranks have work)."""
+        from .step_input import make_step_input
+        meta = make_step_input([], [], [], [0], [], torch.zeros(0, 1, dtype=torch.int32), logits_idx=[],
+                               num_prefill=0, device=self.device)
+        self.model.forward(meta, self.kv_caches)
+
+    @torch.inference_mode()
     def sample(self, hidden: torch.Tensor, meta: StepInput, rows: Optional[Sequence[SampleRow]],
                greedy: Optional[bool] = None) -> SampleOutput:
         """rows is None on ranks that do not own the sampler: they still join the collectives of the

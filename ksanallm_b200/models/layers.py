@@ -86,6 +86,7 @@ class Attention:
         self.k_norm = w.get(prefix + ".key_layernorm.weight")
         self.rope_cache = rope_cache
         self.scale = 1.0 / math.sqrt(self.d)
+        self.k_scale = self.v_scale = 1.0  # fp8 KV cache scaling factors (models/kv_scales.py)
         self.alibi = None
         if cfg.position_encoding == "alibi":
             full = ref.alibi_slopes(cfg.num_heads)
@@ -100,8 +101,8 @@ class Attention:
         v = qkv[:, nq + nk:].view(T, self.hk, self.d)
         ops.rope_qknorm_cache(q, k, v, meta.positions, self.rope_cache, meta.slot_mapping, kv_cache,
                               self.q_norm, self.k_norm, self.cfg.rms_norm_eps, self.cfg.rope_interleaved,
-                              self.cfg.rotary_dim)
-        o = ops.paged_attention(q, kv_cache, meta, self.scale, self.alibi)
+                              self.cfg.rotary_dim, self.k_scale, self.v_scale)
+        o = ops.paged_attention(q, kv_cache, meta, self.scale, self.alibi, self.k_scale, self.v_scale)
         return o.reshape(T, nq)
 
 
@@ -189,7 +190,7 @@ class MoEFFN:
         self.w_gate_up = w[prefix + ".experts.up_gate_proj.weight"]  # [E_local, 2I, H]
         self.w_down = w[prefix + ".experts.down_proj.weight"]        # [E_local, H, I]
         self.e_local = self.w_gate_up.shape[0]
-        self.expert_offset = tp.rank * self.e_local if self.e_local < cfg.num_experts else 0
+        self.expert_offset = tp.ep_rank * self.e_local if self.e_local < cfg.num_experts else 0
         self.shared = None
         if cfg.num_shared_experts:
             self.shared = DenseFFN(cfg, w, prefix + ".shared_expert", tp)
@@ -199,6 +200,8 @@ class MoEFFN:
         """Per-rank partial sum of the block output (needs a cross-rank sum when size > 1)."""
         c = self.cfg
         ep = self.tp.ep
+        if ep is not None and self.tp.ep_dp and self.e_local < c.num_experts:
+            return self._dp_exchange(h, ep)
         if (ep is not None and h.is_cuda and h.dtype == torch.bfloat16 and self.e_local < c.num_experts and
                 h.shape[0] <= ep.t_cap * ep.size):
             return self._partial_dispatch(h, ep)
@@ -213,6 +216,20 @@ class MoEFFN:
                 s = s * g
             y = y + s
         return y
+
+    def _dp_exchange(self, h: torch.Tensor, ep) -> torch.Tensor:
+        """Attention data parallelism: ``h`` holds only this rank's tokens (possibly none); the routed experts are
+        reached through the exchange, whose slot stride for this step was agreed by the DP coordinator."""
+        c = self.cfg
+        logits = ops.linear(h.float() if self.gate_w.dtype == torch.float32 else h, self.gate_w)
+        ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
+                                 c.topk_group, c.routed_scaling_factor, self.bias)
+        s = None
+        if self.shared is not None and h.shape[0]:
+            s = self.shared.down(self.shared.core(h))
+            if self.shared_gate is not None:
+                s = s * torch.sigmoid(ops.linear(h, self.shared_gate).float()).to(s.dtype)
+        return ep.moe(h, ids, wts, self.w_gate_up, self.w_down, ep.step_stride, add=s)
 
     def _partial_dispatch(self, h: torch.Tensor, ep) -> torch.Tensor:
         """Expert-parallel path: this rank routes only its own slice of the tokens, sends each row to the ranks

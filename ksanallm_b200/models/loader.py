@@ -561,8 +561,12 @@ class WeightLoader:
 def load_model_weights(cfg: ModelConfig, model_dir: str = "", tp_rank: int = 0, tp_size: int = 1, device="cpu",
                        dtype: Optional[torch.dtype] = None, quantize: Optional[str] = None,
                        synthetic_seed: Optional[int] = None, synthetic_std: float = 0.02,
-                       layer_range: Optional[range] = None) -> Dict[str, torch.Tensor]:
-    loader = WeightLoader(cfg, tp_rank, tp_size, device, dtype, quantize, model_dir=model_dir, layer_range=layer_range)
+                       layer_range: Optional[range] = None, ep_rank: Optional[int] = None,
+                       ep_size: Optional[int] = None) -> Dict[str, torch.Tensor]:
+    """``ep_rank`` / ``ep_size`` shard the routed experts independently of the tensor-parallel slicing (attention
+    data parallelism: tp_size 1, experts spread over the DP ranks)."""
+    loader = WeightLoader(cfg, tp_rank, tp_size, device, dtype, quantize, ep_rank=ep_rank, ep_size=ep_size,
+                          model_dir=model_dir, layer_range=layer_range)
     if synthetic_seed is not None or not model_dir:
         src = synthetic_checkpoint(cfg, synthetic_seed or 0, synthetic_std, device=device, dtype=dtype)
     else:

@@ -68,6 +68,8 @@ class DenseExecutor:
                 return False
             if layer.ln2 is None or getattr(layer, "ln2_b", None) is not None:
                 return False
+            if layer.attn.k_scale != 1.0 or layer.attn.v_scale != 1.0:
+                return False  # per-layer fp8 KV scales: Python layer path
         if tp.size > 1:
             fc = tp.fused
             if fc is None or not fc.single_kernel or fc.hidden % 256 or fc.hidden > 9216 or fc.hidden != cfg.hidden_size:

@@ -30,6 +30,8 @@ class TPGroup:
         self.use_fused = use_fused and size > 1
         self.fused = None  # parallel.fused.FusedComm, attached by init_fused()
         self.ep = None     # parallel.ep.EPExchange, attached by init_ep()
+        self.ep_dp = False  # attention data parallelism: this rank's tokens are its own (parallel/attn_dp.py)
+        self.ep_rank, self.ep_size = rank, size  # expert sharding (differs from rank/size under attention DP)
         self.stats = {"all_reduce": 0, "all_gather": 0, "fused": 0}
 
     def init_fused(self, hidden: int, max_tokens: int, use_multicast: Optional[bool] = None) -> bool:

@@ -42,6 +42,7 @@ class EPExchange:
         self._handle = symm_mem.rendezvous(self.buf, gname)
         self._ptrs = (ctypes.c_void_p * size)(*[int(p) for p in self._handle.buffer_ptrs])
         self.epoch = 0
+        self.step_stride = 0  # attention-DP mode: slot stride of the current step (set by the engine)
         lib = kcuda.lib()
         P, I, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint
         lib.ksana_ep_dispatch.argtypes = [I, I, P, P, P, I, P, P, I, I, I, I, I, U, P]

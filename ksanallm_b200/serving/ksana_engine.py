@@ -223,6 +223,11 @@ class KsanaLLMEngine:
                                             self.serving.setting.tokenization.skip_special_tokens, a.chat_template)
         kvd = self.serving.setting.quantization_config.kv_cache.dtype
         kv_dtype = torch.float8_e4m3fn if kvd == "fp8_e4m3" else (torch.float8_e5m2 if kvd == "fp8_e5m2" else None)
+        if kv_dtype is not None and not a.synthetic_model:
+            from ..models.kv_scales import apply_kv_scales, find_kv_scales_file, load_kv_cache_scales
+            scales_file = find_kv_scales_file(a.model_dir)
+            if scales_file:
+                apply_kv_scales(model, load_kv_cache_scales(scales_file, tp.rank, cfg.num_layers))
         self.llm = LLMEngine(model, self.serving, tp, detokenize=lambda ids: self.tokenizer.decode(ids),
                              kv_dtype=kv_dtype)
         if tp.size > 1:

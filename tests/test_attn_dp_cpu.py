@@ -1,0 +1,80 @@
+"""Attention data parallelism on CPU (gloo, 2 ranks): each rank serves its own requests with its own scheduler and
+cache, the routed experts are sharded over the ranks and reached through the exchange; ranks with nothing to do run
+mock steps. Outputs must equal a single-process run of the same prompts."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ksanallm_b200.config.model_config import model_config_from_dict
+from ksanallm_b200.config.schema import parse_serving_config
+from ksanallm_b200.engine.llm_engine import LLMEngine
+from ksanallm_b200.engine.sampling_params import SamplingParams
+from ksanallm_b200.models.loader import load_model_weights
+from ksanallm_b200.models.transformer import TransformerModel
+from ksanallm_b200.parallel.attn_dp import DPCoordinator, GatherEPExchange
+from ksanallm_b200.parallel.comm import TPGroup
+
+
+def _cfg():
+    return model_config_from_dict(dict(model_type="mixtral", hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                       num_key_value_heads=2, intermediate_size=96, num_local_experts=4,
+                                       num_experts_per_tok=2, vocab_size=300, torch_dtype="float32", eos_token_id=2))
+
+
+def _serving():
+    return parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 64,
+                                                                 "max_token_len": 128}}})
+
+
+PROMPTS = {0: [[5, 9, 77, 120, 33, 4, 8], [8, 6, 4]], 1: [[200, 3, 3, 19, 250, 7, 7, 7, 91, 12, 13, 14, 15, 16]]}
+NEW = {0: 9, 1: 3}  # rank 1 finishes early and must keep stepping (mock steps) until rank 0 is done
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32, ep_rank=rank, ep_size=world)
+    tp = TPGroup()
+    tp.ep_rank, tp.ep_size = rank, world
+    tp.ep = GatherEPExchange(dist.group.WORLD, rank, world, cfg.num_experts_per_tok, cfg.num_experts)
+    model = TransformerModel(cfg, w, tp)
+    eng = LLMEngine(model, _serving(), tp, num_blocks=64, num_host_blocks=0)
+    eng.attach_dp(DPCoordinator(dist.group.WORLD))
+    reqs = [eng.add_request(p, SamplingParams(topk=1, max_new_tokens=NEW[rank], ignore_eos=True)) for p in PROMPTS[rank]]
+    steps = eng.run_dp(max_steps=200)
+    out.put((rank, [r.output_token_ids[0] for r in reqs], steps, eng.stats.get("mock_steps", 0)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_attention_dp_two_ranks_match_single_process():
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32)
+    want = {}
+    for r in (0, 1):
+        eng = LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=64, num_host_blocks=0)
+        want[r] = [q.output_token_ids[0] for q in
+                   eng.generate(PROMPTS[r], SamplingParams(topk=1, max_new_tokens=NEW[r], ignore_eos=True))]
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict()
+    for _ in range(2):
+        rank, toks, steps, mocks = q.get(timeout=120)
+        got[rank] = (toks, steps, mocks)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got[0][0] == want[0] and got[1][0] == want[1]
+    assert got[0][1] == got[1][1], "ranks must take the same number of steps"
+    assert got[1][2] > 0, "the rank that finished first must have run mock steps"

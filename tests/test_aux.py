@@ -131,3 +131,30 @@ def test_registry():
     assert registry.resolve_family("Qwen3_MoE".lower()) == "qwen3_moe"
     assert registry.resolve_family("fairseq-transformer") == "gpt2"
     assert registry.resolve_family("totally_unknown") is None
+
+
+def test_kv_cache_scales_file(tmp_path):
+    import json
+
+    import pytest
+    import torch
+
+    from ksanallm_b200.config.model_config import model_config_from_dict
+    from ksanallm_b200.models.kv_scales import apply_kv_scales, find_kv_scales_file, load_kv_cache_scales
+    from ksanallm_b200.models.loader import load_model_weights
+    from ksanallm_b200.models.transformer import TransformerModel
+
+    doc = {"model_type": "llama", "kv_cache": {"dtype": "float8_e4m3fn",
+                                               "scaling_factor": {"0": {"0": 0.5, "1": 0.25}}}}
+    (tmp_path / "kv_cache_scales.json").write_text(json.dumps(doc))
+    path = find_kv_scales_file(str(tmp_path))
+    assert path is not None
+    assert load_kv_cache_scales(path, 1, 3) == [0.5, 0.25, 1.0]  # rank 1 falls back to the rank-0 table
+    with pytest.raises(ValueError):
+        load_kv_cache_scales(path, 0, 2, expect_model_type="qwen2")
+    cfg = model_config_from_dict(dict(model_type="llama", hidden_size=64, num_hidden_layers=2, num_attention_heads=2,
+                                      num_key_value_heads=2, intermediate_size=128, vocab_size=100,
+                                      torch_dtype="float32"))
+    m = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, dtype=torch.float32))
+    apply_kv_scales(m, [0.5, 0.25])
+    assert m.layers[0].attn.k_scale == 0.5 and m.layers[1].attn.v_scale == 0.25
