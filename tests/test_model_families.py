@@ -1,0 +1,130 @@
+"""Checkpoint naming conventions of the model families: a synthetic Llama-named checkpoint is re-expressed in each
+family's own tensor names / packings and must load into the SAME model (identical hidden states), or - where the
+architecture itself differs (GPT-2, ChatGLM) - load and run."""
+import torch
+
+from ksanallm_b200.config.model_config import model_config_from_dict
+from ksanallm_b200.engine.step_input import make_step_input
+from ksanallm_b200.models.loader import WeightLoader, synthetic_checkpoint
+from ksanallm_b200.models.transformer import TransformerModel
+
+BASE = dict(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=256,
+            vocab_size=300, torch_dtype="float32", max_position_embeddings=64)
+
+
+def _hidden(cfg, sd):
+    w = WeightLoader(cfg, dtype=torch.float32).load(sd)
+    model = TransformerModel(cfg, w, max_positions=64)
+    T = 11
+    meta = make_step_input(list(range(5, 5 + T)), list(range(T)), list(range(T)), [0, T], [T], [[0, 1]], device="cpu")
+    h = model.forward(meta, model.allocate_kv_cache(2, 16))
+    logits = model.compute_logits(h, meta.logits_idx)
+    assert torch.isfinite(logits).all()
+    return h
+
+
+def _llama_reference(**over):
+    cfg = model_config_from_dict(dict(BASE, model_type="llama", **over))
+    sd = list(synthetic_checkpoint(cfg, seed=3, dtype=torch.float32))
+    return cfg, sd, _hidden(cfg, sd)
+
+
+def test_baichuan_w_pack():
+    cfg, sd, want = _llama_reference(num_key_value_heads=4)
+    d = dict(sd)
+    out = []
+    for k, v in sd:
+        if ".q_proj." in k:
+            p = k.replace("q_proj", "{}")
+            out.append((k.replace("q_proj", "W_pack"), torch.cat([d[p.format(n)] for n in ("q_proj", "k_proj", "v_proj")], 0)))
+        elif ".k_proj." in k or ".v_proj." in k:
+            continue
+        else:
+            out.append((k, v))
+    got = _hidden(model_config_from_dict(dict(BASE, model_type="baichuan", num_key_value_heads=4)), out)
+    assert torch.equal(got, want)
+
+
+def test_internlm2_wqkv_and_names():
+    cfg, sd, want = _llama_reference()
+    d = dict(sd)
+    hq, hk, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    g = hq // hk
+    out = []
+    for k, v in sd:
+        k2 = (k.replace("model.embed_tokens.", "model.tok_embeddings.").replace("lm_head.", "output.")
+              .replace(".self_attn.o_proj.", ".attention.wo.").replace(".mlp.gate_proj.", ".feed_forward.w1.")
+              .replace(".mlp.up_proj.", ".feed_forward.w3.").replace(".mlp.down_proj.", ".feed_forward.w2.")
+              .replace(".input_layernorm.", ".attention_norm.").replace(".post_attention_layernorm.", ".ffn_norm."))
+        if ".q_proj." in k:
+            q = d[k].view(hk, g, hd, -1)
+            kk = d[k.replace("q_proj", "k_proj")].view(hk, 1, hd, -1)
+            vv = d[k.replace("q_proj", "v_proj")].view(hk, 1, hd, -1)
+            out.append((k.replace(".self_attn.q_proj.", ".attention.wqkv."),
+                        torch.cat((q, kk, vv), 1).reshape((g + 2) * hk * hd, -1)))
+        elif ".k_proj." in k or ".v_proj." in k:
+            continue
+        else:
+            out.append((k2, v))
+    got = _hidden(model_config_from_dict(dict(BASE, model_type="internlm2")), out)
+    assert torch.equal(got, want)
+
+
+def test_qwen3_and_mixtral_style_renames_are_exact():
+    cfg = model_config_from_dict(dict(BASE, model_type="qwen3", head_dim=32))
+    sd = list(synthetic_checkpoint(cfg, seed=3, dtype=torch.float32))
+    want = _hidden(cfg, sd)
+    hf = [(k.replace("query_layernorm", "q_norm").replace("key_layernorm", "k_norm"), v) for k, v in sd]
+    assert torch.equal(_hidden(cfg, hf), want)
+
+
+def test_gpt2_conv1d_learned_positions_layernorm():
+    cfg = model_config_from_dict(dict(model_type="gpt2", n_embd=64, n_layer=2, n_head=4, n_positions=64, vocab_size=200,
+                                      torch_dtype="float32"))
+    assert cfg.position_encoding == "learned" and cfg.norm_type == "layernorm" and not cfg.gated_mlp
+    H, I = 64, 256
+    g = torch.Generator().manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.05  # noqa: E731
+    sd = [("wte.weight", rnd(200, H)), ("wpe.weight", rnd(64, H)), ("ln_f.weight", torch.ones(H)), ("ln_f.bias", torch.zeros(H))]
+    for i in range(2):
+        p = f"h.{i}."
+        sd += [(p + "ln_1.weight", torch.ones(H)), (p + "ln_1.bias", torch.zeros(H)),
+               (p + "ln_2.weight", torch.ones(H)), (p + "ln_2.bias", torch.zeros(H)),
+               (p + "attn.c_attn.weight", rnd(H, 3 * H)), (p + "attn.c_attn.bias", rnd(3 * H)),
+               (p + "attn.c_proj.weight", rnd(H, H)), (p + "attn.c_proj.bias", rnd(H)),
+               (p + "mlp.c_fc.weight", rnd(H, I)), (p + "mlp.c_fc.bias", rnd(I)),
+               (p + "mlp.c_proj.weight", rnd(I, H)), (p + "mlp.c_proj.bias", rnd(H))]
+    h = _hidden(cfg, sd)
+    assert h.shape == (11, H)
+
+
+def test_chatglm_packed_qkv_multi_query_partial_rotary():
+    cfg = model_config_from_dict(dict(model_type="chatglm", hidden_size=128, num_layers=2, num_attention_heads=4,
+                                      multi_query_attention=True, multi_query_group_num=2, kv_channels=32,
+                                      ffn_hidden_size=256, padded_vocab_size=300, seq_length=64, layernorm_epsilon=1e-5,
+                                      rmsnorm=True, add_qkv_bias=True, torch_dtype="float32"))
+    assert cfg.num_kv_heads == 2 and cfg.rotary_dim == 16 and cfg.rope_interleaved
+    H, d, hq, hk, I = 128, 32, 4, 2, 256
+    g = torch.Generator().manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.05  # noqa: E731
+    sd = [("transformer.embedding.word_embeddings.weight", rnd(300, H)),
+          ("transformer.encoder.final_layernorm.weight", torch.ones(H)), ("transformer.output_layer.weight", rnd(300, H))]
+    for i in range(2):
+        p = f"transformer.encoder.layers.{i}."
+        sd += [(p + "input_layernorm.weight", torch.ones(H)), (p + "post_attention_layernorm.weight", torch.ones(H)),
+               (p + "self_attention.query_key_value.weight", rnd((hq + 2 * hk) * d, H)),
+               (p + "self_attention.query_key_value.bias", rnd((hq + 2 * hk) * d)),
+               (p + "self_attention.dense.weight", rnd(H, hq * d)),
+               (p + "mlp.dense_h_to_4h.weight", rnd(2 * I, H)), (p + "mlp.dense_4h_to_h.weight", rnd(H, I))]
+    h = _hidden(cfg, sd)
+    assert h.shape == (11, H)
+
+
+def test_minicpm_scaling_factors():
+    cfg = model_config_from_dict(dict(BASE, model_type="minicpm", scale_emb=12, scale_depth=1.4, dim_model_base=64))
+    assert cfg.emb_scale == 12 and abs(cfg.residual_scale - 1.4 / (2 ** 0.5)) < 1e-6
+    assert abs(cfg.logit_scale - 64 / 128) < 1e-9
+    sd = list(synthetic_checkpoint(cfg, seed=3, dtype=torch.float32))
+    h = _hidden(cfg, sd)
+    plain = _hidden(model_config_from_dict(dict(BASE, model_type="llama")), sd)
+    assert not torch.allclose(h, plain)
