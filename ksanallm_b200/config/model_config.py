@@ -67,6 +67,14 @@ class ModelConfig:
     mlp_bias: bool = False
     gated_mlp: bool = True
     qk_norm: bool = False  # per-head RMSNorm on q and k before RoPE (Qwen3)
+    qk_norm_after_rope: bool = False  # ... applied after RoPE instead (Hunyuan)
+    qk_l2_norm: bool = False  # weightless RMS normalisation of q and k after RoPE on the RoPE layers (Llama 4)
+    rope_layers: List[int] = field(default_factory=list)  # per layer: 1 = RoPE, 0 = no position encoding (Llama 4)
+    moe_layers: List[int] = field(default_factory=list)   # explicit MoE layer indices (Llama 4); empty: by frequency
+    moe_router: str = "standard"  # standard | llama4 (top-k on logits, sigmoid score scales the expert INPUT)
+    attn_temperature_tuning: bool = False  # Llama 4: query scaling on the no-RoPE layers
+    attn_floor_scale: float = 8192.0
+    attn_scale_coef: float = 0.1
     bos_token_id: Optional[int] = None
     eos_token_ids: List[int] = field(default_factory=list)
     pad_token_id: Optional[int] = None
@@ -109,6 +117,8 @@ class ModelConfig:
     def is_moe_layer(self, layer_idx: int) -> bool:
         if not self.is_moe:
             return False
+        if self.moe_layers:
+            return layer_idx in self.moe_layers
         return layer_idx >= self.first_k_dense_replace and (layer_idx % max(self.moe_layer_freq, 1) == 0)
 
     @property
@@ -164,6 +174,14 @@ def _quant(d: Optional[Dict[str, Any]]) -> QuantConfig:
 
 
 def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
+    if isinstance(c.get("text_config"), dict) and str(c.get("model_type", "")).lower() in ("llama4",):
+        # multimodal wrapper configs keep the language model under "text_config"
+        inner = dict(c["text_config"])
+        inner.setdefault("model_type", "llama4_text")
+        for k in ("torch_dtype", "dtype", "quantization_config"):
+            if k in c and k not in inner:
+                inner[k] = c[k]
+        c = inner
     mt = str(c.get("model_type", "llama")).lower()
     m = ModelConfig(model_type=mt, architectures=list(c.get("architectures", []) or []), raw=c)
     g = c.get
@@ -182,8 +200,13 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
     m.intermediate_size = int(g("intermediate_size", g("ffn_hidden_size", g("n_inner", None) or 4 * m.hidden_size)))
     m.max_position_embeddings = int(g("max_position_embeddings", g("n_positions", g("seq_length", 4096))))
     m.rms_norm_eps = float(g("rms_norm_eps", g("layer_norm_epsilon", g("layernorm_epsilon", g("layer_norm_eps", 1e-6)))))
-    m.rope_theta = float(g("rope_theta", g("rotary_emb_base", 10000.0)))
-    m.rope_scaling = _rope_scaling(g("rope_scaling", None), c)
+    # transformers >= 5 folds rope_theta and the scaling block into one "rope_parameters" dict
+    rp = g("rope_parameters", None) or {}
+    m.rope_theta = float(g("rope_theta", None) or rp.get("rope_theta", None) or g("rotary_emb_base", 10000.0))
+    rs_dict = g("rope_scaling", None)
+    if rs_dict is None and rp and str(rp.get("rope_type", rp.get("type", "default"))) != "default":
+        rs_dict = rp
+    m.rope_scaling = _rope_scaling(rs_dict, c)
     m.tie_word_embeddings = bool(g("tie_word_embeddings", False))
     m.hidden_act = str(g("hidden_act", g("activation_function", "silu")))
     m.torch_dtype = str(g("torch_dtype", g("dtype", "bfloat16")))
@@ -199,6 +222,16 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
     if mt in ("qwen3", "qwen3_moe"):
         m.qk_norm = True
         m.qkv_bias = bool(g("attention_bias", False))
+    if mt.startswith("hunyuan"):
+        m.qk_norm = bool(g("use_qk_norm", True))
+        m.qk_norm_after_rope = m.qk_norm
+    if mt.startswith("llama4"):
+        m.rope_interleaved = True
+        m.qk_l2_norm = bool(g("use_qk_norm", True))
+        m.rope_layers = [int(x) for x in (g("no_rope_layers", None) or [])]
+        m.attn_temperature_tuning = bool(g("attn_temperature_tuning", False))
+        m.attn_floor_scale = float(g("floor_scale", 8192))
+        m.attn_scale_coef = float(g("attn_scale", 0.1))
     if mt in ("gpt2", "fairseq_transformer", "gpt"):
         m.norm_type, m.post_norm, m.gated_mlp, m.position_encoding = "layernorm", False, False, "learned"
         m.qkv_bias = m.o_bias = m.mlp_bias = True
@@ -213,6 +246,12 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
         m.rotary_dim = m.head_dim // 2
         m.qkv_bias = bool(g("add_qkv_bias", True))
         m.rope_theta = 10000.0 * float(g("rope_ratio", 1.0))
+    if mt in ("glm", "glm4"):
+        # the HF port of GLM-4: interleaved rotary pairs on a fraction of the head, fused gate_up_proj
+        m.rope_interleaved = True
+        prf = float(g("partial_rotary_factor", None) or rp.get("partial_rotary_factor", 0.5) or 0.5)
+        m.rotary_dim = int(m.head_dim * prf)
+        m.qkv_bias = bool(g("attention_bias", True))
     if mt in ("internlm2", "internvl_chat", "internlmxcomposer2"):
         m.qkv_bias = bool(g("bias", False))
     if mt in ("minicpm", "minicpm3"):
@@ -224,10 +263,13 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
 
     # ---- MoE ------------------------------------------------------------------------------
     ne = g("num_experts", None) or g("num_local_experts", None) or g("n_routed_experts", None) or 0
+    if isinstance(ne, (list, tuple)):
+        ne = ne[0] if ne else 0
     m.num_experts = int(ne or 0)
     if m.num_experts:
         m.num_experts_per_tok = int(g("num_experts_per_tok", g("moe_topk", 2)))
-        m.moe_intermediate_size = int(g("moe_intermediate_size", m.intermediate_size))
+        mis = g("moe_intermediate_size", m.intermediate_size)
+        m.moe_intermediate_size = int(mis[0] if isinstance(mis, (list, tuple)) else mis)
         m.norm_topk_prob = bool(g("norm_topk_prob", mt == "mixtral"))
         m.num_shared_experts = int(g("n_shared_experts", 0) or 0)
         sei = g("shared_expert_intermediate_size", 0) or 0
@@ -239,11 +281,31 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
             m.shared_expert_intermediate_size = m.moe_intermediate_size * m.num_shared_experts
         m.first_k_dense_replace = int(g("first_k_dense_replace", 0) or 0)
         m.moe_layer_freq = int(g("moe_layer_freq", g("decoder_sparse_step", 1)) or 1)
-        m.scoring_func = str(g("scoring_func", "softmax"))
+        v3_like = mt in ("deepseek_v3", "deepseek_v32", "kimi_k2")  # sigmoid routing even when the field is absent
+        m.scoring_func = str(g("scoring_func", "sigmoid" if v3_like else "softmax"))
         m.n_group = int(g("n_group", 1) or 1)
         m.topk_group = int(g("topk_group", 1) or 1)
         m.routed_scaling_factor = float(g("routed_scaling_factor", 1.0) or 1.0)
-        m.topk_method = str(g("topk_method", "greedy"))
+        m.topk_method = str(g("topk_method", "noaux_tc" if v3_like else "greedy"))
+        if mt.startswith("llama4"):
+            # experts use intermediate_size, the dense layers and nothing else intermediate_size_mlp
+            m.moe_intermediate_size = int(g("intermediate_size", m.moe_intermediate_size))
+            m.intermediate_size = int(g("intermediate_size_mlp", m.intermediate_size))
+            m.num_shared_experts, m.shared_expert_intermediate_size = 1, m.moe_intermediate_size
+            m.moe_router = "llama4"
+            ml = g("moe_layers", None)
+            step = int(g("interleave_moe_layer_step", 1) or 1)
+            m.moe_layers = [int(x) for x in ml] if ml is not None else list(range(step - 1, m.num_layers, step))
+        if mt.startswith("hunyuan"):
+            tk = g("moe_topk", m.num_experts_per_tok)
+            m.num_experts_per_tok = int(tk[0] if isinstance(tk, (list, tuple)) else tk)
+            ne_ = g("num_experts", m.num_experts)
+            m.num_experts = int(ne_[0] if isinstance(ne_, (list, tuple)) else ne_)
+            m.moe_intermediate_size = m.intermediate_size  # the experts are full-width MLPs
+            nse = g("num_shared_expert", 1)
+            m.num_shared_experts = int(nse[0] if isinstance(nse, (list, tuple)) else nse) or 1
+            m.shared_expert_intermediate_size = m.intermediate_size * m.num_shared_experts
+            m.norm_topk_prob = True
 
     # ---- MLA ------------------------------------------------------------------------------
     if g("kv_lora_rank", None):
@@ -254,7 +316,7 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
         m.qk_rope_head_dim = int(g("qk_rope_head_dim", 64))
         m.v_head_dim = int(g("v_head_dim", 128))
         m.num_kv_heads = 1
-        m.rope_interleaved = True
+        m.rope_interleaved = bool(g("rope_interleave", True))
     m.num_nextn_predict_layers = int(g("num_nextn_predict_layers", 0) or 0)
     m.quant = _quant(g("quantization_config", None))
     return m

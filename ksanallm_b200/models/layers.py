@@ -85,6 +85,16 @@ class Attention:
         self.q_norm = w.get(prefix + ".query_layernorm.weight")
         self.k_norm = w.get(prefix + ".key_layernorm.weight")
         self.rope_cache = rope_cache
+        self.use_rope = True
+        if cfg.rope_layers and layer_idx < len(cfg.rope_layers) and not cfg.rope_layers[layer_idx]:
+            self.rope_cache, self.use_rope = None, False  # a layer without position encoding (Llama 4)
+        self.norm_after_rope = cfg.qk_norm_after_rope
+        if cfg.qk_l2_norm and self.use_rope:
+            # weightless RMS normalisation after RoPE: the ordinary path with unit weights
+            ones = torch.ones(self.d, dtype=self.qkv.weight.dtype if self.qkv.weight is not None else torch.float32,
+                              device=self.o_proj.weight.device)
+            self.q_norm = self.k_norm = ones
+            self.norm_after_rope = True
         self.scale = 1.0 / math.sqrt(self.d)
         self.k_scale = self.v_scale = 1.0  # fp8 KV cache scaling factors (models/kv_scales.py)
         self.alibi = None
@@ -101,7 +111,11 @@ class Attention:
         v = qkv[:, nq + nk:].view(T, self.hk, self.d)
         ops.rope_qknorm_cache(q, k, v, meta.positions, self.rope_cache, meta.slot_mapping, kv_cache,
                               self.q_norm, self.k_norm, self.cfg.rms_norm_eps, self.cfg.rope_interleaved,
-                              self.cfg.rotary_dim, self.k_scale, self.v_scale)
+                              self.cfg.rotary_dim, self.k_scale, self.v_scale, self.norm_after_rope)
+        if self.cfg.attn_temperature_tuning and not self.use_rope:
+            # Llama 4 temperature tuning of the position-free layers: q *= log1p(floor((pos + 1) / floor)) * c + 1
+            t = torch.log1p(torch.floor((meta.positions.float() + 1.0) / self.cfg.attn_floor_scale))
+            q.mul_((t * self.cfg.attn_scale_coef + 1.0).to(q.dtype).view(T, 1, 1))
         o = ops.paged_attention(q, kv_cache, meta, self.scale, self.alibi, self.k_scale, self.v_scale)
         return o.reshape(T, nq)
 
@@ -148,8 +162,8 @@ class MLAttention:
         q_nope, q_rope = q[..., :self.dn], q[..., self.dn:].contiguous()
         cs = self.rope_cache[meta.positions.long()]
         cos, sin = cs[:, :self.dr // 2], cs[:, self.dr // 2:]
-        q_rope = ref.apply_rope(q_rope, cos, sin, True, self.dr)
-        k_rope = ref.apply_rope(k_rope.view(T, 1, self.dr), cos, sin, True, self.dr).view(T, self.dr)
+        q_rope = ref.apply_rope(q_rope, cos, sin, self.cfg.rope_interleaved, self.dr)
+        k_rope = ref.apply_rope(k_rope.view(T, 1, self.dr), cos, sin, self.cfg.rope_interleaved, self.dr).view(T, self.dr)
         ops.mla_cache_append(latent, k_rope, meta.slot_mapping, cache)
         q_lat = torch.einsum("thd,hdr->thr", q_nope.to(self.w_uk.dtype), self.w_uk)
         o_lat = ops.mla_paged_attention(q_lat.contiguous(), q_rope, cache, meta, self.scale)
@@ -206,15 +220,33 @@ class MoEFFN:
                 h.shape[0] <= ep.t_cap * ep.size):
             return self._partial_dispatch(h, ep)
         logits = ops.linear(h.float() if self.gate_w.dtype == torch.float32 else h, self.gate_w)
-        ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
-                                 c.topk_group, c.routed_scaling_factor, self.bias)
-        y = ops.moe_experts(h, ids, wts, self.w_gate_up, self.w_down, self.expert_offset)
+        if c.moe_router == "llama4":
+            y = self._llama4_experts(h, logits)
+        else:
+            ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
+                                     c.topk_group, c.routed_scaling_factor, self.bias)
+            y = ops.moe_experts(h, ids, wts, self.w_gate_up, self.w_down, self.expert_offset)
         if self.shared is not None:
             s = self.shared.down(self.shared.core(h), add_bias=self.tp.rank == 0)
             if self.shared_gate is not None:
                 g = torch.sigmoid(ops.linear(h, self.shared_gate).float()).to(s.dtype)
                 s = s * g
             y = y + s
+        return y
+
+    def _llama4_experts(self, h: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        """Llama 4 routing: top-k on the raw logits, score = sigmoid(logit), and the score scales the expert's
+        INPUT (the expert MLP is non-linear, so this is not the usual output weighting)."""
+        k = self.cfg.num_experts_per_tok
+        top, ids = torch.topk(logits.float(), k, dim=-1)
+        score = torch.sigmoid(top)
+        ones = torch.ones_like(score[:, :1])
+        y = None
+        for j in range(k):
+            xj = (h.float() * score[:, j:j + 1]).to(h.dtype)
+            yj = ops.moe_experts(xj, ids[:, j:j + 1].to(torch.int32).contiguous(), ones, self.w_gate_up, self.w_down,
+                                 self.expert_offset)
+            y = yj if y is None else y + yj
         return y
 
     def _dp_exchange(self, h: torch.Tensor, ep) -> torch.Tensor:

@@ -223,7 +223,10 @@ class WeightLoader:
         self.device = torch.device(device)
         self.dtype = dtype or getattr(torch, cfg.torch_dtype, torch.bfloat16)
         self.quantize = quantize  # None | "fp8_block" | "int4"
-        self.rules = load_weight_map(model_dir, cfg.model_type) + _RENAMES.get(cfg.model_type, [])
+        from .registry import resolve_family
+        fam = resolve_family(cfg.model_type, model_dir) or cfg.model_type
+        self.rules = load_weight_map(model_dir, cfg.model_type) + (_RENAMES.get(cfg.model_type) or _RENAMES.get(fam, []))
+        self.family = fam
         self.layer_range = layer_range
         self.out: Dict[str, torch.Tensor] = {}
         self._pending: Dict[str, Dict[str, torch.Tensor]] = defaultdict(dict)
@@ -313,6 +316,23 @@ class WeightLoader:
             return
         layer, block, rest = m.groups()
         key = f"{layer}.{block}"
+        # stacked experts (transformers >= 5 state dicts, fused-expert checkpoints):
+        # experts.gate_up_proj [E, 2I, H] (gate rows, then up rows) and experts.down_proj [E, H, I]
+        if rest in ("experts.gate_up_proj", "experts.down_proj") and t.dim() == 3:
+            if self.family == "llama4":
+                t = t.transpose(1, 2)  # Llama 4 keeps [E, in, out] for its batched matmul
+            per = max(cfg.num_experts // self.ep_size, 1)
+            for e in range(t.shape[0]):
+                if self.ep_size > 1 and not (self.ep_rank * per <= e < (self.ep_rank + 1) * per):
+                    continue
+                if rest == "experts.gate_up_proj":
+                    half = t.shape[1] // 2
+                    self._experts[key][(e, "gate_proj.weight")] = t[e, :half]
+                    self._experts[key][(e, "up_proj.weight")] = t[e, half:]
+                else:
+                    self._experts[key][(e, "down_proj.weight")] = t[e]
+            self._maybe_flush_experts(key)
+            return
         # expert weights: experts.E.{gate,up,down}_proj.(weight|weight_scale_inv)
         em = re.match(r"experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv)$", rest)
         if em:

@@ -22,6 +22,7 @@ FAMILIES: Dict[str, str] = {
     "qwen2_vl": "qwen2 text tower + plugin vision embeddings (input_refit_embedding)",
     "baichuan": "packed W_pack qkv; ALiBi for the 13B size",
     "chatglm": "packed qkv with multi-query groups, interleaved partial rotary",
+    "glm": "GLM-4 in its transformers layout: separate q/k/v, fused gate_up_proj, interleaved partial rotary",
     "gpt2": "learned positions, LayerNorm, GELU MLP with biases (also fairseq-transformer / openai-gpt)",
     "internlm2": "packed wqkv per KV group",
     "internvl_chat": "internlm2 / qwen2 language tower + vision plugin",

@@ -72,7 +72,11 @@ def embedding(ids, table, scale=1.0):
 
 
 def rope_qknorm_cache(q, k, v, positions, cos_sin, slot_mapping, kv_cache, q_norm_w=None, k_norm_w=None,
-                      eps=1e-6, interleaved=False, rotary_dim=0, k_scale=1.0, v_scale=1.0):
+                      eps=1e-6, interleaved=False, rotary_dim=0, k_scale=1.0, v_scale=1.0, norm_after_rope=False):
+    if norm_after_rope and q_norm_w is not None:
+        # the fused kernel normalises before rotating: this order goes through the reference implementation
+        return ref.rope_qknorm_cache(q, k, v, positions, cos_sin, slot_mapping, kv_cache, q_norm_w, k_norm_w, eps,
+                                     interleaved, rotary_dim, k_scale, v_scale, True)
     if q.is_cuda:
         return _cuda().rope_qknorm_cache(q, k, v, positions, cos_sin, slot_mapping, kv_cache, q_norm_w, k_norm_w,
                                          eps, interleaved, rotary_dim, k_scale, v_scale)

@@ -221,13 +221,14 @@ def rope_qknorm_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positio
                       cos_sin: Optional[torch.Tensor], slot_mapping: torch.Tensor, kv_cache: torch.Tensor,
                       q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None,
                       eps: float = 1e-6, interleaved: bool = False, rotary_dim: int = 0,
-                      k_scale: float = 1.0, v_scale: float = 1.0) -> None:
-    """In place: optional per-head RMSNorm on q,k -> RoPE on q,k -> append k,v to the paged cache.
+                      k_scale: float = 1.0, v_scale: float = 1.0, norm_after_rope: bool = False) -> None:
+    """In place: optional per-head RMSNorm on q,k -> RoPE on q,k -> append k,v to the paged cache
+    (``norm_after_rope``: RoPE first, then the norm, as Hunyuan does).
 
     q: [T, h, d], k/v: [T, hk, d]; cos_sin: [max_pos, rotary_dim] = [cos | sin] or None (no RoPE);
     slot_mapping[t] = block * block_size + offset."""
     T, hk, d = k.shape
-    if q_norm_w is not None:
+    if q_norm_w is not None and not norm_after_rope:
         q.copy_(rms_norm(q, q_norm_w, eps))
         k.copy_(rms_norm(k, k_norm_w, eps))
     if cos_sin is not None:
@@ -236,6 +237,9 @@ def rope_qknorm_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positio
         cos, sin = cs[:, : rd // 2], cs[:, rd // 2:]
         q.copy_(apply_rope(q, cos, sin, interleaved, rd))
         k.copy_(apply_rope(k, cos, sin, interleaved, rd))
+    if q_norm_w is not None and norm_after_rope:
+        q.copy_(rms_norm(q, q_norm_w, eps))
+        k.copy_(rms_norm(k, k_norm_w, eps))
     bs = kv_cache.shape[3]
     blk = (slot_mapping // bs).long()
     off = (slot_mapping % bs).long()
