@@ -28,6 +28,12 @@ CASES = {
     "llama": ("LlamaConfig", "LlamaForCausalLM", BASE),
     "llama3_rope": ("LlamaConfig", "LlamaForCausalLM", dict(BASE, rope_scaling=dict(
         rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=32))),
+    "llama_linear_rope": ("LlamaConfig", "LlamaForCausalLM", dict(BASE, rope_scaling=dict(rope_type="linear", factor=4.0))),
+    "llama_yarn": ("LlamaConfig", "LlamaForCausalLM", dict(BASE, rope_scaling=dict(
+        rope_type="yarn", factor=4.0, original_max_position_embeddings=16))),
+    "deepseek_v3_yarn": ("DeepseekV3Config", "DeepseekV3ForCausalLM", dict(DS, rope_scaling=dict(
+        rope_type="yarn", factor=4.0, original_max_position_embeddings=16, beta_fast=32.0, beta_slow=1.0, mscale=1.0,
+        mscale_all_dim=1.0))),
     "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", BASE),
     "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(BASE, head_dim=32)),
     "mistral": ("MistralConfig", "MistralForCausalLM", dict(BASE, sliding_window=None)),
