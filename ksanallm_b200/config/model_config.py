@@ -68,6 +68,8 @@ class ModelConfig:
     gated_mlp: bool = True
     qk_norm: bool = False  # per-head RMSNorm on q and k before RoPE (Qwen3)
     qk_norm_after_rope: bool = False  # ... applied after RoPE instead (Hunyuan)
+    sliding_window: int = 0  # attention window in tokens (0: full causal); per layer via sliding_layers
+    sliding_layers: List[int] = field(default_factory=list)  # 1 = windowed layer; empty with a window: every layer
     qk_l2_norm: bool = False  # weightless RMS normalisation of q and k after RoPE on the RoPE layers (Llama 4)
     rope_layers: List[int] = field(default_factory=list)  # per layer: 1 = RoPE, 0 = no position encoding (Llama 4)
     moe_layers: List[int] = field(default_factory=list)   # explicit MoE layer indices (Llama 4); empty: by frequency
@@ -216,6 +218,12 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
     m.pad_token_id = g("pad_token_id", None)
     m.qkv_bias = bool(g("attention_bias", g("qkv_bias", g("add_qkv_bias", False))))
     m.mlp_bias = bool(g("mlp_bias", False))
+    sw = g("sliding_window", None)
+    if sw and g("use_sliding_window", True):
+        m.sliding_window = int(sw)
+        lt = g("layer_types", None)
+        if lt:
+            m.sliding_layers = [1 if str(t) == "sliding_attention" else 0 for t in lt]
 
     if mt in ("qwen2", "qwen2_moe", "qwen", "qwen2_vl", "qwen2_5_vl"):
         m.qkv_bias = True if g("attention_bias", None) is None else bool(g("attention_bias"))

@@ -85,6 +85,10 @@ class Attention:
         self.q_norm = w.get(prefix + ".query_layernorm.weight")
         self.k_norm = w.get(prefix + ".key_layernorm.weight")
         self.rope_cache = rope_cache
+        self.window = 0
+        if cfg.sliding_window and (not cfg.sliding_layers or
+                                   (layer_idx < len(cfg.sliding_layers) and cfg.sliding_layers[layer_idx])):
+            self.window = cfg.sliding_window
         self.use_rope = True
         if cfg.rope_layers and layer_idx < len(cfg.rope_layers) and not cfg.rope_layers[layer_idx]:
             self.rope_cache, self.use_rope = None, False  # a layer without position encoding (Llama 4)
@@ -116,7 +120,7 @@ class Attention:
             # Llama 4 temperature tuning of the position-free layers: q *= log1p(floor((pos + 1) / floor)) * c + 1
             t = torch.log1p(torch.floor((meta.positions.float() + 1.0) / self.cfg.attn_floor_scale))
             q.mul_((t * self.cfg.attn_scale_coef + 1.0).to(q.dtype).view(T, 1, 1))
-        o = ops.paged_attention(q, kv_cache, meta, self.scale, self.alibi, self.k_scale, self.v_scale)
+        o = ops.paged_attention(q, kv_cache, meta, self.scale, self.alibi, self.k_scale, self.v_scale, self.window)
         return o.reshape(T, nq)
 
 

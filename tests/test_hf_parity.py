@@ -37,6 +37,9 @@ CASES = {
     "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", BASE),
     "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(BASE, head_dim=32)),
     "mistral": ("MistralConfig", "MistralForCausalLM", dict(BASE, sliding_window=None)),
+    "mistral_sliding_window": ("MistralConfig", "MistralForCausalLM", dict(BASE, sliding_window=4)),
+    "qwen2_mixed_window_layers": ("Qwen2Config", "Qwen2ForCausalLM", dict(
+        BASE, num_hidden_layers=3, use_sliding_window=True, sliding_window=5, max_window_layers=1)),
     "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(BASE, num_local_experts=4, num_experts_per_tok=2)),
     "qwen2_moe": ("Qwen2MoeConfig", "Qwen2MoeForCausalLM", dict(
         BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=128,
@@ -84,3 +87,33 @@ def test_logits_match_transformers(name):
     h = model.forward(meta, model.allocate_kv_cache(2, 64 if c.use_mla else 16))
     got = model.compute_logits(h, meta.logits_idx)[0]
     assert (got - want).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("name", ["llama", "deepseek_v3", "qwen3_moe", "mistral_sliding_window"])
+def test_engine_greedy_generation_matches_transformers(name):
+    """Continuous batching over the paged cache (prefill + decode steps, several requests at once) against
+    ``generate(do_sample=False)`` of the transformers model, request by request."""
+    from ksanallm_b200.config.schema import parse_serving_config
+    from ksanallm_b200.engine.llm_engine import LLMEngine
+    from ksanallm_b200.engine.sampling_params import SamplingParams
+    cfg_cls, model_cls, kw = CASES[name]
+    cfg = getattr(transformers, cfg_cls)(**kw)
+    torch.manual_seed(1)
+    hf = getattr(transformers, model_cls)(cfg).eval().float()
+    prompts = [[5, 9, 77, 120, 33, 4, 8], [200, 3, 3, 19, 250, 7, 7, 7, 91, 12, 13, 14, 15, 16, 17, 18, 19, 20], [8, 6]]
+    new = 7
+    want = []
+    for p in prompts:
+        with torch.no_grad():
+            out = hf.generate(torch.tensor([p]), max_new_tokens=new, do_sample=False, pad_token_id=0, eos_token_id=None)
+        want.append(out[0, len(p):].tolist())
+    c = model_config_from_dict(cfg.to_dict())
+    c.eos_token_ids = []
+    w = WeightLoader(c, dtype=torch.float32).load(list(hf.state_dict().items()))
+    model = TransformerModel(c, w, max_positions=64)
+    serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 16,
+                                                                     "max_token_len": 64, "split_fuse_token_num": 16}}})
+    eng = LLMEngine(model, serving, num_blocks=32, num_host_blocks=0)
+    got = [r.output_token_ids[0] for r in
+           eng.generate(prompts, SamplingParams(topk=1, max_new_tokens=new, ignore_eos=True))]
+    assert got == want
