@@ -671,6 +671,29 @@ class LLMEngine:
                 break
         return steps
 
+    def warmup(self, max_len: int = 2048, step: int = 64, new_tokens: int = 2) -> int:
+        """Runs throw-away requests of 64, 128, ... tokens (2 new tokens each) so that every lazily initialised piece
+        (kernel modules, tensor-map and workspace set-up, allocator pools, collective buffers) is paid for before
+        the first user request, then drops the cached blocks they left behind. The driving rank calls this; the
+        followers are already in ``follow``. Reference: InferenceEngine::DoWarmupRun
+        (src/ksana_llm/service/inference_engine.cpp:447-506)."""
+        limit = min(max_len, self.sched_cfg.max_token_len - new_tokens - 1, self.sched_cfg.max_step_tokens)
+        lens = list(range(step, limit + 1, step)) or [max(limit, 1)]
+        vocab = max(self.cfg.vocab_size, 8)
+        done = 0
+        for n in lens:
+            prompt = [3 + (7 * i + n) % (vocab - 4) for i in range(n)]
+            req = self.add_request(prompt, SamplingParams(topk=1, max_new_tokens=new_tokens, ignore_eos=True))
+            while not req.finished and self.has_unfinished():
+                self.step()
+            done += 1
+        self._drain_inflight()
+        with self.lock:
+            self.cache.clear_unreferenced()
+        for k in ("generated_tokens", "prompt_tokens", "steps"):
+            self.stats[k] = 0
+        return done
+
     def start(self) -> None:
         """Background step loop (serving mode)."""
         if self._loop_thread is not None:

@@ -235,6 +235,11 @@ class KsanaLLMEngine:
             self.llm.attach_control_group(dist.new_group(backend="gloo"))
         self._load_plugin()
         if tp.rank == 0:
+            import os
+            if os.environ.get("KSANA_SKIP_WARMUP", "0") != "1" and tp.size == 1:
+                # multi-rank instances warm up through their first requests: the followers only enter their loop
+                # after initialisation returns
+                self.llm.warmup(max_len=min(2048, self.serving.setting.batch_scheduler.max_token_len))
             self.llm.start()
 
     def serve_follower(self) -> None:

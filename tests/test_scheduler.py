@@ -257,3 +257,25 @@ def test_draft_trie_and_balancer():
     a = host.balance_workloads([10, 1, 7, 3], [0, 0])
     loads = [sum(w for w, g in zip([10, 1, 7, 3], a) if g == k) for k in (0, 1)]
     assert max(loads) <= 11
+
+
+
+def test_warmup_leaves_a_clean_engine():
+    import torch
+
+    from ksanallm_b200.config.model_config import model_config_from_dict
+    from ksanallm_b200.config.schema import parse_serving_config
+    from ksanallm_b200.engine.llm_engine import LLMEngine
+    from ksanallm_b200.models.loader import load_model_weights
+    from ksanallm_b200.models.transformer import TransformerModel
+    cfg = model_config_from_dict(dict(model_type="llama", hidden_size=64, num_hidden_layers=1, num_attention_heads=2,
+                                      num_key_value_heads=2, intermediate_size=128, vocab_size=200,
+                                      torch_dtype="float32"))
+    serving = parse_serving_config({"setting": {"batch_scheduler": {
+        "max_batch_size": 4, "max_step_tokens": 256, "max_token_len": 256, "enable_auto_prefix_cache": True}}})
+    eng = LLMEngine(TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, dtype=torch.float32)), serving,
+                    num_blocks=64, num_host_blocks=0)
+    n = eng.warmup(max_len=128, step=32)
+    assert n >= 3 and not eng.has_unfinished()
+    assert eng.stats["generated_tokens"] == 0 and eng.cache.num_cached_blocks == 0
+    assert eng.cache.num_free_blocks == eng.num_blocks
