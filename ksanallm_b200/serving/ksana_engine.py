@@ -235,7 +235,6 @@ class KsanaLLMEngine:
             self.llm.attach_control_group(dist.new_group(backend="gloo"))
         self._load_plugin()
         if tp.rank == 0:
-            import os
             if os.environ.get("KSANA_SKIP_WARMUP", "0") != "1" and tp.size == 1:
                 # multi-rank instances warm up through their first requests: the followers only enter their loop
                 # after initialisation returns
