@@ -133,7 +133,7 @@ def _rope_scaling(d: Optional[Dict[str, Any]], cfg: Dict[str, Any]) -> RopeScali
     if not d:
         return rs
     t = d.get("rope_type", d.get("type", "default")) or "default"
-    rs.type = {"ntk": "dynamic", "dynamic_ntk": "dynamic", "deepseek_yarn": "yarn"}.get(t, t)
+    rs.type = {"ntk": "dynamic", "dynamic_ntk": "dynamic", "deepseek_yarn": "yarn", "mrope": "default"}.get(t, t)
     rs.factor = float(d.get("factor", 1.0) or 1.0)
     rs.original_max_position_embeddings = int(
         d.get("original_max_position_embeddings", cfg.get("max_position_embeddings", 0)) or 0)
@@ -206,7 +206,8 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
     rp = g("rope_parameters", None) or {}
     m.rope_theta = float(g("rope_theta", None) or rp.get("rope_theta", None) or g("rotary_emb_base", 10000.0))
     rs_dict = g("rope_scaling", None)
-    if rs_dict is None and rp and str(rp.get("rope_type", rp.get("type", "default"))) != "default":
+    if rs_dict is None and rp and (str(rp.get("rope_type", rp.get("type", "default"))) != "default" or
+                                   rp.get("mrope_section")):
         rs_dict = rp
     m.rope_scaling = _rope_scaling(rs_dict, c)
     m.tie_word_embeddings = bool(g("tie_word_embeddings", False))

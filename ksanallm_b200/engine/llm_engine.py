@@ -75,6 +75,8 @@ class Request:
         self.generators: Dict[int, torch.Generator] = {}
         self.tries: Dict[int, Any] = {}
         self.beam = None
+        self.mrope = None      # [3, prompt_len] multimodal RoPE positions (None: text-only)
+        self.mrope_delta = 0
 
     def notify(self) -> None:
         with self.cond:
@@ -185,12 +187,20 @@ class LLMEngine:
 
     # ---- request intake --------------------------------------------------------------------------------
     def add_request(self, prompt_tokens: Sequence[int], params: Optional[SamplingParams] = None,
-                    refit=None, grammar=None, probe=None) -> Request:
+                    refit=None, grammar=None, probe=None, mrope_positions=None) -> Request:
+        """``mrope_positions``: [3, prompt_len] (temporal, height, width) positions of the prompt tokens for models
+        with multimodal RoPE; generated tokens continue from max + 1 on all three axes."""
         params = params or SamplingParams()
         params.verify()
         now = time.time()
         req = Request(next(self._ids), list(int(t) for t in prompt_tokens), params, now)
         req.refit, req.grammar, req.probe = refit, grammar, probe
+        if mrope_positions is not None:
+            mp = torch.as_tensor(mrope_positions, dtype=torch.int32).reshape(3, -1)
+            if mp.shape[1] != len(req.prompt_tokens):
+                raise EngineError(_host.RET_INVALID_ARGUMENT, "mrope_positions must be [3, prompt_len]")
+            req.mrope = mp
+            req.mrope_delta = int(mp.max()) + 1 - mp.shape[1] if mp.numel() else 0
         n_out = max(params.num_beams, params.num_return_sequences, 1)
         if params.num_beams > 1:
             import dataclasses
@@ -203,7 +213,7 @@ class LLMEngine:
             first = self._enqueue_seq(req, req.prompt_tokens)
             req._pending_fanout = n_out - 1 if params.num_beams <= 1 else 0
             self.requests[req.req_id] = req
-            req._complex = self._needs_host_tokens(params, req) or n_out > 1
+            req._complex = self._needs_host_tokens(params, req) or n_out > 1 or mrope_positions is not None
             self._complex_requests += 1 if req._complex else 0
             self.stats["prompt_tokens"] += len(req.prompt_tokens)
         self._wake.set()
@@ -302,6 +312,7 @@ class LLMEngine:
         ta = time.perf_counter()
         self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
         meta = self.runner.upload(layout)
+        self._attach_mrope(plan, meta)
         if self.pipeline is not None and self.pipeline.topo.num_stages > 1:
             out, hidden = self._pipeline_step_driver(meta, refit, rows, greedy)
             tb = time.perf_counter()
@@ -397,6 +408,24 @@ class LLMEngine:
         st["t_sample_sync"] += t2 - tb
         st["t_apply"] += t3 - t2
         return n_new
+
+    def _attach_mrope(self, plan, meta) -> None:
+        """Builds the step's [3, T] multimodal positions when any scheduled request carries them."""
+        if not any(getattr(self.seq_owner[e.seq_id][0], "mrope", None) is not None for e in plan.entries
+                   if e.seq_id in self.seq_owner):
+            return
+        cols = []
+        for e in plan.entries:
+            req = self.seq_owner[e.seq_id][0]
+            idx = torch.arange(e.q_start, e.q_start + e.q_len, dtype=torch.int32)
+            mp = getattr(req, "mrope", None)
+            if mp is None:
+                cols.append(idx.unsqueeze(0).expand(3, -1))
+                continue
+            P = mp.shape[1]
+            inside = idx.clamp(max=max(P - 1, 0)).long()
+            cols.append(torch.where(idx.unsqueeze(0) < P, mp[:, inside], (idx + req.mrope_delta).unsqueeze(0).expand(3, -1)))
+        meta.mrope_positions = torch.cat(cols, dim=1).to(self.runner.device)
 
     def _sample_rows(self, plan):
         rows: List[SampleRow] = []

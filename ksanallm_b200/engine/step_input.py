@@ -38,6 +38,10 @@ class StepInput:
     # host copies of the small per-sequence arrays (kernel launch decisions never sync the device)
     cu_q_host: Optional[np.ndarray] = None
     kv_lens_host: Optional[np.ndarray] = None
+    # multimodal RoPE: [3, T] (temporal, height, width) positions; None for plain text steps
+    mrope_positions: Optional[torch.Tensor] = None
+    _mrope_table: Optional[torch.Tensor] = None
+    _arange: Optional[torch.Tensor] = None
 
     @property
     def num_decode_tokens(self) -> int:

@@ -113,7 +113,15 @@ class Attention:
         q = qkv[:, :nq].view(T, self.h, self.d)
         k = qkv[:, nq:nq + nk].view(T, self.hk, self.d)
         v = qkv[:, nq + nk:].view(T, self.hk, self.d)
-        ops.rope_qknorm_cache(q, k, v, meta.positions, self.rope_cache, meta.slot_mapping, kv_cache,
+        positions, table = meta.positions, self.rope_cache
+        sections = self.cfg.rope_scaling.mrope_section
+        if sections and table is not None and getattr(meta, "mrope_positions", None) is not None:
+            # multimodal RoPE: a per-token cos/sin table built once per step, indexed by the token's row
+            if meta._mrope_table is None:
+                meta._mrope_table = ref.mrope_rows(table, meta.mrope_positions, sections)
+                meta._arange = torch.arange(T, dtype=torch.int32, device=q.device)
+            positions, table = meta._arange, meta._mrope_table
+        ops.rope_qknorm_cache(q, k, v, positions, table, meta.slot_mapping, kv_cache,
                               self.q_norm, self.k_norm, self.cfg.rms_norm_eps, self.cfg.rope_interleaved,
                               self.cfg.rotary_dim, self.k_scale, self.v_scale, self.norm_after_rope)
         if self.cfg.attn_temperature_tuning and not self.use_rope:

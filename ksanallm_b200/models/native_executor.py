@@ -168,6 +168,8 @@ class DenseExecutor:
         T = meta.total_tokens
         if T == 0 or n_layers == 0 or kv_caches[0].dim() != 5 or kv_caches[0].shape[3] != 16:
             return False
+        if getattr(meta, "mrope_positions", None) is not None:
+            return False
         if kv_caches[0].dtype != torch.bfloat16 and meta.num_prefill:
             return False  # fp8 cache prefill chunks take the dequantising path
         if self.tp.size > 1:

@@ -500,6 +500,24 @@ def build_rope_cache(rotary_dim: int, max_pos: int, theta: float, scaling=None, 
     return out.to(device)
 
 
+def mrope_rows(cos_sin: torch.Tensor, positions3: torch.Tensor, sections) -> torch.Tensor:
+    """Multimodal RoPE (Qwen2-VL): frequency indices [0, s0) rotate by the temporal position, [s0, s0 + s1) by the
+    height position, the rest by the width position. cos_sin: [max_pos, rd] = [cos | sin]; positions3: [3, T].
+    Returns a per-token table [T, rd] to be indexed with positions 0..T-1 by the ordinary RoPE code."""
+    rd = cos_sin.shape[1]
+    half = rd // 2
+    assert sum(sections) == half, "mrope_section must cover half of the rotary dimension"
+    p = positions3.long()
+    rows = [cos_sin[p[i]] for i in range(3)]  # each [T, rd]
+    cos_parts, sin_parts, lo = [], [], 0
+    for i, sec in enumerate(sections):
+        src = rows[i % 3]
+        cos_parts.append(src[:, lo:lo + sec])
+        sin_parts.append(src[:, half + lo:half + lo + sec])
+        lo += sec
+    return torch.cat(cos_parts + sin_parts, dim=-1).contiguous()
+
+
 def alibi_slopes(num_heads: int) -> torch.Tensor:
     def pow2(n):
         start = 2 ** (-(2 ** -(math.log2(n) - 3)))

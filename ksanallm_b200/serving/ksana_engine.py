@@ -291,11 +291,14 @@ class KsanaLLMEngine:
             for p, e in zip(pos, vals):
                 t = torch.as_tensor(e, dtype=torch.float32)
                 refit.append((int(p), t.view(-1, self.model_config.hidden_size)))
+        self._last_mrope = (request_dict.get("additional_params") or {}).get("mrope_positions")
         if self.plugin is not None:
             extra = self.plugin.preprocess(request_dict, tokens)
             if extra:
                 tokens = extra.get("input_tokens", tokens)
                 refit = extra.get("refit", refit)
+                # vision plugins of M-RoPE models return [3, prompt_len] (temporal, height, width) positions
+                self._last_mrope = extra.get("mrope_positions", self._last_mrope)
         return tokens, refit
 
     def _grammar_for(self, sp: SamplingParams):
@@ -327,7 +330,7 @@ class KsanaLLMEngine:
             sp = self._build_sampling(request_dict)
             tokens, refit = self._build_tokens(request_dict)
             grammar = self._grammar_for(sp)
-            req = self.llm.add_request(tokens, sp, refit=refit, grammar=grammar)
+            req = self.llm.add_request(tokens, sp, refit=refit, grammar=grammar, mrope_positions=self._last_mrope)
             req.ctx = req_ctx or {}
         except EngineError as ex:
             return Status(ex.code, str(ex)), None

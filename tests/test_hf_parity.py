@@ -117,3 +117,67 @@ def test_engine_greedy_generation_matches_transformers(name):
     got = [r.output_token_ids[0] for r in
            eng.generate(prompts, SamplingParams(topk=1, max_new_tokens=new, ignore_eos=True))]
     assert got == want
+
+
+def test_multimodal_rope_matches_qwen2_vl_text_model():
+    if not hasattr(transformers, "Qwen2VLTextModel"):
+        pytest.skip("no Qwen2VLTextModel in this transformers")
+    cfg = transformers.Qwen2VLTextConfig(**dict(BASE, rope_scaling=dict(type="mrope", mrope_section=[4, 6, 6])))
+    torch.manual_seed(0)
+    hf = transformers.Qwen2VLTextModel(cfg).eval().float()
+    T = 11
+    ids = list(range(5, 5 + T))
+    # an "image" in the middle: temporal position frozen, height / width walking a 2 x 2 grid
+    pos3 = torch.tensor([[0, 1, 2, 3, 3, 3, 3, 5, 6, 7, 8],
+                         [0, 1, 2, 3, 3, 4, 4, 5, 6, 7, 8],
+                         [0, 1, 2, 3, 4, 3, 4, 5, 6, 7, 8]])
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([ids]), position_ids=pos3.unsqueeze(1)).last_hidden_state[0]
+    d = cfg.to_dict()
+    d["model_type"] = "qwen2_vl"
+    c = model_config_from_dict(d)
+    assert c.rope_scaling.mrope_section == [4, 6, 6] and c.qkv_bias
+    sd = [("model." + k, v) for k, v in hf.state_dict().items()] + [("lm_head.weight", torch.zeros(300, 128))]
+    model = TransformerModel(c, WeightLoader(c, dtype=torch.float32).load(sd), max_positions=64)
+    meta = make_step_input(ids, list(range(T)), list(range(T)), [0, T], [T], [[0, 1]], device="cpu")
+    meta.mrope_positions = pos3
+    got = model.forward(meta, model.allocate_kv_cache(2, 16))
+    assert (got - want).abs().max().item() < 1e-4
+
+
+def test_engine_generation_with_multimodal_positions():
+    """Prompt with image-like 3-d positions, then greedy decoding: generated tokens continue from max + 1 on all
+    three axes (the transformers rule), over chunked prefill and the paged cache."""
+    if not hasattr(transformers, "Qwen2VLTextModel"):
+        pytest.skip("no Qwen2VLTextModel in this transformers")
+    from ksanallm_b200.config.schema import parse_serving_config
+    from ksanallm_b200.engine.llm_engine import LLMEngine
+    from ksanallm_b200.engine.sampling_params import SamplingParams
+    cfg = transformers.Qwen2VLTextConfig(**dict(BASE, rope_scaling=dict(type="mrope", mrope_section=[4, 6, 6])))
+    torch.manual_seed(0)
+    hf = transformers.Qwen2VLTextModel(cfg).eval().float()
+    head = torch.randn(300, 128) * 0.1
+    ids = list(range(5, 16))
+    pos3 = torch.tensor([[0, 1, 2, 3, 3, 3, 3, 5, 6, 7, 8], [0, 1, 2, 3, 3, 4, 4, 5, 6, 7, 8],
+                         [0, 1, 2, 3, 4, 3, 4, 5, 6, 7, 8]])
+    # reference: re-run the full sequence every step with explicit positions
+    want, seq, p3 = [], list(ids), pos3.clone()
+    for _ in range(5):
+        with torch.no_grad():
+            h = hf(input_ids=torch.tensor([seq]), position_ids=p3.unsqueeze(1)).last_hidden_state[0, -1]
+        tok = int((h @ head.t()).argmax())
+        want.append(tok)
+        seq.append(tok)
+        p3 = torch.cat((p3, (p3.max() + 1).view(1, 1).expand(3, 1)), dim=1)
+    d = cfg.to_dict()
+    d["model_type"] = "qwen2_vl"
+    c = model_config_from_dict(d)
+    c.eos_token_ids = []
+    sd = [("model." + k, v) for k, v in hf.state_dict().items()] + [("lm_head.weight", head)]
+    model = TransformerModel(c, WeightLoader(c, dtype=torch.float32).load(sd), max_positions=64)
+    serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 2, "max_step_tokens": 16,
+                                                                     "max_token_len": 64, "split_fuse_token_num": 4}}})
+    eng = LLMEngine(model, serving, num_blocks=16, num_host_blocks=0)
+    req = eng.add_request(ids, SamplingParams(topk=1, max_new_tokens=5, ignore_eos=True), mrope_positions=pos3)
+    eng.run_until_done()
+    assert req.output_token_ids[0] == want
