@@ -12,6 +12,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from .. import _build
+from . import gemm_tune
 from . import reference as ref
 
 _lib = None
@@ -116,6 +117,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
         out = torch.empty(M, N, dtype=out_dtype, device=x.device)
     if M == 0:
         return out
+    if bn == 0 and splits == 0 and gemm_tune._MAP:
+        bn, splits = gemm_tune.lookup(M, N, K)
     ws = workspace(x.device)
     code = lib().ksana_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), _ptr(bias), M, N, K, x.stride(0), w.stride(0),
                                  out.stride(0), 1 if out.dtype == torch.float32 else 0, bn, splits, _ptr(ws.gemm_ws),

@@ -234,6 +234,8 @@ class KsanaLLMEngine:
             import torch.distributed as dist
             self.llm.attach_control_group(dist.new_group(backend="gloo"))
         self._load_plugin()
+        from ..ops import gemm_tune
+        gemm_tune.maybe_load_from_env()  # KSANA_GEMM_TUNE_FILE written by benchmarks/search_best_gemm.py
         if tp.rank == 0:
             if os.environ.get("KSANA_SKIP_WARMUP", "0") != "1" and tp.size == 1:
                 # multi-rank instances warm up through their first requests: the followers only enter their loop

@@ -158,3 +158,16 @@ def test_kv_cache_scales_file(tmp_path):
     m = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, dtype=torch.float32))
     apply_kv_scales(m, [0.5, 0.25])
     assert m.layers[0].attn.k_scale == 0.5 and m.layers[1].attn.v_scale == 0.25
+
+
+def test_gemm_tuning_map(tmp_path):
+    from ksanallm_b200.ops import gemm_tune
+    p = tmp_path / "map.yaml"
+    p.write_text("gemm_bf16:\n  - {n: 4096, k: 4096, m_max: 64, bn: 128, splits: 4}\n"
+                 "  - {n: 4096, k: 4096, m_max: 1024, bn: 256, splits: 0}\n")
+    assert gemm_tune.load_map(str(p)) == 2
+    assert gemm_tune.lookup(16, 4096, 4096) == (128, 4)
+    assert gemm_tune.lookup(512, 4096, 4096) == (256, 0)
+    assert gemm_tune.lookup(4096, 4096, 4096) == (0, 0) and gemm_tune.lookup(16, 11008, 4096) == (0, 0)
+    gemm_tune.clear()
+    assert gemm_tune.lookup(16, 4096, 4096) == (0, 0)
