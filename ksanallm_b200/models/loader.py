@@ -192,14 +192,110 @@ def synthetic_checkpoint(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dev
 # sharding helpers
 # ---------------------------------------------------------------------------------------------------
 
-def _rows(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+class QuantW:
+    """A 4-bit group-quantised linear weight travelling through the loader in place of a dense tensor:
+    ``q`` [N, K] uint8 values 0..15, ``scales`` / ``zeros`` [N, K / group] fp32, w = (q - zero) * scale.
+    Supports exactly the operations the loader applies to weights (row / column slices, row concatenation), so
+    tensor-parallel slicing and projection fusing keep the checkpoint's quantisation grid bit for bit."""
+
+    dtype = torch.uint8
+
+    def __init__(self, q: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group: int):
+        self.q, self.scales, self.zeros, self.group = q, scales, zeros, group
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    def dim(self) -> int:
+        return 2
+
+    def rows(self, a: int, b: int) -> "QuantW":
+        return QuantW(self.q[a:b], self.scales[a:b], self.zeros[a:b], self.group)
+
+    def cols(self, a: int, b: int) -> "QuantW":
+        g = self.group
+        if a % g or b % g:
+            raise ValueError(f"a K slice [{a}, {b}) must fall on group boundaries (group {g})")
+        return QuantW(self.q[:, a:b], self.scales[:, a // g:b // g], self.zeros[:, a // g:b // g], g)
+
+    @staticmethod
+    def cat0(parts) -> "QuantW":
+        return QuantW(torch.cat([p.q for p in parts], 0), torch.cat([p.scales for p in parts], 0),
+                      torch.cat([p.zeros for p in parts], 0), parts[0].group)
+
+    def dequant(self) -> torch.Tensor:
+        N, K = self.q.shape
+        qf = self.q.float().view(N, K // self.group, self.group)
+        return ((qf - self.zeros.unsqueeze(-1)) * self.scales.unsqueeze(-1)).view(N, K)
+
+
+_AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)  # nibble i of an AutoAWQ word holds column 8 * word + _AWQ_ORDER[i]
+
+
+def _unpack_nibbles(packed: torch.Tensor, dim: int, order=None) -> torch.Tensor:
+    """int32 words -> uint8 values 0..15, eight per word laid out along ``dim`` (nibble i -> position order[i])."""
+    p = packed.to(torch.int64) & 0xFFFFFFFF
+    parts = [((p >> (4 * i)) & 0xF).to(torch.uint8) for i in range(8)]
+    if order is not None:
+        inv = [0] * 8
+        for i, o in enumerate(order):
+            inv[o] = i
+        parts = [parts[inv[c]] for c in range(8)]
+    st = torch.stack(parts, dim=dim + 1)
+    shape = list(packed.shape)
+    shape[dim] *= 8
+    return st.reshape(shape)
+
+
+def unpack_gptq(qweight, qzeros, scales, g_idx, group: int, v1_zero_offset: bool):
+    """AutoGPTQ layout: qweight [K/8, N] (packed along K), qzeros [K/g, N/8] (packed along N; the v1 format stores
+    zero - 1), scales [K/g, N], g_idx [K]. Returns (QuantW or None, dense fp32 weight or None): act-order
+    checkpoints (groups not contiguous in K) are returned dense."""
+    q = _unpack_nibbles(qweight, 0).t().contiguous()                 # [N, K]
+    z = _unpack_nibbles(qzeros, 1).t().contiguous().float()          # [N, K/g]
+    if v1_zero_offset:
+        z = z + 1.0
+    sc = scales.float().t().contiguous()                             # [N, K/g]
+    K = q.shape[1]
+    if g_idx is not None:
+        gi = g_idx.to(torch.int64)
+        trivial = torch.equal(gi, torch.arange(K, device=gi.device) // group)
+        if not trivial:
+            w = (q.float() - z[:, gi]) * sc[:, gi]
+            return None, w
+    return QuantW(q, sc, z, group), None
+
+
+def unpack_awq(qweight, qzeros, scales, group: int):
+    """AutoAWQ GEMM layout: qweight [K, N/8], qzeros [K/g, N/8] (both packed along N in the AWQ nibble order),
+    scales [K/g, N]."""
+    q = _unpack_nibbles(qweight, 1, _AWQ_ORDER).t().contiguous()     # [N, K]
+    z = _unpack_nibbles(qzeros, 1, _AWQ_ORDER).t().contiguous().float()
+    return QuantW(q, scales.float().t().contiguous(), z, group)
+
+
+def _rows(t, rank: int, size: int):
     n = t.shape[0] // size
+    if isinstance(t, QuantW):
+        return t.rows(rank * n, (rank + 1) * n)
     return t[rank * n:(rank + 1) * n]
 
 
-def _cols(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+def _cols(t, rank: int, size: int):
     n = t.shape[1] // size
+    if isinstance(t, QuantW):
+        return t.cols(rank * n, (rank + 1) * n)
     return t[:, rank * n:(rank + 1) * n]
+
+
+def _cat0(parts):
+    if any(isinstance(p, QuantW) for p in parts):
+        if not all(isinstance(p, QuantW) for p in parts):
+            parts = [p.dequant() if isinstance(p, QuantW) else p.float() for p in parts]
+            return torch.cat(parts, 0)
+        return QuantW.cat0(parts)
+    return torch.cat(parts, 0)
 
 
 def _kv_rows(t: torch.Tensor, rank: int, size: int, num_kv_heads: int, d: int) -> torch.Tensor:
@@ -208,6 +304,8 @@ def _kv_rows(t: torch.Tensor, rank: int, size: int, num_kv_heads: int, d: int) -
         return _rows(t, rank, size)
     rep = size // num_kv_heads
     hidx = rank // rep
+    if isinstance(t, QuantW):
+        return t.rows(hidx * d, (hidx + 1) * d)
     return t[hidx * d:(hidx + 1) * d]
 
 
@@ -231,6 +329,7 @@ class WeightLoader:
         self.out: Dict[str, torch.Tensor] = {}
         self._pending: Dict[str, Dict[str, torch.Tensor]] = defaultdict(dict)
         self._experts: Dict[str, Dict[Tuple[int, str], torch.Tensor]] = defaultdict(dict)
+        self._qparts: Dict[str, Dict[str, torch.Tensor]] = defaultdict(dict)  # GPTQ / AWQ tensors of one linear
 
     # ---- placement --------------------------------------------------------------------------------
     def _own(self, t: torch.Tensor) -> torch.Tensor:
@@ -249,6 +348,12 @@ class WeightLoader:
     def _put_linear(self, prefix: str, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None) -> None:
         """Stores a linear weight, quantising at load time when requested. Norms, embeddings, the router
         and lm_head stay in the model dtype."""
+        if isinstance(w, QuantW):
+            # a GPTQ / AWQ checkpoint: keep its grid, only re-pack into this engine's word layout
+            self.out[prefix + ".qweight"] = self._own(ref.pack_int4(w.q.to(torch.int32)))
+            self.out[prefix + ".scales"] = self._own(w.scales.to(self.dtype))
+            self.out[prefix + ".zeros"] = self._own(w.zeros.to(self.dtype))
+            return
         if scale_inv is not None:
             self.out[prefix + ".weight"] = self._own(w)
             self.out[prefix + ".weight_scale_inv"] = self._own(scale_inv.float())
@@ -343,8 +448,38 @@ class WeightLoader:
             self._experts[key][(e, em.group(2) + "." + em.group(3))] = t
             self._maybe_flush_experts(key)
             return
+        qm = re.match(r"(.+)\.(qweight|qzeros|scales|g_idx)$", rest)
+        if qm and cfg.quant.method in ("gptq", "awq"):
+            stem, part = qm.groups()
+            parts = self._qparts[f"{key}.{stem}"]
+            parts[part] = t
+            need = {"qweight", "qzeros", "scales"} | ({"g_idx"} if cfg.quant.method == "gptq" else set())
+            if need <= set(parts):
+                del self._qparts[f"{key}.{stem}"]
+                self._consume_quantised(layer, block, stem, parts)
+            return
         self._pending[key][rest] = t
         self._maybe_flush(key)
+
+    def _consume_quantised(self, layer: str, block: str, stem: str, parts: Dict[str, torch.Tensor]) -> None:
+        """All tensors of one GPTQ / AWQ linear have arrived: unpack them and continue as if the checkpoint had
+        carried a ``.weight`` - a QuantW for the dense attention / FFN projections (grid preserved), a dequantised
+        tensor for everything else (experts, MLA projections, act-order GPTQ)."""
+        cfg = self.cfg
+        g = cfg.quant.group_size if cfg.quant.group_size > 0 else parts["qweight"].shape[0] * 8
+        dense = None
+        if cfg.quant.method == "gptq":
+            v1 = str(cfg.raw.get("quantization_config", {}).get("checkpoint_format", "gptq")) != "gptq_v2"
+            qw, dense = unpack_gptq(parts["qweight"], parts["qzeros"], parts["scales"], parts.get("g_idx"), g, v1)
+        else:
+            qw = unpack_awq(parts["qweight"], parts["qzeros"], parts["scales"], g)
+        keep_grid = (not cfg.use_mla and block in ("self_attn", "mlp") and
+                     re.fullmatch(r"(shared_expert\.)?(q_proj|k_proj|v_proj|o_proj|gate_proj|up_proj|down_proj)", stem)
+                     and (qw is not None) and qw.shape[1] % 128 == 0 and g % 64 == 0)
+        value = qw if keep_grid else (dense if dense is not None else qw.dequant())
+        if not isinstance(value, QuantW):
+            value = value.to(self.dtype)
+        self._consume(f"{layer}.{block}.{stem}.weight", value)
 
     # ---- streaming: a block is assembled as soon as all of its parts have arrived ----------------------
     @staticmethod
@@ -461,7 +596,7 @@ class WeightLoader:
                 qs, ks, vs = _rows(q, r, n), _kv_rows(k, r, n, hk, max(d // 128, 1)), _kv_rows(v, r, n, hk, max(d // 128, 1))
                 self.out[f"{key}.query_key_value.weight_scale_inv"] = torch.cat((qs, ks, vs), 0).float().to(self.device)
                 continue
-            fused = torch.cat((_rows(q, r, n), _kv_rows(k, r, n, hk, d), _kv_rows(v, r, n, hk, d)), 0)
+            fused = _cat0((_rows(q, r, n), _kv_rows(k, r, n, hk, d), _kv_rows(v, r, n, hk, d)))
             if suffix == "bias":
                 self._put(f"{key}.query_key_value.bias", fused)
             elif fused.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
@@ -530,7 +665,7 @@ class WeightLoader:
                 continue
             gs, us, ds = (p.get(pre + f"{x}_proj.weight_scale_inv") for x in ("gate", "up", "down"))
             if gate is not None:
-                fused = torch.cat((_rows(gate, r, n), _rows(up, r, n)), 0)
+                fused = _cat0((_rows(gate, r, n), _rows(up, r, n)))
                 fs = None if gs is None else torch.cat((_rows(gs, r, n), _rows(us, r, n)), 0)
                 self._put_linear(f"{key}.{pre}gate_up_proj", fused, fs)
             else:

@@ -1,0 +1,102 @@
+"""GPTQ and AWQ checkpoint layouts: a tiny Llama is quantised, written in each tool's tensor layout under the usual
+Hugging Face names, loaded back (single rank and tensor-parallel) and must reproduce the model built from the
+dequantised dense weights."""
+import pytest
+import torch
+
+from ksanallm_b200.config.model_config import model_config_from_dict
+from ksanallm_b200.engine.step_input import make_step_input
+from ksanallm_b200.models.loader import WeightLoader, synthetic_checkpoint
+from ksanallm_b200.models.transformer import TransformerModel
+from ksanallm_b200.ops import reference as ref
+
+BASE = dict(model_type="llama", hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+            intermediate_size=256, vocab_size=300, torch_dtype="float32", max_position_embeddings=64)
+GROUP = 64
+AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)
+
+
+def _pack_along(vals: torch.Tensor, dim: int, order=None) -> torch.Tensor:
+    """uint4 values -> int32 words, eight consecutive positions of ``dim`` per word."""
+    v = vals.to(torch.int64).movedim(dim, -1)
+    v = v.reshape(*v.shape[:-1], v.shape[-1] // 8, 8)
+    out = torch.zeros(v.shape[:-1], dtype=torch.int64)
+    for i in range(8):
+        out |= v[..., (order[i] if order else i)] << (4 * i)
+    out = torch.where(out >= 2 ** 31, out - 2 ** 32, out).to(torch.int32)
+    return out.movedim(-1, dim)
+
+
+def _quantised_checkpoint(fmt: str, act_order: bool = False):
+    cfg = model_config_from_dict(BASE)
+    dense, quant = [], []
+    for name, w in synthetic_checkpoint(cfg, seed=5, dtype=torch.float32):
+        is_linear = name.endswith("_proj.weight")
+        if not is_linear:
+            dense.append((name, w))
+            quant.append((name, w))
+            continue
+        packed, scales, zeros = ref.quant_int4_group(w, GROUP)
+        q = ref.unpack_int4(packed)                      # [N, K] values 0..15
+        dense.append((name, ref.dequant_int4_group(packed, scales, zeros, GROUP)))
+        stem = name[:-len(".weight")]
+        N, K = q.shape
+        if fmt == "gptq":
+            g_idx = torch.arange(K, dtype=torch.int32) // GROUP
+            qk = q
+            if act_order:  # shuffle input channels inside the checkpoint: groups are no longer contiguous
+                perm = torch.randperm(K, generator=torch.Generator().manual_seed(1))
+                qk, g_idx = q[:, perm], g_idx[perm]
+                dense[-1] = (name, dense[-1][1][:, perm])
+            quant += [(stem + ".qweight", _pack_along(qk.t().contiguous(), 0)),
+                      (stem + ".qzeros", _pack_along((zeros - 1).to(torch.int64).t().contiguous(), 1)),
+                      (stem + ".scales", scales.t().contiguous().half()), (stem + ".g_idx", g_idx)]
+            dense[-1] = (name, (qk.float() - zeros[:, g_idx.long()]) * scales.half().float()[:, g_idx.long()])
+        else:
+            quant += [(stem + ".qweight", _pack_along(q.t().contiguous(), 1, AWQ_ORDER)),
+                      (stem + ".qzeros", _pack_along(zeros.to(torch.int64).t().contiguous(), 1, AWQ_ORDER)),
+                      (stem + ".scales", scales.t().contiguous().half())]
+            dense[-1] = (name, (q.float().view(N, K // GROUP, GROUP) - zeros.unsqueeze(-1)).mul(
+                scales.half().float().unsqueeze(-1)).view(N, K))
+    qc = dict(BASE, quantization_config=dict(quant_method=fmt, bits=4, group_size=GROUP, desc_act=act_order,
+                                             zero_point=True))
+    return model_config_from_dict(BASE), dense, model_config_from_dict(qc), quant
+
+
+def _hidden(cfg, sd, **kw):
+    w = WeightLoader(cfg, dtype=torch.float32, **kw).load(sd)
+    model = TransformerModel(cfg, w, max_positions=64)
+    T = 9
+    meta = make_step_input(list(range(5, 5 + T)), list(range(T)), list(range(T)), [0, T], [T], [[0, 1]], device="cpu")
+    return model.forward(meta, model.allocate_kv_cache(2, 16)), w
+
+
+@pytest.mark.parametrize("fmt", ["gptq", "awq"])
+def test_quantised_checkpoint_keeps_its_grid(fmt):
+    cfg, dense, qcfg, quant = _quantised_checkpoint(fmt)
+    want, _ = _hidden(cfg, dense)
+    got, w = _hidden(qcfg, quant)
+    assert "model.layers.0.self_attn.query_key_value.qweight" in w and "model.layers.0.mlp.down_proj.qweight" in w
+    assert "model.layers.0.self_attn.query_key_value.weight" not in w
+    assert (got - want).abs().max().item() < 1e-5
+
+
+def test_gptq_act_order_falls_back_to_dense():
+    cfg, dense, qcfg, quant = _quantised_checkpoint("gptq", act_order=True)
+    want, _ = _hidden(cfg, dense)
+    got, w = _hidden(qcfg, quant)
+    assert "model.layers.0.self_attn.query_key_value.weight" in w  # permuted groups: stored dequantised
+    assert (got - want).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("fmt", ["gptq", "awq"])
+def test_quantised_checkpoint_tensor_parallel_slices(fmt):
+    cfg, dense, qcfg, quant = _quantised_checkpoint(fmt)
+    for rank in range(2):
+        wd = WeightLoader(cfg, tp_rank=rank, tp_size=2, dtype=torch.float32).load(dense)
+        wq = WeightLoader(qcfg, tp_rank=rank, tp_size=2, dtype=torch.float32).load(quant)
+        for stem in ("self_attn.query_key_value", "self_attn.o_proj", "mlp.gate_up_proj", "mlp.down_proj"):
+            p = f"model.layers.1.{stem}"
+            deq = ref.dequant_int4_group(wq[p + ".qweight"], wq[p + ".scales"].float(), wq[p + ".zeros"].float(), GROUP)
+            assert deq.shape == wd[p + ".weight"].shape
+            assert (deq - wd[p + ".weight"]).abs().max().item() < 1e-6, (rank, stem)
