@@ -50,6 +50,12 @@ CASES = {
     "deepseek_v3": ("DeepseekV3Config", "DeepseekV3ForCausalLM", DS),
     "deepseek_v3_rope_halves": ("DeepseekV3Config", "DeepseekV3ForCausalLM", dict(DS, rope_interleave=False,
                                                                                  q_lora_rank=None)),
+    "deepseek_v2": ("DeepseekV2Config", "DeepseekV2ForCausalLM", dict(
+        hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, intermediate_size=256,
+        vocab_size=300, max_position_embeddings=64, n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=2,
+        moe_intermediate_size=64, first_k_dense_replace=1, topk_method="greedy", norm_topk_prob=False,
+        routed_scaling_factor=16.0, q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8,
+        v_head_dim=16)),
     "gpt2": ("GPT2Config", "GPT2LMHeadModel", dict(n_embd=64, n_layer=2, n_head=4, n_positions=64, vocab_size=200)),
     "glm4": ("GlmConfig", "GlmForCausalLM", dict(BASE, head_dim=32, pad_token_id=0)),
     "hunyuan_dense": ("HunYuanDenseV1Config", "HunYuanDenseV1ForCausalLM", dict(BASE, head_dim=32)),
