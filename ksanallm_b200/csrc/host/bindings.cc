@@ -223,7 +223,8 @@ PYBIND11_MODULE(_ksana_host, m) {
           py::arg("plan"), py::arg("buffer"), py::arg("max_blocks") = 0)
       .def("packed_words", &Scheduler::PackedWords)
       .def("update", &Scheduler::Update, py::arg("plan"), py::arg("sampled"), py::arg("now_ms") = 0)
-      .def("resolve", &Scheduler::Resolve, py::arg("plan"), py::arg("real"));
+      .def("resolve", &Scheduler::Resolve, py::arg("plan"), py::arg("real"))
+      .def("set_micro_batch", &Scheduler::SetMicroBatch, py::arg("mb"), py::arg("count") = 1);
 
   py::class_<DraftTrie>(m, "DraftTrie")
       .def(py::init<int, int>(), py::arg("max_depth") = 16, py::arg("max_nodes") = 1 << 18)

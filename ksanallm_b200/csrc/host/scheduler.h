@@ -83,6 +83,7 @@ struct Sequence {
   int state = SEQ_WAITING;
   int finish_reason = FINISH_NONE;
   int preempt_count = 0;
+  int mb = -1;  // pipeline micro-batch this sequence belongs to (-1: none), fixed at admission
   // in-flight step
   int sched_q_len = 0;
   int sched_drafts = 0;
@@ -243,6 +244,13 @@ class Scheduler {
     if (it != seqs_.end() && it->second->state == SEQ_FINISHED) seqs_.erase(it);
   }
 
+  // Pipeline micro-batches: with a filter set, Schedule() only touches the sequences of that micro-batch (and
+  // assigns it to the sequences it admits), so that the other micro-batches' in-flight steps are left alone.
+  void SetMicroBatch(int mb, int count = 1) {
+    mb_filter_ = mb;
+    mb_count_ = count < 1 ? 1 : count;
+  }
+
   StepPlan Schedule(int64_t now_ms) {
     StepPlan plan;
     ++stats_.steps;
@@ -258,6 +266,11 @@ class Scheduler {
     while (!running_.empty()) {
       int64_t id = running_.front();
       Sequence& s = *seqs_.at(id);
+      if (mb_filter_ >= 0 && s.mb != mb_filter_) {
+        running_.pop_front();
+        keep.push_back(id);
+        continue;
+      }
       int remaining = static_cast<int>(s.tokens.size()) - s.num_computed;  // >= 1
       bool mid_prefill = remaining > 1;
       int n_drafts = mid_prefill ? 0 : std::min<int>(static_cast<int>(s.drafts.size()), cfg_.max_draft_tokens);
@@ -275,8 +288,18 @@ class Scheduler {
       while (!ok) {
         // Pre-empt the most recently admitted sequence that is not yet planned this step.
         if (running_.size() <= 1) break;
-        int64_t victim = running_.back();
-        running_.pop_back();
+        // (with a micro-batch filter only this micro-batch's sequences are candidates: the others may be in flight)
+        auto vit = running_.end();
+        for (auto it2 = running_.end(); it2 != running_.begin() + 1;) {
+          --it2;
+          if (mb_filter_ < 0 || seqs_.at(*it2)->mb == mb_filter_) {
+            vit = it2;
+            break;
+          }
+        }
+        if (vit == running_.end()) break;
+        int64_t victim = *vit;
+        running_.erase(vit);
         Preempt(victim, &plan);
         ok = cache_->EnsureCapacity(id, s.num_computed + q_len);
       }
@@ -301,6 +324,7 @@ class Scheduler {
     while (!swapped_.empty() && batch_budget > 0 && token_budget > 0 && plan.swap_out.empty()) {
       int64_t id = swapped_.front();
       Sequence& s = *seqs_.at(id);
+      if (mb_filter_ >= 0 && s.mb != mb_filter_) break;
       int need_now = 1 + std::min<int>(static_cast<int>(s.drafts.size()), cfg_.max_draft_tokens);
       int blocks_after = (s.num_computed + need_now + cfg_.block_size - 1) / cfg_.block_size;
       int extra = blocks_after - cache_->NumBlocks(id);
@@ -334,7 +358,12 @@ class Scheduler {
     // ---- 3. waiting queue -------------------------------------------------------------------
     bool preempted_now = !plan.swap_out.empty() || preempted_this_step_;
     preempted_this_step_ = false;
-    while (!waiting_.empty() && batch_budget > 0 && token_budget > 0 && swapped_.empty() && !preempted_now) {
+    // with micro-batches, one call admits its share of the queue so that the others get work too
+    int admit_left = mb_filter_ >= 0 ? std::max<int>(1, (static_cast<int>(waiting_.size()) + mb_count_ - 1) / mb_count_)
+                                     : (1 << 30);
+    while (!waiting_.empty() && batch_budget > 0 && token_budget > 0 && swapped_.empty() && !preempted_now &&
+           admit_left > 0) {
+      --admit_left;
       int64_t id = waiting_.front();
       Sequence& s = *seqs_.at(id);
       if (!cache_->Has(id)) {
@@ -379,6 +408,7 @@ class Scheduler {
       }
       waiting_.pop_front();
       s.state = SEQ_RUNNING;
+      if (mb_filter_ >= 0) s.mb = mb_filter_;
       running_.push_back(id);
       bool final_chunk = (s.num_computed + q_len) == static_cast<int>(s.tokens.size());
       bool as_decode = s.num_computed > 0 && q_len <= cfg_.decode_token_threshold;
@@ -683,6 +713,7 @@ class Scheduler {
   std::deque<int64_t> waiting_, running_, swapped_;
   std::unordered_set<int64_t> aborted_;
   std::vector<CopyPair> pending_copies_;
+  int mb_filter_ = -1, mb_count_ = 1;
   bool preempted_this_step_ = false;
   SchedStats stats_;
 };

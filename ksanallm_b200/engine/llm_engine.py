@@ -271,11 +271,14 @@ class LLMEngine:
         self._wake.set()
 
     def has_unfinished(self) -> bool:
-        return self.sched.has_unfinished() or self._inflight is not None
+        return (self.sched.has_unfinished() or self._inflight is not None or
+                any(x is not None for x in getattr(self, "_mb_inflight", ())))
 
     # ---- one step ----------------------------------------------------------------------------------------
     def step(self) -> int:
         """Schedules and runs one step. Returns the number of tokens generated."""
+        if self.pipeline is not None and getattr(self, "pp_micro_batches", 1) > 1 and self.is_driver:
+            return self._step_pipelined()
         if self.async_mode and self.is_driver:
             if self._complex_requests == 0 and (self.pipeline is None or self.pipeline.topo.num_stages == 1):
                 return self._step_async()
@@ -654,11 +657,67 @@ class LLMEngine:
         return steps
 
     # ---- pipeline parallelism ---------------------------------------------------------------------------------
-    def attach_pipeline(self, stage) -> None:
+    def attach_pipeline(self, stage, micro_batches: int = 1) -> None:
         """``stage``: parallel.pipeline.PipelineStage of this rank. The driver is rank 0 (first stage); the last
-        stage computes the tokens and returns them to the driver."""
+        stage computes the tokens and returns them to the driver. With ``micro_batches`` > 1 the driver keeps that
+        many disjoint groups of sequences in flight: while a later stage works on one group the first stage already
+        runs the next (reference: pp_multibatch + MultiBatchController)."""
+        from ..parallel.pipeline import MultiBatchController
         self.pipeline = stage
         self.is_driver = stage.topo.rank == 0
+        self.async_mode = False
+        self.pp_micro_batches = max(int(micro_batches), 1) if stage.topo.num_stages > 1 else 1
+        self.mbc = MultiBatchController(self.pp_micro_batches)
+        self._mb_inflight = [None] * self.pp_micro_batches
+        self._mb_next = 0
+
+    def _collect_micro_batch(self, mb: int) -> int:
+        from .sampler import SampleOutput
+        plan, n = self._mb_inflight[mb]
+        self._mb_inflight[mb] = None
+        pl = self.pipeline
+        toks = []
+        if n:
+            toks = pl.channel.recv_tokens(n, pl.topo.num_stages * pl.topo.tp_size - pl.topo.tp_size).to("cpu").tolist()
+            self.runner.d2h_bytes += 4 * n
+        with self.lock:
+            out = SampleOutput(tokens=toks, logprobs=[None] * n, chosen_logprob=[None] * n)
+            got = self._apply_results(plan, out, None, None)
+        self.mbc.collected(mb)
+        return got
+
+    def _step_pipelined(self) -> int:
+        """One driver step with several pipeline micro-batches: collect the oldest in-flight step of this
+        micro-batch (its tokens come back from the last stage), then schedule and launch its next step."""
+        mb = self._mb_next
+        self._mb_next = (mb + 1) % self.pp_micro_batches
+        n_new = 0
+        if self._mb_inflight[mb] is not None:
+            n_new += self._collect_micro_batch(mb)
+        with self.lock:
+            self.sched.set_micro_batch(mb, self.pp_micro_batches)
+            plan = self.sched.schedule(int(time.time() * 1000))
+            self.sched.set_micro_batch(-1)
+            for sid, reason in plan.dropped:
+                self._finish_seq(sid, reason)
+            if plan.empty():
+                return n_new
+            self.runner.staging.flip()
+            layout = self.sched.pack(plan, self.runner.staging.host_np, self.runner.max_blocks_per_seq)
+            rows, greedy, refit = self._sample_rows(plan)
+        if not greedy:
+            raise NotImplementedError("pipeline-parallel serving samples greedily")
+        self._broadcast_plan(layout, plan, True)
+        self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
+        meta = self.runner.upload(layout)
+        self.mbc.ready(mb)
+        self.mbc.start(mb)
+        self.pipeline.run(meta, self.runner.kv_caches, refit)  # first stage: forward + send, returns None
+        self.mbc.done(mb)  # this stage is free for the next micro-batch; the results are still travelling
+        self._mb_inflight[mb] = (plan, meta.total_logits)
+        self.step_count += 1
+        self.stats["steps"] += 1
+        return n_new
 
     def _pipeline_step_driver(self, meta, refit, rows, greedy):
         from .sampler import SampleOutput

@@ -90,7 +90,11 @@ class HiddenChannel:
         return buf
 
     def send_tokens(self, toks: torch.Tensor, dst_rank: int = 0) -> None:
-        dist.send(toks.to(torch.int32).contiguous(), dst=dst_rank, group=self.group)
+        """Non-blocking: with several micro-batches in flight the driver only posts the matching receive after it
+        has launched the next micro-batch, so a blocking send here could dead-lock against its plan broadcast."""
+        buf = toks.to(torch.int32).contiguous()
+        self._pending_sends = [(w, b) for w, b in getattr(self, "_pending_sends", []) if not w.is_completed()]
+        self._pending_sends.append((dist.isend(buf, dst=dst_rank, group=self.group), buf))
 
     def recv_tokens(self, count: int, src_rank: int) -> torch.Tensor:
         buf = torch.empty(count, dtype=torch.int32, device=self.device)

@@ -59,7 +59,7 @@ def _serving():
 PROMPTS = [[5, 9, 77, 120, 33, 4, 8], [400, 3, 3, 19, 250, 7, 7, 7, 91, 12, 13], [8, 6, 4]]
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, micro_batches=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     topo = StageTopology(world, 1, rank)
@@ -72,17 +72,21 @@ def _worker(rank, world, port, out):
     eng = LLMEngine(model, _serving(), num_blocks=64, num_host_blocks=0)
     eng.attach_control_group(dist.group.WORLD)
     eng.attach_pipeline(PipelineStage(model, topo, HiddenChannel(topo, cfg.hidden_size, torch.float32,
-                                                                 torch.device("cpu"))))
+                                                                 torch.device("cpu"))), micro_batches)
     if rank == 0:
         reqs = eng.generate(PROMPTS, SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True))
         eng.shutdown_followers()
-        out.put([r.output_token_ids[0] for r in reqs])
+        out.put(([r.output_token_ids[0] for r in reqs], list(getattr(eng, "mbc").history)))
     else:
         eng.follow()
     dist.destroy_process_group()
 
 
-def test_pp2_matches_single_process():
+import pytest
+
+
+@pytest.mark.parametrize("micro_batches", [1, 2])
+def test_pp2_matches_single_process(micro_batches):
     cfg = _cfg()
     w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32)
     eng = LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=64, num_host_blocks=0)
@@ -93,11 +97,13 @@ def test_pp2_matches_single_process():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, micro_batches)) for r in range(2)]
     for p in procs:
         p.start()
-    got = q.get(timeout=120)
+    got, history = q.get(timeout=120)
     for p in procs:
         p.join(timeout=30)
         assert p.exitcode == 0
     assert got == want
+    if micro_batches == 2:
+        assert set(history) == {0, 1}, "both micro-batches must have carried work"
