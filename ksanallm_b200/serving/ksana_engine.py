@@ -234,6 +234,12 @@ class KsanaLLMEngine:
             import torch.distributed as dist
             self.llm.attach_control_group(dist.new_group(backend="gloo"))
         self._load_plugin()
+        self.connector = None
+        cs = self.serving.setting.connector
+        if cs.group_role in ("prefill", "decode", "both") and tp.rank == 0:
+            from .connector import PDConnector
+            self.connector = PDConnector(self.llm, cs)
+            self.connector.start()
         from ..ops import gemm_tune
         gemm_tune.maybe_load_from_env()  # KSANA_GEMM_TUNE_FILE written by benchmarks/search_best_gemm.py
         if tp.rank == 0:
@@ -248,6 +254,8 @@ class KsanaLLMEngine:
         self.llm.follow()
 
     def shutdown(self) -> None:
+        if getattr(self, "connector", None) is not None:
+            self.connector.stop()
         if self.llm is not None:
             self.llm.stop()
 
@@ -316,7 +324,10 @@ class KsanaLLMEngine:
             seqs = req.beam.best(req)
         elif req.params.num_return_sequences < len(seqs) and req.finished:
             seqs = seqs[:req.params.num_return_sequences]
-        out.output_tokens = [list(s.output_tokens) for s in seqs]
+        first = list(getattr(req, "pd_first", []) or [])
+        out.output_tokens = [first + list(s.output_tokens) for s in seqs]
+        if first:
+            out.input_tokens = list(req.prompt_tokens[:req.pd_prompt_len])
         out.logprobs = [s.logprobs for s in seqs] if req.params.logprobs else []
         out.finish_reasons = [s.finish_reason for s in seqs]
         out.finished = req.finished
@@ -328,12 +339,32 @@ class KsanaLLMEngine:
     async def generate(self, request_dict: Dict[str, Any], streamer: Optional[bool] = None,
                        req_ctx: Optional[Dict[str, str]] = None):
         """Returns (Status, KsanaPythonOutput) or (Status, async iterator of KsanaPythonOutput) when streaming."""
+        pd_first: List[int] = []
+        pd_rid = (req_ctx or {}).get("kv-comm-request-id") if getattr(self, "connector", None) is not None else None
         try:
             sp = self._build_sampling(request_dict)
             tokens, refit = self._build_tokens(request_dict)
             grammar = self._grammar_for(sp)
+            if pd_rid and self.connector.role == "decode":
+                # the prefill instance computes the prompt and pushes its KV blocks + first token here
+                loop0 = asyncio.get_running_loop()
+                got = await loop0.run_in_executor(None, self.connector.wait_import, pd_rid,
+                                                  float(self.serving.setting.connector.connector_waiting_sec))
+                if got is None:
+                    return Status(RetCode.RET_REQUEST_TIMEOUT,
+                                  "timed out waiting for the prefill instance's KV transfer"), None
+                _, pd_first, _ = got
+                if pd_first:
+                    import dataclasses as _dc
+                    tokens = list(tokens) + list(pd_first)
+                    sp = _dc.replace(sp, max_new_tokens=max(sp.max_new_tokens - len(pd_first), 0))
+            elif pd_rid and self.connector.role == "prefill":
+                import dataclasses as _dc
+                sp = _dc.replace(sp, max_new_tokens=1)
             req = self.llm.add_request(tokens, sp, refit=refit, grammar=grammar, mrope_positions=self._last_mrope)
             req.ctx = req_ctx or {}
+            req.pd_first = pd_first
+            req.pd_prompt_len = len(tokens) - len(pd_first)
         except EngineError as ex:
             return Status(ex.code, str(ex)), None
         except (ValueError, KeyError, TypeError) as ex:
@@ -345,6 +376,10 @@ class KsanaLLMEngine:
         while not req.finished:
             v = await loop.run_in_executor(None, req.wait, v, 1.0)
         out = self._snapshot(req)
+        if pd_rid and self.connector.role == "prefill" and req.error is None:
+            # hand the request over: KV of the prompt's full blocks + the first token
+            await loop.run_in_executor(None, self.connector.export, pd_rid, (req_ctx or {}).get("kv-comm-group-key", ""),
+                                       list(req.prompt_tokens), list(req.seqs[0].output_tokens))
         if self.plugin is not None:
             self.plugin.postprocess(request_dict, out)
         return out.finish_status, out

@@ -26,6 +26,7 @@ HEARTBEAT_TIMEOUT_S = 30.0
 
 class NodeRegistry:
     def __init__(self, path: str = ":memory:", heartbeat_timeout: float = HEARTBEAT_TIMEOUT_S):
+        self.transfer_addrs: Dict[str, str] = {}
         self.db = sqlite3.connect(path, check_same_thread=False)
         self.lock = threading.Lock()
         self.timeout = heartbeat_timeout
@@ -36,10 +37,12 @@ class NodeRegistry:
             self.db.execute("CREATE TABLE IF NOT EXISTS comm_ids (group_key TEXT PRIMARY KEY, comm_id TEXT, created REAL)")
             self.db.commit()
 
-    def register(self, group_name: str, role: str, addr: str, world_size: int = 1, node_id: Optional[str] = None) -> str:
+    def register(self, group_name: str, role: str, addr: str, world_size: int = 1, node_id: Optional[str] = None,
+                 transfer_addr: str = "") -> str:
         if role not in ("prefill", "decode", "both"):
             raise ValueError("role must be prefill, decode or both")
         node_id = node_id or uuid.uuid4().hex
+        self.transfer_addrs[node_id] = transfer_addr  # where a decode node accepts KV transfers
         with self.lock:
             self.db.execute("INSERT OR REPLACE INTO nodes VALUES (?, ?, ?, ?, ?, ?, 0, 1)",
                             (node_id, group_name, role, addr, world_size, time.time()))
@@ -95,7 +98,10 @@ class NodeRegistry:
             rows = self.db.execute("SELECT node_id, group_name, role, addr, world_size, last_heartbeat, inflight, "
                                    "online FROM nodes").fetchall()
         keys = ["node_id", "group_name", "role", "addr", "world_size", "last_heartbeat", "inflight", "online"]
-        return [dict(zip(keys, r)) for r in rows]
+        out = [dict(zip(keys, r)) for r in rows]
+        for n in out:
+            n["transfer_addr"] = self.transfer_addrs.get(n["node_id"], "")
+        return out
 
 
 def create_app(registry: Optional[NodeRegistry] = None, http_client_factory=None) -> FastAPI:
@@ -113,7 +119,8 @@ def create_app(registry: Optional[NodeRegistry] = None, http_client_factory=None
     async def register_node(req: Request):
         b = await req.json()
         try:
-            nid = reg.register(b["group_name"], b["role"], b["addr"], int(b.get("world_size", 1)), b.get("node_id"))
+            nid = reg.register(b["group_name"], b["role"], b["addr"], int(b.get("world_size", 1)), b.get("node_id"),
+                               str(b.get("transfer_addr", "") or ""))
         except (KeyError, ValueError) as ex:
             raise HTTPException(400, str(ex))
         return {"node_id": nid, "heartbeat_timeout_s": reg.timeout}
