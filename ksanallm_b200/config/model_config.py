@@ -108,6 +108,8 @@ class ModelConfig:
     v_head_dim: int = 0
     # MTP
     num_nextn_predict_layers: int = 0
+    num_register_token: int = 0  # parallel token prediction: register tokens appended per step (0 = off)
+    reg_token_id: int = 0
     # quantisation
     quant: QuantConfig = field(default_factory=QuantConfig)
     raw: Dict[str, Any] = field(default_factory=dict)
@@ -327,6 +329,8 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
         m.num_kv_heads = 1
         m.rope_interleaved = bool(g("rope_interleave", True))
     m.num_nextn_predict_layers = int(g("num_nextn_predict_layers", 0) or 0)
+    m.num_register_token = int(g("num_register_token", 0) or 0)  # reference: models/common/common_config.h:36-37
+    m.reg_token_id = int(g("reg_token_id", 0) or 0)
     m.quant = _quant(g("quantization_config", None))
     return m
 

@@ -90,6 +90,7 @@ PYBIND11_MODULE(_ksana_host, m) {
       .def_readwrite("launch_block_threshold", &SchedulerConfig::launch_block_threshold)
       .def_readwrite("swapin_block_threshold", &SchedulerConfig::swapin_block_threshold)
       .def_readwrite("max_draft_tokens", &SchedulerConfig::max_draft_tokens)
+      .def_readwrite("ptp_mode", &SchedulerConfig::ptp_mode)
       .def_readwrite("decode_token_threshold", &SchedulerConfig::decode_token_threshold);
 
   py::class_<SchedStats>(m, "SchedStats")

@@ -65,6 +65,11 @@ struct SchedulerConfig {
   double launch_block_threshold = 2.0;
   double swapin_block_threshold = 2.0;
   int max_draft_tokens = 0;       // speculative tokens verified per decode step
+  // Parallel token prediction: the "drafts" are register tokens appended after the sequence's last real tokens; the
+  // model answers every register position with one more token, all of them are kept (nothing is verified) and the
+  // registers' own KV entries are dropped. The reference: runtime/draft_generator/ptp_generator.cpp,
+  // runtime/ptp_generation_controller.cpp.
+  bool ptp_mode = false;
   int decode_token_threshold = 1;  // q_len <= threshold with cached KV counts as a decode entry
 };
 
@@ -277,7 +282,12 @@ class Scheduler {
       int q_len = remaining;
       if (mid_prefill && cfg_.split_fuse_token_num > 0) q_len = std::min(q_len, cfg_.split_fuse_token_num);
       q_len = std::min(q_len, std::max(token_budget, 0));
-      if (!mid_prefill) q_len = remaining + n_drafts;
+      if (mid_prefill && cfg_.ptp_mode && q_len == remaining) {
+        // the chunk reaches the sequence's end: the register tokens ride along if they still fit
+        int want = std::min<int>(static_cast<int>(s.drafts.size()), cfg_.max_draft_tokens);
+        if (remaining + want <= token_budget) n_drafts = want;
+      }
+      if (!mid_prefill || n_drafts > 0) q_len = remaining + n_drafts;
       if (batch_budget <= 0 || q_len <= 0 || q_len > token_budget) {
         // No room this step: the sequence simply waits in place (keeps its cache).
         running_.pop_front();
@@ -521,7 +531,7 @@ class Scheduler {
       }
       // Draft verification: sampled[i] is the model's token after (real tokens + drafts[0..i)).
       int accepted = 0;
-      while (accepted < e.n_drafts && sampled[base + accepted] == s.drafts[accepted] &&
+      while (!cfg_.ptp_mode && accepted < e.n_drafts && sampled[base + accepted] == s.drafts[accepted] &&
              !IsStop(s, sampled[base + accepted])) {
         ++accepted;
       }
@@ -529,7 +539,10 @@ class Scheduler {
       r.accepted_drafts = accepted;
       s.num_computed += real + accepted;
       int reason = FINISH_NONE;
-      for (int i = 0; i <= accepted; ++i) {
+      // parallel token prediction keeps the token of every register position; their KV is recomputed from the real
+      // tokens in the next step (num_computed did not advance over the registers)
+      int keep_upto = cfg_.ptp_mode ? e.n_drafts : accepted;
+      for (int i = 0; i <= keep_upto; ++i) {
         int32_t tok = sampled[base + i];
         s.tokens.push_back(tok);
         r.new_tokens.push_back(tok);

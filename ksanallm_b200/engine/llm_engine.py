@@ -130,7 +130,14 @@ class LLMEngine:
         sc.preempt_mode = bs_cfg.preempt_mode if num_host_blocks > 0 else 1
         sc.launch_block_threshold = bs_cfg.launch_block_threshold
         sc.swapin_block_threshold = bs_cfg.swapin_block_threshold
-        sc.max_draft_tokens = max(self.mtp_steps, self.trie_drafts)
+        # parallel token prediction (config.json: num_register_token / reg_token_id): N register tokens follow the
+        # last real token and every position yields a token (reference: runtime/draft_generator/ptp_generator.cpp)
+        self.ptp_steps = int(getattr(model.cfg, "num_register_token", 0) or 0)
+        self.ptp_token = int(getattr(model.cfg, "reg_token_id", 0) or 0)
+        if self.ptp_steps:
+            self.mtp_steps = self.trie_drafts = 0
+        sc.max_draft_tokens = max(self.mtp_steps, self.trie_drafts, self.ptp_steps)
+        sc.ptp_mode = self.ptp_steps > 0
         sc.decode_token_threshold = 1 + sc.max_draft_tokens
         self.cache = _host.KVCacheManager(num_blocks, num_host_blocks, self.block_size,
                                           bool(bs_cfg.enable_auto_prefix_cache))
@@ -155,7 +162,8 @@ class LLMEngine:
         self.pipeline = None  # parallel.pipeline.PipelineStage when the model is split over stages
         # asynchronous scheduling (setting.batch_scheduler.enable_async): step N + 1 is planned and launched while
         # step N still runs; its tokens reach the host one step late
-        self.async_mode = bool(bs_cfg.enable_async) and not self.mtp_steps and not self.trie_drafts
+        self.async_mode = bool(bs_cfg.enable_async) and not self.mtp_steps and not self.trie_drafts and \
+            not self.ptp_steps
         self._inflight = None       # (plan, token handle) of the step whose tokens are not on the host yet
         self._complex_requests = 0  # live requests that need per-token host state (grammar, beams, penalties, ...)
         self.dp = None              # parallel.attn_dp.DPCoordinator under attention data parallelism
@@ -496,6 +504,8 @@ class LLMEngine:
                     d = trie.propose(self.trie_drafts)
                     if d:
                         self.sched.set_drafts(r.seq_id, d)
+                if self.ptp_steps:
+                    self.sched.set_drafts(r.seq_id, [self.ptp_token] * self.ptp_steps)
             # fan-out of parallel samples once the prompt's blocks are cached
             if getattr(req, "_pending_fanout", 0) and r.new_tokens:
                 k = req._pending_fanout

@@ -14,6 +14,11 @@ from ksanallm_b200.models.transformer import TransformerModel
 
 def plain_forward(sd, cfg, tokens):
     """Dense causal forward with HF-named weights; returns logits of the last position."""
+    return plain_forward_all(sd, cfg, tokens)[-1]
+
+
+def plain_forward_all(sd, cfg, tokens):
+    """Dense causal forward with HF-named weights; returns the logits of every position."""
     H, nh, d = cfg.hidden_size, cfg.num_heads, cfg.head_dim
     x = sd["model.embed_tokens.weight"][tokens]
     T = len(tokens)
@@ -44,7 +49,7 @@ def plain_forward(sd, cfg, tokens):
         g = torch.nn.functional.silu(h @ sd[p + "mlp.gate_proj.weight"].t()) * (h @ sd[p + "mlp.up_proj.weight"].t())
         x = x + g @ sd[p + "mlp.down_proj.weight"].t()
     x = norm(x, sd["model.norm.weight"])
-    return x[-1] @ sd["lm_head.weight"].t()
+    return x @ sd["lm_head.weight"].t()
 
 
 def test_tiny_llama_greedy_matches_plain_forward():
