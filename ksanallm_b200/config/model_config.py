@@ -67,6 +67,7 @@ class ModelConfig:
     mlp_bias: bool = False
     gated_mlp: bool = True
     qk_norm: bool = False  # per-head RMSNorm on q and k before RoPE (Qwen3)
+    cla_share_factor: int = 0  # cross-layer attention: K/V projections shared by groups of this many layers (Hunyuan)
     qk_norm_after_rope: bool = False  # ... applied after RoPE instead (Hunyuan)
     sliding_window: int = 0  # attention window in tokens (0: full causal); per layer via sliding_layers
     sliding_layers: List[int] = field(default_factory=list)  # 1 = windowed layer; empty with a window: every layer
@@ -75,6 +76,7 @@ class ModelConfig:
     moe_layers: List[int] = field(default_factory=list)   # explicit MoE layer indices (Llama 4); empty: by frequency
     moe_router: str = "standard"  # standard | llama4 (top-k on logits, sigmoid score scales the expert INPUT)
     attn_temperature_tuning: bool = False  # Llama 4: query scaling on the no-RoPE layers
+    attention_chunk_size: int = 0  # Llama 4: RoPE layers attend inside blocks of this many positions (0 = off)
     attn_floor_scale: float = 8192.0
     attn_scale_coef: float = 0.1
     bos_token_id: Optional[int] = None
@@ -212,6 +214,16 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
                                    rp.get("mrope_section")):
         rs_dict = rp
     m.rope_scaling = _rope_scaling(rs_dict, c)
+    xd = g("xdrope_section", None)
+    if xd and g("position_embedding_xdrope", True):
+        # XD-RoPE (Arc-Hunyuan-Video): four position axes, sections given as fractions of half the head size; the
+        # table itself is the alpha-scaled NTK one (reference: arc_hunyuan_video_config_parser.cpp:72-93,
+        # rotary_embedding.cu:361-372)
+        half = (m.head_dim or m.hidden_size // m.num_heads) // 2
+        m.rope_scaling.mrope_section = [int(float(f) * half) for f in xd]
+        if m.rope_scaling.type in ("default", "xdrope"):
+            m.rope_scaling.type = "dynamic"
+            m.rope_scaling.alpha = float((rs_dict or {}).get("alpha", 1000.0))
     m.tie_word_embeddings = bool(g("tie_word_embeddings", False))
     m.hidden_act = str(g("hidden_act", g("activation_function", "silu")))
     m.torch_dtype = str(g("torch_dtype", g("dtype", "bfloat16")))
@@ -236,12 +248,15 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
     if mt.startswith("hunyuan"):
         m.qk_norm = bool(g("use_qk_norm", True))
         m.qk_norm_after_rope = m.qk_norm
+        if g("use_cla", False):
+            m.cla_share_factor = int(g("cla_share_factor", 0) or 0)
     if mt.startswith("llama4"):
         m.rope_interleaved = True
         m.qk_l2_norm = bool(g("use_qk_norm", True))
         m.rope_layers = [int(x) for x in (g("no_rope_layers", None) or [])]
         m.attn_temperature_tuning = bool(g("attn_temperature_tuning", False))
         m.attn_floor_scale = float(g("floor_scale", 8192))
+        m.attention_chunk_size = int(g("attention_chunk_size", 0) or 0)
         m.attn_scale_coef = float(g("attn_scale", 0.1))
     if mt in ("gpt2", "fairseq_transformer", "gpt"):
         m.norm_type, m.post_norm, m.gated_mlp, m.position_encoding = "layernorm", False, False, "learned"

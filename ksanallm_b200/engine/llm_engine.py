@@ -204,9 +204,10 @@ class LLMEngine:
         req = Request(next(self._ids), list(int(t) for t in prompt_tokens), params, now)
         req.refit, req.grammar, req.probe = refit, grammar, probe
         if mrope_positions is not None:
-            mp = torch.as_tensor(mrope_positions, dtype=torch.int32).reshape(3, -1)
+            axes = self._rope_axes()
+            mp = torch.as_tensor(mrope_positions, dtype=torch.int32).reshape(axes, -1)
             if mp.shape[1] != len(req.prompt_tokens):
-                raise EngineError(_host.RET_INVALID_ARGUMENT, "mrope_positions must be [3, prompt_len]")
+                raise EngineError(_host.RET_INVALID_ARGUMENT, f"mrope_positions must be [{axes}, prompt_len]")
             req.mrope = mp
             req.mrope_delta = int(mp.max()) + 1 - mp.shape[1] if mp.numel() else 0
         n_out = max(params.num_beams, params.num_return_sequences, 1)
@@ -420,22 +421,28 @@ class LLMEngine:
         st["t_apply"] += t3 - t2
         return n_new
 
+    def _rope_axes(self) -> int:
+        """Position axes per token: 3 for M-RoPE (temporal, height, width), 4 for XD-RoPE."""
+        sec = self.runner.model.cfg.rope_scaling.mrope_section
+        return 4 if len(sec) == 4 else 3
+
     def _attach_mrope(self, plan, meta) -> None:
-        """Builds the step's [3, T] multimodal positions when any scheduled request carries them."""
+        """Builds the step's [axes, T] multimodal positions when any scheduled request carries them."""
         if not any(getattr(self.seq_owner[e.seq_id][0], "mrope", None) is not None for e in plan.entries
                    if e.seq_id in self.seq_owner):
             return
         cols = []
+        axes = self._rope_axes()
         for e in plan.entries:
             req = self.seq_owner[e.seq_id][0]
             idx = torch.arange(e.q_start, e.q_start + e.q_len, dtype=torch.int32)
             mp = getattr(req, "mrope", None)
             if mp is None:
-                cols.append(idx.unsqueeze(0).expand(3, -1))
+                cols.append(idx.unsqueeze(0).expand(axes, -1))
                 continue
             P = mp.shape[1]
             inside = idx.clamp(max=max(P - 1, 0)).long()
-            cols.append(torch.where(idx.unsqueeze(0) < P, mp[:, inside], (idx + req.mrope_delta).unsqueeze(0).expand(3, -1)))
+            cols.append(torch.where(idx.unsqueeze(0) < P, mp[:, inside], (idx + req.mrope_delta).unsqueeze(0).expand(axes, -1)))
         meta.mrope_positions = torch.cat(cols, dim=1).to(self.runner.device)
 
     def _sample_rows(self, plan):

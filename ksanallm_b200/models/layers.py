@@ -92,6 +92,10 @@ class Attention:
         self.use_rope = True
         if cfg.rope_layers and layer_idx < len(cfg.rope_layers) and not cfg.rope_layers[layer_idx]:
             self.rope_cache, self.use_rope = None, False  # a layer without position encoding (Llama 4)
+        if cfg.attention_chunk_size and self.use_rope and not self.window:
+            # Llama 4 chunked attention on the RoPE layers: a query sees the keys of its own block of
+            # `attention_chunk_size` positions only; passed down as a negative window
+            self.window = -cfg.attention_chunk_size
         self.norm_after_rope = cfg.qk_norm_after_rope
         if cfg.qk_l2_norm and self.use_rope:
             # weightless RMS normalisation after RoPE: the ordinary path with unit weights
@@ -100,6 +104,12 @@ class Attention:
             self.q_norm = self.k_norm = ones
             self.norm_after_rope = True
         self.scale = 1.0 / math.sqrt(self.d)
+        # cross-layer attention (Hunyuan-Large): of every `cla_share_factor` layers only the first projects K and V,
+        # the others project queries and attend over that layer's K / V projections (their own norm weights and
+        # their own cache pages still apply). Reference: modules/attention/cross_layer_attention.cpp:51-90.
+        f = cfg.cla_share_factor
+        self.cla_owner = bool(f) and layer_idx % f == 0
+        self.cla_follower = bool(f) and layer_idx % f != 0
         self.k_scale = self.v_scale = 1.0  # fp8 KV cache scaling factors (models/kv_scales.py)
         self.alibi = None
         if cfg.position_encoding == "alibi":
@@ -111,8 +121,14 @@ class Attention:
         qkv = self.qkv(h)
         nq, nk = self.h * self.d, self.hk * self.d
         q = qkv[:, :nq].view(T, self.h, self.d)
-        k = qkv[:, nq:nq + nk].view(T, self.hk, self.d)
-        v = qkv[:, nq + nk:].view(T, self.hk, self.d)
+        if self.cla_follower:
+            k, v = meta._cla_kv
+            k = k.clone()  # RoPE / QK-norm below work in place and every follower applies its own
+        else:
+            k = qkv[:, nq:nq + nk].view(T, self.hk, self.d)
+            v = qkv[:, nq + nk:].view(T, self.hk, self.d)
+            if self.cla_owner:
+                meta._cla_kv = (k.clone(), v)
         positions, table = meta.positions, self.rope_cache
         sections = self.cfg.rope_scaling.mrope_section
         if sections and table is not None and getattr(meta, "mrope_positions", None) is not None:

@@ -145,8 +145,9 @@ def synthetic_checkpoint(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dev
             yield a + ".o_proj.weight", rnd(H, cfg.num_heads * cfg.v_head_dim)
         else:
             yield a + ".q_proj.weight", rnd(cfg.num_heads * d, H)
-            yield a + ".k_proj.weight", rnd(cfg.num_kv_heads * d, H)
-            yield a + ".v_proj.weight", rnd(cfg.num_kv_heads * d, H)
+            if not (cfg.cla_share_factor and i % cfg.cla_share_factor):
+                yield a + ".k_proj.weight", rnd(cfg.num_kv_heads * d, H)
+                yield a + ".v_proj.weight", rnd(cfg.num_kv_heads * d, H)
             if cfg.qkv_bias:
                 yield a + ".q_proj.bias", rnd(cfg.num_heads * d)
                 yield a + ".k_proj.bias", rnd(cfg.num_kv_heads * d)
@@ -573,6 +574,15 @@ class WeightLoader:
         d, hq, hk = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
         for suffix in ("weight", "bias", "weight_scale_inv"):
             q = k = v = None
+            if f"q_proj.{suffix}" in p and f"k_proj.{suffix}" not in p and cfg.cla_share_factor:
+                # cross-layer attention: this layer projects queries only and reuses the K/V projections of the
+                # preceding layer that owns them (reference: modules/attention/cross_layer_attention.cpp:16-24)
+                fused = _rows(p[f"q_proj.{suffix}"], r, n)
+                if suffix == "bias":
+                    self._put(f"{key}.query_key_value.bias", fused)
+                elif suffix == "weight":
+                    self._put_linear(f"{key}.query_key_value", fused)
+                continue
             if f"q_proj.{suffix}" in p:
                 q, k, v = p[f"q_proj.{suffix}"], p[f"k_proj.{suffix}"], p[f"v_proj.{suffix}"]
             elif f"wpack.{suffix}" in p:  # [q | k | v] stacked rows (Baichuan W_pack, ChatGLM)

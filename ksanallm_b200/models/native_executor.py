@@ -57,7 +57,7 @@ class DenseExecutor:
         if (cfg.use_mla or cfg.norm_type != "rmsnorm" or cfg.residual_scale != 1.0 or cfg.head_dim != 128 or
                 cfg.position_encoding not in ("rope", "none") or not cfg.gated_mlp or
                 cfg.hidden_act not in ("silu", "swish") or cfg.sliding_window or
-                cfg.qk_norm_after_rope or cfg.qk_l2_norm or cfg.rope_layers or cfg.attn_temperature_tuning):
+                cfg.qk_norm_after_rope or cfg.qk_l2_norm or cfg.cla_share_factor or cfg.rope_layers or cfg.attn_temperature_tuning):
             return False
         for layer in model.layers:
             if layer.is_moe or not hasattr(layer.attn, "qkv"):

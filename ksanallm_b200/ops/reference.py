@@ -259,7 +259,8 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch
     """Causal attention of each sequence's new tokens over its whole paged context.
 
     q: [T, h, d]; the new tokens of sequence b are rows cu_q[b]:cu_q[b+1] and occupy context
-    positions kv_lens[b]-q_len .. kv_lens[b]-1 (their K/V are already in the cache)."""
+    positions kv_lens[b]-q_len .. kv_lens[b]-1 (their K/V are already in the cache). ``window`` > 0: sliding window
+    of that many keys; ``window`` < 0: chunked attention over blocks of ``-window`` positions (Llama 4)."""
     T, h, d = q.shape
     nb, _, hk, bs, dv = kv_cache.shape
     out = torch.empty(T, h, dv, dtype=q.dtype, device=q.device)
@@ -286,6 +287,8 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch
         mask = kpos > qpos
         if window > 0:
             mask = mask | (kpos <= qpos - window)
+        elif window < 0:  # chunked attention: keys of the query's own block of -window positions
+            mask = mask | (kpos < (qpos // -window) * -window)
         if alibi_slopes is not None:
             s = s + alibi_slopes.float().view(h, 1, 1) * (kpos - qpos).float().unsqueeze(0)
         s = s.masked_fill(mask.unsqueeze(0), float("-inf"))
@@ -501,17 +504,20 @@ def build_rope_cache(rotary_dim: int, max_pos: int, theta: float, scaling=None, 
 
 
 def mrope_rows(cos_sin: torch.Tensor, positions3: torch.Tensor, sections) -> torch.Tensor:
-    """Multimodal RoPE (Qwen2-VL): frequency indices [0, s0) rotate by the temporal position, [s0, s0 + s1) by the
-    height position, the rest by the width position. cos_sin: [max_pos, rd] = [cos | sin]; positions3: [3, T].
-    Returns a per-token table [T, rd] to be indexed with positions 0..T-1 by the ordinary RoPE code."""
+    """Multi-axis RoPE. Qwen2-VL (M-RoPE, 3 axes): frequency indices [0, s0) rotate by the temporal position,
+    [s0, s0 + s1) by the height position, the rest by the width position. Arc-Hunyuan-Video (XD-RoPE, 4 axes): the
+    same with one more axis in front. cos_sin: [max_pos, rd] = [cos | sin]; positions3: [axes, T]. Returns a
+    per-token table [T, rd] to be indexed with positions 0..T-1 by the ordinary RoPE code. Reference:
+    rotary_embedding.cu:150-235 (section lookup per rotary offset)."""
     rd = cos_sin.shape[1]
     half = rd // 2
-    assert sum(sections) == half, "mrope_section must cover half of the rotary dimension"
+    assert sum(sections) == half, "the rope sections must cover half of the rotary dimension"
     p = positions3.long()
-    rows = [cos_sin[p[i]] for i in range(3)]  # each [T, rd]
+    axes = p.shape[0]
+    rows = [cos_sin[p[i]] for i in range(axes)]  # each [T, rd]
     cos_parts, sin_parts, lo = [], [], 0
     for i, sec in enumerate(sections):
-        src = rows[i % 3]
+        src = rows[i % axes]
         cos_parts.append(src[:, lo:lo + sec])
         sin_parts.append(src[:, half + lo:half + lo + sec])
         lo += sec

@@ -64,6 +64,9 @@ CASES = {
     "llama4": ("Llama4TextConfig", "Llama4ForCausalLM", dict(
         L4, num_hidden_layers=4, num_experts_per_tok=1, interleave_moe_layer_step=2, use_qk_norm=True,
         attn_temperature_tuning=True, floor_scale=4, attn_scale=0.3, no_rope_layers=[1, 1, 1, 0])),
+    "llama4_chunked_attention": ("Llama4TextConfig", "Llama4ForCausalLM", dict(
+        L4, num_hidden_layers=4, num_experts_per_tok=1, interleave_moe_layer_step=2, use_qk_norm=True,
+        attn_temperature_tuning=False, no_rope_layers=[1, 1, 1, 0], attention_chunk_size=4)),
     "llama4_top2": ("Llama4TextConfig", "Llama4ForCausalLM", dict(
         L4, num_hidden_layers=2, num_experts_per_tok=2, interleave_moe_layer_step=1, use_qk_norm=False,
         attn_temperature_tuning=False)),

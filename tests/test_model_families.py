@@ -128,3 +128,64 @@ def test_minicpm_scaling_factors():
     h = _hidden(cfg, sd)
     plain = _hidden(model_config_from_dict(dict(BASE, model_type="llama")), sd)
     assert not torch.allclose(h, plain)
+
+
+def test_cross_layer_attention_shares_kv_projections():
+    """Hunyuan-Large style CLA: with a share factor of 2 the odd layers have no K / V projections."""
+    import dataclasses
+    from ksanallm_b200.config.model_config import tiny_llama_config
+    from ksanallm_b200.config.schema import parse_serving_config
+    from ksanallm_b200.engine.llm_engine import LLMEngine
+    from ksanallm_b200.engine.sampling_params import SamplingParams
+    from test_tiny_llama_oracle import plain_forward_all
+    parsed = model_config_from_dict(dict(BASE, model_type="hunyuan_v1_dense", use_cla=True, cla_share_factor=2))
+    assert parsed.cla_share_factor == 2
+    cfg = dataclasses.replace(tiny_llama_config(), num_layers=4, cla_share_factor=2)
+    sd = dict(synthetic_checkpoint(cfg, seed=5, std=0.02, dtype=torch.float32))
+    assert "model.layers.1.self_attn.k_proj.weight" not in sd and "model.layers.2.self_attn.k_proj.weight" in sd
+    model = TransformerModel(cfg, WeightLoader(cfg, dtype=torch.float32).load(sd.items()))
+    serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 64,
+                                                                     "max_token_len": 128, "split_fuse_token_num": 16},
+                                                "block_manager": {"block_token_num": 16}}})
+    eng = LLMEngine(model, serving, num_blocks=32, num_host_blocks=0)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(3, 31000, (n,), generator=g).tolist() for n in (9, 37)]
+    reqs = eng.generate(prompts, SamplingParams(topk=1, max_new_tokens=8, ignore_eos=True))
+    for prompt, req in zip(prompts, reqs):
+        toks = list(prompt)
+        for _ in range(8):
+            toks.append(int(plain_forward_all(sd, cfg, toks, cla=2)[-1].argmax()))
+        assert req.output_token_ids[0] == toks[len(prompt):]
+
+
+def test_xd_rope_four_axes():
+    """Arc-Hunyuan-Video XD-RoPE: four position axes over quarter sections of the alpha-scaled NTK table."""
+    from ksanallm_b200.ops import reference as ref
+    cfg = model_config_from_dict(dict(BASE, model_type="hunyuan_v1_dense", use_qk_norm=False,
+                                      rope_scaling={"type": "dynamic", "alpha": 1000.0, "factor": 1.0},
+                                      xdrope_section=[0.25, 0.25, 0.25, 0.25]))
+    assert cfg.rope_scaling.mrope_section == [4, 4, 4, 4] and cfg.rope_scaling.alpha == 1000.0
+    rd, T = cfg.head_dim, 9
+    table = ref.build_rope_cache(rd, 64, cfg.rope_theta, cfg.rope_scaling)
+    pos4 = torch.tensor([[0, 1, 2, 3, 3, 3, 3, 4, 5], [0, 1, 2, 0, 0, 0, 0, 4, 5],
+                         [0, 1, 2, 3, 3, 4, 4, 4, 5], [0, 1, 2, 3, 4, 3, 4, 4, 5]])
+    rows = ref.mrope_rows(table, pos4, cfg.rope_scaling.mrope_section)
+    base = cfg.rope_theta * 1000.0 ** (rd / (rd - 2))
+    inv = 1.0 / base ** (torch.arange(rd // 2, dtype=torch.float64) * 2 / rd)
+    axis = torch.arange(rd // 2) // 4
+    ang = pos4[axis].t().double() * inv  # [T, rd / 2]
+    assert torch.allclose(rows, torch.cat((ang.cos(), ang.sin()), -1).float(), atol=1e-6)
+    # identical positions on all four axes are ordinary RoPE
+    sd = list(synthetic_checkpoint(cfg, seed=3, dtype=torch.float32))
+    model = TransformerModel(cfg, WeightLoader(cfg, dtype=torch.float32).load(sd), max_positions=64)
+    ids, p = list(range(5, 5 + T)), list(range(T))
+    outs = []
+    for with_axes in (False, True):
+        meta = make_step_input(ids, p, p, [0, T], [T], [[0, 1]], device="cpu")
+        if with_axes:
+            meta.mrope_positions = torch.tensor([p] * 4)
+        outs.append(model.forward(meta, model.allocate_kv_cache(2, 16)))
+    assert torch.allclose(outs[0], outs[1], atol=1e-6)
+    meta = make_step_input(ids, p, p, [0, T], [T], [[0, 1]], device="cpu")
+    meta.mrope_positions = pos4
+    assert not torch.allclose(model.forward(meta, model.allocate_kv_cache(2, 16)), outs[0], atol=1e-4)

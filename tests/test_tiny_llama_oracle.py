@@ -17,8 +17,9 @@ def plain_forward(sd, cfg, tokens):
     return plain_forward_all(sd, cfg, tokens)[-1]
 
 
-def plain_forward_all(sd, cfg, tokens):
-    """Dense causal forward with HF-named weights; returns the logits of every position."""
+def plain_forward_all(sd, cfg, tokens, cla=0):
+    """Dense causal forward with HF-named weights; returns the logits of every position. ``cla``: cross-layer
+    attention, layers with ``i % cla != 0`` attend over the K / V projections of the last layer that has them."""
     H, nh, d = cfg.hidden_size, cfg.num_heads, cfg.head_dim
     x = sd["model.embed_tokens.weight"][tokens]
     T = len(tokens)
@@ -38,9 +39,10 @@ def plain_forward_all(sd, cfg, tokens):
         p = f"model.layers.{i}."
         h = norm(x, sd[p + "input_layernorm.weight"])
         q = (h @ sd[p + "self_attn.q_proj.weight"].t()).view(T, nh, d)
-        k = (h @ sd[p + "self_attn.k_proj.weight"].t()).view(T, nh, d)
-        v = (h @ sd[p + "self_attn.v_proj.weight"].t()).view(T, nh, d)
-        q, k = rope(q), rope(k)
+        if not (cla and i % cla):
+            k_raw = (h @ sd[p + "self_attn.k_proj.weight"].t()).view(T, nh, d)
+            v = (h @ sd[p + "self_attn.v_proj.weight"].t()).view(T, nh, d)
+        q, k = rope(q), rope(k_raw)
         s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(d)
         s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
         a = torch.einsum("hqk,khd->qhd", s.softmax(-1), v).reshape(T, H)
