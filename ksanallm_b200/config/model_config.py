@@ -109,6 +109,11 @@ class ModelConfig:
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
     # MTP
+    # sparse attention indexer (DeepSeek-V3.2, GLM DSA): every query keeps the index_topk best-scoring keys
+    mla_norm_eps: float = 0.0  # epsilon of the low-rank q / kv norms when it differs from rms_norm_eps (0: same)
+    index_topk: int = 0
+    index_n_heads: int = 0
+    index_head_dim: int = 0
     num_nextn_predict_layers: int = 0
     num_register_token: int = 0  # parallel token prediction: register tokens appended per step (0 = off)
     reg_token_id: int = 0
@@ -307,7 +312,7 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
             m.shared_expert_intermediate_size = m.moe_intermediate_size * m.num_shared_experts
         m.first_k_dense_replace = int(g("first_k_dense_replace", 0) or 0)
         m.moe_layer_freq = int(g("moe_layer_freq", g("decoder_sparse_step", 1)) or 1)
-        v3_like = mt in ("deepseek_v3", "deepseek_v32", "kimi_k2")  # sigmoid routing even when the field is absent
+        v3_like = mt in ("deepseek_v3", "deepseek_v32", "kimi_k2", "glm_moe_dsa")  # sigmoid routing even when the field is absent
         m.scoring_func = str(g("scoring_func", "sigmoid" if v3_like else "softmax"))
         m.n_group = int(g("n_group", 1) or 1)
         m.topk_group = int(g("topk_group", 1) or 1)
@@ -322,6 +327,10 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
             ml = g("moe_layers", None)
             step = int(g("interleave_moe_layer_step", 1) or 1)
             m.moe_layers = [int(x) for x in ml] if ml is not None else list(range(step - 1, m.num_layers, step))
+        mlt = g("mlp_layer_types", None)
+        if mlt:  # explicit per-layer list of "dense" / "sparse" (GLM MoE)
+            m.moe_layers = [i for i, t in enumerate(mlt) if str(t) == "sparse"]
+            m.first_k_dense_replace = 0
         if mt.startswith("hunyuan"):
             tk = g("moe_topk", m.num_experts_per_tok)
             m.num_experts_per_tok = int(tk[0] if isinstance(tk, (list, tuple)) else tk)
@@ -342,7 +351,13 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
         m.qk_rope_head_dim = int(g("qk_rope_head_dim", 64))
         m.v_head_dim = int(g("v_head_dim", 128))
         m.num_kv_heads = 1
-        m.rope_interleaved = bool(g("rope_interleave", True))
+        m.rope_interleaved = bool(g("rope_interleave", mt != "glm_moe_dsa"))
+        if mt == "glm_moe_dsa":
+            m.mla_norm_eps = 1e-6  # the transformers implementation keeps the default there
+        if g("index_topk", None) and (mt in ("deepseek_v32", "glm_moe_dsa") or g("index_n_heads", None)):
+            m.index_topk = int(g("index_topk"))
+            m.index_n_heads = int(g("index_n_heads", 64))
+            m.index_head_dim = int(g("index_head_dim", 128))
     m.num_nextn_predict_layers = int(g("num_nextn_predict_layers", 0) or 0)
     m.num_register_token = int(g("num_register_token", 0) or 0)  # reference: models/common/common_config.h:36-37
     m.reg_token_id = int(g("reg_token_id", 0) or 0)

@@ -172,10 +172,33 @@ class MLAttention:
         if rs.type == "yarn" and rs.mscale_all_dim:
             m = ref.yarn_mscale(rs.factor, rs.mscale_all_dim)
             self.scale *= m * m
+        # sparse attention (DeepSeek-V3.2 / GLM DSA): a light multi-head scorer with its own key per token picks the
+        # index_topk keys each query attends to. Reference: modules/attention (SparseMlaIndexer), DSA kernels in
+        # 3rdparty/LLM_kernels; the scoring rule is score[q, t] = sum_h w[q, h] * relu(q_idx[q, h] . k_idx[t]).
+        self.index_topk = cfg.index_topk if (cfg.index_topk and prefix + ".indexer.wq_b.weight" in w) else 0
+        if self.index_topk:
+            assert self.q_lora, "the sparse-attention indexer reads the low-rank query"
+            ip = prefix + ".indexer"
+            self.idx_wq, self.idx_wk = w[ip + ".wq_b.weight"], w[ip + ".wk.weight"]
+            self.idx_kn_w, self.idx_kn_b = w[ip + ".k_norm.weight"], w[ip + ".k_norm.bias"]
+            self.idx_wproj = w[ip + ".weights_proj.weight"]
+            self.idx_h, self.idx_d = cfg.index_n_heads, cfg.index_head_dim
+
+    def _indexer(self, h: torch.Tensor, q_a: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
+        """Indexer queries [T, Hi, Di], per-head weights [T, Hi] (scales folded in) and keys [T, Di]. The first
+        qk_rope_head_dim entries of every indexer head are rotated (half-split layout)."""
+        T = h.shape[0]
+        q = (q_a @ self.idx_wq.t().to(q_a.dtype)).view(T, self.idx_h, self.idx_d)
+        q = ref.apply_rope(q, cos, sin, False, self.dr)
+        k = torch.nn.functional.layer_norm((h @ self.idx_wk.t().to(h.dtype)).float(), (self.idx_d,),
+                                           self.idx_kn_w.float(), self.idx_kn_b.float(), 1e-6).to(h.dtype)
+        k = ref.apply_rope(k.view(T, 1, self.idx_d), cos, sin, False, self.dr).view(T, self.idx_d)
+        wts = (h @ self.idx_wproj.t().to(h.dtype)).float() * (self.idx_h ** -0.5) * (self.idx_d ** -0.5)
+        return q, wts, k
 
     def core(self, h: torch.Tensor, meta, cache: torch.Tensor) -> torch.Tensor:
         T = h.shape[0]
-        eps = self.cfg.rms_norm_eps
+        eps = self.cfg.mla_norm_eps or self.cfg.rms_norm_eps
         a = self.fused_a(h)
         if self.q_lora:
             q_a = ops.rms_norm(a[:, :self.q_lora].contiguous(), self.q_a_norm, eps)
@@ -192,9 +215,16 @@ class MLAttention:
         cos, sin = cs[:, :self.dr // 2], cs[:, self.dr // 2:]
         q_rope = ref.apply_rope(q_rope, cos, sin, self.cfg.rope_interleaved, self.dr)
         k_rope = ref.apply_rope(k_rope.view(T, 1, self.dr), cos, sin, self.cfg.rope_interleaved, self.dr).view(T, self.dr)
-        ops.mla_cache_append(latent, k_rope, meta.slot_mapping, cache)
         q_lat = torch.einsum("thd,hdr->thr", q_nope.to(self.w_uk.dtype), self.w_uk)
-        o_lat = ops.mla_paged_attention(q_lat.contiguous(), q_rope, cache, meta, self.scale)
+        if self.index_topk:
+            iq, iw, ik = self._indexer(h, q_a, cos, sin)
+            flat = cache.view(-1, cache.shape[-1])
+            flat[meta.slot_mapping.long()] = torch.cat((latent, k_rope, ik), -1).to(cache.dtype)
+            o_lat = ref.mla_sparse_paged_attention(q_lat, q_rope, iq, iw, cache, meta.block_tables, meta.cu_q,
+                                                   meta.kv_lens, self.scale, self.r + self.dr, self.index_topk)
+        else:
+            ops.mla_cache_append(latent, k_rope, meta.slot_mapping, cache)
+            o_lat = ops.mla_paged_attention(q_lat.contiguous(), q_rope, cache, meta, self.scale)
         o = torch.einsum("thr,hrd->thd", o_lat.to(self.w_uv.dtype), self.w_uv)
         return o.reshape(T, self.h * self.dv)
 

@@ -141,6 +141,12 @@ def synthetic_checkpoint(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dev
                 yield a + ".q_proj.weight", rnd(cfg.num_heads * cfg.q_head_dim, H)
             yield a + ".kv_a_proj_with_mqa.weight", rnd(cfg.kv_lora_rank + cfg.qk_rope_head_dim, H)
             yield a + ".kv_a_layernorm.weight", ones(cfg.kv_lora_rank)
+            if cfg.index_topk:
+                yield a + ".indexer.wq_b.weight", rnd(cfg.index_n_heads * cfg.index_head_dim, cfg.q_lora_rank)
+                yield a + ".indexer.wk.weight", rnd(cfg.index_head_dim, H)
+                yield a + ".indexer.k_norm.weight", ones(cfg.index_head_dim)
+                yield a + ".indexer.k_norm.bias", rnd(cfg.index_head_dim)
+                yield a + ".indexer.weights_proj.weight", rnd(cfg.index_n_heads, H)
             yield a + ".kv_b_proj.weight", rnd(cfg.num_heads * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank)
             yield a + ".o_proj.weight", rnd(H, cfg.num_heads * cfg.v_head_dim)
         else:
@@ -411,6 +417,20 @@ class WeightLoader:
         if name.startswith("model.norm.") or "layernorm" in name or name.endswith("norm.weight") \
                 or name.endswith("norm.bias") or ".enorm." in name or ".hnorm." in name:
             self._put(name, t)
+            return
+        if ".self_attn.indexer." in name:
+            # sparse-attention indexer (DeepSeek-V3.2 / GLM DSA): small replicated projections; block-scaled fp8
+            # tensors are dequantised once their scale has arrived
+            stem, part = name.rsplit(".", 1)
+            if part == "weight_scale_inv" or self._fp8(t):
+                got = self._qparts["indexer:" + stem]
+                got[part] = t
+                if {"weight", "weight_scale_inv"} <= set(got):
+                    del self._qparts["indexer:" + stem]
+                    self._put(stem + ".weight", ref.dequant_fp8_block_weight(
+                        got["weight"].to(self.device), got["weight_scale_inv"].to(self.device)).to(self.dtype))
+            else:
+                self._put(name, t)
             return
         m = re.match(r"(model\.layers\.\d+)\.(self_attn|mlp)\.(.*)$", name)
         if not m:

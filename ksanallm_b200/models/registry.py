@@ -30,13 +30,14 @@ FAMILIES: Dict[str, str] = {
     "hunyuan": "MoE with shared MLP, QK norm, cross-layer attention sharing",
     "mixtral": "softmax top-2 MoE (w1 / w2 / w3 expert names)",
     "deepseek_v2": "MLA + group-limited softmax routing + shared experts",
-    "deepseek_v3": "MLA + sigmoid routing with correction bias, 8 groups / top-4, MTP layer, fp8 block weights",
+    "deepseek_v3": "MLA + sigmoid routing with correction bias, 8 groups / top-4, MTP layer, fp8 block weights; "
+                   "V3.2 / GLM DSA: sparse attention over the keys picked by the indexer",
     "kimi_k2": "deepseek_v3 architecture with 384 experts",
     "minicpm": "embedding / residual / logit scaling; reranker head",
 }
 
 _ALIASES = {"fairseq-transformer": "gpt2", "fairseq_transformer": "gpt2", "openai-gpt": "gpt2", "gpt": "gpt2",
-            "deepseek_v32": "deepseek_v3", "qwen2_5_vl": "qwen2_vl", "arc_hunyuan_video": "hunyuan",
+            "deepseek_v32": "deepseek_v3", "glm_moe_dsa": "deepseek_v3", "qwen2_5_vl": "qwen2_vl", "arc_hunyuan_video": "hunyuan",
             "hunyuan_turbo": "hunyuan", "hunyuan_large": "hunyuan", "minicpm3": "minicpm", "mistral": "llama",
             "yi": "llama", "vicuna": "llama", "internlm": "llama"}
 

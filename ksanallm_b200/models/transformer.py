@@ -119,7 +119,7 @@ class TransformerModel:
         cfg = self.cfg
         esz = torch.empty(0, dtype=kv_dtype or self.dtype).element_size()
         if cfg.use_mla:
-            per_layer = block_size * (cfg.kv_lora_rank + cfg.qk_rope_head_dim) * esz
+            per_layer = block_size * (cfg.kv_lora_rank + cfg.qk_rope_head_dim + cfg.index_head_dim * bool(cfg.index_topk)) * esz
         else:
             hk = max(cfg.num_kv_heads // self.tp.size, 1)
             per_layer = 2 * hk * block_size * cfg.head_dim * esz
@@ -131,8 +131,9 @@ class TransformerModel:
         caches = []
         for _ in range(self.num_cache_layers):
             if cfg.use_mla:
-                c = torch.zeros(num_blocks, block_size, cfg.kv_lora_rank + cfg.qk_rope_head_dim, dtype=dt,
-                                device=self.device)
+                # with a sparse-attention indexer every cache row also carries the token's indexer key
+                width = cfg.kv_lora_rank + cfg.qk_rope_head_dim + (cfg.index_head_dim if cfg.index_topk else 0)
+                c = torch.zeros(num_blocks, block_size, width, dtype=dt, device=self.device)
             else:
                 hk = max(cfg.num_kv_heads // self.tp.size, 1)
                 c = torch.zeros(num_blocks, 2, hk, block_size, cfg.head_dim, dtype=dt, device=self.device)

@@ -331,6 +331,43 @@ def mla_paged_attention(q_latent: torch.Tensor, q_rope: torch.Tensor, cache: tor
     return out
 
 
+def mla_sparse_paged_attention(q_latent: torch.Tensor, q_rope: torch.Tensor, idx_q: torch.Tensor, idx_w: torch.Tensor,
+                               cache: torch.Tensor, block_tables: torch.Tensor, cu_q: torch.Tensor,
+                               kv_lens: torch.Tensor, scale: float, main_width: int, topk: int) -> torch.Tensor:
+    """Absorbed MLA attention restricted to the keys an indexer selects (DeepSeek sparse attention).
+
+    Cache rows are [latent | k_rope | indexer key]; ``main_width`` = r + dr. idx_q: [T, Hi, Di], idx_w: [T, Hi].
+    index score[q, t] = sum_h idx_w[q, h] * relu(idx_q[q, h] . k_idx[t]) over the causally visible keys; each query
+    attends to its ``topk`` best keys (all of them while the context is shorter than topk)."""
+    T, h, r = q_latent.shape
+    bs = cache.shape[1]
+    out = torch.empty(T, h, r, dtype=q_latent.dtype, device=q_latent.device)
+    cu, kl = cu_q.tolist(), kv_lens.tolist()
+    qcat = torch.cat((q_latent, q_rope), dim=-1).float()
+    for b in range(len(kl)):
+        qs, qe = cu[b], cu[b + 1]
+        ql, L = qe - qs, kl[b]
+        if ql == 0:
+            continue
+        nblk = (L + bs - 1) // bs
+        rows = cache[block_tables[b, :nblk].long()].reshape(nblk * bs, -1)[:L].float()
+        c, kidx = rows[:, :main_width], rows[:, main_width:]
+        qpos = torch.arange(L - ql, L, device=rows.device).unsqueeze(1)
+        kpos = torch.arange(L, device=rows.device).unsqueeze(0)
+        hidden = kpos > qpos
+        isc = torch.einsum("qhd,kd->qhk", idx_q[qs:qe].float(), kidx).relu()
+        isc = torch.einsum("qhk,qh->qk", isc, idx_w[qs:qe].float()).masked_fill(hidden, float("-inf"))
+        if L > topk:
+            keep = torch.zeros(ql, L, dtype=torch.bool, device=rows.device)
+            keep.scatter_(1, isc.topk(topk, dim=-1).indices, True)
+            hidden = hidden | ~keep
+        s = torch.einsum("qhd,kd->hqk", qcat[qs:qe], c) * scale
+        s = s.masked_fill(hidden.unsqueeze(0), float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        out[qs:qe] = torch.einsum("hqk,kd->qhd", p, c[:, :r]).to(out.dtype)
+    return out
+
+
 # ---- MoE ------------------------------------------------------------------------------------------
 
 def moe_route(logits: torch.Tensor, top_k: int, scoring: str = "softmax", norm_topk: bool = False,

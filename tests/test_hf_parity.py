@@ -64,6 +64,8 @@ CASES = {
     "llama4": ("Llama4TextConfig", "Llama4ForCausalLM", dict(
         L4, num_hidden_layers=4, num_experts_per_tok=1, interleave_moe_layer_step=2, use_qk_norm=True,
         attn_temperature_tuning=True, floor_scale=4, attn_scale=0.3, no_rope_layers=[1, 1, 1, 0])),
+    "glm_moe_dsa_sparse_attention": ("GlmMoeDsaConfig", "GlmMoeDsaForCausalLM", dict(
+        DS, mlp_layer_types=["dense", "sparse"], index_topk=4, index_head_dim=16, index_n_heads=4)),
     "llama4_chunked_attention": ("Llama4TextConfig", "Llama4ForCausalLM", dict(
         L4, num_hidden_layers=4, num_experts_per_tok=1, interleave_moe_layer_step=2, use_qk_norm=True,
         attn_temperature_tuning=False, no_rope_layers=[1, 1, 1, 0], attention_chunk_size=4)),
@@ -79,6 +81,10 @@ def test_logits_match_transformers(name):
     if not hasattr(transformers, cfg_cls) or not hasattr(transformers, model_cls):
         pytest.skip(f"transformers {transformers.__version__} has no {model_cls}")
     cfg = getattr(transformers, cfg_cls)(**kw)
+    if name.startswith("glm_moe_dsa"):
+        # with the fused-kernel attention back-ends this transformers model receives no materialised causal mask and
+        # its indexer mask alone would let queries see later keys; the eager path carries the causal mask explicitly
+        cfg._attn_implementation = "eager"
     torch.manual_seed(0)
     hf = getattr(transformers, model_cls)(cfg).eval().float()
     with torch.no_grad():
@@ -98,7 +104,8 @@ def test_logits_match_transformers(name):
     assert (got - want).abs().max().item() < 1e-4
 
 
-@pytest.mark.parametrize("name", ["llama", "deepseek_v3", "qwen3_moe", "mistral_sliding_window"])
+@pytest.mark.parametrize("name", ["llama", "deepseek_v3", "qwen3_moe", "mistral_sliding_window",
+                                  "glm_moe_dsa_sparse_attention"])
 def test_engine_greedy_generation_matches_transformers(name):
     """Continuous batching over the paged cache (prefill + decode steps, several requests at once) against
     ``generate(do_sample=False)`` of the transformers model, request by request."""
@@ -107,6 +114,8 @@ def test_engine_greedy_generation_matches_transformers(name):
     from ksanallm_b200.engine.sampling_params import SamplingParams
     cfg_cls, model_cls, kw = CASES[name]
     cfg = getattr(transformers, cfg_cls)(**kw)
+    if name.startswith("glm_moe_dsa"):
+        cfg._attn_implementation = "eager"  # see test_logits_match_transformers
     torch.manual_seed(1)
     hf = getattr(transformers, model_cls)(cfg).eval().float()
     prompts = [[5, 9, 77, 120, 33, 4, 8], [200, 3, 3, 19, 250, 7, 7, 7, 91, 12, 13, 14, 15, 16, 17, 18, 19, 20], [8, 6]]

@@ -189,3 +189,27 @@ def test_xd_rope_four_axes():
     meta = make_step_input(ids, p, p, [0, T], [T], [[0, 1]], device="cpu")
     meta.mrope_positions = pos4
     assert not torch.allclose(model.forward(meta, model.allocate_kv_cache(2, 16)), outs[0], atol=1e-4)
+
+
+def test_deepseek_v32_config_enables_the_sparse_attention_indexer():
+    cfg = model_config_from_dict(dict(
+        model_type="deepseek_v32", hidden_size=128, num_hidden_layers=2, num_attention_heads=4, vocab_size=300,
+        intermediate_size=256, q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+        n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, first_k_dense_replace=1,
+        index_topk=4, index_n_heads=4, index_head_dim=16, torch_dtype="float32", max_position_embeddings=64))
+    assert (cfg.index_topk, cfg.index_n_heads, cfg.index_head_dim) == (4, 4, 16) and cfg.rope_interleaved
+    sd = list(synthetic_checkpoint(cfg, seed=3, dtype=torch.float32))
+    assert any(k.endswith("indexer.weights_proj.weight") for k, _ in sd)
+    w = WeightLoader(cfg, dtype=torch.float32).load(sd)
+    model = TransformerModel(cfg, w, max_positions=64)
+    assert model.layers[0].attn.index_topk == 4
+    cache = model.allocate_kv_cache(2, 16)
+    assert cache[0].shape[-1] == 32 + 8 + 16  # latent | rope key | indexer key
+    T = 11
+    meta = make_step_input(list(range(5, 5 + T)), list(range(T)), list(range(T)), [0, T], [T], [[0, 1]], device="cpu")
+    sparse = model.forward(meta, cache)
+    for layer in model.layers:
+        layer.attn.index_topk = 64  # every key selected: dense attention through the same code path
+    dense = model.forward(meta, model.allocate_kv_cache(2, 16))
+    assert torch.isfinite(sparse).all() and torch.allclose(sparse[:4], dense[:4], atol=1e-6)  # <= 4 keys: identical
+    assert not torch.allclose(sparse[-1], dense[-1], atol=1e-6)
