@@ -29,6 +29,7 @@ PYBIND11_MODULE(_ksana_host, m) {
   py::class_<CacheStats>(m, "CacheStats")
       .def_readonly("prefix_query_tokens", &CacheStats::prefix_query_tokens)
       .def_readonly("prefix_hit_tokens", &CacheStats::prefix_hit_tokens)
+      .def_readonly("flexible_hit_tokens", &CacheStats::flexible_hit_tokens)
       .def_readonly("evicted_blocks", &CacheStats::evicted_blocks)
       .def_readonly("merged_blocks", &CacheStats::merged_blocks)
       .def_readonly("swapped_out_blocks", &CacheStats::swapped_out_blocks)
@@ -54,6 +55,12 @@ PYBIND11_MODULE(_ksana_host, m) {
              return PairsToArray(c.CommitFilled(seq, tokens, n));
            })
       .def("block_table", &KVCacheManager::BlockTable)
+      .def("flexible_reserve",
+           [](KVCacheManager& c, int64_t seq, const std::vector<int32_t>& tokens, int shared, int min_len) -> py::object {
+             FlexibleRun run;
+             if (!c.FlexibleReserve(seq, tokens, shared, min_len, &run)) return py::none();
+             return py::make_tuple(run.dst_begin, run.src_slots, run.dst_slots, run.src_pos);
+           })
       .def("num_blocks", &KVCacheManager::NumBlocks)
       .def("free_seq", &KVCacheManager::FreeSeq)
       .def("truncate", &KVCacheManager::Truncate)
@@ -91,6 +98,7 @@ PYBIND11_MODULE(_ksana_host, m) {
       .def_readwrite("swapin_block_threshold", &SchedulerConfig::swapin_block_threshold)
       .def_readwrite("max_draft_tokens", &SchedulerConfig::max_draft_tokens)
       .def_readwrite("ptp_mode", &SchedulerConfig::ptp_mode)
+      .def_readwrite("min_flexible_cache_num", &SchedulerConfig::min_flexible_cache_num)
       .def_readwrite("decode_token_threshold", &SchedulerConfig::decode_token_threshold);
 
   py::class_<SchedStats>(m, "SchedStats")
@@ -116,6 +124,12 @@ PYBIND11_MODULE(_ksana_host, m) {
       .def_property_readonly("swap_out", [](const StepPlan& p) { return PairsToArray(p.swap_out); })
       .def_property_readonly("swap_in", [](const StepPlan& p) { return PairsToArray(p.swap_in); })
       .def_property_readonly("block_copies", [](const StepPlan& p) { return PairsToArray(p.block_copies); })
+      .def_property_readonly("flexible",
+                             [](const StepPlan& p) {
+                               py::array_t<int32_t> a({static_cast<py::ssize_t>(p.flexible.size() / 4), py::ssize_t(4)});
+                               std::copy(p.flexible.begin(), p.flexible.end(), a.mutable_data());
+                               return a;
+                             })
       .def_property_readonly("dropped",
                              [](const StepPlan& p) {
                                std::vector<std::pair<int64_t, int>> v;

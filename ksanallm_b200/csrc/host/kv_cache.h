@@ -11,6 +11,7 @@
 //   * swap-out/in is pure bookkeeping here: the caller receives (device, host) copy pairs and
 //     executes them on its copy stream.
 #pragma once
+#include <algorithm>
 #include <cstdint>
 #include <deque>
 #include <list>
@@ -90,6 +91,15 @@ struct CacheStats {
   int64_t merged_blocks = 0;
   int64_t swapped_out_blocks = 0;
   int64_t swapped_in_blocks = 0;
+  int64_t flexible_hit_tokens = 0;
+};
+
+// Result of KVCacheManager::FlexibleReserve: token i of the run has its KV copied from cache slot src_slots[i]
+// (written at position src_pos[i]) to slot dst_slots[i] (position dst_begin + i).
+struct FlexibleRun {
+  int dst_begin = 0;
+  std::vector<int32_t> src_slots, dst_slots, src_pos;
+  int size() const { return static_cast<int>(src_slots.size()); }
 };
 
 class KVCacheManager {
@@ -197,12 +207,79 @@ class KVCacheManager {
         node->active_refs = 1;
         node->last_use = ++tick_;
         parent->children.emplace(node->key, node);
+        by_tokens_.emplace(HashBlock(0, tk), node);
         ++cached_nodes_;
         sb.shared.push_back(node);
       }
       sb.own.erase(sb.own.begin());
     }
     return merged;
+  }
+
+  // Flexible (non-prefix) reuse, the reference's min_flexible_cache_num feature
+  // (cache_manager/prefix_cache_manager.cpp:254-389): after the cached prefix of `shared` tokens, the tokens that
+  // follow may already sit in the tree at OTHER positions (a dialogue whose middle changed length). Looks for the
+  // longest run of cached full blocks whose tokens equal tokens[shared ...] - the run may start inside a block, up
+  // to block_size - 1 tokens late, in which case the tail of that block's parent must match too - and, when it is
+  // at least `min_len` tokens long, reserves the sequence's blocks for it and returns the per-token copy list.
+  // Keys need their rotary phase moved from src_pos to the new position by the caller. At least one token of the
+  // sequence is always left to compute.
+  bool FlexibleReserve(int64_t seq, const std::vector<int32_t>& tokens, int shared, int min_len, FlexibleRun* out) {
+    if (!prefix_ || min_len <= 0 || shared % block_size_ != 0) return false;
+    const int n = static_cast<int>(tokens.size());
+    const int bs = block_size_;
+    std::vector<PrefixNode*> best;
+    int best_len = 0, best_lead = 0;
+    for (int lead = 0; lead < bs; ++lead) {
+      int offset = shared + lead;
+      if (offset + bs >= n) break;
+      auto range = by_tokens_.equal_range(HashBlock(0, tokens.data() + offset));
+      for (auto it = range.first; it != range.second; ++it) {
+        PrefixNode* node = it->second;
+        if (!std::equal(node->tokens.begin(), node->tokens.end(), tokens.begin() + offset)) continue;
+        std::vector<PrefixNode*> chain;
+        if (lead > 0) {
+          PrefixNode* par = node->parent;
+          if (par == nullptr || par == &root_) continue;
+          if (!std::equal(par->tokens.end() - lead, par->tokens.end(), tokens.begin() + shared)) continue;
+          chain.push_back(par);
+        }
+        chain.push_back(node);
+        int hit = bs;
+        PrefixNode* cur = node;
+        while (offset + hit + bs < n) {
+          PrefixNode* nxt = FindChild(cur, tokens.data() + offset + hit);
+          if (!nxt) break;
+          chain.push_back(nxt);
+          cur = nxt;
+          hit += bs;
+        }
+        if (lead + hit >= min_len && lead + hit > best_len) {
+          best = chain;
+          best_len = lead + hit;
+          best_lead = lead;
+        }
+      }
+    }
+    if (best.empty()) return false;
+    for (auto* nd : best) Pin(nd);  // the reservation below must not evict (and hand out) the source blocks
+    bool ok = EnsureCapacity(seq, shared + best_len);
+    for (auto* nd : best) Unpin(nd);
+    if (!ok) return false;
+    std::vector<BlockId> table = BlockTable(seq);
+    int depth = 0;  // position of the first source block
+    for (PrefixNode* a = best.front()->parent; a != nullptr && a != &root_; a = a->parent) ++depth;
+    int src0 = depth * bs + (best_lead > 0 ? bs - best_lead : 0);
+    out->dst_begin = shared;
+    for (int i = 0; i < best_len; ++i) {
+      int sp = src0 + i, dp = shared + i;
+      PrefixNode* nd = best[sp / bs - depth];
+      out->src_pos.push_back(sp);
+      out->src_slots.push_back(nd->block * bs + sp % bs);
+      out->dst_slots.push_back(table[dp / bs] * bs + dp % bs);
+    }
+    stats_.flexible_hit_tokens += best_len;
+    return true;
   }
 
   // Block table in logical order.
@@ -375,10 +452,19 @@ class KVCacheManager {
       dev_.Release(n->block);
       --cached_nodes_;
       ++stats_.evicted_blocks;
+      ForgetTokens(n);
       delete n;
       return true;
     }
     return false;
+  }
+  void ForgetTokens(PrefixNode* n) {
+    auto range = by_tokens_.equal_range(HashBlock(0, n->tokens.data()));
+    for (auto it = range.first; it != range.second; ++it)
+      if (it->second == n) {
+        by_tokens_.erase(it);
+        return;
+      }
   }
   void FreeSubtree(PrefixNode* n) {
     for (auto& kv : n->children) {
@@ -395,6 +481,7 @@ class KVCacheManager {
   PrefixNode root_;
   std::unordered_map<int64_t, SeqBlocks> seqs_;
   std::set<std::pair<uint64_t, PrefixNode*>> lru_;
+  std::unordered_multimap<uint64_t, PrefixNode*> by_tokens_;  // hash of a block's own tokens -> nodes (any depth)
   int evictable_ = 0;
   int cached_nodes_ = 0;
   uint64_t tick_ = 0;

@@ -70,6 +70,9 @@ struct SchedulerConfig {
   // registers' own KV entries are dropped. The reference: runtime/draft_generator/ptp_generator.cpp,
   // runtime/ptp_generation_controller.cpp.
   bool ptp_mode = false;
+  // Non-prefix cache reuse: a run of at least this many tokens found elsewhere in the prefix tree is copied (keys
+  // re-rotated) instead of being computed; 0 turns the search off (reference: min_flexible_cache_num).
+  int min_flexible_cache_num = 0;
   int decode_token_threshold = 1;  // q_len <= threshold with cached KV counts as a decode entry
 };
 
@@ -115,6 +118,9 @@ struct StepPlan {
   std::vector<CopyPair> swap_out;       // device -> host
   std::vector<CopyPair> swap_in;        // host -> device
   std::vector<CopyPair> block_copies;   // device -> device (fork copy-on-write)
+  // flexible cache reuse, one row per token: (source slot, destination slot, source position, destination position);
+  // executed before every other block operation of the step
+  std::vector<int32_t> flexible;
   std::vector<SeqEvent> dropped;        // timed out / aborted before running
   int num_prefill = 0;
   int num_decode = 0;
@@ -376,6 +382,7 @@ class Scheduler {
       --admit_left;
       int64_t id = waiting_.front();
       Sequence& s = *seqs_.at(id);
+      size_t flex_mark = plan.flexible.size();
       if (!cache_->Has(id)) {
         int hit = cache_->MatchPrefix(s.tokens);
         int remaining = static_cast<int>(s.tokens.size()) - hit;
@@ -394,6 +401,16 @@ class Scheduler {
         if (blocks_needed + headroom > cache_->num_available_blocks() && !running_.empty()) break;
         cache_->CreateSeq(id, s.tokens);
         s.num_computed = cache_->NumBlocks(id) * cfg_.block_size;
+        flex_mark = plan.flexible.size();
+        FlexibleRun run;
+        if (cfg_.min_flexible_cache_num > 0 &&
+            cache_->FlexibleReserve(id, s.tokens, s.num_computed, cfg_.min_flexible_cache_num, &run)) {
+          for (int i = 0; i < run.size(); ++i) {
+            plan.flexible.insert(plan.flexible.end(),
+                                 {run.src_slots[i], run.dst_slots[i], run.src_pos[i], run.dst_begin + i});
+          }
+          s.num_computed += run.size();
+        }
       }
       int remaining = static_cast<int>(s.tokens.size()) - s.num_computed;
       int q_len = remaining;
@@ -408,11 +425,13 @@ class Scheduler {
           if (q_len <= 0 || !cache_->EnsureCapacity(id, s.num_computed + q_len)) {
             cache_->FreeSeq(id);
             s.num_computed = 0;
+            plan.flexible.resize(flex_mark);
             break;
           }
         } else {
           cache_->FreeSeq(id);
           s.num_computed = 0;
+          plan.flexible.resize(flex_mark);
           break;
         }
       }

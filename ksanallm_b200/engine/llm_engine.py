@@ -138,6 +138,7 @@ class LLMEngine:
             self.mtp_steps = self.trie_drafts = 0
         sc.max_draft_tokens = max(self.mtp_steps, self.trie_drafts, self.ptp_steps)
         sc.ptp_mode = self.ptp_steps > 0
+        sc.min_flexible_cache_num = self._flexible_cache_min(bs_cfg, model, kv_dtype)
         sc.decode_token_threshold = 1 + sc.max_draft_tokens
         self.cache = _host.KVCacheManager(num_blocks, num_host_blocks, self.block_size,
                                           bool(bs_cfg.enable_auto_prefix_cache))
@@ -168,6 +169,20 @@ class LLMEngine:
         self._complex_requests = 0  # live requests that need per-token host state (grammar, beams, penalties, ...)
         self.dp = None              # parallel.attn_dp.DPCoordinator under attention data parallelism
         self.dp_any_work = True
+
+    @staticmethod
+    def _flexible_cache_min(bs_cfg, model, kv_dtype) -> int:
+        """setting.batch_scheduler.min_flexible_cache_num when the model's cached keys can be moved to another
+        position by a rotation (or do not depend on the position at all) and the cache keeps the model's own dtype;
+        0 (off) otherwise."""
+        want = int(getattr(bs_cfg, "min_flexible_cache_num", 0) or 0)
+        cfg = model.cfg
+        if want <= 0 or not bs_cfg.enable_auto_prefix_cache:
+            return 0
+        movable = (cfg.position_encoding in ("rope", "alibi") and not cfg.qk_norm_after_rope and not cfg.qk_l2_norm
+                   and not cfg.rope_layers and not cfg.rope_scaling.mrope_section and not cfg.index_topk
+                   and not cfg.cla_share_factor)
+        return want if movable and kv_dtype is None else 0
 
     # ---- sizing ----------------------------------------------------------------------------------------
     def _derive_num_blocks(self, kv_dtype) -> int:
@@ -322,6 +337,7 @@ class LLMEngine:
         if self._has_followers():
             self._broadcast_plan(layout, plan, greedy)
         ta = time.perf_counter()
+        self.runner.apply_flexible(plan.flexible)
         self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
         meta = self.runner.upload(layout)
         self._attach_mrope(plan, meta)
@@ -396,6 +412,7 @@ class LLMEngine:
         if self._has_followers():
             self._broadcast_plan(layout, plan, True, fixup=fix)
         ta = time.perf_counter()
+        self.runner.apply_flexible(plan.flexible)
         self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
         meta = self.runner.upload(layout)
         if fix:
@@ -611,16 +628,17 @@ class LLMEngine:
             h[30] = 1 if greedy else 0
             h[34] = 1 if fixup else 0
             so, si, bc = plan.swap_out, plan.swap_in, plan.block_copies
-            h[31], h[32], h[33] = len(so), len(si), len(bc)
+            fx = np.asarray(plan.flexible, dtype=np.int32).reshape(-1, 2)  # [n, 4] travels as 2n pairs
+            h[31], h[32], h[33], h[35] = len(so), len(si), len(bc), len(fx)
         hdr = torch.from_numpy(h)
         dist.broadcast(hdr, src=0, group=self._ctl)
         if stop:
             return
         n = int(h[18])
         dist.broadcast(self.runner.staging.host[:n], src=0, group=self._ctl)
-        extra = int(h[31] + h[32] + h[33])
+        extra = int(h[31] + h[32] + h[33] + h[35])
         if extra:
-            arr = np.concatenate([np.asarray(a, dtype=np.int32).reshape(-1, 2) for a in (so, si, bc)], 0)
+            arr = np.concatenate([np.asarray(a, dtype=np.int32).reshape(-1, 2) for a in (so, si, bc, fx)], 0)
             dist.broadcast(torch.from_numpy(np.ascontiguousarray(arr)), src=0, group=self._ctl)
 
     def follow(self) -> None:
@@ -638,13 +656,14 @@ class LLMEngine:
             n = layout["total_words"]
             self.runner.staging.flip()  # the previous step's host-to-device copy may still be pending
             dist.broadcast(self.runner.staging.host[:n], src=0, group=self._ctl)
-            nso, nsi, nbc = int(h[31]), int(h[32]), int(h[33])
-            so = si = bc = np.zeros((0, 2), dtype=np.int32)
-            if nso + nsi + nbc:
-                arr = torch.zeros(nso + nsi + nbc, 2, dtype=torch.int32)
+            nso, nsi, nbc, nfx = int(h[31]), int(h[32]), int(h[33]), int(h[35])
+            so = si = bc = fx = np.zeros((0, 2), dtype=np.int32)
+            if nso + nsi + nbc + nfx:
+                arr = torch.zeros(nso + nsi + nbc + nfx, 2, dtype=torch.int32)
                 dist.broadcast(arr, src=0, group=self._ctl)
                 a = arr.numpy()
-                so, si, bc = a[:nso], a[nso:nso + nsi], a[nso + nsi:]
+                so, si, bc, fx = a[:nso], a[nso:nso + nsi], a[nso + nsi:nso + nsi + nbc], a[nso + nsi + nbc:]
+            self.runner.apply_flexible(fx.reshape(-1, 4))
             self.runner.apply_block_ops(so, si, bc)
             meta = self.runner.upload(layout)
             if h[34]:
@@ -725,6 +744,7 @@ class LLMEngine:
         if not greedy:
             raise NotImplementedError("pipeline-parallel serving samples greedily")
         self._broadcast_plan(layout, plan, True)
+        self.runner.apply_flexible(plan.flexible)
         self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
         meta = self.runner.upload(layout)
         self.mbc.ready(mb)

@@ -62,6 +62,44 @@ class ModelRunner:
             for dev in self.kv_caches:
                 dev[dst] = dev[src]
 
+    def apply_flexible(self, rows: np.ndarray) -> None:
+        """Flexible cache reuse: ``rows`` = [n, 4] (source slot, destination slot, source position, destination
+        position). Values are copied; keys are moved from the rotary phase of their old position to the new one,
+        R(dst) = R(dst - src) R(src), with cos / sin of the difference formed from the two table rows (which also
+        cancels a YaRN magnitude factor folded into the table). The reference does this with a reverse-RoPE pass
+        over per-token copy tasks (cache_manager/prefix_cache_manager.cpp:366-388, model_input flexible-cache copy
+        lists)."""
+        if not len(rows):
+            return
+        cfg, model = self.model.cfg, self.model
+        r = torch.from_numpy(np.ascontiguousarray(rows)).long().to(self.device)
+        src, dst, sp, dp = r[:, 0], r[:, 1], r[:, 2], r[:, 3]
+        bs = self.block_size
+        sb, so, db, do = src // bs, src % bs, dst // bs, dst % bs
+        table = model.rope_cache
+        rd = cfg.qk_rope_head_dim if cfg.use_mla else (cfg.rotary_dim or cfg.head_dim)
+        if table is not None:
+            half = rd // 2
+            cs, cd = table[sp].float(), table[dp].float()
+            m2 = (cs[:, :1] ** 2 + cs[:, half:half + 1] ** 2)
+            cos = (cd[:, :half] * cs[:, :half] + cd[:, half:] * cs[:, half:]) / m2
+            sin = (cd[:, half:] * cs[:, :half] - cd[:, :half] * cs[:, half:]) / m2
+        from ..ops import reference as ref
+        for cache in self.kv_caches:
+            if cfg.use_mla:
+                rows_ = cache[sb, so].clone()  # [n, r + dr (+ indexer key)]
+                if table is not None:
+                    lo = cfg.kv_lora_rank
+                    k = rows_[:, lo:lo + rd].float().unsqueeze(1)
+                    rows_[:, lo:lo + rd] = ref.apply_rope(k, cos, sin, cfg.rope_interleaved, rd)[:, 0].to(cache.dtype)
+                cache[db, do] = rows_
+            else:
+                k = cache[sb, 0, :, so].float()  # [n, hk, d]
+                if table is not None:
+                    k = ref.apply_rope(k, cos, sin, cfg.rope_interleaved, rd)
+                cache[db, 0, :, do] = k.to(cache.dtype)
+                cache[db, 1, :, do] = cache[sb, 1, :, so]
+
     # ---- forward ---------------------------------------------------------------------------------------
     def upload(self, layout: Dict[str, int]) -> StepInput:
         meta = self.staging.upload(layout)
