@@ -115,6 +115,7 @@ class ModelConfig:
     index_n_heads: int = 0
     index_head_dim: int = 0
     num_nextn_predict_layers: int = 0
+    reranker_start_layer: int = 0  # layer-wise reranker: depth of the first scoring head lm_head.0.linear_head
     num_register_token: int = 0  # parallel token prediction: register tokens appended per step (0 = off)
     reg_token_id: int = 0
     # quantisation
@@ -359,6 +360,8 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
             m.index_n_heads = int(g("index_n_heads", 64))
             m.index_head_dim = int(g("index_head_dim", 128))
     m.num_nextn_predict_layers = int(g("num_nextn_predict_layers", 0) or 0)
+    if g("start_layer", None) is not None:  # reference: models/bge_reranker_minicpm/bge_reranker_minicpm_config.h:19
+        m.reranker_start_layer = int(g("start_layer"))
     m.num_register_token = int(g("num_register_token", 0) or 0)  # reference: models/common/common_config.h:36-37
     m.reg_token_id = int(g("reg_token_id", 0) or 0)
     m.quant = _quant(g("quantization_config", None))

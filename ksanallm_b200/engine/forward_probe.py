@@ -5,6 +5,11 @@ src/ksana_llm/utils/request.cpp:109-201): each target names ``transformer`` (hid
 ``layernorm`` (after it) or ``logits``; rows are selected with ``slice_pos`` = list of inclusive [l, r] intervals
 (negative = from the end) or ``token_id`` positions; ``token_reduce_mode`` is ``GATHER_ALL`` (whole rows / all vocab
 logits) or ``GATHER_TOKEN_ID`` (logits target only: softmax probability each row assigns to the NEXT input token).
+
+Layer-wise rerankers (bge-reranker-v2-minicpm-layerwise) add the ``lm_head`` target: ``cutoff_layer`` = [n] stops the
+decoder after n layers, the final norm and that depth's one-row scoring head ``lm_head.{n - start_layer}.linear_head``
+follow, and the scores of all rows are returned (reference: models/bge_reranker_minicpm/bge_reranker_minicpm_model.cpp
+:192-217).
 """
 from __future__ import annotations
 
@@ -14,7 +19,7 @@ from typing import Any, Dict, List, Sequence
 import numpy as np
 import torch
 
-VALID_TARGETS = ("transformer", "layernorm", "logits")
+VALID_TARGETS = ("transformer", "layernorm", "logits", "lm_head")
 
 
 def validate_targets(targets: Sequence[Dict[str, Any]], num_tokens: int) -> None:
@@ -25,6 +30,8 @@ def validate_targets(targets: Sequence[Dict[str, Any]], num_tokens: int) -> None
         mode = t.get("token_reduce_mode", "GATHER_ALL")
         if mode not in ("GATHER_ALL", "GATHER_TOKEN_ID"):
             raise ValueError(f"Invalid token_reduce_mode {mode}")
+        if name == "lm_head" and mode != "GATHER_ALL":
+            raise ValueError("the lm_head target returns every row (GATHER_ALL)")
         if mode == "GATHER_TOKEN_ID" and name != "logits":
             raise ValueError("GATHER_TOKEN_ID is only supported for the logits target")
         if t.get("slice_pos") and t.get("token_id"):
@@ -68,12 +75,27 @@ def _encode(t: torch.Tensor) -> Dict[str, Any]:
     return {"data": base64.b64encode(a.tobytes()).decode("ascii"), "shape": list(a.shape), "dtype": "float32"}
 
 
-def run_probe(model, targets, hidden: torch.Tensor, prenorm: torch.Tensor, tokens: Sequence[int]) -> List[Dict[str, Any]]:
-    """hidden: final-norm output rows of this request [n, H]; prenorm: residual stream rows [n, H]."""
+def reranker_scores(model, cutoff_hidden: torch.Tensor, cutoff_layer: int) -> torch.Tensor:
+    """cutoff_hidden: final-norm output after ``cutoff_layer`` decoder layers [n, H] -> scores [n, 1]."""
+    start = int(getattr(model.cfg, "reranker_start_layer", 0) or 0)
+    w = model.w.get(f"lm_head.{cutoff_layer - start}.linear_head.weight")
+    if w is None or cutoff_layer < start:
+        raise ValueError(f"no scoring head for cutoff_layer {cutoff_layer}")
+    return cutoff_hidden.float() @ w.float().t()
+
+
+def run_probe(model, targets, hidden: torch.Tensor, prenorm: torch.Tensor, tokens: Sequence[int],
+              cutoff_forward=None) -> List[Dict[str, Any]]:
+    """hidden: final-norm output rows of this request [n, H]; prenorm: residual stream rows [n, H];
+    ``cutoff_forward(n_layers)`` -> final-norm output of this request after n_layers decoder layers."""
     n = hidden.shape[0]
     out = []
     for t in targets:
         name = t["target_name"]
+        if name == "lm_head":
+            depth = max(int(c) for c in (t.get("cutoff_layer") or [len(model.layers)]))
+            out.append({"target_name": name, "tensor": _encode(reranker_scores(model, cutoff_forward(depth), depth))})
+            continue
         rows = _rows(t, n)
         idx = torch.tensor(rows, device=hidden.device, dtype=torch.long)
         if name == "transformer":

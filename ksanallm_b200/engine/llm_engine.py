@@ -604,8 +604,21 @@ class LLMEngine:
             from .forward_probe import run_probe
             b = [x.seq_id for x in plan.entries].index(e.seq_id)
             lo, hi = int(meta.cu_q_host[b]), int(meta.cu_q_host[b + 1])
-            owner[0].probe_result = run_probe(self.model, owner[0].probe, hidden[lo:hi],
-                                              self.model.last_residual[lo:hi], owner[0].prompt_tokens)
+            prenorm = self.model.last_residual[lo:hi]
+
+            def cutoff_forward(depth, seq_id=e.seq_id, n=hi - lo, toks=owner[0].prompt_tokens):
+                # a layer-wise reranker head reads the stack after `depth` layers: one more pass over this request's
+                # rows only (its cache pages receive the same values again)
+                from .step_input import make_step_input
+                table = self.cache.block_table(seq_id)
+                bs = self.block_size
+                slots = [table[p // bs] * bs + p % bs for p in range(n)]
+                m1 = make_step_input(list(toks[:n]), list(range(n)), slots, [0, n], [n], [table],
+                                     device=self.runner.device)
+                return self.model.forward(m1, self.runner.kv_caches, cutoff_layer=depth)
+
+            owner[0].probe_result = run_probe(self.model, owner[0].probe, hidden[lo:hi], prenorm,
+                                              owner[0].prompt_tokens, cutoff_forward)
 
     # ---- multi-rank plan distribution ---------------------------------------------------------------------
     def attach_control_group(self, group) -> None:

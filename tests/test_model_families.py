@@ -213,3 +213,38 @@ def test_deepseek_v32_config_enables_the_sparse_attention_indexer():
     dense = model.forward(meta, model.allocate_kv_cache(2, 16))
     assert torch.isfinite(sparse).all() and torch.allclose(sparse[:4], dense[:4], atol=1e-6)  # <= 4 keys: identical
     assert not torch.allclose(sparse[-1], dense[-1], atol=1e-6)
+
+
+def test_layerwise_reranker_head_through_the_engine():
+    """bge-reranker-v2-minicpm-layerwise: the lm_head probe stops after `cutoff_layer` layers, applies the final norm
+    and the scoring head of that depth to every prompt row."""
+    import base64
+    import numpy as np
+    from ksanallm_b200.config.schema import parse_serving_config
+    from ksanallm_b200.engine.llm_engine import LLMEngine
+    from ksanallm_b200.engine.forward_probe import validate_targets
+    from ksanallm_b200.engine.sampling_params import SamplingParams
+    cfg = model_config_from_dict(dict(BASE, model_type="minicpm", num_hidden_layers=3, scale_emb=2.0, scale_depth=1.4,
+                                      dim_model_base=64, start_layer=1, tie_word_embeddings=True))
+    assert cfg.reranker_start_layer == 1
+    sd = [(k, v) for k, v in synthetic_checkpoint(cfg, seed=3, dtype=torch.float32) if k != "lm_head.weight"]
+    g = torch.Generator().manual_seed(0)
+    heads = [torch.randn(1, 128, generator=g) for _ in range(3)]
+    sd += [(f"lm_head.{i}.linear_head.weight", h) for i, h in enumerate(heads)]
+    model = TransformerModel(cfg, WeightLoader(cfg, dtype=torch.float32).load(sd), max_positions=64)
+    serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 2, "max_step_tokens": 64,
+                                                                     "max_token_len": 64}}})
+    eng = LLMEngine(model, serving, num_blocks=8, num_host_blocks=0)
+    ids = list(range(5, 16))
+    targets = [{"target_name": "lm_head", "cutoff_layer": [2], "token_reduce_mode": "GATHER_ALL"}]
+    validate_targets(targets, len(ids))
+    req = eng.add_request(ids, SamplingParams(topk=1, max_new_tokens=1, ignore_eos=True), probe=targets)
+    eng.run_until_done()
+    t = req.probe_result[0]["tensor"]
+    got = torch.from_numpy(np.frombuffer(base64.b64decode(t["data"]), dtype=np.float32).reshape(t["shape"]).copy())
+    T = len(ids)
+    meta = make_step_input(ids, list(range(T)), list(range(T)), [0, T], [T], [[0, 1]], device="cpu")
+    h2 = model.forward(meta, model.allocate_kv_cache(2, 64), cutoff_layer=2)
+    assert got.shape == (T, 1) and torch.allclose(got, h2 @ heads[1].t(), atol=1e-5)
+    h3 = model.forward(meta, model.allocate_kv_cache(2, 64))
+    assert not torch.allclose(h2, h3, atol=1e-4)
