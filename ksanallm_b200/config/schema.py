@@ -58,9 +58,11 @@ class GlobalSetting:
 
 @dataclass
 class AttentionDpLbConfig:
+    # reference defaults: utils/config/schedule_config_parser.cpp:268-275
     enable_balance: bool = False
-    waiting_time_ms: int = 20
-    min_qps_for_waiting: float = 0.0
+    max_waiting_steps: int = 50
+    max_waiting_time_in_ms: int = 1000
+    min_qps_for_waiting: float = -1.0
     extra: Dict[str, Any] = field(default_factory=dict)
 
 

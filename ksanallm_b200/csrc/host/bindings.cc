@@ -99,6 +99,7 @@ PYBIND11_MODULE(_ksana_host, m) {
       .def_readwrite("max_draft_tokens", &SchedulerConfig::max_draft_tokens)
       .def_readwrite("ptp_mode", &SchedulerConfig::ptp_mode)
       .def_readwrite("min_flexible_cache_num", &SchedulerConfig::min_flexible_cache_num)
+      .def_readwrite("pp_wb_strategy", &SchedulerConfig::pp_wb_strategy)
       .def_readwrite("decode_token_threshold", &SchedulerConfig::decode_token_threshold);
 
   py::class_<SchedStats>(m, "SchedStats")
@@ -107,6 +108,7 @@ PYBIND11_MODULE(_ksana_host, m) {
       .def_readonly("preempt_swap", &SchedStats::preempt_swap)
       .def_readonly("swap_in", &SchedStats::swap_in)
       .def_readonly("draft_proposed", &SchedStats::draft_proposed)
+      .def_readonly("mb_migrations", &SchedStats::mb_migrations)
       .def_readonly("draft_accepted", &SchedStats::draft_accepted)
       .def_readonly("timeouts", &SchedStats::timeouts)
       .def_readonly("finished", &SchedStats::finished);
@@ -208,6 +210,8 @@ PYBIND11_MODULE(_ksana_host, m) {
              return d;
            })
       .def("schedule", &Scheduler::Schedule, py::arg("now_ms") = 0)
+      .def("micro_batch_of", &Scheduler::MicroBatchOf)
+      .def("set_hold_waiting", &Scheduler::SetHoldWaiting)
       .def(
           "pack",
           [](const Scheduler& s, const StepPlan& plan, py::array_t<int32_t, py::array::c_style> buf, int max_blocks) {

@@ -73,6 +73,11 @@ struct SchedulerConfig {
   // Non-prefix cache reuse: a run of at least this many tokens found elsewhere in the prefix tree is copied (keys
   // re-rotated) instead of being computed; 0 turns the search off (reference: min_flexible_cache_num).
   int min_flexible_cache_num = 0;
+  // Pipeline micro-batch workload balancing (reference: batch_scheduler/workload_balance/pp_multibatch_balancer.cpp):
+  // 0 = none (waiting sequences go to whichever micro-batch admits them), 1 = new sequences go to the least loaded
+  // micro-batch, one unit per sequence; 2 = the same plus moving work off a micro-batch that exceeds 1.2x the mean;
+  // 3 = like 2 with a sequence weighing 1 + (tokens to compute) / 200; 4 = like 2 weighing the tokens to compute.
+  int pp_wb_strategy = 0;
   int decode_token_threshold = 1;  // q_len <= threshold with cached KV counts as a decode entry
 };
 
@@ -143,6 +148,7 @@ struct SchedStats {
   int64_t preempt_recompute = 0;
   int64_t preempt_swap = 0;
   int64_t swap_in = 0;
+  int64_t mb_migrations = 0;  // sequences moved between pipeline micro-batches by the workload balancer
   int64_t draft_proposed = 0;
   int64_t draft_accepted = 0;
   int64_t timeouts = 0;
@@ -257,9 +263,89 @@ class Scheduler {
 
   // Pipeline micro-batches: with a filter set, Schedule() only touches the sequences of that micro-batch (and
   // assigns it to the sequences it admits), so that the other micro-batches' in-flight steps are left alone.
+  // While set, Schedule() admits nothing from the waiting queue (running and swapped sequences go on). Attention
+  // data parallelism uses it to line the ranks' prefills up (parallel/attn_dp.py ADPBalance).
+  void SetHoldWaiting(bool hold) { hold_waiting_ = hold; }
+
   void SetMicroBatch(int mb, int count = 1) {
     mb_filter_ = mb;
     mb_count_ = count < 1 ? 1 : count;
+  }
+
+  int MicroBatchOf(int64_t id) const {
+    auto it = seqs_.find(id);
+    return it == seqs_.end() ? -1 : it->second->mb;
+  }
+
+  long SeqWorkload(const Sequence& s) const {
+    long todo = std::max<long>(static_cast<long>(s.tokens.size()) - s.num_computed, 1);
+    switch (cfg_.pp_wb_strategy) {
+      case 3: return todo / 200 + 1;
+      case 4: return todo;
+      default: return 1;
+    }
+  }
+
+  // Assigns unassigned waiting sequences to the least loaded micro-batch and, for the dynamic strategies, moves
+  // work off the micro-batch about to be scheduled when it carries more than 1.2x the mean: waiting sequences
+  // first, then running ones from the back of the queue. Only the micro-batch being scheduled gives work away (its
+  // previous step has been collected, none of its sequences is in flight).
+  void BalanceMicroBatches() {
+    if (mb_filter_ < 0 || mb_count_ <= 1 || cfg_.pp_wb_strategy == 0) return;
+    std::vector<long> load(mb_count_, 0);
+    auto least = [&](int skip) {
+      int best = -1;
+      for (int m = 0; m < mb_count_; ++m)
+        if (m != skip && (best < 0 || load[m] < load[best])) best = m;
+      return best;
+    };
+    int mine = 0;
+    for (auto* q : {&running_, &swapped_, &waiting_})
+      for (int64_t id : *q) {
+        Sequence& s = *seqs_.at(id);
+        if (s.mb >= 0 && s.mb < mb_count_) {
+          load[s.mb] += SeqWorkload(s);
+          mine += s.mb == mb_filter_;
+        }
+      }
+    for (int64_t id : waiting_) {
+      Sequence& s = *seqs_.at(id);
+      if (s.mb >= 0 && s.mb < mb_count_) continue;
+      s.mb = least(-1);
+      load[s.mb] += SeqWorkload(s);
+      mine += s.mb == mb_filter_;
+    }
+    if (cfg_.pp_wb_strategy == 1 || mine < 5) return;
+    long total = 0;
+    for (long l : load) total += l;
+    long ideal = (total + mb_count_ - 1) / mb_count_;
+    if (load[mb_filter_] <= static_cast<long>(ideal * 1.2)) return;
+    long to_move = load[mb_filter_] - ideal, moved = 0;
+    auto give = [&](Sequence& s) {
+      long w = SeqWorkload(s);
+      if (moved + w > to_move) return false;
+      load[mb_filter_] -= w;
+      s.mb = least(mb_filter_);
+      load[s.mb] += w;
+      moved += w;
+      ++stats_.mb_migrations;
+      return true;
+    };
+    bool waiting_left = false;
+    for (int64_t id : waiting_) {
+      Sequence& s = *seqs_.at(id);
+      if (s.mb != mb_filter_ || cache_->Has(id)) continue;
+      if (moved >= to_move || !give(s)) {
+        waiting_left = true;
+        break;
+      }
+    }
+    if (waiting_left) return;
+    for (auto it = running_.rbegin(); it != running_.rend() && moved < to_move; ++it) {
+      Sequence& s = *seqs_.at(*it);
+      if (s.mb != mb_filter_) continue;
+      if (!give(s)) break;
+    }
   }
 
   StepPlan Schedule(int64_t now_ms) {
@@ -267,6 +353,7 @@ class Scheduler {
     ++stats_.steps;
     plan.block_copies.swap(pending_copies_);
     DropAbortedAndTimedOut(now_ms, &plan);
+    BalanceMicroBatches();
 
     int token_budget = cfg_.max_step_tokens;
     int batch_budget = cfg_.max_batch_size;
@@ -375,11 +462,23 @@ class Scheduler {
     bool preempted_now = !plan.swap_out.empty() || preempted_this_step_;
     preempted_this_step_ = false;
     // with micro-batches, one call admits its share of the queue so that the others get work too
-    int admit_left = mb_filter_ >= 0 ? std::max<int>(1, (static_cast<int>(waiting_.size()) + mb_count_ - 1) / mb_count_)
-                                     : (1 << 30);
-    while (!waiting_.empty() && batch_budget > 0 && token_budget > 0 && swapped_.empty() && !preempted_now &&
-           admit_left > 0) {
+    int admit_left = (mb_filter_ >= 0 && cfg_.pp_wb_strategy == 0)
+                         ? std::max<int>(1, (static_cast<int>(waiting_.size()) + mb_count_ - 1) / mb_count_)
+                         : (1 << 30);
+    while (!hold_waiting_ && !waiting_.empty() && batch_budget > 0 && token_budget > 0 && swapped_.empty() &&
+           !preempted_now && admit_left > 0) {
       --admit_left;
+      if (mb_filter_ >= 0 && cfg_.pp_wb_strategy > 0) {
+        // balanced micro-batches: admit this micro-batch's own waiting sequences, oldest first
+        auto mine = std::find_if(waiting_.begin(), waiting_.end(),
+                                 [&](int64_t w) { int m = seqs_.at(w)->mb; return m == mb_filter_ || m < 0; });
+        if (mine == waiting_.end()) break;
+        if (mine != waiting_.begin()) {
+          int64_t w = *mine;
+          waiting_.erase(mine);
+          waiting_.push_front(w);
+        }
+      }
       int64_t id = waiting_.front();
       Sequence& s = *seqs_.at(id);
       size_t flex_mark = plan.flexible.size();
@@ -746,6 +845,7 @@ class Scheduler {
   std::unordered_set<int64_t> aborted_;
   std::vector<CopyPair> pending_copies_;
   int mb_filter_ = -1, mb_count_ = 1;
+  bool hold_waiting_ = false;
   bool preempted_this_step_ = false;
   SchedStats stats_;
 };

@@ -138,6 +138,7 @@ class LLMEngine:
             self.mtp_steps = self.trie_drafts = 0
         sc.max_draft_tokens = max(self.mtp_steps, self.trie_drafts, self.ptp_steps)
         sc.ptp_mode = self.ptp_steps > 0
+        sc.pp_wb_strategy = int(getattr(bs_cfg, "pp_multibatch_wb_strategy", 0) or 0)
         sc.min_flexible_cache_num = self._flexible_cache_min(bs_cfg, model, kv_dtype)
         sc.decode_token_threshold = 1 + sc.max_draft_tokens
         self.cache = _host.KVCacheManager(num_blocks, num_host_blocks, self.block_size,
@@ -168,6 +169,8 @@ class LLMEngine:
         self._inflight = None       # (plan, token handle) of the step whose tokens are not on the host yet
         self._complex_requests = 0  # live requests that need per-token host state (grammar, beams, penalties, ...)
         self.dp = None              # parallel.attn_dp.DPCoordinator under attention data parallelism
+        self.adp_balance = None     # parallel.attn_dp.ADPBalance (attention_dp_lb_config.enable_balance)
+        self._dp_arrivals = 0
         self.dp_any_work = True
 
     @staticmethod
@@ -245,6 +248,7 @@ class LLMEngine:
 
     def _enqueue_seq(self, req: Request, tokens: List[int]) -> SequenceOutput:
         sid = next(self._seq_ids)
+        self._dp_arrivals += 1
         p = req.params
         eos = list(self.cfg.eos_token_ids)
         if req.beam is not None:
@@ -313,6 +317,10 @@ class LLMEngine:
     def _step_sync(self) -> int:
         t0 = time.perf_counter()
         with self.lock:
+            if self.adp_balance is not None:
+                arrivals, self._dp_arrivals = self._dp_arrivals, 0
+                allow = self.adp_balance.decide(self.sched.num_waiting, self.sched.num_running, arrivals)
+                self.sched.set_hold_waiting(not allow)
             plan = self.sched.schedule(int(time.time() * 1000))
             for sid, reason in plan.dropped:
                 self._finish_seq(sid, reason)
@@ -694,6 +702,11 @@ class LLMEngine:
         self.dp = coordinator
         self.async_mode = False
         self.tp.ep_dp = True
+        lb = self.serving.setting.batch_scheduler.attention_dp_lb_config
+        if lb.enable_balance:
+            from ..parallel.attn_dp import ADPBalance
+            self.adp_balance = ADPBalance(coordinator, lb.max_waiting_steps, lb.max_waiting_time_in_ms,
+                                          lb.min_qps_for_waiting)
 
     def run_dp(self, max_steps: int = 1 << 30) -> int:
         """Steps until NO rank has unfinished work (a rank whose own requests are done keeps running mock steps)."""

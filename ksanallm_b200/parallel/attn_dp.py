@@ -9,6 +9,7 @@ still run a step (batch_scheduler/batch_scheduler.cpp:472-519) and the cross-DP 
 """
 from __future__ import annotations
 
+import time
 from typing import Optional, Tuple
 
 import torch
@@ -31,6 +32,68 @@ class DPCoordinator:
         t = torch.tensor([local_tokens, 1 if has_unfinished else 0], dtype=torch.int64, device=self.device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
         return int(t[0]), bool(t[1])
+
+
+class ADPBalance:
+    """Lines the DP ranks' prefills up. The ranks step in lock-step (the MoE exchange joins them), so one rank's
+    long prefill stretches the decode step of all the others; holding new prompts back until EVERY rank has one to
+    start - or some rank has nothing to decode, or the wait has lasted too long, or traffic is high enough that
+    prompts arrive everywhere anyway - makes the long steps coincide. Reference: BatchScheduler::BalanceADPRequests,
+    IsADPBalanceTimeout, UpdateQPS (batch_scheduler/batch_scheduler.cpp:588-737) and
+    setting.batch_scheduler.attention_dp_lb_config.
+
+    Every rank owns its requests here, so the rule reads "every rank has a waiting request" where the reference,
+    which re-deals one global waiting pool, counts them. Clocks differ between processes: rank 0 evaluates the
+    time-based conditions and its verdict travels with the gathered counts, so all ranks decide alike."""
+
+    def __init__(self, coord: DPCoordinator, max_waiting_steps: int = 50, max_waiting_time_ms: int = 1000,
+                 min_qps_for_waiting: float = -1.0, qps_window_s: float = 1.0, clock=time.monotonic):
+        self.coord = coord
+        self.max_steps, self.max_ms, self.min_qps = int(max_waiting_steps), int(max_waiting_time_ms), float(min_qps_for_waiting)
+        self.window, self.clock = float(qps_window_s), clock
+        self.waiting_iters = 0
+        self.hold_started = 0.0
+        self.qps = 0.0
+        self._arrivals, self._window_start = 0, clock()
+        self.held_steps = self.released_by_timeout = 0
+
+    def _update_qps(self, arrivals: int) -> None:
+        self._arrivals += arrivals
+        now = self.clock()
+        if now - self._window_start >= self.window:
+            self.qps = self._arrivals / (now - self._window_start)
+            self._arrivals, self._window_start = 0, now
+
+    def decide(self, num_waiting: int, num_running: int, arrivals: int = 0) -> bool:
+        """One call per step on every rank (a collective). True: this step may start new prompts."""
+        t = torch.tensor([num_waiting, num_running, arrivals, 0, 0], dtype=torch.int64, device=self.coord.device)
+        rows = [torch.empty_like(t) for _ in range(self.coord.size)]
+        if self.coord.rank == 0:
+            self._update_qps(0)  # the window also closes in steps without arrivals
+            busy = self.min_qps >= 0 and self.qps > self.min_qps
+            timed_out = self.waiting_iters > 0 and (self.clock() - self.hold_started) * 1000.0 >= self.max_ms
+            t[3], t[4] = int(timed_out), int(busy)
+        dist.all_gather(rows, t, group=self.coord.group)
+        g = torch.stack(rows).tolist()
+        if self.coord.rank == 0:
+            self._update_qps(sum(r[2] for r in g))
+        waiting, running = [r[0] for r in g], [r[1] for r in g]
+        timed_out, busy = bool(g[0][3]), bool(g[0][4])
+        if sum(waiting) == 0:
+            self.waiting_iters = 0
+            return True
+        timeout = busy or timed_out or self.waiting_iters >= self.max_steps
+        proceed = all(w > 0 for w in waiting) or not all(r > 0 for r in running) or timeout
+        if proceed:
+            if timeout and not all(w > 0 for w in waiting):
+                self.released_by_timeout += 1
+            self.waiting_iters = 0
+            return True
+        if self.waiting_iters == 0:
+            self.hold_started = self.clock()
+        self.waiting_iters += 1
+        self.held_steps += 1
+        return False
 
 
 class GatherEPExchange:

@@ -78,3 +78,68 @@ def test_attention_dp_two_ranks_match_single_process():
     assert got[0][0] == want[0] and got[1][0] == want[1]
     assert got[0][1] == got[1][1], "ranks must take the same number of steps"
     assert got[1][2] > 0, "the rank that finished first must have run mock steps"
+
+
+def _balance_worker(rank, world, port, out, max_wait_steps):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32, ep_rank=rank, ep_size=world)
+    tp = TPGroup()
+    tp.ep_rank, tp.ep_size = rank, world
+    tp.ep = GatherEPExchange(dist.group.WORLD, rank, world, cfg.num_experts_per_tok, cfg.num_experts)
+    serving = parse_serving_config({"setting": {"batch_scheduler": {
+        "max_batch_size": 4, "max_step_tokens": 64, "max_token_len": 128,
+        "attention_dp_lb_config": {"enable_balance": True, "max_waiting_steps": max_wait_steps,
+                                   "max_waiting_time_in_ms": 600000}}}})
+    eng = LLMEngine(TransformerModel(cfg, w, tp), serving, tp, num_blocks=64, num_host_blocks=0)
+    eng.attach_dp(DPCoordinator(dist.group.WORLD))
+    assert eng.adp_balance is not None
+    sp = SamplingParams(topk=1, max_new_tokens=30, ignore_eos=True)
+    eng.add_request([5 + rank, 9, 77, 120], sp)          # step 0: both ranks start a prompt together
+    second_at = {0: 3, 1: 8}[rank]                        # the second prompt reaches rank 1 five steps later
+    prefill_steps, cur = [], [0]
+    eng.on_step = lambda info: prefill_steps.append(cur[0]) if info["prefill"] else None
+    for step in range(20):
+        cur[0] = step
+        if step == second_at:
+            eng.add_request([40 + rank, 41, 42, 43, 44, 45], sp)
+        eng._step_sync()
+    out.put((rank, prefill_steps, eng.adp_balance.held_steps, eng.adp_balance.released_by_timeout))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _run_balance(max_wait_steps):
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_balance_worker, args=(r, 2, port, q, max_wait_steps)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(2):
+        rank, steps, held, by_timeout = q.get(timeout=120)
+        got[rank] = (steps, held, by_timeout)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return got
+
+
+def test_adp_balance_aligns_prefills_across_ranks():
+    got = _run_balance(50)
+    # rank 0's second prompt waits until rank 1 has one as well: both prefills run in step 8
+    assert got[0][0] == [0, 8] and got[1][0] == [0, 8]
+    assert got[0][1] == got[1][1] == 5 and got[0][2] == 0
+
+
+def test_adp_balance_gives_up_after_max_waiting_steps():
+    got = _run_balance(2)
+    # held in steps 3 and 4, released by the step limit in step 5; rank 1's prompt then waits for nobody... but
+    # rank 0 has nothing waiting at step 8, so rank 1 is held for two steps as well
+    assert got[0][0] == [0, 5] and got[1][0] == [0, 10]
+    assert got[0][2] == got[1][2] == 2

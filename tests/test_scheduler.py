@@ -67,6 +67,7 @@ def make(num_blocks=64, host_blocks=0, prefix=False, **kw):
     cfg.max_draft_tokens = kw.get("drafts", 0)
     cfg.waiting_timeout_ms = kw.get("timeout_ms", 3600000)
     cfg.max_waiting_queue_len = kw.get("queue", 100)
+    cfg.pp_wb_strategy = kw.get("pp_wb", 0)
     cache = host.KVCacheManager(num_blocks, host_blocks, 4, prefix)
     return host.Scheduler(cfg, cache), cache, FakeRunner(num_blocks, host_blocks, 4)
 
@@ -279,3 +280,59 @@ def test_warmup_leaves_a_clean_engine():
     assert n >= 3 and not eng.has_unfinished()
     assert eng.stats["generated_tokens"] == 0 and eng.cache.num_cached_blocks == 0
     assert eng.cache.num_free_blocks == eng.num_blocks
+
+
+@pytest.mark.parametrize("strategy", [1, 2, 4])
+def test_pipeline_micro_batch_workload_balancing(strategy):
+    """Two micro-batches scheduled alternately: new sequences go to the lighter one (by count, or by the tokens they
+    still have to compute), an overloaded micro-batch hands work over, and the outputs stay exact."""
+    sched, cache, runner = make(num_blocks=256, max_batch=16, max_step_tokens=256, pp_wb=strategy)
+    prompts = {1: list(range(10, 90)), 2: [5, 6, 7], 3: [8, 9, 10], 4: [11, 12], 5: [13, 14, 15], 6: [16, 17],
+               7: [18, 19], 8: [20, 21, 22]}
+    for sid, p in prompts.items():
+        sched.enqueue(sid, p, 6)
+    outputs, inflight, steps = {}, [None, None], 0
+    assignment = None
+    while sched.has_unfinished() or any(x is not None for x in inflight):
+        mb = steps % 2
+        if inflight[mb] is not None:
+            plan, sampled = inflight[mb]
+            for r in sched.update(plan, sampled, steps):
+                outputs.setdefault(r.seq_id, []).extend(r.new_tokens)
+            inflight[mb] = None
+        sched.set_micro_batch(mb, 2)
+        plan = sched.schedule(steps)
+        sched.set_micro_batch(-1)
+        if steps == 0:
+            assignment = {sid: sched.micro_batch_of(sid) for sid in prompts}
+        if not plan.empty():
+            inflight[mb] = (plan, runner.run(sched, plan))
+        steps += 1
+        assert steps < 500
+    for sid, p in prompts.items():
+        assert outputs[sid] == expected_output(p, 6)
+    groups = [sorted(s for s, m in assignment.items() if m == k) for k in (0, 1)]
+    if strategy == 4:
+        # the 80-token prompt weighs as much as all the short ones together
+        assert groups[0] == [1] and len(groups[1]) == 7
+    else:
+        assert len(groups[0]) == 4 and len(groups[1]) == 4
+
+
+def test_pipeline_micro_batch_offload_moves_running_work():
+    sched, cache, runner = make(num_blocks=256, max_batch=16, max_step_tokens=256, pp_wb=2)
+    for sid in range(1, 9):
+        sched.enqueue(sid, [sid, sid + 1, sid + 2], 8)
+    # every sequence is admitted by micro-batch 0 while it is the only one scheduling (count = 1) ...
+    sched.set_micro_batch(0, 1)
+    plan = sched.schedule(0)
+    outs = {}
+    for r in sched.update(plan, runner.run(sched, plan), 0):
+        outs.setdefault(r.seq_id, []).extend(r.new_tokens)
+    assert all(sched.micro_batch_of(s) == 0 for s in range(1, 9))
+    # ... then a second micro-batch appears: scheduling micro-batch 0 hands half of its running work over
+    sched.set_micro_batch(0, 2)
+    plan = sched.schedule(1)
+    moved = [s for s in range(1, 9) if sched.micro_batch_of(s) == 1]
+    assert len(moved) == 4 and sched.stats.mb_migrations == 4
+    assert sorted(plan.seq_ids) == sorted(s for s in range(1, 9) if s not in moved)
