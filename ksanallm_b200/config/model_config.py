@@ -194,6 +194,13 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
             if k in c and k not in inner:
                 inner[k] = c[k]
         c = inner
+    if isinstance(c.get("text_config"), dict) and str(c.get("model_type", "")).lower() in ("qwen2_vl", "qwen2_5_vl"):
+        inner = dict(c["text_config"])
+        inner["model_type"] = str(c["model_type"]).lower()
+        for k in ("torch_dtype", "dtype", "quantization_config", "tie_word_embeddings", "architectures"):
+            if k in c and k not in inner:
+                inner[k] = c[k]
+        c = inner
     mt = str(c.get("model_type", "llama")).lower()
     m = ModelConfig(model_type=mt, architectures=list(c.get("architectures", []) or []), raw=c)
     g = c.get

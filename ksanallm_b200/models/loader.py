@@ -59,7 +59,8 @@ _RENAMES: Dict[str, List[Tuple[str, str]]] = {
     "hunyuan": [(r"\.mlp\.shared_mlp\.", ".mlp.shared_expert."), (r"\.query_layernorm\.", ".query_layernorm."),
                 (r"\.mlp\.gate\.wg\.", ".mlp.gate.")],
 }
-_RENAMES["qwen2_vl"] = []
+# multimodal checkpoints: the language tower sits under model.language_model (transformers >= 4.52) or model.
+_RENAMES["qwen2_vl"] = [(r"^model\.language_model\.", "model.")]
 _RENAMES["internvl_chat"] = [(r"^language_model\.", "")] + _RENAMES["internlm2"]
 _RENAMES["internlmxcomposer2"] = _RENAMES["internlm2"]
 _RENAMES["llama4"] = [(r"^language_model\.", ""), (r"\.feed_forward\.", ".mlp."), (r"\.router\.", ".gate.")]
@@ -385,6 +386,8 @@ class WeightLoader:
     # ---- main entry -------------------------------------------------------------------------------
     def load(self, tensors: Iterable[Tuple[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
         for raw_name, t in tensors:
+            if re.match(r"(model\.)?(visual|vision_tower|vision_model|vit)\.", raw_name):
+                continue  # vision towers belong to the serving plugin, not to the language model
             name = normalise_name(raw_name, self.rules)
             li = self._layer_of(name)
             if li is not None and self.layer_range is not None and li not in self.layer_range \

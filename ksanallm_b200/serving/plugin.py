@@ -11,29 +11,60 @@ import os
 from typing import Any, Dict, List, Optional
 
 
+class RefitEmbedding:
+    """Mutable stand-in for the reference's ``ksana_python_input.input_refit_embedding``: a plugin writes the splice
+    positions, one embedding tensor per position and optional extra tensors (multimodal RoPE: [positions, delta])."""
+
+    def __init__(self):
+        self.pos: List[int] = []
+        self.embeddings: List[Any] = []
+        self.embedding_tensors: List[Any] = []
+        self.additional_tensors: List[Any] = []
+
+
+class PluginInput:
+    """What a plugin sees as ``ksana_python_input`` (reference: KsanaPythonInput in torch_op/serving_op.cpp)."""
+
+    def __init__(self, tokens: List[int]):
+        self.input_tokens: List[int] = list(tokens)
+        self.input_refit_embedding = RefitEmbedding()
+
+
 class PluginHost:
     def __init__(self, impl, engine):
         self.impl = impl
         self.engine = engine
 
     def preprocess(self, request_dict: Dict[str, Any], tokens: List[int]) -> Optional[Dict[str, Any]]:
+        """Runs the plugin's ``preprocess``. Both contracts are understood: the reference's (the plugin mutates
+        ``ksana_python_input``: input_tokens, input_refit_embedding.pos / embedding_tensors / additional_tensors)
+        and a returned dict with ``input_tokens``, ``input_refit_embedding`` {pos, embeddings}, ``mrope_positions``."""
         fn = getattr(self.impl, "preprocess", None)
         if fn is None:
             return None
-        res = fn(ksana_python_input=None, request_dict=request_dict, input_tokens=tokens,
-                 tokenizer=self.engine.tokenizer.tokenizer, messages=request_dict.get("messages"))
-        if not res:
-            return None
+        import torch
+        pin = PluginInput(tokens)
+        res = fn(ksana_python_input=pin, request_dict=request_dict, input_tokens=tokens,
+                 tokenizer=self.engine.tokenizer.tokenizer, messages=request_dict.get("messages"),
+                 additional_params=request_dict.get("additional_params") or {}) or {}
         out: Dict[str, Any] = {}
+        hs = self.engine.model_config.hidden_size
         if "input_tokens" in res:
             out["input_tokens"] = list(res["input_tokens"])
+        elif list(pin.input_tokens) != list(tokens):
+            out["input_tokens"] = list(pin.input_tokens)
         emb = res.get("input_refit_embedding")
-        if emb:
-            import torch
-            hs = self.engine.model_config.hidden_size
-            out["refit"] = [(int(p), torch.as_tensor(e, dtype=torch.float32).view(-1, hs))
-                            for p, e in zip(emb["pos"], emb["embeddings"])]
-        return out
+        pos, vals = (emb["pos"], emb["embeddings"]) if emb else \
+            (pin.input_refit_embedding.pos,
+             pin.input_refit_embedding.embedding_tensors or pin.input_refit_embedding.embeddings)
+        if pos and vals:
+            out["refit"] = [(int(p), torch.as_tensor(e, dtype=torch.float32).view(-1, hs)) for p, e in zip(pos, vals)]
+        extra = pin.input_refit_embedding.additional_tensors
+        if res.get("mrope_positions") is not None:
+            out["mrope_positions"] = res["mrope_positions"]
+        elif extra:
+            out["mrope_positions"] = extra[0]  # [axes, prompt_len]; the delta follows from it
+        return out or None
 
     def postprocess(self, request_dict: Dict[str, Any], output) -> None:
         fn = getattr(self.impl, "postprocess", None)

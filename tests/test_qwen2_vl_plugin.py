@@ -1,0 +1,86 @@
+"""Multimodal end to end on CPU: a tiny random Qwen2-VL checkpoint (transformers) is saved to disk and served through
+the engine with the bundled vision plugin; an image in the request becomes spliced embeddings + three-axis positions.
+Greedy tokens must equal ``generate`` of the transformers model given the same pixels."""
+import asyncio
+import base64
+import io
+import json
+import os
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from ksanallm_b200.config.schema import parse_serving_config  # noqa: E402
+from ksanallm_b200.serving.ksana_engine import EngineArgs, KsanaLLMEngine  # noqa: E402
+from ksanallm_b200.serving.plugins.qwen2_vl import mrope_positions  # noqa: E402
+
+IMG, VSTART, VEND = 290, 291, 292
+
+
+def _tiny_model(tmp):
+    cfg = transformers.Qwen2VLConfig(
+        text_config=dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         intermediate_size=128, vocab_size=300, max_position_embeddings=512,
+                         rope_scaling=dict(type="mrope", mrope_section=[2, 3, 3]), tie_word_embeddings=False),
+        vision_config=dict(depth=2, embed_dim=32, hidden_size=64, num_heads=4, mlp_ratio=2, patch_size=14,
+                           spatial_merge_size=2, temporal_patch_size=2, in_channels=3),
+        image_token_id=IMG, video_token_id=293, vision_start_token_id=VSTART, vision_end_token_id=VEND,
+        tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = transformers.Qwen2VLForConditionalGeneration(cfg).eval().float()
+    hf.generation_config.eos_token_id = None
+    hf.save_pretrained(tmp, safe_serialization=True)
+    with open(os.path.join(tmp, "ksana_plugin.py"), "w") as f:
+        f.write("from ksanallm_b200.serving.plugins.qwen2_vl import KsanaPlugin  # noqa: F401\n")
+    return hf
+
+
+def test_mrope_positions_rule():
+    # text, a 1 x 4 x 6-patch image (2 x 3 merged tokens), text
+    toks = [5, 6, IMG, IMG, IMG, IMG, IMG, IMG, 7, 8]
+    pos = mrope_positions(toks, [(1, 4, 6)], IMG, 2)
+    assert pos[0].tolist() == [0, 1, 2, 2, 2, 2, 2, 2, 5, 6]
+    assert pos[1].tolist() == [0, 1, 2, 2, 2, 3, 3, 3, 5, 6]
+    assert pos[2].tolist() == [0, 1, 2, 3, 4, 2, 3, 4, 5, 6]
+
+
+def test_image_request_matches_transformers_generate(tmp_path):
+    from PIL import Image
+    tmp = str(tmp_path)
+    hf = _tiny_model(tmp)
+    g = torch.Generator().manual_seed(1)
+    img = Image.fromarray((torch.rand(56, 84, 3, generator=g) * 255).byte().numpy())
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+    args = EngineArgs(config_file="", model_dir=tmp, device="cpu",
+                      serving=parse_serving_config({"setting": {"batch_scheduler": {
+                          "max_batch_size": 2, "max_step_tokens": 128, "max_token_len": 256,
+                          "split_fuse_token_num": 16}, "block_manager": {"block_token_num": 16}}}))
+    eng = KsanaLLMEngine(args)
+    eng.initialize()
+    try:
+        assert eng.plugin is not None and eng.model_config.rope_scaling.mrope_section == [2, 3, 3]
+        prompt = [5, 9, VSTART, IMG, VEND, 33, 4, 8]
+        body = {"input_tokens": prompt, "stream": False,
+                "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}},
+                                                          {"type": "text", "text": "x"}]}],
+                "sampling_config": {"max_new_tokens": 6, "topk": 1, "ignore_eos": True}}
+        st, out = asyncio.run(eng.generate(json.loads(json.dumps(body)), streamer=False))
+        assert st.OK()
+        wide = out.input_tokens
+        n_img = wide.count(IMG)
+        assert n_img > 1 and len(wide) == len(prompt) - 1 + n_img
+        # the same pixels through the transformers model
+        feats = eng.plugin.impl.image_processor(images=[img.convert("RGB")], return_tensors="pt")
+        assert int(feats["image_grid_thw"].prod()) // 4 == n_img
+        with torch.no_grad():
+            want = hf.generate(input_ids=torch.tensor([wide]), pixel_values=feats["pixel_values"],
+                               image_grid_thw=feats["image_grid_thw"], attention_mask=torch.ones(1, len(wide), dtype=torch.long),
+                               max_new_tokens=6, do_sample=False)[0, len(wide):].tolist()
+        assert out.output_tokens[0] == want
+    finally:
+        eng.shutdown()
