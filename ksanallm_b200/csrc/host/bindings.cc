@@ -48,7 +48,7 @@ PYBIND11_MODULE(_ksana_host, m) {
       .def_property_readonly("stats", &KVCacheManager::stats)
       .def("has", &KVCacheManager::Has)
       .def("match_prefix", &KVCacheManager::MatchPrefix)
-      .def("create_seq", &KVCacheManager::CreateSeq)
+      .def("create_seq", &KVCacheManager::CreateSeq, py::arg("seq"), py::arg("tokens"), py::arg("use_prefix") = true)
       .def("ensure_capacity", &KVCacheManager::EnsureCapacity)
       .def("commit_filled",
            [](KVCacheManager& c, int64_t seq, const std::vector<int32_t>& tokens, int n) {
@@ -170,8 +170,9 @@ PYBIND11_MODULE(_ksana_host, m) {
           "enqueue",
           [](Scheduler& s, int64_t id, const std::vector<int32_t>& tokens, int max_new_tokens, bool ignore_eos,
              const std::vector<int32_t>& eos_ids, const std::vector<int32_t>& stop_ids, int64_t arrival_ms,
-             int64_t group_id) {
+             int64_t group_id, bool no_cache) {
             Sequence q;
+            q.no_cache = no_cache;
             q.id = id;
             q.group_id = group_id;
             q.tokens = tokens;
@@ -184,7 +185,7 @@ PYBIND11_MODULE(_ksana_host, m) {
           },
           py::arg("seq_id"), py::arg("tokens"), py::arg("max_new_tokens"), py::arg("ignore_eos") = false,
           py::arg("eos_ids") = std::vector<int32_t>{}, py::arg("stop_ids") = std::vector<int32_t>{},
-          py::arg("arrival_ms") = 0, py::arg("group_id") = 0)
+          py::arg("arrival_ms") = 0, py::arg("group_id") = 0, py::arg("no_cache") = false)
       .def("abort", &Scheduler::Abort)
       .def("fork", &Scheduler::Fork)
       .def("finish", &Scheduler::Finish)

@@ -81,6 +81,7 @@ struct SeqBlocks {
   std::vector<BlockId> own;         // private blocks after the shared ones
   std::vector<BlockId> host;        // host copies while swapped out (own blocks only)
   bool swapped = false;
+  bool no_commit = false;  // blocks never enter the prefix tree (token ids do not determine the KV: spliced embeddings)
   int NumBlocks() const { return static_cast<int>(shared.size() + own.size()); }
 };
 
@@ -140,11 +141,12 @@ class KVCacheManager {
   }
 
   // Registers a sequence and pins its cached prefix. Returns number of prefix tokens reused.
-  int CreateSeq(int64_t seq, const std::vector<int32_t>& tokens) {
+  int CreateSeq(int64_t seq, const std::vector<int32_t>& tokens, bool use_prefix = true) {
     if (seqs_.count(seq)) throw std::runtime_error("KVCacheManager: duplicate seq");
     SeqBlocks& sb = seqs_[seq];
+    sb.no_commit = !use_prefix;
     stats_.prefix_query_tokens += static_cast<int64_t>(tokens.size());
-    if (!prefix_) return 0;
+    if (!prefix_ || !use_prefix) return 0;
     PrefixNode* cur = &root_;
     const int max_full = (static_cast<int>(tokens.size()) - 1) / block_size_;
     for (int b = 0; b < max_full; ++b) {
@@ -185,6 +187,7 @@ class KVCacheManager {
     std::vector<CopyPair> merged;
     if (!prefix_) return merged;
     SeqBlocks& sb = seqs_.at(seq);
+    if (sb.no_commit) return merged;
     int full = num_computed / block_size_;
     while (static_cast<int>(sb.shared.size()) < full && !sb.own.empty()) {
       int bidx = static_cast<int>(sb.shared.size());
@@ -329,6 +332,7 @@ class KVCacheManager {
     if (p.swapped) return false;
     if (static_cast<int>(p.own.size()) > num_available_blocks()) return false;
     SeqBlocks c;
+    c.no_commit = p.no_commit;
     for (auto* n : p.shared) {
       Pin(n);
       c.shared.push_back(n);

@@ -88,6 +88,7 @@ struct Sequence {
   int prompt_len = 0;
   int num_computed = 0;  // tokens whose KV is valid in the cache
   std::vector<int32_t> drafts;
+  bool no_cache = false;  // the prompt's KV is not a function of its token ids alone: no prefix reuse, no commit
   int max_new_tokens = 16;
   bool ignore_eos = false;
   std::vector<int32_t> eos_ids;
@@ -483,7 +484,7 @@ class Scheduler {
       Sequence& s = *seqs_.at(id);
       size_t flex_mark = plan.flexible.size();
       if (!cache_->Has(id)) {
-        int hit = cache_->MatchPrefix(s.tokens);
+        int hit = s.no_cache ? 0 : cache_->MatchPrefix(s.tokens);
         int remaining = static_cast<int>(s.tokens.size()) - hit;
         int first = remaining;
         if (cfg_.split_fuse_token_num > 0) first = std::min(first, cfg_.split_fuse_token_num);
@@ -498,11 +499,11 @@ class Scheduler {
         int blocks_needed = (hit + first + cfg_.block_size - 1) / cfg_.block_size - hit / cfg_.block_size;
         int headroom = static_cast<int>(cfg_.launch_block_threshold * running_.size());
         if (blocks_needed + headroom > cache_->num_available_blocks() && !running_.empty()) break;
-        cache_->CreateSeq(id, s.tokens);
+        cache_->CreateSeq(id, s.tokens, !s.no_cache);
         s.num_computed = cache_->NumBlocks(id) * cfg_.block_size;
         flex_mark = plan.flexible.size();
         FlexibleRun run;
-        if (cfg_.min_flexible_cache_num > 0 &&
+        if (cfg_.min_flexible_cache_num > 0 && !s.no_cache &&
             cache_->FlexibleReserve(id, s.tokens, s.num_computed, cfg_.min_flexible_cache_num, &run)) {
           for (int i = 0; i < run.size(); ++i) {
             plan.flexible.insert(plan.flexible.end(),

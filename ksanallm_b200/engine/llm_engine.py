@@ -251,13 +251,15 @@ class LLMEngine:
         self._dp_arrivals += 1
         p = req.params
         eos = list(self.cfg.eos_token_ids)
+        # spliced embeddings (images): equal token ids no longer mean equal KV, so the prefix tree is bypassed
+        no_cache = req.refit is not None
         if req.beam is not None:
             # the beam state applies EOS / length rules itself (a finished hypothesis is not a finished request)
             code = self.sched.enqueue(sid, tokens, p.max_new_tokens + 1, True, [], [], int(req.arrival * 1000),
-                                      req.req_id)
+                                      req.req_id, no_cache)
         else:
             code = self.sched.enqueue(sid, tokens, p.max_new_tokens, p.ignore_eos, eos, list(p.stop_token_ids),
-                                      int(req.arrival * 1000), req.req_id)
+                                      int(req.arrival * 1000), req.req_id, no_cache)
         if code != _host.RET_SUCCESS:
             msg = {_host.RET_EXCEED_CAPACITY: "waiting queue is full",
                    _host.RET_INPUT_LENGTH_EXCEEDED: "input length exceeds max_token_len",
@@ -342,13 +344,15 @@ class LLMEngine:
             layout = self.sched.pack(plan, self.runner.staging.host_np, self.runner.max_blocks_per_seq)
             rows, greedy, refit = self._sample_rows(plan)
         t1 = time.perf_counter()
+        mrope = self._build_mrope(plan)
         if self._has_followers():
-            self._broadcast_plan(layout, plan, greedy)
+            self._broadcast_plan(layout, plan, greedy, refit=refit, mrope=mrope)
         ta = time.perf_counter()
         self.runner.apply_flexible(plan.flexible)
         self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
         meta = self.runner.upload(layout)
-        self._attach_mrope(plan, meta)
+        if mrope is not None:
+            meta.mrope_positions = mrope.to(self.runner.device)
         if self.pipeline is not None and self.pipeline.topo.num_stages > 1:
             out, hidden = self._pipeline_step_driver(meta, refit, rows, greedy)
             tb = time.perf_counter()
@@ -452,10 +456,15 @@ class LLMEngine:
         return 4 if len(sec) == 4 else 3
 
     def _attach_mrope(self, plan, meta) -> None:
-        """Builds the step's [axes, T] multimodal positions when any scheduled request carries them."""
+        mp = self._build_mrope(plan)
+        if mp is not None:
+            meta.mrope_positions = mp.to(self.runner.device)
+
+    def _build_mrope(self, plan) -> Optional[torch.Tensor]:
+        """The step's [axes, T] multimodal positions (host tensor) when any scheduled request carries them."""
         if not any(getattr(self.seq_owner[e.seq_id][0], "mrope", None) is not None for e in plan.entries
                    if e.seq_id in self.seq_owner):
-            return
+            return None
         cols = []
         axes = self._rope_axes()
         for e in plan.entries:
@@ -468,15 +477,21 @@ class LLMEngine:
             P = mp.shape[1]
             inside = idx.clamp(max=max(P - 1, 0)).long()
             cols.append(torch.where(idx.unsqueeze(0) < P, mp[:, inside], (idx + req.mrope_delta).unsqueeze(0).expand(axes, -1)))
-        meta.mrope_positions = torch.cat(cols, dim=1).to(self.runner.device)
+        return torch.cat(cols, dim=1).to(torch.int32).contiguous()
 
     def _sample_rows(self, plan):
         rows: List[SampleRow] = []
         refit = None
+        row0 = 0  # first row of the entry in the step's flat token order
         for e in plan.entries:
             req, so = self.seq_owner[e.seq_id]
-            if req.refit is not None and e.q_start == 0:
-                refit = (refit or []) + [(pos + 0, emb) for pos, emb in req.refit]
+            if req.refit is not None and e.q_start < len(req.prompt_tokens):
+                # the part of every spliced run that falls into this chunk [q_start, q_start + q_len)
+                for pos, emb in req.refit:
+                    lo, hi = max(pos, e.q_start), min(pos + emb.shape[0], e.q_start + e.q_len)
+                    if lo < hi:
+                        refit = (refit or []) + [(row0 + lo - e.q_start, emb[lo - pos:hi - pos])]
+            row0 += e.q_len
             for j in range(e.num_logits):
                 bm = None
                 if req.grammar is not None and j == 0:
@@ -636,7 +651,8 @@ class LLMEngine:
         """Other ranks execute this engine's plans: tensor-parallel peers and / or later pipeline stages."""
         return self.tp.size > 1 or (self.pipeline is not None and self.pipeline.topo.num_stages > 1)
 
-    def _broadcast_plan(self, layout, plan, greedy: bool, stop: bool = False, fixup: bool = False) -> None:
+    def _broadcast_plan(self, layout, plan, greedy: bool, stop: bool = False, fixup: bool = False, refit=None,
+                        mrope=None) -> None:
         keys = ["num_seqs", "num_prefill", "num_decode", "total_tokens", "total_logits", "max_q_len", "max_kv_len",
                 "max_blocks", "input_ids", "positions", "slot_mapping", "seq_of_token", "cu_q", "kv_lens", "q_starts",
                 "logits_idx", "block_tables", "total_words"]
@@ -651,6 +667,9 @@ class LLMEngine:
             so, si, bc = plan.swap_out, plan.swap_in, plan.block_copies
             fx = np.asarray(plan.flexible, dtype=np.int32).reshape(-1, 2)  # [n, 4] travels as 2n pairs
             h[31], h[32], h[33], h[35] = len(so), len(si), len(bc), len(fx)
+            h[36] = len(refit) if refit else 0
+            h[37] = sum(int(e.shape[0]) for _, e in refit) if refit else 0
+            h[38] = int(mrope.shape[0]) if mrope is not None else 0
         hdr = torch.from_numpy(h)
         dist.broadcast(hdr, src=0, group=self._ctl)
         if stop:
@@ -661,6 +680,13 @@ class LLMEngine:
         if extra:
             arr = np.concatenate([np.asarray(a, dtype=np.int32).reshape(-1, 2) for a in (so, si, bc, fx)], 0)
             dist.broadcast(torch.from_numpy(np.ascontiguousarray(arr)), src=0, group=self._ctl)
+        if refit:
+            # multimodal: (first row, row count) of every spliced run, then all embedding rows
+            runs = torch.tensor([[p, e.shape[0]] for p, e in refit], dtype=torch.int32)
+            dist.broadcast(runs, src=0, group=self._ctl)
+            dist.broadcast(torch.cat([e.float().cpu() for _, e in refit]).contiguous(), src=0, group=self._ctl)
+        if mrope is not None:
+            dist.broadcast(mrope, src=0, group=self._ctl)
 
     def follow(self) -> None:
         """Step loop of a non-driver rank: receive plan, run the shard, join the collectives."""
@@ -684,15 +710,31 @@ class LLMEngine:
                 dist.broadcast(arr, src=0, group=self._ctl)
                 a = arr.numpy()
                 so, si, bc, fx = a[:nso], a[nso:nso + nsi], a[nso + nsi:nso + nsi + nbc], a[nso + nsi + nbc:]
+            refit = None
+            if h[36]:
+                runs = torch.zeros(int(h[36]), 2, dtype=torch.int32)
+                dist.broadcast(runs, src=0, group=self._ctl)
+                vals = torch.zeros(int(h[37]), self.cfg.hidden_size, dtype=torch.float32)
+                dist.broadcast(vals, src=0, group=self._ctl)
+                refit, at = [], 0
+                for p, n in runs.tolist():
+                    refit.append((p, vals[at:at + n].to(self.runner.device)))
+                    at += n
+            mrope = None
+            if h[38]:
+                mrope = torch.zeros(int(h[38]), layout["total_tokens"], dtype=torch.int32)
+                dist.broadcast(mrope, src=0, group=self._ctl)
             self.runner.apply_flexible(fx.reshape(-1, 4))
             self.runner.apply_block_ops(so, si, bc)
             meta = self.runner.upload(layout)
+            if mrope is not None:
+                meta.mrope_positions = mrope.to(self.runner.device)
             if h[34]:
                 self.runner.fixup_inputs(meta)
             if self.pipeline is not None and self.pipeline.topo.num_stages > 1:
                 self._pipeline_step_follower(meta)
                 continue
-            hidden = self.runner.forward(meta)
+            hidden = self.runner.forward(meta, refit)
             self.runner.sample(hidden, meta, None, bool(h[30]))
 
     # ---- attention data parallelism ------------------------------------------------------------------------------

@@ -46,41 +46,56 @@ def test_mrope_positions_rule():
     assert pos[2].tolist() == [0, 1, 2, 3, 4, 2, 3, 4, 5, 6]
 
 
-def test_image_request_matches_transformers_generate(tmp_path):
+def _png_url(img):
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+
+def test_image_requests_match_transformers_generate(tmp_path):
+    """Two requests with the SAME token ids and different images run concurrently (their KV must not be shared through
+    the prefix tree); the second image spans several prefill chunks."""
     from PIL import Image
     tmp = str(tmp_path)
     hf = _tiny_model(tmp)
     g = torch.Generator().manual_seed(1)
-    img = Image.fromarray((torch.rand(56, 84, 3, generator=g) * 255).byte().numpy())
-    buf = io.BytesIO()
-    img.save(buf, format="PNG")
-    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
-
+    imgs = [Image.fromarray((torch.rand(h, w, 3, generator=g) * 255).byte().numpy()) for h, w in ((56, 84), (112, 140))]
     args = EngineArgs(config_file="", model_dir=tmp, device="cpu",
                       serving=parse_serving_config({"setting": {"batch_scheduler": {
-                          "max_batch_size": 2, "max_step_tokens": 128, "max_token_len": 256,
-                          "split_fuse_token_num": 16}, "block_manager": {"block_token_num": 16}}}))
+                          "max_batch_size": 4, "max_step_tokens": 128, "max_token_len": 256,
+                          "split_fuse_token_num": 16, "enable_auto_prefix_cache": True},
+                          "block_manager": {"block_token_num": 16}}}))
     eng = KsanaLLMEngine(args)
     eng.initialize()
     try:
         assert eng.plugin is not None and eng.model_config.rope_scaling.mrope_section == [2, 3, 3]
         prompt = [5, 9, VSTART, IMG, VEND, 33, 4, 8]
-        body = {"input_tokens": prompt, "stream": False,
-                "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}},
-                                                          {"type": "text", "text": "x"}]}],
-                "sampling_config": {"max_new_tokens": 6, "topk": 1, "ignore_eos": True}}
-        st, out = asyncio.run(eng.generate(json.loads(json.dumps(body)), streamer=False))
-        assert st.OK()
-        wide = out.input_tokens
-        n_img = wide.count(IMG)
-        assert n_img > 1 and len(wide) == len(prompt) - 1 + n_img
-        # the same pixels through the transformers model
-        feats = eng.plugin.impl.image_processor(images=[img.convert("RGB")], return_tensors="pt")
-        assert int(feats["image_grid_thw"].prod()) // 4 == n_img
-        with torch.no_grad():
-            want = hf.generate(input_ids=torch.tensor([wide]), pixel_values=feats["pixel_values"],
-                               image_grid_thw=feats["image_grid_thw"], attention_mask=torch.ones(1, len(wide), dtype=torch.long),
-                               max_new_tokens=6, do_sample=False)[0, len(wide):].tolist()
-        assert out.output_tokens[0] == want
+
+        def body(img):
+            return {"input_tokens": prompt, "stream": False,
+                    "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": _png_url(img)}},
+                                                              {"type": "text", "text": "x"}]}],
+                    "sampling_config": {"max_new_tokens": 6, "topk": 1, "ignore_eos": True}}
+
+        async def both():
+            return await asyncio.gather(*[eng.generate(json.loads(json.dumps(body(i))), streamer=False) for i in imgs])
+
+        results = asyncio.run(both())
+        # once more, one after the other: nothing of the first round may have been cached under these token ids
+        results += [asyncio.run(eng.generate(json.loads(json.dumps(body(i))), streamer=False)) for i in imgs]
+        for k, (st, out) in enumerate(results):
+            img = imgs[k % 2]
+            assert st.OK()
+            wide = out.input_tokens
+            n_img = wide.count(IMG)
+            assert n_img == (6, 20)[k % 2] and len(wide) == len(prompt) - 1 + n_img
+            feats = eng.plugin.impl.image_processor(images=[img.convert("RGB")], return_tensors="pt")
+            with torch.no_grad():
+                want = hf.generate(input_ids=torch.tensor([wide]), pixel_values=feats["pixel_values"],
+                                   image_grid_thw=feats["image_grid_thw"],
+                                   attention_mask=torch.ones(1, len(wide), dtype=torch.long),
+                                   max_new_tokens=6, do_sample=False)[0, len(wide):].tolist()
+            assert out.output_tokens[0] == want
+        assert eng.llm.cache.stats.prefix_hit_tokens == 0
     finally:
         eng.shutdown()

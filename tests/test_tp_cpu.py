@@ -72,3 +72,69 @@ def test_tp2_matches_single_rank(enable_async):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got == want
+
+
+def _mm_cfg():
+    return model_config_from_dict(dict(model_type="qwen2_vl", hidden_size=128, num_hidden_layers=2,
+                                       num_attention_heads=4, num_key_value_heads=2, intermediate_size=256,
+                                       vocab_size=500, torch_dtype="float32", eos_token_id=2,
+                                       rope_scaling=dict(type="mrope", mrope_section=[4, 6, 6])))
+
+
+def _mm_request():
+    g = torch.Generator().manual_seed(7)
+    prompt = [5, 9, 77] + [300] * 20 + [33, 4, 8]
+    refit = [(3, torch.randn(20, 128, generator=g) * 0.05)]  # an "image" spanning two prefill chunks
+    idx = torch.arange(20)
+    img = torch.stack((torch.full((20,), 3), 3 + idx // 5, 3 + idx % 5))
+    pos3 = torch.cat((torch.arange(3).expand(3, 3), img, (8 + torch.arange(3)).expand(3, 3)), dim=1)
+    return prompt, refit, pos3
+
+
+def _mm_run(eng):
+    prompt, refit, pos3 = _mm_request()
+    sp = SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True)
+    reqs = [eng.add_request(prompt, sp, refit=refit, mrope_positions=pos3), eng.add_request(PROMPTS[0], sp)]
+    eng.run_until_done()
+    return [r.output_token_ids[0] for r in reqs]
+
+
+def _mm_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    tp = TPGroup(rank, world, dist.group.WORLD, torch.device("cpu"))
+    cfg = _mm_cfg()
+    w = load_model_weights(cfg, synthetic_seed=1, tp_rank=rank, tp_size=world, dtype=torch.float32)
+    serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 64,
+                                                                     "max_token_len": 128, "split_fuse_token_num": 16}}})
+    eng = LLMEngine(TransformerModel(cfg, w, tp), serving, tp, num_blocks=64, num_host_blocks=0)
+    eng.attach_control_group(dist.group.WORLD)
+    if rank == 0:
+        out.put(_mm_run(eng))
+        eng.shutdown_followers()
+    else:
+        eng.follow()
+    dist.destroy_process_group()
+
+
+def test_tp2_multimodal_inputs_reach_the_follower():
+    """Spliced embeddings and three-axis positions are part of the step plan the driver broadcasts."""
+    cfg = _mm_cfg()
+    w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32)
+    serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 64,
+                                                                     "max_token_len": 128, "split_fuse_token_num": 16}}})
+    want = _mm_run(LLMEngine(TransformerModel(cfg, w), serving, num_blocks=64, num_host_blocks=0))
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_mm_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == want
