@@ -732,7 +732,7 @@ class LLMEngine:
             if h[34]:
                 self.runner.fixup_inputs(meta)
             if self.pipeline is not None and self.pipeline.topo.num_stages > 1:
-                self._pipeline_step_follower(meta)
+                self._pipeline_step_follower(meta, bool(h[30]))
                 continue
             hidden = self.runner.forward(meta, refit)
             self.runner.sample(hidden, meta, None, bool(h[30]))
@@ -777,15 +777,18 @@ class LLMEngine:
 
     def _collect_micro_batch(self, mb: int) -> int:
         from .sampler import SampleOutput
-        plan, n = self._mb_inflight[mb]
+        plan, n, rows, greedy = self._mb_inflight[mb]
         self._mb_inflight[mb] = None
         pl = self.pipeline
-        toks = []
-        if n:
-            toks = pl.channel.recv_tokens(n, pl.topo.num_stages * pl.topo.tp_size - pl.topo.tp_size).to("cpu").tolist()
+        last = pl.topo.num_stages * pl.topo.tp_size - pl.topo.tp_size
+        out = SampleOutput(tokens=[], logprobs=[], chosen_logprob=[])
+        if n and greedy:
+            toks = pl.channel.recv_tokens(n, last).to("cpu").tolist()
             self.runner.d2h_bytes += 4 * n
-        with self.lock:
             out = SampleOutput(tokens=toks, logprobs=[None] * n, chosen_logprob=[None] * n)
+        elif n:
+            out = self.runner.sampler.sample(pl.channel.recv_logits(n, self.cfg.vocab_size, last), rows)
+        with self.lock:
             got = self._apply_results(plan, out, None, None)
         self.mbc.collected(mb)
         return got
@@ -809,9 +812,7 @@ class LLMEngine:
             self.runner.staging.flip()
             layout = self.sched.pack(plan, self.runner.staging.host_np, self.runner.max_blocks_per_seq)
             rows, greedy, refit = self._sample_rows(plan)
-        if not greedy:
-            raise NotImplementedError("pipeline-parallel serving samples greedily")
-        self._broadcast_plan(layout, plan, True)
+        self._broadcast_plan(layout, plan, greedy)
         self.runner.apply_flexible(plan.flexible)
         self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
         meta = self.runner.upload(layout)
@@ -819,36 +820,44 @@ class LLMEngine:
         self.mbc.start(mb)
         self.pipeline.run(meta, self.runner.kv_caches, refit)  # first stage: forward + send, returns None
         self.mbc.done(mb)  # this stage is free for the next micro-batch; the results are still travelling
-        self._mb_inflight[mb] = (plan, meta.total_logits)
+        self._mb_inflight[mb] = (plan, meta.total_logits, rows, greedy)
         self.step_count += 1
         self.stats["steps"] += 1
         return n_new
 
     def _pipeline_step_driver(self, meta, refit, rows, greedy):
         from .sampler import SampleOutput
-        if not greedy:
-            raise NotImplementedError("pipeline-parallel serving samples greedily (top-k/top-p state lives on the "
-                                      "driver, the logits on the last stage)")
         pl = self.pipeline
         hidden = pl.run(meta, self.runner.kv_caches, refit)
         n = meta.total_logits
         if n == 0:
             return SampleOutput(tokens=[]), hidden
+        last = pl.topo.num_stages * pl.topo.tp_size - pl.topo.tp_size
+        if not greedy:
+            # sampling state lives here, the logits on the last stage: it returns the rows' logits
+            logits = self.model.compute_logits(hidden, meta.logits_idx) if pl.topo.is_last else \
+                pl.channel.recv_logits(n, self.cfg.vocab_size, last)
+            return self.runner.sampler.sample(logits, rows), hidden
         if pl.topo.is_last:
             toks = self.model.greedy_tokens(hidden, meta.logits_idx)
         else:
-            toks = pl.channel.recv_tokens(n, pl.topo.num_stages * pl.topo.tp_size - pl.topo.tp_size)
+            toks = pl.channel.recv_tokens(n, last)
         host = toks.to("cpu").tolist()
         self.runner.d2h_bytes += 4 * n
         return SampleOutput(tokens=host, logprobs=[None] * n, chosen_logprob=[None] * n), hidden
 
-    def _pipeline_step_follower(self, meta) -> None:
+    def _pipeline_step_follower(self, meta, greedy: bool = True) -> None:
         pl = self.pipeline
         hidden = pl.run(meta, self.runner.kv_caches)
         if pl.topo.is_last and meta.total_logits:
-            toks = self.model.greedy_tokens(hidden, meta.logits_idx)
-            if pl.topo.tp_rank == 0:
-                pl.channel.send_tokens(toks, 0)
+            if greedy:
+                toks = self.model.greedy_tokens(hidden, meta.logits_idx)
+                if pl.topo.tp_rank == 0:
+                    pl.channel.send_tokens(toks, 0)
+            else:
+                logits = self.model.compute_logits(hidden, meta.logits_idx)
+                if pl.topo.tp_rank == 0:
+                    pl.channel.send_logits(logits, 0)
 
     def shutdown_followers(self) -> None:
         if self._has_followers() and self.is_driver and self._ctl is not None:

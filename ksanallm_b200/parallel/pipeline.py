@@ -96,6 +96,20 @@ class HiddenChannel:
         self._pending_sends = [(w, b) for w, b in getattr(self, "_pending_sends", []) if not w.is_completed()]
         self._pending_sends.append((dist.isend(buf, dst=dst_rank, group=self.group), buf))
 
+    def send_logits(self, logits: torch.Tensor, dst_rank: int = 0) -> None:
+        """Rows that are not sampled greedily: the sampling state (penalties, generators, grammar masks) lives on the
+        driver, so the last stage returns the fp32 logits of those rows instead of tokens (non-blocking, see
+        send_tokens). The reference returns the hidden states to the chief node, which owns lm_head + sampler
+        (runtime/llm_runtime.cpp:76-110); here lm_head stays with the last stage."""
+        buf = logits.float().contiguous()
+        self._pending_sends = [(w, b) for w, b in getattr(self, "_pending_sends", []) if not w.is_completed()]
+        self._pending_sends.append((dist.isend(buf, dst=dst_rank, group=self.group), buf))
+
+    def recv_logits(self, count: int, vocab: int, src_rank: int) -> torch.Tensor:
+        buf = torch.empty(count, vocab, dtype=torch.float32, device=self.device)
+        dist.recv(buf, src=src_rank, group=self.group)
+        return buf
+
     def recv_tokens(self, count: int, src_rank: int) -> torch.Tensor:
         buf = torch.empty(count, dtype=torch.int32, device=self.device)
         dist.recv(buf, src=src_rank, group=self.group)

@@ -59,7 +59,11 @@ def _serving():
 PROMPTS = [[5, 9, 77, 120, 33, 4, 8], [400, 3, 3, 19, 250, 7, 7, 7, 91, 12, 13], [8, 6, 4]]
 
 
-def _worker(rank, world, port, out, micro_batches=1):
+GREEDY = dict(topk=1, max_new_tokens=6, ignore_eos=True)
+SAMPLED = dict(topk=20, topp=0.9, temperature=0.8, repetition_penalty=1.1, seed=1234, max_new_tokens=6, ignore_eos=True)
+
+
+def _worker(rank, world, port, out, micro_batches=1, sampling=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     topo = StageTopology(world, 1, rank)
@@ -74,7 +78,7 @@ def _worker(rank, world, port, out, micro_batches=1):
     eng.attach_pipeline(PipelineStage(model, topo, HiddenChannel(topo, cfg.hidden_size, torch.float32,
                                                                  torch.device("cpu"))), micro_batches)
     if rank == 0:
-        reqs = eng.generate(PROMPTS, SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True))
+        reqs = eng.generate(PROMPTS, SamplingParams(**(sampling or GREEDY)))
         eng.shutdown_followers()
         out.put(([r.output_token_ids[0] for r in reqs], list(getattr(eng, "mbc").history)))
     else:
@@ -107,3 +111,29 @@ def test_pp2_matches_single_process(micro_batches):
     assert got == want
     if micro_batches == 2:
         assert set(history) == {0, 1}, "both micro-batches must have carried work"
+
+
+@pytest.mark.parametrize("micro_batches", [1, 2])
+def test_pp2_seeded_sampling_matches_single_process(micro_batches):
+    """Top-k / top-p / temperature / repetition penalty with a per-request seed: the last stage returns the rows'
+    logits, the driver samples, and the tokens equal the single-process run with the same seed."""
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32)
+    eng = LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=64, num_host_blocks=0)
+    want = [r.output_token_ids[0] for r in eng.generate(PROMPTS, SamplingParams(**SAMPLED))]
+    greedy = [r.output_token_ids[0] for r in eng.generate(PROMPTS, SamplingParams(**GREEDY))]
+    assert want != greedy
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, micro_batches, SAMPLED)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got, _ = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    assert got == want
