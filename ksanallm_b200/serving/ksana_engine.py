@@ -212,12 +212,37 @@ class KsanaLLMEngine:
             (torch.bfloat16 if device.type == "cuda" else getattr(torch, cfg.torch_dtype, torch.float32))
         qmethod = self.serving.setting.quantization_config.weight.quant_method
         quantize = {"fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "int4": "int4"}.get(qmethod)
-        weights = load_model_weights(cfg, "" if a.synthetic_model else a.model_dir, tp.rank, tp.size, device, dtype,
-                                     quantize, synthetic_seed=0 if a.synthetic_model else None)
         bs = self.serving.setting.batch_scheduler
-        if tp.size > 1 and device.type == "cuda":
+        g = self.serving.setting.global_
+        world_tp = tp
+        topo = layer_range = None
+        if g.pipeline_para_size > 1:
+            # pipeline stages: world = stages x tensor_para_size, stage-major rank order; every stage gets its own
+            # tensor-parallel group and a contiguous layer range (reference: PipelineConfig + layer allocation in
+            # distributed/control_channel.cpp, here parallel/pipeline.py)
+            import torch.distributed as dist
+            from ..parallel.pipeline import StageTopology, split_layers
+            if world_tp.size != g.pipeline_para_size * g.tensor_para_size:
+                raise ValueError(f"pipeline_para_size x tensor_para_size = {g.pipeline_para_size * g.tensor_para_size}"
+                                 f" but {world_tp.size} ranks were started")
+            topo = StageTopology(world_tp.size, g.tensor_para_size, world_tp.rank)
+            layer_range = split_layers(cfg.num_layers, topo.num_stages)[topo.stage]
+            stage_group = None
+            for st in range(topo.num_stages):  # every rank creates every group, in the same order
+                ranks = list(range(st * topo.tp_size, (st + 1) * topo.tp_size))
+                grp = dist.new_group(ranks) if topo.tp_size > 1 else None
+                if st == topo.stage:
+                    stage_group = grp
+            tp = TPGroup(topo.tp_rank, topo.tp_size, stage_group, device, use_fused=False) if topo.tp_size > 1 \
+                else TPGroup(0, 1, None, device, use_fused=False)
+        weights = load_model_weights(cfg, "" if a.synthetic_model else a.model_dir, tp.rank, tp.size, device, dtype,
+                                     quantize, synthetic_seed=0 if a.synthetic_model else None,
+                                     layer_range=layer_range)
+        if tp.size > 1 and device.type == "cuda" and topo is None:
             tp.init_fused(cfg.hidden_size, bs.max_step_tokens)
-        model = TransformerModel(cfg, weights, tp, max_positions=max(bs.max_token_len, 2048))
+        model = TransformerModel(cfg, weights, tp, max_positions=max(bs.max_token_len, 2048), layer_range=layer_range)
+        if topo is not None and not topo.is_last:
+            model.norm_w = None  # the next stage continues from the un-normalised residual stream
         self.tokenizer = TokenizerProcessor(a.tokenizer_path or a.model_dir, cfg.vocab_size,
                                             self.serving.setting.tokenization.add_special_tokens,
                                             self.serving.setting.tokenization.skip_special_tokens, a.chat_template)
@@ -230,20 +255,25 @@ class KsanaLLMEngine:
                 apply_kv_scales(model, load_kv_cache_scales(scales_file, tp.rank, cfg.num_layers))
         self.llm = LLMEngine(model, self.serving, tp, detokenize=lambda ids: self.tokenizer.decode(ids),
                              kv_dtype=kv_dtype)
-        if tp.size > 1:
+        if world_tp.size > 1:
             import torch.distributed as dist
             self.llm.attach_control_group(dist.new_group(backend="gloo"))
+        if topo is not None:
+            from ..parallel.pipeline import HiddenChannel, PipelineStage
+            self.llm.attach_pipeline(PipelineStage(model, topo, HiddenChannel(topo, cfg.hidden_size, dtype, device)),
+                                     max(int(bs.max_pp_batch_num), 1))
+        self.is_driver = world_tp.rank == 0
         self._load_plugin()
         self.connector = None
         cs = self.serving.setting.connector
-        if cs.group_role in ("prefill", "decode", "both") and tp.rank == 0:
+        if cs.group_role in ("prefill", "decode", "both") and world_tp.rank == 0:
             from .connector import PDConnector
             self.connector = PDConnector(self.llm, cs)
             self.connector.start()
         from ..ops import gemm_tune
         gemm_tune.maybe_load_from_env()  # KSANA_GEMM_TUNE_FILE written by benchmarks/search_best_gemm.py
-        if tp.rank == 0:
-            if os.environ.get("KSANA_SKIP_WARMUP", "0") != "1" and tp.size == 1:
+        if world_tp.rank == 0:
+            if os.environ.get("KSANA_SKIP_WARMUP", "0") != "1" and world_tp.size == 1:
                 # multi-rank instances warm up through their first requests: the followers only enter their loop
                 # after initialisation returns
                 self.llm.warmup(max_len=min(2048, self.serving.setting.batch_scheduler.max_token_len))
