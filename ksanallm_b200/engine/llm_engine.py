@@ -170,6 +170,8 @@ class LLMEngine:
         self._complex_requests = 0  # live requests that need per-token host state (grammar, beams, penalties, ...)
         self.dp = None              # parallel.attn_dp.DPCoordinator under attention data parallelism
         self.adp_balance = None     # parallel.attn_dp.ADPBalance (attention_dp_lb_config.enable_balance)
+        self.dp_router = None       # parallel.attn_dp.DPRequestRouter on the rank that owns the HTTP front-end
+        self.dp_worker = None       # parallel.attn_dp.DPRequestWorker on the other DP ranks
         self._dp_arrivals = 0
         self.dp_any_work = True
 
@@ -213,14 +215,33 @@ class LLMEngine:
 
     # ---- request intake --------------------------------------------------------------------------------
     def add_request(self, prompt_tokens: Sequence[int], params: Optional[SamplingParams] = None,
-                    refit=None, grammar=None, probe=None, mrope_positions=None) -> Request:
+                    refit=None, grammar=None, probe=None, mrope_positions=None, local: bool = False) -> Request:
         """``mrope_positions``: [3, prompt_len] (temporal, height, width) positions of the prompt tokens for models
-        with multimodal RoPE; generated tokens continue from max + 1 on all three axes."""
+        with multimodal RoPE; generated tokens continue from max + 1 on all three axes. Under served attention data
+        parallelism the request may be placed on another DP rank (``local`` forces this rank)."""
         params = params or SamplingParams()
         params.verify()
         now = time.time()
         req = Request(next(self._ids), list(int(t) for t in prompt_tokens), params, now)
         req.refit, req.grammar, req.probe = refit, grammar, probe
+        if self.dp_router is not None and not local:
+            weight = len(req.prompt_tokens) + params.max_new_tokens
+            plain = (refit is None and grammar is None and probe is None and mrope_positions is None and
+                     max(params.num_beams, params.num_return_sequences, 1) == 1 and not params.logprobs and
+                     not self._needs_host_tokens(params, req))
+            rank = self.dp_router.place(weight) if plain else 0
+            if not plain:
+                self.dp_router.load[0] += weight
+            req.dp_weight = weight
+            if rank != 0:
+                # runs in another rank's engine; its progress is mirrored into this object by the router's reader
+                if len(req.prompt_tokens) >= self.sched_cfg.max_token_len:
+                    self.dp_router.release(rank, weight)
+                    raise EngineError(_host.RET_INPUT_LENGTH_EXCEEDED, "input length exceeds max_token_len")
+                req.seqs.append(SequenceOutput(-req.req_id))
+                self.stats["prompt_tokens"] += len(req.prompt_tokens)
+                self.dp_router.submit(rank, req, weight)
+                return req
         if mrope_positions is not None:
             axes = self._rope_axes()
             mp = torch.as_tensor(mrope_positions, dtype=torch.int32).reshape(axes, -1)
@@ -293,6 +314,9 @@ class LLMEngine:
         return so
 
     def abort(self, req: Request) -> None:
+        if getattr(req, "dp_remote", None) is not None:
+            self.dp_router.abort(req)
+            return
         with self.lock:
             req.aborted = True
             for s in req.seqs:
@@ -613,6 +637,8 @@ class LLMEngine:
             req.finished = True
             req.finish_time = time.time()
             self.requests.pop(req.req_id, None)
+            if self.dp_router is not None and getattr(req, "dp_weight", 0):
+                self.dp_router.release(0, req.dp_weight)
             if getattr(req, "_complex", False):
                 req._complex = False
                 self._complex_requests -= 1
@@ -903,6 +929,9 @@ class LLMEngine:
         self._stop.clear()
 
         def loop():
+            if self.dp is not None:
+                self.serve_dp()
+                return
             while not self._stop.is_set():
                 if self.has_unfinished():
                     try:
@@ -916,12 +945,32 @@ class LLMEngine:
         self._loop_thread = threading.Thread(target=loop, name="ksana-step-loop", daemon=True)
         self._loop_thread.start()
 
+    def serve_dp(self) -> None:
+        """Step loop of a served attention-DP rank: all ranks step together for as long as the instance lives (the
+        MoE exchange and the per-step agreement are collectives), idling briefly when nobody has work; a shutdown
+        requested on any rank reaches all of them in the same step."""
+        while True:
+            try:
+                self._step_sync()
+            except Exception as ex:
+                self._fail_all(ex)
+            if self.dp_worker is not None:
+                self.dp_worker.report()
+            if self.dp.stopping:
+                return
+            if not self.dp_any_work:
+                time.sleep(0.002)
+
     def stop(self) -> None:
         self._stop.set()
         self._wake.set()
+        if self.dp is not None:
+            self.dp.stop_requested = True
         if self._loop_thread is not None:
             self._loop_thread.join(timeout=10)
             self._loop_thread = None
+        if self.dp_router is not None:
+            self.dp_router.close()
         self.shutdown_followers()
 
     def _fail_all(self, ex: Exception) -> None:

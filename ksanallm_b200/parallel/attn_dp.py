@@ -10,7 +10,11 @@ still run a step (batch_scheduler/batch_scheduler.cpp:472-519) and the cross-DP 
 from __future__ import annotations
 
 import time
-from typing import Optional, Tuple
+import threading
+import struct
+import socket
+import json
+from typing import Any, Dict, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -29,9 +33,14 @@ class DPCoordinator:
         self.size = dist.get_world_size(group)
 
     def sync(self, local_tokens: int, has_unfinished: bool) -> Tuple[int, bool]:
-        t = torch.tensor([local_tokens, 1 if has_unfinished else 0], dtype=torch.int64, device=self.device)
+        t = torch.tensor([local_tokens, 1 if has_unfinished else 0, 1 if self.stop_requested else 0],
+                         dtype=torch.int64, device=self.device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        self.stopping = bool(t[2])  # every rank learns of a shutdown in the same step and leaves the loop together
         return int(t[0]), bool(t[1])
+
+    stop_requested = False
+    stopping = False
 
 
 class ADPBalance:
@@ -126,3 +135,200 @@ class GatherEPExchange:
         dist.all_reduce(y, group=self.group)
         out = y[self.rank * t_stride:self.rank * t_stride + T].to(x.dtype)
         return out if add is None else out + add
+
+
+# ---- request distribution for a served DP instance ------------------------------------------------------------------
+# One process per GPU means one scheduler per DP rank, but a served instance has ONE HTTP front-end (rank 0). Rank 0
+# deals every request to the least loaded rank (the reference: BatchScheduler::BalanceWaitingReqs deals its waiting
+# pool over the attention-DP groups by token load, batch_scheduler_balance_reqs_algo.cpp:11-55); remote ranks run the
+# request in their own engine and stream the new tokens back over a TCP link.
+
+def _send_msg(sock: socket.socket, obj) -> None:
+    data = json.dumps(obj).encode()
+    sock.sendall(struct.pack("<I", len(data)) + data)
+
+
+def _recv_msg(sock: socket.socket):
+    hdr = b""
+    while len(hdr) < 4:
+        c = sock.recv(4 - len(hdr))
+        if not c:
+            return None
+        hdr += c
+    n = struct.unpack("<I", hdr)[0]
+    buf = bytearray()
+    while len(buf) < n:
+        c = sock.recv(min(n - len(buf), 1 << 20))
+        if not c:
+            return None
+        buf += c
+    return json.loads(bytes(buf))
+
+
+class DPRequestRouter:
+    """Rank 0: owns the links to the other DP ranks, places requests, mirrors remote progress into local Request
+    objects so that the serving layer streams them like its own."""
+
+    def __init__(self, engine, host: str, port: int, world: int, accept_timeout: float = 120.0):
+        self.engine, self.world = engine, world
+        self.links: Dict[int, socket.socket] = {}
+        self.load = [0] * world          # outstanding prompt + budgeted output tokens per rank
+        self.remote: Dict[int, Tuple[Any, int, int]] = {}  # rid -> (Request, rank, weight)
+        self.lock = threading.Lock()
+        self._rid = 0
+        self.placed = [0] * world
+        srv = socket.socket()
+        srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        srv.bind((host, port))
+        srv.listen(world)
+        srv.settimeout(accept_timeout)
+        self.port = srv.getsockname()[1]
+        self._srv = srv
+
+    def accept_all(self) -> None:
+        while len(self.links) < self.world - 1:
+            conn, _ = self._srv.accept()
+            hello = _recv_msg(conn)
+            self.links[int(hello["rank"])] = conn
+            threading.Thread(target=self._reader, args=(int(hello["rank"]), conn), daemon=True).start()
+        self._srv.close()
+
+    def place(self, n_tokens: int) -> int:
+        with self.lock:
+            r = min(range(self.world), key=lambda i: (self.load[i], i))
+            self.load[r] += n_tokens
+            self.placed[r] += 1
+            return r
+
+    def release(self, rank: int, n_tokens: int) -> None:
+        with self.lock:
+            self.load[rank] -= n_tokens
+
+    def submit(self, rank: int, req, weight: int) -> None:
+        import dataclasses
+        with self.lock:
+            self._rid += 1
+            rid = self._rid
+            self.remote[rid] = (req, rank, weight)
+        req.dp_remote = (rank, rid)
+        _send_msg(self.links[rank], {"op": "add", "rid": rid, "tokens": list(req.prompt_tokens),
+                                     "params": dataclasses.asdict(req.params)})
+
+    def abort(self, req) -> None:
+        rank, rid = req.dp_remote
+        try:
+            _send_msg(self.links[rank], {"op": "abort", "rid": rid})
+        except OSError:
+            pass
+
+    def _reader(self, rank: int, conn: socket.socket) -> None:
+        while True:
+            try:
+                m = _recv_msg(conn)
+            except OSError:
+                m = None
+            if m is None:
+                break
+            with self.lock:
+                ent = self.remote.get(m["rid"])
+            if ent is None:
+                continue
+            req, _, weight = ent
+            so = req.seqs[0]
+            so.output_tokens.extend(m.get("tokens", []))
+            now = time.time()
+            if m.get("tokens") and req.first_token_time is None:
+                req.first_token_time = now
+            req.token_times.extend([now] * len(m.get("tokens", [])))
+            if m.get("finished"):
+                so.finished, so.finish_reason = True, m.get("reason")
+                if m.get("error"):
+                    from ..engine.llm_engine import EngineError
+                    req.error = EngineError(int(m.get("code", 7)), m["error"])
+                req.finished, req.finish_time = True, now
+                with self.lock:
+                    self.remote.pop(m["rid"], None)
+                self.release(rank, weight)
+            req.notify()
+        # a lost link fails what that rank still owed
+        with self.lock:
+            lost = [(rid, e) for rid, e in self.remote.items() if e[1] == rank]
+        for rid, (req, _, weight) in lost:
+            from ..engine.llm_engine import EngineError
+            req.error = EngineError(7, f"attention-DP rank {rank} is gone")
+            req.seqs[0].finished = req.finished = True
+            req.notify()
+
+    def close(self) -> None:
+        for c in self.links.values():
+            try:
+                c.close()
+            except OSError:
+                pass
+
+
+class DPRequestWorker:
+    """Ranks > 0: receives requests from rank 0, runs them in the local engine, reports progress after every step."""
+
+    def __init__(self, engine, host: str, port: int, rank: int, connect_timeout: float = 120.0):
+        self.engine, self.rank = engine, rank
+        deadline = time.time() + connect_timeout
+        while True:
+            try:
+                self.sock = socket.create_connection((host, port), timeout=5)
+                break
+            except OSError:
+                if time.time() > deadline:
+                    raise
+                time.sleep(0.1)
+        self.sock.settimeout(None)
+        _send_msg(self.sock, {"rank": rank})
+        self.active: Dict[int, Tuple[Any, int]] = {}  # rid -> (Request, tokens already reported)
+        self.lock = threading.Lock()
+        threading.Thread(target=self._reader, daemon=True).start()
+
+    def _reader(self) -> None:
+        from ..engine.sampling_params import SamplingParams
+        while True:
+            try:
+                m = _recv_msg(self.sock)
+            except OSError:
+                m = None
+            if m is None:
+                return
+            if m["op"] == "add":
+                try:
+                    req = self.engine.add_request(m["tokens"], SamplingParams.from_dict(m["params"]), local=True)
+                    with self.lock:
+                        self.active[m["rid"]] = (req, 0)
+                except Exception as ex:  # reported back instead of killing the link
+                    _send_msg(self.sock, {"rid": m["rid"], "finished": True, "reason": "error", "error": str(ex),
+                                          "code": getattr(ex, "code", 7)})
+            elif m["op"] == "abort":
+                with self.lock:
+                    ent = self.active.get(m["rid"])
+                if ent is not None:
+                    self.engine.abort(ent[0])
+
+    def report(self) -> None:
+        """Called by the step loop after every step."""
+        with self.lock:
+            items = list(self.active.items())
+        for rid, (req, sent) in items:
+            toks = req.seqs[0].output_tokens if req.seqs else []
+            if len(toks) == sent and not req.finished:
+                continue
+            msg = {"rid": rid, "tokens": list(toks[sent:]), "finished": bool(req.finished)}
+            if req.finished:
+                msg["reason"] = req.seqs[0].finish_reason if req.seqs else "error"
+                if req.error is not None:
+                    msg["error"], msg["code"] = str(req.error), req.error.code
+            try:
+                _send_msg(self.sock, msg)
+            except OSError:
+                return
+            with self.lock:
+                if req.finished:
+                    self.active.pop(rid, None)
+                else:
+                    self.active[rid] = (req, len(toks))

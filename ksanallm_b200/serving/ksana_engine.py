@@ -235,9 +235,31 @@ class KsanaLLMEngine:
                     stage_group = grp
             tp = TPGroup(topo.tp_rank, topo.tp_size, stage_group, device, use_fused=False) if topo.tp_size > 1 \
                 else TPGroup(0, 1, None, device, use_fused=False)
+        dp_world = None
+        ep_rank = ep_size = None
+        if g.attn_data_para_size > 1:
+            # attention data parallelism: every rank is a DP group of its own (attention / dense weights replicated,
+            # own scheduler and KV cache), the routed experts are sharded over all ranks (reference: attn_data_para_size
+            # + expert_para_size, service/inference_engine.cpp:201-260)
+            if topo is not None or g.attn_data_para_size != world_tp.size:
+                raise ValueError("attn_data_para_size must equal the number of ranks (DP groups of one GPU) and "
+                                 "cannot be combined with pipeline stages")
+            dp_world = world_tp
+            tp = TPGroup(0, 1, None, device, use_fused=False)
+            if cfg.is_moe:
+                ep_rank, ep_size = dp_world.rank, dp_world.size
+                tp.ep_rank, tp.ep_size = ep_rank, ep_size
+                if device.type == "cuda" and 2 <= dp_world.size <= 8 and cfg.num_experts % dp_world.size == 0:
+                    from ..parallel.ep import EPExchange
+                    tp.ep = EPExchange(dp_world.group, dp_world.rank, dp_world.size, device, cfg.hidden_size,
+                                       cfg.num_experts_per_tok, cfg.num_experts, bs.max_step_tokens)
+                else:
+                    from ..parallel.attn_dp import GatherEPExchange
+                    tp.ep = GatherEPExchange(dp_world.group, dp_world.rank, dp_world.size, cfg.num_experts_per_tok,
+                                             cfg.num_experts)
         weights = load_model_weights(cfg, "" if a.synthetic_model else a.model_dir, tp.rank, tp.size, device, dtype,
                                      quantize, synthetic_seed=0 if a.synthetic_model else None,
-                                     layer_range=layer_range)
+                                     layer_range=layer_range, ep_rank=ep_rank, ep_size=ep_size)
         if tp.size > 1 and device.type == "cuda" and topo is None:
             tp.init_fused(cfg.hidden_size, bs.max_step_tokens)
         model = TransformerModel(cfg, weights, tp, max_positions=max(bs.max_token_len, 2048), layer_range=layer_range)
@@ -255,7 +277,20 @@ class KsanaLLMEngine:
                 apply_kv_scales(model, load_kv_cache_scales(scales_file, tp.rank, cfg.num_layers))
         self.llm = LLMEngine(model, self.serving, tp, detokenize=lambda ids: self.tokenizer.decode(ids),
                              kv_dtype=kv_dtype)
-        if world_tp.size > 1:
+        if dp_world is not None:
+            import torch.distributed as dist
+            from ..parallel.attn_dp import DPCoordinator, DPRequestRouter, DPRequestWorker
+            self.llm.attach_dp(DPCoordinator(dp_world.group, device if device.type == "cuda" else None))
+            host = os.environ.get("MASTER_ADDR", "127.0.0.1")
+            port = int(os.environ.get("KSANA_DP_PORT", int(os.environ.get("MASTER_PORT", "29511")) + 17))
+            if dp_world.rank == 0:
+                self.llm.dp_router = DPRequestRouter(self.llm, host, port, dp_world.size)
+                dist.barrier(group=dp_world.group)  # the listener exists before anybody connects
+                self.llm.dp_router.accept_all()
+            else:
+                dist.barrier(group=dp_world.group)
+                self.llm.dp_worker = DPRequestWorker(self.llm, host, port, dp_world.rank)
+        elif world_tp.size > 1:
             import torch.distributed as dist
             self.llm.attach_control_group(dist.new_group(backend="gloo"))
         if topo is not None:
@@ -280,8 +315,12 @@ class KsanaLLMEngine:
             self.llm.start()
 
     def serve_follower(self) -> None:
-        """Blocks in the follower loop (ranks > 0)."""
-        self.llm.follow()
+        """Blocks in the follower loop (ranks > 0): executes rank 0's plans (TP / PP), or - as an attention-DP rank -
+        runs its own scheduler on the requests rank 0 places here."""
+        if self.llm.dp is not None:
+            self.llm.serve_dp()
+        else:
+            self.llm.follow()
 
     def shutdown(self) -> None:
         if getattr(self, "connector", None) is not None:

@@ -20,34 +20,44 @@ def _serving(**glob):
         "block_manager": {"block_token_num": 16}}})
 
 
-def _engine(**glob):
-    eng = KsanaLLMEngine(EngineArgs(config_file="", synthetic_model="tiny-llama", device="cpu", serving=_serving(**glob)))
+def _engine(model="tiny-llama", **glob):
+    eng = KsanaLLMEngine(EngineArgs(config_file="", synthetic_model=model, device="cpu", serving=_serving(**glob)))
     eng.initialize()
     return eng
 
 
-def _worker(rank, world, port, out, glob):
+def _bodies(n):
+    out = []
+    for k in range(n):
+        b = dict(BODY)
+        b["input_tokens"] = [(t + 11 * k) % 200 + 3 for t in BODY["input_tokens"]][:23 - 3 * k]
+        out.append(b)
+    return out
+
+
+def _worker(rank, world, port, out, glob, model="tiny-llama", n=3):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank), KSANA_SKIP_WARMUP="1")
-    eng = _engine(**glob)
+    eng = _engine(model, **glob)
     if rank == 0:
         async def run():
-            return await asyncio.gather(*[eng.generate(dict(BODY), streamer=False) for _ in range(3)])
+            return await asyncio.gather(*[eng.generate(b, streamer=False) for b in _bodies(n)])
         res = asyncio.run(run())
-        out.put([o.output_tokens[0] for st, o in res if st.OK()])
+        placed = list(eng.llm.dp_router.placed) if eng.llm.dp_router is not None else []
+        out.put(([o.output_tokens[0] for st, o in res if st.OK()], placed))
         eng.shutdown()
     else:
         eng.serve_follower()
 
 
-def _spawn(world, glob):
+def _spawn(world, glob, model="tiny-llama", n=3):
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, glob)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, glob, model, n)) for r in range(world)]
     for p in procs:
         p.start()
     got = q.get(timeout=180)
@@ -57,21 +67,36 @@ def _spawn(world, glob):
     return got
 
 
+def _single(model, n):
+    os.environ["KSANA_SKIP_WARMUP"] = "1"
+    eng = _engine(model)
+    outs = []
+    for b in _bodies(n):
+        st, out = asyncio.run(eng.generate(b, streamer=False))
+        assert st.OK()
+        outs.append(out.output_tokens[0])
+    eng.shutdown()
+    return outs
+
+
 @pytest.fixture(scope="module")
 def want():
-    os.environ["KSANA_SKIP_WARMUP"] = "1"
-    eng = _engine()
-    st, out = asyncio.run(eng.generate(dict(BODY), streamer=False))
-    eng.shutdown()
-    assert st.OK()
-    return out.output_tokens[0]
+    return _single("tiny-llama", 3)
 
 
 def test_pipeline_stages_from_serving_config(want):
-    got = _spawn(2, dict(pipeline_para_size=2, tensor_para_size=1))
-    assert got == [want, want, want]
+    got, _ = _spawn(2, dict(pipeline_para_size=2, tensor_para_size=1))
+    assert got == want
 
 
 def test_tensor_parallel_from_serving_config(want):
-    got = _spawn(2, dict(tensor_para_size=2))
-    assert got == [want, want, want]
+    got, _ = _spawn(2, dict(tensor_para_size=2))
+    assert got == want
+
+
+def test_attention_dp_with_expert_parallel_from_serving_config():
+    """Two DP ranks, experts sharded over them; rank 0 owns the front-end and deals the requests by load."""
+    want = _single("tiny-moe", 4)
+    got, placed = _spawn(2, dict(tensor_para_size=2, attn_data_para_size=2, expert_para_size=2), "tiny-moe", 4)
+    assert got == want
+    assert placed == [2, 2]
