@@ -261,6 +261,10 @@ class MoEFFN:
         self.bias = w.get(prefix + ".gate.e_score_correction_bias")
         self.w_gate_up = w[prefix + ".experts.up_gate_proj.weight"]  # [E_local, 2I, H]
         self.w_down = w[prefix + ".experts.down_proj.weight"]        # [E_local, H, I]
+        # block-scaled fp8 experts (DeepSeek-V3 checkpoints, or quant_method fp8): e4m3 weights + one fp32 scale per
+        # 128 x 128 block; they stay in fp8 and every expert's two GEMMs run through the block-scaled fp8 GEMM
+        self.s_gate_up = w.get(prefix + ".experts.up_gate_proj.weight_scale_inv")
+        self.s_down = w.get(prefix + ".experts.down_proj.weight_scale_inv")
         self.e_local = self.w_gate_up.shape[0]
         self.expert_offset = tp.ep_rank * self.e_local if self.e_local < cfg.num_experts else 0
         self.shared = None
@@ -272,6 +276,8 @@ class MoEFFN:
         """Per-rank partial sum of the block output (needs a cross-rank sum when size > 1)."""
         c = self.cfg
         ep = self.tp.ep
+        if self.s_gate_up is not None:
+            ep = None  # the dispatch / combine kernels and the gathered exchange take bf16 expert weights
         if ep is not None and self.tp.ep_dp and self.e_local < c.num_experts:
             return self._dp_exchange(h, ep)
         if (ep is not None and h.is_cuda and h.dtype == torch.bfloat16 and self.e_local < c.num_experts and
@@ -283,7 +289,10 @@ class MoEFFN:
         else:
             ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
                                      c.topk_group, c.routed_scaling_factor, self.bias)
-            y = ops.moe_experts(h, ids, wts, self.w_gate_up, self.w_down, self.expert_offset)
+            if self.s_gate_up is not None:
+                y = self._fp8_experts(h, ids, wts)
+            else:
+                y = ops.moe_experts(h, ids, wts, self.w_gate_up, self.w_down, self.expert_offset)
         if self.shared is not None:
             s = self.shared.down(self.shared.core(h), add_bias=self.tp.rank == 0)
             if self.shared_gate is not None:
@@ -291,6 +300,31 @@ class MoEFFN:
                 s = s * g
             y = y + s
         return y
+
+    def _fp8_experts(self, h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor) -> torch.Tensor:
+        """Local experts with block-scaled fp8 weights: tokens are grouped by expert on the host and each group goes
+        through two fp8 GEMMs (activations quantised per token per 128 channels). One launch pair per active expert,
+        not a grouped kernel."""
+        T, H = h.shape
+        out = torch.zeros(T, H, dtype=torch.float32, device=h.device)
+        local = (ids >= self.expert_offset) & (ids < self.expert_offset + self.e_local)
+        tok, slot = local.nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            return out.to(h.dtype)
+        eid = (ids[tok, slot] - self.expert_offset).long()
+        order = torch.argsort(eid, stable=True)
+        tok, slot, eid = tok[order], slot[order], eid[order]
+        counts = torch.bincount(eid, minlength=self.e_local).tolist()
+        at = 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            t = tok[at:at + n]
+            a = ops.silu_and_mul(ops.linear_fp8_block(h[t], self.w_gate_up[e], self.s_gate_up[e]))
+            y = ops.linear_fp8_block(a, self.w_down[e], self.s_down[e]).float()
+            out.index_add_(0, t, y * wts[t, slot[at:at + n]].unsqueeze(-1).float())
+            at += n
+        return out.to(h.dtype)
 
     def _llama4_experts(self, h: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         """Llama 4 routing: top-k on the raw logits, score = sigmoid(logit), and the score scales the expert's

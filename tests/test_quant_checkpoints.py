@@ -100,3 +100,39 @@ def test_quantised_checkpoint_tensor_parallel_slices(fmt):
             deq = ref.dequant_int4_group(wq[p + ".qweight"], wq[p + ".scales"].float(), wq[p + ".zeros"].float(), GROUP)
             assert deq.shape == wd[p + ".weight"].shape
             assert (deq - wd[p + ".weight"]).abs().max().item() < 1e-6, (rank, stem)
+
+
+def test_fp8_block_scaled_experts_stay_fp8_and_match_dequantised_weights():
+    """A DeepSeek-V3 style checkpoint whose expert (and dense) projections are e4m3 with 128 x 128 block scales: the
+    experts stay in fp8, and the outputs agree with the same checkpoint dequantised to fp32 up to the activation
+    quantisation (one scale per token per 128 channels) the fp8 GEMM applies."""
+    import torch
+    from ksanallm_b200.config.model_config import model_config_from_dict
+    from ksanallm_b200.engine.step_input import make_step_input
+    from ksanallm_b200.models.loader import WeightLoader, synthetic_checkpoint
+    from ksanallm_b200.models.transformer import TransformerModel
+    from ksanallm_b200.ops import reference as ref
+    cfg = model_config_from_dict(dict(model_type="mixtral", hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                      num_key_value_heads=2, intermediate_size=256, num_local_experts=4,
+                                      num_experts_per_tok=2, vocab_size=300, torch_dtype="float32",
+                                      max_position_embeddings=64))
+    fp8, deq = [], []
+    for k, v in synthetic_checkpoint(cfg, seed=3, std=0.05, dtype=torch.float32):
+        if ".experts." in k and k.endswith("_proj.weight"):
+            q, s = ref.quant_fp8_block_weight(v)
+            fp8 += [(k, q), (k + "_scale_inv", s)]
+            deq.append((k, ref.dequant_fp8_block_weight(q, s)))
+        else:
+            fp8.append((k, v))
+            deq.append((k, v))
+    w8 = WeightLoader(cfg, dtype=torch.float32).load(fp8)
+    assert w8["model.layers.0.mlp.experts.up_gate_proj.weight"].dtype == torch.float8_e4m3fn
+    assert w8["model.layers.0.mlp.experts.up_gate_proj.weight_scale_inv"].shape == (4, 4, 1)
+    T = 12
+    meta = make_step_input(list(range(5, 5 + T)), list(range(T)), list(range(T)), [0, T], [T], [[0, 1]], device="cpu")
+    outs = []
+    for w in (w8, WeightLoader(cfg, dtype=torch.float32).load(deq)):
+        model = TransformerModel(cfg, w, max_positions=64)
+        outs.append(model.forward(meta, model.allocate_kv_cache(2, 16)))
+    err = (outs[0] - outs[1]).abs().max().item()
+    assert 0 < err < 0.05 * outs[1].abs().max().item()
