@@ -104,10 +104,15 @@ class NodeRegistry:
         return out
 
 
-def create_app(registry: Optional[NodeRegistry] = None, http_client_factory=None) -> FastAPI:
+def create_app(registry: Optional[NodeRegistry] = None, http_client_factory=None, provider=None) -> FastAPI:
+    """``provider``: a name_service.NameServiceProvider choosing the prefill / decode pair of every request; the
+    default reads this router's own registry."""
+    from .name_service import RegistryProvider
     reg = registry or NodeRegistry()
     app = FastAPI()
     app.state.registry = reg
+    ns = provider or RegistryProvider(reg)
+    app.state.provider = ns
 
     def client():
         if http_client_factory is not None:
@@ -148,10 +153,12 @@ def create_app(registry: Optional[NodeRegistry] = None, http_client_factory=None
 
     @app.post("/generate")
     async def generate(req: Request):
-        pair = reg.pick_pair()
+        pair = ns.get_available_nodes()
         if pair is None:
             raise HTTPException(503, "no alive prefill/decode pair")
-        (p_id, p_group, p_addr, _), (d_id, d_group, d_addr, _) = pair
+        pn, dn = pair
+        p_id, p_group, p_addr = pn["node_id"], pn["group_name"], pn["addr"]
+        d_id, d_group, d_addr = dn["node_id"], dn["group_name"], dn["addr"]
         body = await req.body()
         headers = {"kv-comm-group-key": f"{p_group}__{d_group}", "kv-comm-request-id": uuid.uuid4().hex,
                    "Content-Type": "application/json"}
@@ -160,16 +167,19 @@ def create_app(registry: Optional[NodeRegistry] = None, http_client_factory=None
         c = client()
 
         async def run():
+            p_ok = d_ok = False
             try:
                 # the prefill node computes the prompt and pushes KV to the decode node; its own reply is dropped
                 prefill_task = asyncio.create_task(c.post(f"http://{p_addr}/generate", content=body, headers=headers))
                 async with c.stream("POST", f"http://{d_addr}/generate", content=body, headers=headers) as r:
+                    d_ok = r.status_code == 200
                     async for chunk in r.aiter_bytes():
                         yield chunk
-                await prefill_task
+                p_ok = (await prefill_task).status_code == 200
             finally:
                 reg.add_inflight(p_id, -1)
                 reg.add_inflight(d_id, -1)
+                ns.update_call_result(pn, dn, p_ok, d_ok)
                 await c.aclose()
 
         return StreamingResponse(run())
@@ -184,8 +194,17 @@ def main(argv=None) -> None:
     ap.add_argument("--host", default="0.0.0.0")
     ap.add_argument("--port", type=int, default=9080)
     ap.add_argument("--db", default="router.sqlite3")
+    ap.add_argument("--name-service", default="", help="module exposing create_provider() (default: own registry)")
+    ap.add_argument("--static-pairs", default="", help="prefill_addr=decode_addr[,prefill_addr=decode_addr...]")
     ns = ap.parse_args(argv)
-    uvicorn.run(create_app(NodeRegistry(ns.db)), host=ns.host, port=ns.port)
+    provider = None
+    if ns.name_service:
+        from .name_service import load_provider
+        provider = load_provider(ns.name_service)
+    elif ns.static_pairs:
+        from .name_service import StaticProvider
+        provider = StaticProvider([tuple(x.split("=", 1)) for x in ns.static_pairs.split(",")])
+    uvicorn.run(create_app(NodeRegistry(ns.db), provider=provider), host=ns.host, port=ns.port)
 
 
 if __name__ == "__main__":
