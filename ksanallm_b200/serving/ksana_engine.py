@@ -176,6 +176,22 @@ class PyAsyncStreamingIterator:
             pass
 
 
+class _FinishedIterator:
+    """Streaming view of a request that is already complete (one item)."""
+
+    def __init__(self, out: KsanaPythonOutput):
+        self.out = out
+
+    def __aiter__(self):
+        return self
+
+    async def __anext__(self) -> KsanaPythonOutput:
+        if self.out is None:
+            raise StopAsyncIteration
+        out, self.out = self.out, None
+        return out
+
+
 class KsanaLLMEngine:
     def __init__(self, args: EngineArgs):
         self.args = args
@@ -425,8 +441,18 @@ class KsanaLLMEngine:
                 _, pd_first, _ = got
                 if pd_first:
                     import dataclasses as _dc
+                    stops = set(sp.stop_token_ids or [])
+                    if not sp.ignore_eos:
+                        stops |= set(self.model_config.eos_token_ids)
+                    left = sp.max_new_tokens - len(pd_first)
+                    if pd_first[-1] in stops or left <= 0:
+                        # the prefill instance's token already ended the request
+                        out = KsanaPythonOutput(input_tokens=list(tokens), output_tokens=[list(pd_first)],
+                                                finish_reasons=["stop" if pd_first[-1] in stops else "length"],
+                                                finished=True)
+                        return Status(), (_FinishedIterator(out) if streamer else out)
                     tokens = list(tokens) + list(pd_first)
-                    sp = _dc.replace(sp, max_new_tokens=max(sp.max_new_tokens - len(pd_first), 0))
+                    sp = _dc.replace(sp, max_new_tokens=left)
             elif pd_rid and self.connector.role == "prefill":
                 import dataclasses as _dc
                 sp = _dc.replace(sp, max_new_tokens=1)
@@ -438,7 +464,8 @@ class KsanaLLMEngine:
             return Status(ex.code, str(ex)), None
         except (ValueError, KeyError, TypeError) as ex:
             return Status(RetCode.RET_INVALID_ARGUMENT, str(ex)), None
-        if streamer:
+        handing_over = bool(pd_rid) and self.connector.role == "prefill"
+        if streamer and not handing_over:
             return Status(), PyAsyncStreamingIterator(self, req)
         loop = asyncio.get_running_loop()
         v = -1
@@ -451,6 +478,8 @@ class KsanaLLMEngine:
                                        list(req.prompt_tokens), list(req.seqs[0].output_tokens))
         if self.plugin is not None:
             self.plugin.postprocess(request_dict, out)
+        if streamer:  # a prefill instance answers a streaming request with its single item
+            return out.finish_status, _FinishedIterator(out)
         return out.finish_status, out
 
     def generate_sync(self, request_dict: Dict[str, Any]) -> Tuple[Status, Optional[KsanaPythonOutput]]:

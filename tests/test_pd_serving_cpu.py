@@ -64,6 +64,36 @@ def test_static_peer(want):
         prefill.shutdown()
 
 
+def test_streaming_requests_and_first_token_stop(want):
+    """The router forwards the client's body unchanged, so both instances may see stream=true: the prefill instance
+    still completes and exports, the decode instance streams. A first token that is a stop token ends the request on
+    the decode side without another step."""
+    decode = _make("decode")
+    prefill = _make("prefill", peer_transfer_addr="%s:%d" % decode.connector.transfer_addr)
+    try:
+        async def both(body, ctx):
+            d = asyncio.create_task(decode.generate(dict(body), streamer=True, req_ctx=ctx))
+            p = asyncio.create_task(prefill.generate(dict(body), streamer=True, req_ctx=ctx))
+            (pst, pit), (dst, dit) = await asyncio.gather(p, d)
+            assert pst.OK() and dst.OK()
+            last = None
+            async for item in dit:
+                last = item
+            return [x async for x in pit], last
+
+        p_items, last = asyncio.run(both(BODY, {"kv-comm-request-id": "s1"}))
+        assert len(p_items) == 1 and last.finished and last.output_tokens == want.output_tokens
+        stop_body = dict(BODY, sampling_config=dict(BODY["sampling_config"], ignore_eos=False,
+                                                    stop_token_ids=[want.output_tokens[0][0]]))
+        steps = decode.llm.stats["steps"]
+        _, last = asyncio.run(both(stop_body, {"kv-comm-request-id": "s2"}))
+        assert last.finished and last.output_tokens == [want.output_tokens[0][:1]] and last.finish_reasons == ["stop"]
+        assert decode.llm.stats["steps"] == steps
+    finally:
+        decode.shutdown()
+        prefill.shutdown()
+
+
 def test_decode_times_out_without_prefill():
     decode = _make("decode")
     decode.serving.setting.connector.connector_waiting_sec = 1
