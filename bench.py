@@ -52,7 +52,7 @@ def reference_arm(args) -> None:
     ref_dir = os.path.join(REPO, "baseline", "_ref")
     reason = None
     if not os.path.isdir(ref_dir) or not os.listdir(ref_dir):
-        reason = ("reference not installed: pip install of /root/reference fails offline (CMake fetches ~25 "
+        reason = ("reference not installed: its pip install fails offline (CMake fetches ~25 "
                   "dependencies + DeepGEMM/flashinfer from the network, submodules are empty, no sm_100 target)")
     else:
         sys.path.insert(0, ref_dir)
