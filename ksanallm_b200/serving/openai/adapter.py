@@ -132,6 +132,11 @@ class OpenAIServing:
             return _err(f"chat template failed: {ex}")
         n_lp = max(int(r.top_logprobs or 0), 1) if r.logprobs else 0
         req_dict = {"input_tokens": input_tokens, "sampling_config": self._sampling_config(r, n_lp)}
+        if any(isinstance(m.get("content"), list) and any(isinstance(p, dict) and p.get("type") != "text"
+                                                          for p in m["content"]) for m in r.messages):
+            # image / video / audio parts: the model's plugin turns them into spliced embeddings
+            # (reference: openaiapi/request_converter.py multimodal message parsing -> plugin preprocess)
+            req_dict["messages"] = r.messages
         if enable_thinking is not None:
             req_dict["sampling_config"]["enable_thinking"] = enable_thinking
         rid, created = _id("chatcmpl"), int(time.time())

@@ -99,3 +99,42 @@ def test_image_requests_match_transformers_generate(tmp_path):
         assert eng.llm.cache.stats.prefix_hit_tokens == 0
     finally:
         eng.shutdown()
+
+
+def test_openai_chat_route_hands_image_parts_to_the_plugin(tmp_path):
+    """/v1/chat/completions with an image_url part: the raw messages reach the plugin (the stand-in chat template
+    renders no image placeholder, so the test inserts the one a vision-language template would) and the request
+    runs to completion."""
+    from fastapi.testclient import TestClient
+    from PIL import Image
+    from ksanallm_b200.serving.server import LLMServer
+    tmp = str(tmp_path)
+    _tiny_model(tmp)
+    img = Image.fromarray((torch.rand(56, 84, 3) * 255).byte().numpy())
+    args = EngineArgs(config_file="", model_dir=tmp, device="cpu",
+                      serving=parse_serving_config({"setting": {"batch_scheduler": {
+                          "max_batch_size": 2, "max_step_tokens": 128, "max_token_len": 256}}}))
+    os.environ["KSANA_SKIP_WARMUP"] = "1"
+    server = LLMServer(args)
+    server.initialize()
+    try:
+        seen = {}
+        impl = server.model.plugin.impl
+        orig = impl.preprocess
+
+        def spy(**kw):
+            seen["messages"] = kw.get("messages")
+            toks = list(kw["input_tokens"])
+            kw["input_tokens"] = toks[:2] + [VSTART, IMG, VEND] + toks[2:]  # what a VL chat template would render
+            return orig(**kw)
+
+        impl.preprocess = spy
+        with TestClient(server.app) as c:
+            r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+                {"type": "image_url", "image_url": {"url": _png_url(img)}}, {"type": "text", "text": "hi"}]}],
+                "max_tokens": 4, "temperature": 0, "ignore_eos": True})
+        assert r.status_code == 200, r.text
+        assert seen["messages"][0]["content"][0]["type"] == "image_url"
+        assert r.json()["usage"]["completion_tokens"] == 4
+    finally:
+        server.model.shutdown()
