@@ -157,6 +157,7 @@ class LLMEngine:
         self.metrics = None  # utils.metrics.Metrics, attached by the server
         self.tracer = None
         self._ctl = None  # CPU process group for plan broadcast
+        self._ctl_src = 0
         self._hdr = np.zeros(64, dtype=np.int32)
         self.stats = {"generated_tokens": 0, "prompt_tokens": 0, "steps": 0, "forward_time": 0.0, "schedule_time": 0.0,
                       "t_broadcast": 0.0, "t_launch": 0.0, "t_sample_sync": 0.0, "t_apply": 0.0}
@@ -350,6 +351,17 @@ class LLMEngine:
             plan = self.sched.schedule(int(time.time() * 1000))
             for sid, reason in plan.dropped:
                 self._finish_seq(sid, reason)
+            layout = rows = refit = mrope = None
+            greedy = True
+            if not plan.empty():
+                layout = self.sched.pack(plan, self.runner.staging.host_np, self.runner.max_blocks_per_seq)
+                rows, greedy, refit = self._sample_rows(plan)
+                mrope = self._build_mrope(plan)
+            dp_group = self.dp is not None and self._has_followers()
+            if dp_group:
+                # a DP group with tensor parallelism inside: its followers hear about EVERY step, also the empty
+                # ones, because the per-step agreement below and the mock steps are collectives they take part in
+                self._broadcast_plan(layout, plan, greedy, refit=refit, mrope=mrope, noplan=plan.empty())
             if self.dp is not None:
                 # attention data parallelism: all ranks step together; a rank without work runs a mock step
                 stride, anybody = self.dp.sync(plan.total_tokens, self.sched.has_unfinished())
@@ -362,14 +374,9 @@ class LLMEngine:
                         self.stats["mock_steps"] = self.stats.get("mock_steps", 0) + 1
                     return 0
             if plan.empty():
-                if self.tp.size > 1 and len(plan.swap_out) + len(plan.swap_in) + len(plan.block_copies) > 0:
-                    pass
                 return 0
-            layout = self.sched.pack(plan, self.runner.staging.host_np, self.runner.max_blocks_per_seq)
-            rows, greedy, refit = self._sample_rows(plan)
         t1 = time.perf_counter()
-        mrope = self._build_mrope(plan)
-        if self._has_followers():
+        if self._has_followers() and not dp_group:
             self._broadcast_plan(layout, plan, greedy, refit=refit, mrope=mrope)
         ta = time.perf_counter()
         self.runner.apply_flexible(plan.flexible)
@@ -670,22 +677,25 @@ class LLMEngine:
                                               owner[0].prompt_tokens, cutoff_forward)
 
     # ---- multi-rank plan distribution ---------------------------------------------------------------------
-    def attach_control_group(self, group) -> None:
+    def attach_control_group(self, group, src: int = 0) -> None:
+        """``group``: CPU process group over which the driving rank broadcasts its step plans; ``src``: that rank's
+        GLOBAL rank (not 0 for the DP groups after the first)."""
         self._ctl = group
+        self._ctl_src = src
 
     def _has_followers(self) -> bool:
         """Other ranks execute this engine's plans: tensor-parallel peers and / or later pipeline stages."""
         return self.tp.size > 1 or (self.pipeline is not None and self.pipeline.topo.num_stages > 1)
 
     def _broadcast_plan(self, layout, plan, greedy: bool, stop: bool = False, fixup: bool = False, refit=None,
-                        mrope=None) -> None:
+                        mrope=None, noplan: bool = False) -> None:
         keys = ["num_seqs", "num_prefill", "num_decode", "total_tokens", "total_logits", "max_q_len", "max_kv_len",
                 "max_blocks", "input_ids", "positions", "slot_mapping", "seq_of_token", "cu_q", "kv_lens", "q_starts",
                 "logits_idx", "block_tables", "total_words"]
         h = self._hdr
         h[:] = 0
-        h[0] = 2 if stop else 1
-        if not stop:
+        h[0] = 2 if stop else (3 if noplan else 1)
+        if not stop and not noplan:
             for i, k in enumerate(keys):
                 h[1 + i] = layout[k]
             h[30] = 1 if greedy else 0
@@ -697,22 +707,22 @@ class LLMEngine:
             h[37] = sum(int(e.shape[0]) for _, e in refit) if refit else 0
             h[38] = int(mrope.shape[0]) if mrope is not None else 0
         hdr = torch.from_numpy(h)
-        dist.broadcast(hdr, src=0, group=self._ctl)
-        if stop:
+        dist.broadcast(hdr, src=self._ctl_src, group=self._ctl)
+        if stop or noplan:
             return
         n = int(h[18])
-        dist.broadcast(self.runner.staging.host[:n], src=0, group=self._ctl)
+        dist.broadcast(self.runner.staging.host[:n], src=self._ctl_src, group=self._ctl)
         extra = int(h[31] + h[32] + h[33] + h[35])
         if extra:
             arr = np.concatenate([np.asarray(a, dtype=np.int32).reshape(-1, 2) for a in (so, si, bc, fx)], 0)
-            dist.broadcast(torch.from_numpy(np.ascontiguousarray(arr)), src=0, group=self._ctl)
+            dist.broadcast(torch.from_numpy(np.ascontiguousarray(arr)), src=self._ctl_src, group=self._ctl)
         if refit:
             # multimodal: (first row, row count) of every spliced run, then all embedding rows
             runs = torch.tensor([[p, e.shape[0]] for p, e in refit], dtype=torch.int32)
-            dist.broadcast(runs, src=0, group=self._ctl)
-            dist.broadcast(torch.cat([e.float().cpu() for _, e in refit]).contiguous(), src=0, group=self._ctl)
+            dist.broadcast(runs, src=self._ctl_src, group=self._ctl)
+            dist.broadcast(torch.cat([e.float().cpu() for _, e in refit]).contiguous(), src=self._ctl_src, group=self._ctl)
         if mrope is not None:
-            dist.broadcast(mrope, src=0, group=self._ctl)
+            dist.broadcast(mrope, src=self._ctl_src, group=self._ctl)
 
     def follow(self) -> None:
         """Step loop of a non-driver rank: receive plan, run the shard, join the collectives."""
@@ -721,27 +731,37 @@ class LLMEngine:
                 "logits_idx", "block_tables", "total_words"]
         hdr = torch.zeros(64, dtype=torch.int32)
         while True:
-            dist.broadcast(hdr, src=0, group=self._ctl)
+            dist.broadcast(hdr, src=self._ctl_src, group=self._ctl)
             h = hdr.numpy()
             if h[0] == 2:
                 return
+            if h[0] == 3:
+                # a DP group's step without a plan: still agree with the other groups, run a mock step if they work
+                stride, _ = self.dp.sync(0, False)
+                if self.tp.ep is not None:
+                    self.tp.ep.step_stride = max(stride, 1)
+                if stride > 0:
+                    self.runner.mock_forward()
+                if self.dp.stopping:
+                    return
+                continue
             layout = {k: int(h[1 + i]) for i, k in enumerate(keys)}
             n = layout["total_words"]
             self.runner.staging.flip()  # the previous step's host-to-device copy may still be pending
-            dist.broadcast(self.runner.staging.host[:n], src=0, group=self._ctl)
+            dist.broadcast(self.runner.staging.host[:n], src=self._ctl_src, group=self._ctl)
             nso, nsi, nbc, nfx = int(h[31]), int(h[32]), int(h[33]), int(h[35])
             so = si = bc = fx = np.zeros((0, 2), dtype=np.int32)
             if nso + nsi + nbc + nfx:
                 arr = torch.zeros(nso + nsi + nbc + nfx, 2, dtype=torch.int32)
-                dist.broadcast(arr, src=0, group=self._ctl)
+                dist.broadcast(arr, src=self._ctl_src, group=self._ctl)
                 a = arr.numpy()
                 so, si, bc, fx = a[:nso], a[nso:nso + nsi], a[nso + nsi:nso + nsi + nbc], a[nso + nsi + nbc:]
             refit = None
             if h[36]:
                 runs = torch.zeros(int(h[36]), 2, dtype=torch.int32)
-                dist.broadcast(runs, src=0, group=self._ctl)
+                dist.broadcast(runs, src=self._ctl_src, group=self._ctl)
                 vals = torch.zeros(int(h[37]), self.cfg.hidden_size, dtype=torch.float32)
-                dist.broadcast(vals, src=0, group=self._ctl)
+                dist.broadcast(vals, src=self._ctl_src, group=self._ctl)
                 refit, at = [], 0
                 for p, n in runs.tolist():
                     refit.append((p, vals[at:at + n].to(self.runner.device)))
@@ -749,7 +769,11 @@ class LLMEngine:
             mrope = None
             if h[38]:
                 mrope = torch.zeros(int(h[38]), layout["total_tokens"], dtype=torch.int32)
-                dist.broadcast(mrope, src=0, group=self._ctl)
+                dist.broadcast(mrope, src=self._ctl_src, group=self._ctl)
+            if self.dp is not None:
+                stride, _ = self.dp.sync(layout["total_tokens"], True)
+                if self.tp.ep is not None:
+                    self.tp.ep.step_stride = max(stride, 1)
             self.runner.apply_flexible(fx.reshape(-1, 4))
             self.runner.apply_block_ops(so, si, bc)
             meta = self.runner.upload(layout)
@@ -762,6 +786,8 @@ class LLMEngine:
                 continue
             hidden = self.runner.forward(meta, refit)
             self.runner.sample(hidden, meta, None, bool(h[30]))
+            if self.dp is not None and self.dp.stopping:
+                return
 
     # ---- attention data parallelism ------------------------------------------------------------------------------
     def attach_dp(self, coordinator) -> None:
@@ -771,7 +797,7 @@ class LLMEngine:
         self.async_mode = False
         self.tp.ep_dp = True
         lb = self.serving.setting.batch_scheduler.attention_dp_lb_config
-        if lb.enable_balance:
+        if lb.enable_balance and self.tp.size == 1:  # (its collective is not part of the followers' step protocol)
             from ..parallel.attn_dp import ADPBalance
             self.adp_balance = ADPBalance(coordinator, lb.max_waiting_steps, lb.max_waiting_time_in_ms,
                                           lb.min_qps_for_waiting)
@@ -971,7 +997,8 @@ class LLMEngine:
             self._loop_thread = None
         if self.dp_router is not None:
             self.dp_router.close()
-        self.shutdown_followers()
+        if self.dp is None:  # a DP group's followers leave with the agreed stop, nobody listens any more
+            self.shutdown_followers()
 
     def _fail_all(self, ex: Exception) -> None:
         with self.lock:

@@ -350,9 +350,16 @@ class MoEFFN:
                                  c.topk_group, c.routed_scaling_factor, self.bias)
         s = None
         if self.shared is not None and h.shape[0]:
-            s = self.shared.down(self.shared.core(h))
+            s = self.shared.down(self.shared.core(h), add_bias=self.tp.rank == 0)
             if self.shared_gate is not None:
                 s = s * torch.sigmoid(ops.linear(h, self.shared_gate).float()).to(s.dtype)
+        if self.tp.size > 1:
+            # a DP group that is tensor-parallel inside: every rank of the group holds the same rows, so one of them
+            # sends them through the exchange and the others join it empty-handed; the block's output is a partial
+            # sum over the group (the routed part counted once, the sliced shared expert on every rank)
+            if self.tp.rank != 0:
+                ep.moe(h[:0], ids[:0], wts[:0], self.w_gate_up, self.w_down, ep.step_stride)
+                return s if s is not None else torch.zeros_like(h)
         return ep.moe(h, ids, wts, self.w_gate_up, self.w_down, ep.step_stride, add=s)
 
     def _partial_dispatch(self, h: torch.Tensor, ep) -> torch.Tensor:

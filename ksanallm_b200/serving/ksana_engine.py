@@ -257,11 +257,21 @@ class KsanaLLMEngine:
             # attention data parallelism: every rank is a DP group of its own (attention / dense weights replicated,
             # own scheduler and KV cache), the routed experts are sharded over all ranks (reference: attn_data_para_size
             # + expert_para_size, service/inference_engine.cpp:201-260)
-            if topo is not None or g.attn_data_para_size != world_tp.size:
-                raise ValueError("attn_data_para_size must equal the number of ranks (DP groups of one GPU) and "
+            if topo is not None or world_tp.size % g.attn_data_para_size:
+                raise ValueError("the number of ranks must be a multiple of attn_data_para_size, and attention DP "
                                  "cannot be combined with pipeline stages")
+            import torch.distributed as dist
             dp_world = world_tp
+            attn_tp = world_tp.size // g.attn_data_para_size  # ranks per DP group (tensor-parallel inside)
+            dp_group_id, dp_tp_rank = world_tp.rank // attn_tp, world_tp.rank % attn_tp
             tp = TPGroup(0, 1, None, device, use_fused=False)
+            dp_ctl = None
+            if attn_tp > 1:
+                for gi in range(g.attn_data_para_size):  # every rank creates every group, in the same order
+                    ranks = list(range(gi * attn_tp, (gi + 1) * attn_tp))
+                    grp, ctl = dist.new_group(ranks), dist.new_group(ranks, backend="gloo")
+                    if gi == dp_group_id:
+                        tp, dp_ctl = TPGroup(dp_tp_rank, attn_tp, grp, device, use_fused=False), ctl
             if cfg.is_moe:
                 ep_rank, ep_size = dp_world.rank, dp_world.size
                 tp.ep_rank, tp.ep_size = ep_rank, ep_size
@@ -276,7 +286,7 @@ class KsanaLLMEngine:
         weights = load_model_weights(cfg, "" if a.synthetic_model else a.model_dir, tp.rank, tp.size, device, dtype,
                                      quantize, synthetic_seed=0 if a.synthetic_model else None,
                                      layer_range=layer_range, ep_rank=ep_rank, ep_size=ep_size)
-        if tp.size > 1 and device.type == "cuda" and topo is None:
+        if tp.size > 1 and device.type == "cuda" and topo is None and dp_world is None:
             tp.init_fused(cfg.hidden_size, bs.max_step_tokens)
         model = TransformerModel(cfg, weights, tp, max_positions=max(bs.max_token_len, 2048), layer_range=layer_range)
         if topo is not None and not topo.is_last:
@@ -297,15 +307,19 @@ class KsanaLLMEngine:
             import torch.distributed as dist
             from ..parallel.attn_dp import DPCoordinator, DPRequestRouter, DPRequestWorker
             self.llm.attach_dp(DPCoordinator(dp_world.group, device if device.type == "cuda" else None))
+            if dp_ctl is not None:
+                self.llm.attach_control_group(dp_ctl, src=dp_group_id * attn_tp)
+                self.llm.is_driver = dp_tp_rank == 0
             host = os.environ.get("MASTER_ADDR", "127.0.0.1")
             port = int(os.environ.get("KSANA_DP_PORT", int(os.environ.get("MASTER_PORT", "29511")) + 17))
             if dp_world.rank == 0:
-                self.llm.dp_router = DPRequestRouter(self.llm, host, port, dp_world.size)
+                self.llm.dp_router = DPRequestRouter(self.llm, host, port, g.attn_data_para_size)
                 dist.barrier(group=dp_world.group)  # the listener exists before anybody connects
                 self.llm.dp_router.accept_all()
             else:
                 dist.barrier(group=dp_world.group)
-                self.llm.dp_worker = DPRequestWorker(self.llm, host, port, dp_world.rank)
+                if dp_tp_rank == 0:  # the leaders of the other DP groups take requests from rank 0
+                    self.llm.dp_worker = DPRequestWorker(self.llm, host, port, dp_group_id)
         elif world_tp.size > 1:
             import torch.distributed as dist
             self.llm.attach_control_group(dist.new_group(backend="gloo"))
@@ -333,8 +347,8 @@ class KsanaLLMEngine:
     def serve_follower(self) -> None:
         """Blocks in the follower loop (ranks > 0): executes rank 0's plans (TP / PP), or - as an attention-DP rank -
         runs its own scheduler on the requests rank 0 places here."""
-        if self.llm.dp is not None:
-            self.llm.serve_dp()
+        if self.llm.dp is not None and self.llm.is_driver:
+            self.llm.serve_dp()  # the leader of a DP group
         else:
             self.llm.follow()
 

@@ -100,3 +100,12 @@ def test_attention_dp_with_expert_parallel_from_serving_config():
     got, placed = _spawn(2, dict(tensor_para_size=2, attn_data_para_size=2, expert_para_size=2), "tiny-moe", 4)
     assert got == want
     assert placed == [2, 2]
+
+
+def test_attention_dp_groups_with_tensor_parallel_inside():
+    """Four ranks = two DP groups of two tensor-parallel ranks; experts sharded over all four. Each group's leader
+    schedules its own requests, its follower hears about every step (also the empty ones) and joins the exchange."""
+    want = _single("tiny-moe", 4)
+    got, placed = _spawn(4, dict(tensor_para_size=4, attn_data_para_size=2, expert_para_size=4), "tiny-moe", 4)
+    assert got == want
+    assert placed == [2, 2]
