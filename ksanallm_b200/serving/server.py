@@ -137,19 +137,30 @@ def main(argv=None) -> None:
     server = LLMServer(args)
     rank = int(os.environ.get("RANK", "0"))
     server.model.initialize()
+    def _leave():
+        import gc
+        import torch.distributed as dist
+        server.model.llm = None  # the engine's references to the process groups go first ...
+        gc.collect()
+        if dist.is_initialized():
+            dist.destroy_process_group()  # ... then the backend's threads are joined before the interpreter exits
+
     if rank != 0:
         server.model.serve_follower()
+        _leave()
         return
     server.initialize()
 
     def _term(signum, frame):
         server.model.shutdown()
+        _leave()
         sys.exit(0)
 
     signal.signal(signal.SIGTERM, _term)
     uvicorn.run(server.app, host=args.host, port=args.port, log_level="info" if args.access_log else "warning",
                 access_log=args.access_log, ssl_keyfile=args.ssl_keyfile, ssl_certfile=args.ssl_certfile)
     server.model.shutdown()
+    _leave()
 
 
 if __name__ == "__main__":
