@@ -9,6 +9,7 @@ layers/nvidia/moe_layer.cpp:208-377.
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional
 
 import torch
@@ -17,6 +18,24 @@ from .. import ops
 from ..config.model_config import ModelConfig
 from ..ops import reference as ref
 from ..parallel.comm import TPGroup
+
+
+_EPLB_LAYERS: Dict[str, "MoEFFN"] = {}
+
+
+def dump_eplb_counts(path: Optional[str] = None, rank: int = 0) -> Optional[str]:
+    """Writes {layer prefix: times each expert was chosen} gathered since start-up (enabled by DUMP_EPLB_PATH) for
+    ``python -m ksanallm_b200.tools.eplb``. Reference: moe_layer.cpp:412-415, 465-471 (per-step top-k id dumps)."""
+    import json
+    path = path or os.environ.get("DUMP_EPLB_PATH")
+    if not path or not _EPLB_LAYERS:
+        return None
+    os.makedirs(path, exist_ok=True)
+    out = os.path.join(path, f"expert_counts_rank{rank}.json")
+    with open(out, "w", encoding="utf-8") as f:
+        json.dump({k.replace(".mlp", "").replace("model.layers.", "layer_"): v._eplb_counts.tolist()
+                   for k, v in _EPLB_LAYERS.items()}, f)
+    return out
 
 
 class LinearW:
@@ -263,6 +282,11 @@ class MoEFFN:
         self.w_down = w[prefix + ".experts.down_proj.weight"]        # [E_local, H, I]
         # block-scaled fp8 experts (DeepSeek-V3 checkpoints, or quant_method fp8): e4m3 weights + one fp32 scale per
         # 128 x 128 block; they stay in fp8 and every expert's two GEMMs run through the block-scaled fp8 GEMM
+        self.perm = w.get(prefix + ".expert_perm")  # logical -> physical expert ids (load-balanced placement)
+        self._eplb_counts = None
+        if os.environ.get("DUMP_EPLB_PATH"):
+            self._eplb_counts = torch.zeros(cfg.num_experts, dtype=torch.int64)
+            _EPLB_LAYERS[prefix] = self
         self.s_gate_up = w.get(prefix + ".experts.up_gate_proj.weight_scale_inv")
         self.s_down = w.get(prefix + ".experts.down_proj.weight_scale_inv")
         self.e_local = self.w_gate_up.shape[0]
@@ -289,6 +313,7 @@ class MoEFFN:
         else:
             ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
                                      c.topk_group, c.routed_scaling_factor, self.bias)
+            ids = self._place(ids)
             if self.s_gate_up is not None:
                 y = self._fp8_experts(h, ids, wts)
             else:
@@ -300,6 +325,15 @@ class MoEFFN:
                 s = s * g
             y = y + s
         return y
+
+    def _place(self, ids: torch.Tensor) -> torch.Tensor:
+        """Router output (logical expert ids) -> the ids the expert kernels and the exchange work with. Counts the
+        choices when a routing dump was asked for (DUMP_EPLB_PATH)."""
+        if self._eplb_counts is not None and ids.numel():
+            self._eplb_counts += torch.bincount(ids.reshape(-1).long().cpu(), minlength=self.cfg.num_experts)
+        if self.perm is not None:
+            return self.perm[ids.long()].to(ids.dtype)
+        return ids
 
     def _fp8_experts(self, h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor) -> torch.Tensor:
         """Local experts with block-scaled fp8 weights: tokens are grouped by expert on the host and each group goes
@@ -348,6 +382,7 @@ class MoEFFN:
         logits = ops.linear(h.float() if self.gate_w.dtype == torch.float32 else h, self.gate_w)
         ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
                                  c.topk_group, c.routed_scaling_factor, self.bias)
+        ids = self._place(ids)
         s = None
         if self.shared is not None and h.shape[0]:
             s = self.shared.down(self.shared.core(h), add_bias=self.tp.rank == 0)
@@ -374,6 +409,7 @@ class MoEFFN:
         logits = ops.linear(mine.float() if self.gate_w.dtype == torch.float32 else mine, self.gate_w)
         ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
                                  c.topk_group, c.routed_scaling_factor, self.bias)
+        ids = self._place(ids)
         y = torch.zeros_like(h)
         if self.shared is not None:
             s = self.shared.down(self.shared.core(h), add_bias=self.tp.rank == 0)

@@ -334,6 +334,14 @@ class WeightLoader:
         self.rules = load_weight_map(model_dir, cfg.model_type) + (_RENAMES.get(cfg.model_type) or _RENAMES.get(fam, []))
         self.family = fam
         self.layer_range = layer_range
+        # expert-parallel load balancing: EPLB_WEIGHT names a placement (or routing-count) file; experts are stored
+        # in "physical" order (rank r hosts slots [r * E / ranks, ...)), the layer keeps the logical -> physical map
+        # and applies it to the router's choices (reference: moe_layer.cpp:124-129, 416-422 expert map, tools/eplb)
+        self.expert_perm: Dict[int, List[int]] = {}
+        eplb = os.environ.get("EPLB_WEIGHT", "")
+        if eplb and cfg.num_experts and self.ep_size > 1 and os.path.isfile(eplb):
+            from ..tools.eplb import load_expert_permutations
+            self.expert_perm = load_expert_permutations(eplb, cfg.num_experts, self.ep_size)
         self.out: Dict[str, torch.Tensor] = {}
         self._pending: Dict[str, Dict[str, torch.Tensor]] = defaultdict(dict)
         self._experts: Dict[str, Dict[Tuple[int, str], torch.Tensor]] = defaultdict(dict)
@@ -378,6 +386,17 @@ class WeightLoader:
             self.out[prefix + ".zeros"] = z.to(self.dtype).contiguous()
             return
         self._put(prefix + ".weight", w)
+
+    def _perm_of(self, layer_name: str) -> Optional[List[int]]:
+        """Logical -> physical expert permutation of ``model.layers.N`` (None: identity); also leaves the map in the
+        weight dict for the MoE block."""
+        if not self.expert_perm:
+            return None
+        li = int(layer_name.rsplit(".", 1)[1])
+        perm = self.expert_perm.get(li)
+        if perm is not None and f"{layer_name}.mlp.expert_perm" not in self.out:
+            self.out[f"{layer_name}.mlp.expert_perm"] = torch.tensor(perm, dtype=torch.int32, device=self.device)
+        return perm
 
     def _layer_of(self, name: str) -> Optional[int]:
         m = re.match(r"model\.layers\.(\d+)\.", name)
@@ -451,21 +470,26 @@ class WeightLoader:
             if self.family == "llama4":
                 t = t.transpose(1, 2)  # Llama 4 keeps [E, in, out] for its batched matmul
             per = max(cfg.num_experts // self.ep_size, 1)
-            for e in range(t.shape[0]):
+            perm = self._perm_of(layer)
+            for le in range(t.shape[0]):
+                e = perm[le] if perm else le  # physical slot of logical expert le
                 if self.ep_size > 1 and not (self.ep_rank * per <= e < (self.ep_rank + 1) * per):
                     continue
                 if rest == "experts.gate_up_proj":
                     half = t.shape[1] // 2
-                    self._experts[key][(e, "gate_proj.weight")] = t[e, :half]
-                    self._experts[key][(e, "up_proj.weight")] = t[e, half:]
+                    self._experts[key][(e, "gate_proj.weight")] = t[le, :half]
+                    self._experts[key][(e, "up_proj.weight")] = t[le, half:]
                 else:
-                    self._experts[key][(e, "down_proj.weight")] = t[e]
+                    self._experts[key][(e, "down_proj.weight")] = t[le]
             self._maybe_flush_experts(key)
             return
         # expert weights: experts.E.{gate,up,down}_proj.(weight|weight_scale_inv)
         em = re.match(r"experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv)$", rest)
         if em:
             e = int(em.group(1))
+            perm = self._perm_of(layer)
+            if perm:
+                e = perm[e]
             per = max(cfg.num_experts // self.ep_size, 1)
             if self.ep_size > 1 and not (self.ep_rank * per <= e < (self.ep_rank + 1) * per):
                 return

@@ -353,6 +353,8 @@ class KsanaLLMEngine:
             self.llm.follow()
 
     def shutdown(self) -> None:
+        from ..models.layers import dump_eplb_counts
+        dump_eplb_counts(rank=int(os.environ.get("RANK", "0")))  # no-op unless DUMP_EPLB_PATH asked for routing counts
         if getattr(self, "connector", None) is not None:
             self.connector.stop()
         if self.llm is not None:

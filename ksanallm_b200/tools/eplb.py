@@ -36,6 +36,42 @@ def balance_experts(load: List[float], num_ranks: int, redundant: int = 0) -> Di
             "rank_load": rank_load}
 
 
+def permutation_from_map(rank_of_expert: List[int], num_ranks: int) -> List[int]:
+    """Logical expert id -> physical slot, where rank r hosts the physical slots [r * E / ranks, (r + 1) * E / ranks).
+    Experts keep their relative order inside a rank; a rank given more than its share passes the surplus on to the
+    ranks with room (the placement must be a permutation: replicas are not expressed here)."""
+    E = len(rank_of_expert)
+    per = E // num_ranks
+    buckets: List[List[int]] = [[] for _ in range(num_ranks)]
+    spill = []
+    for e, r in enumerate(rank_of_expert):
+        (buckets[r] if len(buckets[r]) < per else spill).append(e)
+    for b in buckets:
+        while len(b) < per and spill:
+            b.append(spill.pop(0))
+    perm = [0] * E
+    for r, b in enumerate(buckets):
+        for i, e in enumerate(b):
+            perm[e] = r * per + i
+    return perm
+
+
+def load_expert_permutations(path: str, num_experts: int, num_ranks: int) -> Dict[int, List[int]]:
+    """Reads a placement file written by this tool ({layer: {"rank_of_expert": [...]}}) or a dump of routing counts
+    ({layer: [count per expert]}, balanced here) and returns {layer index: permutation}."""
+    with open(path, "r", encoding="utf-8") as f:
+        raw = json.load(f)
+    out = {}
+    for layer, v in raw.items():
+        if isinstance(v, dict) and "rank_of_expert" in v:
+            roe = v["rank_of_expert"]
+        else:
+            roe = balance_experts([float(x) for x in v], num_ranks)["rank_of_expert"]
+        if len(roe) == num_experts:
+            out[int(str(layer).split("_")[-1])] = permutation_from_map(roe, num_ranks)
+    return out
+
+
 def load_from_topk_ids(ids_per_layer: Dict[str, List[List[int]]], num_experts: int) -> Dict[str, List[float]]:
     out = {}
     for layer, rows in ids_per_layer.items():
@@ -57,7 +93,11 @@ def main(argv=None):
     a = ap.parse_args(argv)
     with open(a.stats) as f:
         stats = json.load(f)
-    loads = load_from_topk_ids(stats, a.experts)
+    first = next(iter(stats.values()))
+    if first and isinstance(first[0], (int, float)):  # the engine's dump: routing counts per expert
+        loads = {layer: [float(x) for x in v] for layer, v in stats.items()}
+    else:
+        loads = load_from_topk_ids(stats, a.experts)
     result = {layer: balance_experts(l, a.ranks, a.redundant) for layer, l in loads.items()}
     with open(a.out, "w") as f:
         json.dump(result, f)

@@ -33,8 +33,9 @@ PROMPTS = {0: [[5, 9, 77, 120, 33, 4, 8], [8, 6, 4]], 1: [[200, 3, 3, 19, 250, 7
 NEW = {0: 9, 1: 3}  # rank 1 finishes early and must keep stepping (mock steps) until rank 0 is done
 
 
-def _worker(rank, world, port, out):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+def _worker(rank, world, port, out, eplb=""):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      EPLB_WEIGHT=eplb)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     cfg = _cfg()
     w = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32, ep_rank=rank, ep_size=world)
@@ -51,7 +52,19 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_attention_dp_two_ranks_match_single_process():
+import pytest
+
+
+@pytest.mark.parametrize("placement", [None, [1, 0, 0, 1]])
+def test_attention_dp_two_ranks_match_single_process(placement, tmp_path):
+    """``placement``: rank of every expert as an expert-load-balancing file gives it (experts 1 and 2 on rank 0, 0 and
+    3 on rank 1); where the experts live must not change any token."""
+    import json
+    eplb = ""
+    if placement is not None:
+        eplb = str(tmp_path / "eplb.json")
+        with open(eplb, "w") as f:
+            json.dump({f"layer_{i}": {"rank_of_expert": placement} for i in range(2)}, f)
     cfg = _cfg()
     w = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32)
     want = {}
@@ -65,7 +78,7 @@ def test_attention_dp_two_ranks_match_single_process():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, eplb)) for r in range(2)]
     for p in procs:
         p.start()
     got = dict()
@@ -143,3 +156,35 @@ def test_adp_balance_gives_up_after_max_waiting_steps():
     # rank 0 has nothing waiting at step 8, so rank 1 is held for two steps as well
     assert got[0][0] == [0, 5] and got[1][0] == [0, 10]
     assert got[0][2] == got[1][2] == 2
+
+
+def test_expert_placement_permutation_and_routing_dump(tmp_path, monkeypatch):
+    from ksanallm_b200.tools.eplb import balance_experts, permutation_from_map
+    assert permutation_from_map([1, 0, 0, 1], 2) == [2, 0, 1, 3]
+    assert sorted(permutation_from_map([0, 0, 0, 1], 2)) == [0, 1, 2, 3]  # an overfull rank spills, still a permutation
+    # the loader stores the experts in physical order and leaves the map for the layer
+    import json
+    path = tmp_path / "eplb.json"
+    path.write_text(json.dumps({"layer_0": {"rank_of_expert": [1, 0, 0, 1]}, "layer_1": [5.0, 1.0, 1.0, 5.0]}))
+    monkeypatch.setenv("EPLB_WEIGHT", str(path))
+    cfg = _cfg()
+    full = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32)
+    parts = [load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32, ep_rank=r, ep_size=2) for r in range(2)]
+    key = "model.layers.0.mlp.experts.down_proj.weight"
+    assert parts[0]["model.layers.0.mlp.expert_perm"].tolist() == [2, 0, 1, 3]
+    assert torch.equal(parts[0][key], full[key][[1, 2]]) and torch.equal(parts[1][key], full[key][[0, 3]])
+    hot = parts[0]["model.layers.1.mlp.expert_perm"].tolist()  # counts: the two hot experts end up on different ranks
+    assert hot[0] // 2 != hot[3] // 2
+    assert balance_experts([5.0, 1.0, 1.0, 5.0], 2)["rank_load"] == [6.0, 6.0]
+    # routing dump
+    monkeypatch.setenv("EPLB_WEIGHT", "")
+    monkeypatch.setenv("DUMP_EPLB_PATH", str(tmp_path / "dump"))
+    from ksanallm_b200.models import layers
+    layers._EPLB_LAYERS.clear()
+    eng = LLMEngine(TransformerModel(cfg, full), _serving(), num_blocks=64, num_host_blocks=0)
+    eng.generate(PROMPTS[0], SamplingParams(topk=1, max_new_tokens=4, ignore_eos=True))
+    out = layers.dump_eplb_counts()
+    counts = json.load(open(out))
+    n_tok = sum(len(p) for p in PROMPTS[0]) + 2 * 3
+    assert set(counts) == {"layer_0", "layer_1"} and sum(counts["layer_0"]) == 2 * n_tok
+    layers._EPLB_LAYERS.clear()
