@@ -117,3 +117,35 @@ def test_openai_chat_and_completions(client):
 def test_metrics_endpoint(client):
     t = client.get("/metrics").text
     assert "ksana_time_to_first_token_us_count" in t and "ksana_generated_token_num" in t
+
+
+def test_structured_output_json_schema_and_regex(client):
+    """Grammar-constrained decoding: whatever the random model prefers, the output must satisfy the schema / the
+    regular expression (token bitmask applied in the sampler), for greedy and for sampled requests."""
+    pytest.importorskip("xgrammar")
+    import re
+    schema = {"type": "object", "properties": {"a": {"type": "integer"}, "ok": {"type": "boolean"}},
+              "required": ["a", "ok"], "additionalProperties": False}
+    for seed in (7, 8):
+        body = {"prompt": "give json", "stream": False,
+                "sampling_config": dict(topk=40, temperature=1.0, seed=seed, max_new_tokens=96, json_schema=schema)}
+        r = client.post("/generate", content=json.dumps(body))
+        assert r.status_code == 200, r.text
+        obj = json.loads(r.json()["texts"][0])
+        assert set(obj) == {"a", "ok"} and isinstance(obj["a"], int) and isinstance(obj["ok"], bool)
+    # greedy: this random model keeps choosing white space, which JSON allows anywhere between tokens; what it emits
+    # is still a prefix the grammar accepts
+    body = {"prompt": "give json", "stream": False, "sampling_config": dict(topk=1, max_new_tokens=16, json_schema=schema)}
+    assert re.fullmatch(r'\{\s*("a"\s*:?\s*-?\d*)?[\s\S]*', client.post("/generate", content=json.dumps(body)).json()["texts"][0])
+    body = {"prompt": "phone", "stream": False,
+            "sampling_config": {"topk": 1, "max_new_tokens": 32, "structured_output_regex": r"\d{3}-\d{4}"}}
+    text = client.post("/generate", content=json.dumps(body)).json()["texts"][0]
+    assert re.fullmatch(r"\d{3}-\d{4}", text)
+    # the OpenAI route: response_format json_schema
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "json please"}],
+                                                  "max_tokens": 96, "temperature": 1.0, "top_k": 40, "seed": 7,
+                                                  "response_format": {"type": "json_schema", "json_schema": {
+                                                      "name": "t", "schema": schema}}})
+    assert r.status_code == 200, r.text
+    obj = json.loads(r.json()["choices"][0]["message"]["content"])
+    assert set(obj) == {"a", "ok"}
