@@ -194,9 +194,11 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
             if k in c and k not in inner:
                 inner[k] = c[k]
         c = inner
-    if isinstance(c.get("text_config"), dict) and str(c.get("model_type", "")).lower() in ("qwen2_vl", "qwen2_5_vl"):
+    if isinstance(c.get("text_config"), dict) and str(c.get("model_type", "")).lower() in ("qwen2_vl", "qwen2_5_vl",
+                                                                                              "internvl"):
         inner = dict(c["text_config"])
-        inner["model_type"] = str(c["model_type"]).lower()
+        if str(c["model_type"]).lower() != "internvl":  # InternVL's tower keeps its own type (qwen2, llama, ...)
+            inner["model_type"] = str(c["model_type"]).lower()
         for k in ("torch_dtype", "dtype", "quantization_config", "tie_word_embeddings", "architectures"):
             if k in c and k not in inner:
                 inner[k] = c[k]

@@ -62,6 +62,7 @@ _RENAMES: Dict[str, List[Tuple[str, str]]] = {
 # multimodal checkpoints: the language tower sits under model.language_model (transformers >= 4.52) or model.
 _RENAMES["qwen2_vl"] = [(r"^model\.language_model\.", "model.")]
 _RENAMES["internvl_chat"] = [(r"^language_model\.", "")] + _RENAMES["internlm2"]
+_RENAMES["internvl"] = [(r"^model\.language_model\.", "model.")]  # transformers layout: qwen2 / llama tower
 _RENAMES["internlmxcomposer2"] = _RENAMES["internlm2"]
 _RENAMES["llama4"] = [(r"^language_model\.", ""), (r"\.feed_forward\.", ".mlp."), (r"\.router\.", ".gate.")]
 
@@ -331,7 +332,12 @@ class WeightLoader:
         self.quantize = quantize  # None | "fp8_block" | "int4"
         from .registry import resolve_family
         fam = resolve_family(cfg.model_type, model_dir) or cfg.model_type
-        self.rules = load_weight_map(model_dir, cfg.model_type) + (_RENAMES.get(cfg.model_type) or _RENAMES.get(fam, []))
+        # multimodal wrappers keep the language tower under model.language_model.* / language_model.*
+        generic = [(r"^model\.language_model\.model\.", "model."), (r"^model\.language_model\.lm_head\.", "lm_head."),
+                   (r"^model\.language_model\.", "model."), (r"^language_model\.model\.", "model."),
+                   (r"^language_model\.lm_head\.", "lm_head.")]
+        self.rules = load_weight_map(model_dir, cfg.model_type) + generic + \
+            (_RENAMES.get(cfg.model_type) or _RENAMES.get(fam, []))
         self.family = fam
         self.layer_range = layer_range
         # expert-parallel load balancing: EPLB_WEIGHT names a placement (or routing-count) file; experts are stored
@@ -405,7 +411,7 @@ class WeightLoader:
     # ---- main entry -------------------------------------------------------------------------------
     def load(self, tensors: Iterable[Tuple[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
         for raw_name, t in tensors:
-            if re.match(r"(model\.)?(visual|vision_tower|vision_model|vit)\.", raw_name):
+            if re.match(r"(model\.)?(visual|vision_tower|vision_model|vit|multi_modal_projector|mlp1)\.", raw_name):
                 continue  # vision towers belong to the serving plugin, not to the language model
             name = normalise_name(raw_name, self.rules)
             li = self._layer_of(name)
