@@ -278,8 +278,15 @@ class MoEFFN:
         self.tp = tp
         self.gate_w = w[prefix + ".gate.weight"]
         self.bias = w.get(prefix + ".gate.e_score_correction_bias")
-        self.w_gate_up = w[prefix + ".experts.up_gate_proj.weight"]  # [E_local, 2I, H]
-        self.w_down = w[prefix + ".experts.down_proj.weight"]        # [E_local, H, I]
+        self.w_gate_up = w.get(prefix + ".experts.up_gate_proj.weight")  # [E_local, 2I, H]
+        self.w_down = w.get(prefix + ".experts.down_proj.weight")        # [E_local, H, I]
+        # 4-bit group-quantised experts (GPTQ / AWQ checkpoints): packed words [E_local, N, K / 8] + scales / zeros
+        self.q4 = None
+        if self.w_gate_up is None:
+            e = prefix + ".experts."
+            self.q4 = tuple((w[e + n + ".qweight"], w[e + n + ".scales"], w[e + n + ".zeros"])
+                            for n in ("up_gate_proj", "down_proj"))
+            self.w_gate_up, self.w_down = self.q4[0][0], self.q4[1][0]  # (shape carriers: E_local = dim 0)
         # block-scaled fp8 experts (DeepSeek-V3 checkpoints, or quant_method fp8): e4m3 weights + one fp32 scale per
         # 128 x 128 block; they stay in fp8 and every expert's two GEMMs run through the block-scaled fp8 GEMM
         self.perm = w.get(prefix + ".expert_perm")  # logical -> physical expert ids (load-balanced placement)
@@ -300,7 +307,10 @@ class MoEFFN:
         """Per-rank partial sum of the block output (needs a cross-rank sum when size > 1)."""
         c = self.cfg
         ep = self.tp.ep
-        if self.s_gate_up is not None:
+        if self.s_gate_up is not None or self.q4 is not None:
+            if self.tp.ep_dp and self.e_local < c.num_experts:
+                raise NotImplementedError("attention data parallelism exchanges tokens between the ranks' experts "
+                                          "in bf16; quantised experts need tensor / expert parallelism instead")
             ep = None  # the dispatch / combine kernels and the gathered exchange take bf16 expert weights
         if ep is not None and self.tp.ep_dp and self.e_local < c.num_experts:
             return self._dp_exchange(h, ep)
@@ -314,7 +324,7 @@ class MoEFFN:
             ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
                                      c.topk_group, c.routed_scaling_factor, self.bias)
             ids = self._place(ids)
-            if self.s_gate_up is not None:
+            if self.s_gate_up is not None or self.q4 is not None:
                 y = self._fp8_experts(h, ids, wts)
             else:
                 y = ops.moe_experts(h, ids, wts, self.w_gate_up, self.w_down, self.expert_offset)
@@ -336,9 +346,9 @@ class MoEFFN:
         return ids
 
     def _fp8_experts(self, h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor) -> torch.Tensor:
-        """Local experts with block-scaled fp8 weights: tokens are grouped by expert on the host and each group goes
-        through two fp8 GEMMs (activations quantised per token per 128 channels). One launch pair per active expert,
-        not a grouped kernel."""
+        """Local experts with quantised weights - block-scaled fp8 (activations quantised per token per 128 channels)
+        or 4-bit group-quantised: tokens are grouped by expert on the host and each group goes through that
+        format's two GEMMs. One launch pair per active expert, not a grouped kernel."""
         T, H = h.shape
         out = torch.zeros(T, H, dtype=torch.float32, device=h.device)
         local = (ids >= self.expert_offset) & (ids < self.expert_offset + self.e_local)
@@ -354,8 +364,14 @@ class MoEFFN:
             if n == 0:
                 continue
             t = tok[at:at + n]
-            a = ops.silu_and_mul(ops.linear_fp8_block(h[t], self.w_gate_up[e], self.s_gate_up[e]))
-            y = ops.linear_fp8_block(a, self.w_down[e], self.s_down[e]).float()
+            if self.q4 is not None:
+                (q1, s1, z1), (q2, s2, z2) = self.q4
+                g1, g2 = q1.shape[2] * 8 // s1.shape[2], q2.shape[2] * 8 // s2.shape[2]
+                a = ops.silu_and_mul(ops.linear_int4(h[t], q1[e], s1[e], z1[e], None, g1))
+                y = ops.linear_int4(a, q2[e], s2[e], z2[e], None, g2).float()
+            else:
+                a = ops.silu_and_mul(ops.linear_fp8_block(h[t], self.w_gate_up[e], self.s_gate_up[e]))
+                y = ops.linear_fp8_block(a, self.w_down[e], self.s_down[e]).float()
             out.index_add_(0, t, y * wts[t, slot[at:at + n]].unsqueeze(-1).float())
             at += n
         return out.to(h.dtype)

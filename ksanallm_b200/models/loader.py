@@ -530,6 +530,9 @@ class WeightLoader:
         keep_grid = (not cfg.use_mla and block in ("self_attn", "mlp") and
                      re.fullmatch(r"(shared_expert\.)?(q_proj|k_proj|v_proj|o_proj|gate_proj|up_proj|down_proj)", stem)
                      and (qw is not None) and qw.shape[1] % 128 == 0 and g % 64 == 0)
+        # routed experts keep their 4-bit grid too (also under MLA): they are most of a MoE checkpoint's bytes
+        keep_grid = keep_grid or (block == "mlp" and (qw is not None) and g % 64 == 0 and qw.shape[1] % g == 0 and
+                                  bool(re.fullmatch(r"experts\.\d+\.(gate_proj|up_proj|down_proj)", stem)))
         value = qw if keep_grid else (dense if dense is not None else qw.dequant())
         if not isinstance(value, QuantW):
             value = value.to(self.dtype)
@@ -749,6 +752,16 @@ class WeightLoader:
 
     def _finish_experts(self, key: str, ex: Dict[Tuple[int, str], torch.Tensor]) -> None:
         ids = sorted({e for e, _ in ex})
+        if isinstance(ex[(ids[0], "gate_proj.weight")], QuantW):
+            # GPTQ / AWQ experts: stacked packed words + group scales / zeros, [gate | up] rows fused per expert
+            gus = [QuantW.cat0((ex[(e, "gate_proj.weight")], ex[(e, "up_proj.weight")])) for e in ids]
+            dns = [ex[(e, "down_proj.weight")] for e in ids]
+            for name, qs in (("up_gate_proj", gus), ("down_proj", dns)):
+                self.out[f"{key}.experts.{name}.qweight"] = self._own(
+                    torch.stack([ref.pack_int4(q.q.to(torch.int32)) for q in qs]))
+                self.out[f"{key}.experts.{name}.scales"] = self._own(torch.stack([q.scales for q in qs]).to(self.dtype))
+                self.out[f"{key}.experts.{name}.zeros"] = self._own(torch.stack([q.zeros for q in qs]).to(self.dtype))
+            return
         has_scale = (ids[0], "gate_proj.weight_scale_inv") in ex
         gu = torch.stack([torch.cat((ex[(e, "gate_proj.weight")], ex[(e, "up_proj.weight")]), 0) for e in ids])
         dn = torch.stack([ex[(e, "down_proj.weight")] for e in ids])

@@ -136,3 +136,41 @@ def test_fp8_block_scaled_experts_stay_fp8_and_match_dequantised_weights():
         outs.append(model.forward(meta, model.allocate_kv_cache(2, 16)))
     err = (outs[0] - outs[1]).abs().max().item()
     assert 0 < err < 0.05 * outs[1].abs().max().item()
+
+
+@pytest.mark.parametrize("fmt", ["gptq", "awq"])
+def test_quantised_experts_keep_their_grid(fmt):
+    """A MoE checkpoint whose expert projections are GPTQ / AWQ tensors: the experts stay packed (stacked words +
+    scales + zeros per expert) and the model equals the one built from the dequantised experts."""
+    base = dict(model_type="mixtral", hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, intermediate_size=128, num_local_experts=4, num_experts_per_tok=2,
+                vocab_size=300, torch_dtype="float32", max_position_embeddings=64)
+    cfg = model_config_from_dict(base)
+    dense, quant = [], []
+    for name, w in synthetic_checkpoint(cfg, seed=5, dtype=torch.float32):
+        if ".experts." not in name:
+            dense.append((name, w))
+            quant.append((name, w))
+            continue
+        packed, scales, zeros = ref.quant_int4_group(w, GROUP)
+        q = ref.unpack_int4(packed)
+        stem = name[:-len(".weight")]
+        N, K = q.shape
+        deq = (q.float().view(N, K // GROUP, GROUP) - zeros.unsqueeze(-1)).mul(scales.half().float().unsqueeze(-1)).view(N, K)
+        dense.append((name, deq))
+        if fmt == "gptq":
+            quant += [(stem + ".qweight", _pack_along(q.t().contiguous(), 0)),
+                      (stem + ".qzeros", _pack_along((zeros - 1).to(torch.int64).t().contiguous(), 1)),
+                      (stem + ".scales", scales.t().contiguous().half()),
+                      (stem + ".g_idx", torch.arange(K, dtype=torch.int32) // GROUP)]
+        else:
+            quant += [(stem + ".qweight", _pack_along(q.t().contiguous(), 1, AWQ_ORDER)),
+                      (stem + ".qzeros", _pack_along(zeros.to(torch.int64).t().contiguous(), 1, AWQ_ORDER)),
+                      (stem + ".scales", scales.t().contiguous().half())]
+    qcfg = model_config_from_dict(dict(base, quantization_config=dict(quant_method=fmt, bits=4, group_size=GROUP,
+                                                                      desc_act=False, zero_point=True)))
+    want, _ = _hidden(cfg, dense)
+    got, w = _hidden(qcfg, quant)
+    assert w["model.layers.0.mlp.experts.up_gate_proj.qweight"].shape == (4, 256, 16)
+    assert "model.layers.0.mlp.experts.up_gate_proj.weight" not in w
+    assert torch.allclose(got, want, atol=2e-4)
