@@ -9,6 +9,7 @@ samples. Other ranks run :meth:`LLMEngine.follow`. Reference counterparts: Infer
 from __future__ import annotations
 
 import itertools
+import json
 import threading
 import time
 from dataclasses import dataclass, field
@@ -171,6 +172,8 @@ class LLMEngine:
         self._complex_requests = 0  # live requests that need per-token host state (grammar, beams, penalties, ...)
         self.dp = None              # parallel.attn_dp.DPCoordinator under attention data parallelism
         self.adp_balance = None     # parallel.attn_dp.ADPBalance (attention_dp_lb_config.enable_balance)
+        self._ctl_ops: List[Tuple[Dict[str, Any], threading.Event]] = []  # control messages for the follower ranks
+        self.on_control: Optional[Callable[[Dict[str, Any]], None]] = None   # follower side: handler of such messages
         self.dp_router = None       # parallel.attn_dp.DPRequestRouter on the rank that owns the HTTP front-end
         self.dp_worker = None       # parallel.attn_dp.DPRequestWorker on the other DP ranks
         self._dp_arrivals = 0
@@ -332,6 +335,8 @@ class LLMEngine:
     # ---- one step ----------------------------------------------------------------------------------------
     def step(self) -> int:
         """Schedules and runs one step. Returns the number of tokens generated."""
+        if self._ctl_ops:
+            self._flush_control_ops()
         if self.pipeline is not None and getattr(self, "pp_micro_batches", 1) > 1 and self.is_driver:
             return self._step_pipelined()
         if self.async_mode and self.is_driver:
@@ -683,6 +688,35 @@ class LLMEngine:
         self._ctl = group
         self._ctl_src = src
 
+    def post_control(self, msg: Dict[str, Any], wait: float = 60.0) -> bool:
+        """Queues a control message for the follower ranks; it travels in the same ordered stream as the step plans
+        (sent at the start of the next step, before that step is scheduled). Returns once it has been sent."""
+        return self.enqueue_control(msg).wait(wait)
+
+    def enqueue_control(self, msg: Dict[str, Any]) -> threading.Event:
+        """The non-waiting half of ``post_control``: callers that hold the engine lock (so that no step can be
+        scheduled between their change and the message) enqueue here and wait on the event after releasing it."""
+        ev = threading.Event()
+        if not self._has_followers():
+            ev.set()
+            return ev
+        with self.lock:
+            self._ctl_ops.append((msg, ev))
+        self._wake.set()
+        return ev
+
+    def _flush_control_ops(self) -> None:
+        with self.lock:
+            ops, self._ctl_ops = self._ctl_ops, []
+        for msg, ev in ops:
+            data = np.frombuffer(json.dumps(msg).encode(), dtype=np.uint8).copy()
+            h = self._hdr
+            h[:] = 0
+            h[0], h[1] = 4, len(data)
+            dist.broadcast(torch.from_numpy(h), src=self._ctl_src, group=self._ctl)
+            dist.broadcast(torch.from_numpy(data), src=self._ctl_src, group=self._ctl)
+            ev.set()
+
     def _has_followers(self) -> bool:
         """Other ranks execute this engine's plans: tensor-parallel peers and / or later pipeline stages."""
         return self.tp.size > 1 or (self.pipeline is not None and self.pipeline.topo.num_stages > 1)
@@ -735,6 +769,12 @@ class LLMEngine:
             h = hdr.numpy()
             if h[0] == 2:
                 return
+            if h[0] == 4:
+                data = torch.zeros(int(h[1]), dtype=torch.uint8)
+                dist.broadcast(data, src=self._ctl_src, group=self._ctl)
+                if self.on_control is not None:
+                    self.on_control(json.loads(bytes(data.numpy())))
+                continue
             if h[0] == 3:
                 # a DP group's step without a plan: still agree with the other groups, run a mock step if they work
                 stride, _ = self.dp.sync(0, False)
@@ -959,6 +999,8 @@ class LLMEngine:
                 self.serve_dp()
                 return
             while not self._stop.is_set():
+                if self._ctl_ops and not self.has_unfinished():
+                    self._flush_control_ops()
                 if self.has_unfinished():
                     try:
                         self.step()

@@ -164,7 +164,7 @@ class TransferEngine:
         return torch.zeros(4, dtype=torch.int64)
 
     def export_request(self, tokens: Sequence[int], first_tokens: Sequence[int], peer: int,
-                       tracker: Optional[LayerProgressTracker] = None) -> int:
+                       tracker: Optional[LayerProgressTracker] = None, on_blocks=None) -> int:
         """Sends the KV of every FULL block of ``tokens`` (they must still be in the prefix tree: the request was
         just prefilled with prefix caching on) followed by the tokens generated so far. Returns blocks sent."""
         toks = [int(t) for t in tokens]
@@ -173,6 +173,8 @@ class TransferEngine:
         n_blocks = hit // self.block_size
         blocks = list(self.cache.block_table(tmp))[:n_blocks]
         try:
+            if on_blocks is not None:
+                on_blocks(blocks)  # tensor-parallel instances: the other ranks send their shard of the same blocks
             h = self._hdr()
             h[0], h[1], h[2], h[3] = len(toks), n_blocks, len(first_tokens), len(self.kv)
             self.tr.send(h, peer)
@@ -202,6 +204,7 @@ class TransferEngine:
         """Receives one exported request. Returns (prompt tokens, tokens already generated, blocks placed in the
         prefix tree)."""
         h = self._hdr()
+        self.last_import = (0, [])
         self.tr.recv(h, peer)
         n_tok, n_blocks, n_first, n_layers = (int(x) for x in h)
         assert n_layers == len(self.kv), "both instances must hold the same layers"
@@ -227,6 +230,40 @@ class TransferEngine:
         if ok:
             self.cache.commit_filled(tmp, toks[:covered] + [0], covered)
             placed = n_blocks - have
+        self.last_import = (have, table[have:n_blocks] if ok else [])  # which received blocks went where
         self.cache.free_seq(tmp)
         self.recv_blocks += placed
         return toks, first, placed
+
+    # ---- shards of a tensor-parallel instance: same block ids on every rank, no token metadata ----------------
+    def export_shard(self, blocks: Sequence[int], peer: int = 0) -> None:
+        h = self._hdr()
+        h[1], h[3] = len(blocks), len(self.kv)
+        self.tr.send(h, peer)
+        if blocks:
+            idx = torch.tensor(list(blocks), dtype=torch.long, device=self.kv[0].device)
+            for l in range(len(self.kv)):
+                self.tr.send(self.kv[l].index_select(0, idx), peer)
+
+    def import_shard(self, peer: int = 0) -> List[torch.Tensor]:
+        """Receives one shard into host tensors (one per layer, [n_blocks, ...]); ``place_shard`` puts them into the
+        cache once the driving rank has said which blocks they belong to."""
+        h = self._hdr()
+        self.tr.recv(h, peer)
+        n_blocks, n_layers = int(h[1]), int(h[3])
+        assert n_layers == len(self.kv), "both instances must hold the same layers"
+        bufs = []
+        for l in range(n_layers):
+            buf = torch.empty((n_blocks,) + tuple(self.kv[l].shape[1:]), dtype=self.kv[l].dtype)
+            if n_blocks:
+                self.tr.recv(buf, peer)
+            bufs.append(buf)
+        return bufs
+
+    def place_shard(self, bufs: Sequence[torch.Tensor], skip: int, blocks: Sequence[int]) -> None:
+        if not blocks:
+            return
+        dev = self.kv[0].device
+        idx = torch.tensor(list(blocks), dtype=torch.long, device=dev)
+        for l, buf in enumerate(bufs):
+            self.kv[l].index_copy_(0, idx, buf[skip:skip + len(blocks)].to(dev))

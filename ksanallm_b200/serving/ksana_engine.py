@@ -335,6 +335,10 @@ class KsanaLLMEngine:
             from .connector import PDConnector
             self.connector = PDConnector(self.llm, cs)
             self.connector.start()
+        elif cs.group_role in ("prefill", "decode", "both") and topo is None and dp_world is None:
+            from .connector import PDShardWorker
+            self.connector = PDShardWorker(self.llm, cs, world_tp.rank)
+            self.connector.start()
         from ..ops import gemm_tune
         gemm_tune.maybe_load_from_env()  # KSANA_GEMM_TUNE_FILE written by benchmarks/search_best_gemm.py
         if world_tp.rank == 0:

@@ -3,6 +3,7 @@ pipeline_para_size = 2 (two stages, two micro-batches) must generate what a sing
 import asyncio
 import os
 import socket
+import time
 
 import pytest
 import torch.multiprocessing as mp
@@ -115,3 +116,71 @@ def test_attention_dp_groups_with_tensor_parallel_inside():
     got, placed = _spawn(4, dict(tensor_para_size=4, attn_data_para_size=2, expert_para_size=4), "tiny-moe", 4)
     assert got == want
     assert placed == [2, 2]
+
+
+def _pd_worker(role, rank, world, port, out, transfer_port, peer):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), KSANA_SKIP_WARMUP="1")
+    serving = _serving(tensor_para_size=world)
+    serving.setting.batch_scheduler.enable_auto_prefix_cache = True
+    cs = serving.setting.connector
+    cs.group_role, cs.connector_waiting_sec = role, 60
+    if role == "decode":
+        cs.extra["transfer_port"] = transfer_port
+    else:
+        cs.extra["peer_transfer_addr"] = peer
+    eng = KsanaLLMEngine(EngineArgs(config_file="", synthetic_model="tiny-llama", device="cpu", serving=serving))
+    eng.initialize()
+    if rank == 0:
+        body = dict(BODY, input_tokens=[(5 * i + 1) % 200 + 3 for i in range(40)])
+        st, o = asyncio.run(eng.generate(body, streamer=False, req_ctx={"kv-comm-request-id": "tp-pd-1"}))
+        hits = eng.llm.cache.stats.prefix_hit_tokens
+        out.put((role, st.OK(), o.output_tokens[0] if o is not None else None, hits))
+        time.sleep(1.0 if role == "prefill" else 0.0)  # the followers' shards are still on their way
+        eng.shutdown()
+    else:
+        eng.serve_follower()
+        out.put((role + "-follower", eng.connector.exported, eng.connector.imported, 0))
+    import gc
+    import torch.distributed as dist
+    del eng
+    gc.collect()
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def test_prefill_decode_disaggregation_between_tensor_parallel_instances():
+    """A two-rank prefill instance hands a request to a two-rank decode instance: rank 0 of each moves the request
+    and its own KV shard, the other ranks move theirs when the message in the plan stream tells them which blocks."""
+    import time as _t
+    os.environ["KSANA_SKIP_WARMUP"] = "1"
+    eng = _engine()
+    body = dict(BODY, input_tokens=[(5 * i + 1) % 200 + 3 for i in range(40)])
+    st, o = asyncio.run(eng.generate(body, streamer=False))
+    eng.shutdown()
+    want = o.output_tokens[0]
+    ports = []
+    for _ in range(3):
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        ports.append(s.getsockname()[1])
+        s.close()
+    tport = ports[2]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_pd_worker, args=("decode", r, 2, ports[0], q, tport, "")) for r in range(2)]
+    procs += [ctx.Process(target=_pd_worker, args=("prefill", r, 2, ports[1], q, 0, f"127.0.0.1:{tport}"))
+              for r in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(4):
+        role, a, b, c = q.get(timeout=180)
+        got[role] = (a, b, c)
+    for p in procs:
+        p.join(timeout=60)
+    assert [p.exitcode for p in procs] == [0, 0, 0, 0]
+    assert got["prefill"][0] and got["decode"][0]
+    assert got["prefill"][1] == want[:1] and got["decode"][1] == want
+    assert got["decode"][2] >= 32  # the prompt's two full blocks arrived instead of being computed
+    assert got["prefill-follower"][0] == 1 and got["decode-follower"][1] == 1
