@@ -38,11 +38,11 @@ def make_requests(args):
     return out
 
 
-async def one_request(session, url, tokens, n_out, results, args):
+async def one_request(session, url, tokens, n_out, results, args, index=0):
     body = {"input_tokens": tokens, "stream": True,
             "sampling_config": {"max_new_tokens": n_out, "topk": 1, "ignore_eos": True}}
     t0 = time.perf_counter()
-    stamps, n_prev = [], 0
+    stamps, n_prev, last = [], 0, None
     try:
         async with session.post(url, data=json.dumps(body)) as resp:
             buf = b""
@@ -52,14 +52,15 @@ async def one_request(session, url, tokens, n_out, results, args):
                     piece, buf = buf.split(b"\0", 1)
                     if not piece:
                         continue
-                    n = len(json.loads(piece)["output_token_ids"][0])
+                    last = json.loads(piece)
+                    n = len(last["output_token_ids"][0])
                     now = time.perf_counter()
                     stamps.extend([now] * (n - n_prev))
                     n_prev = n
         ok = n_prev > 0
     except Exception:
         ok = False
-    results.append(dict(ok=ok, t0=t0, stamps=stamps, n_in=len(tokens), n_out=n_prev))
+    results.append(dict(ok=ok, t0=t0, stamps=stamps, n_in=len(tokens), n_out=n_prev, index=index, last=last))
 
 
 async def run(args):
@@ -71,8 +72,8 @@ async def run(args):
         t_start = time.perf_counter()
         tasks = []
         rng = random.Random(args.seed + 1)
-        for toks, n_out in reqs:
-            tasks.append(asyncio.create_task(one_request(session, url, toks, n_out, results, args)))
+        for i, (toks, n_out) in enumerate(reqs):
+            tasks.append(asyncio.create_task(one_request(session, url, toks, n_out, results, args, i)))
             if args.request_rate > 0:
                 await asyncio.sleep(rng.expovariate(args.request_rate))
         await asyncio.gather(*tasks)
@@ -98,6 +99,13 @@ async def run(args):
         "tpot_s": {"mean": statistics.fmean(tpot) if tpot else None, "p50": pct(tpot, 50), "p99": pct(tpot, 99)},
     }
     print(json.dumps(rep, indent=1))
+    if args.output:
+        # one line per request, in request order: what benchmarks/check_diff.py compares between two runs
+        with open(args.output, "w", encoding="utf-8") as f:
+            for r in sorted(results, key=lambda r: r["index"]):
+                last = r["last"] or {}
+                f.write(json.dumps({"index": r["index"], "output_token_ids": (last.get("output_token_ids") or [[]])[0],
+                                    "text": (last.get("texts") or [""])[0]}) + "\n")
     return rep
 
 
@@ -117,6 +125,7 @@ def main():
     ap.add_argument("--output_len_max", type=int, default=1024)
     ap.add_argument("--vocab_size", type=int, default=32000)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--output", default="", help="write every request's generated tokens / text to this JSONL file")
     asyncio.run(run(ap.parse_args()))
 
 
