@@ -449,6 +449,7 @@ class KsanaLLMEngine:
         try:
             sp = self._build_sampling(request_dict)
             tokens, refit = self._build_tokens(request_dict)
+            mrope = self._last_mrope  # taken before any await: other requests share the attribute
             grammar = self._grammar_for(sp)
             if pd_rid and self.connector.role == "decode":
                 # the prefill instance computes the prompt and pushes its KV blocks + first token here
@@ -476,7 +477,7 @@ class KsanaLLMEngine:
             elif pd_rid and self.connector.role == "prefill":
                 import dataclasses as _dc
                 sp = _dc.replace(sp, max_new_tokens=1)
-            req = self.llm.add_request(tokens, sp, refit=refit, grammar=grammar, mrope_positions=self._last_mrope)
+            req = self.llm.add_request(tokens, sp, refit=refit, grammar=grammar, mrope_positions=mrope)
             req.ctx = req_ctx or {}
             req.pd_first = pd_first
             req.pd_prompt_len = len(tokens) - len(pd_first)
