@@ -125,7 +125,9 @@ def init_distributed(device_type: str = "cuda", use_fused: bool = True) -> TPGro
     LOCAL_RANK, MASTER_ADDR, MASTER_PORT). Single-process runs need no environment at all."""
     global _WORLD
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
+    # torchrun names first; the reference's launch variables (NODE_RANK / MASTER_HOST, README "multi-node") are
+    # accepted for processes started by hand, one per GPU
+    rank = int(os.environ.get("RANK", os.environ.get("NODE_RANK", "0")))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     if device_type == "cuda":
         torch.cuda.set_device(local)
@@ -136,7 +138,7 @@ def init_distributed(device_type: str = "cuda", use_fused: bool = True) -> TPGro
         _WORLD = TPGroup(0, 1, None, device, use_fused=False)
         return _WORLD
     if not dist.is_initialized():
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_ADDR", os.environ.get("MASTER_HOST", "127.0.0.1"))
         os.environ.setdefault("MASTER_PORT", "29511")
         backend = "nccl" if device_type == "cuda" else "gloo"
         kwargs = {"device_id": device} if device_type == "cuda" else {}

@@ -135,7 +135,7 @@ def main(argv=None) -> None:
     import uvicorn
     args = EngineArgs.from_command_line(argv)
     server = LLMServer(args)
-    rank = int(os.environ.get("RANK", "0"))
+    rank = int(os.environ.get("RANK", os.environ.get("NODE_RANK", "0")))
     server.model.initialize()
     def _leave():
         import gc
