@@ -199,3 +199,37 @@ def test_engine_generation_with_multimodal_positions():
     req = eng.add_request(ids, SamplingParams(topk=1, max_new_tokens=5, ignore_eos=True), mrope_positions=pos3)
     eng.run_until_done()
     assert req.output_token_ids[0] == want
+
+
+def test_beam_search_matches_transformers():
+    """Three beams over a fixed budget without EOS: the hypotheses returned (best first) must equal transformers'
+    beam search - the per-step expansion / pruning and the copy-on-write forks keep the right KV for every beam."""
+    from ksanallm_b200.config.schema import parse_serving_config
+    from ksanallm_b200.engine.llm_engine import LLMEngine
+    from ksanallm_b200.engine.sampling_params import SamplingParams
+    cfg = transformers.LlamaConfig(**BASE)
+    torch.manual_seed(3)
+    hf = transformers.LlamaForCausalLM(cfg).eval().float()
+    with torch.no_grad():
+        hf.lm_head.weight.mul_(8.0)  # sharper distributions: beams differ from greedy and from each other
+    prompt = [5, 9, 77, 120, 33, 4, 8, 200, 3]
+    new = 6
+    with torch.no_grad():
+        out = hf.generate(torch.tensor([prompt]), max_new_tokens=new, num_beams=3, num_return_sequences=2,
+                          do_sample=False, eos_token_id=None, pad_token_id=0, length_penalty=1.0, early_stopping=False)
+        greedy = hf.generate(torch.tensor([prompt]), max_new_tokens=new, do_sample=False, eos_token_id=None,
+                             pad_token_id=0)[0, len(prompt):].tolist()
+    want = [o[len(prompt):].tolist() for o in out]
+    c = model_config_from_dict(cfg.to_dict())
+    c.eos_token_ids = []
+    model = TransformerModel(c, WeightLoader(c, dtype=torch.float32).load(list(hf.state_dict().items())),
+                             max_positions=64)
+    serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 8, "max_step_tokens": 32,
+                                                                     "max_token_len": 64}}})
+    eng = LLMEngine(model, serving, num_blocks=64, num_host_blocks=0)
+    req = eng.add_request(prompt, SamplingParams(num_beams=3, num_return_sequences=2, max_new_tokens=new,
+                                                 ignore_eos=True, length_penalty=1.0))
+    eng.run_until_done()
+    got = [h.tokens for h in sorted(req.beam.finished, key=lambda h: -h.score)[:2]]
+    assert got == want
+    assert want[0] != greedy or want[1] != greedy
