@@ -117,8 +117,9 @@ class LLMEngine:
         self.runner = ModelRunner(model, num_blocks, self.block_size, num_host_blocks, bs_cfg.max_step_tokens,
                                   bs_cfg.max_batch_size, max_blocks_per_seq, kv_dtype, seed)
         self.is_driver = self.tp.rank == 0  # with pipeline stages: re-set by attach_pipeline (global rank 0 drives)
-        self.mtp_steps = bs_cfg.mtp_step_num if (bs_cfg.enable_speculative_decoding or bs_cfg.mtp_step_num) and \
-            model.mtp_layers else 0
+        # one draft per step from the first next-n module (a larger mtp_step_num is clamped)
+        self.mtp_steps = min(bs_cfg.mtp_step_num, 1) if (bs_cfg.enable_speculative_decoding or bs_cfg.mtp_step_num) \
+            and model.mtp_layers else 0
         self.trie_drafts = 3 if (bs_cfg.enable_speculative_decoding and not model.mtp_layers) else 0
         sc = _host.SchedulerConfig()
         sc.block_size = self.block_size
@@ -544,6 +545,8 @@ class LLMEngine:
         # beam search rewrites the sampled tokens from the top-2k log-probs before the scheduler sees them
         if results is None:
             results = self.sched.update(plan, sampled, int(now * 1000))
+        if self.mtp_steps and hidden is not None and meta is not None:
+            self._mtp_propose(plan, meta, hidden, results)
         row = 0
         row_of = {}
         for e in plan.entries:
@@ -656,6 +659,75 @@ class LLMEngine:
                 self._complex_requests -= 1
             if self.metrics is not None:
                 self.metrics.observe_request(req)
+
+    def _mtp_propose(self, plan, meta, hidden, results) -> None:
+        """Multi-token prediction drafts (DeepSeek next-n module): after the main model's step the MTP layer runs
+        over the same rows with every row's FOLLOWING token as its second input (the next prompt token, the next fed
+        token, or - at a sequence's last accepted row - the token just generated); the arg-max at that row is the
+        draft the next step verifies. The layer keeps its own KV pages under the same block tables; rows of rejected
+        drafts are written again when their positions are fed again. Reference: LlmRuntime::MtpForward
+        (runtime/llm_runtime.cpp:172-240), deepseek_v3_model.cpp:231-288. One draft per step."""
+        model = self.model
+        mtp = model.mtp_layers[0]
+        by_seq = {r.seq_id: r for r in results}
+        fix_rows, fix_vals, draft_rows, draft_seqs = [], [], [], []
+        row0 = 0
+        for e in plan.entries:
+            q, real = e.q_len, e.q_len - e.n_drafts
+            owner = self.seq_owner.get(e.seq_id)
+            r = by_seq.get(e.seq_id)
+            if e.num_logits == 0:
+                if owner is not None:  # a prompt chunk: what follows it is the next prompt token
+                    toks = owner[0].prompt_tokens
+                    nxt_pos = e.q_start + q
+                    if nxt_pos < len(toks):
+                        fix_rows.append(row0 + q - 1)
+                        fix_vals.append(int(toks[nxt_pos]))
+            elif r is not None and len(r.new_tokens) > r.accepted_drafts:
+                last = row0 + real - 1 + r.accepted_drafts
+                fix_rows.append(last)
+                fix_vals.append(int(r.new_tokens[r.accepted_drafts]))  # the token after the accepted drafts
+                if r.finish_reason == _host.FINISH_NONE:
+                    draft_rows.append(last)
+                    draft_seqs.append(e.seq_id)
+            row0 += q
+        nxt = torch.roll(meta.input_ids, -1)
+        if fix_rows:
+            nxt[torch.tensor(fix_rows, device=nxt.device)] = torch.tensor(fix_vals, dtype=nxt.dtype, device=nxt.device)
+        rows = torch.tensor(draft_rows, dtype=torch.int32, device=nxt.device)
+        if self._has_followers():
+            # tensor-parallel peers run the same draft pass (its collectives need them): they get the shifted ids
+            n = torch.tensor([len(draft_rows)], dtype=torch.int32)
+            dist.broadcast(n, src=self._ctl_src, group=self._ctl)
+            dist.broadcast(nxt.to("cpu", torch.int32), src=self._ctl_src, group=self._ctl)
+            if draft_rows:
+                dist.broadcast(rows.cpu(), src=self._ctl_src, group=self._ctl)
+        drafts = self._mtp_forward(mtp, nxt, rows, meta, hidden)
+        if drafts is not None:
+            for sid, d in zip(draft_seqs, drafts.tolist()):
+                self.sched.set_drafts(sid, [int(d)])
+
+    @torch.inference_mode()
+    def _mtp_forward(self, mtp, nxt, rows, meta, hidden):
+        model = self.model
+        from .. import ops
+        embeds = ops.embedding(nxt, model.embed, model.cfg.emb_scale)
+        h = mtp.forward(embeds, hidden, meta, self.runner.kv_caches[len(model.layers)])
+        if rows.numel() == 0:
+            return None
+        return model.greedy_tokens(h, rows)
+
+    def _mtp_follow(self, meta, hidden) -> None:
+        """Follower half of ``_mtp_propose``."""
+        n = torch.zeros(1, dtype=torch.int32)
+        dist.broadcast(n, src=self._ctl_src, group=self._ctl)
+        nxt = torch.zeros(meta.total_tokens, dtype=torch.int32)
+        dist.broadcast(nxt, src=self._ctl_src, group=self._ctl)
+        rows = torch.zeros(int(n[0]), dtype=torch.int32)
+        if int(n[0]):
+            dist.broadcast(rows, src=self._ctl_src, group=self._ctl)
+        dev = self.runner.device
+        self._mtp_forward(self.model.mtp_layers[0], nxt.to(dev), rows.to(dev), meta, hidden)
 
     def _run_probes(self, plan, meta, hidden) -> None:
         for e in plan.entries:
@@ -826,6 +898,8 @@ class LLMEngine:
                 continue
             hidden = self.runner.forward(meta, refit)
             self.runner.sample(hidden, meta, None, bool(h[30]))
+            if self.mtp_steps:
+                self._mtp_follow(meta, hidden)
             if self.dp is not None and self.dp.stopping:
                 return
 
