@@ -1,0 +1,39 @@
+"""The engine under KV memory pressure on CPU (real model, real cache tensors): swap pre-emption to host blocks,
+recompute pre-emption, prefix reuse, chunked prefill and parallel sampling all at once; every request's tokens must
+equal those of a run with plenty of memory."""
+import pytest
+import torch
+
+from ksanallm_b200.config.model_config import tiny_llama_config
+from ksanallm_b200.config.schema import parse_serving_config
+from ksanallm_b200.engine.llm_engine import LLMEngine
+from ksanallm_b200.engine.sampling_params import SamplingParams
+from ksanallm_b200.models.loader import load_model_weights
+from ksanallm_b200.models.transformer import TransformerModel
+
+
+def _engine(model, num_blocks, host_blocks, preempt_mode, split_fuse):
+    serving = parse_serving_config({"setting": {"batch_scheduler": {
+        "max_batch_size": 6, "max_step_tokens": 96, "max_token_len": 256, "enable_auto_prefix_cache": True,
+        "preempt_mode": preempt_mode, "split_fuse_token_num": split_fuse}, "block_manager": {"block_token_num": 16}}})
+    return LLMEngine(model, serving, num_blocks=num_blocks, num_host_blocks=host_blocks)
+
+
+@pytest.mark.parametrize("preempt_mode,host_blocks", [(0, 32), (1, 0)])
+def test_outputs_survive_preemption(preempt_mode, host_blocks):
+    cfg = tiny_llama_config()
+    model = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.02, dtype=torch.float32))
+    g = torch.Generator().manual_seed(5)
+    stem = torch.randint(3, 31000, (32,), generator=g).tolist()
+    prompts = [stem + torch.randint(3, 31000, (n,), generator=g).tolist() for n in (5, 17, 30, 9, 22, 3)]
+    sp = SamplingParams(topk=1, max_new_tokens=40, ignore_eos=True)
+    roomy = _engine(model, 128, 0, 1, 0)
+    want = [r.output_token_ids[0] for r in roomy.generate(prompts, sp)]
+    tight = _engine(model, 20, host_blocks, preempt_mode, 24)  # 20 blocks = 320 tokens for ~6 x 90 tokens of demand
+    got = [r.output_token_ids[0] for r in tight.generate(prompts, sp)]
+    assert got == want
+    st = tight.sched.stats
+    assert (st.preempt_swap if preempt_mode == 0 else st.preempt_recompute) > 0
+    assert tight.cache.stats.prefix_hit_tokens >= 32
+    if preempt_mode == 0:
+        assert tight.cache.stats.swapped_out_blocks > 0 and tight.cache.stats.swapped_in_blocks > 0
