@@ -37,3 +37,31 @@ def test_outputs_survive_preemption(preempt_mode, host_blocks):
     assert tight.cache.stats.prefix_hit_tokens >= 32
     if preempt_mode == 0:
         assert tight.cache.stats.swapped_out_blocks > 0 and tight.cache.stats.swapped_in_blocks > 0
+
+
+def test_fp8_kv_cache_with_scales_stays_close_to_the_full_precision_cache():
+    """fp8 (e4m3) KV cache with per-layer scaling factors: same engine, 8-bit pages; logits of a long prompt stay
+    close to the fp32-cache run and greedy decoding runs to completion."""
+    from ksanallm_b200.engine.step_input import make_step_input
+    from ksanallm_b200.models.kv_scales import apply_kv_scales
+    cfg = tiny_llama_config()
+    model = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.02, dtype=torch.float32))
+    T = 40
+    ids = torch.randint(3, 31000, (T,), generator=torch.Generator().manual_seed(2)).tolist()
+    meta = make_step_input(ids, list(range(T)), list(range(T)), [0, T], [T], [[0, 1, 2]], device="cpu")
+    full = model.compute_logits(model.forward(meta, model.allocate_kv_cache(4, 16)), meta.logits_idx)[0]
+    apply_kv_scales(model, [0.05] * cfg.num_layers)
+    cache8 = model.allocate_kv_cache(4, 16, torch.float8_e4m3fn)
+    assert cache8[0].dtype == torch.float8_e4m3fn
+    # prefill in two chunks so that the second one reads 8-bit pages written by the first
+    m1 = make_step_input(ids[:24], list(range(24)), list(range(24)), [0, 24], [24], [[0, 1, 2]], device="cpu")
+    model.forward(m1, cache8)
+    m2 = make_step_input(ids[24:], list(range(24, T)), list(range(24, T)), [0, T - 24], [T], [[0, 1, 2]], device="cpu")
+    low = model.compute_logits(model.forward(m2, cache8), m2.logits_idx)[0]
+    rel = (low - full).abs().max().item() / full.abs().max().item()
+    assert 0 < rel < 0.1
+    serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 2, "max_step_tokens": 64,
+                                                                     "max_token_len": 128}}})
+    eng = LLMEngine(model, serving, num_blocks=16, num_host_blocks=0, kv_dtype=torch.float8_e4m3fn)
+    req = eng.generate([ids], SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True))[0]
+    assert len(req.output_token_ids[0]) == 6
