@@ -1,0 +1,62 @@
+"""One tiny Llama written to disk as (a) one safetensors file, (b) sharded safetensors, (c) a PyTorch ``.bin``,
+(d) safetensors under foreign tensor names plus a ``<model_type>_weight_map.json``: every directory, loaded through
+the same entry point, yields the same logits."""
+import json
+import os
+
+import torch
+from safetensors.torch import save_file
+
+from ksanallm_b200.config.model_config import load_model_config
+from ksanallm_b200.engine.step_input import make_step_input
+from ksanallm_b200.models.loader import load_model_weights, synthetic_checkpoint
+from ksanallm_b200.models.transformer import TransformerModel
+
+CONFIG = dict(model_type="llama", hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              intermediate_size=128, vocab_size=300, torch_dtype="float32", max_position_embeddings=64,
+              rms_norm_eps=1e-5, rope_theta=10000.0)
+
+
+def _logits(model_dir):
+    cfg = load_model_config(model_dir)
+    model = TransformerModel(cfg, load_model_weights(cfg, model_dir, dtype=torch.float32), max_positions=64)
+    T = 9
+    meta = make_step_input(list(range(5, 5 + T)), list(range(T)), list(range(T)), [0, T], [T], [[0]], device="cpu")
+    return model.compute_logits(model.forward(meta, model.allocate_kv_cache(1, 16)), meta.logits_idx)[0]
+
+
+def _dir(tmp_path, name, config=CONFIG):
+    d = tmp_path / name
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(config))
+    return str(d)
+
+
+def test_all_formats_load_to_the_same_model(tmp_path):
+    cfg = load_model_config(_dir(tmp_path, "cfg_only"))
+    sd = {k: v.contiguous() for k, v in synthetic_checkpoint(cfg, seed=7, dtype=torch.float32)}
+    a = _dir(tmp_path, "single")
+    save_file(sd, os.path.join(a, "model.safetensors"))
+    want = _logits(a)
+
+    b = _dir(tmp_path, "sharded")
+    keys = sorted(sd)
+    for i in range(3):
+        part = {k: sd[k] for k in keys[i::3]}
+        save_file(part, os.path.join(b, f"model-{i + 1:05d}-of-00003.safetensors"))
+    assert torch.equal(_logits(b), want)
+
+    c = _dir(tmp_path, "bin")
+    torch.save(sd, os.path.join(c, "pytorch_model.bin"))
+    assert torch.equal(_logits(c), want)
+
+    # foreign names + a weight map (regex -> replacement) next to the checkpoint
+    d = _dir(tmp_path, "mapped", dict(CONFIG, model_type="mymodel"))
+    foreign = {k.replace("model.layers.", "decoder.blocks.").replace("self_attn.", "attn.")
+               .replace("model.embed_tokens", "decoder.wte").replace("model.norm", "decoder.ln_out"): v
+               for k, v in sd.items()}
+    save_file(foreign, os.path.join(d, "model.safetensors"))
+    with open(os.path.join(d, "mymodel_weight_map.json"), "w") as f:
+        json.dump({r"^decoder\.blocks\.": "model.layers.", r"\.attn\.": ".self_attn.",
+                   r"^decoder\.wte": "model.embed_tokens", r"^decoder\.ln_out": "model.norm"}, f)
+    assert torch.equal(_logits(d), want)
