@@ -159,7 +159,7 @@ class PyAsyncStreamingIterator:
         if self.done:
             raise StopAsyncIteration
         loop = asyncio.get_running_loop()
-        self.version = await loop.run_in_executor(None, self.req.wait, self.version, 1.0)
+        self.version = await loop.run_in_executor(self.engine.pool, self.req.wait, self.version, 1.0)
         out = self.engine._snapshot(self.req)
         if self.req.finished:
             self.done = True
@@ -201,6 +201,12 @@ class KsanaLLMEngine:
         self.model_config: Optional[ModelConfig] = None
         self.plugin = None
         self.think_end_token_id: Optional[int] = None
+        # every in-flight request parks one thread while it waits for its next tokens; the event loop's default
+        # executor (a few dozen threads) would make hundreds of concurrent streams take turns (the reference runs its
+        # blocking calls in a 1024-thread executor as well: ksana_engine.py)
+        from concurrent.futures import ThreadPoolExecutor
+        self.pool = ThreadPoolExecutor(max_workers=int(os.environ.get("KSANA_WAITER_THREADS", "1024")),
+                                       thread_name_prefix="ksana-wait")
 
     @classmethod
     def from_engine_args(cls, args: EngineArgs) -> "KsanaLLMEngine":
@@ -363,6 +369,7 @@ class KsanaLLMEngine:
             self.connector.stop()
         if self.llm is not None:
             self.llm.stop()
+        self.pool.shutdown(wait=False)
 
     def _load_plugin(self) -> None:
         from .plugin import load_plugin
@@ -454,7 +461,7 @@ class KsanaLLMEngine:
             if pd_rid and self.connector.role == "decode":
                 # the prefill instance computes the prompt and pushes its KV blocks + first token here
                 loop0 = asyncio.get_running_loop()
-                got = await loop0.run_in_executor(None, self.connector.wait_import, pd_rid,
+                got = await loop0.run_in_executor(self.pool, self.connector.wait_import, pd_rid,
                                                   float(self.serving.setting.connector.connector_waiting_sec))
                 if got is None:
                     return Status(RetCode.RET_REQUEST_TIMEOUT,
@@ -491,11 +498,11 @@ class KsanaLLMEngine:
         loop = asyncio.get_running_loop()
         v = -1
         while not req.finished:
-            v = await loop.run_in_executor(None, req.wait, v, 1.0)
+            v = await loop.run_in_executor(self.pool, req.wait, v, 1.0)
         out = self._snapshot(req)
         if pd_rid and self.connector.role == "prefill" and req.error is None:
             # hand the request over: KV of the prompt's full blocks + the first token
-            await loop.run_in_executor(None, self.connector.export, pd_rid, (req_ctx or {}).get("kv-comm-group-key", ""),
+            await loop.run_in_executor(self.pool, self.connector.export, pd_rid, (req_ctx or {}).get("kv-comm-group-key", ""),
                                        list(req.prompt_tokens), list(req.seqs[0].output_tokens))
         if self.plugin is not None:
             self.plugin.postprocess(request_dict, out)
@@ -527,7 +534,7 @@ class KsanaLLMEngine:
         for q in reqs:
             v = -1
             while not q.finished:
-                v = await loop.run_in_executor(None, q.wait, v, 1.0)
+                v = await loop.run_in_executor(self.pool, q.wait, v, 1.0)
         responses = [{"input_token_ids": list(q.prompt_tokens), "response": q.probe_result or []} for q in reqs]
         payload = {"responses": responses}
         data = json.dumps(payload).encode() if is_json else msgpack.packb(payload, use_bin_type=True)

@@ -87,3 +87,20 @@ def test_dropping_the_stream_aborts_the_request(eng):
     assert req.finished and len(req.seqs[0].output_tokens) < 200
     assert req.seqs[0].finish_reason == "abort"
     assert not eng.llm.has_unfinished()
+
+
+def test_many_concurrent_requests_complete_and_match_sequential_runs(eng):
+    """More requests in flight than the event loop's default executor has threads: each parks a waiter thread in the
+    engine's own pool; all finish, and batching changes no token."""
+    import time
+    bodies = [{"input_tokens": [5 + (i % 7), 9, 77 + i, 120, 33], "stream": False,
+               "sampling_config": {"topk": 1, "max_new_tokens": 6, "ignore_eos": True}} for i in range(72)]
+    seq = [asyncio.run(eng.generate(dict(b), streamer=False))[1].output_tokens[0] for b in bodies[:6]]
+
+    async def burst():
+        return await asyncio.gather(*[eng.generate(dict(b), streamer=False) for b in bodies])
+
+    t0 = time.time()
+    res = asyncio.run(burst())
+    assert all(st.OK() for st, _ in res) and time.time() - t0 < 60
+    assert [o.output_tokens[0] for _, o in res[:6]] == seq
