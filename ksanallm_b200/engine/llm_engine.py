@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import itertools
 import json
+import os
 import threading
 import time
 from dataclasses import dataclass, field
@@ -173,6 +174,7 @@ class LLMEngine:
         self._complex_requests = 0  # live requests that need per-token host state (grammar, beams, penalties, ...)
         self.dp = None              # parallel.attn_dp.DPCoordinator under attention data parallelism
         self.adp_balance = None     # parallel.attn_dp.ADPBalance (attention_dp_lb_config.enable_balance)
+        self._status_every = int(os.environ.get("KSANA_STATUS_CHECK_STEPS", "64"))  # 0: never read the status word
         self._ctl_ops: List[Tuple[Dict[str, Any], threading.Event]] = []  # control messages for the follower ranks
         self.on_control: Optional[Callable[[Dict[str, Any]], None]] = None   # follower side: handler of such messages
         self.dp_router = None       # parallel.attn_dp.DPRequestRouter on the rank that owns the HTTP front-end
@@ -545,6 +547,11 @@ class LLMEngine:
         # beam search rewrites the sampled tokens from the top-2k log-probs before the scheduler sees them
         if results is None:
             results = self.sched.update(plan, sampled, int(now * 1000))
+        # reading the status word waits for the device: cheap after a synchronous step (it is idle), but under
+        # asynchronous scheduling it would wait for the step in flight, so that path looks 16 times less often
+        every = self._status_every * (16 if hidden is None else 1)
+        if every and self.step_count % every == every - 1:
+            self.runner.check_device_status()  # raises: the serve loop then fails what is in flight
         if self.mtp_steps and hidden is not None and meta is not None:
             self._mtp_propose(plan, meta, hidden, results)
         row = 0

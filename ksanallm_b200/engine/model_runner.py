@@ -100,6 +100,17 @@ class ModelRunner:
                 cache[db, 0, :, do] = k.to(cache.dtype)
                 cache[db, 1, :, do] = cache[sb, 1, :, so]
 
+    def check_device_status(self) -> None:
+        """Kernels whose bounded waits expire (a peer that stopped answering, a barrier that never completed) do not
+        hang: they set a bit in a device status word and return. This reads the word (and clears it); a non-zero
+        value means a recent step produced garbage on this GPU, so the caller fails the requests in flight."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import cuda as kc
+        code = kc.read_error(clear=True)
+        if code:
+            raise RuntimeError(f"device status word 0x{code:x}: a kernel gave up waiting (peer or barrier timeout)")
+
     # ---- forward ---------------------------------------------------------------------------------------
     def upload(self, layout: Dict[str, int]) -> StepInput:
         meta = self.staging.upload(layout)
