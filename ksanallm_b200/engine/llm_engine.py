@@ -378,7 +378,7 @@ class LLMEngine:
                     self.tp.ep.step_stride = max(stride, 1)
                 if plan.empty():
                     if stride > 0:
-                        self.runner.mock_forward()
+                        self.runner.mock_forward(bool(self.mtp_steps))
                         self.stats["mock_steps"] = self.stats.get("mock_steps", 0) + 1
                     return 0
             if plan.empty():
@@ -860,7 +860,7 @@ class LLMEngine:
                 if self.tp.ep is not None:
                     self.tp.ep.step_stride = max(stride, 1)
                 if stride > 0:
-                    self.runner.mock_forward()
+                    self.runner.mock_forward(bool(self.mtp_steps))
                 if self.dp.stopping:
                     return
                 continue

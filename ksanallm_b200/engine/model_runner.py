@@ -124,13 +124,17 @@ class ModelRunner:
         return hidden
 
     @torch.inference_mode()
-    def mock_forward(self) -> None:
+    def mock_forward(self, with_mtp: bool = False) -> None:
         """A step with zero tokens: only the collectives inside the layers matter (expert-parallel exchanges of
         the MoE blocks when other data-parallel ranks have work)."""
         from .step_input import make_step_input
         meta = make_step_input([], [], [], [0], [], torch.zeros(0, 1, dtype=torch.int32), logits_idx=[],
                                num_prefill=0, device=self.device)
-        self.model.forward(meta, self.kv_caches)
+        h = self.model.forward(meta, self.kv_caches)
+        if with_mtp and self.model.mtp_layers:
+            # the draft pass of the working ranks goes through the expert exchange once more: join it
+            mtp = self.model.mtp_layers[0]
+            mtp.forward(h.new_zeros(0, h.shape[-1]), h, meta, self.kv_caches[len(self.model.layers)])
 
     @torch.inference_mode()
     def sample(self, hidden: torch.Tensor, meta: StepInput, rows: Optional[Sequence[SampleRow]],

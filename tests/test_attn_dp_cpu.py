@@ -188,3 +188,62 @@ def test_expert_placement_permutation_and_routing_dump(tmp_path, monkeypatch):
     n_tok = sum(len(p) for p in PROMPTS[0]) + 2 * 3
     assert set(counts) == {"layer_0", "layer_1"} and sum(counts["layer_0"]) == 2 * n_tok
     layers._EPLB_LAYERS.clear()
+
+
+def _mtp_dp_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      EPLB_WEIGHT="")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = _mtp_cfg()
+    w = load_model_weights(cfg, synthetic_seed=4, dtype=torch.float32, ep_rank=rank, ep_size=world)
+    tp = TPGroup()
+    tp.ep_rank, tp.ep_size = rank, world
+    tp.ep = GatherEPExchange(dist.group.WORLD, rank, world, cfg.num_experts_per_tok, cfg.num_experts)
+    serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 64,
+                                                                     "max_token_len": 128, "mtp_step_num": 1}}})
+    eng = LLMEngine(TransformerModel(cfg, w, tp), serving, tp, num_blocks=64, num_host_blocks=0)
+    eng.attach_dp(DPCoordinator(dist.group.WORLD))
+    reqs = [eng.add_request(p, SamplingParams(topk=1, max_new_tokens=NEW[rank], ignore_eos=True)) for p in PROMPTS[rank]]
+    steps = eng.run_dp(max_steps=200)
+    out.put((rank, [r.output_token_ids[0] for r in reqs], steps, eng.sched.stats.draft_proposed))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _mtp_cfg():
+    return model_config_from_dict(dict(
+        model_type="deepseek_v3", hidden_size=128, num_hidden_layers=2, num_attention_heads=4, vocab_size=300,
+        intermediate_size=256, n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1, moe_intermediate_size=64,
+        first_k_dense_replace=1, n_group=4, topk_group=2, norm_topk_prob=True, routed_scaling_factor=2.5,
+        q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+        num_nextn_predict_layers=1, torch_dtype="float32", max_position_embeddings=256, eos_token_id=2))
+
+
+def test_mtp_drafts_under_attention_dp_keep_the_ranks_in_step():
+    """The draft pass goes through the expert exchange a second time per step; a rank that idles (mock steps) joins
+    that one too. Outputs equal single-process decoding without drafts."""
+    cfg = _mtp_cfg()
+    w = load_model_weights(cfg, synthetic_seed=4, dtype=torch.float32)
+    want = {}
+    for r in (0, 1):
+        eng = LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=64, num_host_blocks=0)
+        want[r] = [q.output_token_ids[0] for q in
+                   eng.generate(PROMPTS[r], SamplingParams(topk=1, max_new_tokens=NEW[r], ignore_eos=True))]
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_mtp_dp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(2):
+        rank, toks, steps, proposed = q.get(timeout=120)
+        got[rank] = (toks, steps, proposed)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got[0][0] == want[0] and got[1][0] == want[1]
+    assert got[0][1] == got[1][1] and got[0][2] > 0
