@@ -54,7 +54,9 @@ class ReasoningParser:
 
     # ---- streaming split ---------------------------------------------------------------------------------------
     def new_stream_state(self, enable_thinking: Optional[bool] = None) -> Dict:
-        return {"mode": "reasoning" if self.in_reasoning_at_start(enable_thinking) else "unknown", "buf": ""}
+        # "head": nothing emitted yet - a model that starts in reasoning mode may still write the opening tag itself
+        return {"mode": "reasoning" if self.in_reasoning_at_start(enable_thinking) else "unknown", "buf": "",
+                "head": True}
 
     def extract_streaming(self, state: Dict, delta: str) -> Tuple[Optional[str], Optional[str]]:
         """Feeds one text delta, returns (reasoning_delta, content_delta). Tags split across deltas are handled by
@@ -78,6 +80,15 @@ class ReasoningParser:
                 state["mode"] = "content" if self.end_token not in buf else "reasoning"
                 continue
             # reasoning
+            if state.get("head"):
+                stripped = buf.lstrip()
+                if stripped.startswith(self.start_token):
+                    buf = state["buf"] = stripped[len(self.start_token):]
+                    state["head"] = False
+                elif stripped and self.start_token.startswith(stripped):
+                    break  # might still become the opening tag
+                elif stripped:
+                    state["head"] = False
             i = buf.find(self.end_token)
             if i >= 0:
                 r_out += buf[:i]
