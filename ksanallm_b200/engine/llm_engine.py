@@ -593,11 +593,11 @@ class LLMEngine:
                 self._finish_seq(r.seq_id, reason, notify=False)
             else:
                 trie = req.tries.get(r.seq_id)
-                if trie is not None:
+                if trie is not None and req.grammar is None:
                     d = trie.propose(self.trie_drafts)
                     if d:
                         self.sched.set_drafts(r.seq_id, d)
-                if self.ptp_steps:
+                if self.ptp_steps and req.grammar is None:
                     self.sched.set_drafts(r.seq_id, [self.ptp_token] * self.ptp_steps)
             # fan-out of parallel samples once the prompt's blocks are cached
             if getattr(req, "_pending_fanout", 0) and r.new_tokens:
@@ -694,7 +694,8 @@ class LLMEngine:
                 last = row0 + real - 1 + r.accepted_drafts
                 fix_rows.append(last)
                 fix_vals.append(int(r.new_tokens[r.accepted_drafts]))  # the token after the accepted drafts
-                if r.finish_reason == _host.FINISH_NONE:
+                # (a grammar-constrained request takes no drafts: only its first logits row carries the token mask)
+                if r.finish_reason == _host.FINISH_NONE and (owner is None or owner[0].grammar is None):
                     draft_rows.append(last)
                     draft_seqs.append(e.seq_id)
             row0 += q
