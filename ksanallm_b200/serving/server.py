@@ -136,7 +136,12 @@ def main(argv=None) -> None:
     args = EngineArgs.from_command_line(argv)
     server = LLMServer(args)
     rank = int(os.environ.get("RANK", os.environ.get("NODE_RANK", "0")))
+    from ..utils.logger import StateReporter, setup_logging
+    log = setup_logging(rank=rank)
+    log.info("starting: config %s, model %s", args.config_file, args.model_dir or args.synthetic_model)
     server.model.initialize()
+    if rank == 0:
+        StateReporter(server.model.llm).start()
     def _leave():
         import gc
         import torch.distributed as dist

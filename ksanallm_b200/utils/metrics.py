@@ -125,6 +125,9 @@ class Metrics:
             self.c["spec_draft_token_num"] = st.draft_proposed
             self.c["spec_accepted_token_num"] = st.draft_accepted
             self.c["forward_req_timeout_num"] = st.timeouts
+            self.c["flexible_cache_hit_token_num"] = cs.flexible_hit_tokens
+            self.c["pp_micro_batch_migration_num"] = st.mb_migrations
+            self.g["spec_draft_hit_rate"] = st.draft_accepted / st.draft_proposed if st.draft_proposed else 0.0
 
     # ---- exposition --------------------------------------------------------------------------------------------
     def prometheus_text(self) -> str:

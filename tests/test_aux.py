@@ -171,3 +171,35 @@ def test_gemm_tuning_map(tmp_path):
     assert gemm_tune.lookup(4096, 4096, 4096) == (0, 0) and gemm_tune.lookup(16, 11008, 4096) == (0, 0)
     gemm_tune.clear()
     assert gemm_tune.lookup(16, 4096, 4096) == (0, 0)
+
+
+def test_logging_levels_categories_and_state_lines(tmp_path):
+    import json
+    import logging
+    from ksanallm_b200.config.model_config import tiny_llama_config
+    from ksanallm_b200.config.schema import parse_serving_config
+    from ksanallm_b200.engine.llm_engine import LLMEngine
+    from ksanallm_b200.engine.sampling_params import SamplingParams
+    from ksanallm_b200.models.loader import load_model_weights
+    from ksanallm_b200.models.transformer import TransformerModel
+    from ksanallm_b200.utils import logger as kl
+    kl._configured = False
+    logf = tmp_path / "log" / "k.log"
+    main = kl.setup_logging("WARNING,SCHEDULER", str(logf))
+    assert main.getEffectiveLevel() == logging.WARNING
+    assert kl.get_logger("SCHEDULER").getEffectiveLevel() == logging.DEBUG
+    assert kl.get_logger("MOE").getEffectiveLevel() == logging.WARNING
+    cfg = tiny_llama_config()
+    eng = LLMEngine(TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, dtype=torch.float32)),
+                    parse_serving_config({"setting": {"batch_scheduler": {"max_token_len": 64}}}), num_blocks=16,
+                    num_host_blocks=0)
+    eng.generate([[5, 6, 7]], SamplingParams(topk=1, max_new_tokens=3, ignore_eos=True))
+    rep = kl.StateReporter(eng, stat_file=str(tmp_path / "stat.jsonl"))
+    s = rep.report_once()
+    assert s["generated_tokens"] == 3 and s["running"] == 0 and s["blocks_total"] == 16
+    assert json.loads((tmp_path / "stat.jsonl").read_text().splitlines()[0])["prompt_tokens"] == 3
+    for h in logging.getLogger("ksanallm").handlers:
+        h.flush()
+    assert "state step=" in logf.read_text()
+    logging.getLogger("ksanallm").handlers.clear()
+    kl._configured = False
