@@ -8,6 +8,7 @@ samples. Other ranks run :meth:`LLMEngine.follow`. Reference counterparts: Infer
 """
 from __future__ import annotations
 
+import contextlib
 import itertools
 import json
 import os
@@ -25,6 +26,7 @@ from ..config.model_config import ModelConfig
 from ..config.schema import ServingConfig
 from ..models.transformer import TransformerModel
 from ..parallel.comm import TPGroup
+from ..utils import tracing as _tracing
 from .model_runner import ModelRunner
 from .sampler import SampleRow
 from .sampling_params import SamplingParams
@@ -158,7 +160,10 @@ class LLMEngine:
         self._wake = threading.Event()
         self.step_count = 0
         self.metrics = None  # utils.metrics.Metrics, attached by the server
-        self.tracer = None
+        # KLLM_SCHED_TRACE_LEVEL=1|2: Begin / End events of every step's phases (and, at level 2, of every request)
+        # go to sched_events_node_<rank>.csv; ENABLE_PROFILE_EVENT adds NVTX ranges around the same phases
+        from ..utils.tracing import ScheduleEventTracer
+        self.tracer = ScheduleEventTracer(self.tp.rank, directory=os.environ.get("KLLM_SCHED_TRACE_DIR", "."))
         self._ctl = None  # CPU process group for plan broadcast
         self._ctl_src = 0
         self._hdr = np.zeros(64, dtype=np.int32)
@@ -349,8 +354,18 @@ class LLMEngine:
             return drained + self._step_sync()
         return self._step_sync()
 
+    @contextlib.contextmanager
+    def _phase(self, name: str, batch: int = 0, tokens: int = 0):
+        """One phase of a step for the tracers (no cost when both are off)."""
+        if not self.tracer.enabled and not _tracing._NVTX:
+            yield
+            return
+        with _tracing.profile_scope(name), self.tracer.span(name, self.step_count, batch, tokens):
+            yield
+
     def _step_sync(self) -> int:
         t0 = time.perf_counter()
+        self.tracer.record("Schedule", "B", self.step_count)
         with self.lock:
             if self.adp_balance is not None:
                 arrivals, self._dp_arrivals = self._dp_arrivals, 0
@@ -380,29 +395,44 @@ class LLMEngine:
                     if stride > 0:
                         self.runner.mock_forward(bool(self.mtp_steps))
                         self.stats["mock_steps"] = self.stats.get("mock_steps", 0) + 1
+                    self.tracer.record("Schedule", "E", self.step_count)
                     return 0
             if plan.empty():
+                self.tracer.record("Schedule", "E", self.step_count)
                 return 0
         t1 = time.perf_counter()
+        nb, nt = len(plan.entries), plan.total_tokens
+        self.tracer.record("Schedule", "E", self.step_count, -1, nb, nt)
+        if self.tracer.level >= 2:
+            for e in plan.entries:
+                self.tracer.record("ForwardRequest", "B", self.step_count, e.seq_id, 1, e.q_len, level=2)
         if self._has_followers() and not dp_group:
-            self._broadcast_plan(layout, plan, greedy, refit=refit, mrope=mrope)
+            with self._phase("BroadcastPlan", nb, nt):
+                self._broadcast_plan(layout, plan, greedy, refit=refit, mrope=mrope)
         ta = time.perf_counter()
-        self.runner.apply_flexible(plan.flexible)
-        self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
-        meta = self.runner.upload(layout)
-        if mrope is not None:
-            meta.mrope_positions = mrope.to(self.runner.device)
+        with self._phase("PrepareForwarding", nb, nt):
+            self.runner.apply_flexible(plan.flexible)
+            self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
+            meta = self.runner.upload(layout)
+            if mrope is not None:
+                meta.mrope_positions = mrope.to(self.runner.device)
         if self.pipeline is not None and self.pipeline.topo.num_stages > 1:
-            out, hidden = self._pipeline_step_driver(meta, refit, rows, greedy)
+            with self._phase("ForwardingLayers", nb, nt):
+                out, hidden = self._pipeline_step_driver(meta, refit, rows, greedy)
             tb = time.perf_counter()
         else:
-            hidden = self.runner.forward(meta, refit)
-            self._run_probes(plan, meta, hidden)
+            with self._phase("ForwardingLayers", nb, nt):
+                hidden = self.runner.forward(meta, refit)
+                self._run_probes(plan, meta, hidden)
             tb = time.perf_counter()
-            out = self.runner.sample(hidden, meta, rows, greedy)
+            with self._phase("LmHeadSampling", nb, nt):
+                out = self.runner.sample(hidden, meta, rows, greedy)
         t2 = time.perf_counter()
-        with self.lock:
+        with self.lock, self._phase("UpdateResults", nb, nt):
             n_new = self._apply_results(plan, out, meta, hidden)
+        if self.tracer.level >= 2:
+            for e in plan.entries:
+                self.tracer.record("ForwardRequest", "E", self.step_count, e.seq_id, 1, e.q_len, level=2)
         t3 = time.perf_counter()
         self.step_count += 1
         st = self.stats
@@ -463,15 +493,18 @@ class LLMEngine:
         if self._has_followers():
             self._broadcast_plan(layout, plan, True, fixup=fix)
         ta = time.perf_counter()
-        self.runner.apply_flexible(plan.flexible)
-        self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
-        meta = self.runner.upload(layout)
-        if fix:
-            self.runner.fixup_inputs(meta)
-        hidden = self.runner.forward(meta, None)
-        handle = self.runner.sample_greedy_async(hidden, meta)
+        nb, nt = len(plan.entries), plan.total_tokens
+        with self._phase("LaunchStep", nb, nt):
+            self.runner.apply_flexible(plan.flexible)
+            self.runner.apply_block_ops(plan.swap_out, plan.swap_in, plan.block_copies)
+            meta = self.runner.upload(layout)
+            if fix:
+                self.runner.fixup_inputs(meta)
+            hidden = self.runner.forward(meta, None)
+            handle = self.runner.sample_greedy_async(hidden, meta)
         tb = time.perf_counter()
-        n_new = self._drain_inflight()  # the PREVIOUS step: its tokens were produced before this one started
+        with self._phase("ResolvePreviousStep", nb, nt):
+            n_new = self._drain_inflight()  # the PREVIOUS step: its tokens were produced before this one started
         t2 = time.perf_counter()
         with self.lock:
             placeholders = [-(1 + i) for i in range(plan.total_logits)]

@@ -203,3 +203,33 @@ def test_logging_levels_categories_and_state_lines(tmp_path):
     assert "state step=" in logf.read_text()
     logging.getLogger("ksanallm").handlers.clear()
     kl._configured = False
+
+
+def test_engine_writes_schedule_events(tmp_path, monkeypatch):
+    """KLLM_SCHED_TRACE_LEVEL=2: every step's phases and every request's steps appear as Begin / End pairs."""
+    from ksanallm_b200.config.model_config import tiny_llama_config
+    from ksanallm_b200.config.schema import parse_serving_config
+    from ksanallm_b200.engine.llm_engine import LLMEngine
+    from ksanallm_b200.engine.sampling_params import SamplingParams
+    from ksanallm_b200.models.loader import load_model_weights
+    from ksanallm_b200.models.transformer import TransformerModel
+    from ksanallm_b200.utils.tracing import summarise_trace
+    monkeypatch.setenv("KLLM_SCHED_TRACE_LEVEL", "2")
+    monkeypatch.setenv("KLLM_SCHED_TRACE_DIR", str(tmp_path))
+    cfg = tiny_llama_config()
+    eng = LLMEngine(TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, dtype=torch.float32)),
+                    parse_serving_config({"setting": {"batch_scheduler": {"max_token_len": 64}}}), num_blocks=16,
+                    num_host_blocks=0)
+    eng.generate([[5, 6, 7], [8, 9]], SamplingParams(topk=1, max_new_tokens=4, ignore_eos=True))
+    eng.tracer.close()
+    path = tmp_path / "sched_events_node_0.csv"
+    rows = path.read_text().splitlines()
+    assert rows[0].startswith("time_ns,node_rank,event,phase")
+    events = [r.split(",") for r in rows[1:]]
+    names = {e[2] for e in events}
+    assert {"Schedule", "PrepareForwarding", "ForwardingLayers", "LmHeadSampling", "UpdateResults",
+            "ForwardRequest"} <= names
+    for n in names:
+        assert sum(e[3] == "B" for e in events if e[2] == n) == sum(e[3] == "E" for e in events if e[2] == n)
+    summary = summarise_trace(str(path), str(tmp_path / "trace.json"))
+    assert summary["ForwardingLayers"]["count"] == eng.stats["steps"] and (tmp_path / "trace.json").exists()
