@@ -179,6 +179,7 @@ class LLMEngine:
         self._complex_requests = 0  # live requests that need per-token host state (grammar, beams, penalties, ...)
         self.dp = None              # parallel.attn_dp.DPCoordinator under attention data parallelism
         self.adp_balance = None     # parallel.attn_dp.ADPBalance (attention_dp_lb_config.enable_balance)
+        self._check_blocks = bool(getattr(bm_cfg, "enable_block_checksum", False))
         self._status_every = int(os.environ.get("KSANA_STATUS_CHECK_STEPS", "64"))  # 0: never read the status word
         self._ctl_ops: List[Tuple[Dict[str, Any], threading.Event]] = []  # control messages for the follower ranks
         self.on_control: Optional[Callable[[Dict[str, Any]], None]] = None   # follower side: handler of such messages
@@ -416,6 +417,7 @@ class LLMEngine:
             meta = self.runner.upload(layout)
             if mrope is not None:
                 meta.mrope_positions = mrope.to(self.runner.device)
+        guard = self._checksum_guard(plan) if self._check_blocks else None
         if self.pipeline is not None and self.pipeline.topo.num_stages > 1:
             with self._phase("ForwardingLayers", nb, nt):
                 out, hidden = self._pipeline_step_driver(meta, refit, rows, greedy)
@@ -427,6 +429,8 @@ class LLMEngine:
             tb = time.perf_counter()
             with self._phase("LmHeadSampling", nb, nt):
                 out = self.runner.sample(hidden, meta, rows, greedy)
+        if guard is not None:
+            self._checksum_verify(guard)
         t2 = time.perf_counter()
         with self.lock, self._phase("UpdateResults", nb, nt):
             n_new = self._apply_results(plan, out, meta, hidden)
@@ -699,6 +703,31 @@ class LLMEngine:
                 self._complex_requests -= 1
             if self.metrics is not None:
                 self.metrics.observe_request(req)
+
+    def _checksum_guard(self, plan):
+        """setting.block_manager.enable_block_checksum (debug): the blocks that were already full before this step -
+        cached prefixes included - must come out of the step unchanged. Checksums of the first and last layer's
+        pages are taken before the forward and compared after it (reference: CalculateChecksum, cache_copy.cu:407,
+        verification in models/base/model_input.cpp:380-530)."""
+        from ..utils.memory_checker import block_checksums
+        blocks = set()
+        for e in plan.entries:
+            table = self.cache.block_table(e.seq_id)
+            blocks.update(table[:e.q_start // self.block_size])
+        blocks = sorted(blocks)
+        if not blocks:
+            return None
+        layers = sorted({0, len(self.runner.kv_caches) - 1})
+        return blocks, layers, [block_checksums(self.runner.kv_caches[l], blocks) for l in layers]
+
+    def _checksum_verify(self, guard) -> None:
+        from ..utils.memory_checker import block_checksums
+        blocks, layers, before = guard
+        for l, b in zip(layers, before):
+            now = block_checksums(self.runner.kv_caches[l], blocks)
+            bad = [blocks[i] for i in (now != b).nonzero().flatten().tolist()]
+            if bad:
+                raise RuntimeError(f"KV block checksum changed during step {self.step_count}: layer {l}, blocks {bad[:8]}")
 
     def _mtp_propose(self, plan, meta, hidden, results) -> None:
         """Multi-token prediction drafts (DeepSeek next-n module): after the main model's step the MTP layer runs

@@ -800,6 +800,17 @@ def load_model_weights(cfg: ModelConfig, model_dir: str = "", tp_rank: int = 0, 
                           model_dir=model_dir, layer_range=layer_range)
     if synthetic_seed is not None or not model_dir:
         src = synthetic_checkpoint(cfg, synthetic_seed or 0, synthetic_std, device=device, dtype=dtype)
-    else:
-        src = iter_checkpoint(model_dir)
-    return loader.load(src)
+        return loader.load(src)
+    # ENABLE_MODEL_CACHE=1: the processed (sliced, fused, quantised) tensors of this rank are kept as one
+    # safetensors file and reloaded at the next start instead of running the loader again
+    from . import model_cache
+    tag = "_".join(str(x) for x in (quantize or "plain", str(loader.dtype).split(".")[-1],
+                                    f"ep{loader.ep_rank}of{loader.ep_size}",
+                                    f"l{layer_range.start}-{layer_range.stop}" if layer_range is not None else "all"))
+    cached = model_cache.cache_file(model_dir, tp_rank, tp_size, tag)
+    if cached and os.path.isfile(cached):
+        return model_cache.load_weights(cached, device)
+    weights = loader.load(iter_checkpoint(model_dir))
+    if cached:
+        model_cache.save_weights(cached, weights)
+    return weights

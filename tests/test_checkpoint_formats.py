@@ -60,3 +60,18 @@ def test_all_formats_load_to_the_same_model(tmp_path):
         json.dump({r"^decoder\.blocks\.": "model.layers.", r"\.attn\.": ".self_attn.",
                    r"^decoder\.wte": "model.embed_tokens", r"^decoder\.ln_out": "model.norm"}, f)
     assert torch.equal(_logits(d), want)
+
+
+def test_processed_weight_cache_is_written_and_reused(tmp_path, monkeypatch):
+    cfg = load_model_config(_dir(tmp_path, "cfg_only"))
+    sd = {k: v.contiguous() for k, v in synthetic_checkpoint(cfg, seed=7, dtype=torch.float32)}
+    d = _dir(tmp_path, "cached")
+    save_file(sd, os.path.join(d, "model.safetensors"))
+    want = _logits(d)
+    monkeypatch.setenv("ENABLE_MODEL_CACHE", "1")
+    monkeypatch.setenv("MODEL_CACHE_PATH", str(tmp_path / "cache"))
+    assert torch.equal(_logits(d), want)
+    files = os.listdir(tmp_path / "cache")
+    assert len(files) == 1 and files[0].startswith("rank0of1")
+    os.remove(os.path.join(d, "model.safetensors"))  # the second start never opens the checkpoint
+    assert torch.equal(_logits(d), want)

@@ -65,3 +65,32 @@ def test_fp8_kv_cache_with_scales_stays_close_to_the_full_precision_cache():
     eng = LLMEngine(model, serving, num_blocks=16, num_host_blocks=0, kv_dtype=torch.float8_e4m3fn)
     req = eng.generate([ids], SamplingParams(topk=1, max_new_tokens=6, ignore_eos=True))[0]
     assert len(req.output_token_ids[0]) == 6
+
+
+def test_block_checksum_guard_passes_on_a_clean_run_and_catches_a_stray_write():
+    """enable_block_checksum: blocks that were full before a step must leave it unchanged. A clean run (prefix
+    reuse + chunked prefill + decode) raises nothing; a forward that scribbles into an old block is caught."""
+    cfg = tiny_llama_config()
+    model = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.02, dtype=torch.float32))
+    serving = parse_serving_config({"setting": {"batch_scheduler": {
+        "max_batch_size": 4, "max_step_tokens": 64, "max_token_len": 256, "enable_auto_prefix_cache": True,
+        "split_fuse_token_num": 16}, "block_manager": {"block_token_num": 16, "enable_block_checksum": True}}})
+    eng = LLMEngine(model, serving, num_blocks=32, num_host_blocks=0)
+    assert eng._check_blocks
+    g = torch.Generator().manual_seed(9)
+    stem = torch.randint(3, 31000, (32,), generator=g).tolist()
+    sp = SamplingParams(topk=1, max_new_tokens=20, ignore_eos=True)
+    eng.generate([stem + [7, 8, 9], stem + [10, 11]], sp)
+    # now a "kernel bug": every forward also overwrites slot 0 of block 0 in the first layer
+    orig = eng.runner.forward
+
+    def bad_forward(meta, refit=None):
+        h = orig(meta, refit)
+        eng.runner.kv_caches[0][eng.cache.block_table(req.seqs[0].seq_id)[0]].view(-1)[0] += 1.0
+        return h
+
+    eng.runner.forward = bad_forward
+    req = eng.add_request(stem + [12, 13, 14], sp)
+    with pytest.raises(RuntimeError, match="checksum changed"):
+        for _ in range(10):
+            eng.step()
