@@ -102,8 +102,9 @@ class LLMEngine:
     def __init__(self, model: TransformerModel, serving: ServingConfig, tp: Optional[TPGroup] = None,
                  num_blocks: Optional[int] = None, num_host_blocks: Optional[int] = None,
                  detokenize: Optional[Callable[[List[int]], str]] = None, seed: int = 0,
-                 kv_dtype: Optional[torch.dtype] = None):
+                 kv_dtype: Optional[torch.dtype] = None, block_sync_group=None):
         self.model = model
+        self._block_sync_group = block_sync_group  # pipeline stages: world group for the block-count agreement
         self.cfg: ModelConfig = model.cfg
         self.serving = serving
         self.tp = tp or model.tp
@@ -214,9 +215,12 @@ class LLMEngine:
             n = max(int(budget // per_block), 16)
         else:
             n = 512
-        if self.tp.size > 1:
+        # every rank that shares block tables must own the same number of blocks: the smallest offer wins
+        # (tensor-parallel peers; pipeline stages hold different layers, so their offers differ too)
+        for grp in ([self.tp.group] if self.tp.size > 1 else []) + \
+                ([self._block_sync_group] if self._block_sync_group is not None else []):
             t = torch.tensor([n], dtype=torch.int64, device=self.model.device)
-            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.tp.group)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=grp)
             n = int(t.item())
         cap = self.serving.setting.batch_scheduler
         need = (cap.max_token_len // self.block_size + 2) * max(cap.max_batch_size, 1) * 4

@@ -308,7 +308,7 @@ class KsanaLLMEngine:
             if scales_file:
                 apply_kv_scales(model, load_kv_cache_scales(scales_file, tp.rank, cfg.num_layers))
         self.llm = LLMEngine(model, self.serving, tp, detokenize=lambda ids: self.tokenizer.decode(ids),
-                             kv_dtype=kv_dtype)
+                             kv_dtype=kv_dtype, block_sync_group=world_tp.group if topo is not None else None)
         if dp_world is not None:
             import torch.distributed as dist
             from ..parallel.attn_dp import DPCoordinator, DPRequestRouter, DPRequestWorker
