@@ -334,6 +334,7 @@ class KsanaLLMEngine:
             self.llm.attach_pipeline(PipelineStage(model, topo, HiddenChannel(topo, cfg.hidden_size, dtype, device)),
                                      max(int(bs.max_pp_batch_num), 1))
         self.is_driver = world_tp.rank == 0
+        self._start_heartbeat(world_tp)
         self._load_plugin()
         self.connector = None
         cs = self.serving.setting.connector
@@ -354,6 +355,28 @@ class KsanaLLMEngine:
                 self.llm.warmup(max_len=min(2048, self.serving.setting.batch_scheduler.max_token_len))
             self.llm.start()
 
+    def _start_heartbeat(self, world) -> None:
+        """Failure detection between the ranks of one instance: every rank beats to rank 0 over the TCP control
+        channel; a rank that falls silent (process gone, host down) is reported, rank 0 fails what is in flight and
+        refuses new requests instead of waiting in a collective for ever. KSANA_HEARTBEAT_TIMEOUT_S (default 120, 0 =
+        off). Reference: distributed/control_channel.cpp heartbeat -> cluster shutdown."""
+        self.control = None
+        self.failed_ranks = []
+        timeout = float(os.environ.get("KSANA_HEARTBEAT_TIMEOUT_S", "120"))
+        if world.size <= 1 or timeout <= 0:
+            return
+        from ..parallel.control_channel import ControlMaster, ControlWorker
+        host = os.environ.get("MASTER_ADDR", "127.0.0.1")
+        port = int(os.environ.get("KSANA_CONTROL_PORT", int(os.environ.get("MASTER_PORT", "29511")) + 23))
+        interval = max(min(timeout / 4.0, 30.0), 0.05)
+        if world.rank == 0:
+            def lost(rank: int) -> None:
+                self.failed_ranks.append(rank)
+                self.llm._fail_all(RuntimeError(f"rank {rank} stopped sending heartbeats"))
+            self.control = ControlMaster(host, port, world.size, interval, timeout, on_failure=lost)
+        else:
+            self.control = ControlWorker(host, port, world.rank, interval, timeout, connect_timeout=120.0)
+
     def serve_follower(self) -> None:
         """Blocks in the follower loop (ranks > 0): executes rank 0's plans (TP / PP), or - as an attention-DP rank -
         runs its own scheduler on the requests rank 0 places here."""
@@ -363,6 +386,8 @@ class KsanaLLMEngine:
             self.llm.follow()
 
     def shutdown(self) -> None:
+        if getattr(self, "control", None) is not None:
+            (self.control.shutdown if hasattr(self.control, "shutdown") else self.control.close)()
         from ..models.layers import dump_eplb_counts
         dump_eplb_counts(rank=int(os.environ.get("RANK", "0")))  # no-op unless DUMP_EPLB_PATH asked for routing counts
         if getattr(self, "connector", None) is not None:
@@ -451,6 +476,8 @@ class KsanaLLMEngine:
     async def generate(self, request_dict: Dict[str, Any], streamer: Optional[bool] = None,
                        req_ctx: Optional[Dict[str, str]] = None):
         """Returns (Status, KsanaPythonOutput) or (Status, async iterator of KsanaPythonOutput) when streaming."""
+        if getattr(self, "failed_ranks", None):
+            return Status(RetCode.RET_INTERNAL_ERROR, f"ranks {self.failed_ranks} of this instance are gone"), None
         pd_first: List[int] = []
         pd_rid = (req_ctx or {}).get("kv-comm-request-id") if getattr(self, "connector", None) is not None else None
         try:

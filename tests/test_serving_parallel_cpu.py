@@ -184,3 +184,45 @@ def test_prefill_decode_disaggregation_between_tensor_parallel_instances():
     assert got["prefill"][1] == want[:1] and got["decode"][1] == want
     assert got["decode"][2] >= 32  # the prompt's two full blocks arrived instead of being computed
     assert got["prefill-follower"][0] == 1 and got["decode-follower"][1] == 1
+
+
+def _hb_worker(rank, world, port, out):
+    import threading
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), KSANA_SKIP_WARMUP="1", KSANA_HEARTBEAT_TIMEOUT_S="1.0")
+    eng = _engine(tensor_para_size=2)
+    if rank == 0:
+        st1, _ = asyncio.run(eng.generate(dict(BODY), streamer=False))
+        deadline = time.time() + 20
+        while not eng.failed_ranks and time.time() < deadline:
+            time.sleep(0.1)
+        st2, o2 = asyncio.run(eng.generate(dict(BODY), streamer=False))
+        out.put((st1.OK(), list(eng.failed_ranks), st2.OK(), st2.GetMessage()))
+        eng.shutdown()
+    else:
+        # a host-side failure: this rank keeps working but falls silent on the control channel
+        threading.Timer(1.0, lambda: setattr(eng.control, "paused", True)).start()
+        eng.serve_follower()
+    import gc
+    import torch.distributed as dist
+    del eng
+    gc.collect()
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def test_a_silent_rank_is_detected_and_new_requests_are_refused():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_hb_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    ok1, failed, ok2, msg = q.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+    assert [p.exitcode for p in procs] == [0, 0]
+    assert ok1 and failed == [1] and not ok2 and "gone" in msg
