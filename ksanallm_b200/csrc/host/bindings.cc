@@ -100,6 +100,7 @@ PYBIND11_MODULE(_ksana_host, m) {
       .def_readwrite("ptp_mode", &SchedulerConfig::ptp_mode)
       .def_readwrite("min_flexible_cache_num", &SchedulerConfig::min_flexible_cache_num)
       .def_readwrite("pp_wb_strategy", &SchedulerConfig::pp_wb_strategy)
+      .def_readwrite("lookahead_slots", &SchedulerConfig::lookahead_slots)
       .def_readwrite("decode_token_threshold", &SchedulerConfig::decode_token_threshold);
 
   py::class_<SchedStats>(m, "SchedStats")

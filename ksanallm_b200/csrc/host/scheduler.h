@@ -78,6 +78,9 @@ struct SchedulerConfig {
   // micro-batch, one unit per sequence; 2 = the same plus moving work off a micro-batch that exceeds 1.2x the mean;
   // 3 = like 2 with a sequence weighing 1 + (tokens to compute) / 200; 4 = like 2 weighing the tokens to compute.
   int pp_wb_strategy = 0;
+  // Extra KV slots reserved past the tokens of a step: a multi-step draft module writes its own cache entries for
+  // the positions it drafts ahead of (mtp_step_num - 1).
+  int lookahead_slots = 0;
   int decode_token_threshold = 1;  // q_len <= threshold with cached KV counts as a decode entry
 };
 
@@ -388,7 +391,7 @@ class Scheduler {
         keep.push_back(id);
         continue;
       }
-      bool ok = cache_->EnsureCapacity(id, s.num_computed + q_len);
+      bool ok = cache_->EnsureCapacity(id, s.num_computed + q_len + cfg_.lookahead_slots);
       while (!ok) {
         // Pre-empt the most recently admitted sequence that is not yet planned this step.
         if (running_.size() <= 1) break;
@@ -405,7 +408,7 @@ class Scheduler {
         int64_t victim = *vit;
         running_.erase(vit);
         Preempt(victim, &plan);
-        ok = cache_->EnsureCapacity(id, s.num_computed + q_len);
+        ok = cache_->EnsureCapacity(id, s.num_computed + q_len + cfg_.lookahead_slots);
       }
       if (!ok) {
         // Even alone it does not fit right now: pre-empt itself.
@@ -437,7 +440,7 @@ class Scheduler {
           !running_.empty())
         break;
       if (!cache_->SwapIn(id, &plan.swap_in)) break;
-      if (!cache_->EnsureCapacity(id, s.num_computed + need_now)) {
+      if (!cache_->EnsureCapacity(id, s.num_computed + need_now + cfg_.lookahead_slots)) {
         // Could not grow after coming back: stay resident, run next step.
         swapped_.pop_front();
         s.state = SEQ_RUNNING;
@@ -517,12 +520,12 @@ class Scheduler {
       if (cfg_.split_fuse_token_num > 0) q_len = std::min(q_len, cfg_.split_fuse_token_num);
       q_len = std::min(q_len, token_budget);
       if (q_len <= 0) break;
-      if (!cache_->EnsureCapacity(id, s.num_computed + q_len)) {
+      if (!cache_->EnsureCapacity(id, s.num_computed + q_len + cfg_.lookahead_slots)) {
         if (running_.empty() && prefill.empty() && decode.empty()) {
           // Nothing else holds memory besides the cache itself; shrink the chunk to what fits.
           int fit = cache_->num_available_blocks() * cfg_.block_size;
           q_len = std::min(q_len, fit);
-          if (q_len <= 0 || !cache_->EnsureCapacity(id, s.num_computed + q_len)) {
+          if (q_len <= 0 || !cache_->EnsureCapacity(id, s.num_computed + q_len + cfg_.lookahead_slots)) {
             cache_->FreeSeq(id);
             s.num_computed = 0;
             plan.flexible.resize(flex_mark);

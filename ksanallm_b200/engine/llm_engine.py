@@ -121,9 +121,12 @@ class LLMEngine:
         self.runner = ModelRunner(model, num_blocks, self.block_size, num_host_blocks, bs_cfg.max_step_tokens,
                                   bs_cfg.max_batch_size, max_blocks_per_seq, kv_dtype, seed)
         self.is_driver = self.tp.rank == 0  # with pipeline stages: re-set by attach_pipeline (global rank 0 drives)
-        # one draft per step from the first next-n module (a larger mtp_step_num is clamped)
-        self.mtp_steps = min(bs_cfg.mtp_step_num, 1) if (bs_cfg.enable_speculative_decoding or bs_cfg.mtp_step_num) \
+        # drafts per step from the first next-n module (applied repeatedly for more than one; with tensor-parallel
+        # peers one draft, since the further passes are not part of the followers' step protocol)
+        self.mtp_steps = bs_cfg.mtp_step_num if (bs_cfg.enable_speculative_decoding or bs_cfg.mtp_step_num) \
             and model.mtp_layers else 0
+        if self.tp.size > 1:
+            self.mtp_steps = min(self.mtp_steps, 1)
         self.trie_drafts = 3 if (bs_cfg.enable_speculative_decoding and not model.mtp_layers) else 0
         sc = _host.SchedulerConfig()
         sc.block_size = self.block_size
@@ -145,6 +148,7 @@ class LLMEngine:
         sc.max_draft_tokens = max(self.mtp_steps, self.trie_drafts, self.ptp_steps)
         sc.ptp_mode = self.ptp_steps > 0
         sc.pp_wb_strategy = int(getattr(bs_cfg, "pp_multibatch_wb_strategy", 0) or 0)
+        sc.lookahead_slots = max(self.mtp_steps - 1, 0)
         sc.min_flexible_cache_num = self._flexible_cache_min(bs_cfg, model, kv_dtype)
         sc.decode_token_threshold = 1 + sc.max_draft_tokens
         self.cache = _host.KVCacheManager(num_blocks, num_host_blocks, self.block_size,
@@ -777,16 +781,54 @@ class LLMEngine:
             if draft_rows:
                 dist.broadcast(rows.cpu(), src=self._ctl_src, group=self._ctl)
         drafts = self._mtp_forward(mtp, nxt, rows, meta, hidden)
-        if drafts is not None:
-            for sid, d in zip(draft_seqs, drafts.tolist()):
-                self.sched.set_drafts(sid, [int(d)])
+        if drafts is None:
+            return
+        chains = [[int(d)] for d in drafts.tolist()]
+        if self.mtp_steps > 1:
+            # further drafts: the module is applied again at the following positions, fed with its own previous
+            # output and the token it just drafted (its cache entries for those positions live in the look-ahead
+            # slots the scheduler reserved)
+            pos0 = {}
+            for e in plan.entries:
+                r = by_seq.get(e.seq_id)
+                if r is not None:
+                    pos0[e.seq_id] = e.q_start + (e.q_len - e.n_drafts) + r.accepted_drafts
+            self._mtp_chain(mtp, draft_seqs, [pos0[s_] for s_ in draft_seqs], chains, rows)
+        for sid, ch in zip(draft_seqs, chains):
+            self.sched.set_drafts(sid, ch)
+
+    @torch.inference_mode()
+    def _mtp_chain(self, mtp, seqs, positions, chains, rows) -> None:
+        from .. import ops
+        from .step_input import make_step_input
+        model, bs = self.model, self.block_size
+        cache = self.runner.kv_caches[len(model.layers)]
+        prev = self._mtp_residual.index_select(0, rows.long())
+        tables = [self.cache.block_table(s_) for s_ in seqs]
+        n = len(seqs)
+        for k in range(1, self.mtp_steps):
+            pos = [p + k - 1 for p in positions]
+            if any(p // bs >= len(t) for p, t in zip(pos, tables)):
+                return  # no reserved slot (end of the length budget): shorter chains for everybody
+            slots = [t[p // bs] * bs + p % bs for p, t in zip(pos, tables)]
+            width = max(len(t) for t in tables)
+            bt = [list(t) + [0] * (width - len(t)) for t in tables]
+            ids = [c[-1] for c in chains]
+            meta = make_step_input(ids, pos, slots, list(range(n + 1)), [p + 1 for p in pos], bt, logits_idx=list(range(n)),
+                                   num_prefill=0, device=self.runner.device)
+            emb = ops.embedding(meta.input_ids, model.embed, model.cfg.emb_scale)
+            h, prev = mtp.forward(emb, prev, meta, cache, return_residual=True)
+            nxt = model.greedy_tokens(h, meta.logits_idx).tolist()
+            for c, d in zip(chains, nxt):
+                c.append(int(d))
 
     @torch.inference_mode()
     def _mtp_forward(self, mtp, nxt, rows, meta, hidden):
         model = self.model
         from .. import ops
         embeds = ops.embedding(nxt, model.embed, model.cfg.emb_scale)
-        h = mtp.forward(embeds, hidden, meta, self.runner.kv_caches[len(model.layers)])
+        h, self._mtp_residual = mtp.forward(embeds, hidden, meta, self.runner.kv_caches[len(model.layers)],
+                                            return_residual=True)
         if rows.numel() == 0:
             return None
         return model.greedy_tokens(h, rows)

@@ -242,11 +242,15 @@ class MTPLayer:
         self.layer = DecoderLayer(cfg, w, idx, tp, rope_cache)
         self.final_norm = w[p + ".shared_head.norm.weight"]
 
-    def forward(self, embeds: torch.Tensor, prev_hidden: torch.Tensor, meta, kv_cache) -> torch.Tensor:
+    def forward(self, embeds: torch.Tensor, prev_hidden: torch.Tensor, meta, kv_cache,
+                return_residual: bool = False):
+        """Returns the module's output after its head norm; with ``return_residual`` also the un-normalised output,
+        which is the ``prev_hidden`` of the next draft step when the module is applied repeatedly."""
         eps = self.cfg.rms_norm_eps
         e = ops.rms_norm(embeds, self.enorm, eps)
         h = ops.rms_norm(prev_hidden, self.hnorm, eps)
         x = self.eh_proj(torch.cat((e, h), dim=-1))
         residual = x.clone()
         hn = ops.rms_norm(x, self.layer.ln1, eps)
-        return self.layer.forward(hn, residual, meta, kv_cache, self.final_norm)
+        out = self.layer.forward(hn, residual, meta, kv_cache, self.final_norm)
+        return (out, residual) if return_residual else out

@@ -158,3 +158,47 @@ def test_mtp_under_tensor_parallelism_matches_plain_decoding():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got == want and proposed > 0
+
+
+def test_two_draft_steps_are_lossless_and_the_second_draft_follows_the_chain_rule():
+    """mtp_step_num = 2: the module is applied a second time one position further, fed with its own un-normalised
+    output and the token it just drafted. Decoding stays exact; the first proposal after the prompt equals a
+    hand-written two-step chain."""
+    from ksanallm_b200.engine.step_input import make_step_input
+    from ksanallm_b200 import ops
+    cfg = _ds_cfg()
+    w = load_model_weights(cfg, synthetic_seed=4, dtype=torch.float32)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, 290, (n,), generator=g).tolist() for n in (7, 19, 33)]
+    plain, _ = _run(cfg, w, prompts, 12)
+    spec, eng = _run(cfg, w, prompts, 12, mtp_step_num=2)
+    assert eng.mtp_steps == 2 and eng.sched_cfg.lookahead_slots == 1 and spec == plain
+    assert eng.sched.stats.draft_proposed >= 2 * 3  # two drafts per sequence and step
+
+    model = TransformerModel(cfg, w)
+    tokens = prompts[1]
+    T = len(tokens)
+    caches = model.allocate_kv_cache(4, 64)
+    meta = make_step_input(tokens, list(range(T)), list(range(T)), [0, T], [T], [[0, 1, 2, 3]], device="cpu")
+    h = model.forward(meta, caches)
+    t1 = int(model.compute_logits(h, meta.logits_idx)[0].argmax())
+    mtp, mc = model.mtp_layers[0], caches[len(model.layers)]
+    nxt = torch.tensor(tokens[1:] + [t1], dtype=torch.int32)
+    hp, res = mtp.forward(ops.embedding(nxt, model.embed, cfg.emb_scale), h, meta, mc, return_residual=True)
+    d1 = int(model.compute_logits(hp[-1:])[0].argmax())
+    m2 = make_step_input([d1], [T], [T], [0, 1], [T + 1], [[0, 1, 2, 3]], device="cpu")
+    hp2 = mtp.forward(ops.embedding(m2.input_ids, model.embed, cfg.emb_scale), res[-1:], m2, mc)
+    d2 = int(model.compute_logits(hp2)[0].argmax())
+
+    eng2 = LLMEngine(model, _serving(mtp_step_num=2), num_blocks=64, num_host_blocks=0)
+    seen = []
+    orig = eng2._mtp_chain
+
+    def spy(mtp_, seqs, positions, chains, rows):
+        orig(mtp_, seqs, positions, chains, rows)
+        seen.append([list(c) for c in chains])
+
+    eng2._mtp_chain = spy
+    req = eng2.add_request(tokens, SamplingParams(topk=1, max_new_tokens=3, ignore_eos=True))
+    eng2.run_until_done()
+    assert req.output_token_ids[0][0] == t1 and seen[0] == [[d1, d2]]
