@@ -94,9 +94,25 @@ def read_gguf(path: str) -> Tuple[Dict[str, Any], Dict[str, torch.Tensor]]:
     return meta, tensors
 
 
+def unpermute_rope_rows(w: torch.Tensor, n_head: int) -> torch.Tensor:
+    """llama.cpp's converter reorders the rows of q / k projections of Llama-architecture models so that its
+    adjacent-pair rotary kernel matches the half-split convention of the original weights (rows [head][2][d/2] ->
+    [head][d/2][2]); this is the inverse, giving back the Hugging Face row order."""
+    rows = w.shape[0]
+    return w.reshape(n_head, rows // n_head // 2, 2, *w.shape[1:]).swapaxes(1, 2).reshape(w.shape)
+
+
 def iter_gguf(path: str) -> Iterator[Tuple[str, torch.Tensor]]:
-    _, tensors = read_gguf(path)
+    meta, tensors = read_gguf(path)
+    arch = str(meta.get("general.architecture", ""))
+    n_head = int(meta.get(f"{arch}.attention.head_count", 0) or 0)
+    n_kv = int(meta.get(f"{arch}.attention.head_count_kv", n_head) or n_head)
     for name, t in tensors.items():
+        if arch == "llama" and n_head and t.dim() == 2:
+            if name.endswith("attn_q.weight"):
+                t = unpermute_rope_rows(t, n_head)
+            elif name.endswith("attn_k.weight"):
+                t = unpermute_rope_rows(t, n_kv)
         hf = name
         for pat, rep in _NAME_MAP:
             hf = re.sub(pat, rep, hf)

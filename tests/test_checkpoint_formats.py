@@ -75,3 +75,41 @@ def test_processed_weight_cache_is_written_and_reused(tmp_path, monkeypatch):
     assert len(files) == 1 and files[0].startswith("rank0of1")
     os.remove(os.path.join(d, "model.safetensors"))  # the second start never opens the checkpoint
     assert torch.equal(_logits(d), want)
+
+
+def test_gguf_llama_checkpoint_with_converter_row_order(tmp_path):
+    """A GGUF file as llama.cpp's converter writes it for Llama-architecture models (q / k rows reordered for its
+    rotary kernel, llama.cpp tensor names) loads to the same logits as the original safetensors."""
+    from ksanallm_b200.models import gguf_reader
+    cfg = load_model_config(_dir(tmp_path, "cfg_only"))
+    sd = {k: v.contiguous() for k, v in synthetic_checkpoint(cfg, seed=7, dtype=torch.float32)}
+    a = _dir(tmp_path, "st")
+    save_file(sd, os.path.join(a, "model.safetensors"))
+    want = _logits(a)
+
+    def permute(w, n_head):  # the converter's reordering
+        return w.reshape(n_head, 2, w.shape[0] // n_head // 2, *w.shape[1:]).swapaxes(1, 2).reshape(w.shape)
+
+    names = {"model.embed_tokens.weight": "token_embd.weight", "model.norm.weight": "output_norm.weight",
+             "lm_head.weight": "output.weight"}
+    per_layer = {"input_layernorm": "attn_norm", "post_attention_layernorm": "ffn_norm", "self_attn.q_proj": "attn_q",
+                 "self_attn.k_proj": "attn_k", "self_attn.v_proj": "attn_v", "self_attn.o_proj": "attn_output",
+                 "mlp.gate_proj": "ffn_gate", "mlp.up_proj": "ffn_up", "mlp.down_proj": "ffn_down"}
+    g = {}
+    for k, v in sd.items():
+        if k in names:
+            g[names[k]] = v
+            continue
+        _, _, li, rest = k.split(".", 3)
+        stem = rest[:-len(".weight")]
+        t = v
+        if stem == "self_attn.q_proj":
+            t = permute(v, cfg.num_heads)
+        elif stem == "self_attn.k_proj":
+            t = permute(v, cfg.num_kv_heads)
+        g[f"blk.{li}.{per_layer[stem]}.weight"] = t.contiguous()
+    d = _dir(tmp_path, "gguf")
+    gguf_reader.write_gguf(os.path.join(d, "model.gguf"), g, {
+        "general.architecture": "llama", "llama.block_count": cfg.num_layers,
+        "llama.attention.head_count": cfg.num_heads, "llama.attention.head_count_kv": cfg.num_kv_heads})
+    assert torch.allclose(_logits(d), want, atol=1e-6)
