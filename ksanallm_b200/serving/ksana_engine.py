@@ -508,6 +508,13 @@ class KsanaLLMEngine:
                         return Status(), (_FinishedIterator(out) if streamer else out)
                     tokens = list(tokens) + list(pd_first)
                     sp = _dc.replace(sp, max_new_tokens=left)
+                    if mrope is not None:
+                        # multi-axis positions cover the prompt; the handed-over tokens continue from max + 1 on
+                        # every axis, as generated tokens do
+                        mp = torch.as_tensor(mrope, dtype=torch.int32)
+                        mp = mp.reshape(-1, len(tokens) - len(pd_first))
+                        tail = (int(mp.max()) + 1 + torch.arange(len(pd_first), dtype=torch.int32)).expand(mp.shape[0], -1)
+                        mrope = torch.cat((mp, tail), dim=1)
             elif pd_rid and self.connector.role == "prefill":
                 import dataclasses as _dc
                 sp = _dc.replace(sp, max_new_tokens=1)
