@@ -138,3 +138,48 @@ def test_openai_chat_route_hands_image_parts_to_the_plugin(tmp_path):
         assert r.json()["usage"]["completion_tokens"] == 4
     finally:
         server.model.shutdown()
+
+
+def test_image_request_across_a_prefill_decode_hand_over(tmp_path):
+    """Prefill and decode instances both run the plugin on the forwarded request; the decode side continues from the
+    handed-over first token with positions extended past the prompt's three-axis layout, and answers like a single
+    instance."""
+    from PIL import Image
+    tmp = str(tmp_path)
+    _tiny_model(tmp)
+    os.environ["KSANA_SKIP_WARMUP"] = "1"
+    img = Image.fromarray((torch.rand(56, 84, 3, generator=torch.Generator().manual_seed(4)) * 255).byte().numpy())
+
+    def make(role, **extra):
+        serving = parse_serving_config({"setting": {"batch_scheduler": {
+            "max_batch_size": 2, "max_step_tokens": 128, "max_token_len": 256, "enable_auto_prefix_cache": True},
+            "block_manager": {"block_token_num": 16}}})
+        cs = serving.setting.connector
+        cs.group_role, cs.connector_waiting_sec = role, 30
+        cs.extra.update(extra)
+        e = KsanaLLMEngine(EngineArgs(config_file="", model_dir=tmp, device="cpu", serving=serving))
+        e.initialize()
+        return e
+
+    body = {"input_tokens": [5, 9, VSTART, IMG, VEND, 33, 4, 8], "stream": False,
+            "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": _png_url(img)}}]}],
+            "sampling_config": {"max_new_tokens": 6, "topk": 1, "ignore_eos": True}}
+    single = make("none")
+    decode = make("decode")
+    prefill = make("prefill", peer_transfer_addr="%s:%d" % decode.connector.transfer_addr)
+    try:
+        st, want = asyncio.run(single.generate(json.loads(json.dumps(body)), streamer=False))
+        assert st.OK()
+        ctx = {"kv-comm-request-id": "img-1"}
+
+        async def both():
+            d = asyncio.create_task(decode.generate(json.loads(json.dumps(body)), streamer=False, req_ctx=ctx))
+            p = asyncio.create_task(prefill.generate(json.loads(json.dumps(body)), streamer=False, req_ctx=ctx))
+            return await asyncio.gather(p, d)
+
+        (pst, pout), (dst, dout) = asyncio.run(both())
+        assert pst.OK() and dst.OK()
+        assert dout.output_tokens == want.output_tokens and dout.input_tokens == want.input_tokens
+    finally:
+        for e in (single, decode, prefill):
+            e.shutdown()
