@@ -120,6 +120,7 @@ class LLMEngine:
         max_blocks_per_seq = (bs_cfg.max_token_len + self.block_size - 1) // self.block_size + 1
         self.runner = ModelRunner(model, num_blocks, self.block_size, num_host_blocks, bs_cfg.max_step_tokens,
                                   bs_cfg.max_batch_size, max_blocks_per_seq, kv_dtype, seed)
+        self.runner.sampler.eos_token_ids = list(model.cfg.eos_token_ids)
         self.is_driver = self.tp.rank == 0  # with pipeline stages: re-set by attach_pipeline (global rank 0 drives)
         # drafts per step from the first next-n module (applied repeatedly for more than one; with tensor-parallel
         # peers one draft, since the further passes are not part of the followers' step protocol)
@@ -470,6 +471,7 @@ class LLMEngine:
         greedy = p.do_sample is False or p.topk == 1
         return (not greedy or p.logprobs > 0 or p.repetition_penalty != 1.0 or p.no_repeat_ngram_size > 0 or
                 p.encoder_no_repeat_ngram_size > 0 or p.decoder_no_repeat_ngram_size > 0 or p.num_beams > 1 or
+                p.presence_penalty != 0.0 or p.frequency_penalty != 0.0 or bool(p.logit_bias) or p.min_tokens > 0 or
                 bool(p.stop_strings) or req.grammar is not None or req.probe is not None or req.refit is not None)
 
     def _drain_inflight(self) -> int:

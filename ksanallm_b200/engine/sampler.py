@@ -54,6 +54,7 @@ class Sampler:
         self.device = torch.device(device)
         self.gen = torch.Generator(device=self.device)
         self.gen.manual_seed(seed)
+        self.eos_token_ids: List[int] = []  # set by the engine (model EOS ids, for min_tokens)
 
     @staticmethod
     def all_greedy(rows: Sequence[SampleRow]) -> bool:
@@ -81,9 +82,37 @@ class Sampler:
             sub = x.index_select(0, sel)
             sub = torch.where(seen, torch.where(sub > 0, sub / pen, sub * pen), sub)
             x = x.index_copy(0, sel, sub)
+        add_r, add_t, add_v = [], [], []
+        for i, r in enumerate(rows):
+            p = r.params
+            if p.presence_penalty or p.frequency_penalty:
+                counts: Dict[int, int] = {}
+                for t in r.output_tokens:
+                    counts[int(t)] = counts.get(int(t), 0) + 1
+                for t, c in counts.items():
+                    if 0 <= t < V:
+                        add_r.append(i)
+                        add_t.append(t)
+                        add_v.append(-(p.presence_penalty + p.frequency_penalty * c))
+            if p.logit_bias:
+                for t, b in p.logit_bias.items():
+                    if 0 <= int(t) < V:
+                        add_r.append(i)
+                        add_t.append(int(t))
+                        add_v.append(float(b))
+        if add_r:
+            if x.data_ptr() == logits.data_ptr():
+                x = x.clone()
+            x.index_put_((torch.tensor(add_r, device=self.device), torch.tensor(add_t, device=self.device)),
+                         torch.tensor(add_v, dtype=torch.float32, device=self.device), accumulate=True)
         ban_r, ban_t = [], []
         for i, r in enumerate(rows):
             p = r.params
+            if p.min_tokens > len(r.output_tokens):
+                for t in list(p.stop_token_ids) + ([] if p.ignore_eos else list(self.eos_token_ids)):
+                    if 0 <= int(t) < V:
+                        ban_r.append(i)
+                        ban_t.append(int(t))
             hist = list(r.prompt_tokens) + list(r.output_tokens)
             for n, src in ((p.no_repeat_ngram_size, hist), (p.encoder_no_repeat_ngram_size, None),
                            (p.decoder_no_repeat_ngram_size, list(r.output_tokens))):

@@ -34,6 +34,12 @@ class SamplingParams:
     structured_output_regex: Optional[str] = None
     enable_thinking: Optional[bool] = None
     seed: Optional[int] = None
+    # OpenAI-style controls (the reference's request converter forwards them: openaiapi/request_converter.py:175-211,
+    # 394): additive penalties on tokens already generated, per-token bias, and a floor on the output length
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    logit_bias: Optional[dict] = None   # {token id (int or str): bias added to that logit}
+    min_tokens: int = 0                 # EOS / stop tokens are not allowed before this many output tokens
 
     def verify(self) -> None:
         if not (1 <= self.topk <= 1024):
@@ -52,6 +58,10 @@ class SamplingParams:
             raise ValueError("num_return_sequences must be <= num_beams")
         if self.logprobs < 0 or self.logprobs > 64:
             raise ValueError("logprobs must be in [0, 64]")
+        if not (-2.0 <= self.presence_penalty <= 2.0) or not (-2.0 <= self.frequency_penalty <= 2.0):
+            raise ValueError("presence_penalty and frequency_penalty must be in [-2, 2]")
+        if self.min_tokens < 0 or self.min_tokens > self.max_new_tokens:
+            raise ValueError("min_tokens must be in [0, max_new_tokens]")
 
     @property
     def use_greedy(self) -> bool:
@@ -64,6 +74,8 @@ class SamplingParams:
     @property
     def needs_logits_processing(self) -> bool:
         return (self.repetition_penalty != 1.0 or self.no_repeat_ngram_size > 0 or
+                self.presence_penalty != 0.0 or self.frequency_penalty != 0.0 or bool(self.logit_bias) or
+                self.min_tokens > 0 or
                 self.encoder_no_repeat_ngram_size > 0 or self.decoder_no_repeat_ngram_size > 0 or
                 self.enable_structured_output or self.json_schema is not None or
                 self.structured_output_regex is not None)

@@ -67,6 +67,12 @@ class OpenAIServing:
             sc["topk"], sc["do_sample"] = 1, False  # the engine's default is greedy
         if r.repetition_penalty:
             sc["repetition_penalty"] = r.repetition_penalty
+        for name in ("presence_penalty", "frequency_penalty", "min_tokens"):
+            v = getattr(r, name, None)
+            if v:
+                sc[name] = v
+        if getattr(r, "logit_bias", None):
+            sc["logit_bias"] = {int(k): float(v) for k, v in r.logit_bias.items()}
         if r.seed is not None:
             sc["seed"] = r.seed
         if r.use_beam_search:

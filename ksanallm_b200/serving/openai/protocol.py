@@ -81,6 +81,7 @@ class ChatCompletionRequest(OpenAIBase):
     max_completion_tokens: Optional[int] = None
     n: Optional[int] = 1
     presence_penalty: Optional[float] = 0.0
+    min_tokens: Optional[int] = 0
     response_format: Optional[ResponseFormat] = None
     seed: Optional[int] = None
     stop: Optional[Union[str, List[str]]] = None
@@ -118,6 +119,7 @@ class CompletionRequest(OpenAIBase):
     max_tokens: Optional[int] = 16
     n: Optional[int] = 1
     presence_penalty: Optional[float] = 0.0
+    min_tokens: Optional[int] = 0
     seed: Optional[int] = None
     stop: Optional[Union[str, List[str]]] = None
     stream: Optional[bool] = False

@@ -80,3 +80,22 @@ def test_logprobs_report_the_chosen_token_and_the_top_n():
     lp = torch.log_softmax(logits[0], -1)
     assert out.tokens == [0] and abs(out.chosen_logprob[0] - lp[0].item()) < 1e-5
     assert [t for t, _ in out.logprobs[0]] == [0, 1] and abs(out.logprobs[0][1][1] - lp[1].item()) < 1e-5
+
+
+def test_openai_style_penalties_bias_and_min_tokens():
+    s = Sampler(V, torch.device("cpu"))
+    s.eos_token_ids = [2]
+    logits = torch.zeros(1, V)
+    logits[0, 7], logits[0, 8], logits[0, 2] = 3.0, 2.5, 9.0
+    # presence + frequency: token 7 was generated twice -> 3 - (0.5 + 2 * 0.4) = 1.7 < 2.5
+    x = s.process_logits(logits, [_row(prompt=[7], out=[7, 7, 9], topk=1, presence_penalty=0.5, frequency_penalty=0.4,
+                                       ignore_eos=True)])
+    assert abs(x[0, 7].item() - 1.7) < 1e-6 and abs(x[0, 9].item() + 0.9) < 1e-6 and x[0, 8].item() == 2.5
+    # logit_bias accepts string keys as the OpenAI API sends them
+    x = s.process_logits(logits, [_row(prompt=[1], topk=1, logit_bias={"8": 5.0, 7: -100.0}, ignore_eos=True)])
+    assert x[0, 8].item() == 7.5 and x[0, 7].item() == -97.0
+    # min_tokens: EOS and stop ids are out of reach until enough tokens exist
+    out = s.sample(logits.clone(), [_row(prompt=[1], out=[4], topk=1, min_tokens=3, stop_token_ids=[7])])
+    assert out.tokens == [8]
+    out = s.sample(logits.clone(), [_row(prompt=[1], out=[4, 5, 6], topk=1, min_tokens=3, stop_token_ids=[7])])
+    assert out.tokens == [2]

@@ -149,3 +149,14 @@ def test_structured_output_json_schema_and_regex(client):
     assert r.status_code == 200, r.text
     obj = json.loads(r.json()["choices"][0]["message"]["content"])
     assert set(obj) == {"a", "ok"}
+
+
+def test_openai_logit_bias_and_penalties_reach_the_sampler(client):
+    r = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 6, "temperature": 0, "ignore_eos": True,
+                                             "logit_bias": {"100": 50}})
+    assert r.json()["choices"][0]["text"] == "aaaaaa"  # id 100 is the byte 'a' of the stand-in tokenizer
+    r = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 6, "temperature": 0, "ignore_eos": True,
+                                             "logit_bias": {"100": 50, "101": 49.5}, "frequency_penalty": 1.0})
+    text = r.json()["choices"][0]["text"]
+    assert set(text) == {"a", "b"} and text.startswith("ab")  # every use of a token costs it one logit
+    assert client.post("/v1/completions", json={"prompt": "x", "max_tokens": 4, "presence_penalty": 3.0}).status_code != 200
