@@ -307,11 +307,14 @@ class MoEFFN:
         """Per-rank partial sum of the block output (needs a cross-rank sum when size > 1)."""
         c = self.cfg
         ep = self.tp.ep
-        if self.s_gate_up is not None or self.q4 is not None:
+        quantised = self.s_gate_up is not None or self.q4 is not None
+        if quantised:
             if self.tp.ep_dp and self.e_local < c.num_experts:
-                raise NotImplementedError("attention data parallelism exchanges tokens between the ranks' experts "
-                                          "in bf16; quantised experts need tensor / expert parallelism instead")
-            ep = None  # the dispatch / combine kernels and the gathered exchange take bf16 expert weights
+                if not getattr(ep, "custom_experts", False):
+                    raise NotImplementedError("the peer-memory expert exchange runs bf16 experts only; quantised "
+                                              "experts under attention DP use the collective exchange")
+            else:
+                ep = None  # (the dispatch / combine kernels of the TP + EP path take bf16 expert weights)
         if ep is not None and self.tp.ep_dp and self.e_local < c.num_experts:
             return self._dp_exchange(h, ep)
         if (ep is not None and h.is_cuda and h.dtype == torch.bfloat16 and self.e_local < c.num_experts and
@@ -399,6 +402,9 @@ class MoEFFN:
         ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
                                  c.topk_group, c.routed_scaling_factor, self.bias)
         ids = self._place(ids)
+        kw = {}
+        if self.s_gate_up is not None or self.q4 is not None:
+            kw["experts_fn"] = self._fp8_experts  # quantised local experts over the gathered rows
         s = None
         if self.shared is not None and h.shape[0]:
             s = self.shared.down(self.shared.core(h), add_bias=self.tp.rank == 0)
@@ -409,9 +415,9 @@ class MoEFFN:
             # sends them through the exchange and the others join it empty-handed; the block's output is a partial
             # sum over the group (the routed part counted once, the sliced shared expert on every rank)
             if self.tp.rank != 0:
-                ep.moe(h[:0], ids[:0], wts[:0], self.w_gate_up, self.w_down, ep.step_stride)
+                ep.moe(h[:0], ids[:0], wts[:0], self.w_gate_up, self.w_down, ep.step_stride, **kw)
                 return s if s is not None else torch.zeros_like(h)
-        return ep.moe(h, ids, wts, self.w_gate_up, self.w_down, ep.step_stride, add=s)
+        return ep.moe(h, ids, wts, self.w_gate_up, self.w_down, ep.step_stride, add=s, **kw)
 
     def _partial_dispatch(self, h: torch.Tensor, ep) -> torch.Tensor:
         """Expert-parallel path: this rank routes only its own slice of the tokens, sends each row to the ranks

@@ -116,7 +116,11 @@ class GatherEPExchange:
         self.e_local = num_experts // size
         self.step_stride = 0
 
-    def moe(self, x, ids, weights, w_gate_up, w_down, t_stride, add=None):
+    custom_experts = True  # moe() accepts experts_fn (quantised expert weights)
+
+    def moe(self, x, ids, weights, w_gate_up, w_down, t_stride, add=None, experts_fn=None):
+        """``experts_fn(x_all, ids_all, weights_all) -> y_all``: the rank's local experts over the gathered tokens,
+        for expert weights that are not plain bf16 / fp32 tensors (fp8 block-scaled, 4-bit)."""
         T, H = x.shape
         k = self.top_k
         xp = x.new_zeros(t_stride, H)
@@ -130,7 +134,10 @@ class GatherEPExchange:
         dist.all_gather(xg, xp, group=self.group)
         dist.all_gather(ig, ip, group=self.group)
         dist.all_gather(wg, wp, group=self.group)
-        y = ops.moe_experts(torch.cat(xg), torch.cat(ig), torch.cat(wg), w_gate_up, w_down, self.rank * self.e_local)
+        if experts_fn is not None:
+            y = experts_fn(torch.cat(xg), torch.cat(ig), torch.cat(wg))
+        else:
+            y = ops.moe_experts(torch.cat(xg), torch.cat(ig), torch.cat(wg), w_gate_up, w_down, self.rank * self.e_local)
         y = y.float()
         dist.all_reduce(y, group=self.group)
         out = y[self.rank * t_stride:self.rank * t_stride + T].to(x.dtype)

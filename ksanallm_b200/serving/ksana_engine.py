@@ -281,7 +281,9 @@ class KsanaLLMEngine:
             if cfg.is_moe:
                 ep_rank, ep_size = dp_world.rank, dp_world.size
                 tp.ep_rank, tp.ep_size = ep_rank, ep_size
-                if device.type == "cuda" and 2 <= dp_world.size <= 8 and cfg.num_experts % dp_world.size == 0:
+                plain_experts = cfg.quant.method in ("none", "", None) and not quantize
+                if device.type == "cuda" and 2 <= dp_world.size <= 8 and cfg.num_experts % dp_world.size == 0 \
+                        and plain_experts:  # (quantised experts go through the collective exchange)
                     from ..parallel.ep import EPExchange
                     tp.ep = EPExchange(dp_world.group, dp_world.rank, dp_world.size, device, cfg.hidden_size,
                                        cfg.num_experts_per_tok, cfg.num_experts, bs.max_step_tokens)

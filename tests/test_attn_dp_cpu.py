@@ -247,3 +247,55 @@ def test_mtp_drafts_under_attention_dp_keep_the_ranks_in_step():
         assert p.exitcode == 0
     assert got[0][0] == want[0] and got[1][0] == want[1]
     assert got[0][1] == got[1][1] and got[0][2] > 0
+
+
+def _fp8_dp_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      EPLB_WEIGHT="")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = _fp8_cfg()
+    w = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32, quantize="fp8_block", ep_rank=rank, ep_size=world)
+    assert w["model.layers.0.mlp.experts.down_proj.weight"].dtype == torch.float8_e4m3fn
+    tp = TPGroup()
+    tp.ep_rank, tp.ep_size = rank, world
+    tp.ep = GatherEPExchange(dist.group.WORLD, rank, world, cfg.num_experts_per_tok, cfg.num_experts)
+    eng = LLMEngine(TransformerModel(cfg, w, tp), _serving(), tp, num_blocks=64, num_host_blocks=0)
+    eng.attach_dp(DPCoordinator(dist.group.WORLD))
+    reqs = [eng.add_request(p, SamplingParams(topk=1, max_new_tokens=NEW[rank], ignore_eos=True)) for p in PROMPTS[rank]]
+    eng.run_dp(max_steps=200)
+    out.put((rank, [r.output_token_ids[0] for r in reqs]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _fp8_cfg():
+    return model_config_from_dict(dict(model_type="mixtral", hidden_size=128, num_hidden_layers=2,
+                                       num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                                       num_local_experts=4, num_experts_per_tok=2, vocab_size=300,
+                                       torch_dtype="float32", eos_token_id=2))
+
+
+def test_fp8_experts_under_attention_dp_match_single_process():
+    """Block-scaled fp8 experts sharded over two DP ranks: the gathered exchange runs each rank's experts through
+    the fp8 path; tokens equal a single process holding all (equally quantised) experts."""
+    cfg = _fp8_cfg()
+    w = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32, quantize="fp8_block")
+    want = {}
+    for r in (0, 1):
+        eng = LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=64, num_host_blocks=0)
+        want[r] = [q.output_token_ids[0] for q in
+                   eng.generate(PROMPTS[r], SamplingParams(topk=1, max_new_tokens=NEW[r], ignore_eos=True))]
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_fp8_dp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got[0] == want[0] and got[1] == want[1]
