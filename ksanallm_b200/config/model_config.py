@@ -380,7 +380,21 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
 def load_model_config(model_dir: str) -> ModelConfig:
     path = os.path.join(model_dir, "config.json")
     with open(path, "r", encoding="utf-8") as f:
-        return model_config_from_dict(json.load(f))
+        cfg = model_config_from_dict(json.load(f))
+    # generation_config.json may name further end-of-sequence ids (Llama 3: <|eot_id|> next to <|end_of_text|>);
+    # the reference adds them to every request's stop ids (python/ksana_llm/processor_op_base.py:74-90)
+    gen = os.path.join(model_dir, "generation_config.json")
+    if os.path.isfile(gen):
+        try:
+            with open(gen, "r", encoding="utf-8") as f:
+                eos = json.load(f).get("eos_token_id")
+        except (OSError, ValueError):
+            eos = None
+        extra = eos if isinstance(eos, (list, tuple)) else ([eos] if eos is not None else [])
+        for t in extra:
+            if int(t) not in cfg.eos_token_ids:
+                cfg.eos_token_ids.append(int(t))
+    return cfg
 
 
 # ---- named synthetic configurations used by benchmarks and tests ---------------------------------

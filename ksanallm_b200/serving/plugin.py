@@ -72,10 +72,33 @@ class PluginHost:
             fn(ksana_python_input=None, ksana_python_output=output, request_dict=request_dict)
 
 
+BUNDLED = {"qwen2_vl": "qwen2_vl", "qwen2_5_vl": "qwen2_vl", "internvl": "internvl", "internvl_chat": "internvl"}
+
+
+def search_plugin_path(model_dir: str, plugin_cfg: Dict[str, Any]) -> Optional[str]:
+    """An explicit ``plugin_path``, else ``ksana_plugin.py`` in the model directory, else the bundled plugin named
+    by ``model_spec.plugin_model.plugin_name`` (reference: KsanaPlugin.search_plugin_path, ksana_plugin.py)."""
+    cfg = plugin_cfg or {}
+    for cand in (cfg.get("plugin_path"), os.path.join(model_dir or "", "ksana_plugin.py")):
+        if cand and os.path.isfile(cand):
+            return cand
+    name = BUNDLED.get(str(cfg.get("plugin_name", "") or "").lower())
+    if name:
+        return os.path.join(os.path.dirname(os.path.abspath(__file__)), "plugins", name + ".py")
+    return None
+
+
 def load_plugin(model_dir: str, plugin_cfg: Dict[str, Any], engine) -> Optional[PluginHost]:
-    path = (plugin_cfg or {}).get("plugin_path") or os.path.join(model_dir or "", "ksana_plugin.py")
-    if not path or not os.path.isfile(path):
+    path = search_plugin_path(model_dir, plugin_cfg)
+    if not path:
         return None
+    if os.path.dirname(path) == os.path.join(os.path.dirname(os.path.abspath(__file__)), "plugins"):
+        from importlib import import_module
+        mod = import_module(f"{__package__}.plugins.{os.path.basename(path)[:-3]}")
+        impl = mod.KsanaPlugin()
+        impl.init_plugin(python_plugin_path=path, model_path=model_dir, preprocess=True, postprocess=True,
+                         **{k: v for k, v in (plugin_cfg or {}).items() if k not in ("plugin_path", "plugin_name")})
+        return PluginHost(impl, engine)
     spec = importlib.util.spec_from_file_location("ksana_plugin", path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)

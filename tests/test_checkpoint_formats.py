@@ -113,3 +113,24 @@ def test_gguf_llama_checkpoint_with_converter_row_order(tmp_path):
         "general.architecture": "llama", "llama.block_count": cfg.num_layers,
         "llama.attention.head_count": cfg.num_heads, "llama.attention.head_count_kv": cfg.num_kv_heads})
     assert torch.allclose(_logits(d), want, atol=1e-6)
+
+
+def test_generation_config_adds_end_of_sequence_ids(tmp_path):
+    d = _dir(tmp_path, "gen", dict(CONFIG, eos_token_id=2))
+    with open(os.path.join(d, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": [2, 7]}, f)
+    assert load_model_config(d).eos_token_ids == [2, 7]
+
+
+def test_reference_package_names_and_bundled_plugin_lookup(tmp_path):
+    import ksana_llm
+    from ksanallm_b200.serving.plugin import search_plugin_path
+    assert ksana_llm.KsanaLLMEngine is not None and ksana_llm.PluginConfig(plugin_name="qwen2_vl").plugin_name == "qwen2_vl"
+    tok = ksana_llm.TokenizerProcessorOpBase(str(tmp_path), None, None)
+    assert tok.decode(tok.encode("hi", add_special_tokens=False)) == "hi"
+    assert search_plugin_path(str(tmp_path), {"plugin_name": "qwen2_vl"}).endswith("plugins/qwen2_vl.py")
+    assert search_plugin_path(str(tmp_path), {"plugin_name": "internvl_chat"}).endswith("plugins/internvl.py")
+    assert search_plugin_path(str(tmp_path), {}) is None
+    own = tmp_path / "ksana_plugin.py"
+    own.write_text("class KsanaPlugin:\n    pass\n")
+    assert search_plugin_path(str(tmp_path), {"plugin_name": "qwen2_vl"}) == str(own)
