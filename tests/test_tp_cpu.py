@@ -138,3 +138,56 @@ def test_tp2_multimodal_inputs_reach_the_follower():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got == want
+
+
+MIXED = [dict(num_beams=3, num_return_sequences=2, max_new_tokens=5, ignore_eos=True),
+         dict(topk=20, topp=0.9, temperature=0.8, seed=11, logprobs=3, repetition_penalty=1.2, max_new_tokens=6,
+              ignore_eos=True),
+         dict(topk=1, max_new_tokens=6, ignore_eos=True, num_return_sequences=1, frequency_penalty=0.5)]
+
+
+def _mixed_run(eng):
+    reqs = [eng.add_request(p, SamplingParams(**kw)) for p, kw in zip(PROMPTS, MIXED)]
+    eng.run_until_done()
+    beams = [h.tokens for h in sorted(reqs[0].beam.finished, key=lambda h: -h.score)[:2]]
+    lps = [round(e["logprob"], 4) for e in reqs[1].seqs[0].logprobs]
+    return beams, reqs[1].output_token_ids[0], lps, reqs[2].output_token_ids[0]
+
+
+def _mixed_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    tp = TPGroup(rank, world, dist.group.WORLD, torch.device("cpu"))
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=1, tp_rank=rank, tp_size=world, dtype=torch.float32)
+    eng = LLMEngine(TransformerModel(cfg, w, tp), _serving(), tp, num_blocks=64, num_host_blocks=0)
+    eng.attach_control_group(dist.group.WORLD)
+    if rank == 0:
+        out.put(_mixed_run(eng))
+        eng.shutdown_followers()
+    else:
+        eng.follow()
+    dist.destroy_process_group()
+
+
+def test_tp2_beam_search_sampling_logprobs_and_penalties_in_one_batch():
+    """Beam search (copy-on-write forks), seeded top-k / top-p sampling with log-probs and penalties, and a greedy
+    request share steps under tensor parallelism: the follower joins the full-logits path the driver picks."""
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32)
+    want = _mixed_run(LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=64, num_host_blocks=0))
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_mixed_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got[0] == want[0] and got[1] == want[1] and got[3] == want[3]
+    assert all(abs(a - b) < 2e-3 for a, b in zip(got[2], want[2]))
