@@ -122,12 +122,10 @@ class LLMEngine:
                                   bs_cfg.max_batch_size, max_blocks_per_seq, kv_dtype, seed)
         self.runner.sampler.eos_token_ids = list(model.cfg.eos_token_ids)
         self.is_driver = self.tp.rank == 0  # with pipeline stages: re-set by attach_pipeline (global rank 0 drives)
-        # drafts per step from the first next-n module (applied repeatedly for more than one; with tensor-parallel
-        # peers one draft, since the further passes are not part of the followers' step protocol)
+        # drafts per step from the first next-n module (applied repeatedly for more than one; tensor-parallel peers
+        # receive each further pass's rows from the driver)
         self.mtp_steps = bs_cfg.mtp_step_num if (bs_cfg.enable_speculative_decoding or bs_cfg.mtp_step_num) \
             and model.mtp_layers else 0
-        if self.tp.size > 1:
-            self.mtp_steps = min(self.mtp_steps, 1)
         self.trie_drafts = 3 if (bs_cfg.enable_speculative_decoding and not model.mtp_layers) else 0
         sc = _host.SchedulerConfig()
         sc.block_size = self.block_size
@@ -808,14 +806,21 @@ class LLMEngine:
         prev = self._mtp_residual.index_select(0, rows.long())
         tables = [self.cache.block_table(s_) for s_ in seqs]
         n = len(seqs)
+        peers = self._has_followers()
         for k in range(1, self.mtp_steps):
             pos = [p + k - 1 for p in positions]
             if any(p // bs >= len(t) for p, t in zip(pos, tables)):
+                if peers:
+                    dist.broadcast(torch.zeros(2, dtype=torch.int32), src=self._ctl_src, group=self._ctl)
                 return  # no reserved slot (end of the length budget): shorter chains for everybody
             slots = [t[p // bs] * bs + p % bs for p, t in zip(pos, tables)]
             width = max(len(t) for t in tables)
             bt = [list(t) + [0] * (width - len(t)) for t in tables]
             ids = [c[-1] for c in chains]
+            if peers:  # the same pass on the tensor-parallel peers: [rows, table width], then ids | pos | slots | tables
+                dist.broadcast(torch.tensor([n, width], dtype=torch.int32), src=self._ctl_src, group=self._ctl)
+                flat = ids + pos + slots + [b for t in bt for b in t]
+                dist.broadcast(torch.tensor(flat, dtype=torch.int32), src=self._ctl_src, group=self._ctl)
             meta = make_step_input(ids, pos, slots, list(range(n + 1)), [p + 1 for p in pos], bt, logits_idx=list(range(n)),
                                    num_prefill=0, device=self.runner.device)
             emb = ops.embedding(meta.input_ids, model.embed, model.cfg.emb_scale)
@@ -845,7 +850,29 @@ class LLMEngine:
         if int(n[0]):
             dist.broadcast(rows, src=self._ctl_src, group=self._ctl)
         dev = self.runner.device
-        self._mtp_forward(self.model.mtp_layers[0], nxt.to(dev), rows.to(dev), meta, hidden)
+        model, mtp = self.model, self.model.mtp_layers[0]
+        self._mtp_forward(mtp, nxt.to(dev), rows.to(dev), meta, hidden)
+        if self.mtp_steps > 1 and int(n[0]):
+            from .. import ops
+            from .step_input import make_step_input
+            cache = self.runner.kv_caches[len(model.layers)]
+            prev = self._mtp_residual.index_select(0, rows.to(dev).long())
+            for _ in range(1, self.mtp_steps):
+                head = torch.zeros(2, dtype=torch.int32)
+                dist.broadcast(head, src=self._ctl_src, group=self._ctl)
+                m, width = int(head[0]), int(head[1])
+                if m == 0:
+                    break
+                flat = torch.zeros(m * (3 + width), dtype=torch.int32)
+                dist.broadcast(flat, src=self._ctl_src, group=self._ctl)
+                flat = flat.tolist()
+                ids, pos, slots = flat[:m], flat[m:2 * m], flat[2 * m:3 * m]
+                bt = [flat[3 * m + i * width:3 * m + (i + 1) * width] for i in range(m)]
+                cm = make_step_input(ids, pos, slots, list(range(m + 1)), [p + 1 for p in pos], bt,
+                                     logits_idx=list(range(m)), num_prefill=0, device=dev)
+                emb = ops.embedding(cm.input_ids, model.embed, model.cfg.emb_scale)
+                h, prev = mtp.forward(emb, prev, cm, cache, return_residual=True)
+                model.greedy_tokens(h, cm.logits_idx)
 
     def _run_probes(self, plan, meta, hidden) -> None:
         for e in plan.entries:
@@ -1028,6 +1055,9 @@ class LLMEngine:
         self.dp = coordinator
         self.async_mode = False
         self.tp.ep_dp = True
+        # further draft passes run on the ranks that have drafts only, while the experts' exchange needs every rank
+        # in every pass: one draft per step under attention data parallelism
+        self.mtp_steps = min(self.mtp_steps, 1)
         lb = self.serving.setting.batch_scheduler.attention_dp_lb_config
         if lb.enable_balance and self.tp.size == 1:  # (its collective is not part of the followers' step protocol)
             from ..parallel.attn_dp import ADPBalance

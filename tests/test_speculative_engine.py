@@ -1,5 +1,6 @@
 """Speculative decoding through the engine is lossless: with MTP draft layers (DeepSeek next-n) or the n-gram trie the
 greedy outputs equal plain decoding token for token, and drafts are really proposed / verified."""
+import pytest
 import torch
 
 from ksanallm_b200.config.model_config import model_config_from_dict, tiny_llama_config
@@ -118,7 +119,7 @@ def _ds_cfg():
 TP_PROMPTS = [[5, 9, 77, 120, 33, 4, 8], [200, 3, 3, 19, 250, 7, 7, 7, 91, 12, 13], [8, 6, 4]]
 
 
-def _tp_worker(rank, world, port, out):
+def _tp_worker(rank, world, port, out, steps=1):
     import os
     import torch.distributed as dist
     from ksanallm_b200.parallel.comm import TPGroup
@@ -127,7 +128,7 @@ def _tp_worker(rank, world, port, out):
     tp = TPGroup(rank, world, dist.group.WORLD, torch.device("cpu"))
     cfg = _ds_cfg()
     w = load_model_weights(cfg, synthetic_seed=4, tp_rank=rank, tp_size=world, dtype=torch.float32)
-    eng = LLMEngine(TransformerModel(cfg, w, tp), _serving(mtp_step_num=1), tp, num_blocks=64, num_host_blocks=0)
+    eng = LLMEngine(TransformerModel(cfg, w, tp), _serving(mtp_step_num=steps), tp, num_blocks=64, num_host_blocks=0)
     eng.attach_control_group(dist.group.WORLD)
     if rank == 0:
         reqs = eng.generate(TP_PROMPTS, SamplingParams(topk=1, max_new_tokens=8, ignore_eos=True))
@@ -138,7 +139,9 @@ def _tp_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_mtp_under_tensor_parallelism_matches_plain_decoding():
+@pytest.mark.parametrize("steps", [1, 2])
+def test_mtp_under_tensor_parallelism_matches_plain_decoding(steps):
+    """One draft per step, and two (the second pass's rows reach the follower from the driver)."""
     import socket
     import torch.multiprocessing as mp
     cfg = _ds_cfg()
@@ -150,7 +153,7 @@ def test_mtp_under_tensor_parallelism_matches_plain_decoding():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q, steps)) for r in range(2)]
     for p in procs:
         p.start()
     got, proposed = q.get(timeout=180)
