@@ -380,7 +380,17 @@ def model_config_from_dict(c: Dict[str, Any]) -> ModelConfig:
 def load_model_config(model_dir: str) -> ModelConfig:
     path = os.path.join(model_dir, "config.json")
     with open(path, "r", encoding="utf-8") as f:
-        cfg = model_config_from_dict(json.load(f))
+        raw = json.load(f)
+    # ModelOpt / TensorRT-LLM exports describe their quantisation in hf_quant_config.json:
+    # {"quantization": {"quant_algo": "W4A8_AWQ", "group_size": 128, ...}}
+    # (reference: utils/config/quant_config_parser.cpp:52-60)
+    hq = os.path.join(model_dir, "hf_quant_config.json")
+    if "quantization_config" not in raw and os.path.isfile(hq):
+        with open(hq, "r", encoding="utf-8") as f:
+            qd = json.load(f).get("quantization") or {}
+        if qd.get("quant_algo"):
+            raw["quantization_config"] = dict(qd, modules_to_not_convert=qd.get("exclude_modules") or [])
+    cfg = model_config_from_dict(raw)
     # generation_config.json may name further end-of-sequence ids (Llama 3: <|eot_id|> next to <|end_of_text|>);
     # the reference adds them to every request's stop ids (python/ksana_llm/processor_op_base.py:74-90)
     gen = os.path.join(model_dir, "generation_config.json")

@@ -54,6 +54,14 @@ class LinearW:
         self.zeros = weights.get(prefix + ".zeros")
         self.group = 128
         self.sz = None
+        # AWQ smoothing factor of W4A8 checkpoints: y = (x * pre) @ W^T. Folded into a dense weight once; a weight
+        # that kept its 4-bit grid gets its input scaled at run time.
+        self.pre = weights.get(prefix + ".pre_quant_scale")
+        if self.pre is not None and self.qweight is None and self.weight is not None and self.scale_inv is None:
+            self.weight = (self.weight.float() * self.pre.float().unsqueeze(0)).to(self.weight.dtype)
+            weights[prefix + ".weight"] = self.weight
+            weights.pop(prefix + ".pre_quant_scale")
+            self.pre = None
         if self.qweight is not None:
             self.kind = "int4"
             self.group = self.qweight.shape[1] * 8 // self.scales.shape[1]
@@ -81,6 +89,8 @@ class LinearW:
 
     def __call__(self, x: torch.Tensor, add_bias: bool = True) -> torch.Tensor:
         b = self.bias if add_bias else None
+        if self.pre is not None:
+            x = x * self.pre.to(x.dtype)
         if self.kind == "dense":
             return ops.linear(x, self.weight, b)
         if self.kind == "fp8_block":
@@ -289,6 +299,18 @@ class MoEFFN:
             self.w_gate_up, self.w_down = self.q4[0][0], self.q4[1][0]  # (shape carriers: E_local = dim 0)
         # block-scaled fp8 experts (DeepSeek-V3 checkpoints, or quant_method fp8): e4m3 weights + one fp32 scale per
         # 128 x 128 block; they stay in fp8 and every expert's two GEMMs run through the block-scaled fp8 GEMM
+        self.pqs = (w.get(prefix + ".experts.up_gate_proj.pre_quant_scale"),   # [E_local, H] / [E_local, I]: AWQ
+                    w.get(prefix + ".experts.down_proj.pre_quant_scale"))      # smoothing of W4A8 experts' inputs
+        if self.q4 is None and w.get(prefix + ".experts.up_gate_proj.weight_scale_inv") is None:
+            for i, n in enumerate(("up_gate_proj", "down_proj")):  # dense experts: folded into the weights once
+                if self.pqs[i] is not None:
+                    k = prefix + ".experts." + n
+                    w[k + ".weight"] = (w[k + ".weight"].float() * self.pqs[i].float().unsqueeze(1)).to(w[k + ".weight"].dtype)
+                    w.pop(k + ".pre_quant_scale")
+            if any(p_ is not None for p_ in self.pqs):
+                self.w_gate_up, self.w_down = (w[prefix + ".experts.up_gate_proj.weight"],
+                                               w[prefix + ".experts.down_proj.weight"])
+                self.pqs = (None, None)
         self.perm = w.get(prefix + ".expert_perm")  # logical -> physical expert ids (load-balanced placement)
         self._eplb_counts = None
         if os.environ.get("DUMP_EPLB_PATH"):
@@ -370,7 +392,10 @@ class MoEFFN:
             if self.q4 is not None:
                 (q1, s1, z1), (q2, s2, z2) = self.q4
                 g1, g2 = q1.shape[2] * 8 // s1.shape[2], q2.shape[2] * 8 // s2.shape[2]
-                a = ops.silu_and_mul(ops.linear_int4(h[t], q1[e], s1[e], z1[e], None, g1))
+                x = h[t] if self.pqs[0] is None else h[t] * self.pqs[0][e].to(h.dtype)
+                a = ops.silu_and_mul(ops.linear_int4(x, q1[e], s1[e], z1[e], None, g1))
+                if self.pqs[1] is not None:
+                    a = a * self.pqs[1][e].to(a.dtype)
                 y = ops.linear_int4(a, q2[e], s2[e], z2[e], None, g2).float()
             else:
                 a = ops.silu_and_mul(ops.linear_fp8_block(h[t], self.w_gate_up[e], self.s_gate_up[e]))

@@ -276,6 +276,16 @@ def unpack_gptq(qweight, qzeros, scales, g_idx, group: int, v1_zero_offset: bool
     return QuantW(q, sc, z, group), None
 
 
+def unpack_w4a8(packed: torch.Tensor, weight_scale: torch.Tensor) -> "QuantW":
+    """ModelOpt / TensorRT-LLM W4A8_AWQ layout: ``weight`` [N / 2, K] bytes, two signed 4-bit values per byte along
+    N (low nibble = even output row), ``weight_scale`` [N, K / group]; w = nibble * weight_scale. Re-expressed on
+    the unsigned grid with zero point 8. Reference: models/weight_method/w4a8_awq_method.cpp:19-31, 154-196."""
+    b = packed.view(torch.uint8)
+    q = torch.stack((b & 0xF, b >> 4), 1).reshape(2 * b.shape[0], b.shape[1]) ^ 8  # two's complement -> offset 8
+    sc = weight_scale.float()
+    return QuantW(q, sc, torch.full_like(sc, 8.0), b.shape[1] // sc.shape[1])
+
+
 def unpack_awq(qweight, qzeros, scales, group: int):
     """AutoAWQ GEMM layout: qweight [K, N/8], qzeros [K/g, N/8] (both packed along N in the AWQ nibble order),
     scales [K/g, N]."""
@@ -352,6 +362,7 @@ class WeightLoader:
         self._pending: Dict[str, Dict[str, torch.Tensor]] = defaultdict(dict)
         self._experts: Dict[str, Dict[Tuple[int, str], torch.Tensor]] = defaultdict(dict)
         self._qparts: Dict[str, Dict[str, torch.Tensor]] = defaultdict(dict)  # GPTQ / AWQ tensors of one linear
+        self._expert_pqs: Dict[str, Dict[Tuple[int, str], torch.Tensor]] = defaultdict(dict)
 
     # ---- placement --------------------------------------------------------------------------------
     def _own(self, t: torch.Tensor) -> torch.Tensor:
@@ -489,6 +500,11 @@ class WeightLoader:
                     self._experts[key][(e, "down_proj.weight")] = t[le]
             self._maybe_flush_experts(key)
             return
+        if cfg.quant.method in ("w4a8_awq", "modelopt"):
+            wm = re.match(r"(.+)\.(weight|weight_scale|weight_scale_2|input_scale|pre_quant_scale)$", rest)
+            if wm and not isinstance(t, QuantW) and (wm.group(2) != "weight" or t.dtype in (torch.int8, torch.uint8)):
+                self._consume_w4a8(layer, block, wm.group(1), wm.group(2), t)
+                return
         # expert weights: experts.E.{gate,up,down}_proj.(weight|weight_scale_inv)
         em = re.match(r"experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv)$", rest)
         if em:
@@ -527,6 +543,53 @@ class WeightLoader:
             qw, dense = unpack_gptq(parts["qweight"], parts["qzeros"], parts["scales"], parts.get("g_idx"), g, v1)
         else:
             qw = unpack_awq(parts["qweight"], parts["qzeros"], parts["scales"], g)
+        self._emit_quantised(layer, block, stem, qw, dense, g)
+
+    def _consume_w4a8(self, layer: str, block: str, stem: str, part: str, t: torch.Tensor) -> None:
+        """One tensor of a W4A8_AWQ linear. The weights keep their 4-bit grid and run through the 4-bit GEMM with
+        16-bit activations, so the two activation-side scalars (``input_scale``, ``weight_scale_2``: the fp8 range
+        of activations and of the rescaled weights) are not needed; ``pre_quant_scale`` (AWQ's per-input-channel
+        smoothing factor) multiplies the layer's input and is stored beside the weight."""
+        if part in ("weight_scale_2", "input_scale"):
+            return
+        if part == "pre_quant_scale":
+            self._put_pre_quant(layer, block, stem, t.float().flatten())
+            return
+        parts = self._qparts[f"{layer}.{block}.{stem}"]
+        parts[part] = t
+        if {"weight", "weight_scale"} <= set(parts):
+            del self._qparts[f"{layer}.{block}.{stem}"]
+            qw = unpack_w4a8(parts["weight"], parts["weight_scale"])
+            self._emit_quantised(layer, block, stem, qw, None, qw.group)
+
+    def _put_pre_quant(self, layer: str, block: str, stem: str, t: torch.Tensor) -> None:
+        r, n = self.rank, self.size
+        em = re.fullmatch(r"experts\.(\d+)\.(gate_proj|up_proj|down_proj)", stem)
+        if em:
+            e = int(em.group(1))
+            perm = self._perm_of(layer)
+            if perm:
+                e = perm[e]
+            per = max(self.cfg.num_experts // self.ep_size, 1)
+            if self.ep_size > 1 and not (self.ep_rank * per <= e < (self.ep_rank + 1) * per):
+                return
+            if em.group(2) != "up_proj":  # (gate and up read the same input)
+                self._expert_pqs[f"{layer}.{block}"][(e, "down_proj" if em.group(2) == "down_proj" else "up_gate_proj")] = t
+            return
+        if self.cfg.use_mla and block == "self_attn":
+            raise NotImplementedError("pre_quant_scale on multi-head latent attention projections is not supported")
+        pre, _, leaf = stem.rpartition(".")
+        pre = pre + "." if pre else ""
+        if leaf in ("k_proj", "v_proj", "up_proj"):
+            return  # fused with q_proj / gate_proj, which read the same input
+        if leaf in ("o_proj", "down_proj"):  # row-parallel: this rank's slice of the input channels
+            k = t.numel() // n
+            t = t[r * k:(r + 1) * k]
+        leaf = {"q_proj": "query_key_value", "gate_proj": "gate_up_proj"}.get(leaf, leaf)
+        self._put(f"{layer}.{block}.{pre}{leaf}.pre_quant_scale", t)
+
+    def _emit_quantised(self, layer: str, block: str, stem: str, qw, dense, g: int) -> None:
+        cfg = self.cfg
         keep_grid = (not cfg.use_mla and block in ("self_attn", "mlp") and
                      re.fullmatch(r"(shared_expert\.)?(q_proj|k_proj|v_proj|o_proj|gate_proj|up_proj|down_proj)", stem)
                      and (qw is not None) and qw.shape[1] % 128 == 0 and g % 64 == 0)
@@ -622,6 +685,12 @@ class WeightLoader:
                 self._finish_mlp(key, parts)
         for key, ex in list(self._experts.items()):
             self._finish_experts(key, ex)
+        for key, pq in self._expert_pqs.items():  # [E_local, K] per projection, in local expert order
+            for name in ("up_gate_proj", "down_proj"):
+                ids = sorted(e for e, nm in pq if nm == name)
+                if ids:
+                    self._put(f"{key}.experts.{name}.pre_quant_scale", torch.stack([pq[(e, name)] for e in ids]))
+        self._expert_pqs.clear()
         self._pending.clear()
         self._experts.clear()
 

@@ -174,3 +174,69 @@ def test_quantised_experts_keep_their_grid(fmt):
     assert w["model.layers.0.mlp.experts.up_gate_proj.qweight"].shape == (4, 256, 16)
     assert "model.layers.0.mlp.experts.up_gate_proj.weight" not in w
     assert torch.allclose(got, want, atol=2e-4)
+
+
+def _w4a8_tensors(name, w, with_pre=True, seed=0):
+    """One linear in the ModelOpt W4A8_AWQ layout and the dense weight it stands for (smoothing factor folded in)."""
+    g = torch.Generator().manual_seed(seed)
+    N, K = w.shape
+    pre = (torch.rand(K, generator=g) + 0.5) if with_pre else torch.ones(K)
+    target = w / pre                                            # AWQ: W' = W / s, x' = x * s
+    scale = target.view(N, K // GROUP, GROUP).abs().amax(-1).clamp_min(1e-8) / 7.0
+    q = (target.view(N, K // GROUP, GROUP) / scale.unsqueeze(-1)).round().clamp(-8, 7)
+    deq = (q * scale.unsqueeze(-1)).view(N, K) * pre            # what the layer computes on an un-smoothed input
+    qi = q.view(N, K).to(torch.int8)
+    packed = ((qi[0::2] & 0xF) | ((qi[1::2] & 0xF) << 4)).to(torch.uint8)   # two output rows per byte
+    stem = name[:-len(".weight")]
+    out = [(stem + ".input_scale", torch.tensor(0.02)), (stem + ".weight", packed),
+           (stem + ".weight_scale", scale), (stem + ".weight_scale_2", torch.tensor(0.01))]
+    if with_pre:
+        out.insert(1, (stem + ".pre_quant_scale", pre))
+    return out, deq
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_w4a8_awq_checkpoint_runs_on_its_four_bit_grid(moe, tmp_path):
+    """ModelOpt W4A8_AWQ: [N / 2, K] bytes of signed nibbles + group scales + per-channel smoothing factors. The
+    weights stay 4-bit (16-bit activations), q/k/v and gate/up share one smoothing vector, row-parallel inputs are
+    sliced with their weights, and the model equals the one built from the dequantised weights - also split over two
+    tensor-parallel ranks. hf_quant_config.json selects the method."""
+    import json
+    from ksanallm_b200.config.model_config import load_model_config
+    base = dict(BASE, intermediate_size=128)
+    if moe:
+        base = dict(base, model_type="mixtral", num_local_experts=4, num_experts_per_tok=2)
+    (tmp_path / "config.json").write_text(json.dumps(base))
+    (tmp_path / "hf_quant_config.json").write_text(json.dumps(
+        {"producer": {"name": "modelopt"}, "quantization": {"quant_algo": "W4A8_AWQ", "group_size": GROUP,
+                                                           "exclude_modules": ["lm_head"]}}))
+    qcfg = load_model_config(str(tmp_path))
+    assert qcfg.quant.method == "w4a8_awq"
+    cfg = model_config_from_dict(base)
+    dense, quant = [], []
+    shared_pre = {}
+    for i, (name, w) in enumerate(synthetic_checkpoint(cfg, seed=5, dtype=torch.float32)):
+        if not name.endswith("_proj.weight"):
+            dense.append((name, w))
+            quant.append((name, w))
+            continue
+        # projections reading the same input carry the same smoothing vector
+        group_key = name.replace("k_proj", "q_proj").replace("v_proj", "q_proj").replace("up_proj", "gate_proj")
+        seed = shared_pre.setdefault(group_key, i)
+        ts, deq = _w4a8_tensors(name, w, seed=seed)
+        quant += ts
+        dense.append((name, deq))
+    want, _ = _hidden(cfg, dense)
+    got, w = _hidden(qcfg, quant)
+    assert "model.layers.0.self_attn.query_key_value.qweight" in w
+    assert "model.layers.0.self_attn.o_proj.pre_quant_scale" in w
+    if moe:
+        assert w["model.layers.0.mlp.experts.up_gate_proj.qweight"].shape == (4, 256, 16)
+        assert w["model.layers.0.mlp.experts.down_proj.pre_quant_scale"].shape == (4, 128)
+    assert torch.allclose(got, want, atol=3e-4), (got - want).abs().max()
+    for rank in range(2):  # row-parallel inputs: the smoothing vector is sliced with the weight's input channels
+        wq = WeightLoader(qcfg, tp_rank=rank, tp_size=2, dtype=torch.float32).load(quant)
+        wd = WeightLoader(cfg, tp_rank=rank, tp_size=2, dtype=torch.float32).load(dense)
+        p = "model.layers.1.self_attn.o_proj"
+        deq = ref.dequant_int4_group(wq[p + ".qweight"], wq[p + ".scales"].float(), wq[p + ".zeros"].float(), GROUP)
+        assert torch.allclose(deq * wq[p + ".pre_quant_scale"].float(), wd[p + ".weight"], atol=1e-5)
