@@ -13,7 +13,6 @@ targets sm_100a only and needs no configure step.
 """
 from __future__ import annotations
 
-import hashlib
 import os
 import subprocess
 import sys

@@ -60,7 +60,6 @@ class GrammarState:
         return m
 
     def next_bitmask(self, seq_id: int) -> Optional[np.ndarray]:
-        import torch
         import xgrammar as xgr
         m = self._matcher(seq_id)
         if self.thinking.get(seq_id):

@@ -6,7 +6,6 @@ from __future__ import annotations
 
 import importlib.util
 import sys
-from pathlib import Path
 
 from . import _build
 

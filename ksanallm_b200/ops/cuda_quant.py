@@ -1,8 +1,6 @@
 """Quantised linear layers on the GPU: fp8 128x128 block-scaled weights and int4 group-quantised weights."""
 from __future__ import annotations
 
-import torch
-
 from . import reference as ref
 
 

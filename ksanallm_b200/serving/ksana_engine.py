@@ -9,7 +9,6 @@ from __future__ import annotations
 
 import argparse
 import asyncio
-import base64
 import json
 import os
 from dataclasses import dataclass, field
