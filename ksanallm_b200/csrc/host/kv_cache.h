@@ -265,9 +265,15 @@ class KVCacheManager {
       }
     }
     if (best.empty()) return false;
-    for (auto* nd : best) Pin(nd);  // the reservation below must not evict (and hand out) the source blocks
+    // the reservation below must not evict (and hand out) the source blocks; their ancestors are pinned with them,
+    // because an unreferenced node above a referenced one counts as obtainable but can never be evicted
+    std::vector<PrefixNode*> pinned;
+    for (PrefixNode* a = best.front()->parent; a != nullptr && a != &root_; a = a->parent) pinned.push_back(a);
+    std::reverse(pinned.begin(), pinned.end());  // root side first: released in the order a sequence would
+    pinned.insert(pinned.end(), best.begin(), best.end());
+    for (auto* nd : pinned) Pin(nd);
     bool ok = EnsureCapacity(seq, shared + best_len);
-    for (auto* nd : best) Unpin(nd);
+    for (auto* nd : pinned) Unpin(nd);
     if (!ok) return false;
     std::vector<BlockId> table = BlockTable(seq);
     int depth = 0;  // position of the first source block
