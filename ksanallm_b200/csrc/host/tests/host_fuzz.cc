@@ -108,6 +108,22 @@ static void OneRound(uint32_t seed) {
         ++next_id;
       }
     }
+    if (!live.empty() && rnd(0, 50) == 0) {  // stop string found by the detokenizer / beam pruned: finished from outside
+      auto it = live.begin();
+      std::advance(it, rnd(0, static_cast<int>(live.size()) - 1));
+      const Sequence* p = sched.Get(*it);
+      if (p != nullptr && p->state == SEQ_RUNNING && sched.Finish(*it, FINISH_ABORTED)) {
+        sched.Forget(*it);
+        live.erase(it);
+      }
+    }
+    if (!live.empty() && rnd(0, 20) == 0) {  // beam search rewrites the token it just got
+      auto it = live.begin();
+      std::advance(it, rnd(0, static_cast<int>(live.size()) - 1));
+      const Sequence* p = sched.Get(*it);
+      if (p != nullptr && p->state == SEQ_RUNNING && p->num_generated() > 0) sched.ReplaceLastToken(*it, rnd(1, 99));
+    }
+    sched.SetHoldWaiting(rnd(0, 15) == 0);  // the data-parallel balancer holds admissions back for a step
     for (int64_t id : live) {  // drafts from the trie for decoding sequences
       const Sequence* s = sched.Get(id);
       if (cfg.max_draft_tokens && s != nullptr && s->state == SEQ_RUNNING && s->num_generated() > 0 && rnd(0, 1)) {
