@@ -94,3 +94,43 @@ def test_block_checksum_guard_passes_on_a_clean_run_and_catches_a_stray_write():
     with pytest.raises(RuntimeError, match="checksum changed"):
         for _ in range(10):
             eng.step()
+
+
+@pytest.mark.parametrize("seed", list(range(int(__import__("os").environ.get("KSANA_FUZZ_SEEDS", "10")))))
+def test_randomised_configurations_and_arrivals_keep_greedy_outputs(seed):
+    """Random block-pool sizes, pre-emption mode, chunk size, trie speculation, asynchronous scheduling and staggered
+    arrivals: none of them may change what a greedy request generates."""
+    import random
+    rnd = random.Random(seed)
+    cfg = tiny_llama_config()
+    model = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.02, dtype=torch.float32))
+    g = torch.Generator().manual_seed(100 + seed)
+    stem = torch.randint(3, 31000, (rnd.choice([16, 32, 40]),), generator=g).tolist()
+    prompts = [(stem if rnd.random() < 0.7 else []) + torch.randint(3, 31000, (rnd.randint(2, 34),), generator=g).tolist()
+               for _ in range(8)]
+    params = [SamplingParams(topk=1, max_new_tokens=rnd.randint(4, 36), ignore_eos=True) for _ in prompts]
+    roomy = _engine(model, 160, 0, 1, 0)
+    want = [roomy.generate([p], sp)[0].output_token_ids[0] for p, sp in zip(prompts, params)]
+    host_blocks = rnd.choice([0, 24])
+    split = rnd.choice([0, 16, 40])
+    serving = parse_serving_config({"setting": {"batch_scheduler": {
+        "max_batch_size": rnd.choice([3, 6, 8]), "max_step_tokens": 96, "max_token_len": 256,
+        "enable_auto_prefix_cache": rnd.random() < 0.8, "preempt_mode": rnd.choice([0, 1]) if host_blocks else 1,
+        "split_fuse_token_num": split, "enable_speculative_decoding": rnd.random() < 0.5,
+        "enable_async": split == 0 and rnd.random() < 0.6},  # (the two are refused together, as in the reference)
+        "block_manager": {"block_token_num": 16}}})
+    eng = LLMEngine(model, serving, num_blocks=rnd.randint(14, 26), num_host_blocks=host_blocks)
+    reqs = []
+    order = list(range(len(prompts)))
+    rnd.shuffle(order)
+    while order:
+        for _ in range(rnd.randint(1, 3)):
+            if order:
+                i = order.pop()
+                reqs.append((i, eng.add_request(prompts[i], params[i])))
+        for _ in range(rnd.randint(0, 4)):
+            eng.step()
+    eng.run_until_done()
+    for i, r in reqs:
+        assert r.output_token_ids[0] == want[i], (seed, i)
+    assert eng.cache.num_free_blocks + eng.cache.num_cached_blocks == eng.cache.num_device_blocks
