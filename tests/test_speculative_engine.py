@@ -205,3 +205,42 @@ def test_two_draft_steps_are_lossless_and_the_second_draft_follows_the_chain_rul
     req = eng2.add_request(tokens, SamplingParams(topk=1, max_new_tokens=3, ignore_eos=True))
     eng2.run_until_done()
     assert req.output_token_ids[0][0] == t1 and seen[0] == [[d1, d2]]
+
+
+@pytest.mark.parametrize("seed", list(range(int(__import__("os").environ.get("KSANA_FUZZ_SEEDS", "8")))))
+def test_mtp_under_memory_pressure_and_staggered_arrivals_is_lossless(seed):
+    """One or two MTP drafts per step while the block pool is too small for the batch (recompute or swap
+    pre-emption, chunked prefill, look-ahead slots for the second draft), requests arriving between steps: the
+    greedy outputs still equal plain decoding, and every block returns to the pool."""
+    import random
+    rnd = random.Random(seed)
+    cfg = _ds_cfg()
+    w = load_model_weights(cfg, synthetic_seed=4, dtype=torch.float32)
+    g = torch.Generator().manual_seed(50 + seed)
+    stem = torch.randint(3, 290, (rnd.choice([16, 24, 32]),), generator=g).tolist()
+    prompts = [(stem if rnd.random() < 0.6 else []) + torch.randint(3, 290, (rnd.randint(2, 30),), generator=g).tolist()
+               for _ in range(6)]
+    params = [SamplingParams(topk=1, max_new_tokens=rnd.randint(4, 30), ignore_eos=True) for _ in prompts]
+    model = TransformerModel(cfg, w)
+    roomy = LLMEngine(model, _serving(), num_blocks=96, num_host_blocks=0)
+    want = [roomy.generate([p], sp)[0].output_token_ids[0] for p, sp in zip(prompts, params)]
+    host_blocks = rnd.choice([0, 16])
+    eng = LLMEngine(model, _serving(mtp_step_num=rnd.choice([1, 2]), max_batch_size=rnd.choice([3, 6]),
+                                    preempt_mode=rnd.choice([0, 1]) if host_blocks else 1,
+                                    split_fuse_token_num=rnd.choice([0, 16]),
+                                    enable_auto_prefix_cache=rnd.random() < 0.7),
+                    num_blocks=rnd.randint(10, 18), num_host_blocks=host_blocks)
+    reqs, order = [], list(range(len(prompts)))
+    rnd.shuffle(order)
+    while order:
+        for _ in range(rnd.randint(1, 3)):
+            if order:
+                i = order.pop()
+                reqs.append((i, eng.add_request(prompts[i], params[i])))
+        for _ in range(rnd.randint(0, 4)):
+            eng.step()
+    eng.run_until_done()
+    for i, r in reqs:
+        assert r.output_token_ids[0] == want[i], (seed, i)
+    assert eng.sched.stats.draft_proposed > 0
+    assert eng.cache.num_free_blocks + eng.cache.num_cached_blocks == eng.cache.num_device_blocks
