@@ -214,6 +214,7 @@ PYBIND11_MODULE(_ksana_host, m) {
       .def("schedule", &Scheduler::Schedule, py::arg("now_ms") = 0)
       .def("micro_batch_of", &Scheduler::MicroBatchOf)
       .def("set_hold_waiting", &Scheduler::SetHoldWaiting)
+      .def("set_paused", &Scheduler::SetPaused)
       .def(
           "pack",
           [](const Scheduler& s, const StepPlan& plan, py::array_t<int32_t, py::array::c_style> buf, int max_blocks) {

@@ -101,6 +101,9 @@ struct Sequence {
   int finish_reason = FINISH_NONE;
   int preempt_count = 0;
   int mb = -1;  // pipeline micro-batch this sequence belongs to (-1: none), fixed at admission
+  // Held back from every queue's scheduling (it keeps its cache unless pre-empted): a beam that already has this
+  // position's candidates waits here until the other beams of its request have theirs.
+  bool paused = false;
   // in-flight step
   int sched_q_len = 0;
   int sched_drafts = 0;
@@ -227,6 +230,7 @@ class Scheduler {
     auto c = std::make_unique<Sequence>(p);
     c->id = child;
     c->drafts.clear();
+    c->paused = false;
     seqs_[child] = std::move(c);
     auto pos = std::find(running_.begin(), running_.end(), parent);
     running_.insert(pos + 1, child);
@@ -270,6 +274,12 @@ class Scheduler {
   // While set, Schedule() admits nothing from the waiting queue (running and swapped sequences go on). Attention
   // data parallelism uses it to line the ranks' prefills up (parallel/attn_dp.py ADPBalance).
   void SetHoldWaiting(bool hold) { hold_waiting_ = hold; }
+  bool SetPaused(int64_t id, bool paused) {
+    auto it = seqs_.find(id);
+    if (it == seqs_.end()) return false;
+    it->second->paused = paused;
+    return true;
+  }
 
   void SetMicroBatch(int mb, int count = 1) {
     mb_filter_ = mb;
@@ -368,7 +378,7 @@ class Scheduler {
     while (!running_.empty()) {
       int64_t id = running_.front();
       Sequence& s = *seqs_.at(id);
-      if (mb_filter_ >= 0 && s.mb != mb_filter_) {
+      if ((mb_filter_ >= 0 && s.mb != mb_filter_) || s.paused) {
         running_.pop_front();
         keep.push_back(id);
         continue;
@@ -428,9 +438,14 @@ class Scheduler {
     running_.swap(keep);
 
     // ---- 2. swapped queue -------------------------------------------------------------------
+    // (paused sequences move behind the others, in both queues, and end the scan when they are reached)
+    auto not_paused = [&](int64_t q) { return !seqs_.at(q)->paused; };
+    std::stable_partition(swapped_.begin(), swapped_.end(), not_paused);
+    std::stable_partition(waiting_.begin(), waiting_.end(), not_paused);
     while (!swapped_.empty() && batch_budget > 0 && token_budget > 0 && plan.swap_out.empty()) {
       int64_t id = swapped_.front();
       Sequence& s = *seqs_.at(id);
+      if (s.paused) break;
       if (mb_filter_ >= 0 && s.mb != mb_filter_) break;
       int need_now = 1 + std::min<int>(static_cast<int>(s.drafts.size()), cfg_.max_draft_tokens);
       int blocks_after = (s.num_computed + need_now + cfg_.block_size - 1) / cfg_.block_size;
@@ -469,13 +484,15 @@ class Scheduler {
     int admit_left = (mb_filter_ >= 0 && cfg_.pp_wb_strategy == 0)
                          ? std::max<int>(1, (static_cast<int>(waiting_.size()) + mb_count_ - 1) / mb_count_)
                          : (1 << 30);
-    while (!hold_waiting_ && !waiting_.empty() && batch_budget > 0 && token_budget > 0 && swapped_.empty() &&
+    const bool swapped_ahead = !swapped_.empty() && !seqs_.at(swapped_.front())->paused;
+    while (!hold_waiting_ && !waiting_.empty() && batch_budget > 0 && token_budget > 0 && !swapped_ahead &&
            !preempted_now && admit_left > 0) {
+      if (seqs_.at(waiting_.front())->paused) break;
       --admit_left;
       if (mb_filter_ >= 0 && cfg_.pp_wb_strategy > 0) {
         // balanced micro-batches: admit this micro-batch's own waiting sequences, oldest first
         auto mine = std::find_if(waiting_.begin(), waiting_.end(),
-                                 [&](int64_t w) { int m = seqs_.at(w)->mb; return m == mb_filter_ || m < 0; });
+                                 [&](int64_t w) { int m = seqs_.at(w)->mb; return (m == mb_filter_ || m < 0) && !seqs_.at(w)->paused; });
         if (mine == waiting_.end()) break;
         if (mine != waiting_.begin()) {
           int64_t w = *mine;

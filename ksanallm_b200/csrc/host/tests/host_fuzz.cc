@@ -61,7 +61,7 @@ static void OneRound(uint32_t seed) {
     for (auto& t : s) t = rnd(1, 50);
     stems.push_back(s);
   }
-  std::set<int64_t> live;
+  std::set<int64_t> live, paused;
   int64_t next_id = 1, now = 0;
   const int total_requests = rnd(20, 80);
   int issued = 0;
@@ -122,6 +122,15 @@ static void OneRound(uint32_t seed) {
       std::advance(it, rnd(0, static_cast<int>(live.size()) - 1));
       const Sequence* p = sched.Get(*it);
       if (p != nullptr && p->state == SEQ_RUNNING && p->num_generated() > 0) sched.ReplaceLastToken(*it, rnd(1, 99));
+    }
+    if (!live.empty() && rnd(0, 6) == 0) {  // a beam ahead of its siblings is held back for a few steps
+      auto it = live.begin();
+      std::advance(it, rnd(0, static_cast<int>(live.size()) - 1));
+      if (sched.SetPaused(*it, true)) paused.insert(*it);
+    }
+    if (step % 5 == 0) {
+      for (int64_t id : paused) sched.SetPaused(id, false);
+      paused.clear();
     }
     sched.SetHoldWaiting(rnd(0, 15) == 0);  // the data-parallel balancer holds admissions back for a step
     for (int64_t id : live) {  // drafts from the trie for decoding sequences

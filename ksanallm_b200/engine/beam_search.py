@@ -30,6 +30,7 @@ class BeamState:
         self.scores: Dict[int, float] = {}  # seq_id -> cumulative log-prob of live beams
         self.finished: List[Hypothesis] = []
         self.done = False
+        self.pending: Dict[int, Tuple[List[int], List[Tuple[int, float]]]] = {}  # beams waiting for their siblings
 
     def _norm(self, s: float, n: int) -> float:
         return s / (max(n, 1) ** self.lp)
@@ -38,7 +39,20 @@ class BeamState:
         return 2 * self.k
 
     def step(self, engine, req, rows: Dict[int, Tuple[List[int], List[Tuple[int, float]]]], eos_ids) -> None:
-        """rows: seq_id -> (output tokens BEFORE this step's token, top-n (token, logprob) of this step's row)."""
+        """rows: seq_id -> (output tokens BEFORE this step's token, top-n (token, logprob) of this step's row).
+
+        The beams of a request are ranked against each other, so a position is expanded only once EVERY live beam has
+        its candidates: under a batch cap or after a pre-emption some beams run a step later than others. A beam
+        that is ahead is paused in the scheduler (it keeps its cache) until the others have caught up."""
+        self.pending.update(rows)
+        live = set(self.scores) if self.scores else set(self.pending)
+        if not live <= set(self.pending):
+            for sid in rows:
+                engine.sched.set_paused(sid, True)
+            return
+        rows, self.pending = self.pending, {}
+        for sid in rows:
+            engine.sched.set_paused(sid, False)
         cands: List[Tuple[float, int, int, float]] = []  # (new cumulative score, parent seq, token, token logprob)
         for sid, (_prev, top) in rows.items():
             base = self.scores.get(sid, 0.0)

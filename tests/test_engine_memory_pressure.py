@@ -134,3 +134,44 @@ def test_randomised_configurations_and_arrivals_keep_greedy_outputs(seed):
     for i, r in reqs:
         assert r.output_token_ids[0] == want[i], (seed, i)
     assert eng.cache.num_free_blocks + eng.cache.num_cached_blocks == eng.cache.num_device_blocks
+
+
+@pytest.mark.parametrize("seed", list(range(int(__import__("os").environ.get("KSANA_FUZZ_SEEDS", "6")))))
+def test_beam_search_and_seeded_parallel_sampling_survive_preemption(seed):
+    """Beam search (forks + pruning), seeded sampling with several returned sequences and greedy requests mixed in one
+    engine whose block pool forces pre-emption: results equal those of an engine with plenty of blocks."""
+    import random
+    rnd = random.Random(seed)
+    cfg = tiny_llama_config()
+    model = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.02, dtype=torch.float32))
+    g = torch.Generator().manual_seed(300 + seed)
+    prompts = [torch.randint(3, 31000, (rnd.randint(3, 40),), generator=g).tolist() for _ in range(6)]
+
+    def params(i):
+        kind = i % 3
+        n = 6 + (i * 5) % 17
+        if kind == 0:
+            return SamplingParams(num_beams=2 + i % 2, num_return_sequences=2, max_new_tokens=n, ignore_eos=True)
+        if kind == 1:
+            return SamplingParams(topk=30, topp=0.9, temperature=0.9, seed=17 + i, num_return_sequences=2,
+                                  max_new_tokens=n, ignore_eos=True)
+        return SamplingParams(topk=1, max_new_tokens=n, ignore_eos=True)
+
+    def outputs(eng):
+        reqs = [eng.add_request(p, params(i)) for i, p in enumerate(prompts)]
+        eng.run_until_done()
+        res = []
+        for r in reqs:
+            if r.beam is not None:
+                res.append([h.tokens for h in sorted(r.beam.finished, key=lambda h: -h.score)[:2]])
+            else:
+                res.append(r.output_token_ids)
+        return res
+
+    want = outputs(_engine(model, 200, 0, 1, 0))
+    host_blocks = rnd.choice([0, 24])
+    tight = _engine(model, rnd.randint(16, 24), host_blocks, rnd.choice([0, 1]) if host_blocks else 1,
+                    rnd.choice([0, 24]))
+    got = outputs(tight)
+    assert got == want
+    assert tight.cache.num_free_blocks + tight.cache.num_cached_blocks == tight.cache.num_device_blocks
