@@ -191,3 +191,88 @@ def test_tp2_beam_search_sampling_logprobs_and_penalties_in_one_batch():
         assert p.exitcode == 0
     assert got[0] == want[0] and got[1] == want[1] and got[3] == want[3]
     assert all(abs(a - b) < 2e-3 for a, b in zip(got[2], want[2]))
+
+
+def _pressure_case(seed):
+    import random
+    rnd = random.Random(seed)
+    g = torch.Generator().manual_seed(900 + seed)
+    stem = torch.randint(3, 490, (32,), generator=g).tolist()
+    prompts = [(stem if rnd.random() < 0.6 else []) + torch.randint(3, 490, (rnd.randint(2, 30),), generator=g).tolist()
+               for _ in range(7)]
+    kw = []
+    for i in range(len(prompts)):
+        n = rnd.randint(4, 24)
+        kw.append([dict(topk=1, max_new_tokens=n, ignore_eos=True),
+                   dict(num_beams=2, num_return_sequences=2, max_new_tokens=n, ignore_eos=True),
+                   dict(topk=20, topp=0.9, seed=5 + i, max_new_tokens=n, ignore_eos=True)][i % 3])
+    host = rnd.choice([0, 24])
+    bs = {"max_batch_size": rnd.choice([4, 6]), "max_step_tokens": 96, "max_token_len": 200,
+          "enable_auto_prefix_cache": True, "preempt_mode": rnd.choice([0, 1]) if host else 1,
+          "split_fuse_token_num": rnd.choice([0, 24])}
+    return prompts, kw, bs, rnd.randint(14, 22), host, rnd
+
+
+def _pressure_run(eng, prompts, kw, rnd=None):
+    reqs, order = {}, list(range(len(prompts)))
+    while order:
+        for _ in range(rnd.randint(1, 3) if rnd else len(order)):
+            if order:
+                i = order.pop(0)
+                reqs[i] = eng.add_request(prompts[i], SamplingParams(**kw[i]))
+        for _ in range(rnd.randint(0, 3) if rnd else 0):
+            eng.step()
+    eng.run_until_done()
+    out = []
+    for i in range(len(prompts)):
+        r = reqs[i]
+        out.append([h.tokens for h in sorted(r.beam.finished, key=lambda h: -h.score)[:2]] if r.beam is not None
+                   else r.output_token_ids)
+    return out
+
+
+def _pressure_worker(rank, world, port, out, seed):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    tp = TPGroup(rank, world, dist.group.WORLD, torch.device("cpu"))
+    cfg = _cfg()
+    prompts, kw, bs, blocks, host, rnd = _pressure_case(seed)
+    serving = parse_serving_config({"setting": {"batch_scheduler": bs, "block_manager": {"block_token_num": 16}}})
+    w = load_model_weights(cfg, synthetic_seed=1, tp_rank=rank, tp_size=world, dtype=torch.float32)
+    eng = LLMEngine(TransformerModel(cfg, w, tp), serving, tp, num_blocks=blocks, num_host_blocks=host)
+    eng.attach_control_group(dist.group.WORLD)
+    if rank == 0:
+        res = _pressure_run(eng, prompts, kw, rnd)
+        st = eng.sched.stats
+        eng.shutdown_followers()
+        out.put((res, st.preempt_swap + st.preempt_recompute))
+    else:
+        eng.follow()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_tp2_under_memory_pressure_matches_a_roomy_single_rank(seed):
+    """Followers replay the driver's swap-out / swap-in / copy-on-write block operations: with a block pool that
+    forces pre-emption, chunked prefill, beams and seeded sampling arriving between steps, two ranks generate what
+    one rank with plenty of blocks generates."""
+    cfg = _cfg()
+    prompts, kw, bs, _, _, _ = _pressure_case(seed)
+    roomy = parse_serving_config({"setting": {"batch_scheduler": dict(bs, split_fuse_token_num=0, preempt_mode=1),
+                                              "block_manager": {"block_token_num": 16}}})
+    w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32)
+    want = _pressure_run(LLMEngine(TransformerModel(cfg, w), roomy, num_blocks=200, num_host_blocks=0), prompts, kw)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_pressure_worker, args=(r, 2, port, q, seed)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got, preemptions = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == want
