@@ -137,3 +137,93 @@ def test_pp2_seeded_sampling_matches_single_process(micro_batches):
         p.join(timeout=30)
         assert p.exitcode == 0
     assert got == want
+
+
+def _pressure_case(seed):
+    import random
+    rnd = random.Random(seed)
+    g = torch.Generator().manual_seed(1200 + seed)
+    stem = torch.randint(3, 490, (32,), generator=g).tolist()
+    prompts = [(stem if rnd.random() < 0.6 else []) + torch.randint(3, 490, (rnd.randint(2, 30),), generator=g).tolist()
+               for _ in range(8)]
+    kw = []
+    for i in range(len(prompts)):
+        n = rnd.randint(4, 24)
+        kw.append([dict(topk=1, max_new_tokens=n, ignore_eos=True),
+                   dict(topk=20, topp=0.9, seed=5 + i, max_new_tokens=n, ignore_eos=True),
+                   dict(num_beams=2, num_return_sequences=2, max_new_tokens=n, ignore_eos=True)][i % 3])
+    host = rnd.choice([0, 24])
+    bs = {"max_batch_size": rnd.choice([4, 6]), "max_step_tokens": 96, "max_token_len": 200,
+          "enable_auto_prefix_cache": True, "preempt_mode": rnd.choice([0, 1]) if host else 1,
+          "split_fuse_token_num": rnd.choice([0, 24]), "pp_multibatch_wb_strategy": rnd.choice([0, 1, 2, 3, 4])}
+    return prompts, kw, bs, rnd.randint(16, 24), host, rnd.choice([1, 2, 3]), rnd
+
+
+def _pressure_run(eng, prompts, kw, rnd=None):
+    reqs, order = {}, list(range(len(prompts)))
+    while order:
+        for _ in range(rnd.randint(1, 3) if rnd else len(order)):
+            if order:
+                i = order.pop(0)
+                reqs[i] = eng.add_request(prompts[i], SamplingParams(**kw[i]))
+        for _ in range(rnd.randint(0, 3) if rnd else 0):
+            eng.step()
+    eng.run_until_done()
+    out = []
+    for i in range(len(prompts)):
+        r = reqs[i]
+        out.append([h.tokens for h in sorted(r.beam.finished, key=lambda h: -h.score)[:2]] if r.beam is not None
+                   else r.output_token_ids)
+    return out
+
+
+def _pressure_worker(rank, world, port, out, seed):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    topo = StageTopology(world, 1, rank)
+    cfg = _cfg()
+    prompts, kw, bs, blocks, host, mbs, rnd = _pressure_case(seed)
+    serving = parse_serving_config({"setting": {"batch_scheduler": bs, "block_manager": {"block_token_num": 16}}})
+    ranges = split_layers(cfg.num_layers, topo.num_stages)
+    w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32, layer_range=ranges[topo.stage])
+    model = TransformerModel(cfg, w, TPGroup(), layer_range=ranges[topo.stage])
+    if not topo.is_last:
+        model.norm_w = None
+    eng = LLMEngine(model, serving, num_blocks=blocks, num_host_blocks=host)
+    eng.attach_control_group(dist.group.WORLD)
+    eng.attach_pipeline(PipelineStage(model, topo, HiddenChannel(topo, cfg.hidden_size, torch.float32,
+                                                                 torch.device("cpu"))), mbs)
+    if rank == 0:
+        res = _pressure_run(eng, prompts, kw, rnd)
+        eng.shutdown_followers()
+        out.put(res)
+    else:
+        eng.follow()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_pp2_under_memory_pressure_matches_a_roomy_single_process(seed):
+    """Two pipeline stages, one to three micro-batches in flight with a random balancing strategy, a block pool that
+    forces pre-emption, chunked prefill, beams and seeded sampling arriving between steps: same results as one
+    process with plenty of blocks."""
+    cfg = _cfg()
+    prompts, kw, bs, _, _, _, _ = _pressure_case(seed)
+    roomy = parse_serving_config({"setting": {"batch_scheduler": dict(bs, split_fuse_token_num=0, preempt_mode=1),
+                                              "block_manager": {"block_token_num": 16}}})
+    w = load_model_weights(cfg, synthetic_seed=1, dtype=torch.float32)
+    want = _pressure_run(LLMEngine(TransformerModel(cfg, w), roomy, num_blocks=240, num_host_blocks=0), prompts, kw)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_pressure_worker, args=(r, 2, port, q, seed)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == want
