@@ -299,3 +299,77 @@ def test_fp8_experts_under_attention_dp_match_single_process():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got[0] == want[0] and got[1] == want[1]
+
+
+def _dp_pressure_case(seed, rank):
+    import random
+    rnd = random.Random(seed * 10 + rank)
+    g = torch.Generator().manual_seed(40 + seed * 10 + rank)
+    stem = torch.randint(3, 290, (32,), generator=g).tolist()
+    prompts = [(stem if rnd.random() < 0.6 else []) + torch.randint(3, 290, (rnd.randint(2, 30),), generator=g).tolist()
+               for _ in range(rnd.randint(2, 6))]
+    news = [rnd.randint(3, 22) for _ in prompts]
+    host = rnd.choice([0, 16])
+    bs = {"max_batch_size": rnd.choice([3, 6]), "max_step_tokens": 96, "max_token_len": 200,
+          "enable_auto_prefix_cache": True, "preempt_mode": rnd.choice([0, 1]) if host else 1,
+          "split_fuse_token_num": rnd.choice([0, 24])}
+    return prompts, news, bs, rnd.randint(9, 14), host, rnd
+
+
+def _dp_pressure_worker(rank, world, port, out, seed):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = _cfg()
+    prompts, news, bs, blocks, host, rnd = _dp_pressure_case(seed, rank)
+    serving = parse_serving_config({"setting": {"batch_scheduler": bs, "block_manager": {"block_token_num": 16}}})
+    w = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32, ep_rank=rank, ep_size=world)
+    tp = TPGroup()
+    tp.ep_rank, tp.ep_size = rank, world
+    tp.ep = GatherEPExchange(dist.group.WORLD, rank, world, cfg.num_experts_per_tok, cfg.num_experts)
+    eng = LLMEngine(TransformerModel(cfg, w, tp), serving, tp, num_blocks=blocks, num_host_blocks=host)
+    eng.attach_dp(DPCoordinator(dist.group.WORLD))
+    reqs, order = {}, list(range(len(prompts)))
+    for _ in range(8):  # both ranks take the same number of steps; arrivals fall between them
+        for _ in range(rnd.randint(0, 2)):
+            if order:
+                i = order.pop(0)
+                reqs[i] = eng.add_request(prompts[i], SamplingParams(topk=1, max_new_tokens=news[i], ignore_eos=True))
+        eng._step_sync()
+    for i in order:
+        reqs[i] = eng.add_request(prompts[i], SamplingParams(topk=1, max_new_tokens=news[i], ignore_eos=True))
+    eng.run_dp(max_steps=2000)
+    st = eng.sched.stats
+    out.put((rank, [reqs[i].output_token_ids[0] for i in range(len(prompts))], st.preempt_swap + st.preempt_recompute))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_attention_dp_ranks_under_their_own_memory_pressure(seed):
+    """Each DP rank has its own small block pool, chunking, pre-emption mode and arrival times; the lock-step exchange
+    must keep working while one rank pre-empts, idles or prefills, and every request equals a single-process run."""
+    cfg = _cfg()
+    w = load_model_weights(cfg, synthetic_seed=2, dtype=torch.float32)
+    want = {}
+    for r in range(2):
+        prompts, news, _, _, _, _ = _dp_pressure_case(seed, r)
+        eng = LLMEngine(TransformerModel(cfg, w), _serving(), num_blocks=128, num_host_blocks=0)
+        want[r] = [eng.generate([p], SamplingParams(topk=1, max_new_tokens=n, ignore_eos=True))[0].output_token_ids[0]
+                   for p, n in zip(prompts, news)]
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_dp_pressure_worker, args=(r, 2, port, q, seed)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(2):
+        rank, toks, pre = q.get(timeout=240)
+        got[rank] = toks
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got[0] == want[0] and got[1] == want[1]
