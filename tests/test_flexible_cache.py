@@ -76,3 +76,41 @@ def test_engine_reuses_shifted_context_and_first_layer_kv_is_exact():
     assert not torch.allclose(got1[2:], want1[2:], atol=1e-5)  # deeper layers saw a different context: approximate
     eng.run_until_done()
     assert len(req.output_token_ids[0]) == 2
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("seed", list(range(int(__import__("os").environ.get("KSANA_FUZZ_SEEDS", "6")))))
+def test_shifted_reuse_under_memory_pressure_keeps_the_pool_consistent(seed):
+    """Multi-turn style traffic (a common context with a varying head and tail) against a small block pool with
+    non-prefix reuse on: requests are admitted while others are pre-empted and cached blocks are evicted. Reused
+    keys are approximations beyond the first layer, so outputs are not compared; every request must finish with
+    its full length, the checksum-free accounting must hold (all blocks free or cached at the end), and the copy
+    lists must only ever name slots inside the pool (checked by the runner's index_select)."""
+    import random
+    rnd = random.Random(seed)
+    cfg = tiny_llama_config()
+    model = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.02, dtype=torch.float32))
+    host = rnd.choice([0, 24])
+    serving = parse_serving_config({"setting": {"batch_scheduler": {
+        "max_batch_size": rnd.choice([3, 6]), "max_step_tokens": 128, "max_token_len": 256,
+        "enable_auto_prefix_cache": True, "min_flexible_cache_num": rnd.choice([16, 32]),
+        "preempt_mode": rnd.choice([0, 1]) if host else 1, "split_fuse_token_num": rnd.choice([0, 32])},
+        "block_manager": {"block_token_num": BS}}})
+    eng = LLMEngine(model, serving, num_blocks=rnd.randint(18, 30), num_host_blocks=host)
+    g = torch.Generator().manual_seed(seed)
+    contexts = [torch.randint(3, 31000, (rnd.choice([48, 64, 80]),), generator=g).tolist() for _ in range(2)]
+    reqs = []
+    for turn in range(14):
+        head = torch.randint(3, 31000, (rnd.randint(0, 20),), generator=g).tolist()
+        tail = torch.randint(3, 31000, (rnd.randint(1, 12),), generator=g).tolist()
+        n = rnd.randint(2, 16)
+        reqs.append((n, eng.add_request(head + rnd.choice(contexts) + tail,
+                                        SamplingParams(topk=1, max_new_tokens=n, ignore_eos=True))))
+        for _ in range(rnd.randint(0, 5)):
+            eng.step()
+    eng.run_until_done()
+    for n, r in reqs:
+        assert r.finished and len(r.output_token_ids[0]) == n
+    assert eng.cache.num_free_blocks + eng.cache.num_cached_blocks == eng.cache.num_device_blocks
