@@ -77,3 +77,62 @@ def test_resolve_patches_placeholders():
     assert s.tokens(1)[-1] == 2 and res[0].finish_reason == _host.FINISH_EOS
     assert s.update(plan2, [-1], 0) == []  # the in-flight follow-up step is ignored
     assert not s.has_unfinished()
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("seed", list(range(int(__import__("os").environ.get("KSANA_FUZZ_SEEDS", "8")))))
+def test_async_engine_switching_between_fast_and_host_state_steps(seed):
+    """Plain greedy requests run through the asynchronous path; requests with penalties, log-probs, stop ids or
+    seeded sampling need per-token host state and force synchronous steps while they live. Arrivals at random times
+    make the engine switch back and forth with placeholders in flight; every request must equal a synchronous run."""
+    import random
+    import torch
+    from ksanallm_b200.config.model_config import tiny_llama_config
+    from ksanallm_b200.config.schema import parse_serving_config
+    from ksanallm_b200.engine.llm_engine import LLMEngine
+    from ksanallm_b200.engine.sampling_params import SamplingParams
+    from ksanallm_b200.models.loader import load_model_weights
+    from ksanallm_b200.models.transformer import TransformerModel
+    rnd = random.Random(seed)
+    cfg = tiny_llama_config()
+    model = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.02, dtype=torch.float32))
+
+    def engine(enable_async, blocks):
+        serving = parse_serving_config({"setting": {"batch_scheduler": {
+            "max_batch_size": 6, "max_step_tokens": 128, "max_token_len": 256, "enable_auto_prefix_cache": True,
+            "enable_async": enable_async}, "block_manager": {"block_token_num": 16}}})
+        return LLMEngine(model, serving, num_blocks=blocks, num_host_blocks=0)
+    g = torch.Generator().manual_seed(2000 + seed)
+    prompts = [torch.randint(3, 31000, (rnd.randint(2, 40),), generator=g).tolist() for _ in range(10)]
+
+    def params(i):
+        n = 4 + (7 * i + seed) % 20
+        kind = (i + seed) % 5
+        if kind == 0:
+            return SamplingParams(topk=1, max_new_tokens=n, ignore_eos=True, repetition_penalty=1.3, presence_penalty=0.4)
+        if kind == 1:
+            return SamplingParams(topk=1, max_new_tokens=n, ignore_eos=True, logprobs=2)
+        if kind == 2:
+            return SamplingParams(topk=25, topp=0.9, seed=3 + i, max_new_tokens=n, ignore_eos=True)
+        if kind == 3:
+            return SamplingParams(topk=1, max_new_tokens=n, stop_token_ids=[int(prompts[i][0])], min_tokens=2)
+        return SamplingParams(topk=1, max_new_tokens=n, ignore_eos=True)
+    sync = engine(False, 160)
+    want = [sync.generate([p], params(i))[0].output_token_ids[0] for i, p in enumerate(prompts)]
+    eng = engine(True, rnd.randint(20, 40))
+    assert eng.async_mode
+    reqs, order = {}, list(range(len(prompts)))
+    rnd.shuffle(order)
+    while order:
+        for _ in range(rnd.randint(1, 2)):
+            if order:
+                i = order.pop()
+                reqs[i] = eng.add_request(prompts[i], params(i))
+        for _ in range(rnd.randint(0, 6)):
+            eng.step()
+    eng.run_until_done()
+    for i in range(len(prompts)):
+        assert reqs[i].output_token_ids[0] == want[i], (seed, i)
+    assert eng.cache.num_free_blocks + eng.cache.num_cached_blocks == eng.cache.num_device_blocks
