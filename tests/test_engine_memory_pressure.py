@@ -175,3 +175,50 @@ def test_beam_search_and_seeded_parallel_sampling_survive_preemption(seed):
     got = outputs(tight)
     assert got == want
     assert tight.cache.num_free_blocks + tight.cache.num_cached_blocks == tight.cache.num_device_blocks
+
+
+@pytest.mark.parametrize("seed", list(range(int(__import__("os").environ.get("KSANA_FUZZ_SEEDS", "6")))))
+def test_spliced_embeddings_with_chunking_preemption_and_prefix_cache(seed):
+    """Requests whose prompt embeddings are partly replaced (multimodal splice) share the engine with plain requests
+    that hit the prefix cache; chunk boundaries fall inside the spliced spans and pre-emption recomputes them. The
+    spliced requests bypass the prefix tree (same token ids, different embeddings) and must still equal a run alone."""
+    import random
+    rnd = random.Random(seed)
+    cfg = tiny_llama_config()
+    model = TransformerModel(cfg, load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.02, dtype=torch.float32))
+    g = torch.Generator().manual_seed(500 + seed)
+    stem = torch.randint(3, 31000, (40,), generator=g).tolist()
+    items = []
+    for i in range(8):
+        toks = stem + torch.randint(3, 31000, (rnd.randint(2, 30),), generator=g).tolist()
+        refit = None
+        if i % 2 == 0:  # the SAME token ids as other requests, but some embeddings replaced
+            refit = []
+            pos = rnd.randint(0, 10)
+            while pos < len(toks) - 2 and len(refit) < 3:
+                n = rnd.randint(1, min(12, len(toks) - 1 - pos))
+                refit.append((pos, torch.randn(n, cfg.hidden_size, generator=g) * 0.02))
+                pos += n + rnd.randint(1, 9)
+        items.append((toks, refit, SamplingParams(topk=1, max_new_tokens=rnd.randint(3, 24), ignore_eos=True)))
+    roomy = _engine(model, 200, 0, 1, 0)
+    want = []
+    for toks, refit, sp in items:
+        r = roomy.add_request(toks, sp, refit=refit)
+        roomy.run_until_done()
+        want.append(r.output_token_ids[0])
+    host_blocks = rnd.choice([0, 24])
+    tight = _engine(model, rnd.randint(16, 26), host_blocks, rnd.choice([0, 1]) if host_blocks else 1,
+                    rnd.choice([0, 16, 24]))
+    reqs, order = {}, list(range(len(items)))
+    rnd.shuffle(order)
+    while order:
+        for _ in range(rnd.randint(1, 3)):
+            if order:
+                i = order.pop()
+                reqs[i] = tight.add_request(items[i][0], items[i][2], refit=items[i][1])
+        for _ in range(rnd.randint(0, 4)):
+            tight.step()
+    tight.run_until_done()
+    for i in range(len(items)):
+        assert reqs[i].output_token_ids[0] == want[i], (seed, i)
+    assert tight.cache.num_free_blocks + tight.cache.num_cached_blocks == tight.cache.num_device_blocks
