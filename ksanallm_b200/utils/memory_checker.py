@@ -32,10 +32,16 @@ class GuardedBuffer:
 
 
 def block_checksums(kv_cache: torch.Tensor, blocks: Iterable[int]) -> torch.Tensor:
-    """64-bit sums of the raw bytes of the given blocks of one layer's cache."""
+    """64-bit position-weighted sums (odd multipliers, wrapping) of the raw 32-bit words of the given blocks of one
+    layer's cache: a plain byte sum misses changes that move a carry between bytes of one value."""
     idx = torch.as_tensor(list(blocks), dtype=torch.long, device=kv_cache.device)
     sel = kv_cache.index_select(0, idx).contiguous()
-    return sel.view(sel.shape[0], -1).view(torch.uint8).to(torch.int64).sum(dim=1)
+    raw = sel.view(sel.shape[0], -1).view(torch.uint8)
+    if raw.shape[1] % 4:
+        raw = torch.nn.functional.pad(raw, (0, 4 - raw.shape[1] % 4))
+    words = raw.view(torch.int32).to(torch.int64)
+    weights = torch.arange(words.shape[1], dtype=torch.int64, device=words.device) * 2 + 1
+    return (words * weights).sum(dim=1)
 
 
 class BlockChecksumTracker:
