@@ -276,11 +276,7 @@ KSANA_API int ksana_paged_decode(const void* q, int ldq, const void* cache, int 
   {                                                                                                                  \
     auto kern = paged_decode_kernel<128, 16, RM, CT>;                                                                \
     const size_t smem = (RM * 128 + DEC_WARPS * RM * 128 + 2 * DEC_WARPS * RM) * sizeof(float);                      \
-    static bool once = false;                                                                                        \
-    if (!once) {                                                                                                     \
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));               \
-      once = true;                                                                                                   \
-    }                                                                                                                \
+    if (KSANA_SMEM_ONCE(kern, static_cast<int>(smem)) != 0) return -4;                                               \
     kern<<<grid, DEC_WARPS * 32, smem, stream>>>(Q, ldq, reinterpret_cast<const CT*>(cache), block_tables,           \
                                                  max_blocks, cu_q, kv_lens, seq_base, h, hk, scale_log2, alibi,      \
                                                  k_scale, v_scale, O, ldo, part_o, part_lse, splits,                 \

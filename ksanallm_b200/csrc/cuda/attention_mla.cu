@@ -437,12 +437,7 @@ KSANA_API int ksana_mla_decode(const void* q_cat, int total_tokens, const void* 
                    MLA_DQK, MLA_DQK, MLA_PAGE, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
   if (reinterpret_cast<uintptr_t>(q_cat) & 15) return -1;
-  static bool once = false;
-  if (!once) {
-    if (cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MLA_SMEM) != cudaSuccess)
-      return -4;
-    once = true;
-  }
+  if (KSANA_SMEM_ONCE(mla_decode_kernel, MLA_SMEM) != 0) return -4;
   const int sms = sm_count();
   const int n_tiles = (max_kv_len + MLA_TOK - 1) / MLA_TOK;
   // KV splits by a wave-count model: time ~ waves * (tiles per split + fixed per-CTA cost) (+ the merge when split)

@@ -328,22 +328,12 @@ KSANA_API int ksana_paged_prefill(const void* q, int ldq, int total_tokens, cons
   auto O = reinterpret_cast<__nv_bfloat16*>(out);
   if (d == 128) {
     auto kern = paged_prefill_kernel<128>;
-    static bool once = false;
-    if (!once) {
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PrefillSmem<128>::TOTAL) != cudaSuccess)
-        return -4;
-      once = true;
-    }
+    if (KSANA_SMEM_ONCE(kern, PrefillSmem<128>::TOTAL) != 0) return -4;
     kern<<<grid, 128, PrefillSmem<128>::TOTAL, stream>>>(tmQ, tmKV, block_tables, max_blocks, cu_q, kv_lens, seq_base, h,
                                                          hk, scale_log2, alibi, O, ldo, error_word());
   } else {
     auto kern = paged_prefill_kernel<64>;
-    static bool once = false;
-    if (!once) {
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PrefillSmem<64>::TOTAL) != cudaSuccess)
-        return -4;
-      once = true;
-    }
+    if (KSANA_SMEM_ONCE(kern, PrefillSmem<64>::TOTAL) != 0) return -4;
     kern<<<grid, 128, PrefillSmem<64>::TOTAL, stream>>>(tmQ, tmKV, block_tables, max_blocks, cu_q, kv_lens, seq_base, h,
                                                         hk, scale_log2, alibi, O, ldo, error_word());
   }

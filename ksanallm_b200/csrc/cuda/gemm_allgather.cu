@@ -318,12 +318,7 @@ KSANA_API int ksana_gemm_allgather(int rank, int ws, void* const* a_bufs, void* 
   CUtensorMap tmB;
   if (make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, AG_BN, AG_BK, CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
-  static bool once = false;
-  if (!once) {
-    if (cudaFuncSetAttribute(gemm_ag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AG_SMEM) != cudaSuccess)
-      return -4;
-    once = true;
-  }
+  if (KSANA_SMEM_ONCE(gemm_ag_kernel, AG_SMEM) != 0) return -4;
   ag_publish_kernel<<<1, 32, 0, stream>>>(ctx, epoch);
   const int tiles = ws * ((rows_per + AG_BM - 1) / AG_BM) * ((N + AG_BN - 1) / AG_BN);
   int grid = tiles < sm_count() ? tiles : sm_count();

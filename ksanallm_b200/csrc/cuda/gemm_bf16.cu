@@ -304,11 +304,7 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
   if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B)) return -2;
   if (make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
   auto kern = gemm_bf16_kernel<BN, STAGES, OutT>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) return -4;
-    attr_set = true;
-  }
+  if (KSANA_SMEM_ONCE(kern, L::TOTAL) != 0) return -4;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles * splits;
   if (grid > max_ctas) grid = max_ctas;

@@ -287,11 +287,7 @@ static int launch_cluster_splitk(const void* A, const void* W, void* C, const vo
   if (make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, CS_BN, CS_BK, CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
   auto kern = gemm_bf16_cluster_splitk_kernel<OutT>;
-  static bool once = false;
-  if (!once) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CS_SMEM) != cudaSuccess) return -4;
-    once = true;
-  }
+  if (KSANA_SMEM_ONCE(kern, CS_SMEM) != 0) return -4;
   const int tiles = ((M + CS_BM - 1) / CS_BM) * ((N + CS_BN - 1) / CS_BN);
   int clusters = sms / splits;
   if (clusters > tiles) clusters = tiles;

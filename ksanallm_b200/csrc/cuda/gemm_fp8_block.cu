@@ -293,21 +293,13 @@ KSANA_API int ksana_gemm_fp8_block(const void* A8, const float* sa, const void* 
   if (grid > sms) grid = sms;
   if (out_fp32) {
     auto kern = gemm_fp8_block_kernel<float>;
-    static bool once = false;
-    if (!once) {
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM) != cudaSuccess) return -4;
-      once = true;
-    }
+    if (KSANA_SMEM_ONCE(kern, F8_SMEM) != 0) return -4;
     kern<<<grid, F8_THREADS, F8_SMEM, stream>>>(tmA, tmB, sa, sw, reinterpret_cast<float*>(C),
                                                 reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, splits, ws,
                                                 counters, error_word());
   } else {
     auto kern = gemm_fp8_block_kernel<__nv_bfloat16>;
-    static bool once = false;
-    if (!once) {
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM) != cudaSuccess) return -4;
-      once = true;
-    }
+    if (KSANA_SMEM_ONCE(kern, F8_SMEM) != 0) return -4;
     kern<<<grid, F8_THREADS, F8_SMEM, stream>>>(tmA, tmB, sa, sw, reinterpret_cast<__nv_bfloat16*>(C),
                                                 reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, splits, ws,
                                                 counters, error_word());

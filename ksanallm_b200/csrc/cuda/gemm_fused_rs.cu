@@ -525,12 +525,7 @@ KSANA_API int ksana_gemm_rs_norm_ag(const void* A, const void* W, int M, int N, 
   }
   ctx.hbuf_mc = reinterpret_cast<__nv_bfloat16*>(hbuf_mc);
 
-  static bool once = false;
-  if (!once) {
-    if (cudaFuncSetAttribute(gemm_rs_norm_ag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FR_SMEM) != cudaSuccess)
-      return -4;
-    once = true;
-  }
+  if (KSANA_SMEM_ONCE(gemm_rs_norm_ag_kernel, FR_SMEM) != 0) return -4;
   const int sms = sm_count();
   const int tiles = ((M + FR_BM - 1) / FR_BM) * (N / FR_BN);
   const int rows_per = (M + ws - 1) / ws;

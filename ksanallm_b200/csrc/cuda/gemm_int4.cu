@@ -416,15 +416,9 @@ KSANA_API int ksana_gemm_int4(const void* A, const void* Wq, const float* sz, co
   }
   int grid = tiles * splits;
   if (grid > sms) grid = sms;
-  static bool once = false;
-  if (!once) {
-    if (cudaFuncSetAttribute(gemm_int4_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, QCfg<128>::SMEM) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(gemm_int4_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, QCfg<256>::SMEM) !=
-            cudaSuccess)
-      return -4;
-    once = true;
-  }
+  if (KSANA_SMEM_ONCE(gemm_int4_kernel<128>, QCfg<128>::SMEM) != 0 ||
+      KSANA_SMEM_ONCE(gemm_int4_kernel<256>, QCfg<256>::SMEM) != 0)
+    return -4;
   auto Cb = reinterpret_cast<__nv_bfloat16*>(C);
   auto Bb = reinterpret_cast<const __nv_bfloat16*>(bias);
   auto Wb = reinterpret_cast<const uint8_t*>(Wq);
@@ -686,11 +680,7 @@ static int launch_int4_small(const void* A, const void* Wq, const float* sz, con
   CUtensorMap tmA;
   if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, MP, Q_BK, CU_TENSOR_MAP_SWIZZLE_128B)) return -2;
   auto kern = gemm_int4_small_kernel<MP>;
-  static bool once = false;
-  if (!once) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -4;
-    once = true;
-  }
+  if (KSANA_SMEM_ONCE(kern, SMEM) != 0) return -4;
   const int tiles = (N + 127) / 128;
   kern<<<tiles * splits, QS_THREADS, SMEM, stream>>>(tmA, reinterpret_cast<const uint8_t*>(Wq),
                                                     reinterpret_cast<const float2*>(sz), K / group, group,

@@ -74,6 +74,16 @@ int sm_count() {
   return g_sms[dev];
 }
 
+int set_max_smem_once(unsigned long long* done_mask, const void* kernel, int bytes) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (__atomic_load_n(done_mask, __ATOMIC_ACQUIRE) & bit) return 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -4;
+  __atomic_fetch_or(done_mask, bit, __ATOMIC_RELEASE);
+  return 0;
+}
+
 }  // namespace ksana
 
 // Reads and clears the status word of the current device. 0 = no kernel reported a problem.

@@ -29,4 +29,13 @@ int make_tmap_nd(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
 unsigned int* error_word();
 int sm_count();
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute and a process may drive several devices:
+// `done_mask` (one static word per call site) keeps one bit per device ordinal. Returns 0 on success.
+int set_max_smem_once(unsigned long long* done_mask, const void* kernel, int bytes);
+#define KSANA_SMEM_ONCE(kern, bytes)                                                                \
+  ([&]() -> int {                                                                                   \
+    static unsigned long long mask__ = 0;                                                           \
+    return ::ksana::set_max_smem_once(&mask__, reinterpret_cast<const void*>(kern), (bytes));       \
+  }())
+
 }  // namespace ksana

@@ -438,12 +438,7 @@ KSANA_API int ksana_moe_grouped_gemm(const void* A, const void* W, void* C, cons
   if (make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(E) * N, K, K, G_BN, G_BK,
                    CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
-  static bool once = false;
-  if (!once) {
-    if (cudaFuncSetAttribute(moe_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM) != cudaSuccess)
-      return -4;
-    once = true;
-  }
+  if (KSANA_SMEM_ONCE(moe_grouped_gemm_kernel, G_SMEM) != 0) return -4;
   moe_grouped_gemm_kernel<<<sm_count(), 192, G_SMEM, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C), offsets, E,
                                                               N, K, N, error_word());
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

@@ -421,8 +421,17 @@ class Scheduler {
         ok = cache_->EnsureCapacity(id, s.num_computed + q_len + cfg_.lookahead_slots);
       }
       if (!ok) {
-        // Even alone it does not fit right now: pre-empt itself.
         running_.pop_front();
+        const int need_blocks =
+            (s.num_computed + q_len + cfg_.lookahead_slots + cfg_.block_size - 1) / cfg_.block_size;
+        if (need_blocks > cache_->num_device_blocks()) {
+          // It can never fit, not even with the whole pool to itself: pre-empting would only make it cycle
+          // (recompute: re-admitted and thrown out again; swap: out, in, out). End it with what it has produced.
+          Retire(s, FINISH_LENGTH);
+          plan.dropped.push_back({id, FINISH_LENGTH});
+          continue;
+        }
+        // Even alone it does not fit right now: pre-empt itself.
         Preempt(id, &plan);
         continue;
       }

@@ -198,7 +198,7 @@ class DenseExecutor:
         epoch = 0
         fc = self.tp.fused if self.tp.size > 1 else None
         if fc is not None:
-            epoch = (fc.epoch + 1) & 0x7FFFFFFF
+            epoch = (fc.epoch + 1) & 0xFFFFFFFF
             fc.epoch += 2 * n_layers
             self._m.two_kernel_max_tokens = fc.two_kernel_max_tokens
         rc = self._fn(ctypes.byref(self._m), ctypes.byref(s), h.data_ptr(), residual.data_ptr(), 0, n_layers, epoch,

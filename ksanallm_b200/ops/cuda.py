@@ -162,8 +162,8 @@ def gemm_fp8_block(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws_inv:
 
 
 def linear_fp8_block(x, wq, w_scale_inv, bias=None):
-    from . import cuda_quant
-    return cuda_quant.linear_fp8_block(x, wq, w_scale_inv, bias)
+    from . import cuda_fp8
+    return cuda_fp8.linear_fp8_block(x, wq, w_scale_inv, bias)
 
 
 def linear_int4(x, packed, scales, zeros, bias=None, group=128, sz=None):

@@ -73,7 +73,7 @@ class EPExchange:
         assert t_stride <= self.t_cap and T <= t_stride and H == self.hidden and ids.shape[1] == k
         offs, (off_x, off_ret, off_ids, off_w) = self._layout()
         self.epoch += 1
-        ep = self.epoch & 0x7FFFFFFF
+        ep = self.epoch & 0xFFFFFFFF
         st = torch.cuda.current_stream().cuda_stream
         idc = ids.to(torch.int32).contiguous()
         wc = weights.float().contiguous()

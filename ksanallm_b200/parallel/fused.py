@@ -124,7 +124,7 @@ class FusedComm:
                                           self.partial_mc or None, self.hbuf_mc or None, T, self.hidden,
                                           residual.data_ptr() if residual is not None else None,
                                           norm_w.data_ptr() if norm_w is not None else None, float(eps),
-                                          self.epoch & 0x7FFFFFFF, mode, 0, torch.cuda.current_stream().cuda_stream)
+                                          self.epoch & 0xFFFFFFFF, mode, 0, torch.cuda.current_stream().cuda_stream)
         kcuda._check(code, "rs_norm_ag")
         return self.hbuf[:T]
 
@@ -154,7 +154,7 @@ class FusedComm:
             x.data_ptr(), weight.data_ptr(), T, self.hidden, K, x.stride(0), weight.stride(0), self.rank, self.size,
             self._recv_ptrs, self._hbuf_ptrs, self._sig_ptrs, self.hbuf_mc or None, self.rows_cap,
             residual.data_ptr() if residual is not None else None,
-            norm_w.data_ptr() if norm_w is not None else None, float(eps), self.epoch & 0x7FFFFFFF, mode,
+            norm_w.data_ptr() if norm_w is not None else None, float(eps), self.epoch & 0xFFFFFFFF, mode,
             self.comm_ctas, 0, torch.cuda.current_stream().cuda_stream)
         kcuda._check(code, "gemm_rs_norm_ag")
         return self.hbuf[:T]
@@ -166,7 +166,7 @@ class FusedComm:
         assert rows <= self.rows_cap
         if self.ag_epoch:
             code = self._lib.ksana_ag_wait_readers(self.rank, self.size, self._agflag_ptrs,
-                                                   self.ag_epoch & 0x7FFFFFFF, torch.cuda.current_stream().cuda_stream)
+                                                   self.ag_epoch & 0xFFFFFFFF, torch.cuda.current_stream().cuda_stream)
             kcuda._check(code, "ag_wait_readers")
         return self.agbuf[:rows]
 
@@ -181,7 +181,7 @@ class FusedComm:
         code = self._lib.ksana_gemm_allgather(self.rank, self.size, self._agbuf_ptrs, self._agflag_ptrs,
                                               self.ag_staged.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
                                               out.data_ptr(), rows_per, total_rows, N, self.hidden, self.hidden,
-                                              weight.stride(0), N, self.ag_epoch & 0x7FFFFFFF,
+                                              weight.stride(0), N, self.ag_epoch & 0xFFFFFFFF,
                                               torch.cuda.current_stream().cuda_stream)
         kcuda._check(code, "gemm_allgather")
         kcuda.launch_count += 2

@@ -106,9 +106,9 @@ def test_ep_dispatch_combine(world):
             if any(p.exitcode not in (None, 0) for p in procs):
                 break
     if rep is None:
+        # survivors leave by themselves (bounded device waits, process-group timeout); they are not killed
         for p in procs:
-            if p.is_alive():
-                p.terminate()
+            p.join(timeout=120)
         pytest.fail("a rank exited without reporting: " + str([p.exitcode for p in procs]))
     for p in procs:
         p.join(timeout=60)

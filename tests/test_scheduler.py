@@ -382,3 +382,30 @@ def test_randomised_many_clients_stress(seed, preempt_mode, host_blocks):
     assert checked >= 20
     cache.clear_unreferenced()
     assert cache.num_free_blocks == 48 and cache.num_free_host_blocks == host_blocks
+
+
+@pytest.mark.parametrize("preempt_mode,host_blocks", [(1, 0), (0, 16)])
+def test_sequence_that_outgrows_the_whole_pool_ends_with_length(preempt_mode, host_blocks):
+    """A prompt that fits but whose prompt + generated tokens exceed every block of the pool must finish (reason
+    LENGTH) with the tokens it produced, instead of pre-empting itself on every step."""
+    sched, cache, runner = make(num_blocks=4, host_blocks=host_blocks, preempt_mode=preempt_mode, max_token_len=4096)
+    prompt = list(range(50, 60))  # 10 tokens, blocks of 4 -> the pool holds 16 tokens
+    assert sched.enqueue(1, prompt, 200) == host.RET_SUCCESS
+    out, dropped = {}, []
+    steps = 0
+    while sched.has_unfinished():
+        plan = sched.schedule(steps)
+        dropped += [(sid, reason) for sid, reason in plan.dropped]
+        if not plan.empty():
+            for r in sched.update(plan, runner.run(sched, plan), steps):
+                out.setdefault(r.seq_id, []).extend(r.new_tokens)
+        steps += 1
+        assert steps < 100, "the sequence neither advances nor ends"
+    assert dropped == [(1, host.FINISH_LENGTH)]
+    n = len(out[1])
+    assert 4 <= n <= 7 and out[1] == expected_output(prompt, n)
+    assert cache.num_free_blocks == 4
+    # the pool is usable again
+    assert sched.enqueue(2, [5, 6, 7], 3) == host.RET_SUCCESS
+    drive(sched, runner, out)
+    assert out[2] == expected_output([5, 6, 7], 3)
