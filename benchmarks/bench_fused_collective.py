@@ -6,6 +6,8 @@ iterations by cycling through distinct weight copies larger than L2):
   fused1   one kernel: tcgen05 GEMM whose epilogue pushes tiles to the row owners + communication CTAs
            (csrc/cuda/gemm_fused_rs.cu)
   fused2   tcgen05 GEMM into symmetric memory, then the reduce/add/norm/gather kernel (csrc/cuda/comm_fused.cu)
+  ll       one kernel for small M: cluster split-K GEMM whose epilogue sends word-flagged slices to the row owners
+           (csrc/cuda/gemm_ll_fused.cu); timed where M <= the kernel's row limit
   nccl     cuBLAS GEMM -> NCCL all-reduce -> add + RMSNorm kernel (the library baseline)
 Roofline per call = max(2*M*N*K / measured bf16 GEMM peak, bytes over NVLink / link bandwidth) with bytes =
 (ws-1)/ws * M*N*2 out (reduce-scatter) and the same in (all-gather) per GPU, one per direction; `roofline_hbm_us`
@@ -168,8 +170,13 @@ def main():
         def run_nccl_ar_only(i):
             dist.all_reduce(ybuf)
 
+        def run_ll(i):
+            fc.gemm_ll_reduce_add_norm(x, ws_list[i % ncopies], residual, norm_w, 1e-6)
+
         res = {}
         parts = (("fused1", run_fused1), ("fused2", run_fused2), ("nccl", run_nccl))
+        if 0 < M <= fc.ll_max_tokens:
+            parts = (("ll", run_ll),) + parts
         if os.environ.get("BENCH_PARTS", "0") == "1":
             parts += (("gemm_only", run_gemm_only), ("reduce_norm_gather_only", run_reduce_only),
                       ("nccl_allreduce_only", run_nccl_ar_only))
@@ -199,7 +206,8 @@ def main():
                          gemm_us=round(t_gemm, 2),
                          link_us=round(t_link, 2), **{k: round(v, 2) for k, v in res.items()},
                          fused1_frac=round(roof / res["fused1"], 3), fused2_frac=round(roof / res["fused2"], 3),
-                         nccl_frac=round(roof / res["nccl"], 3)))
+                         nccl_frac=round(roof / res["nccl"], 3),
+                         ll_frac_of_hbm_roofline=round(max(roof, t_hbm) / res["ll"], 3) if "ll" in res else None))
     ag_rows = bench_allgather_gemm(tp, fc, peaks, Ms, H) if os.environ.get("BENCH_AG", "1") == "1" else []
     ep_rows = bench_ep(tp, peaks) if os.environ.get("BENCH_EP", "1") == "1" else []
     if rank == 0:

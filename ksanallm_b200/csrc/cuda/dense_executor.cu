@@ -34,6 +34,10 @@ int ksana_gemm_rs_norm_ag(const void* A, const void* W, int M, int N, int K, int
                           void* const* recv, void* const* hbuf, void* const* sig, void* hbuf_mc, int rows_cap,
                           void* residual, const void* norm_w, float eps, unsigned int epoch, int mode, int comm_ctas,
                           int force_splits, cudaStream_t stream);
+int ksana_gemm_ll_reduce_norm(const void* A, const void* W, int M, int N, int K, int lda, int ldw, int rank, int ws,
+                              void* const* recv, void* const* hbuf, void* const* flags, void* hbuf_mc, int rows_cap,
+                              void* residual, const void* norm_w, float eps, unsigned int epoch, int mode,
+                              int force_splits, cudaStream_t stream);
 }
 
 #define KSANA_STEP(n, call)                      \
@@ -47,7 +51,7 @@ int ksana_gemm_rs_norm_ag(const void* A, const void* W, int M, int N, int K, int
   } while (0)
 
 KSANA_API int ksana_dense_forward(const KsanaDenseModel* m, const KsanaDenseStep* s, const void* h_in, void* residual,
-                                  int first, int last, unsigned int epoch, void** out_h, int* fail_code,
+                                  int first, int last, unsigned int* epoch_io, void** out_h, int* fail_code,
                                   int* launches, cudaStream_t stream) {
   const int T = s->total_tokens, H = m->hidden, h = m->heads, hk = m->kv_heads, d = m->head_dim, I = m->inter;
   const int nq = h * d, nk = hk * d, nqkv = nq + 2 * nk;
@@ -62,7 +66,17 @@ KSANA_API int ksana_dense_forward(const KsanaDenseModel* m, const KsanaDenseStep
   // Small steps on many ranks are latency-bound: there the plain GEMM followed by the reduce/norm/gather kernel beats
   // the single fused kernel (8 ranks, 64 tokens: 48 us against 81 us), large steps are the other way round.
   const bool two_kernel = m->ws > 1 && T <= m->two_kernel_max_tokens && m->partial != nullptr;
+  // decode-sized steps: one kernel whose chain of NVLink round trips is as short as it gets
+  const bool ll_path = m->ws > 1 && T <= m->ll_max_tokens && m->ll_recv != nullptr;
+  unsigned int epoch = epoch_io != nullptr ? *epoch_io : 0;
+  auto next_epoch = [&]() -> unsigned int {
+    if (++epoch == 0) ++epoch;
+    return epoch;
+  };
   auto row_parallel = [&](const void* a, const void* wt, int K, const void* norm_w, unsigned int ep) -> int {
+    if (ll_path)
+      return ksana_gemm_ll_reduce_norm(a, wt, T, H, K, K, K, m->rank, m->ws, m->ll_recv, m->hbuf, m->ll_flags,
+                                       m->hbuf_mc, m->ll_rows_cap, residual, norm_w, m->eps, ep, 3, 0, stream);
     if (two_kernel) {
       const int c = ksana_gemm_bf16(a, wt, m->partial[m->rank], nullptr, T, H, K, K, K, H, 0, 0, 0, m->gemm_ws,
                                     m->gemm_ws_floats, m->gemm_counters, m->n_counters, stream);
@@ -96,7 +110,7 @@ KSANA_API int ksana_dense_forward(const KsanaDenseModel* m, const KsanaDenseStep
                                        m->attn_buf, nq, m->attn_ws, m->attn_ws_floats, stream));
     const char* h2;
     if (m->ws > 1) {
-      KSANA_STEP(5, row_parallel(m->attn_buf, w.wo, nq, w.ln2, epoch++));
+      KSANA_STEP(5, row_parallel(m->attn_buf, w.wo, nq, w.ln2, next_epoch()));
       h2 = static_cast<const char*>(m->hbuf[m->rank]);
     } else {
       KSANA_STEP(5, ksana_gemm_bf16(m->attn_buf, w.wo, m->proj_buf, nullptr, T, H, nq, nq, nq, H, 0, 0, 0, m->gemm_ws,
@@ -109,7 +123,7 @@ KSANA_API int ksana_dense_forward(const KsanaDenseModel* m, const KsanaDenseStep
                                   m->gemm_ws_floats, m->gemm_counters, m->n_counters, stream));
     KSANA_STEP(8, ksana_silu_mul(m->gu_buf, 2 * I, m->act_buf, I, T, I, stream));
     if (m->ws > 1) {
-      KSANA_STEP(9, row_parallel(m->act_buf, w.wdown, I, w.next_ln, epoch++));
+      KSANA_STEP(9, row_parallel(m->act_buf, w.wdown, I, w.next_ln, next_epoch()));
       hcur = static_cast<const char*>(m->hbuf[m->rank]);
     } else {
       KSANA_STEP(9, ksana_gemm_bf16(m->act_buf, w.wdown, m->proj_buf, nullptr, T, H, I, I, I, H, 0, 0, 0, m->gemm_ws,
@@ -120,5 +134,6 @@ KSANA_API int ksana_dense_forward(const KsanaDenseModel* m, const KsanaDenseStep
     }
   }
   *out_h = const_cast<char*>(hcur);
+  if (epoch_io != nullptr) *epoch_io = epoch;
   return 0;
 }

@@ -36,6 +36,10 @@ struct KsanaDenseModel {
   void* const* partial;  // two-kernel path: GEMM into this rank's symmetric `partial`, then the reduce/norm/gather kernel
   void* partial_mc;
   int two_kernel_max_tokens;  // steps with at most this many tokens take the two-kernel path (0: never)
+  // decode-sized steps: word-flagged single-kernel path (gemm_ll_fused.cu); ll_max_tokens 0 switches it off
+  void* const* ll_recv;
+  void* const* ll_flags;
+  int ll_rows_cap, ll_max_tokens;
   // scratch, all sized for max_tokens rows
   void* qkv_buf;   // [T, (h + 2 hk) d]
   void* attn_buf;  // [T, h d]
@@ -63,12 +67,13 @@ struct KsanaDenseStep {
 };
 
 // h: normalised input of layer `first` ([T, H] bf16; for ws > 1 it may be any buffer), residual: [T, H] running
-// residual stream (updated in place; row-sharded across ranks when ws > 1). Runs layers [first, last). epoch: first
-// collective epoch to use (ws > 1), two are consumed per layer. *out_h receives the pointer of the normalised output
+// residual stream (updated in place; row-sharded across ranks when ws > 1). Runs layers [first, last). *epoch_io: the
+// last collective epoch used on the shared buffers (ws > 1); two more are consumed per layer (0 is skipped) and the
+// last one used is written back. *out_h receives the pointer of the normalised output
 // (one of the scratch buffers or this rank's hbuf). Returns 0, or (layer + 1) * 100 + step on failure with
 // *fail_code holding the failing call's code. Has no counterpart in the reference (its per-layer C++ forward is
 // CommonModel::LayerForward, src/ksana_llm/models/common/common_model.cpp).
 int ksana_dense_forward(const KsanaDenseModel* m, const KsanaDenseStep* s, const void* h, void* residual, int first,
-                        int last, unsigned int epoch, void** out_h, int* fail_code, int* launches,
+                        int last, unsigned int* epoch_io, void** out_h, int* fail_code, int* launches,
                         cudaStream_t stream);
 }

@@ -162,7 +162,8 @@ __global__ void rope_cache_kernel(__nv_bfloat16* __restrict__ q, int ldq, __nv_b
   __nv_bfloat16* p = is_q ? q + static_cast<size_t>(t) * ldq + hh * d : k + static_cast<size_t>(t) * ldk + (hh - h) * d;
   const __nv_bfloat16* nw = is_q ? qw : kw;
   float inv = 1.f;
-  if (nw != nullptr) {
+  const bool fast = d == 128 && rd == 128 && !interleaved;
+  if (nw != nullptr && !fast) {
     float ss = 0.f;
     for (int i = lane * 2; i < d; i += 64) {
       float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + i));
@@ -178,6 +179,42 @@ __global__ void rope_cache_kernel(__nv_bfloat16* __restrict__ q, int ldq, __nv_b
   }
   const int half = rd >> 1;
   const float* cs = cos_sin ? cos_sin + static_cast<size_t>(positions[t]) * rd : nullptr;
+  if (fast) {
+    // the common head: every lane owns elements (2l, 2l + 1) of the low half and their partners in the high half, so
+    // each access of the warp is one full 128-byte line
+    const int e = lane * 2;
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + e));
+    float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + 64 + e));
+    if (nw != nullptr) {
+      const float inv2 = rsqrtf(warp_sum(a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y) / 128.f + eps);
+      const float2 wa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + e));
+      const float2 wb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + 64 + e));
+      a = __bfloat1622float2(__floats2bfloat162_rn(a.x * inv2 * wa.x, a.y * inv2 * wa.y));
+      b = __bfloat1622float2(__floats2bfloat162_rn(b.x * inv2 * wb.x, b.y * inv2 * wb.y));
+    }
+    float2 ra = a, rb = b;
+    if (cs != nullptr) {
+      const float2 c = *reinterpret_cast<const float2*>(cs + e), sn = *reinterpret_cast<const float2*>(cs + 64 + e);
+      ra = make_float2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+      rb = make_float2(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y);
+    }
+    const __nv_bfloat162 oa = __floats2bfloat162_rn(ra.x, ra.y), ob = __floats2bfloat162_rn(rb.x, rb.y);
+    *reinterpret_cast<__nv_bfloat162*>(p + e) = oa;
+    *reinterpret_cast<__nv_bfloat162*>(p + 64 + e) = ob;
+    if (dst != nullptr) {
+      if constexpr (sizeof(CacheT) == 2) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + e) = oa;
+        *reinterpret_cast<__nv_bfloat162*>(dst + 64 + e) = ob;
+      } else {
+        const float2 fa = __bfloat1622float2(oa), fb = __bfloat1622float2(ob);
+        dst[e] = CacheT(fa.x * k_inv_scale);
+        dst[e + 1] = CacheT(fa.y * k_inv_scale);
+        dst[64 + e] = CacheT(fb.x * k_inv_scale);
+        dst[64 + e + 1] = CacheT(fb.y * k_inv_scale);
+      }
+    }
+    return;
+  }
   // rotated part
   for (int i = lane; i < half; i += 32) {
     const int i0 = interleaved ? 2 * i : i;

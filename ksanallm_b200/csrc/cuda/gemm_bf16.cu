@@ -319,6 +319,8 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
 namespace ksana {
 int gemm_bf16_cluster_splitk(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda,
                              int ldw, int ldc, int out_fp32, int splits, cudaStream_t stream);
+int gemm_bf16_pair(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda, int ldw,
+                   int ldc, int out_fp32, int bn, int epi, cudaStream_t stream);
 }
 
 static unsigned long long* g_gemm_trace = nullptr;
@@ -329,7 +331,8 @@ KSANA_API void ksana_gemm_set_trace(void* buf) { g_gemm_trace = reinterpret_cast
 // base pointers 16-byte aligned); C bf16 (out_fp32 = 0) or fp32 (out_fp32 = 1) with row pitch ldc; N % 8 == 0.
 // ws: fp32 workspace of at least splits * M * N floats and counters: zero-initialised uint32 per output tile
 // (both only read when the launcher decides to split K; pass ws_floats = 0 to forbid splitting).
-// bn: 0 = choose, else 64 / 128 / 256. Returns 0 on success.
+// bn: 0 = choose; 64 / 128 / 256 = single-CTA kernel with that tile width; 1128 / 1256 = CTA-pair kernel
+// (gemm_bf16_2cta.cu) with 256 x 128 / 256 x 256 tiles. Returns 0 on success.
 KSANA_API int ksana_gemm_bf16(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda,
                               int ldw, int ldc, int out_fp32, int bn, int force_splits, float* ws, long long ws_floats,
                               unsigned int* counters, int num_counters, cudaStream_t stream) {
@@ -338,6 +341,13 @@ KSANA_API int ksana_gemm_bf16(const void* A, const void* W, void* C, const void*
   if ((N & 7) || (K & 7) || (lda & 7) || (ldw & 7) || (ldc & 3)) return -1;
   const int sms = sm_count();
   const int tiles_m = (M + BM - 1) / BM;
+  if (bn == 1128 || bn == 1256)
+    return gemm_bf16_pair(A, W, C, bias, M, N, K, lda, ldw, ldc, out_fp32, bn - 1000, 0, stream);
+  if (bn == 0 && force_splits == 0 && M >= 384 && N >= 256)
+    // prefill-sized M: CTA pairs with 256 x 256 tiles (the 256 x 128 pair tile runs the tensor cores at half rate
+    // and is only for narrow outputs); measured at or above the library GEMM from M = 512 up, while for M <= 256
+    // the single-CTA tiles and the cluster split-K path below stay ahead
+    return gemm_bf16_pair(A, W, C, bias, M, N, K, lda, ldw, ldc, out_fp32, 256, 0, stream);
   if (bn == 0) {
     // A CTA's K loop is latency-bound (~0.3 us per 64-wide k-block whatever the tile width), so the cost of a
     // launch is (number of waves) x (k-blocks) with a ~15 % surcharge for the wider tile: pick the cheaper one.
@@ -368,7 +378,9 @@ KSANA_API int ksana_gemm_bf16(const void* A, const void* W, void* C, const void*
   }
   if (force_splits < 0) force_splits = -force_splits;
   const int tiles = tiles_m * ((N + bn - 1) / bn);
-  int splits = 1;
+  // the global-workspace reduction runs on request only (the automatic choice for small M is the cluster path above)
+  int splits = force_splits > 1 ? force_splits : 1;
+  if (splits > 16) splits = 16;
   // every split must own at least one k-block
   while (splits > 1 && ((num_kb + splits - 1) / splits) * (splits - 1) >= num_kb) --splits;
   if (splits > 1 && (ws == nullptr || counters == nullptr || static_cast<long long>(splits) * M * N > ws_floats ||

@@ -29,7 +29,8 @@ class _Model(ctypes.Structure):
                 ("eps", F), ("rotary_dim", I), ("rope_interleaved", I), ("block_size", I), ("num_blocks", I),
                 ("kv_kind", I), ("attn_scale", F), ("k_scale", F), ("v_scale", F), ("rope_cache", P),
                 ("rank", I), ("ws", I), ("rows_cap", I), ("comm_ctas", I), ("recv", P), ("hbuf", P), ("sig", P),
-                ("hbuf_mc", P), ("partial", P), ("partial_mc", P), ("two_kernel_max_tokens", I), ("qkv_buf", P), ("attn_buf", P), ("gu_buf", P), ("act_buf", P), ("proj_buf", P),
+                ("hbuf_mc", P), ("partial", P), ("partial_mc", P), ("two_kernel_max_tokens", I), ("ll_recv", P), ("ll_flags", P),
+                ("ll_rows_cap", I), ("ll_max_tokens", I), ("qkv_buf", P), ("attn_buf", P), ("gu_buf", P), ("act_buf", P), ("proj_buf", P),
                 ("h_buf", P * 2), ("gemm_ws", P), ("gemm_ws_floats", LL), ("gemm_counters", P), ("n_counters", I),
                 ("attn_ws", P), ("attn_ws_floats", LL), ("layers", P)]
 
@@ -115,6 +116,9 @@ class DenseExecutor:
             m.partial = ctypes.cast(fc._partial_ptrs, P)
             m.partial_mc = fc.partial_mc or None
             m.two_kernel_max_tokens = fc.two_kernel_max_tokens
+            m.ll_recv = ctypes.cast(fc._ll_recv_ptrs, P)
+            m.ll_flags = ctypes.cast(fc._ll_flag_ptrs, P)
+            m.ll_rows_cap, m.ll_max_tokens = fc.ll_rows_cap, fc.ll_max_tokens
         ws = kcuda.workspace(model.device)
         self._ws = ws
         m.gemm_ws, m.gemm_ws_floats = _p(ws.gemm_ws), ws.gemm_ws.numel()
@@ -126,7 +130,7 @@ class DenseExecutor:
         self._kv_key = None
         self._step = _Step()
         lib = kcuda.lib()
-        lib.ksana_dense_forward.argtypes = [P, P, P, P, I, I, ctypes.c_uint, P, P, P, P]
+        lib.ksana_dense_forward.argtypes = [P, P, P, P, I, I, P, P, P, P, P]
         lib.ksana_dense_forward.restype = I
         self._fn = lib.ksana_dense_forward
         self._out = P()
@@ -195,16 +199,18 @@ class DenseExecutor:
             s.max_kv_decode = int(kl[n_pre:n_pre + n_dec].max())
         else:
             s.max_q_decode = s.max_kv_decode = 0
-        epoch = 0
         fc = self.tp.fused if self.tp.size > 1 else None
+        epoch = ctypes.c_uint(0)
         if fc is not None:
-            epoch = (fc.epoch + 1) & 0xFFFFFFFF
-            fc.epoch += 2 * n_layers
+            epoch.value = fc.epoch & 0xFFFFFFFF
             self._m.two_kernel_max_tokens = fc.two_kernel_max_tokens
-        rc = self._fn(ctypes.byref(self._m), ctypes.byref(s), h.data_ptr(), residual.data_ptr(), 0, n_layers, epoch,
-                      ctypes.byref(self._out), ctypes.byref(self._fail), ctypes.byref(self._launches),
-                      torch.cuda.current_stream().cuda_stream)
+            self._m.ll_max_tokens = fc.ll_max_tokens
+        rc = self._fn(ctypes.byref(self._m), ctypes.byref(s), h.data_ptr(), residual.data_ptr(), 0, n_layers,
+                      ctypes.byref(epoch), ctypes.byref(self._out), ctypes.byref(self._fail),
+                      ctypes.byref(self._launches), torch.cuda.current_stream().cuda_stream)
         kcuda.launch_count += self._launches.value
+        if fc is not None:
+            fc.epoch = epoch.value  # every collective of the stack took its epoch from the shared counter
         if rc != 0:
             raise RuntimeError(f"native dense forward failed at layer {rc // 100 - 1}, step {rc % 100}, "
                                f"code {self._fail.value}")

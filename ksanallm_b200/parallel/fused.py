@@ -5,7 +5,8 @@ mapped into every peer's address space, plus an NVLS multicast mapping when the 
 
 * ``partial``  [max_tokens, H] bf16 - where this rank's row-parallel GEMM writes its un-reduced output,
 * ``hbuf``     [max_tokens, H] bf16 - where the owners of each row deposit the reduced + normalised activations,
-* ``sig``      uint32 flag words for the epoch-stamped cross-rank barriers.
+* ``sig``      uint32 flag words for the epoch-stamped cross-rank barriers,
+* ``ll_recv``  8-byte words {2 x bf16, epoch} and ``ll_flags`` row flags of the latency-optimised small-step kernel.
 
 The kernels (csrc/cuda/comm_fused.cu) issue the NVLink traffic themselves (``multimem.ld_reduce`` / ``multimem.st``
 or plain peer loads/stores); NCCL is only the bootstrap and the measured baseline. Reference counterparts:
@@ -40,6 +41,15 @@ class FusedComm:
         self.agbuf = symm_mem.empty(self.rows_cap, hidden, dtype=torch.bfloat16, device=device)
         self.agflags = symm_mem.empty(1024, dtype=torch.int32, device=device)
         self.ag_staged = torch.empty(size * self.rows_cap, hidden, dtype=torch.bfloat16, device=device)
+        # decode-sized steps: GEMM + word-flagged reduce-scatter + norm + gather in one kernel (gemm_ll_fused.cu)
+        self.ll_max_tokens = int(os.environ.get("KSANA_LL_MAX_TOKENS", "256"))
+        if hidden % 128 or hidden > 8192:
+            self.ll_max_tokens = 0
+        self.ll_rows_cap = (max(self.ll_max_tokens, 1) + size - 1) // size
+        self.ll_recv = symm_mem.empty(size * self.ll_rows_cap * (hidden // 2) * 2, dtype=torch.int32, device=device)
+        self.ll_flags = symm_mem.empty(max(self.ll_max_tokens, 64), dtype=torch.int32, device=device)
+        self.ll_recv.zero_()
+        self.ll_flags.zero_()
         self.agbuf.zero_()
         self.agflags.zero_()
         self.recv.zero_()
@@ -53,6 +63,8 @@ class FusedComm:
         self._h_recv = symm_mem.rendezvous(self.recv, gname)
         self._h_agbuf = symm_mem.rendezvous(self.agbuf, gname)
         self._h_agflags = symm_mem.rendezvous(self.agflags, gname)
+        self._h_ll_recv = symm_mem.rendezvous(self.ll_recv, gname)
+        self._h_ll_flags = symm_mem.rendezvous(self.ll_flags, gname)
         if use_multicast is None:
             use_multicast = os.environ.get("KSANA_DISABLE_MULTIMEM", "0") != "1"
         mc_ok = bool(use_multicast)
@@ -67,6 +79,8 @@ class FusedComm:
         self._recv_ptrs = arr(*[int(p) for p in self._h_recv.buffer_ptrs])
         self._agbuf_ptrs = arr(*[int(p) for p in self._h_agbuf.buffer_ptrs])
         self._agflag_ptrs = arr(*[int(p) for p in self._h_agflags.buffer_ptrs])
+        self._ll_recv_ptrs = arr(*[int(p) for p in self._h_ll_recv.buffer_ptrs])
+        self._ll_flag_ptrs = arr(*[int(p) for p in self._h_ll_flags.buffer_ptrs])
         self.ag_epoch = 0
         self.single_kernel = os.environ.get("KSANA_DISABLE_FUSED_GEMM_RS", "0") != "1"
         self.comm_ctas = int(os.environ.get("KSANA_FUSED_COMM_CTAS", "16"))
@@ -89,6 +103,12 @@ class FusedComm:
                                               ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                               ctypes.c_void_p]
         lib.ksana_gemm_rs_norm_ag.restype = ctypes.c_int
+        P, I = ctypes.c_void_p, ctypes.c_int
+        lib.ksana_gemm_ll_reduce_norm.argtypes = [P, P, I, I, I, I, I, I, I, P, P, P, P, I, P, P, ctypes.c_float,
+                                                  ctypes.c_uint, I, I, P]
+        lib.ksana_gemm_ll_reduce_norm.restype = I
+        lib.ksana_ll_reduce_norm.argtypes = [P, I, I, I, I, I, P, P, P, P, I, P, P, ctypes.c_float, ctypes.c_uint, I, P]
+        lib.ksana_ll_reduce_norm.restype = I
         lib.ksana_ag_wait_readers.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_uint,
                                               ctypes.c_void_p]
         lib.ksana_ag_wait_readers.restype = ctypes.c_int
@@ -116,15 +136,55 @@ class FusedComm:
     def can_linear_reduce_norm(self, x: torch.Tensor, lin) -> bool:
         return x.dtype == torch.bfloat16 and lin.out_features == self.hidden and x.shape[0] <= self.max_tokens
 
-    # ---- kernels ------------------------------------------------------------------------------------------------
-    def _launch(self, T: int, residual: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    def next_epoch(self) -> int:
+        """Epoch of the next collective on the shared buffers: grows by one per call, wraps modulo 2^32, never 0
+        (0 is what untouched flag words hold)."""
         self.epoch += 1
+        if self.epoch & 0xFFFFFFFF == 0:
+            self.epoch += 1
+        return self.epoch & 0xFFFFFFFF
+
+    # ---- kernels ------------------------------------------------------------------------------------------------
+    def _launch_ll(self, y: torch.Tensor, residual, norm_w, eps: float) -> torch.Tensor:
+        """Reduce (+ residual + norm) + gather of a partial sum in memory through the small-step kernel."""
+        T = y.shape[0]
+        if y.stride(1) != 1 or y.stride(0) % 4 or y.data_ptr() % 8:
+            y = y.contiguous()
+        mode = (1 if norm_w is not None else 0) | (2 if residual is not None else 0)
+        code = self._lib.ksana_ll_reduce_norm(
+            y.data_ptr(), y.stride(0), T, self.hidden, self.rank, self.size, self._ll_recv_ptrs, self._hbuf_ptrs,
+            self._ll_flag_ptrs, self.hbuf_mc or None, self.ll_rows_cap,
+            residual.data_ptr() if residual is not None else None,
+            norm_w.data_ptr() if norm_w is not None else None, float(eps), self.next_epoch(), mode,
+            torch.cuda.current_stream().cuda_stream)
+        kcuda._check(code, "ll_reduce_norm")
+        kcuda.launch_count += 1
+        return self.hbuf[:T]
+
+    def gemm_ll_reduce_add_norm(self, x, weight, residual, norm_w, eps) -> torch.Tensor:
+        """Small steps: tcgen05 GEMM whose epilogue sends word-flagged slices to the row owners, which reduce,
+        normalise and broadcast (csrc/cuda/gemm_ll_fused.cu)."""
+        T, K = x.shape
+        if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+            x = x.contiguous()
+        mode = (1 if norm_w is not None else 0) | (2 if residual is not None else 0)
+        code = self._lib.ksana_gemm_ll_reduce_norm(
+            x.data_ptr(), weight.data_ptr(), T, self.hidden, K, x.stride(0), weight.stride(0), self.rank, self.size,
+            self._ll_recv_ptrs, self._hbuf_ptrs, self._ll_flag_ptrs, self.hbuf_mc or None, self.ll_rows_cap,
+            residual.data_ptr() if residual is not None else None,
+            norm_w.data_ptr() if norm_w is not None else None, float(eps), self.next_epoch(), mode, 0,
+            torch.cuda.current_stream().cuda_stream)
+        kcuda._check(code, "gemm_ll_reduce_norm")
+        kcuda.launch_count += 1
+        return self.hbuf[:T]
+
+    def _launch(self, T: int, residual: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float) -> torch.Tensor:
         mode = (1 if norm_w is not None else 0) | (2 if residual is not None else 0)
         code = self._lib.ksana_rs_norm_ag(self.rank, self.size, self._partial_ptrs, self._hbuf_ptrs, self._sig_ptrs,
                                           self.partial_mc or None, self.hbuf_mc or None, T, self.hidden,
                                           residual.data_ptr() if residual is not None else None,
                                           norm_w.data_ptr() if norm_w is not None else None, float(eps),
-                                          self.epoch & 0xFFFFFFFF, mode, 0, torch.cuda.current_stream().cuda_stream)
+                                          self.next_epoch(), mode, 0, torch.cuda.current_stream().cuda_stream)
         kcuda._check(code, "rs_norm_ag")
         return self.hbuf[:T]
 
@@ -132,6 +192,9 @@ class FusedComm:
         """GEMM straight into the symmetric ``partial`` buffer, then the fused reduce/add/norm/gather kernel.
         The returned tensor is a view of ``hbuf`` (valid until the next fused call)."""
         T = x.shape[0]
+        if (0 < T <= self.ll_max_tokens and lin.kind == "dense" and lin.bias is None and x.dim() == 2 and
+                (residual is None or residual.is_contiguous())):
+            return self.gemm_ll_reduce_add_norm(x, lin.weight, residual, norm_w, eps)
         if (self.single_kernel and T > self.two_kernel_max_tokens and lin.kind == "dense" and lin.bias is None and
                 self.hidden % 256 == 0 and self.hidden <= 9216 and T <= 8192 and x.dim() == 2 and
                 residual is not None and residual.is_contiguous()):
@@ -148,13 +211,12 @@ class FusedComm:
         T, K = x.shape
         if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
             x = x.contiguous()
-        self.epoch += 1
         mode = (1 if norm_w is not None else 0) | (2 if residual is not None else 0)
         code = self._lib.ksana_gemm_rs_norm_ag(
             x.data_ptr(), weight.data_ptr(), T, self.hidden, K, x.stride(0), weight.stride(0), self.rank, self.size,
             self._recv_ptrs, self._hbuf_ptrs, self._sig_ptrs, self.hbuf_mc or None, self.rows_cap,
             residual.data_ptr() if residual is not None else None,
-            norm_w.data_ptr() if norm_w is not None else None, float(eps), self.epoch & 0xFFFFFFFF, mode,
+            norm_w.data_ptr() if norm_w is not None else None, float(eps), self.next_epoch(), mode,
             self.comm_ctas, 0, torch.cuda.current_stream().cuda_stream)
         kcuda._check(code, "gemm_rs_norm_ag")
         return self.hbuf[:T]
@@ -189,11 +251,15 @@ class FusedComm:
 
     def reduce_add_norm(self, y, residual, norm_w, eps) -> torch.Tensor:
         T = y.shape[0]
+        if 0 < T <= self.ll_max_tokens and (residual is None or residual.is_contiguous()):
+            return self._launch_ll(y, residual, norm_w, eps)
         self.partial[:T].copy_(y)
         return self._launch(T, residual, norm_w, eps)
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
+        if 0 < T <= self.ll_max_tokens:
+            return self._launch_ll(x, None, None, 0.0).clone()
         self.partial[:T].copy_(x)
         out = self._launch(T, None, None, 0.0)
         return out.clone()

@@ -48,17 +48,40 @@ def test_gemm_split_k(splits):
     _check(200, 384, 2048, splits=splits, out_fp32=True)
 
 
+@pytest.mark.parametrize("bn", [1128, 1256])
+def test_gemm_cta_pair_kernel(bn):
+    """cta_group::2 kernel (256-row tiles over two SMs): full tiles, ragged M / N / K, bias, fp32 output, strided A,
+    more tiles than SM pairs (several rounds per pair, both accumulator buffers in use)."""
+    _check(256, 256, 64, bn=bn)
+    _check(512, 1024, 512, bn=bn)
+    _check(300, 776, 520, bn=bn)
+    _check(129, 264, 200, bn=bn, bias=True)
+    _check(1000, 640, 768, bn=bn, out_fp32=True)
+    _check(700, 512, 1024, bn=bn, strided=True)
+    _check(4096, 5120, 256, bn=bn)
+    # fewer tiles than SM pairs: every tile is cut into k-block ranges of several pairs (partials parked and summed)
+    _check(256, 512, 4096, bn=bn)
+    _check(64, 1024, 11008, bn=bn)
+    _check(200, 384, 2048, bn=bn, out_fp32=True, bias=True)
+
+
+def test_gemm_auto_dispatch_large_m():
+    _check(2048, 4096, 1024)
+    _check(8192, 1536, 512, bias=True)
+
+
 def test_gemm_bias_fp32_out_and_strided_input():
     _check(200, 640, 768, bias=True)
     _check(200, 640, 768, out_fp32=True)
     _check(200, 640, 768, strided=True)
 
 
-def test_gemm_deterministic():
+@pytest.mark.parametrize("bn", [0, 1256])
+def test_gemm_deterministic(bn):
     from ksanallm_b200.ops import cuda
     x = torch.randn(64, 4096, device="cuda").to(torch.bfloat16)
     w = torch.randn(4096, 4096, device="cuda").to(torch.bfloat16)
-    a = cuda.gemm_bf16(x, w)
-    b = cuda.gemm_bf16(x, w)
+    a = cuda.gemm_bf16(x, w, bn=bn)
+    b = cuda.gemm_bf16(x, w, bn=bn)
     torch.cuda.synchronize()
     assert torch.equal(a, b)

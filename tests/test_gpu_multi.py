@@ -36,7 +36,10 @@ def _worker(rank, world, port, use_mc, q):
     fc = tp.fused
     report = {"multicast": fc.multicast}
     errs = []
-    for T in (1, 7, 64, 300):
+    ll_default = fc.ll_max_tokens
+    # every size through the small-step word-flagged kernel (where it applies) and through the reduce kernel
+    for ll, T in [(ll_default, t) for t in (1, 7, 64, 300)] + [(0, t) for t in (1, 7, 64)]:
+        fc.ll_max_tokens = ll
         g = torch.Generator(device=dev).manual_seed(100 + T)
         parts = [torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16) for _ in range(world)]
         res0 = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
@@ -55,6 +58,30 @@ def _worker(rank, world, port, use_mc, q):
         ar = fc.all_reduce(parts[rank])
         torch.cuda.synchronize()
         errs.append((T, (ar.float() - total).abs().max().item() / max(1.0, total.abs().max().item()), 0.0))
+    fc.ll_max_tokens = ll_default
+    # small-step single kernel: GEMM + word-flagged reduce-scatter + norm + gather
+    llerrs = []
+    for T, K in ((1, 256), (64, 512), (200, 1024), (256, 384), (33, 2048)) if ll_default else ():
+        g = torch.Generator(device=dev).manual_seed(11 * T + K)
+        xs = [(torch.randn(T, K, device=dev, generator=g) * 0.5).to(torch.bfloat16) for _ in range(world)]
+        wsl = [(torch.randn(H, K, device=dev, generator=g) * 0.05).to(torch.bfloat16) for _ in range(world)]
+        res0 = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(H, device=dev, generator=g)).to(torch.bfloat16)
+        total = sum((x.float() @ ww.float().t()).to(torch.bfloat16).float() for x, ww in zip(xs, wsl))
+        res_ref = (total + res0.float()).to(torch.bfloat16)
+        want = ref.rms_norm(res_ref, w, 1e-6)
+        residual = res0.clone()
+        out = fc.gemm_ll_reduce_add_norm(xs[rank], wsl[rank], residual, w, 1e-6).clone()
+        torch.cuda.synchronize()
+        rows_per = (T + world - 1) // world
+        lo, hi = rank * rows_per, min(T, (rank + 1) * rows_per)
+        e1 = (out.float() - want.float()).abs().max().item()
+        e2 = (residual[lo:hi].float() - res_ref[lo:hi].float()).abs().max().item() if hi > lo else 0.0
+        llerrs.append((T, K, e1, e2))
+        out2 = fc.gemm_ll_reduce_add_norm(xs[rank], wsl[rank], res0.clone(), w, 1e-6).clone()
+        torch.cuda.synchronize()
+        llerrs.append((T, K, 0.0 if torch.equal(out, out2) else 1.0, 0.0))  # deterministic
+    report["llerrs"] = llerrs
     # single-kernel GEMM + reduce-scatter + norm + all-gather vs (local GEMMs summed in fp32 -> reference norm)
     ferrs = []
     for T, K in ((1, 256), (64, 512), (300, 1024), (500, 384)):
@@ -110,13 +137,16 @@ def _worker(rank, world, port, use_mc, q):
     h_tp = m_tp.forward(meta, kv).clone()
     torch.cuda.synchronize()
     report["native"] = m_tp._native_executor() is not None
-    # the other row-parallel strategy (single fused kernel <-> GEMM + reduce kernel) must agree
-    old = fc.two_kernel_max_tokens
-    fc.two_kernel_max_tokens = 0 if old else 4096
-    h_alt = m_tp.forward(meta, m_tp.allocate_kv_cache(8, 16)).clone()
-    fc.two_kernel_max_tokens = old
-    torch.cuda.synchronize()
-    report["alt_err"] = (h_alt.float() - h_tp.float()).abs().max().item()
+    # the other row-parallel strategies (small-step kernel off: single fused kernel <-> GEMM + reduce kernel) must agree
+    old, old_ll = fc.two_kernel_max_tokens, fc.ll_max_tokens
+    alt = 0.0
+    for two in (0, 4096):
+        fc.ll_max_tokens, fc.two_kernel_max_tokens = 0, two
+        h_alt = m_tp.forward(meta, m_tp.allocate_kv_cache(8, 16)).clone()
+        torch.cuda.synchronize()
+        alt = max(alt, (h_alt.float() - h_tp.float()).abs().max().item())
+    fc.two_kernel_max_tokens, fc.ll_max_tokens = old, old_ll
+    report["alt_err"] = alt
     if rank == 0:
         w_1 = load_model_weights(cfg, synthetic_seed=3, device=dev, dtype=torch.bfloat16)
         m_1 = TransformerModel(cfg, w_1, TPGroup(), max_positions=512)
@@ -171,7 +201,7 @@ def test_fused_reduce_norm_ranks(use_mc, world):
     tol = 6e-2 * max(1.0, (world / 2) ** 0.5)
     for T, e1, e2 in rep["errs"]:
         assert e1 < tol and e2 < tol, (T, e1, e2)
-    for T, K, e1, e2 in rep["ferrs"]:
+    for T, K, e1, e2 in rep["ferrs"] + rep["llerrs"]:
         assert e1 < 8e-2 and e2 < 8e-2, (T, K, e1, e2)
     for rows_per, N, e, m in rep["aerrs"]:
         assert e < 2e-2 * max(1.0, m), (rows_per, N, e, m)
