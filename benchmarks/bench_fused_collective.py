@@ -1,8 +1,9 @@
 #!/usr/bin/env python
 """Micro-benchmark of the row-parallel "GEMM -> all-reduce -> residual add -> RMSNorm" block under tensor parallelism.
 
-Three implementations of the same math, timed on the device (CUDA events, max over ranks, L2 flushed between
-iterations by cycling through distinct weight copies larger than L2):
+Implementations of the same math, timed on the device (CUDA events around ONE launch of a CUDA graph that holds
+`iters` calls - a Python call costs more host time than these kernels run, so timing eager launches would measure the
+host; max over ranks; L2 flushed between iterations by cycling through distinct weight copies larger than L2):
   fused1   one kernel: tcgen05 GEMM whose epilogue pushes tiles to the row owners + communication CTAs
            (csrc/cuda/gemm_fused_rs.cu)
   fused2   tcgen05 GEMM into symmetric memory, then the reduce/add/norm/gather kernel (csrc/cuda/comm_fused.cu)
@@ -32,6 +33,35 @@ from ksanallm_b200.parallel.comm import init_distributed  # noqa: E402
 
 
 def _time(fn, dev, iters=20, warm=4):
+    """Microseconds per call: `iters` calls captured in a CUDA graph that is launched once (every captured call
+    carries its own collective epoch, so a graph is never replayed)."""
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(iters):
+                fn(warm + i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    del graph
+    return float(t.item())
+
+
+def _time_eager(fn, dev, iters=20, warm=4):
+    """Eager launches (for paths that read sizes back to the host and cannot be captured)."""
     for i in range(warm):
         fn(i)
     torch.cuda.synchronize()
@@ -114,7 +144,7 @@ def bench_ep(tp, peaks):
             y = cuda_moe.moe_experts(xg, idg, wg, w1, w2, rank * el)
             dist.reduce_scatter_tensor(ys, y)
 
-        te, tr = _time(run_ep, dev), _time(run_repl, dev)
+        te, tr = _time_eager(run_ep, dev), _time_eager(run_repl, dev)
         flops = 2.0 * Tl * k * 3 * H * I  # per rank on average
         link = 2.0 * Tl * min(k, ws - 1) * (ws - 1) / ws * H * 2 / 2  # out + back, one per direction (upper bound)
         roof = max(flops / (peaks["bf16_tflops"] * 1e12), link / (peaks["nvlink_gbs"] * 1e9),
@@ -181,21 +211,7 @@ def main():
             parts += (("gemm_only", run_gemm_only), ("reduce_norm_gather_only", run_reduce_only),
                       ("nccl_allreduce_only", run_nccl_ar_only))
         for name, fn in parts:
-            for i in range(5):
-                fn(i)
-            torch.cuda.synchronize()
-            dist.barrier()
-            iters = 30
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for i in range(iters):
-                fn(i)
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], device=dev)  # us
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            res[name] = float(t.item())
-            dist.barrier()
+            res[name] = _time(fn, dev, iters=30, warm=5)
         flops = 2.0 * M * H * K
         t_gemm = flops / (peaks["bf16_tflops"] * 1e12) * 1e6
         link_bytes = (ws - 1) / ws * M * H * 2

@@ -35,105 +35,242 @@ int ksana_gemm_rs_norm_ag(const void* A, const void* W, int M, int N, int K, int
                           void* residual, const void* norm_w, float eps, unsigned int epoch, int mode, int comm_ctas,
                           int force_splits, cudaStream_t stream);
 int ksana_gemm_ll_reduce_norm(const void* A, const void* W, int M, int N, int K, int lda, int ldw, int rank, int ws,
-                              void* const* recv, void* const* hbuf, void* const* flags, void* hbuf_mc, int rows_cap,
-                              void* residual, const void* norm_w, float eps, unsigned int epoch, int mode,
-                              int force_splits, cudaStream_t stream);
+                              void* const* recv, long long recv_off, void* const* recv2, void* recv2_mc, void* hbuf,
+                              int rows_cap, int one_shot, void* residual, const void* norm_w, float eps,
+                              unsigned int epoch, int mode, int force_splits, cudaStream_t stream);
+void ksana_gemm_set_lane(int lane);
 }
 
-#define KSANA_STEP(n, call)                      \
-  do {                                           \
-    const int code__ = (call);                   \
-    ++(*launches);                               \
-    if (code__ != 0) {                           \
-      *fail_code = code__;                       \
-      return (L + 1) * 100 + (n);                \
-    }                                            \
-  } while (0)
+namespace {
+
+// One half-batch (or the whole step): rows [r0, r0 + rows) of every [T, ...] buffer, prefill sequences
+// [pre_base, pre_base + n_pre) and decode sequences [dec_base, dec_base + n_dec) of the step's sequence list.
+struct Range {
+  int r0, rows;
+  int pre_base, n_pre, dec_base, n_dec;
+  int max_q_prefill, max_q_decode, max_kv_decode;
+  int lane;  // 0 / 1: which flag region, scratch half and stream this range uses
+  cudaStream_t stream;
+  const char* hcur;  // normalised input rows of the next layer (pointer to row r0)
+  int pp;            // ws == 1: which of the two h buffers receives the next norm output
+};
+
+struct Exec {
+  const KsanaDenseModel* m;
+  const KsanaDenseStep* s;
+  char* residual;
+  unsigned int epoch, ll_seq;
+  int* launches;
+  int fail_step, fail_code;
+  void* sig_lane[2][8];
+
+  unsigned int next_epoch() {
+    if (++epoch == 0) ++epoch;
+    return epoch;
+  }
+  bool step(int n, int code) {
+    ++(*launches);
+    if (code != 0 && fail_step == 0) {
+      fail_step = n;
+      fail_code = code;
+    }
+    return code == 0;
+  }
+
+  // row-parallel GEMM + reduce + residual add + RMSNorm + gather of one range; the output rows land in hbuf
+  int row_parallel(const Range& g, const void* a, const void* wt, int K, const void* norm_w, bool whole_step) {
+    const int H = m->hidden, T = g.rows;
+    char* res = residual + static_cast<size_t>(g.r0) * H * 2;
+    const unsigned int ep = next_epoch();
+    // decode-sized steps: one kernel whose chain of NVLink round trips is as short as it gets
+    if (whole_step && T <= m->ll_max_tokens && m->ll_recv != nullptr) {
+      ++ll_seq;
+      const long long off = m->ll_one_shot ? static_cast<long long>(ll_seq & 1u) * m->ll_half_words : 0;
+      return ksana_gemm_ll_reduce_norm(a, wt, T, H, K, K, K, m->rank, m->ws, m->ll_recv, off, m->ll_recv2,
+                                       m->ll_recv2_mc, m->hbuf[m->rank], m->ll_rows_cap, m->ll_one_shot, res, norm_w,
+                                       m->eps, ep, 3, 0, g.stream);
+    }
+    // Half-batches always take the GEMM + reduce kernel pair: the reduce kernel is small enough to stay resident next
+    // to the other half's GEMM. Whole steps: the pair when latency-bound, else the single fused kernel.
+    const bool two_kernel = !whole_step || (T <= m->two_kernel_max_tokens && m->partial != nullptr);
+    if (two_kernel) {
+      void* partial[8];
+      void* hbuf[8];
+      const size_t off = static_cast<size_t>(g.r0) * H * 2;
+      for (int i = 0; i < m->ws; ++i) {
+        partial[i] = static_cast<char*>(m->partial[i]) + off;
+        hbuf[i] = static_cast<char*>(m->hbuf[i]) + off;
+      }
+      const int c = ksana_gemm_bf16(a, wt, partial[m->rank], nullptr, T, H, K, K, K, H, 0, 0, 0, m->gemm_ws,
+                                    m->gemm_ws_floats, m->gemm_counters, m->n_counters, g.stream);
+      if (c != 0) return c;
+      ++(*launches);
+      return ksana_rs_norm_ag(m->rank, m->ws, partial, hbuf, sig_lane[g.lane],
+                              m->partial_mc ? static_cast<char*>(m->partial_mc) + off : nullptr,
+                              m->hbuf_mc ? static_cast<char*>(m->hbuf_mc) + off : nullptr, T, H, res, norm_w, m->eps, ep,
+                              3, 0, g.stream);
+    }
+    return ksana_gemm_rs_norm_ag(a, wt, T, H, K, K, K, m->rank, m->ws, m->recv, m->hbuf, m->sig, m->hbuf_mc, m->rows_cap,
+                                 res, norm_w, m->eps, ep, 3, m->comm_ctas, 0, g.stream);
+  }
+
+  // one decoder layer over one range
+  bool layer(int L, Range& g, bool whole_step) {
+    const KsanaDenseLayer& w = m->layers[L];
+    const int T = g.rows, H = m->hidden, h = m->heads, hk = m->kv_heads, d = m->head_dim, I = m->inter;
+    const int nq = h * d, nk = hk * d, nqkv = nq + 2 * nk;
+    cudaStream_t st = g.stream;
+    ksana_gemm_set_lane(g.lane);
+    char* qkv_all = static_cast<char*>(m->qkv_buf);
+    char* qkv = qkv_all + static_cast<size_t>(g.r0) * nqkv * 2;
+    char* attn_all = static_cast<char*>(m->attn_buf);
+    char* attn = attn_all + static_cast<size_t>(g.r0) * nq * 2;
+    char* gu = static_cast<char*>(m->gu_buf) + static_cast<size_t>(g.r0) * 2 * I * 2;
+    char* act = static_cast<char*>(m->act_buf) + static_cast<size_t>(g.r0) * I * 2;
+    char* res = residual + static_cast<size_t>(g.r0) * H * 2;
+    if (!step(1, ksana_gemm_bf16(g.hcur, w.wqkv, qkv, w.bqkv, T, nqkv, H, H, H, nqkv, 0, 0, 0, m->gemm_ws,
+                                 m->gemm_ws_floats, m->gemm_counters, m->n_counters, st)))
+      return false;
+    char* q = qkv;
+    char* k = qkv + static_cast<size_t>(nq) * 2;
+    char* v = qkv + static_cast<size_t>(nq + nk) * 2;
+    if (!step(2, ksana_rope_cache(q, nqkv, k, nqkv, v, nqkv, s->positions + g.r0, m->rope_cache, s->slot_mapping + g.r0,
+                                  w.kv_cache, w.q_norm, w.k_norm, m->eps, T, h, hk, d,
+                                  m->rope_cache ? m->rotary_dim : 0, m->rope_interleaved, m->block_size, m->kv_kind,
+                                  m->k_scale, m->v_scale, st)))
+      return false;
+    // the attention kernels index rows through the step's cu_q, so they get the base pointers of all rows
+    if (g.n_pre > 0 &&
+        !step(3, ksana_paged_prefill(qkv_all, nqkv, s->total_tokens, w.kv_cache, m->num_blocks, s->block_tables,
+                                     s->max_blocks, s->cu_q, s->kv_lens, g.pre_base, g.n_pre, g.max_q_prefill, h, hk, d,
+                                     m->block_size, m->attn_scale, nullptr, attn_all, nq, st)))
+      return false;
+    if (g.n_dec > 0) {
+      const long long half = m->attn_ws_floats / 2;
+      if (!step(4, ksana_paged_decode(qkv_all, nqkv, w.kv_cache, m->kv_kind, s->block_tables, s->max_blocks, s->cu_q,
+                                      s->kv_lens, g.dec_base, g.n_dec, g.max_q_decode, g.max_kv_decode, h, hk, d,
+                                      m->block_size, m->attn_scale, nullptr, m->k_scale, m->v_scale, attn_all, nq,
+                                      m->attn_ws + (whole_step ? 0 : g.lane * half),
+                                      whole_step ? m->attn_ws_floats : half, st)))
+        return false;
+    }
+    const char* h2;
+    if (m->ws > 1) {
+      if (!step(5, row_parallel(g, attn, w.wo, nq, w.ln2, whole_step))) return false;
+      h2 = static_cast<const char*>(m->hbuf[m->rank]) + static_cast<size_t>(g.r0) * H * 2;
+    } else {
+      char* proj = static_cast<char*>(m->proj_buf) + static_cast<size_t>(g.r0) * H * 2;
+      char* hb = static_cast<char*>(m->h_buf[g.pp]) + static_cast<size_t>(g.r0) * H * 2;
+      if (!step(5, ksana_gemm_bf16(attn, w.wo, proj, nullptr, T, H, nq, nq, nq, H, 0, 0, 0, m->gemm_ws,
+                                   m->gemm_ws_floats, m->gemm_counters, m->n_counters, st)))
+        return false;
+      if (!step(6, ksana_rms_norm(proj, H, res, H, w.ln2, hb, H, T, H, m->eps, st))) return false;
+      h2 = hb;
+      g.pp ^= 1;
+    }
+    if (!step(7, ksana_gemm_bf16(h2, w.wgu, gu, nullptr, T, 2 * I, H, H, H, 2 * I, 0, 0, 0, m->gemm_ws,
+                                 m->gemm_ws_floats, m->gemm_counters, m->n_counters, st)))
+      return false;
+    if (!step(8, ksana_silu_mul(gu, 2 * I, act, I, T, I, st))) return false;
+    if (m->ws > 1) {
+      if (!step(9, row_parallel(g, act, w.wdown, I, w.next_ln, whole_step))) return false;
+      g.hcur = static_cast<const char*>(m->hbuf[m->rank]) + static_cast<size_t>(g.r0) * H * 2;
+    } else {
+      char* proj = static_cast<char*>(m->proj_buf) + static_cast<size_t>(g.r0) * H * 2;
+      char* hb = static_cast<char*>(m->h_buf[g.pp]) + static_cast<size_t>(g.r0) * H * 2;
+      if (!step(9, ksana_gemm_bf16(act, w.wdown, proj, nullptr, T, H, I, I, I, H, 0, 0, 0, m->gemm_ws,
+                                   m->gemm_ws_floats, m->gemm_counters, m->n_counters, st)))
+        return false;
+      if (!step(10, ksana_rms_norm(proj, H, res, H, w.next_ln, hb, H, T, H, m->eps, st))) return false;
+      g.hcur = hb;
+      g.pp ^= 1;
+    }
+    return true;
+  }
+};
+
+// second stream + events of the two-batch overlap, one set per device, created on first use
+struct OverlapStreams {
+  cudaStream_t side = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+OverlapStreams g_overlap[64];
+
+OverlapStreams* overlap_streams() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  OverlapStreams* o = &g_overlap[dev];
+  if (o->side == nullptr) {
+    if (cudaStreamCreateWithFlags(&o->side, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&o->fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&o->join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  }
+  return o;
+}
+
+}  // namespace
 
 KSANA_API int ksana_dense_forward(const KsanaDenseModel* m, const KsanaDenseStep* s, const void* h_in, void* residual,
                                   int first, int last, unsigned int* epoch_io, void** out_h, int* fail_code,
                                   int* launches, cudaStream_t stream) {
-  const int T = s->total_tokens, H = m->hidden, h = m->heads, hk = m->kv_heads, d = m->head_dim, I = m->inter;
-  const int nq = h * d, nk = hk * d, nqkv = nq + 2 * nk;
-  const char* hcur = static_cast<const char*>(h_in);
-  int pp = 0;
+  const int T = s->total_tokens, H = m->hidden;
   *fail_code = 0;
   *launches = 0;
   if (T <= 0) {
     *out_h = const_cast<void*>(h_in);
     return 0;
   }
-  // Small steps on many ranks are latency-bound: there the plain GEMM followed by the reduce/norm/gather kernel beats
-  // the single fused kernel (8 ranks, 64 tokens: 48 us against 81 us), large steps are the other way round.
-  const bool two_kernel = m->ws > 1 && T <= m->two_kernel_max_tokens && m->partial != nullptr;
-  // decode-sized steps: one kernel whose chain of NVLink round trips is as short as it gets
-  const bool ll_path = m->ws > 1 && T <= m->ll_max_tokens && m->ll_recv != nullptr;
-  unsigned int epoch = epoch_io != nullptr ? *epoch_io : 0;
-  auto next_epoch = [&]() -> unsigned int {
-    if (++epoch == 0) ++epoch;
-    return epoch;
-  };
-  auto row_parallel = [&](const void* a, const void* wt, int K, const void* norm_w, unsigned int ep) -> int {
-    if (ll_path)
-      return ksana_gemm_ll_reduce_norm(a, wt, T, H, K, K, K, m->rank, m->ws, m->ll_recv, m->hbuf, m->ll_flags,
-                                       m->hbuf_mc, m->ll_rows_cap, residual, norm_w, m->eps, ep, 3, 0, stream);
-    if (two_kernel) {
-      const int c = ksana_gemm_bf16(a, wt, m->partial[m->rank], nullptr, T, H, K, K, K, H, 0, 0, 0, m->gemm_ws,
-                                    m->gemm_ws_floats, m->gemm_counters, m->n_counters, stream);
-      if (c != 0) return c;
-      ++(*launches);
-      return ksana_rs_norm_ag(m->rank, m->ws, m->partial, m->hbuf, m->sig, m->partial_mc, m->hbuf_mc, T, H, residual,
-                              norm_w, m->eps, ep, 3, 0, stream);
-    }
-    return ksana_gemm_rs_norm_ag(a, wt, T, H, K, K, K, m->rank, m->ws, m->recv, m->hbuf, m->sig, m->hbuf_mc, m->rows_cap,
-                                 residual, norm_w, m->eps, ep, 3, m->comm_ctas, 0, stream);
-  };
-  for (int L = first; L < last; ++L) {
-    const KsanaDenseLayer& w = m->layers[L];
-    char* qkv = static_cast<char*>(m->qkv_buf);
-    KSANA_STEP(1, ksana_gemm_bf16(hcur, w.wqkv, qkv, w.bqkv, T, nqkv, H, H, H, nqkv, 0, 0, 0, m->gemm_ws,
-                                  m->gemm_ws_floats, m->gemm_counters, m->n_counters, stream));
-    char* q = qkv;
-    char* k = qkv + static_cast<size_t>(nq) * 2;
-    char* v = qkv + static_cast<size_t>(nq + nk) * 2;
-    KSANA_STEP(2, ksana_rope_cache(q, nqkv, k, nqkv, v, nqkv, s->positions, m->rope_cache, s->slot_mapping, w.kv_cache,
-                                   w.q_norm, w.k_norm, m->eps, T, h, hk, d, m->rope_cache ? m->rotary_dim : 0,
-                                   m->rope_interleaved, m->block_size, m->kv_kind, m->k_scale, m->v_scale, stream));
-    if (s->num_prefill > 0)
-      KSANA_STEP(3, ksana_paged_prefill(q, nqkv, T, w.kv_cache, m->num_blocks, s->block_tables, s->max_blocks, s->cu_q,
-                                        s->kv_lens, 0, s->num_prefill, s->max_q_prefill, h, hk, d, m->block_size,
-                                        m->attn_scale, nullptr, m->attn_buf, nq, stream));
-    if (s->num_decode > 0)
-      KSANA_STEP(4, ksana_paged_decode(q, nqkv, w.kv_cache, m->kv_kind, s->block_tables, s->max_blocks, s->cu_q,
-                                       s->kv_lens, s->num_prefill, s->num_decode, s->max_q_decode, s->max_kv_decode, h,
-                                       hk, d, m->block_size, m->attn_scale, nullptr, m->k_scale, m->v_scale,
-                                       m->attn_buf, nq, m->attn_ws, m->attn_ws_floats, stream));
-    const char* h2;
-    if (m->ws > 1) {
-      KSANA_STEP(5, row_parallel(m->attn_buf, w.wo, nq, w.ln2, next_epoch()));
-      h2 = static_cast<const char*>(m->hbuf[m->rank]);
-    } else {
-      KSANA_STEP(5, ksana_gemm_bf16(m->attn_buf, w.wo, m->proj_buf, nullptr, T, H, nq, nq, nq, H, 0, 0, 0, m->gemm_ws,
-                                    m->gemm_ws_floats, m->gemm_counters, m->n_counters, stream));
-      KSANA_STEP(6, ksana_rms_norm(m->proj_buf, H, residual, H, w.ln2, m->h_buf[pp], H, T, H, m->eps, stream));
-      h2 = static_cast<const char*>(m->h_buf[pp]);
-      pp ^= 1;
-    }
-    KSANA_STEP(7, ksana_gemm_bf16(h2, w.wgu, m->gu_buf, nullptr, T, 2 * I, H, H, H, 2 * I, 0, 0, 0, m->gemm_ws,
-                                  m->gemm_ws_floats, m->gemm_counters, m->n_counters, stream));
-    KSANA_STEP(8, ksana_silu_mul(m->gu_buf, 2 * I, m->act_buf, I, T, I, stream));
-    if (m->ws > 1) {
-      KSANA_STEP(9, row_parallel(m->act_buf, w.wdown, I, w.next_ln, next_epoch()));
-      hcur = static_cast<const char*>(m->hbuf[m->rank]);
-    } else {
-      KSANA_STEP(9, ksana_gemm_bf16(m->act_buf, w.wdown, m->proj_buf, nullptr, T, H, I, I, I, H, 0, 0, 0, m->gemm_ws,
-                                    m->gemm_ws_floats, m->gemm_counters, m->n_counters, stream));
-      KSANA_STEP(10, ksana_rms_norm(m->proj_buf, H, residual, H, w.next_ln, m->h_buf[pp], H, T, H, m->eps, stream));
-      hcur = static_cast<const char*>(m->h_buf[pp]);
-      pp ^= 1;
-    }
+  Exec ex;
+  ex.m = m;
+  ex.s = s;
+  ex.residual = static_cast<char*>(residual);
+  ex.epoch = epoch_io != nullptr ? epoch_io[0] : 0;
+  ex.ll_seq = epoch_io != nullptr ? epoch_io[1] : 0;
+  ex.launches = launches;
+  ex.fail_step = ex.fail_code = 0;
+  for (int i = 0; i < 8; ++i) {
+    ex.sig_lane[0][i] = (m->ws > 1 && i < m->ws) ? m->sig[i] : nullptr;
+    ex.sig_lane[1][i] = (m->ws > 1 && i < m->ws) ? static_cast<char*>(m->sig[i]) + static_cast<size_t>(m->sig_words) * 4
+                                                 : nullptr;
   }
-  *out_h = const_cast<char*>(hcur);
-  if (epoch_io != nullptr) *epoch_io = epoch;
+  const bool overlap = m->ws > 1 && s->split_seq > 0 && s->split_row > 0 && s->split_row < T && m->sig_words > 0 &&
+                       m->partial != nullptr;
+  OverlapStreams* os = overlap ? overlap_streams() : nullptr;
+  int failed_layer = -1;
+  if (overlap && os != nullptr) {
+    // ---- two half-batches on two streams; kernels are issued layer by layer, alternating between the halves ----
+    const int n_seq_a = s->split_seq;
+    Range a{0, s->split_row, 0, s->num_prefill, s->num_prefill, s->num_decode, s->max_q_prefill, s->max_q_decode,
+            s->max_kv_decode, 0, stream, static_cast<const char*>(h_in), 0};
+    // the sequence list is "prefill sequences, then decode sequences"; the second half starts at sequence split_seq
+    Range b{s->split_row, T - s->split_row, n_seq_a, s->num_prefill_b, n_seq_a + s->num_prefill_b, s->num_decode_b,
+            s->max_q_prefill_b, s->max_q_decode_b, s->max_kv_decode_b, 1, os->side,
+            static_cast<const char*>(h_in) + static_cast<size_t>(s->split_row) * H * 2, 0};
+    cudaEventRecord(os->fork, stream);
+    cudaStreamWaitEvent(os->side, os->fork, 0);
+    for (int L = first; L < last && failed_layer < 0; ++L) {
+      if (!ex.layer(L, a, false) || !ex.layer(L, b, false)) failed_layer = L;
+    }
+    ksana_gemm_set_lane(0);
+    cudaEventRecord(os->join, os->side);
+    cudaStreamWaitEvent(stream, os->join, 0);
+    *out_h = m->hbuf[m->rank];
+  } else {
+    Range g{0, T, 0, s->num_prefill, s->num_prefill, s->num_decode, s->max_q_prefill, s->max_q_decode,
+            s->max_kv_decode, 0, stream, static_cast<const char*>(h_in), 0};
+    for (int L = first; L < last && failed_layer < 0; ++L) {
+      if (!ex.layer(L, g, true)) failed_layer = L;
+    }
+    *out_h = const_cast<char*>(g.hcur);
+  }
+  if (epoch_io != nullptr) {
+    epoch_io[0] = ex.epoch;
+    epoch_io[1] = ex.ll_seq;
+  }
+  if (failed_layer >= 0) {
+    *fail_code = ex.fail_code;
+    return (failed_layer + 1) * 100 + ex.fail_step;
+  }
   return 0;
 }

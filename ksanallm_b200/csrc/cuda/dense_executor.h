@@ -38,8 +38,10 @@ struct KsanaDenseModel {
   int two_kernel_max_tokens;  // steps with at most this many tokens take the two-kernel path (0: never)
   // decode-sized steps: word-flagged single-kernel path (gemm_ll_fused.cu); ll_max_tokens 0 switches it off
   void* const* ll_recv;
-  void* const* ll_flags;
-  int ll_rows_cap, ll_max_tokens;
+  void* const* ll_recv2;
+  void* ll_recv2_mc;
+  long long ll_half_words;  // 8-byte words of one hop-1 buffer half (one-hop mode alternates between two halves)
+  int ll_rows_cap, ll_max_tokens, ll_one_shot;
   // scratch, all sized for max_tokens rows
   void* qkv_buf;   // [T, (h + 2 hk) d]
   void* attn_buf;  // [T, h d]
@@ -53,6 +55,7 @@ struct KsanaDenseModel {
   int n_counters;
   float* attn_ws;
   long long attn_ws_floats;
+  int sig_words;  // uint32 words of one flag region in `sig`; the second half-batch uses the region after the first
   const KsanaDenseLayer* layers;
 };
 
@@ -64,12 +67,20 @@ struct KsanaDenseStep {
   const int* kv_lens;
   int total_tokens, num_prefill, num_decode, max_blocks;
   int max_q_prefill, max_q_decode, max_kv_decode;
+  // Two-batch overlap (tensor parallel, prefill-sized steps): when split_seq > 0 the step's sequences [0, split_seq)
+  // (rows [0, split_row)) and [split_seq, n) (rows [split_row, total_tokens)) run as two independent half-batches on
+  // two streams, so the NVLink collectives of one half overlap the GEMMs and attention of the other. The halves
+  // hold different sequences, so they never read each other's rows or cache blocks. The maxima of the second half
+  // follow; the fields above then describe the first half.
+  int split_seq, split_row;
+  int num_prefill_b, num_decode_b, max_q_prefill_b, max_q_decode_b, max_kv_decode_b;
 };
 
 // h: normalised input of layer `first` ([T, H] bf16; for ws > 1 it may be any buffer), residual: [T, H] running
 // residual stream (updated in place; row-sharded across ranks when ws > 1). Runs layers [first, last). *epoch_io: the
 // last collective epoch used on the shared buffers (ws > 1); two more are consumed per layer (0 is skipped) and the
-// last one used is written back. *out_h receives the pointer of the normalised output
+// last one used is written back; epoch_io[1] counts the small-step calls (selects the buffer half) the same way.
+// *out_h receives the pointer of the normalised output
 // (one of the scratch buffers or this rank's hbuf). Returns 0, or (layer + 1) * 100 + step on failure with
 // *fail_code holding the failing call's code. Has no counterpart in the reference (its per-layer C++ forward is
 // CommonModel::LayerForward, src/ksana_llm/models/common/common_model.cpp).

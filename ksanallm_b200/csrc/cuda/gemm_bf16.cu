@@ -321,7 +321,12 @@ int gemm_bf16_cluster_splitk(const void* A, const void* W, void* C, const void* 
                              int ldw, int ldc, int out_fp32, int splits, cudaStream_t stream);
 int gemm_bf16_pair(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda, int ldw,
                    int ldc, int out_fp32, int bn, int epi, cudaStream_t stream);
+void gemm_pair_set_lane(int lane);
 }
+
+// GEMM launches of the calling thread that may overlap on the device (two streams) must use different lanes (0 / 1):
+// a lane owns its own parking space for partial tiles. Default lane 0.
+KSANA_API void ksana_gemm_set_lane(int lane) { ksana::gemm_pair_set_lane(lane); }
 
 static unsigned long long* g_gemm_trace = nullptr;
 // Debug aid: device buffer of 8 uint64 that receives the timeline of CTA 0 of subsequent GEMM launches (nullptr: off).

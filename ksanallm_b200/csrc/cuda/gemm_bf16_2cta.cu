@@ -389,13 +389,16 @@ struct PairScratch {
   uint32_t* flags = nullptr;
   uint32_t seq = 0;
 };
-static PairScratch g_pair_scratch[64];
+static PairScratch g_pair_scratch[64][2];
+// Which of the two scratch sets the calling thread's next launches use: launches that may run at the same time (two
+// streams of one device) must not share parked partials and flags.
+static thread_local int g_pair_lane = 0;
 
 static PairScratch* pair_scratch(int pairs) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return nullptr;
-  PairScratch* s = &g_pair_scratch[dev];
+  PairScratch* s = &g_pair_scratch[dev][g_pair_lane & 1];
   if (s->part == nullptr) {
     const size_t bytes = static_cast<size_t>(128) * 2 * P_BM * 256 * sizeof(float);  // up to 128 pairs
     if (cudaMalloc(&s->part, bytes) != cudaSuccess) return nullptr;
@@ -447,6 +450,8 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
     return -5;
   return 0;
 }
+
+void gemm_pair_set_lane(int lane) { g_pair_lane = lane & 1; }
 
 // epi 0: plain (+ bias); epi 1: gated SiLU over 16-row interleaved W (C is [M, N / 2], N % 32 == 0).
 // bn: 128 or 256. Same argument rules as ksana_gemm_bf16.

@@ -131,7 +131,6 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
   } else {
     const int quarter = warp & 3;
     const int et = threadIdx.x - 64;  // 0..127
-    const int rows_slice = CS_BM / splits;
     int it = 0;
     for (int tile = cluster_id; tile < total_tiles; tile += num_clusters, ++it) {
       const int m_idx = tile % tiles_m, n_idx = tile / tiles_m;
@@ -153,16 +152,19 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
       // 1. my fp32 partial tile -> my shared memory (row per thread)
       const int trow = quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * CS_BN;
-#pragma unroll 1
-      for (int c = 0; c < CS_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_row + c * 32, r);
-        tmem_wait_ld();
+      const int rows_valid = min(CS_BM, M - m_idx * CS_BM);  // rows of this tile that exist in the matrix
+      if (quarter * 32 < rows_valid) {
+#pragma unroll 2
+        for (int c = 0; c < CS_BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(stg + trow * CS_PITCH + c * 32 + j) =
-              make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                          __uint_as_float(r[j + 3]));
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(stg + trow * CS_PITCH + c * 32 + j) =
+                make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                            __uint_as_float(r[j + 3]));
+        }
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[as]);
@@ -180,37 +182,54 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
           : "r"(ok_in)
           : "memory");
       if (!ok_all) break;
-      // 4. reduce my slice of rows over all CTAs, in rank order (deterministic), and write the final rows
+      // 4. reduce my slice of the tile's rows over all CTAs, in rank order (deterministic), and write the final rows
       const uint32_t stg_addr = smem_u32(stg);
-#pragma unroll 4
-      for (int i = et; i < rows_slice * (CS_BN / 4); i += 128) {
-        const int lr = split * rows_slice + i / (CS_BN / 4);
-        const int c4 = (i % (CS_BN / 4)) * 4;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int p = 0; p < splits; ++p) {
-          const float4 v = ld_cluster_f4(mapa_u32(stg_addr + (lr * CS_PITCH + c4) * 4, p));
-          acc.x += v.x;
-          acc.y += v.y;
-          acc.z += v.z;
-          acc.w += v.w;
-        }
-        const int row = m_idx * CS_BM + lr;
-        const int col = n_idx * CS_BN + c4;
-        if (row < M && col < N) {
-          if (bias != nullptr) {
-            acc.x += __bfloat162float(bias[col]);
-            acc.y += __bfloat162float(bias[col + 1]);
-            acc.z += __bfloat162float(bias[col + 2]);
-            acc.w += __bfloat162float(bias[col + 3]);
+      const int rows_slice = (rows_valid + splits - 1) / splits;
+      const int r0 = split * rows_slice;
+      const int n_items = max(min(rows_valid, r0 + rows_slice) - r0, 0) * (CS_BN / 4);
+      for (int i0 = et; i0 < n_items; i0 += 128 * 4) {
+        float4 acc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          if (p < splits) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i = i0 + u * 128;
+              if (i < n_items) {
+                const int lr = r0 + i / (CS_BN / 4), c4 = (i % (CS_BN / 4)) * 4;
+                const float4 v = ld_cluster_f4(mapa_u32(stg_addr + (lr * CS_PITCH + c4) * 4, p));
+                acc[u].x += v.x;
+                acc[u].y += v.y;
+                acc[u].z += v.z;
+                acc[u].w += v.w;
+              }
+            }
           }
-          OutT* dst = C + static_cast<size_t>(row) * ldc + col;
-          if constexpr (sizeof(OutT) == 2) {
-            uint2 o;
-            o.x = pack_bf16(acc.x, acc.y);
-            o.y = pack_bf16(acc.z, acc.w);
-            *reinterpret_cast<uint2*>(dst) = o;
-          } else {
-            *reinterpret_cast<float4*>(dst) = acc;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 128;
+          const int lr = r0 + i / (CS_BN / 4), c4 = (i % (CS_BN / 4)) * 4;
+          const int row = m_idx * CS_BM + lr, col = n_idx * CS_BN + c4;
+          if (i < n_items && col < N) {
+            float4 a = acc[u];
+            if (bias != nullptr) {
+              a.x += __bfloat162float(bias[col]);
+              a.y += __bfloat162float(bias[col + 1]);
+              a.z += __bfloat162float(bias[col + 2]);
+              a.w += __bfloat162float(bias[col + 3]);
+            }
+            OutT* dst = C + static_cast<size_t>(row) * ldc + col;
+            if constexpr (sizeof(OutT) == 2) {
+              uint2 o;
+              o.x = pack_bf16(a.x, a.y);
+              o.y = pack_bf16(a.z, a.w);
+              *reinterpret_cast<uint2*>(dst) = o;
+            } else {
+              *reinterpret_cast<float4*>(dst) = a;
+            }
           }
         }
       }

@@ -29,16 +29,18 @@ class _Model(ctypes.Structure):
                 ("eps", F), ("rotary_dim", I), ("rope_interleaved", I), ("block_size", I), ("num_blocks", I),
                 ("kv_kind", I), ("attn_scale", F), ("k_scale", F), ("v_scale", F), ("rope_cache", P),
                 ("rank", I), ("ws", I), ("rows_cap", I), ("comm_ctas", I), ("recv", P), ("hbuf", P), ("sig", P),
-                ("hbuf_mc", P), ("partial", P), ("partial_mc", P), ("two_kernel_max_tokens", I), ("ll_recv", P), ("ll_flags", P),
-                ("ll_rows_cap", I), ("ll_max_tokens", I), ("qkv_buf", P), ("attn_buf", P), ("gu_buf", P), ("act_buf", P), ("proj_buf", P),
+                ("hbuf_mc", P), ("partial", P), ("partial_mc", P), ("two_kernel_max_tokens", I), ("ll_recv", P), ("ll_recv2", P),
+                ("ll_recv2_mc", P), ("ll_half_words", LL), ("ll_rows_cap", I), ("ll_max_tokens", I),
+                ("ll_one_shot", I), ("qkv_buf", P), ("attn_buf", P), ("gu_buf", P), ("act_buf", P), ("proj_buf", P),
                 ("h_buf", P * 2), ("gemm_ws", P), ("gemm_ws_floats", LL), ("gemm_counters", P), ("n_counters", I),
-                ("attn_ws", P), ("attn_ws_floats", LL), ("layers", P)]
+                ("attn_ws", P), ("attn_ws_floats", LL), ("sig_words", I), ("layers", P)]
 
 
 class _Step(ctypes.Structure):
     _fields_ = [("positions", P), ("slot_mapping", P), ("block_tables", P), ("cu_q", P), ("kv_lens", P),
                 ("total_tokens", I), ("num_prefill", I), ("num_decode", I), ("max_blocks", I), ("max_q_prefill", I),
-                ("max_q_decode", I), ("max_kv_decode", I)]
+                ("max_q_decode", I), ("max_kv_decode", I), ("split_seq", I), ("split_row", I), ("num_prefill_b", I),
+                ("num_decode_b", I), ("max_q_prefill_b", I), ("max_q_decode_b", I), ("max_kv_decode_b", I)]
 
 
 def _p(t: Optional[torch.Tensor]):
@@ -116,9 +118,12 @@ class DenseExecutor:
             m.partial = ctypes.cast(fc._partial_ptrs, P)
             m.partial_mc = fc.partial_mc or None
             m.two_kernel_max_tokens = fc.two_kernel_max_tokens
+            m.sig_words = fc.sig_words
             m.ll_recv = ctypes.cast(fc._ll_recv_ptrs, P)
-            m.ll_flags = ctypes.cast(fc._ll_flag_ptrs, P)
-            m.ll_rows_cap, m.ll_max_tokens = fc.ll_rows_cap, fc.ll_max_tokens
+            m.ll_recv2 = ctypes.cast(fc._ll_recv2_ptrs, P)
+            m.ll_recv2_mc = fc.ll_recv2_mc or None
+            m.ll_half_words = fc.ll_half_words
+            m.ll_rows_cap, m.ll_max_tokens, m.ll_one_shot = fc.ll_rows_cap, fc.ll_max_tokens, int(fc.ll_one_shot)
         ws = kcuda.workspace(model.device)
         self._ws = ws
         m.gemm_ws, m.gemm_ws_floats = _p(ws.gemm_ws), ws.gemm_ws.numel()
@@ -126,6 +131,7 @@ class DenseExecutor:
         m.attn_ws, m.attn_ws_floats = _p(ws.attn_ws), ws.attn_ws.numel()
         m.layers = ctypes.cast(self._layers, P)
         self.cap = 0
+        self.overlap_min_tokens = int(os.environ.get("KSANA_OVERLAP_MIN_TOKENS", "1024"))
         self._bufs: List[torch.Tensor] = []
         self._kv_key = None
         self._step = _Step()
@@ -157,7 +163,9 @@ class DenseExecutor:
         self.cap = cap
 
     def _bind_kv(self, kv_caches) -> None:
-        key = (kv_caches[0].data_ptr(), len(kv_caches))
+        # every layer's pointer is part of the key: a new cache (a second engine on the same model) may start at the
+        # address the old one had while its other layers, or its block count, differ
+        key = tuple(c.data_ptr() for c in kv_caches) + tuple(kv_caches[0].shape)
         if key == self._kv_key:
             return
         for i in range(len(self.model.layers)):
@@ -181,6 +189,18 @@ class DenseExecutor:
             return T <= min(8192, fc.max_tokens)
         return True
 
+    def _overlap_split(self, cu, n_seq: int, T: int) -> int:
+        """Sequence index at which a prefill-sized tensor-parallel step is cut into two half-batches that run on two
+        streams (the collectives of one half overlap the compute of the other); 0: run the step as one batch."""
+        fc = self.tp.fused if self.tp.size > 1 else None
+        if fc is None or n_seq < 2 or T < self.overlap_min_tokens or fc.partial is None:
+            return 0
+        split = int(np.abs(cu[1:n_seq] - T // 2).argmin()) + 1
+        rows_a = int(cu[split])
+        if min(rows_a, T - rows_a) < max(256, T // 4):
+            return 0
+        return split
+
     def forward(self, meta, kv_caches, h: torch.Tensor, residual: torch.Tensor, n_layers: int) -> torch.Tensor:
         """h: normalised input of layer 0, residual: the residual stream (both [T, H], contiguous); returns the
         normalised output of layer ``n_layers - 1`` (a view of an internal buffer, valid until the next call)."""
@@ -193,24 +213,37 @@ class DenseExecutor:
         n_pre, n_dec = meta.num_prefill, meta.num_decode
         s.total_tokens, s.num_prefill, s.num_decode, s.max_blocks = T, n_pre, n_dec, meta.max_blocks
         cu, kl = meta.cu_q_host, meta.kv_lens_host
-        s.max_q_prefill = int((cu[1:n_pre + 1] - cu[:n_pre]).max()) if n_pre else 0
-        if n_dec:
-            s.max_q_decode = int((cu[n_pre + 1:n_pre + n_dec + 1] - cu[n_pre:n_pre + n_dec]).max())
-            s.max_kv_decode = int(kl[n_pre:n_pre + n_dec].max())
-        else:
-            s.max_q_decode = s.max_kv_decode = 0
+
+        def maxima(lo, hi):
+            """(prefill count, decode count, max q prefill, max q decode, max kv decode) of sequences [lo, hi)."""
+            p_hi = min(hi, n_pre)
+            q = cu[lo + 1:hi + 1] - cu[lo:hi]
+            n_p, n_d = max(p_hi - lo, 0), hi - max(lo, n_pre)
+            mq_p = int(q[:n_p].max()) if n_p > 0 else 0
+            mq_d = int(q[n_p:].max()) if n_d > 0 else 0
+            mkv = int(kl[max(lo, n_pre):hi].max()) if n_d > 0 else 0
+            return n_p, max(n_d, 0), mq_p, mq_d, mkv
+
+        n_seq = n_pre + n_dec
+        split = self._overlap_split(cu, n_seq, T)
+        s.split_seq, s.split_row = split, int(cu[split]) if split else 0
+        s.num_prefill, s.num_decode, s.max_q_prefill, s.max_q_decode, s.max_kv_decode = maxima(0, split or n_seq)
+        if split:
+            (s.num_prefill_b, s.num_decode_b, s.max_q_prefill_b, s.max_q_decode_b,
+             s.max_kv_decode_b) = maxima(split, n_seq)
         fc = self.tp.fused if self.tp.size > 1 else None
-        epoch = ctypes.c_uint(0)
+        epoch = (ctypes.c_uint * 2)(0, 0)
         if fc is not None:
-            epoch.value = fc.epoch & 0xFFFFFFFF
+            epoch[0], epoch[1] = fc.epoch & 0xFFFFFFFF, fc.ll_seq & 0xFFFFFFFF
             self._m.two_kernel_max_tokens = fc.two_kernel_max_tokens
             self._m.ll_max_tokens = fc.ll_max_tokens
         rc = self._fn(ctypes.byref(self._m), ctypes.byref(s), h.data_ptr(), residual.data_ptr(), 0, n_layers,
-                      ctypes.byref(epoch), ctypes.byref(self._out), ctypes.byref(self._fail),
+                      epoch, ctypes.byref(self._out), ctypes.byref(self._fail),
                       ctypes.byref(self._launches), torch.cuda.current_stream().cuda_stream)
         kcuda.launch_count += self._launches.value
         if fc is not None:
-            fc.epoch = epoch.value  # every collective of the stack took its epoch from the shared counter
+            # every collective of the stack took its epoch (and buffer half) from the shared counters
+            fc.epoch, fc.ll_seq = epoch[0], epoch[1]
         if rc != 0:
             raise RuntimeError(f"native dense forward failed at layer {rc // 100 - 1}, step {rc % 100}, "
                                f"code {self._fail.value}")

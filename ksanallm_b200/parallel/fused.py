@@ -6,7 +6,7 @@ mapped into every peer's address space, plus an NVLS multicast mapping when the 
 * ``partial``  [max_tokens, H] bf16 - where this rank's row-parallel GEMM writes its un-reduced output,
 * ``hbuf``     [max_tokens, H] bf16 - where the owners of each row deposit the reduced + normalised activations,
 * ``sig``      uint32 flag words for the epoch-stamped cross-rank barriers,
-* ``ll_recv``  8-byte words {2 x bf16, epoch} and ``ll_flags`` row flags of the latency-optimised small-step kernel.
+* ``ll_recv`` / ``ll_recv2``  8-byte words {2 x bf16, epoch} of the two hops of the latency-optimised small-step kernel.
 
 The kernels (csrc/cuda/comm_fused.cu) issue the NVLink traffic themselves (``multimem.ld_reduce`` / ``multimem.st``
 or plain peer loads/stores); NCCL is only the bootstrap and the measured baseline. Reference counterparts:
@@ -35,7 +35,8 @@ class FusedComm:
         gname = group.group_name if hasattr(group, "group_name") else group
         self.partial = symm_mem.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
         self.hbuf = symm_mem.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
-        self.sig = symm_mem.empty(8192, dtype=torch.int32, device=device)
+        self.sig_words = 8192  # one flag region; a second one serves the other half-batch of an overlapped step
+        self.sig = symm_mem.empty(2 * self.sig_words, dtype=torch.int32, device=device)
         self.rows_cap = (max_tokens + size - 1) // size
         self.recv = symm_mem.empty(size * self.rows_cap, hidden, dtype=torch.bfloat16, device=device)
         self.agbuf = symm_mem.empty(self.rows_cap, hidden, dtype=torch.bfloat16, device=device)
@@ -45,11 +46,19 @@ class FusedComm:
         self.ll_max_tokens = int(os.environ.get("KSANA_LL_MAX_TOKENS", "256"))
         if hidden % 128 or hidden > 8192:
             self.ll_max_tokens = 0
-        self.ll_rows_cap = (max(self.ll_max_tokens, 1) + size - 1) // size
-        self.ll_recv = symm_mem.empty(size * self.ll_rows_cap * (hidden // 2) * 2, dtype=torch.int32, device=device)
-        self.ll_flags = symm_mem.empty(max(self.ll_max_tokens, 64), dtype=torch.int32, device=device)
+        # two ranks: one hop (both ranks receive and reduce every row; the word buffer has two halves used in turn);
+        # more ranks: reduce-scatter words to the row owners, then the owners' rows as words to everybody
+        self.ll_one_shot = size == 2
+        cap = max(self.ll_max_tokens, 1)
+        self.ll_rows_cap = cap if self.ll_one_shot else (cap + size - 1) // size
+        self.ll_half_words = size * self.ll_rows_cap * (hidden // 2)  # 8-byte words of one hop-1 buffer
+        halves = 2 if self.ll_one_shot else 1
+        self.ll_recv = symm_mem.empty(halves * self.ll_half_words * 2, dtype=torch.int32, device=device)
+        self.ll_recv2 = symm_mem.empty(max(1 if self.ll_one_shot else cap * (hidden // 2), 64) * 2, dtype=torch.int32,
+                                       device=device)
         self.ll_recv.zero_()
-        self.ll_flags.zero_()
+        self.ll_recv2.zero_()
+        self.ll_seq = 0
         self.agbuf.zero_()
         self.agflags.zero_()
         self.recv.zero_()
@@ -64,7 +73,7 @@ class FusedComm:
         self._h_agbuf = symm_mem.rendezvous(self.agbuf, gname)
         self._h_agflags = symm_mem.rendezvous(self.agflags, gname)
         self._h_ll_recv = symm_mem.rendezvous(self.ll_recv, gname)
-        self._h_ll_flags = symm_mem.rendezvous(self.ll_flags, gname)
+        self._h_ll_recv2 = symm_mem.rendezvous(self.ll_recv2, gname)
         if use_multicast is None:
             use_multicast = os.environ.get("KSANA_DISABLE_MULTIMEM", "0") != "1"
         mc_ok = bool(use_multicast)
@@ -80,7 +89,8 @@ class FusedComm:
         self._agbuf_ptrs = arr(*[int(p) for p in self._h_agbuf.buffer_ptrs])
         self._agflag_ptrs = arr(*[int(p) for p in self._h_agflags.buffer_ptrs])
         self._ll_recv_ptrs = arr(*[int(p) for p in self._h_ll_recv.buffer_ptrs])
-        self._ll_flag_ptrs = arr(*[int(p) for p in self._h_ll_flags.buffer_ptrs])
+        self._ll_recv2_ptrs = arr(*[int(p) for p in self._h_ll_recv2.buffer_ptrs])
+        self.ll_recv2_mc = int(self._h_ll_recv2.multicast_ptr) if mc_ok and self._h_ll_recv2.multicast_ptr else 0
         self.ag_epoch = 0
         self.single_kernel = os.environ.get("KSANA_DISABLE_FUSED_GEMM_RS", "0") != "1"
         self.comm_ctas = int(os.environ.get("KSANA_FUSED_COMM_CTAS", "16"))
@@ -104,10 +114,12 @@ class FusedComm:
                                               ctypes.c_void_p]
         lib.ksana_gemm_rs_norm_ag.restype = ctypes.c_int
         P, I = ctypes.c_void_p, ctypes.c_int
-        lib.ksana_gemm_ll_reduce_norm.argtypes = [P, P, I, I, I, I, I, I, I, P, P, P, P, I, P, P, ctypes.c_float,
+        LL = ctypes.c_longlong
+        lib.ksana_gemm_ll_reduce_norm.argtypes = [P, P, I, I, I, I, I, I, I, P, LL, P, P, P, I, I, P, P, ctypes.c_float,
                                                   ctypes.c_uint, I, I, P]
         lib.ksana_gemm_ll_reduce_norm.restype = I
-        lib.ksana_ll_reduce_norm.argtypes = [P, I, I, I, I, I, P, P, P, P, I, P, P, ctypes.c_float, ctypes.c_uint, I, P]
+        lib.ksana_ll_reduce_norm.argtypes = [P, I, I, I, I, I, P, LL, P, P, P, I, I, P, P, ctypes.c_float, ctypes.c_uint,
+                                             I, P]
         lib.ksana_ll_reduce_norm.restype = I
         lib.ksana_ag_wait_readers.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_uint,
                                               ctypes.c_void_p]
@@ -144,6 +156,11 @@ class FusedComm:
             self.epoch += 1
         return self.epoch & 0xFFFFFFFF
 
+    def _ll_recv_off(self) -> int:
+        """Word offset of the hop-1 buffer half for the next small-step call (alternates with one hop)."""
+        self.ll_seq += 1
+        return (self.ll_seq & 1) * self.ll_half_words if self.ll_one_shot else 0
+
     # ---- kernels ------------------------------------------------------------------------------------------------
     def _launch_ll(self, y: torch.Tensor, residual, norm_w, eps: float) -> torch.Tensor:
         """Reduce (+ residual + norm) + gather of a partial sum in memory through the small-step kernel."""
@@ -152,9 +169,9 @@ class FusedComm:
             y = y.contiguous()
         mode = (1 if norm_w is not None else 0) | (2 if residual is not None else 0)
         code = self._lib.ksana_ll_reduce_norm(
-            y.data_ptr(), y.stride(0), T, self.hidden, self.rank, self.size, self._ll_recv_ptrs, self._hbuf_ptrs,
-            self._ll_flag_ptrs, self.hbuf_mc or None, self.ll_rows_cap,
-            residual.data_ptr() if residual is not None else None,
+            y.data_ptr(), y.stride(0), T, self.hidden, self.rank, self.size, self._ll_recv_ptrs, self._ll_recv_off(),
+            self._ll_recv2_ptrs, self.ll_recv2_mc or None, self.hbuf.data_ptr(), self.ll_rows_cap,
+            1 if self.ll_one_shot else 0, residual.data_ptr() if residual is not None else None,
             norm_w.data_ptr() if norm_w is not None else None, float(eps), self.next_epoch(), mode,
             torch.cuda.current_stream().cuda_stream)
         kcuda._check(code, "ll_reduce_norm")
@@ -170,7 +187,8 @@ class FusedComm:
         mode = (1 if norm_w is not None else 0) | (2 if residual is not None else 0)
         code = self._lib.ksana_gemm_ll_reduce_norm(
             x.data_ptr(), weight.data_ptr(), T, self.hidden, K, x.stride(0), weight.stride(0), self.rank, self.size,
-            self._ll_recv_ptrs, self._hbuf_ptrs, self._ll_flag_ptrs, self.hbuf_mc or None, self.ll_rows_cap,
+            self._ll_recv_ptrs, self._ll_recv_off(), self._ll_recv2_ptrs, self.ll_recv2_mc or None,
+            self.hbuf.data_ptr(), self.ll_rows_cap, 1 if self.ll_one_shot else 0,
             residual.data_ptr() if residual is not None else None,
             norm_w.data_ptr() if norm_w is not None else None, float(eps), self.next_epoch(), mode, 0,
             torch.cuda.current_stream().cuda_stream)

@@ -32,7 +32,7 @@ def _worker(rank, world, port, use_mc, q):
     tp = init_distributed("cuda")
     dev = tp.device
     H = 1024
-    tp.init_fused(H, 512, use_multicast=use_mc)
+    tp.init_fused(H, 2048, use_multicast=use_mc)
     fc = tp.fused
     report = {"multicast": fc.multicast}
     errs = []
@@ -129,7 +129,7 @@ def _worker(rank, world, port, use_mc, q):
                                       num_key_value_heads=8, intermediate_size=2816, vocab_size=1000,
                                       torch_dtype="bfloat16"))
     w_tp = load_model_weights(cfg, synthetic_seed=3, tp_rank=rank, tp_size=world, device=dev, dtype=torch.bfloat16)
-    m_tp = TransformerModel(cfg, w_tp, tp, max_positions=512)
+    m_tp = TransformerModel(cfg, w_tp, tp, max_positions=2048)
     T = 40
     ids = list(range(5, 5 + T))
     meta = make_step_input(ids, list(range(T)), list(range(T)), [0, T], [T], [[0, 1, 2, 3]], device=dev)
@@ -147,14 +147,46 @@ def _worker(rank, world, port, use_mc, q):
         alt = max(alt, (h_alt.float() - h_tp.float()).abs().max().item())
     fc.two_kernel_max_tokens, fc.ll_max_tokens = old, old_ll
     report["alt_err"] = alt
+    # prefill-sized step of three sequences + two decode sequences: two half-batches on two streams (the collectives of
+    # one half overlap the compute of the other) against the same step run as one batch
+    lens = [500, 420, 380]
+    ids2, pos2, slots2, cu2, kvl2, bt2 = [], [], [], [0], [], []
+    blk = 0
+    for n in lens + [1, 1]:
+        ctx = n if n > 1 else 33  # the decode sequences own 32 cached tokens (zeros) + the new one
+        nb = (ctx + 15) // 16
+        row = list(range(blk, blk + nb))
+        first = ctx - n
+        ids2 += [7 + (i * 13 + n) % 900 for i in range(n)]
+        pos2 += list(range(first, ctx))
+        slots2 += [row[p // 16] * 16 + p % 16 for p in range(first, ctx)]
+        cu2.append(cu2[-1] + n)
+        kvl2.append(ctx)
+        bt2.append(row + [0] * (40 - nb))
+        blk += nb
+    meta2 = make_step_input(ids2, pos2, slots2, cu2, kvl2, bt2, num_prefill=3, device=dev)
+    ex = m_tp._native_executor()
+    h_ov = m_tp.forward(meta2, m_tp.allocate_kv_cache(blk + 1, 16)).clone()
+    torch.cuda.synchronize()
+    report["overlap_split"] = int(ex._step.split_seq)
+    keep = ex.overlap_min_tokens
+    ex.overlap_min_tokens = 1 << 30
+    h_one = m_tp.forward(meta2, m_tp.allocate_kv_cache(blk + 1, 16)).clone()
+    ex.overlap_min_tokens = keep
+    torch.cuda.synchronize()
+    report["overlap_err"] = (h_ov.float() - h_one.float()).abs().max().item()
     if rank == 0:
         w_1 = load_model_weights(cfg, synthetic_seed=3, device=dev, dtype=torch.bfloat16)
-        m_1 = TransformerModel(cfg, w_1, TPGroup(), max_positions=512)
+        m_1 = TransformerModel(cfg, w_1, TPGroup(), max_positions=2048)
         kv1 = m_1.allocate_kv_cache(8, 16)
         h_1 = m_1.forward(meta, kv1)
         torch.cuda.synchronize()
         report["model_err"] = (h_tp.float() - h_1.float()).abs().max().item()
         report["model_ref_max"] = h_1.float().abs().max().item()
+        h_1b = m_1.forward(meta2, m_1.allocate_kv_cache(blk + 1, 16))
+        torch.cuda.synchronize()
+        report["overlap_model_err"] = (h_ov.float() - h_1b.float()).abs().max().item()
+        report["overlap_ref_max"] = h_1b.float().abs().max().item()
     dist.barrier()
     report["kernel_error2"] = cuda.read_error()
     if rank == 0:
@@ -208,3 +240,6 @@ def test_fused_reduce_norm_ranks(use_mc, world):
     assert rep["native"]
     assert rep["alt_err"] < 0.05 * max(1.0, rep["model_ref_max"])
     assert rep["model_err"] < 0.05 * max(1.0, rep["model_ref_max"])
+    assert rep["overlap_split"] > 0, "the prefill-sized step did not take the two-stream path"
+    assert rep["overlap_err"] < 0.05 * max(1.0, rep["overlap_ref_max"])
+    assert rep["overlap_model_err"] < 0.05 * max(1.0, rep["overlap_ref_max"])

@@ -68,3 +68,28 @@ def test_native_declines_unsupported():
     m = _build("llama", num_hidden_layers=1, hidden_size=512, num_attention_heads=8, num_key_value_heads=8,
                intermediate_size=1024)  # head_dim 64
     assert m._native_executor() is None
+
+
+def test_native_rebinds_a_new_cache_at_the_old_address():
+    """A second KV cache (a new engine on the same model) may start where the freed one started while its other
+    layers sit elsewhere: the executor must not keep the old layer pointers."""
+    m = _build("llama")
+    meta, nblocks = _mixed_meta()
+    kv_1 = m.allocate_kv_cache(nblocks + 1, 16)
+    m.forward(meta, kv_1)
+    torch.cuda.synchronize()
+    first_ptr = kv_1[0].data_ptr()
+    del kv_1
+    # same first layer tensor size (the allocator hands the block back), other layers allocated after a spacer
+    kv_2 = [torch.zeros(nblocks + 1, 2, 4, 16, 128, dtype=torch.bfloat16, device="cuda")]
+    spacer = torch.zeros(3 << 20, dtype=torch.uint8, device="cuda")
+    kv_2 += [torch.zeros(nblocks + 1, 2, 4, 16, 128, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    kv_3 = [c.clone() for c in kv_2]
+    out_native = m.forward(meta, kv_2).clone()
+    m._native = None
+    out_python = m.forward(meta, kv_3).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(out_native, out_python)
+    for a, b in zip(kv_2, kv_3):
+        assert torch.equal(a, b)
+    del spacer, first_ptr
