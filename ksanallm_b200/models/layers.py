@@ -349,7 +349,12 @@ class MoEFFN:
             ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
                                      c.topk_group, c.routed_scaling_factor, self.bias)
             ids = self._place(ids)
-            if self.s_gate_up is not None or self.q4 is not None:
+            if self.s_gate_up is not None and self._grouped_fp8(h):
+                # block-scaled fp8 experts: device-side sort + grouped fp8 tcgen05 GEMMs, no host round trip
+                from ..ops import cuda_moe
+                y = cuda_moe.moe_experts_fp8(h, ids, wts, self.w_gate_up, self.s_gate_up, self.w_down, self.s_down,
+                                             self.expert_offset)
+            elif self.s_gate_up is not None or self.q4 is not None:
                 y = self._fp8_experts(h, ids, wts)
             else:
                 y = ops.moe_experts(h, ids, wts, self.w_gate_up, self.w_down, self.expert_offset)
@@ -360,6 +365,14 @@ class MoEFFN:
                 s = s * g
             y = y + s
         return y
+
+    def _grouped_fp8(self, h: torch.Tensor) -> bool:
+        ok = getattr(self, "_grouped_fp8_ok", None)
+        if ok is None:
+            from ..ops import cuda_moe
+            ok = self._grouped_fp8_ok = bool(h.is_cuda and self.q4 is None and cuda_moe.supports_fp8(
+                h, self.w_gate_up, self.s_gate_up, self.w_down, self.s_down))
+        return ok and h.is_cuda and h.dtype == torch.bfloat16
 
     def _place(self, ids: torch.Tensor) -> torch.Tensor:
         """Router output (logical expert ids) -> the ids the expert kernels and the exchange work with. Counts the

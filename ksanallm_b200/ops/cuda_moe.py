@@ -83,3 +83,72 @@ def moe_experts(x, ids, weights, w_gate_up, w_down, expert_offset=0):
     cuda._check(cuda.lib().ksana_moe_combine(cuda._ptr(y), cuda._ptr(pos), cuda._ptr(wc), T, k, H, cuda._ptr(out),
                                              cuda._stream()), "moe_combine")
     return out
+
+
+def supports_fp8(x, wq_gate_up, s_gate_up, wq_down, s_down) -> bool:
+    """Block-scaled fp8 experts the grouped kernel takes: e4m3 weights [E, 2I, H] / [E, H, I] with one scale per
+    128 x 128 block, H and I multiples of 128 (gate and up blocks then tile the fused matrix exactly)."""
+    if wq_gate_up is None or s_gate_up is None or wq_gate_up.dtype != torch.float8_e4m3fn:
+        return False
+    E, two_i, H = wq_gate_up.shape
+    I_ = two_i // 2
+    return (x.dtype == torch.bfloat16 and H % 128 == 0 and I_ % 128 == 0 and wq_gate_up.is_contiguous() and
+            wq_down.is_contiguous() and tuple(s_gate_up.shape) == (E, two_i // 128, H // 128) and
+            tuple(s_down.shape) == (E, H // 128, I_ // 128))
+
+
+def expert_pipeline_fp8(x, ids, wq_gate_up, s_gate_up, wq_down, s_down, expert_offset=0):
+    """The expert pipeline for block-scaled fp8 weights, entirely on the device: sort the (token, slot) pairs by
+    local expert, quantise the gathered rows per token per 128 channels, grouped fp8 GEMM (gate_up), fused
+    SiLU * mul + re-quantisation, grouped fp8 GEMM (down). Returns (y [T*k, H] bf16, pos [T*k])."""
+    from . import cuda
+    T, H = x.shape
+    k = ids.shape[1]
+    E_local, two_i, _ = wq_gate_up.shape
+    I_ = two_i // 2
+    dev = x.device
+    key = (dev.index, E_local)
+    meta = _meta.get(key)
+    if meta is None:
+        meta = _meta[key] = torch.zeros(3 * E_local + 2, dtype=torch.int32, device=dev)
+    n = T * k
+    pos = torch.empty(n, dtype=torch.int32, device=dev)
+    row_src = torch.empty(n, dtype=torch.int32, device=dev)
+    xs = torch.empty(n, H, dtype=torch.bfloat16, device=dev)
+    lib = cuda.lib()
+    st = cuda._stream()
+    idc = ids if ids.is_contiguous() else ids.contiguous()
+    cuda._check(lib.ksana_moe_permute(cuda._ptr(x), x.stride(0), cuda._ptr(idc), T, k, H, expert_offset, E_local,
+                                      cuda._ptr(meta), cuda._ptr(pos), cuda._ptr(row_src), cuda._ptr(xs), st),
+                "moe_permute")
+    offsets = meta[E_local:2 * E_local + 1]
+    xq, xsc = cuda.quant_fp8_group(xs)
+    h1 = torch.empty(n, two_i, dtype=torch.bfloat16, device=dev)
+    sg = s_gate_up if s_gate_up.is_contiguous() else s_gate_up.contiguous()
+    sd = s_down if s_down.is_contiguous() else s_down.contiguous()
+    cuda._check(lib.ksana_moe_grouped_gemm_fp8(cuda._ptr(xq), cuda._ptr(xsc), cuda._ptr(wq_gate_up), cuda._ptr(sg),
+                                               cuda._ptr(h1), cuda._ptr(offsets), E_local, n, two_i, H, st),
+                "moe_grouped_gemm_fp8(gate_up)")
+    aq = torch.empty(n, I_, dtype=torch.float8_e4m3fn, device=dev)
+    asc = torch.empty(n, I_ // 128, dtype=torch.float32, device=dev)
+    cuda._check(lib.ksana_silu_mul_quant_fp8(cuda._ptr(h1), two_i, cuda._ptr(aq), I_, cuda._ptr(asc), n, I_, st),
+                "silu_mul_quant_fp8")
+    y = torch.empty(n, H, dtype=torch.bfloat16, device=dev)
+    cuda._check(lib.ksana_moe_grouped_gemm_fp8(cuda._ptr(aq), cuda._ptr(asc), cuda._ptr(wq_down), cuda._ptr(sd),
+                                               cuda._ptr(y), cuda._ptr(offsets), E_local, n, H, I_, st),
+                "moe_grouped_gemm_fp8(down)")
+    cuda.launch_count += 8
+    return y, pos
+
+
+def moe_experts_fp8(x, ids, weights, wq_gate_up, s_gate_up, wq_down, s_down, expert_offset=0):
+    """x [T, H] bf16; ids / weights [T, k]; block-scaled e4m3 expert weights. No host synchronisation."""
+    from . import cuda
+    T, H = x.shape
+    k = ids.shape[1]
+    y, pos = expert_pipeline_fp8(x, ids, wq_gate_up, s_gate_up, wq_down, s_down, expert_offset)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    wc = weights if weights.dtype == torch.float32 and weights.is_contiguous() else weights.float().contiguous()
+    cuda._check(cuda.lib().ksana_moe_combine(cuda._ptr(y), cuda._ptr(pos), cuda._ptr(wc), T, k, H, cuda._ptr(out),
+                                             cuda._stream()), "moe_combine")
+    return out

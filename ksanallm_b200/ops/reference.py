@@ -422,6 +422,24 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     return out.to(x.dtype)
 
 
+def moe_experts_fp8(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, wq_gate_up: torch.Tensor,
+                    s_gate_up: torch.Tensor, wq_down: torch.Tensor, s_down: torch.Tensor,
+                    expert_offset: int = 0) -> torch.Tensor:
+    """``moe_experts`` for block-scaled e4m3 expert weights ([E_local, 2I, H] + scales [E_local, 2I/128, H/128],
+    [E_local, H, I] + [E_local, H/128, I/128]); activations are quantised per token per 128 channels before each GEMM."""
+    T, H = x.shape
+    E_local = wq_gate_up.shape[0]
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for e in range(E_local):
+        tok, slot = (ids == e + expert_offset).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        a = silu_and_mul(linear_fp8_block(x[tok], wq_gate_up[e], s_gate_up[e]))
+        y = linear_fp8_block(a, wq_down[e], s_down[e]).float()
+        out.index_add_(0, tok, y * weights[tok, slot].unsqueeze(-1))
+    return out.to(x.dtype)
+
+
 # ---- sampling ---------------------------------------------------------------------------------------
 
 def argmax(logits: torch.Tensor) -> torch.Tensor:
