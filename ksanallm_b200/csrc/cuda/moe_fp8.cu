@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1)
 moe_grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                             const float* __restrict__ sa, const float* __restrict__ sw,
                             __nv_bfloat16* __restrict__ C, const int* __restrict__ offsets, int E, int N, int K,
-                            int ldc, unsigned int* err) {
+                            int ldc, int sa_stride, unsigned int* err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + GF_BAR);
@@ -156,7 +156,7 @@ moe_grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     while (alive && it.get(&e, &mt, &nt)) {
       const int row = offsets[e] + mt * GF_BM + quarter * 32 + lane;
       const bool row_ok = row < offsets[e + 1];
-      const float* sa_row = sa + static_cast<size_t>(row_ok ? row : 0) * num_kb;
+      const float* sa_row = sa + static_cast<size_t>(row_ok ? row : 0) * sa_stride;
       const float* sw_row = sw + (static_cast<size_t>(e) * n_blocks + nt) * num_kb;
       float acc[64];
 #pragma unroll
@@ -250,21 +250,25 @@ __global__ void silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ x, int l
 using namespace ksana;
 
 // C[sorted rows, N] (bf16) = block-scaled A8[sorted rows, K] * W8[e]^T per expert.
-// A8: [max_rows, K] e4m3, sa: [max_rows, K / 128] fp32; W8: [E, N, K] e4m3 contiguous, sw: [E, ceil(N / 128), K / 128]
-// fp32; offsets: [E + 1] device ints (rows of expert e are [offsets[e], offsets[e + 1])). K % 128 == 0, N % 8 == 0.
-KSANA_API int ksana_moe_grouped_gemm_fp8(const void* A8, const float* sa, const void* W8, const float* sw, void* C,
-                                         const int* offsets, int E, int max_rows, int N, int K, cudaStream_t stream) {
+// A8: [max_rows, K] e4m3 with row pitch lda bytes (a multiple of 16), sa: fp32 scales, K / 128 per row, rows
+// sa_stride floats apart (rows that carry their scales behind their values pass lda = K + K / 32 and
+// sa = A8 + K); W8: [E, N, K] e4m3 contiguous, sw: [E, ceil(N / 128), K / 128] fp32; offsets: [E + 1] device ints
+// (rows of expert e are [offsets[e], offsets[e + 1])). K % 128 == 0, N % 8 == 0.
+KSANA_API int ksana_moe_grouped_gemm_fp8(const void* A8, int lda, const float* sa, int sa_stride, const void* W8,
+                                         const float* sw, void* C, const int* offsets, int E, int max_rows, int N,
+                                         int K, cudaStream_t stream) {
   if (max_rows <= 0) return 0;
-  if ((K & 127) || (N & 7)) return -1;
+  if ((K & 127) || (N & 7) || (lda & 15) || lda < K || sa_stride < K / 128) return -1;
   CUtensorMap tmA, tmB;
-  if (make_tmap_2d(&tmA, A8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, max_rows, K, K, GF_BM, GF_BK, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (make_tmap_2d(&tmA, A8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, max_rows, K, lda, GF_BM, GF_BK,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
   if (make_tmap_2d(&tmB, W8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, static_cast<uint64_t>(E) * N, K, K, GF_BN, GF_BK,
                    CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
   if (KSANA_SMEM_ONCE(moe_grouped_gemm_fp8_kernel, GF_SMEM) != 0) return -4;
   moe_grouped_gemm_fp8_kernel<<<sm_count(), GF_THREADS, GF_SMEM, stream>>>(
-      tmA, tmB, sa, sw, reinterpret_cast<__nv_bfloat16*>(C), offsets, E, N, K, N, error_word());
+      tmA, tmB, sa, sw, reinterpret_cast<__nv_bfloat16*>(C), offsets, E, N, K, N, sa_stride, error_word());
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

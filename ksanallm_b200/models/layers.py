@@ -330,13 +330,17 @@ class MoEFFN:
         c = self.cfg
         ep = self.tp.ep
         quantised = self.s_gate_up is not None or self.q4 is not None
-        if quantised:
+        # block-scaled fp8 experts go through the peer-memory exchange with rows quantised before they leave
+        fp8_ep = (quantised and ep is not None and hasattr(ep, "_moe_fp8") and self._grouped_fp8(h) and
+                  h.shape[1] % 512 == 0)
+        self._ep_kw = {"fp8_scales": (self.s_gate_up, self.s_down)} if fp8_ep else {}
+        if quantised and not fp8_ep:
             if self.tp.ep_dp and self.e_local < c.num_experts:
                 if not getattr(ep, "custom_experts", False):
-                    raise NotImplementedError("the peer-memory expert exchange runs bf16 experts only; quantised "
-                                              "experts under attention DP use the collective exchange")
+                    raise NotImplementedError("the peer-memory expert exchange runs bf16 and block-scaled fp8 experts; "
+                                              "other quantised experts under attention DP use the collective exchange")
             else:
-                ep = None  # (the dispatch / combine kernels of the TP + EP path take bf16 expert weights)
+                ep = None  # (int4 experts: local loop over the replicated tokens)
         if ep is not None and self.tp.ep_dp and self.e_local < c.num_experts:
             return self._dp_exchange(h, ep)
         if (ep is not None and h.is_cuda and h.dtype == torch.bfloat16 and self.e_local < c.num_experts and
@@ -440,8 +444,8 @@ class MoEFFN:
         ids, wts = ops.moe_route(logits, c.num_experts_per_tok, c.scoring_func, c.norm_topk_prob, c.n_group,
                                  c.topk_group, c.routed_scaling_factor, self.bias)
         ids = self._place(ids)
-        kw = {}
-        if self.s_gate_up is not None or self.q4 is not None:
+        kw = dict(getattr(self, "_ep_kw", {}))
+        if not kw and (self.s_gate_up is not None or self.q4 is not None):
             kw["experts_fn"] = self._fp8_experts  # quantised local experts over the gathered rows
         s = None
         if self.shared is not None and h.shape[0]:
@@ -476,7 +480,8 @@ class MoEFFN:
             if self.shared_gate is not None:
                 s = s * torch.sigmoid(ops.linear(h, self.shared_gate).float()).to(s.dtype)
             y = s
-        out = ep.moe(mine, ids, wts, self.w_gate_up, self.w_down, per, add=y[lo:hi] if hi > lo else None)
+        out = ep.moe(mine, ids, wts, self.w_gate_up, self.w_down, per, add=y[lo:hi] if hi > lo else None,
+                     **getattr(self, "_ep_kw", {}))
         if hi > lo:
             y[lo:hi] = out
         return y

@@ -47,7 +47,7 @@ class _Sig:
     ksana_moe_permute = ([P, I, P, I, I, I, I, I, P, P, P, P, P], I)
     ksana_moe_grouped_gemm = ([P, P, P, P, I, I, I, I, P], I)
     ksana_moe_combine = ([P, P, P, I, I, I, P, P], I)
-    ksana_moe_grouped_gemm_fp8 = ([P, P, P, P, P, P, I, I, I, I, P], I)
+    ksana_moe_grouped_gemm_fp8 = ([P, I, P, I, P, P, P, P, I, I, I, I, P], I)
     ksana_silu_mul_quant_fp8 = ([P, I, P, I, P, I, I, P], I)
     ksana_gemm_int4_small = ([P, P, P, P, P, I, I, I, I, I, I, P, LL, P, I, I, P], I)
     ksana_gemm_int4 = ([P, P, P, P, P, I, I, I, I, I, I, P, LL, P, I, P], I)

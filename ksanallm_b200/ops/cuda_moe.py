@@ -97,14 +97,29 @@ def supports_fp8(x, wq_gate_up, s_gate_up, wq_down, s_down) -> bool:
             tuple(s_down.shape) == (E, H // 128, I_ // 128))
 
 
-def expert_pipeline_fp8(x, ids, wq_gate_up, s_gate_up, wq_down, s_down, expert_offset=0):
-    """The expert pipeline for block-scaled fp8 weights, entirely on the device: sort the (token, slot) pairs by
-    local expert, quantise the gathered rows per token per 128 channels, grouped fp8 GEMM (gate_up), fused
-    SiLU * mul + re-quantisation, grouped fp8 GEMM (down). Returns (y [T*k, H] bf16, pos [T*k])."""
+def pack_fp8_rows(x: torch.Tensor) -> torch.Tensor:
+    """[T, H] bf16 -> [T, H + H / 32] bytes: the row's e4m3 values (one scale per 128 channels) followed by its fp32
+    scales. This is what travels between ranks under expert parallelism (about half the bytes of the bf16 row) and
+    what the grouped fp8 GEMM reads in place."""
     from . import cuda
     T, H = x.shape
+    q, s = cuda.quant_fp8_group(x if x.is_contiguous() else x.contiguous())
+    packed = torch.empty(T, H + H // 32, dtype=torch.uint8, device=x.device)
+    packed[:, :H] = q.view(torch.uint8)
+    packed[:, H:] = s.view(torch.uint8).view(T, H // 32)
+    return packed
+
+
+def expert_pipeline_fp8(x, ids, wq_gate_up, s_gate_up, wq_down, s_down, expert_offset=0, packed=False):
+    """The expert pipeline for block-scaled fp8 weights, entirely on the device: sort the (token, slot) pairs by
+    local expert, quantise the gathered rows per token per 128 channels, grouped fp8 GEMM (gate_up), fused
+    SiLU * mul + re-quantisation, grouped fp8 GEMM (down). Returns (y [T*k, H] bf16, pos [T*k]).
+    ``packed``: x already holds ``pack_fp8_rows`` rows ([T, (H + H / 32) / 2] viewed as bf16); they are sorted as
+    they are and the GEMM reads values and scales out of the sorted rows."""
+    from . import cuda
+    T = x.shape[0]
     k = ids.shape[1]
-    E_local, two_i, _ = wq_gate_up.shape
+    E_local, two_i, H = wq_gate_up.shape
     I_ = two_i // 2
     dev = x.device
     key = (dev.index, E_local)
@@ -112,21 +127,27 @@ def expert_pipeline_fp8(x, ids, wq_gate_up, s_gate_up, wq_down, s_down, expert_o
     if meta is None:
         meta = _meta[key] = torch.zeros(3 * E_local + 2, dtype=torch.int32, device=dev)
     n = T * k
+    W = x.shape[1]  # bf16 elements per row that the sort moves
     pos = torch.empty(n, dtype=torch.int32, device=dev)
     row_src = torch.empty(n, dtype=torch.int32, device=dev)
-    xs = torch.empty(n, H, dtype=torch.bfloat16, device=dev)
+    xs = torch.empty(n, W, dtype=torch.bfloat16, device=dev)
     lib = cuda.lib()
     st = cuda._stream()
     idc = ids if ids.is_contiguous() else ids.contiguous()
-    cuda._check(lib.ksana_moe_permute(cuda._ptr(x), x.stride(0), cuda._ptr(idc), T, k, H, expert_offset, E_local,
+    cuda._check(lib.ksana_moe_permute(cuda._ptr(x), x.stride(0), cuda._ptr(idc), T, k, W, expert_offset, E_local,
                                       cuda._ptr(meta), cuda._ptr(pos), cuda._ptr(row_src), cuda._ptr(xs), st),
                 "moe_permute")
     offsets = meta[E_local:2 * E_local + 1]
-    xq, xsc = cuda.quant_fp8_group(xs)
+    if packed:
+        assert W * 2 == H + H // 32
+        a_ptr, lda, sa_ptr, sa_stride = xs.data_ptr(), W * 2, xs.data_ptr() + H, W // 2
+    else:
+        xq, xsc = cuda.quant_fp8_group(xs)
+        a_ptr, lda, sa_ptr, sa_stride = xq.data_ptr(), H, xsc.data_ptr(), H // 128
     h1 = torch.empty(n, two_i, dtype=torch.bfloat16, device=dev)
     sg = s_gate_up if s_gate_up.is_contiguous() else s_gate_up.contiguous()
     sd = s_down if s_down.is_contiguous() else s_down.contiguous()
-    cuda._check(lib.ksana_moe_grouped_gemm_fp8(cuda._ptr(xq), cuda._ptr(xsc), cuda._ptr(wq_gate_up), cuda._ptr(sg),
+    cuda._check(lib.ksana_moe_grouped_gemm_fp8(a_ptr, lda, sa_ptr, sa_stride, cuda._ptr(wq_gate_up), cuda._ptr(sg),
                                                cuda._ptr(h1), cuda._ptr(offsets), E_local, n, two_i, H, st),
                 "moe_grouped_gemm_fp8(gate_up)")
     aq = torch.empty(n, I_, dtype=torch.float8_e4m3fn, device=dev)
@@ -134,8 +155,8 @@ def expert_pipeline_fp8(x, ids, wq_gate_up, s_gate_up, wq_down, s_down, expert_o
     cuda._check(lib.ksana_silu_mul_quant_fp8(cuda._ptr(h1), two_i, cuda._ptr(aq), I_, cuda._ptr(asc), n, I_, st),
                 "silu_mul_quant_fp8")
     y = torch.empty(n, H, dtype=torch.bfloat16, device=dev)
-    cuda._check(lib.ksana_moe_grouped_gemm_fp8(cuda._ptr(aq), cuda._ptr(asc), cuda._ptr(wq_down), cuda._ptr(sd),
-                                               cuda._ptr(y), cuda._ptr(offsets), E_local, n, H, I_, st),
+    cuda._check(lib.ksana_moe_grouped_gemm_fp8(cuda._ptr(aq), I_, cuda._ptr(asc), I_ // 128, cuda._ptr(wq_down),
+                                               cuda._ptr(sd), cuda._ptr(y), cuda._ptr(offsets), E_local, n, H, I_, st),
                 "moe_grouped_gemm_fp8(down)")
     cuda.launch_count += 8
     return y, pos

@@ -64,13 +64,19 @@ class EPExchange:
         return (ctypes.c_longlong * 5)(off_x, off_ret, off_ids, off_w, off_flags), (off_x, off_ret, off_ids, off_w)
 
     def moe(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
-            w_down: torch.Tensor, t_stride: int, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+            w_down: torch.Tensor, t_stride: int, add: Optional[torch.Tensor] = None, fp8_scales=None) -> torch.Tensor:
         """x [T_local, H] bf16 (this rank's tokens), ids / weights [T_local, k] with GLOBAL expert ids, expert
         weights of the rank's ``num_experts / size`` local experts. ``t_stride`` >= every rank's T_local and equal
-        on all ranks. Returns [T_local, H] = add + sum_k w_k * expert_k(x)."""
+        on all ranks. Returns [T_local, H] = add + sum_k w_k * expert_k(x).
+
+        ``fp8_scales`` = (gate_up scales, down scales) of block-scaled e4m3 expert weights: the token rows are then
+        quantised BEFORE they leave (e4m3 values + one fp32 scale per 128 channels: H + H / 32 bytes per row instead
+        of 2 H), the receiving rank's grouped fp8 GEMM reads them in place, outputs return in bf16."""
         T, H = x.shape
         k = self.top_k
         assert t_stride <= self.t_cap and T <= t_stride and H == self.hidden and ids.shape[1] == k
+        if fp8_scales is not None:
+            return self._moe_fp8(x, ids, weights, w_gate_up, w_down, fp8_scales, t_stride, add)
         offs, (off_x, off_ret, off_ids, off_w) = self._layout()
         self.epoch += 1
         ep = self.epoch & 0xFFFFFFFF
@@ -86,6 +92,38 @@ class EPExchange:
         recv_x = self.buf[off_x:off_x + rows * H * 2].view(torch.bfloat16).view(rows, H)
         recv_ids = self.buf[off_ids:off_ids + rows * k * 4].view(torch.int32).view(rows, k)
         y, pos = cuda_moe.expert_pipeline(recv_x, recv_ids, w_gate_up, w_down, self.rank * self.e_local)
+        kcuda._check(self._lib.ksana_ep_combine(self.rank, self.size, self._ptrs, offs, y.data_ptr(), pos.data_ptr(),
+                                                t_stride, k, H, ep, st), "ep_combine")
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+        kcuda._check(self._lib.ksana_ep_finish(self.rank, self.size, self._ptrs, offs, idc.data_ptr() if T else None,
+                                               T, t_stride, k, H, self.e_local,
+                                               add.data_ptr() if add is not None else None,
+                                               add.stride(0) if add is not None else 0, out.data_ptr() if T else None,
+                                               H, ep, st), "ep_finish")
+        kcuda.launch_count += 4
+        return out
+
+    def _moe_fp8(self, x, ids, weights, wq_gate_up, wq_down, scales, t_stride, add) -> torch.Tensor:
+        T, H = x.shape
+        k = self.top_k
+        assert H % 512 == 0, "packed fp8 rows need H + H / 32 bytes to be a multiple of 16"
+        hp = (H + H // 32) // 2  # packed row as bf16 elements (the dispatch kernel moves 16-byte pieces)
+        offs, (off_x, off_ret, off_ids, off_w) = self._layout()
+        self.epoch += 1
+        ep = self.epoch & 0xFFFFFFFF
+        st = torch.cuda.current_stream().cuda_stream
+        idc = ids.to(torch.int32).contiguous()
+        wc = weights.float().contiguous()
+        packed = cuda_moe.pack_fp8_rows(x).view(torch.bfloat16) if T else x[:, :hp]
+        kcuda._check(self._lib.ksana_ep_dispatch(self.rank, self.size, self._ptrs, offs,
+                                                 packed.data_ptr() if T else None, hp, idc.data_ptr() if T else None,
+                                                 wc.data_ptr() if T else None, T, t_stride, k, hp, self.e_local, ep,
+                                                 st), "ep_dispatch")
+        rows = self.size * t_stride
+        recv_x = self.buf[off_x:off_x + rows * hp * 2].view(torch.bfloat16).view(rows, hp)
+        recv_ids = self.buf[off_ids:off_ids + rows * k * 4].view(torch.int32).view(rows, k)
+        y, pos = cuda_moe.expert_pipeline_fp8(recv_x, recv_ids, wq_gate_up, scales[0], wq_down, scales[1],
+                                              self.rank * self.e_local, packed=True)
         kcuda._check(self._lib.ksana_ep_combine(self.rank, self.size, self._ptrs, offs, y.data_ptr(), pos.data_ptr(),
                                                 t_stride, k, H, ep, st), "ep_combine")
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)

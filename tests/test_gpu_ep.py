@@ -50,6 +50,25 @@ def _worker(rank, world, port, q):
             if add is not None:
                 want = want + add.float()
             errs.append((it, T, (out.float() - want).abs().max().item(), want.abs().max().item()))
+    # block-scaled fp8 experts: rows leave quantised (values + scales packed), the grouped fp8 GEMM reads them in place
+    q1, s1, q2, s2 = [], [], [], []
+    for e in range(E):
+        a, b = ref.quant_fp8_block_weight(w1[e].float())
+        c, d = ref.quant_fp8_block_weight(w2[e].float())
+        q1.append(a), s1.append(b), q2.append(c), s2.append(d)
+    q1, s1, q2, s2 = torch.stack(q1), torch.stack(s1), torch.stack(q2), torch.stack(s2)
+    sl = slice(rank * el, (rank + 1) * el)
+    for it, (t_stride, t_of) in enumerate(((64, lambda r: 37 + 9 * r), (16, lambda r: 0 if r == 1 else 16))):
+        T = min(t_of(rank), t_stride)
+        gl = torch.Generator(device=dev).manual_seed(5000 * it + rank)
+        x = (torch.randn(T, H, device=dev, generator=gl) * 0.5).to(torch.bfloat16)
+        ids, w = ref.moe_route(torch.randn(T, E, device=dev, generator=gl), k, "softmax", True)
+        out = ex.moe(x, ids, w, q1[sl].contiguous(), q2[sl].contiguous(), t_stride, None,
+                     fp8_scales=(s1[sl].contiguous(), s2[sl].contiguous()))
+        torch.cuda.synchronize()
+        if T:
+            want = ref.moe_experts_fp8(x, ids, w, q1, s1, q2, s2, 0).float()
+            errs.append((50 + it, T, (out.float() - want).abs().max().item() * 0.75, want.abs().max().item()))
     # a 2-layer MoE model: MoE blocks through the exchange vs the replicated-token formulation on the same ranks
     # (same inputs, so the routing decisions agree; a comparison across TP degrees could flip near-tied experts)
     from ksanallm_b200.config.model_config import model_config_from_dict
