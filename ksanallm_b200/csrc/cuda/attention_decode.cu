@@ -227,6 +227,15 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
   }
 }
 
+// The merge step for other kernels that write partials in this layout (attention_decode_gqa.cu).
+int launch_decode_combine(const float* part_o, const float* part_lse, const int* cu_q, int seq_base, int h, int splits,
+                          int max_rows, int num_seqs, void* out, int ldo, cudaStream_t stream) {
+  dim3 cgrid(num_seqs, (max_rows + 3) / 4);
+  decode_combine_kernel<128><<<cgrid, 128, 0, stream>>>(part_o, part_lse, cu_q, seq_base, h, splits, max_rows,
+                                                        reinterpret_cast<__nv_bfloat16*>(out), ldo);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 }  // namespace ksana
 
 using namespace ksana;

@@ -27,6 +27,10 @@ int ksana_paged_decode(const void* q, int ldq, const void* cache, int cache_kind
                        int max_kv_len, int h, int hk, int d, int block_size, float scale, const float* alibi,
                        float k_scale, float v_scale, void* out, int ldo, float* workspace, long long workspace_floats,
                        cudaStream_t stream);
+int ksana_paged_decode_gqa(const void* q, int ldq, int total_tokens, const void* cache, int num_blocks,
+                           const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int seq_base,
+                           int num_seqs, int max_q_len, int max_kv_len, int h, int hk, int d, int block_size, float scale,
+                           void* out, int ldo, float* workspace, long long workspace_floats, cudaStream_t stream);
 int ksana_rs_norm_ag(int rank, int ws, void* const* partial, void* const* hbuf, void* const* sig, void* partial_mc,
                      void* hbuf_mc, int T, int H, void* residual, const void* norm_w, float eps, unsigned int epoch,
                      int mode, int max_ctas, cudaStream_t stream);
@@ -147,11 +151,22 @@ struct Exec {
       return false;
     if (g.n_dec > 0) {
       const long long half = m->attn_ws_floats / 2;
-      if (!step(4, ksana_paged_decode(qkv_all, nqkv, w.kv_cache, m->kv_kind, s->block_tables, s->max_blocks, s->cu_q,
+      float* aws = m->attn_ws + (whole_step ? 0 : g.lane * half);
+      const long long aws_floats = whole_step ? m->attn_ws_floats : half;
+      int gqa = -1;
+      if (m->kv_kind == 0 && h / hk >= 4 && (h / hk) * g.max_q_decode <= 128) {
+        // grouped-query decode on the tensor cores; shapes it declines (-1) and workspace shortfalls (-6) fall through
+        gqa = ksana_paged_decode_gqa(qkv_all, nqkv, s->total_tokens, w.kv_cache, m->num_blocks, s->block_tables,
+                                     s->max_blocks, s->cu_q, s->kv_lens, g.dec_base, g.n_dec, g.max_q_decode,
+                                     g.max_kv_decode, h, hk, d, m->block_size, m->attn_scale, attn_all, nq, aws,
+                                     aws_floats, st);
+        if (gqa != 0 && gqa != -1 && gqa != -6) return step(4, gqa);
+        if (gqa == 0) ++(*launches);
+      }
+      if (gqa != 0 && !step(4, ksana_paged_decode(qkv_all, nqkv, w.kv_cache, m->kv_kind, s->block_tables, s->max_blocks, s->cu_q,
                                       s->kv_lens, g.dec_base, g.n_dec, g.max_q_decode, g.max_kv_decode, h, hk, d,
                                       m->block_size, m->attn_scale, nullptr, m->k_scale, m->v_scale, attn_all, nq,
-                                      m->attn_ws + (whole_step ? 0 : g.lane * half),
-                                      whole_step ? m->attn_ws_floats : half, st)))
+                                      aws, aws_floats, st)))
         return false;
     }
     const char* h2;

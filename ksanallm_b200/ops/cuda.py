@@ -6,6 +6,7 @@ There is no fallback here: if the library is missing or a launcher rejects a sha
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Dict, Optional, Tuple
 
@@ -60,6 +61,7 @@ class _Sig:
     ksana_quant_fp8_group = ([P, I, P, I, P, I, I, P], I)
     ksana_paged_decode = ([P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, F, P, F, F, P, I, P, LL, P], I)
     ksana_paged_prefill = ([P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I, F, P, P, I, P], I)
+    ksana_paged_decode_gqa = ([P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, F, P, I, P, LL, P], I)
     ksana_argmax = ([P, I, I, I, P, P], I)
     ksana_sample = ([P, I, I, I, P, P, P, P, P, P], I)
 
@@ -242,6 +244,9 @@ def quant_fp8_group(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 
 
 # ---- attention ----------------------------------------------------------------------------------------------
+GQA_TENSOR_CORE_MIN_GROUP = int(os.environ.get("KSANA_GQA_TC_MIN_GROUP", "4"))
+
+
 def paged_attention(q, kv_cache, meta, scale, alibi_slopes=None, k_scale=1.0, v_scale=1.0, window=0) -> torch.Tensor:
     T, h, d = q.shape
     nb, _, hk, bs, _ = kv_cache.shape
@@ -269,6 +274,19 @@ def paged_attention(q, kv_cache, meta, scale, alibi_slopes=None, k_scale=1.0, v_
         max_q = int((cu[n_pre + 1:n_pre + n_dec + 1] - cu[n_pre:n_pre + n_dec]).max())
         max_kv = int(meta.kv_lens_host[n_pre:n_pre + n_dec].max())
         ws = workspace(q.device)
+        code = -1
+        if kind == 0 and alibi_slopes is None and h // hk >= GQA_TENSOR_CORE_MIN_GROUP and (h // hk) * max_q <= 128:
+            # grouped-query decode on the tensor cores: the group's heads are the rows of one MMA operand
+            code = lib().ksana_paged_decode_gqa(_ptr(q), ldq, T, _ptr(kv_cache), nb, _ptr(meta.block_tables),
+                                                meta.max_blocks, _ptr(meta.cu_q), _ptr(meta.kv_lens), n_pre, n_dec, max_q,
+                                                max_kv, h, hk, d, bs, float(scale), _ptr(out), ldo, _ptr(ws.attn_ws),
+                                                ws.attn_ws.numel(), _stream())
+            if code not in (0, -1, -6):
+                _check(code, "paged_decode_gqa")
+        if code == 0:
+            global launch_count
+            launch_count += 1
+            return out
         code = lib().ksana_paged_decode(_ptr(q), ldq, _ptr(kv_cache), kind, _ptr(meta.block_tables), meta.max_blocks,
                                         _ptr(meta.cu_q), _ptr(meta.kv_lens), n_pre, n_dec, max_q, max_kv, h, hk, d, bs,
                                         float(scale), _ptr(alibi_slopes), float(k_scale), float(v_scale), _ptr(out), ldo,
