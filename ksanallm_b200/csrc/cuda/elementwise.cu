@@ -279,9 +279,42 @@ __global__ void quant_fp8_group_kernel(const __nv_bfloat16* __restrict__ x, int 
   if (lane == 0) scales[static_cast<size_t>(t) * groups + g] = scale;
 }
 
+// ---- KV block mover ---------------------------------------------------------------------------------------------------
+// Copies whole cache blocks, for every layer at once: pairs[i] = (source block, destination block). Source and
+// destination layers may be device memory or pinned host memory mapped into the device's address space, so the same
+// kernel serves swap-out (device -> host), swap-in (host -> device) and copy-on-write forks (device -> device)
+// without a host-side gather / scatter or a blocking copy. The reference moves blocks with per-block cudaMemcpyAsync
+// calls (src/ksana_llm/cache_manager/block_allocator/, prefix_cache_manager.cpp swap paths).
+__global__ void __launch_bounds__(256)
+block_copy_kernel(const uint4* const* __restrict__ src_layers, uint4* const* __restrict__ dst_layers,
+                  const int* __restrict__ pairs, long long block_vec16) {
+  const int pair = blockIdx.x, layer = blockIdx.y;
+  const uint4* src = src_layers[layer] + static_cast<size_t>(pairs[2 * pair]) * block_vec16;
+  uint4* dst = dst_layers[layer] + static_cast<size_t>(pairs[2 * pair + 1]) * block_vec16;
+  for (long long i = static_cast<long long>(blockIdx.z) * blockDim.x + threadIdx.x; i < block_vec16;
+       i += static_cast<long long>(gridDim.z) * blockDim.x)
+    dst[i] = src[i];
+}
+
 }  // namespace ksana
 
 using namespace ksana;
+
+// src_layers / dst_layers: device arrays of n_layers base pointers; pairs: device int array [n_pairs][2];
+// block_bytes: bytes of one block of one layer (a multiple of 16).
+KSANA_API int ksana_block_copy(const void* src_layers, const void* dst_layers, int n_layers, const int* pairs,
+                               int n_pairs, long long block_bytes, cudaStream_t stream) {
+  if (n_pairs <= 0 || n_layers <= 0) return 0;
+  if (block_bytes & 15) return -1;
+  const long long vec = block_bytes / 16;
+  int z = static_cast<int>((vec + 256 * 8 - 1) / (256 * 8));
+  if (z < 1) z = 1;
+  if (z > 16) z = 16;
+  dim3 grid(n_pairs, n_layers, z);
+  block_copy_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint4* const*>(src_layers),
+                                              reinterpret_cast<uint4* const*>(dst_layers), pairs, vec);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
 
 KSANA_API int ksana_rms_norm(const void* x, int ldx, void* residual, int ldr, const void* w, void* out, int ldo, int T,
                              int H, float eps, cudaStream_t stream) {

@@ -217,6 +217,101 @@ topk_topp_sample_kernel(const float* __restrict__ logits, int ld, int V, const f
   }
 }
 
+
+// ---- batched logits processing -----------------------------------------------------------------------------------
+// One CTA per logits row applies, on the device, what the reference does in per-request host loops on rank 0
+// (src/ksana_llm/samplers/sampler.cpp:90-217, 371-434): repetition penalty over prompt + output tokens (once per
+// distinct token: positive logits divided, negative ones multiplied), presence / frequency penalties over the output
+// tokens, the three no-repeat-n-gram rules, additive edits (logit bias), bans (min_tokens) and the grammar bitmask.
+// hist: the rows' token histories back to back (prompt then output), row r = hist[row_off[r] .. row_off[r + 1]) with
+// prompt_len[r] prompt tokens. fparams[r] = {repetition, presence, frequency}; iparams[r] = {no_repeat_ngram,
+// encoder_no_repeat_ngram, decoder_no_repeat_ngram, has_bitmask}. edits / bans: (row, token[, value]) triples sorted by
+// row with CSR offsets. A V-bit map in shared memory marks the tokens already handled.
+__global__ void __launch_bounds__(512)
+logits_process_kernel(float* __restrict__ x, int ld, int V, const int* __restrict__ hist,
+                      const int* __restrict__ row_off, const int* __restrict__ prompt_len,
+                      const float* __restrict__ fparams, const int* __restrict__ iparams,
+                      const int* __restrict__ edit_off, const int* __restrict__ edit_tok,
+                      const float* __restrict__ edit_val, const int* __restrict__ ban_off,
+                      const int* __restrict__ ban_tok, const int* __restrict__ bitmask, int mask_words) {
+  extern __shared__ unsigned int seen[];  // ceil(V / 32) words
+  const int r = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
+  float* xr = x + static_cast<size_t>(r) * ld;
+  const int* h = hist + row_off[r];
+  const int n = row_off[r + 1] - row_off[r];
+  const int np = min(prompt_len[r], n);
+  const float rep = fparams[3 * r], pres = fparams[3 * r + 1], freq = fparams[3 * r + 2];
+  const int words = (V + 31) >> 5;
+  if (rep != 1.f) {
+    for (int i = tid; i < words; i += nthr) seen[i] = 0u;
+    __syncthreads();
+    for (int i = tid; i < n; i += nthr) {
+      const int t = h[i];
+      if (t < 0 || t >= V) continue;
+      const unsigned int bit = 1u << (t & 31);
+      if (!(atomicOr(&seen[t >> 5], bit) & bit)) {  // first occurrence: this thread alone touches the logit
+        const float v = xr[t];
+        xr[t] = v > 0.f ? v / rep : v * rep;
+      }
+    }
+    __syncthreads();
+  }
+  if (pres != 0.f || freq != 0.f) {
+    for (int i = tid; i < words; i += nthr) seen[i] = 0u;
+    __syncthreads();
+    for (int i = np + tid; i < n; i += nthr) {
+      const int t = h[i];
+      if (t < 0 || t >= V) continue;
+      const unsigned int bit = 1u << (t & 31);
+      float d = -freq;
+      if (!(atomicOr(&seen[t >> 5], bit) & bit)) d -= pres;
+      atomicAdd(&xr[t], d);
+    }
+    __syncthreads();
+  }
+  for (int i = edit_off[r] + tid; i < edit_off[r + 1]; i += nthr) {
+    const int t = edit_tok[i];
+    if (t >= 0 && t < V) atomicAdd(&xr[t], edit_val[i]);
+  }
+  __syncthreads();
+  // n-gram rules: a window of the source that equals the last (size - 1) tokens of the suffix source bans its next token
+  const int sizes[3] = {iparams[4 * r], iparams[4 * r + 1], iparams[4 * r + 2]};
+#pragma unroll
+  for (int rule = 0; rule < 3; ++rule) {
+    const int g = sizes[rule];
+    if (g <= 0) continue;
+    // rule 0: windows and suffix over prompt + output; rule 1: windows over the prompt, suffix of the output;
+    // rule 2: windows and suffix over the output
+    const int* win = rule == 2 ? h + np : h;
+    const int nwin = rule == 0 ? n : (rule == 1 ? np : n - np);
+    const int* suf = rule == 0 ? h : h + np;
+    const int nsuf = rule == 0 ? n : n - np;
+    if (nsuf < g - 1 || nwin < g) continue;
+    const int* tail = suf + nsuf - (g - 1);
+    for (int i = tid; i + g <= nwin; i += nthr) {
+      bool same = true;
+      for (int j = 0; j < g - 1 && same; ++j) same = win[i + j] == tail[j];
+      if (same) {
+        const int t = win[i + g - 1];
+        if (t >= 0 && t < V) xr[t] = -INFINITY;
+      }
+    }
+  }
+  for (int i = ban_off[r] + tid; i < ban_off[r + 1]; i += nthr) {
+    const int t = ban_tok[i];
+    if (t >= 0 && t < V) xr[t] = -INFINITY;
+  }
+  if (iparams[4 * r + 3] && bitmask != nullptr) {
+    __syncthreads();
+    const int* bm = bitmask + static_cast<size_t>(r) * mask_words;
+    for (int t = tid; t < V; t += nthr) {
+      const int w = t >> 5;
+      const unsigned int bits = w < mask_words ? static_cast<unsigned int>(bm[w]) : 0xFFFFFFFFu;
+      if (!((bits >> (t & 31)) & 1u)) xr[t] = -INFINITY;
+    }
+  }
+}
+
 }  // namespace ksana
 
 using namespace ksana;
@@ -231,5 +326,20 @@ KSANA_API int ksana_sample(const float* logits, int ld, int rows, int V, const f
                            const float* top_p, const float* uniform, int* out, cudaStream_t stream) {
   if (rows <= 0) return 0;
   topk_topp_sample_kernel<<<rows, SAMP_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, uniform, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// In-place processing of fp32 logits [rows, V] (row pitch ld); see logits_process_kernel for the arguments. All
+// arrays are device memory; edit_* / ban_* / bitmask may be null when their offsets are all zero / no row has a mask.
+KSANA_API int ksana_logits_process(float* logits, int ld, int rows, int V, const int* hist, const int* row_off,
+                                   const int* prompt_len, const float* fparams, const int* iparams,
+                                   const int* edit_off, const int* edit_tok, const float* edit_val, const int* ban_off,
+                                   const int* ban_tok, const int* bitmask, int mask_words, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int smem = ((V + 31) / 32) * 4;
+  if (smem > 200 * 1024) return -1;
+  if (KSANA_SMEM_ONCE(logits_process_kernel, 200 * 1024) != 0) return -4;
+  logits_process_kernel<<<rows, 512, smem, stream>>>(logits, ld, V, hist, row_off, prompt_len, fparams, iparams, edit_off,
+                                                     edit_tok, edit_val, ban_off, ban_tok, bitmask, mask_words);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -46,6 +46,17 @@ class ModelRunner:
     def apply_block_ops(self, swap_out: np.ndarray, swap_in: np.ndarray, copies: np.ndarray) -> None:
         """Swap-out (device->host) must land before the step overwrites the freed blocks, swap-in and
         fork copies before attention reads them: all are issued on the compute stream ahead of the forward."""
+        if self.device.type == "cuda" and self._mover_ok():
+            # one kernel per kind of move, every layer at once, straight between the device cache and the pinned host
+            # pool: nothing blocks the host and no staging copy is made
+            from ..ops import cuda as kcuda
+            for pairs, src, dst in ((swap_out, self._dev_ptrs, self._host_ptrs), (swap_in, self._host_ptrs, self._dev_ptrs),
+                                    (copies, self._dev_ptrs, self._dev_ptrs)):
+                if len(pairs):
+                    pr = torch.from_numpy(np.ascontiguousarray(pairs[:, :2], dtype=np.int32)).to(self.device,
+                                                                                                 non_blocking=True)
+                    kcuda.block_copy(src, dst, pr, self._block_bytes)
+            return
         if len(swap_out):
             src = torch.from_numpy(np.ascontiguousarray(swap_out[:, 0])).long()
             dst = torch.from_numpy(np.ascontiguousarray(swap_out[:, 1])).long()
@@ -61,6 +72,25 @@ class ModelRunner:
             dst = torch.from_numpy(np.ascontiguousarray(copies[:, 1])).long().to(self.device)
             for dev in self.kv_caches:
                 dev[dst] = dev[src]
+
+    def _mover_ok(self) -> bool:
+        """Prepares (once) the per-layer base-address tables of the device cache and the pinned host pool."""
+        ok = getattr(self, "_mover", None)
+        if ok is None:
+            c0 = self.kv_caches[0]
+            self._block_bytes = c0[0].numel() * c0.element_size()
+            ok = self._block_bytes % 16 == 0 and all(c.is_contiguous() for c in self.kv_caches)
+            if ok:
+                self._dev_ptrs = torch.tensor([c.data_ptr() for c in self.kv_caches], dtype=torch.int64,
+                                              device=self.device)
+                self._host_ptrs = None
+                if self.host_caches is not None:
+                    ok = all(h.is_pinned() and h.is_contiguous() for h in self.host_caches)
+                    if ok:
+                        self._host_ptrs = torch.tensor([h.data_ptr() for h in self.host_caches], dtype=torch.int64,
+                                                       device=self.device)
+            self._mover = ok
+        return ok
 
     def apply_flexible(self, rows: np.ndarray) -> None:
         """Flexible cache reuse: ``rows`` = [n, 4] (source slot, destination slot, source position, destination

@@ -61,9 +61,64 @@ class Sampler:
         return all(r.params.use_greedy and not r.params.needs_logits_processing and r.params.logprobs == 0
                    and r.bitmask is None for r in rows)
 
+    def _process_device(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> torch.Tensor:
+        """The whole step's logit processing as ONE kernel (csrc/cuda/sampling.cu logits_process_kernel): the host
+        only concatenates the token histories and the few (row, token) edits; nothing vocab-sized leaves the device."""
+        from ..ops import cuda as kcuda
+        L, V = logits.shape
+        x = logits.float()
+        if x.data_ptr() == logits.data_ptr() or x.stride(1) != 1:
+            x = x.clone(memory_format=torch.contiguous_format)
+        hist, row_off, plen = [], [0], []
+        fpar = np.zeros((L, 3), dtype=np.float32)
+        ipar = np.zeros((L, 4), dtype=np.int32)
+        e_off, e_tok, e_val, b_off, b_tok = [0], [], [], [0], []
+        words = (V + 31) // 32
+        bm = None
+        for i, r in enumerate(rows):
+            p = r.params
+            need_hist = (p.repetition_penalty != 1.0 or p.presence_penalty or p.frequency_penalty or
+                         p.no_repeat_ngram_size > 0 or p.encoder_no_repeat_ngram_size > 0 or
+                         p.decoder_no_repeat_ngram_size > 0)
+            if need_hist:
+                hist.extend(r.prompt_tokens)
+                hist.extend(r.output_tokens)
+                plen.append(len(r.prompt_tokens))
+            else:
+                plen.append(0)
+            row_off.append(len(hist))
+            fpar[i] = (p.repetition_penalty, p.presence_penalty or 0.0, p.frequency_penalty or 0.0)
+            ipar[i, :3] = (p.no_repeat_ngram_size, p.encoder_no_repeat_ngram_size, p.decoder_no_repeat_ngram_size)
+            if p.logit_bias:
+                for t, b in p.logit_bias.items():
+                    e_tok.append(int(t))
+                    e_val.append(float(b))
+            e_off.append(len(e_tok))
+            if p.min_tokens > len(r.output_tokens):
+                b_tok.extend(int(t) for t in list(p.stop_token_ids) + ([] if p.ignore_eos else list(self.eos_token_ids)))
+            b_off.append(len(b_tok))
+            if r.bitmask is not None:
+                if bm is None:
+                    bm = np.full((L, words), -1, dtype=np.int32)
+                bm[i, :min(len(r.bitmask), words)] = r.bitmask[:words]
+                ipar[i, 3] = 1
+
+        def dev(a, dt):
+            return torch.from_numpy(np.ascontiguousarray(a, dtype=dt)).to(self.device, non_blocking=True)
+
+        return kcuda.logits_process(
+            x, dev(hist or [0], np.int32), dev(row_off, np.int32), dev(plen, np.int32), dev(fpar, np.float32),
+            dev(ipar, np.int32), dev(e_off, np.int32), dev(e_tok or [0], np.int32), dev(e_val or [0.0], np.float32),
+            dev(b_off, np.int32), dev(b_tok or [0], np.int32), dev(bm, np.int32) if bm is not None else None)
+
     def process_logits(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> torch.Tensor:
         """Applies penalties / bans / grammar masks. Returns fp32 logits (a copy only when needed)."""
         L, V = logits.shape
+        if logits.is_cuda and V <= 200 * 1024 * 8:
+            if not any(r.params.needs_logits_processing or r.bitmask is not None or r.params.min_tokens > 0
+                       for r in rows):
+                return logits.float()
+            return self._process_device(logits, rows)
         x = logits.float()
         need_pen = [i for i, r in enumerate(rows) if r.params.repetition_penalty != 1.0]
         if need_pen:

@@ -64,6 +64,8 @@ class _Sig:
     ksana_paged_decode_gqa = ([P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, F, P, I, P, LL, P], I)
     ksana_argmax = ([P, I, I, I, P, P], I)
     ksana_sample = ([P, I, I, I, P, P, P, P, P, P], I)
+    ksana_block_copy = ([P, P, I, P, I, LL, P], I)
+    ksana_logits_process = ([P, I, I, I, P, P, P, P, P, P, P, P, P, P, P, I, P], I)
 
 
 def _stream() -> int:
@@ -339,3 +341,23 @@ def sample(logits, temperature, top_k, top_p, uniform) -> torch.Tensor:
     _check(lib().ksana_sample(_ptr(logits), logits.stride(0), B, V, _ptr(temperature.float()), _ptr(top_k.int()),
                               _ptr(top_p.float()), _ptr(uniform.float()), _ptr(out), _stream()), "sample")
     return out
+
+
+def logits_process(x, hist, row_off, prompt_len, fparams, iparams, edit_off, edit_tok, edit_val, ban_off, ban_tok,
+                   bitmask) -> torch.Tensor:
+    """In-place penalties / n-gram bans / edits / bans / grammar mask on fp32 logits ``x`` [rows, V] (one kernel for
+    the whole step). The other arguments are device tensors laid out as csrc/cuda/sampling.cu describes."""
+    assert x.dtype == torch.float32 and x.stride(1) == 1
+    L, V = x.shape
+    _check(lib().ksana_logits_process(_ptr(x), x.stride(0), L, V, _ptr(hist), _ptr(row_off), _ptr(prompt_len),
+                                      _ptr(fparams), _ptr(iparams), _ptr(edit_off), _ptr(edit_tok), _ptr(edit_val),
+                                      _ptr(ban_off), _ptr(ban_tok), _ptr(bitmask),
+                                      bitmask.shape[1] if bitmask is not None else 0, _stream()), "logits_process")
+    return x
+
+
+def block_copy(src_ptrs: torch.Tensor, dst_ptrs: torch.Tensor, pairs: torch.Tensor, block_bytes: int) -> None:
+    """Copies cache blocks ``pairs[i] = (src, dst)`` of every layer in one launch. ``src_ptrs`` / ``dst_ptrs``:
+    int64 device tensors with one base address per layer (device memory or mapped pinned host memory)."""
+    _check(lib().ksana_block_copy(_ptr(src_ptrs), _ptr(dst_ptrs), src_ptrs.numel(), _ptr(pairs), pairs.shape[0],
+                                  int(block_bytes), _stream()), "block_copy")
