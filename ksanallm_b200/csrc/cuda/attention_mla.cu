@@ -504,3 +504,74 @@ KSANA_API int ksana_mla_cache_append(const void* latent, int ld_l, const void* k
                                                            reinterpret_cast<__nv_bfloat16*>(cache), T, r, dr);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
+
+// ---- fused MLA RoPE + cache append ---------------------------------------------------------------------------------
+// One launch replaces the PyTorch rotary ops of the MLA layer and the separate cache append (reference:
+// src/ksana_llm/modules/attention/multihead_latent_attention.cpp:276-284 rotary + FlashMLA cache copy):
+//   warps 0 .. T*h-1 : rotate the rope part of query (token, head) and write it behind the absorbed latent query in
+//                      q_cat[token][head][r .. r + dr) (the attention kernel reads [latent | rope] rows);
+//   warps T*h ..     : rotate the token's shared rope key and write cache[slot] = [latent | rotated key] (the cache row
+//                      may be wider: extra columns, e.g. an indexer key, are left alone).
+// cos_sin: [max_pos, dr] = [cos(dr/2) | sin(dr/2)] fp32 rows. Pairs are (i, i + dr/2), or (2i, 2i + 1) when interleaved.
+namespace ksana {
+
+__global__ void __launch_bounds__(256)
+mla_rope_append_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, int q_head_stride, int dn,
+                       __nv_bfloat16* __restrict__ q_cat, const __nv_bfloat16* __restrict__ k_rope, int ld_k,
+                       const __nv_bfloat16* __restrict__ latent, int ld_l, const int* __restrict__ positions,
+                       const float* __restrict__ cos_sin, const int* __restrict__ slots,
+                       __nv_bfloat16* __restrict__ cache, int cache_width, int T, int h, int r, int dr,
+                       int interleaved) {
+  const long long gw = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int half = dr >> 1;
+  if (gw < static_cast<long long>(T) * h) {
+    const int t = static_cast<int>(gw / h), hd = static_cast<int>(gw - static_cast<long long>(t) * h);
+    const __nv_bfloat16* src = q + static_cast<size_t>(t) * q_row_stride + static_cast<size_t>(hd) * q_head_stride + dn;
+    __nv_bfloat16* dst = q_cat + (static_cast<size_t>(t) * h + hd) * (r + dr) + r;
+    const float* cs = cos_sin + static_cast<size_t>(positions[t]) * dr;
+    for (int i = lane; i < half; i += 32) {
+      const int i0 = interleaved ? 2 * i : i, i1 = interleaved ? 2 * i + 1 : i + half;
+      const float a = __bfloat162float(src[i0]), b = __bfloat162float(src[i1]);
+      const float c = cs[i], s = cs[half + i];
+      dst[i0] = __float2bfloat16(a * c - b * s);
+      dst[i1] = __float2bfloat16(b * c + a * s);
+    }
+    return;
+  }
+  const long long kt = gw - static_cast<long long>(T) * h;
+  if (kt >= T) return;
+  const int t = static_cast<int>(kt);
+  __nv_bfloat16* row = cache + static_cast<size_t>(slots[t]) * cache_width;
+  for (int i = lane * 2; i < r; i += 64)
+    *reinterpret_cast<__nv_bfloat162*>(row + i) =
+        *reinterpret_cast<const __nv_bfloat162*>(latent + static_cast<size_t>(t) * ld_l + i);
+  const __nv_bfloat16* ksrc = k_rope + static_cast<size_t>(t) * ld_k;
+  const float* cs = cos_sin + static_cast<size_t>(positions[t]) * dr;
+  for (int i = lane; i < half; i += 32) {
+    const int i0 = interleaved ? 2 * i : i, i1 = interleaved ? 2 * i + 1 : i + half;
+    const float a = __bfloat162float(ksrc[i0]), b = __bfloat162float(ksrc[i1]);
+    const float c = cs[i], s = cs[half + i];
+    row[r + i0] = __float2bfloat16(a * c - b * s);
+    row[r + i1] = __float2bfloat16(b * c + a * s);
+  }
+}
+
+}  // namespace ksana
+
+// q: projected queries, element (t, head, j) at q + t * q_row_stride + head * q_head_stride + j with the rope part at
+// j in [dn, dn + dr); q_cat: [T, h, r + dr] contiguous (its [.., :r] part is written by the absorb GEMM); k_rope:
+// [T, dr] (pitch ld_k); latent: [T, r] (pitch ld_l); cache: rows of cache_width >= r + dr elements; r, ld_l even.
+KSANA_API int ksana_mla_rope_append(const void* q, long long q_row_stride, int q_head_stride, int dn, void* q_cat,
+                                    const void* k_rope, int ld_k, const void* latent, int ld_l, const int* positions,
+                                    const float* cos_sin, const int* slots, void* cache, int cache_width, int T, int h,
+                                    int r, int dr, int interleaved, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((r & 1) || (dr & 1) || (ld_l & 1) || cache_width < r + dr || (cache_width & 1)) return -1;
+  const long long warps = static_cast<long long>(T) * h + T;
+  ksana::mla_rope_append_kernel<<<static_cast<unsigned int>((warps + 7) / 8), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(q), q_row_stride, q_head_stride, dn, reinterpret_cast<__nv_bfloat16*>(q_cat),
+      reinterpret_cast<const __nv_bfloat16*>(k_rope), ld_k, reinterpret_cast<const __nv_bfloat16*>(latent), ld_l,
+      positions, cos_sin, slots, reinterpret_cast<__nv_bfloat16*>(cache), cache_width, T, h, r, dr, interleaved);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

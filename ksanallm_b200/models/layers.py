@@ -213,6 +213,20 @@ class MLAttention:
             self.idx_wproj = w[ip + ".weights_proj.weight"]
             self.idx_h, self.idx_d = cfg.index_n_heads, cfg.index_head_dim
 
+    def _fused_core_ok(self, q: torch.Tensor, cache: torch.Tensor) -> bool:
+        ok = getattr(self, "_fused_ok", None)
+        if ok is None:
+            from ..ops import cuda_mla
+            ok = bool(cuda_mla.fused_supported(q, cache, self.r, self.dr, self.dn, self.dv, self.h) and
+                      self.w_uk.dtype == torch.bfloat16 and self.rope_cache is not None and
+                      self.rope_cache.dtype == torch.float32)
+            if ok:
+                # [h, N, K] operands of the head-batched GEMMs: W_UK^T as [h, r, dn], W_UV as [h, dv, r]
+                self.w_uk_nk = self.w_uk.transpose(1, 2).contiguous()
+                self.w_uv_nk = self.w_uv.transpose(1, 2).contiguous()
+            self._fused_ok = ok
+        return ok and q.dtype == torch.bfloat16
+
     def _indexer(self, h: torch.Tensor, q_a: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
         """Indexer queries [T, Hi, Di], per-head weights [T, Hi] (scales folded in) and keys [T, Di]. The first
         qk_rope_head_dim entries of every indexer head are rotated (half-split layout)."""
@@ -239,6 +253,13 @@ class MLAttention:
         latent = ops.rms_norm(rest[:, :self.r].contiguous(), self.kv_a_norm, eps)
         k_rope = rest[:, self.r:].contiguous()
         q = q.view(T, self.h, self.dn + self.dr)
+        if not self.index_topk and h.is_cuda and self._fused_core_ok(q, cache):
+            # absorb GEMMs, RoPE, cache append and attention as four kernels, no PyTorch op in between
+            from ..ops import cuda_mla
+            o = cuda_mla.mla_absorbed_attention(q, self.w_uk_nk, self.w_uv_nk, latent, k_rope, meta.positions,
+                                                self.rope_cache, self.cfg.rope_interleaved, cache, meta, self.scale,
+                                                self.dn, self.dr)
+            return o.reshape(T, self.h * self.dv)
         q_nope, q_rope = q[..., :self.dn], q[..., self.dn:].contiguous()
         cs = self.rope_cache[meta.positions.long()]
         cos, sin = cs[:, :self.dr // 2], cs[:, self.dr // 2:]

@@ -64,6 +64,8 @@ class _Sig:
     ksana_paged_decode_gqa = ([P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, F, P, I, P, LL, P], I)
     ksana_argmax = ([P, I, I, I, P, P], I)
     ksana_sample = ([P, I, I, I, P, P, P, P, P, P], I)
+    ksana_gemm_bf16_batched = ([P, LL, LL, P, P, LL, LL, I, I, I, I, P], I)
+    ksana_mla_rope_append = ([P, LL, I, I, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, P], I)
     ksana_block_copy = ([P, P, I, P, I, LL, P], I)
     ksana_logits_process = ([P, I, I, I, P, P, P, P, P, P, P, P, P, P, P, I, P], I)
 
