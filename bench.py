@@ -73,6 +73,8 @@ def parse_args():
     ap.add_argument("--max-step-tokens", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncates the model (result marked invalid)")
     ap.add_argument("--no-async", action="store_true", help="synchronous scheduling (host waits for every step)")
+    ap.add_argument("--kv-fraction", type=float, default=0.0,
+                    help="fraction of device memory given to the KV cache (0: everything but a fixed reserve)")
     ap.add_argument("--no-tp1-check", action="store_true", help="skip the comparison of TP=N tokens with TP=1")
     return ap.parse_args()
 
@@ -370,7 +372,7 @@ def main():
                             "max_token_len": wl["max_token_len"], "max_waiting_queue_len": 100000, "preempt_mode": 1,
                             "enable_async": not args.no_async, "mtp_step_num": mtp,
                             "enable_auto_prefix_cache": wl["prefix_cache"]},
-        "block_manager": {"block_token_num": 16}}})
+        "block_manager": {"block_token_num": 16, "block_device_memory_ratio": args.kv_fraction or -1.0}}})
     ctl = dist.new_group(backend="gloo") if world > 1 else None
 
     res_a = run_phase("device", args, wl, model, serving, tp, ctl, cfg)
