@@ -361,8 +361,10 @@ def main():
     if args.layers:
         cfg.num_layers = args.layers
     is_moe = bool(getattr(cfg, "num_experts", 0))
+    # the fp8 workloads quantise the synthetic weights at load time (128 x 128 block scales, like the checkpoints)
     weights = load_model_weights(cfg, synthetic_seed=0, synthetic_std=0.006 if is_moe else 0.02, tp_rank=rank,
-                                 tp_size=world, device=dev, dtype=torch.bfloat16)
+                                 tp_size=world, device=dev, dtype=torch.bfloat16,
+                                 quantize="fp8_block" if args.model.endswith("-fp8") else None)
     tp.init_fused(cfg.hidden_size, wl["max_step_tokens"])
     model = TransformerModel(cfg, weights, tp, max_positions=max(4096, wl["max_token_len"]))
     mtp = 1 if args.model == "deepseek-v3-fp8" else 0
@@ -395,7 +397,10 @@ def main():
         line = {
             "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(res_a["ms"] / args.steps, 4),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": ("fp8 (e4m3 weights, 128x128 block scales; bf16 activations and KV)"
+                      if args.model.endswith("-fp8") else "bf16"),
+            "data": "synthetic",
             "impl": args.impl,
             "config": {"model": args.model if not args.layers else f"{args.model}-truncated-{args.layers}L-INVALID",
                        "global_batch": wl["max_batch"], "seq_len": wl["seq_len"], "arrivals": wl["arrivals"],

@@ -42,6 +42,16 @@ int ksana_gemm_ll_reduce_norm(const void* A, const void* W, int M, int N, int K,
                               void* const* recv, long long recv_off, void* const* recv2, void* recv2_mc, void* hbuf,
                               int rows_cap, int one_shot, void* residual, const void* norm_w, float eps,
                               unsigned int epoch, int mode, int force_splits, cudaStream_t stream);
+int ksana_ll_reduce_norm(const void* partial, int ldp, int M, int H, int rank, int ws, void* const* recv,
+                         long long recv_off, void* const* recv2, void* recv2_mc, void* hbuf, int rows_cap, int one_shot,
+                         void* residual, const void* norm_w, float eps, unsigned int epoch, int mode,
+                         cudaStream_t stream);
+int ksana_gemm_fp8_block(const void* A8, const float* sa, const void* W8, const float* sw, void* C, const void* bias,
+                         int M, int N, int K, int lda, int ldw, int ldc, int out_fp32, int force_splits, float* ws,
+                         long long ws_floats, unsigned int* counters, int num_counters, cudaStream_t stream);
+int ksana_quant_fp8_group(const void* x, int ldx, void* q, int ldq, float* scales, int T, int K, cudaStream_t stream);
+int ksana_silu_mul_quant_fp8(const void* x, int ldx, void* q, int ldq, float* scales, int T, int I,
+                             cudaStream_t stream);
 void ksana_gemm_set_lane(int lane);
 }
 
@@ -57,6 +67,7 @@ struct Range {
   cudaStream_t stream;
   const char* hcur;  // normalised input rows of the next layer (pointer to row r0)
   int pp;            // ws == 1: which of the two h buffers receives the next norm output
+  const char* h2 = nullptr;  // normalised rows after the attention half, the MLP's input
 };
 
 struct Exec {
@@ -67,6 +78,12 @@ struct Exec {
   int* launches;
   int fail_step, fail_code;
   void* sig_lane[2][8];
+  // Two-batch overlap: the kernels that wait on peers form one chain across both streams (each starts after the
+  // previous one of the chain has finished), in the same order on every rank. Without the chain, rank A can sit in
+  // the first half's reduction while rank B sits in the second half's: each waits for a peer kernel that is queued
+  // behind a GEMM which finds no room beside the waiting CTAs, and both run into the wait limit.
+  cudaEvent_t chain_ev[2] = {nullptr, nullptr};
+  cudaEvent_t chain_prev = nullptr;
 
   unsigned int next_epoch() {
     if (++epoch == 0) ++epoch;
@@ -81,11 +98,58 @@ struct Exec {
     return code == 0;
   }
 
-  // row-parallel GEMM + reduce + residual add + RMSNorm + gather of one range; the output rows land in hbuf
-  int row_parallel(const Range& g, const void* a, const void* wt, int K, const void* norm_w, bool whole_step) {
+  // fp8 staging rows of one range (the two half-batches use disjoint row ranges of the same buffers)
+  uint8_t* a8(const Range& g) const { return static_cast<uint8_t*>(m->a8_buf) + static_cast<size_t>(g.r0) * m->a8_cols; }
+  float* sa(const Range& g) const { return m->sa_buf + static_cast<size_t>(g.r0) * (m->a8_cols / 128); }
+
+  // block-scaled fp8 GEMM over activations that are already in the staging rows; half-batches never split K
+  // (the split-K workspace is shared between the streams)
+  int gemm_f8(const Range& g, const void* wt, const float* sw, void* out, const void* bias, int N, int K, int ldc,
+              bool whole_step) {
+    return ksana_gemm_fp8_block(a8(g), sa(g), wt, sw, out, bias, g.rows, N, K, K, K, ldc, 0, whole_step ? 0 : 1,
+                                m->gemm_ws, m->gemm_ws_floats, m->gemm_counters, m->n_counters, g.stream);
+  }
+
+  // out[rows, N] = a[rows, K] * wt^T (+ bias), bf16 weights or (sw != null) block-scaled e4m3 weights
+  int linear(const Range& g, const void* a, const void* wt, const float* sw, void* out, const void* bias, int N, int K,
+             int ldc, bool whole_step) {
+    if (sw == nullptr)
+      return ksana_gemm_bf16(a, wt, out, bias, g.rows, N, K, K, K, ldc, 0, 0, 0, m->gemm_ws, m->gemm_ws_floats,
+                             m->gemm_counters, m->n_counters, g.stream);
+    const int c = ksana_quant_fp8_group(a, K, a8(g), K, sa(g), g.rows, K, g.stream);
+    if (c != 0) return c;
+    ++(*launches);
+    return gemm_f8(g, wt, sw, out, bias, N, K, ldc, whole_step);
+  }
+
+  // row-parallel GEMM + reduce + residual add + RMSNorm + gather of one range; the output rows land in hbuf.
+  // sw != null: e4m3 weights, `a` is ignored and the activations are taken from the fp8 staging rows.
+  int row_parallel(const Range& g, const void* a, const void* wt, const float* sw, int K, const void* norm_w,
+                   bool whole_step) {
     const int H = m->hidden, T = g.rows;
     char* res = residual + static_cast<size_t>(g.r0) * H * 2;
     const unsigned int ep = next_epoch();
+    if (sw != nullptr) {
+      // fp8: the GEMM writes this rank's partial sum, a second kernel reduces it over the ranks
+      const size_t off = static_cast<size_t>(g.r0) * H * 2;
+      void* partial[8];
+      void* hbuf[8];
+      for (int i = 0; i < m->ws; ++i) {
+        partial[i] = static_cast<char*>(m->partial[i]) + off;
+        hbuf[i] = static_cast<char*>(m->hbuf[i]) + off;
+      }
+      const int c = gemm_f8(g, wt, sw, partial[m->rank], nullptr, H, K, H, whole_step);
+      if (c != 0) return c;
+      ++(*launches);
+      if (whole_step && T <= m->ll_max_tokens && m->ll_recv != nullptr) {
+        ++ll_seq;
+        const long long loff = m->ll_one_shot ? static_cast<long long>(ll_seq & 1u) * m->ll_half_words : 0;
+        return ksana_ll_reduce_norm(partial[m->rank], H, T, H, m->rank, m->ws, m->ll_recv, loff, m->ll_recv2,
+                                    m->ll_recv2_mc, m->hbuf[m->rank], m->ll_rows_cap, m->ll_one_shot, res, norm_w,
+                                    m->eps, ep, 3, g.stream);
+      }
+      return reduce_kernel(g, partial, hbuf, off, res, norm_w, ep, whole_step);
+    }
     // decode-sized steps: one kernel whose chain of NVLink round trips is as short as it gets
     if (whole_step && T <= m->ll_max_tokens && m->ll_recv != nullptr) {
       ++ll_seq;
@@ -109,17 +173,30 @@ struct Exec {
                                     m->gemm_ws_floats, m->gemm_counters, m->n_counters, g.stream);
       if (c != 0) return c;
       ++(*launches);
-      return ksana_rs_norm_ag(m->rank, m->ws, partial, hbuf, sig_lane[g.lane],
-                              m->partial_mc ? static_cast<char*>(m->partial_mc) + off : nullptr,
-                              m->hbuf_mc ? static_cast<char*>(m->hbuf_mc) + off : nullptr, T, H, res, norm_w, m->eps, ep,
-                              3, 0, g.stream);
+      return reduce_kernel(g, partial, hbuf, off, res, norm_w, ep, whole_step);
     }
     return ksana_gemm_rs_norm_ag(a, wt, T, H, K, K, K, m->rank, m->ws, m->recv, m->hbuf, m->sig, m->hbuf_mc, m->rows_cap,
                                  res, norm_w, m->eps, ep, 3, m->comm_ctas, 0, g.stream);
   }
 
-  // one decoder layer over one range
-  bool layer(int L, Range& g, bool whole_step) {
+  // reduce over the ranks + residual add + RMSNorm + gather of a partial sum in the symmetric buffers
+  int reduce_kernel(const Range& g, void* const* partial, void* const* hbuf, size_t off, char* res, const void* norm_w,
+                    unsigned int ep, bool whole_step) {
+    const bool chained = !whole_step && chain_ev[g.lane] != nullptr;
+    if (chained && chain_prev != nullptr) cudaStreamWaitEvent(g.stream, chain_prev, 0);
+    const int rc = ksana_rs_norm_ag(m->rank, m->ws, partial, hbuf, sig_lane[g.lane],
+                                    m->partial_mc ? static_cast<char*>(m->partial_mc) + off : nullptr,
+                                    m->hbuf_mc ? static_cast<char*>(m->hbuf_mc) + off : nullptr, g.rows, m->hidden, res,
+                                    norm_w, m->eps, ep, 3, 0, g.stream);
+    if (chained) {
+      cudaEventRecord(chain_ev[g.lane], g.stream);
+      chain_prev = chain_ev[g.lane];
+    }
+    return rc;
+  }
+
+  // one decoder layer over one range; part 1 = up to the attention output's reduction, part 2 = the MLP, 0 = both
+  bool layer(int L, Range& g, bool whole_step, int part = 0) {
     const KsanaDenseLayer& w = m->layers[L];
     const int T = g.rows, H = m->hidden, h = m->heads, hk = m->kv_heads, d = m->head_dim, I = m->inter;
     const int nq = h * d, nk = hk * d, nqkv = nq + 2 * nk;
@@ -132,9 +209,8 @@ struct Exec {
     char* gu = static_cast<char*>(m->gu_buf) + static_cast<size_t>(g.r0) * 2 * I * 2;
     char* act = static_cast<char*>(m->act_buf) + static_cast<size_t>(g.r0) * I * 2;
     char* res = residual + static_cast<size_t>(g.r0) * H * 2;
-    if (!step(1, ksana_gemm_bf16(g.hcur, w.wqkv, qkv, w.bqkv, T, nqkv, H, H, H, nqkv, 0, 0, 0, m->gemm_ws,
-                                 m->gemm_ws_floats, m->gemm_counters, m->n_counters, st)))
-      return false;
+    if (part == 2) return mlp(w, g, whole_step, gu, act, res);
+    if (!step(1, linear(g, g.hcur, w.wqkv, w.sqkv, qkv, w.bqkv, nqkv, H, nqkv, whole_step))) return false;
     char* q = qkv;
     char* k = qkv + static_cast<size_t>(nq) * 2;
     char* v = qkv + static_cast<size_t>(nq + nk) * 2;
@@ -169,33 +245,43 @@ struct Exec {
                                       aws, aws_floats, st)))
         return false;
     }
-    const char* h2;
+    if (w.so != nullptr && !step(5, ksana_quant_fp8_group(attn, nq, a8(g), nq, sa(g), T, nq, st))) return false;
     if (m->ws > 1) {
-      if (!step(5, row_parallel(g, attn, w.wo, nq, w.ln2, whole_step))) return false;
-      h2 = static_cast<const char*>(m->hbuf[m->rank]) + static_cast<size_t>(g.r0) * H * 2;
+      if (!step(5, row_parallel(g, attn, w.wo, w.so, nq, w.ln2, whole_step))) return false;
+      g.h2 = static_cast<const char*>(m->hbuf[m->rank]) + static_cast<size_t>(g.r0) * H * 2;
     } else {
       char* proj = static_cast<char*>(m->proj_buf) + static_cast<size_t>(g.r0) * H * 2;
       char* hb = static_cast<char*>(m->h_buf[g.pp]) + static_cast<size_t>(g.r0) * H * 2;
-      if (!step(5, ksana_gemm_bf16(attn, w.wo, proj, nullptr, T, H, nq, nq, nq, H, 0, 0, 0, m->gemm_ws,
-                                   m->gemm_ws_floats, m->gemm_counters, m->n_counters, st)))
-        return false;
+      const int c = w.so != nullptr ? gemm_f8(g, w.wo, w.so, proj, nullptr, H, nq, H, whole_step)
+                                    : ksana_gemm_bf16(attn, w.wo, proj, nullptr, T, H, nq, nq, nq, H, 0, 0, 0, m->gemm_ws,
+                                                      m->gemm_ws_floats, m->gemm_counters, m->n_counters, st);
+      if (!step(5, c)) return false;
       if (!step(6, ksana_rms_norm(proj, H, res, H, w.ln2, hb, H, T, H, m->eps, st))) return false;
-      h2 = hb;
+      g.h2 = hb;
       g.pp ^= 1;
     }
-    if (!step(7, ksana_gemm_bf16(h2, w.wgu, gu, nullptr, T, 2 * I, H, H, H, 2 * I, 0, 0, 0, m->gemm_ws,
-                                 m->gemm_ws_floats, m->gemm_counters, m->n_counters, st)))
+    return part == 1 ? true : mlp(w, g, whole_step, gu, act, res);
+  }
+
+  bool mlp(const KsanaDenseLayer& w, Range& g, bool whole_step, char* gu, char* act, char* res) {
+    const int T = g.rows, H = m->hidden, I = m->inter;
+    cudaStream_t st = g.stream;
+    if (!step(7, linear(g, g.h2, w.wgu, w.sgu, gu, nullptr, 2 * I, H, 2 * I, whole_step))) return false;
+    // fp8 down projection: SiLU * up is written once, already quantised
+    if (!step(8, w.sdown != nullptr ? ksana_silu_mul_quant_fp8(gu, 2 * I, a8(g), I, sa(g), T, I, st)
+                                    : ksana_silu_mul(gu, 2 * I, act, I, T, I, st)))
       return false;
-    if (!step(8, ksana_silu_mul(gu, 2 * I, act, I, T, I, st))) return false;
     if (m->ws > 1) {
-      if (!step(9, row_parallel(g, act, w.wdown, I, w.next_ln, whole_step))) return false;
+      if (!step(9, row_parallel(g, act, w.wdown, w.sdown, I, w.next_ln, whole_step))) return false;
       g.hcur = static_cast<const char*>(m->hbuf[m->rank]) + static_cast<size_t>(g.r0) * H * 2;
     } else {
       char* proj = static_cast<char*>(m->proj_buf) + static_cast<size_t>(g.r0) * H * 2;
       char* hb = static_cast<char*>(m->h_buf[g.pp]) + static_cast<size_t>(g.r0) * H * 2;
-      if (!step(9, ksana_gemm_bf16(act, w.wdown, proj, nullptr, T, H, I, I, I, H, 0, 0, 0, m->gemm_ws,
-                                   m->gemm_ws_floats, m->gemm_counters, m->n_counters, st)))
-        return false;
+      const int c = w.sdown != nullptr ? gemm_f8(g, w.wdown, w.sdown, proj, nullptr, H, I, H, whole_step)
+                                       : ksana_gemm_bf16(act, w.wdown, proj, nullptr, T, H, I, I, I, H, 0, 0, 0,
+                                                         m->gemm_ws, m->gemm_ws_floats, m->gemm_counters, m->n_counters,
+                                                         st);
+      if (!step(9, c)) return false;
       if (!step(10, ksana_rms_norm(proj, H, res, H, w.next_ln, hb, H, T, H, m->eps, st))) return false;
       g.hcur = hb;
       g.pp ^= 1;
@@ -207,7 +293,7 @@ struct Exec {
 // second stream + events of the two-batch overlap, one set per device, created on first use
 struct OverlapStreams {
   cudaStream_t side = nullptr;
-  cudaEvent_t fork = nullptr, join = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr, chain[2] = {nullptr, nullptr};
 };
 OverlapStreams g_overlap[64];
 
@@ -220,6 +306,8 @@ OverlapStreams* overlap_streams() {
     if (cudaStreamCreateWithFlags(&o->side, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&o->fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&o->join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    for (int i = 0; i < 2; ++i)
+      if (cudaEventCreateWithFlags(&o->chain[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
   }
   return o;
 }
@@ -264,8 +352,12 @@ KSANA_API int ksana_dense_forward(const KsanaDenseModel* m, const KsanaDenseStep
             static_cast<const char*>(h_in) + static_cast<size_t>(s->split_row) * H * 2, 0};
     cudaEventRecord(os->fork, stream);
     cudaStreamWaitEvent(os->side, os->fork, 0);
+    ex.chain_ev[0] = os->chain[0];
+    ex.chain_ev[1] = os->chain[1];
     for (int L = first; L < last && failed_layer < 0; ++L) {
-      if (!ex.layer(L, a, false) || !ex.layer(L, b, false)) failed_layer = L;
+      if (!ex.layer(L, a, false, 1) || !ex.layer(L, b, false, 1) || !ex.layer(L, a, false, 2) ||
+          !ex.layer(L, b, false, 2))
+        failed_layer = L;
     }
     ksana_gemm_set_lane(0);
     cudaEventRecord(os->join, os->side);

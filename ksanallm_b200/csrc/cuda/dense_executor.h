@@ -17,6 +17,11 @@ struct KsanaDenseLayer {
   const void* q_norm;   // optional per-head RMSNorm weights [d]
   const void* k_norm;
   void* kv_cache;       // [num_blocks, 2, hk, block_size, d]
+  // 128 x 128 block scales (fp32, [ceil(N / 128), K / 128]) of the four weights when they are e4m3; all null: bf16
+  const float* sqkv;
+  const float* so;
+  const float* sgu;
+  const float* sdown;
 };
 
 struct KsanaDenseModel {
@@ -56,6 +61,10 @@ struct KsanaDenseModel {
   float* attn_ws;
   long long attn_ws_floats;
   int sig_words;  // uint32 words of one flag region in `sig`; the second half-batch uses the region after the first
+  // fp8 weights: the activations of each GEMM are quantised (e4m3, one scale per token per 128 channels) into these
+  void* a8_buf;   // [T, a8_cols] bytes
+  float* sa_buf;  // [T, a8_cols / 128]
+  int a8_cols;    // max(H, h d, I)
   const KsanaDenseLayer* layers;
 };
 

@@ -1,8 +1,8 @@
 """Binding of the native dense-layer executor (csrc/cuda/dense_executor.cu): the whole decoder stack of a step is
 launched by one C call instead of ~8 Python-level kernel wrappers per layer.
 
-Eligible models: dense (no MoE / MLA) RMSNorm + RoPE decoders with a gated SiLU FFN, bf16 weights, head_dim 128 and
-the 16-token KV block, on one GPU or tensor-parallel with the single-kernel fused GEMM + reduce-scatter path. Anything
+Eligible models: dense (no MoE / MLA) RMSNorm + RoPE decoders with a gated SiLU FFN, bf16 weights or 128 x 128
+block-scaled e4m3 weights (all four linears of every layer alike), head_dim 128 and the 16-token KV block, on one GPU or tensor-parallel with the single-kernel fused GEMM + reduce-scatter path. Anything
 else keeps the Python layer code in models/transformer.py (same kernels, launched one by one).
 """
 from __future__ import annotations
@@ -21,7 +21,7 @@ P, I, F, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 
 class _Layer(ctypes.Structure):
     _fields_ = [(n, P) for n in ("wqkv", "bqkv", "wo", "ln2", "wgu", "wdown", "next_ln", "q_norm", "k_norm",
-                                 "kv_cache")]
+                                 "kv_cache", "sqkv", "so", "sgu", "sdown")]
 
 
 class _Model(ctypes.Structure):
@@ -33,7 +33,8 @@ class _Model(ctypes.Structure):
                 ("ll_recv2_mc", P), ("ll_half_words", LL), ("ll_rows_cap", I), ("ll_max_tokens", I),
                 ("ll_one_shot", I), ("qkv_buf", P), ("attn_buf", P), ("gu_buf", P), ("act_buf", P), ("proj_buf", P),
                 ("h_buf", P * 2), ("gemm_ws", P), ("gemm_ws_floats", LL), ("gemm_counters", P), ("n_counters", I),
-                ("attn_ws", P), ("attn_ws_floats", LL), ("sig_words", I), ("layers", P)]
+                ("attn_ws", P), ("attn_ws_floats", LL), ("sig_words", I), ("a8_buf", P), ("sa_buf", P), ("a8_cols", I),
+                ("layers", P)]
 
 
 class _Step(ctypes.Structure):
@@ -66,8 +67,19 @@ class DenseExecutor:
             if layer.is_moe or not hasattr(layer.attn, "qkv"):
                 return False
             lins = (layer.attn.qkv, layer.attn.o_proj, layer.ffn.up, layer.ffn.down)
-            if any(l.kind != "dense" for l in lins) or layer.attn.o_proj.bias is not None:
+            kind = model.layers[0].attn.qkv.kind
+            if kind not in ("dense", "fp8_block") or any(l.kind != kind for l in lins):
                 return False
+            if layer.attn.o_proj.bias is not None:
+                return False
+            if kind == "fp8_block":
+                if tp.size > 1 and (tp.fused is None or tp.fused.partial is None):
+                    return False
+                for l in lins:
+                    w, sc = l.weight, l.scale_inv
+                    if (w.shape[1] % 128 or w.shape[0] % 8 or not w.is_contiguous() or sc.dtype != torch.float32 or
+                            not sc.is_contiguous() or tuple(sc.shape) != ((w.shape[0] + 127) // 128, w.shape[1] // 128)):
+                        return False
             if layer.ffn.up.bias is not None or layer.ffn.down.bias is not None or layer.attn.alibi is not None:
                 return False
             if layer.ln2 is None or getattr(layer, "ln2_b", None) is not None:
@@ -99,6 +111,10 @@ class DenseExecutor:
             L.next_ln = _p(nxt)
             L.q_norm, L.k_norm = _p(layer.attn.q_norm), _p(layer.attn.k_norm)
             L.kv_cache = None
+            if layer.attn.qkv.kind == "fp8_block":
+                L.sqkv, L.so = _p(layer.attn.qkv.scale_inv), _p(layer.attn.o_proj.scale_inv)
+                L.sgu, L.sdown = _p(layer.ffn.up.scale_inv), _p(layer.ffn.down.scale_inv)
+        self.fp8 = model.layers[0].attn.qkv.kind == "fp8_block"
         m = self._m = _Model()
         m.hidden, m.heads, m.kv_heads, m.head_dim, m.inter, m.n_layers = self.H, self.h, self.hk, self.d, self.inter, n
         m.eps = float(cfg.rms_norm_eps)
@@ -153,6 +169,12 @@ class DenseExecutor:
         qkv, attn, gu, act = mk(nqkv), mk(self.h * self.d), mk(2 * self.inter), mk(self.inter)
         self._bufs = [qkv, attn, gu, act]
         m = self._m
+        if self.fp8:
+            cols = max(self.H, self.h * self.d, self.inter)
+            a8 = torch.empty(cap, cols, dtype=torch.uint8, device=dev)
+            sa = torch.empty(cap, cols // 128, dtype=torch.float32, device=dev)
+            self._bufs += [a8, sa]
+            m.a8_buf, m.sa_buf, m.a8_cols = _p(a8), _p(sa), cols
         m.qkv_buf, m.attn_buf, m.gu_buf, m.act_buf = _p(qkv), _p(attn), _p(gu), _p(act)
         if self.tp.size == 1:
             proj, h0, h1 = mk(self.H), mk(self.H), mk(self.H)

@@ -187,6 +187,30 @@ def _worker(rank, world, port, use_mc, q):
         torch.cuda.synchronize()
         report["overlap_model_err"] = (h_ov.float() - h_1b.float()).abs().max().item()
         report["overlap_ref_max"] = h_1b.float().abs().max().item()
+    # the same two steps with 128 x 128 block-scaled e4m3 weights (the shards cut at block boundaries, so the
+    # quantised values equal the single-rank model's): fp8 GEMM into the partial buffer + reduce kernel
+    cfg8 = model_config_from_dict(dict(model_type="qwen3", hidden_size=H, num_hidden_layers=2, num_attention_heads=8,
+                                       num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=1000,
+                                       torch_dtype="bfloat16"))
+    w8 = load_model_weights(cfg8, synthetic_seed=5, tp_rank=rank, tp_size=world, device=dev, dtype=torch.bfloat16,
+                            quantize="fp8_block")
+    m8 = TransformerModel(cfg8, w8, tp, max_positions=2048)
+    report["fp8_native"] = m8._native_executor() is not None and m8._native_executor().fp8
+    h8 = m8.forward(meta, m8.allocate_kv_cache(8, 16)).clone()
+    h8_ov = m8.forward(meta2, m8.allocate_kv_cache(blk + 1, 16)).clone()
+    torch.cuda.synchronize()
+    report["fp8_overlap_split"] = int(m8._native_executor()._step.split_seq) if report["fp8_native"] else 0
+    if rank == 0:
+        w8_1 = load_model_weights(cfg8, synthetic_seed=5, device=dev, dtype=torch.bfloat16, quantize="fp8_block")
+        m8_1 = TransformerModel(cfg8, w8_1, TPGroup(), max_positions=2048)
+        r1 = m8_1.forward(meta, m8_1.allocate_kv_cache(8, 16))
+        r2 = m8_1.forward(meta2, m8_1.allocate_kv_cache(blk + 1, 16))
+        torch.cuda.synchronize()
+        report["fp8_err"] = (h8.float() - r1.float()).abs().max().item()
+        report["fp8_overlap_err"] = (h8_ov.float() - r2.float()).abs().max().item()
+        report["fp8_mean_err"] = max((h8.float() - r1.float()).abs().mean().item(),
+                                     (h8_ov.float() - r2.float()).abs().mean().item())
+        report["fp8_ref_max"] = max(r1.float().abs().max().item(), r2.float().abs().max().item())
     dist.barrier()
     report["kernel_error2"] = cuda.read_error()
     if rank == 0:
@@ -243,3 +267,10 @@ def test_fused_reduce_norm_ranks(use_mc, world):
     assert rep["overlap_split"] > 0, "the prefill-sized step did not take the two-stream path"
     assert rep["overlap_err"] < 0.05 * max(1.0, rep["overlap_ref_max"])
     assert rep["overlap_model_err"] < 0.05 * max(1.0, rep["overlap_ref_max"])
+    assert rep["fp8_native"], "the block-scaled fp8 model did not take the native executor"
+    assert rep["fp8_overlap_split"] > 0
+    # a bf16 rounding difference in a partial sum can move an activation across an e4m3 rounding boundary of the next
+    # layer's quantiser, so single elements differ by up to an fp8 step; the mean shows that nothing else does
+    assert rep["fp8_err"] < 0.12 * max(1.0, rep["fp8_ref_max"]), rep
+    assert rep["fp8_overlap_err"] < 0.12 * max(1.0, rep["fp8_ref_max"]), rep
+    assert rep["fp8_mean_err"] < 0.01 * max(1.0, rep["fp8_ref_max"]), rep

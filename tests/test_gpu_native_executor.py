@@ -7,7 +7,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _build(model_type="llama", **over):
+def _build(model_type="llama", quantize=None, **over):
     from ksanallm_b200.config.model_config import model_config_from_dict
     from ksanallm_b200.models.loader import load_model_weights
     from ksanallm_b200.models.transformer import TransformerModel
@@ -15,7 +15,7 @@ def _build(model_type="llama", **over):
              num_key_value_heads=4, intermediate_size=2816, vocab_size=1000, torch_dtype="bfloat16")
     d.update(over)
     cfg = model_config_from_dict(d)
-    w = load_model_weights(cfg, synthetic_seed=4, device="cuda", dtype=torch.bfloat16)
+    w = load_model_weights(cfg, synthetic_seed=4, device="cuda", dtype=torch.bfloat16, quantize=quantize)
     return TransformerModel(cfg, w, max_positions=512)
 
 
@@ -41,7 +41,8 @@ def _mixed_meta():
     return make_step_input(ids, pos, slots, cu, kv_lens, bt, num_prefill=2, device="cuda"), nxt
 
 
-@pytest.mark.parametrize("model_type,extra", [("llama", {}), ("qwen3", {"head_dim": 128}), ("qwen2", {})])
+@pytest.mark.parametrize("model_type,extra", [("llama", {}), ("qwen3", {"head_dim": 128}), ("qwen2", {}),
+                                              ("qwen3", {"head_dim": 128, "quantize": "fp8_block"})])
 def test_native_matches_python_path(model_type, extra):
     from ksanallm_b200.ops import cuda
     m = _build(model_type, **extra)
@@ -58,9 +59,14 @@ def test_native_matches_python_path(model_type, extra):
     out_python = m.forward(meta, kv_b).clone()
     torch.cuda.synchronize()
     assert cuda.read_error() == 0
-    assert torch.equal(out_native, out_python)
+    if extra.get("quantize"):
+        # block-scaled e4m3 weights: same kernels as the Python path (quantise, fp8 GEMM, fused SiLU-mul-quantise)
+        assert m.layers[0].attn.qkv.kind == "fp8_block"
+        assert (out_native.float() - out_python.float()).abs().max().item() <= 2e-2 * out_python.float().abs().max().item()
+    else:
+        assert torch.equal(out_native, out_python)
     for a, b in zip(kv_a, kv_b):
-        assert torch.equal(a, b)
+        assert torch.equal(a, b) or extra.get("quantize")
     assert native_launches >= 8 * 3
 
 
