@@ -52,6 +52,12 @@ int ksana_gemm_fp8_block(const void* A8, const float* sa, const void* W8, const 
 int ksana_quant_fp8_group(const void* x, int ldx, void* q, int ldq, float* scales, int T, int K, cudaStream_t stream);
 int ksana_silu_mul_quant_fp8(const void* x, int ldx, void* q, int ldq, float* scales, int T, int I,
                              cudaStream_t stream);
+int ksana_quant_fp8_ue8m0(const void* x, int ldx, void* q, int ldq, float* scales, void* sfa, int T, int K,
+                          cudaStream_t stream);
+int ksana_silu_mul_quant_ue8m0(const void* x, int ldx, void* q, int ldq, float* scales, void* sfa, int T, int I,
+                               cudaStream_t stream);
+int ksana_gemm_mxf8(const void* A8, const void* sfa, const void* W8, const void* sfb, void* C, const void* bias, int M,
+                    int N, int K, int lda, int ldw, int ldc, int variant, cudaStream_t stream);
 void ksana_gemm_set_lane(int lane);
 }
 
@@ -100,32 +106,47 @@ struct Exec {
 
   // fp8 staging rows of one range (the two half-batches use disjoint row ranges of the same buffers)
   uint8_t* a8(const Range& g) const { return static_cast<uint8_t*>(m->a8_buf) + static_cast<size_t>(g.r0) * m->a8_cols; }
-  float* sa(const Range& g) const { return m->sa_buf + static_cast<size_t>(g.r0) * (m->a8_cols / 128); }
+  // the second half-batch's scales start at a 128-row boundary: the packed layout covers whole 128-row groups
+  float* sa(const Range& g) const {
+    return m->sa_buf + static_cast<size_t>((g.r0 + 127) / 128 * 128) * (m->a8_cols / 128);
+  }
+  // the scaled tensor-core GEMM serves this product (its activations are then staged with packed scale bytes)
+  bool use_mx(const Range& g, const void* sfb) const {
+    return m->fp8_pow2 != 0 && sfb != nullptr && g.rows >= m->mx_min_rows;
+  }
+
+  // activations -> e4m3 staging rows, with the kind of scales the GEMM of this product wants
+  int quant_f8(const Range& g, const void* a, int K, const void* sfb) {
+    if (m->fp8_pow2 == 0) return ksana_quant_fp8_group(a, K, a8(g), K, sa(g), g.rows, K, g.stream);
+    const bool mx = use_mx(g, sfb);
+    return ksana_quant_fp8_ue8m0(a, K, a8(g), K, mx ? nullptr : sa(g), mx ? sa(g) : nullptr, g.rows, K, g.stream);
+  }
 
   // block-scaled fp8 GEMM over activations that are already in the staging rows; half-batches never split K
   // (the split-K workspace is shared between the streams)
-  int gemm_f8(const Range& g, const void* wt, const float* sw, void* out, const void* bias, int N, int K, int ldc,
-              bool whole_step) {
+  int gemm_f8(const Range& g, const void* wt, const float* sw, const void* sfb, void* out, const void* bias, int N,
+              int K, int ldc, bool whole_step) {
+    if (use_mx(g, sfb)) return ksana_gemm_mxf8(a8(g), sa(g), wt, sfb, out, bias, g.rows, N, K, K, K, ldc, 0, g.stream);
     return ksana_gemm_fp8_block(a8(g), sa(g), wt, sw, out, bias, g.rows, N, K, K, K, ldc, 0, whole_step ? 0 : 1,
                                 m->gemm_ws, m->gemm_ws_floats, m->gemm_counters, m->n_counters, g.stream);
   }
 
   // out[rows, N] = a[rows, K] * wt^T (+ bias), bf16 weights or (sw != null) block-scaled e4m3 weights
-  int linear(const Range& g, const void* a, const void* wt, const float* sw, void* out, const void* bias, int N, int K,
-             int ldc, bool whole_step) {
+  int linear(const Range& g, const void* a, const void* wt, const float* sw, const void* sfb, void* out,
+             const void* bias, int N, int K, int ldc, bool whole_step) {
     if (sw == nullptr)
       return ksana_gemm_bf16(a, wt, out, bias, g.rows, N, K, K, K, ldc, 0, 0, 0, m->gemm_ws, m->gemm_ws_floats,
                              m->gemm_counters, m->n_counters, g.stream);
-    const int c = ksana_quant_fp8_group(a, K, a8(g), K, sa(g), g.rows, K, g.stream);
+    const int c = quant_f8(g, a, K, sfb);
     if (c != 0) return c;
     ++(*launches);
-    return gemm_f8(g, wt, sw, out, bias, N, K, ldc, whole_step);
+    return gemm_f8(g, wt, sw, sfb, out, bias, N, K, ldc, whole_step);
   }
 
   // row-parallel GEMM + reduce + residual add + RMSNorm + gather of one range; the output rows land in hbuf.
   // sw != null: e4m3 weights, `a` is ignored and the activations are taken from the fp8 staging rows.
-  int row_parallel(const Range& g, const void* a, const void* wt, const float* sw, int K, const void* norm_w,
-                   bool whole_step) {
+  int row_parallel(const Range& g, const void* a, const void* wt, const float* sw, const void* sfb, int K,
+                   const void* norm_w, bool whole_step) {
     const int H = m->hidden, T = g.rows;
     char* res = residual + static_cast<size_t>(g.r0) * H * 2;
     const unsigned int ep = next_epoch();
@@ -138,7 +159,7 @@ struct Exec {
         partial[i] = static_cast<char*>(m->partial[i]) + off;
         hbuf[i] = static_cast<char*>(m->hbuf[i]) + off;
       }
-      const int c = gemm_f8(g, wt, sw, partial[m->rank], nullptr, H, K, H, whole_step);
+      const int c = gemm_f8(g, wt, sw, sfb, partial[m->rank], nullptr, H, K, H, whole_step);
       if (c != 0) return c;
       ++(*launches);
       if (whole_step && T <= m->ll_max_tokens && m->ll_recv != nullptr) {
@@ -210,7 +231,7 @@ struct Exec {
     char* act = static_cast<char*>(m->act_buf) + static_cast<size_t>(g.r0) * I * 2;
     char* res = residual + static_cast<size_t>(g.r0) * H * 2;
     if (part == 2) return mlp(w, g, whole_step, gu, act, res);
-    if (!step(1, linear(g, g.hcur, w.wqkv, w.sqkv, qkv, w.bqkv, nqkv, H, nqkv, whole_step))) return false;
+    if (!step(1, linear(g, g.hcur, w.wqkv, w.sqkv, w.fqkv, qkv, w.bqkv, nqkv, H, nqkv, whole_step))) return false;
     char* q = qkv;
     char* k = qkv + static_cast<size_t>(nq) * 2;
     char* v = qkv + static_cast<size_t>(nq + nk) * 2;
@@ -245,14 +266,14 @@ struct Exec {
                                       aws, aws_floats, st)))
         return false;
     }
-    if (w.so != nullptr && !step(5, ksana_quant_fp8_group(attn, nq, a8(g), nq, sa(g), T, nq, st))) return false;
+    if (w.so != nullptr && !step(5, quant_f8(g, attn, nq, w.fo))) return false;
     if (m->ws > 1) {
-      if (!step(5, row_parallel(g, attn, w.wo, w.so, nq, w.ln2, whole_step))) return false;
+      if (!step(5, row_parallel(g, attn, w.wo, w.so, w.fo, nq, w.ln2, whole_step))) return false;
       g.h2 = static_cast<const char*>(m->hbuf[m->rank]) + static_cast<size_t>(g.r0) * H * 2;
     } else {
       char* proj = static_cast<char*>(m->proj_buf) + static_cast<size_t>(g.r0) * H * 2;
       char* hb = static_cast<char*>(m->h_buf[g.pp]) + static_cast<size_t>(g.r0) * H * 2;
-      const int c = w.so != nullptr ? gemm_f8(g, w.wo, w.so, proj, nullptr, H, nq, H, whole_step)
+      const int c = w.so != nullptr ? gemm_f8(g, w.wo, w.so, w.fo, proj, nullptr, H, nq, H, whole_step)
                                     : ksana_gemm_bf16(attn, w.wo, proj, nullptr, T, H, nq, nq, nq, H, 0, 0, 0, m->gemm_ws,
                                                       m->gemm_ws_floats, m->gemm_counters, m->n_counters, st);
       if (!step(5, c)) return false;
@@ -266,18 +287,25 @@ struct Exec {
   bool mlp(const KsanaDenseLayer& w, Range& g, bool whole_step, char* gu, char* act, char* res) {
     const int T = g.rows, H = m->hidden, I = m->inter;
     cudaStream_t st = g.stream;
-    if (!step(7, linear(g, g.h2, w.wgu, w.sgu, gu, nullptr, 2 * I, H, 2 * I, whole_step))) return false;
+    if (!step(7, linear(g, g.h2, w.wgu, w.sgu, w.fgu, gu, nullptr, 2 * I, H, 2 * I, whole_step))) return false;
     // fp8 down projection: SiLU * up is written once, already quantised
-    if (!step(8, w.sdown != nullptr ? ksana_silu_mul_quant_fp8(gu, 2 * I, a8(g), I, sa(g), T, I, st)
-                                    : ksana_silu_mul(gu, 2 * I, act, I, T, I, st)))
-      return false;
+    int c8;
+    if (w.sdown == nullptr) {
+      c8 = ksana_silu_mul(gu, 2 * I, act, I, T, I, st);
+    } else if (m->fp8_pow2 == 0) {
+      c8 = ksana_silu_mul_quant_fp8(gu, 2 * I, a8(g), I, sa(g), T, I, st);
+    } else {
+      const bool mx = use_mx(g, w.fdown);
+      c8 = ksana_silu_mul_quant_ue8m0(gu, 2 * I, a8(g), I, mx ? nullptr : sa(g), mx ? sa(g) : nullptr, T, I, st);
+    }
+    if (!step(8, c8)) return false;
     if (m->ws > 1) {
-      if (!step(9, row_parallel(g, act, w.wdown, w.sdown, I, w.next_ln, whole_step))) return false;
+      if (!step(9, row_parallel(g, act, w.wdown, w.sdown, w.fdown, I, w.next_ln, whole_step))) return false;
       g.hcur = static_cast<const char*>(m->hbuf[m->rank]) + static_cast<size_t>(g.r0) * H * 2;
     } else {
       char* proj = static_cast<char*>(m->proj_buf) + static_cast<size_t>(g.r0) * H * 2;
       char* hb = static_cast<char*>(m->h_buf[g.pp]) + static_cast<size_t>(g.r0) * H * 2;
-      const int c = w.sdown != nullptr ? gemm_f8(g, w.wdown, w.sdown, proj, nullptr, H, I, H, whole_step)
+      const int c = w.sdown != nullptr ? gemm_f8(g, w.wdown, w.sdown, w.fdown, proj, nullptr, H, I, H, whole_step)
                                        : ksana_gemm_bf16(act, w.wdown, proj, nullptr, T, H, I, I, I, H, 0, 0, 0,
                                                          m->gemm_ws, m->gemm_ws_floats, m->gemm_counters, m->n_counters,
                                                          st);

@@ -22,6 +22,11 @@ struct KsanaDenseLayer {
   const float* so;
   const float* sgu;
   const float* sdown;
+  // the same scales as packed power-of-two bytes for the scaled tensor-core GEMM (gemm_mxf8.cu); null: not available
+  const void* fqkv;
+  const void* fo;
+  const void* fgu;
+  const void* fdown;
 };
 
 struct KsanaDenseModel {
@@ -63,8 +68,10 @@ struct KsanaDenseModel {
   int sig_words;  // uint32 words of one flag region in `sig`; the second half-batch uses the region after the first
   // fp8 weights: the activations of each GEMM are quantised (e4m3, one scale per token per 128 channels) into these
   void* a8_buf;   // [T, a8_cols] bytes
-  float* sa_buf;  // [T, a8_cols / 128]
+  float* sa_buf;  // [T + 256, a8_cols / 128]: fp32 scales, or the packed scale bytes of the scaled tensor-core GEMM
   int a8_cols;    // max(H, h d, I)
+  int fp8_pow2;     // the weights' block scales are powers of two: activations get power-of-two group scales
+  int mx_min_rows;  // products with at least this many rows (and packed weight scales) take the scaled GEMM
   const KsanaDenseLayer* layers;
 };
 

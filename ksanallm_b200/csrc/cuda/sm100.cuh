@@ -219,6 +219,40 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// ---- hardware block scaling (kind::mxf8f6f4.block_scale) ----
+// Instruction descriptor of the block-scaled kinds: no accumulator-format field (always fp32); bits [4,6) and [29,31)
+// select which byte of the 32-bit scale word of B / A this instruction uses, bit 23 = scales are UE8M0.
+__host__ __device__ constexpr uint32_t umma_idesc_block_scaled(int m, int n, int a_fmt, int b_fmt, int a_sf_id,
+                                                               int b_sf_id) {
+  return (static_cast<uint32_t>(b_sf_id) << 4) | (static_cast<uint32_t>(a_fmt) << 7) |
+         (static_cast<uint32_t>(b_fmt) << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) |
+         (static_cast<uint32_t>(m >> 4) << 24) | (static_cast<uint32_t>(a_sf_id) << 29);
+}
+// Shared-memory descriptor without swizzle for tcgen05.cp of scale factors: rows of 16 bytes, 8-row groups 128 bytes
+// apart.
+__device__ __forceinline__ uint64_t umma_desc_sf(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;  // SBO
+  d |= static_cast<uint64_t>(1) << 46;         // descriptor version (Blackwell)
+  return d;
+}
+// Copies 32 rows x 16 bytes of scale factors from shared memory into 4 TMEM columns, replicated to all four 32-lane
+// groups. Ordered with the tcgen05.mma instructions the same thread issues afterwards.
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// D[tmem] (+)= (A * 2^sfa)[smem] * (B * 2^sfb)[smem]^T: e4m3 / e5m2 inputs, K = 32 per instruction, one UE8M0 scale
+// per row of A and per row of B, read from TMEM.
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
 // A operand from TMEM (used for P*V in attention: P is written to TMEM as bf16 pairs).
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
                                             uint32_t accumulate) {
@@ -306,6 +340,21 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+// The scaled MMA and the scale copy on a CTA pair: one instruction from the leader acts in both CTAs (each copies
+// from its own shared memory into its own TMEM; each multiplies its 128 rows by all N columns, so both hold the
+// scales of every W row).
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
       : "memory");
 }
 // D[tmem of both CTAs] (+)= A * B^T with M = 256 (128 rows per CTA), each CTA holding its own A rows and its

@@ -74,6 +74,10 @@ class LinearW:
                 self.sz = cuda_int4.pack_scale_zero(self.scales, self.zeros)
         elif self.scale_inv is not None:
             self.kind = "fp8_block"
+            # power-of-two block scales: the activations get power-of-two group scales as well, and prefill-sized
+            # products run with the scales applied by the tensor core (packed scale bytes built on first CUDA use)
+            self.pow2 = self.weight.dim() == 2 and ref.is_pow2(self.scale_inv)
+            self._sfb = None
         elif self.weight is not None:
             self.kind = "dense"
         else:
@@ -87,6 +91,18 @@ class LinearW:
     def in_features(self) -> int:
         return self._k if self.kind == "int4" else self.weight.shape[1]
 
+    def sfb(self) -> Optional[torch.Tensor]:
+        """Packed power-of-two scale bytes of an fp8 block-scaled weight for the scaled tensor-core GEMM, or None."""
+        if self.kind != "fp8_block" or not self.pow2 or not self.weight.is_cuda:
+            return None
+        if self._sfb is None:
+            n, k = self.weight.shape
+            if k % 128 or n % 8 or not self.weight.is_contiguous():
+                return None
+            from ..ops import cuda_fp8
+            self._sfb = cuda_fp8.pack_sfb(self.scale_inv, n, k)
+        return self._sfb
+
     def __call__(self, x: torch.Tensor, add_bias: bool = True) -> torch.Tensor:
         b = self.bias if add_bias else None
         if self.pre is not None:
@@ -94,7 +110,7 @@ class LinearW:
         if self.kind == "dense":
             return ops.linear(x, self.weight, b)
         if self.kind == "fp8_block":
-            return ops.linear_fp8_block(x, self.weight, self.scale_inv, b)
+            return ops.linear_fp8_block(x, self.weight, self.scale_inv, b, self.sfb() if x.is_cuda else None, self.pow2)
         return ops.linear_int4(x, self.qweight, self.scales, self.zeros, b, self.group, self.sz)
 
 

@@ -25,6 +25,10 @@ import torch
 from ..config.model_config import ModelConfig
 from ..ops import reference as ref
 
+# Block-scaled e4m3 linear weights are kept with power-of-two scales (KSANA_FP8_POW2_SCALES=0: the checkpoint's own
+# fp32 scales, which only the kernel with per-K-block promotion can take).
+FP8_POW2_SCALES = os.environ.get("KSANA_FP8_POW2_SCALES", "1") != "0"
+
 # ---------------------------------------------------------------------------------------------------
 # name normalisation: architecture-specific HF names -> Llama-style names
 # ---------------------------------------------------------------------------------------------------
@@ -388,11 +392,14 @@ class WeightLoader:
             self.out[prefix + ".zeros"] = self._own(w.zeros.to(self.dtype))
             return
         if scale_inv is not None:
+            if FP8_POW2_SCALES and w.dim() == 2 and w.dtype == torch.float8_e4m3fn:
+                # power-of-two block scales let the tensor core apply them (ops/cuda_fp8.py): one re-rounding at load
+                w, scale_inv = ref.requant_fp8_block_ue8m0(w.to(self.device), scale_inv.to(self.device))
             self.out[prefix + ".weight"] = self._own(w)
             self.out[prefix + ".weight_scale_inv"] = self._own(scale_inv.float())
             return
         if self.quantize == "fp8_block" and w.dim() == 2 and w.shape[1] % 128 == 0:
-            q, s = ref.quant_fp8_block_weight(w.to(self.device).float())
+            q, s = ref.quant_fp8_block_weight(w.to(self.device).float(), ue8m0=FP8_POW2_SCALES)
             self.out[prefix + ".weight"] = q.contiguous()
             self.out[prefix + ".weight_scale_inv"] = s.contiguous()
             return

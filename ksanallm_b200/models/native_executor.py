@@ -21,7 +21,7 @@ P, I, F, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 
 class _Layer(ctypes.Structure):
     _fields_ = [(n, P) for n in ("wqkv", "bqkv", "wo", "ln2", "wgu", "wdown", "next_ln", "q_norm", "k_norm",
-                                 "kv_cache", "sqkv", "so", "sgu", "sdown")]
+                                 "kv_cache", "sqkv", "so", "sgu", "sdown", "fqkv", "fo", "fgu", "fdown")]
 
 
 class _Model(ctypes.Structure):
@@ -34,7 +34,7 @@ class _Model(ctypes.Structure):
                 ("ll_one_shot", I), ("qkv_buf", P), ("attn_buf", P), ("gu_buf", P), ("act_buf", P), ("proj_buf", P),
                 ("h_buf", P * 2), ("gemm_ws", P), ("gemm_ws_floats", LL), ("gemm_counters", P), ("n_counters", I),
                 ("attn_ws", P), ("attn_ws_floats", LL), ("sig_words", I), ("a8_buf", P), ("sa_buf", P), ("a8_cols", I),
-                ("layers", P)]
+                ("fp8_pow2", I), ("mx_min_rows", I), ("layers", P)]
 
 
 class _Step(ctypes.Structure):
@@ -102,6 +102,9 @@ class DenseExecutor:
         self.inter = model.layers[0].ffn.down.weight.shape[1]
         n = len(model.layers)
         self._layers = (_Layer * n)()
+        # power-of-two scales only if every fp8 weight has them: the activation quantiser is chosen per model
+        pow2 = all(getattr(l, "pow2", False) for layer in model.layers
+                   for l in (layer.attn.qkv, layer.attn.o_proj, layer.ffn.up, layer.ffn.down))
         for i, layer in enumerate(model.layers):
             L = self._layers[i]
             nxt = model.layers[i + 1].ln1 if i + 1 < n else model.norm_w
@@ -114,6 +117,9 @@ class DenseExecutor:
             if layer.attn.qkv.kind == "fp8_block":
                 L.sqkv, L.so = _p(layer.attn.qkv.scale_inv), _p(layer.attn.o_proj.scale_inv)
                 L.sgu, L.sdown = _p(layer.ffn.up.scale_inv), _p(layer.ffn.down.scale_inv)
+                if pow2:
+                    L.fqkv, L.fo = _p(layer.attn.qkv.sfb()), _p(layer.attn.o_proj.sfb())
+                    L.fgu, L.fdown = _p(layer.ffn.up.sfb()), _p(layer.ffn.down.sfb())
         self.fp8 = model.layers[0].attn.qkv.kind == "fp8_block"
         m = self._m = _Model()
         m.hidden, m.heads, m.kv_heads, m.head_dim, m.inter, m.n_layers = self.H, self.h, self.hk, self.d, self.inter, n
@@ -146,6 +152,9 @@ class DenseExecutor:
         m.gemm_counters, m.n_counters = _p(ws.gemm_counters), ws.gemm_counters.numel()
         m.attn_ws, m.attn_ws_floats = _p(ws.attn_ws), ws.attn_ws.numel()
         m.layers = ctypes.cast(self._layers, P)
+        if self.fp8:
+            from ..ops import cuda_fp8
+            m.fp8_pow2, m.mx_min_rows = int(pow2), cuda_fp8.MXF8_MIN_ROWS
         self.cap = 0
         self.overlap_min_tokens = int(os.environ.get("KSANA_OVERLAP_MIN_TOKENS", "1024"))
         self._bufs: List[torch.Tensor] = []
@@ -172,7 +181,7 @@ class DenseExecutor:
         if self.fp8:
             cols = max(self.H, self.h * self.d, self.inter)
             a8 = torch.empty(cap, cols, dtype=torch.uint8, device=dev)
-            sa = torch.empty(cap, cols // 128, dtype=torch.float32, device=dev)
+            sa = torch.empty(cap + 256, cols // 128, dtype=torch.float32, device=dev)
             self._bufs += [a8, sa]
             m.a8_buf, m.sa_buf, m.a8_cols = _p(a8), _p(sa), cols
         m.qkv_buf, m.attn_buf, m.gu_buf, m.act_buf = _p(qkv), _p(attn), _p(gu), _p(act)

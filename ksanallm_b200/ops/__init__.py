@@ -43,10 +43,12 @@ def linear(x, weight, bias=None):
     return ref.linear(x, weight, bias)
 
 
-def linear_fp8_block(x, wq, w_scale_inv, bias=None):
+def linear_fp8_block(x, wq, w_scale_inv, bias=None, sfb=None, pow2=False):
+    """``pow2``: the weight's block scales are powers of two; the activations then get power-of-two group scales
+    too and (CUDA, ``sfb`` = the packed scale bytes) large products run on the scaled tensor-core path."""
     if x.is_cuda:
-        return _cuda().linear_fp8_block(x, wq, w_scale_inv, bias)
-    return ref.linear_fp8_block(x, wq, w_scale_inv, bias)
+        return _cuda().linear_fp8_block(x, wq, w_scale_inv, bias, sfb, pow2)
+    return ref.linear_fp8_block(x, wq, w_scale_inv, bias, ue8m0=pow2)
 
 
 def linear_int4(x, packed, scales, zeros, bias=None, group=128, sz=None):

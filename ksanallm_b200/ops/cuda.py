@@ -59,6 +59,12 @@ class _Sig:
     ksana_embedding = ([P, P, P, I, I, I, F, P], I)
     ksana_rope_cache = ([P, I, P, I, P, I, P, P, P, P, P, P, F, I, I, I, I, I, I, I, I, F, F, P], I)
     ksana_quant_fp8_group = ([P, I, P, I, P, I, I, P], I)
+    ksana_mxf8_sfa_bytes = ([I, I], LL)
+    ksana_mxf8_sfb_bytes = ([I, I], LL)
+    ksana_mxf8_pack_sfb = ([P, P, I, I, P, P], I)
+    ksana_quant_fp8_ue8m0 = ([P, I, P, I, P, P, I, I, P], I)
+    ksana_silu_mul_quant_ue8m0 = ([P, I, P, I, P, P, I, I, P], I)
+    ksana_gemm_mxf8 = ([P, P, P, P, P, P, I, I, I, I, I, I, I, P], I)
     ksana_paged_decode = ([P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, F, P, F, F, P, I, P, LL, P], I)
     ksana_paged_prefill = ([P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I, F, P, P, I, P], I)
     ksana_paged_decode_gqa = ([P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, F, P, I, P, LL, P], I)
@@ -169,9 +175,9 @@ def gemm_fp8_block(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws_inv:
     return out
 
 
-def linear_fp8_block(x, wq, w_scale_inv, bias=None):
+def linear_fp8_block(x, wq, w_scale_inv, bias=None, sfb=None, pow2=False):
     from . import cuda_fp8
-    return cuda_fp8.linear_fp8_block(x, wq, w_scale_inv, bias)
+    return cuda_fp8.linear_fp8_block(x, wq, w_scale_inv, bias, sfb, pow2)
 
 
 def linear_int4(x, packed, scales, zeros, bias=None, group=128, sz=None):

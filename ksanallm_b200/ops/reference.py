@@ -90,20 +90,35 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> tor
 FP8_MAX = 448.0
 
 
-def quant_fp8_group(x: torch.Tensor, group: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Per-token 1 x ``group`` dynamic e4m3 quantisation: returns (q[T, K] fp8, scale[T, K/group] fp32)."""
+def pow2_ceil(s: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= s (s > 0, fp32): the UE8M0 scale the tensor core can apply itself."""
+    m, e = torch.frexp(s.float())  # s = m * 2^e, m in [0.5, 1)
+    return torch.ldexp(torch.ones_like(m), torch.where(m == 0.5, e - 1, e))
+
+
+def is_pow2(s: torch.Tensor) -> bool:
+    m, _ = torch.frexp(s.float())
+    return bool(((m == 0.5) & (s > 0)).all())
+
+
+def quant_fp8_group(x: torch.Tensor, group: int = 128, ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-token 1 x ``group`` dynamic e4m3 quantisation: returns (q[T, K] fp8, scale[T, K/group] fp32).
+    ``ue8m0``: the scale is rounded up to a power of two."""
     T, K = x.shape
     assert K % group == 0
     xf = x.float().view(T, K // group, group)
-    amax = xf.abs().amax(-1).clamp_min(1e-10)
-    scale = amax / FP8_MAX
+    if ue8m0:
+        scale = pow2_ceil(xf.abs().amax(-1).clamp_min(1e-30) / FP8_MAX)
+    else:
+        amax = xf.abs().amax(-1).clamp_min(1e-10)
+        scale = amax / FP8_MAX
     q = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q.view(T, K), scale
 
 
-def quant_fp8_block_weight(w: torch.Tensor, block: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+def quant_fp8_block_weight(w: torch.Tensor, block: int = 128, ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """128x128 block-scaled e4m3 weight: returns (q[N, K] fp8, scale_inv[ceil(N/b), ceil(K/b)] fp32)
-    with ``w ~= q * scale_inv`` (the checkpoint convention ``weight_scale_inv``)."""
+    with ``w ~= q * scale_inv`` (the checkpoint convention ``weight_scale_inv``). ``ue8m0``: power-of-two scales."""
     N, K = w.shape
     nb, kb = (N + block - 1) // block, (K + block - 1) // block
     wp = torch.zeros(nb * block, kb * block, dtype=torch.float32, device=w.device)
@@ -111,8 +126,21 @@ def quant_fp8_block_weight(w: torch.Tensor, block: int = 128) -> Tuple[torch.Ten
     blocks = wp.view(nb, block, kb, block)
     amax = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-10)
     scale = amax / FP8_MAX
+    if ue8m0:
+        scale = pow2_ceil(scale)
     q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q.view(nb * block, kb * block)[:N, :K].contiguous(), scale
+
+
+def requant_fp8_block_ue8m0(q: torch.Tensor, scale_inv: torch.Tensor,
+                            block: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Re-expresses a block-scaled e4m3 weight with power-of-two scales: every block's scale is rounded up to a
+    power of two and its values are re-rounded to e4m3 on the coarser grid (ratio in (0.5, 1], at most one extra
+    rounding step per element)."""
+    N, K = q.shape
+    new = pow2_ceil(scale_inv.float())
+    ratio = (scale_inv.float() / new).repeat_interleave(block, 0)[:N].repeat_interleave(block, 1)[:, :K]
+    return (q.float() * ratio).to(torch.float8_e4m3fn), new
 
 
 def dequant_fp8_block_weight(q: torch.Tensor, scale_inv: torch.Tensor, block: int = 128) -> torch.Tensor:
@@ -122,11 +150,12 @@ def dequant_fp8_block_weight(q: torch.Tensor, scale_inv: torch.Tensor, block: in
 
 
 def linear_fp8_block(x: torch.Tensor, wq: torch.Tensor, w_scale_inv: torch.Tensor,
-                     bias: Optional[torch.Tensor] = None, block: int = 128) -> torch.Tensor:
+                     bias: Optional[torch.Tensor] = None, block: int = 128, ue8m0: bool = False) -> torch.Tensor:
     """bf16 activations are quantised per token per 128 channels, weights are 128x128 block-scaled e4m3;
-    accumulation is fp32 with the scales applied per K-block (same math the tcgen05 kernel performs)."""
+    accumulation is fp32 with the scales applied per K-block (same math the tcgen05 kernel performs).
+    ``ue8m0``: the activation scales are powers of two (the weights' are whatever ``w_scale_inv`` holds)."""
     T, K = x.shape
-    xq, xs = quant_fp8_group(x, block)
+    xq, xs = quant_fp8_group(x, block, ue8m0)
     xd = (xq.float().view(T, K // block, block) * xs.unsqueeze(-1)).view(T, K)
     y = xd @ dequant_fp8_block_weight(wq, w_scale_inv, block).t()
     if bias is not None:
