@@ -17,11 +17,14 @@
 //   warps 2-5 epilogue: TMEM -> bf16 -> global, overlapped with the next tile's K loop (two accumulators in TMEM)
 // TMEM columns: [0, 192) and [192, 384) accumulators, then four sets of 4 columns of A scales + 8 of W scales.
 //
-// Scale layouts in global memory (one byte per row per 32 K elements, so a 1 x 128 group repeats its byte 4 times):
-//   sfa: [ceil(M / 128)][K / 128][512]   byte (r % 32) * 16 + (r / 32) * 4 + c   for row r of the 128-row group, c < 4
-//   sfb: [K / 128][ceil(N / 192)][2][512] the same 512-byte pattern for rows nt * 192 + j * 128 + r of W (j < 2)
-// which is the order tcgen05.cp (32 x 128 bit, replicated to the four lane groups) expects in shared memory, so a
-// stage's scales arrive with one plain bulk copy each.
+// Scale layouts in global memory. The hardware keeps 4 scale bytes per row in one 32-bit TMEM word and an MMA picks one
+// of them; here the 4 bytes are the scales of 4 CONSECUTIVE 128-wide K groups, so one 512-byte block serves 4 stages
+// (copying scales into TMEM every stage costs ~10 % of the GEMM, measured):
+//   sfa: [ceil(M / 128)][ceil(K / 512)][512]   byte (r % 32) * 16 + (r / 32) * 4 + c: row r of the 128-row group,
+//                                              K group 4 q + c of the q-th block
+//   sfb: [ceil(K / 512)][ceil(N / 192)][2][512] the same 512-byte pattern for rows nt * 192 + j * 128 + r of W (j < 2)
+// which is the order tcgen05.cp (32 x 128 bit, replicated to the four lane groups) expects in shared memory, so the
+// scales arrive with one plain bulk copy each in every fourth stage.
 #include "host_common.h"
 #include "sm100.cuh"
 
@@ -86,7 +89,8 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         const int mt = tile % tiles_m, nt = tile / tiles_m;
-        const uint8_t* sfa_t = sfa + static_cast<size_t>(mt) * num_kb * MX_SFA_BYTES;
+        const int num_q = (num_kb + 3) >> 2;
+        const uint8_t* sfa_t = sfa + static_cast<size_t>(mt) * num_q * MX_SFA_BYTES;
         const uint8_t* sfb_t = sfb + static_cast<size_t>(nt) * MX_SFB_BYTES;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, err)) {
@@ -94,13 +98,16 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             break;
           }
           uint8_t* sa = smem + stage * MX_STAGE_PITCH;
-          mbar_expect_tx(&full_bar[stage], MX_STAGE);
+          const bool sf = (kb & 3) == 0;  // this stage also carries the scales of k blocks kb .. kb + 3
+          mbar_expect_tx(&full_bar[stage], sf ? MX_STAGE : MX_A_BYTES + MX_B_BYTES);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * MX_BK, mt * MX_BM);
           tma_load_2d(sa + MX_A_BYTES, &tmB, &full_bar[stage], kb * MX_BK, nt * MX_BN);
-          bulk_load(sa + MX_A_BYTES + MX_B_BYTES, sfa_t + static_cast<size_t>(kb) * MX_SFA_BYTES, MX_SFA_BYTES,
-                    &full_bar[stage]);
-          bulk_load(sa + MX_A_BYTES + MX_B_BYTES + MX_SFA_BYTES,
-                    sfb_t + static_cast<size_t>(kb) * tiles_n * MX_SFB_BYTES, MX_SFB_BYTES, &full_bar[stage]);
+          if (sf) {
+            bulk_load(sa + MX_A_BYTES + MX_B_BYTES, sfa_t + static_cast<size_t>(kb >> 2) * MX_SFA_BYTES, MX_SFA_BYTES,
+                      &full_bar[stage]);
+            bulk_load(sa + MX_A_BYTES + MX_B_BYTES + MX_SFA_BYTES,
+                      sfb_t + static_cast<size_t>(kb >> 2) * tiles_n * MX_SFB_BYTES, MX_SFB_BYTES, &full_bar[stage]);
+          }
           if (++stage == MX_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -125,17 +132,21 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * MX_STAGE_PITCH);
           const uint32_t ssf = sa + MX_A_BYTES + MX_B_BYTES;
+          if ((kb & 3) == 0) {
+            sf_set = (sf_set + 1) & (MX_SF_SETS - 1);
+            const uint32_t t = tmem_base + sf_set * MX_TMEM_SF_SET;
+            tmem_cp_sf(t + MX_TMEM_SFA, umma_desc_sf(ssf));
+            tmem_cp_sf(t + MX_TMEM_SFB, umma_desc_sf(ssf + MX_SFA_BYTES));
+            tmem_cp_sf(t + MX_TMEM_SFB + 4, umma_desc_sf(ssf + MX_SFA_BYTES + 512));
+          }
           const uint32_t t_sfa = tmem_base + MX_TMEM_SFA + sf_set * MX_TMEM_SF_SET;
           const uint32_t t_sfb = tmem_base + MX_TMEM_SFB + sf_set * MX_TMEM_SF_SET;
-          sf_set = (sf_set + 1) & (MX_SF_SETS - 1);
-          tmem_cp_sf(t_sfa, umma_desc_sf(ssf));
-          tmem_cp_sf(t_sfb, umma_desc_sf(ssf + MX_SFA_BYTES));
-          tmem_cp_sf(t_sfb + 4, umma_desc_sf(ssf + MX_SFA_BYTES + 512));
+          const int sf_id = kb & 3;
           const uint64_t da = umma_desc_k128(sa), db = umma_desc_k128(sa + MX_A_BYTES);
+          const uint32_t idesc = umma_idesc_block_scaled(MX_BM, MX_BN, 0, 0, sf_id, sf_id);
 #pragma unroll
           for (int k = 0; k < MX_BK / 32; ++k)
-            umma_mxf8(tmem_base + as * MX_BN, da + 2 * k, db + 2 * k,
-                      umma_idesc_block_scaled(MX_BM, MX_BN, 0, 0, k, k), t_sfa, t_sfb, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_mxf8(tmem_base + as * MX_BN, da + 2 * k, db + 2 * k, idesc, t_sfa, t_sfb, (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
           if (++stage == MX_STAGES) {
             stage = 0;
@@ -290,18 +301,22 @@ gemm_mxf8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const int atom = mt * 2 + static_cast<int>(cta);
         const int row0 = atom * MX_BM;
         const int wrow0 = nt * MX_BN + static_cast<int>(cta) * MP_HALF_N;
+        const int num_q = (num_kb + 3) >> 2;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, err)) {
             ok = false;
             break;
           }
           uint8_t* sa = smem + stage * MP_STAGE_PITCH;
-          if (cta == 0) mbar_expect_tx(&full_bar[stage], 2 * MP_STAGE);
+          const bool sf = (kb & 3) == 0;  // this stage also carries the scales of k blocks kb .. kb + 3
+          if (cta == 0) mbar_expect_tx(&full_bar[stage], 2 * (sf ? MP_STAGE : MP_SF_OFF));
           const uint32_t leader_full = mapa_u32(smem_u32(&full_bar[stage]), 0);
           tma_load_2d_pair(sa, &tmA, leader_full, kb * MX_BK, row0);
           tma_load_2d_pair(sa + MX_A_BYTES, &tmB, leader_full, kb * MX_BK, wrow0);
-          tma_load_2d_pair(sa + MP_SF_OFF, &tmSFA, leader_full, 0, atom * num_kb + kb);
-          tma_load_2d_pair(sa + MP_SF_OFF + MX_SFA_BYTES, &tmSFB, leader_full, 0, kb * tiles_n + nt);
+          if (sf) {
+            tma_load_2d_pair(sa + MP_SF_OFF, &tmSFA, leader_full, 0, atom * num_q + (kb >> 2));
+            tma_load_2d_pair(sa + MP_SF_OFF + MX_SFA_BYTES, &tmSFB, leader_full, 0, (kb >> 2) * tiles_n + nt);
+          }
           if (++stage == MP_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -326,17 +341,20 @@ gemm_mxf8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * MP_STAGE_PITCH);
           const uint32_t ssf = sa + MP_SF_OFF;
+          if ((kb & 3) == 0) {
+            sf_set = (sf_set + 1) & (MX_SF_SETS - 1);
+            const uint32_t t = tmem_base + sf_set * MX_TMEM_SF_SET;
+            tmem_cp_sf_pair(t + MX_TMEM_SFA, umma_desc_sf(ssf));
+            tmem_cp_sf_pair(t + MX_TMEM_SFB, umma_desc_sf(ssf + MX_SFA_BYTES));
+            tmem_cp_sf_pair(t + MX_TMEM_SFB + 4, umma_desc_sf(ssf + MX_SFA_BYTES + 512));
+          }
           const uint32_t t_sfa = tmem_base + MX_TMEM_SFA + sf_set * MX_TMEM_SF_SET;
           const uint32_t t_sfb = tmem_base + MX_TMEM_SFB + sf_set * MX_TMEM_SF_SET;
-          sf_set = (sf_set + 1) & (MX_SF_SETS - 1);
-          tmem_cp_sf_pair(t_sfa, umma_desc_sf(ssf));
-          tmem_cp_sf_pair(t_sfb, umma_desc_sf(ssf + MX_SFA_BYTES));
-          tmem_cp_sf_pair(t_sfb + 4, umma_desc_sf(ssf + MX_SFA_BYTES + 512));
+          const uint32_t idesc = umma_idesc_block_scaled(2 * MX_BM, MX_BN, 0, 0, kb & 3, kb & 3);
           const uint64_t da = umma_desc_k128(sa), db = umma_desc_k128(sa + MX_A_BYTES);
 #pragma unroll
           for (int k = 0; k < MX_BK / 32; ++k)
-            umma_mxf8_pair(tmem_base + as * MX_BN, da + 2 * k, db + 2 * k,
-                           umma_idesc_block_scaled(2 * MX_BM, MX_BN, 0, 0, k, k), t_sfa, t_sfb,
+            umma_mxf8_pair(tmem_base + as * MX_BN, da + 2 * k, db + 2 * k, idesc, t_sfa, t_sfb,
                            (kb > 0 || k > 0) ? 1u : 0u);
           const uint32_t eb = smem_u32(&empty_bar[stage]);
           umma_commit_pair(eb);               // my producer may refill the stage
@@ -421,15 +439,15 @@ __device__ __forceinline__ uint32_t ue8m0_scale(float amax, float* inv) {
   return e;
 }
 
-// where the 4 scale bytes of (row, K group g) live in the packed A-scale layout
+// where the scale byte of (row, K group g) lives in the packed A-scale layout
 __device__ __forceinline__ size_t sfa_offset(int row, int g, int groups) {
   const int r = row & 127;
-  return (static_cast<size_t>(row >> 7) * groups + g) * 512 + (r & 31) * 16 + (r >> 5) * 4;
+  return (static_cast<size_t>(row >> 7) * ((groups + 3) >> 2) + (g >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (g & 3);
 }
 
 __device__ __forceinline__ void store_scale(uint32_t e, int t, int g, int groups, float* scales, uint8_t* sfa) {
   if (scales != nullptr) scales[static_cast<size_t>(t) * groups + g] = __uint_as_float(e << 23);
-  if (sfa != nullptr) *reinterpret_cast<uint32_t*>(sfa + sfa_offset(t, g, groups)) = e * 0x01010101u;
+  if (sfa != nullptr) sfa[sfa_offset(t, g, groups)] = static_cast<uint8_t>(e);
 }
 
 // max over the 8 lanes that share a 128-column group
@@ -490,7 +508,7 @@ quant_fp8_ue8m0_kernel(const __nv_bfloat16* __restrict__ x, int ldx, __nv_fp8_e4
   amax = group8_max(amax);
   if (!in_range) return;
   if (!real) {
-    if (sub == 0 && sfa != nullptr) *reinterpret_cast<uint32_t*>(sfa + sfa_offset(t, g, groups)) = 0x7F7F7F7Fu;
+    if (sub == 0 && sfa != nullptr) sfa[sfa_offset(t, g, groups)] = 127;
     return;
   }
   float inv;
@@ -531,7 +549,7 @@ silu_mul_quant_ue8m0_kernel(const __nv_bfloat16* __restrict__ x, int ldx, __nv_f
   amax = group8_max(amax);
   if (!in_range) return;
   if (!real) {
-    if (sub == 0 && sfa != nullptr) *reinterpret_cast<uint32_t*>(sfa + sfa_offset(t, g, groups)) = 0x7F7F7F7Fu;
+    if (sub == 0 && sfa != nullptr) sfa[sfa_offset(t, g, groups)] = 127;
     return;
   }
   float inv;
@@ -556,8 +574,8 @@ __global__ void pack_sfb_kernel(const float* __restrict__ sw, uint8_t* __restric
     e = (bits >> 23) & 0xFFu;
     if ((bits & 0x807FFFFFu) != 0u || e == 0u || e == 255u) atomicExch(bad, 1);  // not a positive power of two
   }
-  *reinterpret_cast<uint32_t*>(sfb + (static_cast<size_t>(kb) * tiles_n + nt) * MX_SFB_BYTES + j * 512 + (r & 31) * 16 +
-                               (r >> 5) * 4) = e * 0x01010101u;
+  sfb[(static_cast<size_t>(kb >> 2) * tiles_n + nt) * MX_SFB_BYTES + j * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] =
+      static_cast<uint8_t>(e);
 }
 
 }  // namespace ksana
@@ -566,10 +584,10 @@ using namespace ksana;
 
 // Bytes of the packed scale arrays for an [M, K] activation / [N, K] weight.
 KSANA_API long long ksana_mxf8_sfa_bytes(int M, int K) {
-  return static_cast<long long>((M + 127) / 128) * (K / 128) * MX_SFA_BYTES;
+  return static_cast<long long>((M + 127) / 128) * ((K / 128 + 3) / 4) * MX_SFA_BYTES;
 }
 KSANA_API long long ksana_mxf8_sfb_bytes(int N, int K) {
-  return static_cast<long long>((N + MX_BN - 1) / MX_BN) * (K / 128) * MX_SFB_BYTES;
+  return static_cast<long long>((N + MX_BN - 1) / MX_BN) * ((K / 128 + 3) / 4) * MX_SFB_BYTES;
 }
 
 // sw: fp32 [ceil(N / 128), K / 128], every entry a power of two -> sfb (ksana_mxf8_sfb_bytes(N, K) bytes).
@@ -645,10 +663,11 @@ KSANA_API int ksana_gemm_mxf8(const void* A8, const void* sfa, const void* W8, c
   // the scale arrays as 2-d tensors of 32-bit words: one row per (128-row group, k block) / (k block, n tile)
   CUtensorMap tmSFA, tmSFB;
   const uint64_t m_atoms = (M + MX_BM - 1) / MX_BM;
-  if (make_tmap_2d(&tmSFA, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, m_atoms * num_kb, MX_SFA_BYTES / 4, MX_SFA_BYTES / 4, 1,
+  const uint64_t num_q = (num_kb + 3) / 4;
+  if (make_tmap_2d(&tmSFA, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, m_atoms * num_q, MX_SFA_BYTES / 4, MX_SFA_BYTES / 4, 1,
                    MX_SFA_BYTES / 4, CU_TENSOR_MAP_SWIZZLE_NONE))
     return -2;
-  if (make_tmap_2d(&tmSFB, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, static_cast<uint64_t>(num_kb) * tiles_n,
+  if (make_tmap_2d(&tmSFB, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, num_q * tiles_n,
                    MX_SFB_BYTES / 4, MX_SFB_BYTES / 4, 1, MX_SFB_BYTES / 4, CU_TENSOR_MAP_SWIZZLE_NONE))
     return -3;
   if (KSANA_SMEM_ONCE(gemm_mxf8_pair_kernel, MP_SMEM) != 0) return -4;
