@@ -48,16 +48,25 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 #ifndef KSANA_PEER_TIMEOUT_NS
 #define KSANA_PEER_TIMEOUT_NS 8000000000ull  // ranks may be skewed by host work; a lost peer still ends the wait
 #endif
+#ifndef KSANA_PEER_TIMEOUT_AFTER_FAILURE_NS
+#define KSANA_PEER_TIMEOUT_AFTER_FAILURE_NS 1000000ull  // once a peer wait has expired on this GPU: 1 ms per wait
+#endif
 // Waits until *p >= want (epochs / counters only grow within a call). Bounded by wall time: returns false and
-// records KERR_PEER_TIMEOUT on expiry, so a missing peer can never hang the GPU.
+// records KERR_PEER_TIMEOUT on expiry, so a missing peer can never hang the GPU. The full bound is paid once: while
+// the status word carries KERR_PEER_TIMEOUT (until the host has read and cleared it) every further wait gives up
+// after a millisecond, so the kernels queued behind a lost peer drain in milliseconds instead of 8 s each.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, unsigned int* err,
                                              unsigned long long timeout_ns = KSANA_PEER_TIMEOUT_NS) {
   for (int it = 0; it < 64; ++it)
     if (static_cast<int32_t>(ld_acquire_sys(p) - want) >= 0) return true;
   const unsigned long long t0 = global_timer_ns();
+  unsigned int polls = 0;
   while (true) {
     if (static_cast<int32_t>(ld_acquire_sys(p) - want) >= 0) return true;
     __nanosleep(400);
+    if (err != nullptr && (++polls & 255u) == 0u && timeout_ns > KSANA_PEER_TIMEOUT_AFTER_FAILURE_NS &&
+        (*reinterpret_cast<volatile unsigned int*>(err) & KERR_PEER_TIMEOUT) != 0u)
+      timeout_ns = KSANA_PEER_TIMEOUT_AFTER_FAILURE_NS;
     if (global_timer_ns() - t0 > timeout_ns) break;
   }
   if (err) atomicOr(err, KERR_PEER_TIMEOUT);

@@ -102,7 +102,12 @@ __device__ __forceinline__ bool ll_poll8(const uint2* p, uint32_t epoch, uint4* 
     *wa = ld_volatile16(p);
     *wb = ld_volatile16(p + 2);
     if (wa->y == epoch && wa->w == epoch && wb->y == epoch && wb->w == epoch) return true;
-    if (global_timer_ns() - t0 > KSANA_PEER_TIMEOUT_NS) {
+    const unsigned long long dt = global_timer_ns() - t0;
+    // after a millisecond: give up at once if an earlier wait on this GPU has already expired (the host has not yet
+    // read the status word), otherwise keep waiting up to the full bound
+    if (dt > KSANA_PEER_TIMEOUT_NS ||
+        (dt > KSANA_PEER_TIMEOUT_AFTER_FAILURE_NS &&
+         (*reinterpret_cast<volatile unsigned int*>(err) & KERR_PEER_TIMEOUT) != 0u)) {
       atomicOr(err, KERR_PEER_TIMEOUT);
       *alive = false;
     }

@@ -185,6 +185,14 @@ class LLMEngine:
         self.adp_balance = None     # parallel.attn_dp.ADPBalance (attention_dp_lb_config.enable_balance)
         self._check_blocks = bool(getattr(bm_cfg, "enable_block_checksum", False))
         self._status_every = int(os.environ.get("KSANA_STATUS_CHECK_STEPS", "64"))  # 0: never read the status word
+        # A step that took longer than this is suspected of having sat in a bounded peer wait (8 s in the kernels):
+        # the status word is then read right away instead of at the next periodic check. Kept below the kernels' bound
+        # and far below the heartbeat timeout, so a lost peer is reported by whichever notices first.
+        self._slow_step_s = float(os.environ.get("KSANA_STATUS_SLOW_STEP_S", "4"))
+        self._last_apply = time.perf_counter()
+        # set when the device status word was found non-zero: what the kernels of recent steps produced is not to be
+        # trusted. A multi-rank instance then refuses new requests (its ranks no longer agree on what they computed).
+        self.device_fault: Optional[str] = None
         self._ctl_ops: List[Tuple[Dict[str, Any], threading.Event]] = []  # control messages for the follower ranks
         self.on_control: Optional[Callable[[Dict[str, Any]], None]] = None   # follower side: handler of such messages
         self.dp_router = None       # parallel.attn_dp.DPRequestRouter on the rank that owns the HTTP front-end
@@ -241,6 +249,8 @@ class LLMEngine:
         parallelism the request may be placed on another DP rank (``local`` forces this rank)."""
         params = params or SamplingParams()
         params.verify()
+        if self.refusing_requests():
+            raise EngineError(_host.FINISH_ERROR, f"this instance no longer accepts requests: {self.device_fault}")
         now = time.time()
         req = Request(next(self._ids), list(int(t) for t in prompt_tokens), params, now)
         req.refit, req.grammar, req.probe = refit, grammar, probe
@@ -349,6 +359,10 @@ class LLMEngine:
                 any(x is not None for x in getattr(self, "_mb_inflight", ())))
 
     # ---- one step ----------------------------------------------------------------------------------------
+    def refusing_requests(self) -> bool:
+        """True once a device fault was seen on an instance of several ranks."""
+        return self.device_fault is not None and (self.tp.size > 1 or self.pipeline is not None or self.dp is not None)
+
     def step(self) -> int:
         """Schedules and runs one step. Returns the number of tokens generated."""
         if self._ctl_ops:
@@ -595,8 +609,15 @@ class LLMEngine:
         # reading the status word waits for the device: cheap after a synchronous step (it is idle), but under
         # asynchronous scheduling it would wait for the step in flight, so that path looks 16 times less often
         every = self._status_every * (16 if hidden is None else 1)
-        if every and self.step_count % every == every - 1:
-            self.runner.check_device_status()  # raises: the serve loop then fails what is in flight
+        t_now = time.perf_counter()
+        slow = self._status_every > 0 and self._slow_step_s > 0 and t_now - self._last_apply > self._slow_step_s
+        self._last_apply = t_now
+        if slow or (every and self.step_count % every == every - 1):
+            try:
+                self.runner.check_device_status()
+            except RuntimeError as ex:
+                self.device_fault = str(ex)
+                raise  # the serve loop fails what is in flight
         if self.mtp_steps and hidden is not None and meta is not None:
             self._mtp_propose(plan, meta, hidden, results)
         row = 0

@@ -479,6 +479,8 @@ class KsanaLLMEngine:
         """Returns (Status, KsanaPythonOutput) or (Status, async iterator of KsanaPythonOutput) when streaming."""
         if getattr(self, "failed_ranks", None):
             return Status(RetCode.RET_INTERNAL_ERROR, f"ranks {self.failed_ranks} of this instance are gone"), None
+        if self.llm.refusing_requests():
+            return Status(RetCode.RET_INTERNAL_ERROR, f"device fault on this instance: {self.llm.device_fault}"), None
         pd_first: List[int] = []
         pd_rid = (req_ctx or {}).get("kv-comm-request-id") if getattr(self, "connector", None) is not None else None
         try:

@@ -226,3 +226,49 @@ def test_a_silent_rank_is_detected_and_new_requests_are_refused():
         p.join(timeout=60)
     assert [p.exitcode for p in procs] == [0, 0]
     assert ok1 and failed == [1] and not ok2 and "gone" in msg
+
+
+def _fault_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), KSANA_SKIP_WARMUP="1", KSANA_STATUS_CHECK_STEPS="1")
+    eng = _engine(tensor_para_size=2)
+    if rank == 0:
+        st1, _ = asyncio.run(eng.generate(dict(BODY), streamer=False))
+
+        # a fake of the failing call: the read of the device status word finds the peer-timeout bit set, which is
+        # what the runner reports after a kernel gave up waiting for a peer
+        def status_word_set():
+            raise RuntimeError("device status word 0x8: a kernel gave up waiting (peer or barrier timeout)")
+        eng.llm.runner.check_device_status = status_word_set
+        st2, _ = asyncio.run(eng.generate(dict(BODY), streamer=False))      # in flight when the word is read
+        st3, _ = asyncio.run(eng.generate(dict(BODY), streamer=False))      # arrives afterwards
+        out.put((st1.OK(), st2.OK(), st2.GetMessage(), st3.OK(), st3.GetMessage(), eng.llm.device_fault))
+        eng.shutdown()
+    else:
+        eng.serve_follower()
+    import gc
+    import torch.distributed as dist
+    del eng
+    gc.collect()
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def test_a_set_device_status_word_fails_what_is_in_flight_and_refuses_new_requests():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_fault_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    ok1, ok2, msg2, ok3, msg3, fault = q.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+    assert [p.exitcode for p in procs] == [0, 0]
+    assert ok1
+    assert not ok2 and "engine step failed" in msg2 and "status word" in msg2
+    assert not ok3 and "device fault" in msg3
+    assert fault and "0x8" in fault
