@@ -34,6 +34,7 @@ class RetCode:
     RET_REQUEST_TERMINATED = 5
     RET_OUT_OF_MEMORY = 6
     RET_INTERNAL_ERROR = 7
+    RET_STOP_ITERATION = 3011  # a streaming iterator has no further item (the reference's value)
 
 
 class _Code(int):
@@ -165,7 +166,7 @@ class PyAsyncStreamingIterator:
         return out
 
     def abort(self) -> None:
-        if not self.req.finished:
+        if not self.req.finished and not getattr(self, "detached", False):
             self.engine.llm.abort(self.req)
 
     def __del__(self):
