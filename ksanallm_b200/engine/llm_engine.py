@@ -193,6 +193,7 @@ class LLMEngine:
         # set when the device status word was found non-zero: what the kernels of recent steps produced is not to be
         # trusted. A multi-rank instance then refuses new requests (its ranks no longer agree on what they computed).
         self.device_fault: Optional[str] = None
+        self.before_forward = None  # optional hook(plan), called on the step thread right before a forward pass
         self._ctl_ops: List[Tuple[Dict[str, Any], threading.Event]] = []  # control messages for the follower ranks
         self.on_control: Optional[Callable[[Dict[str, Any]], None]] = None   # follower side: handler of such messages
         self.dp_router = None       # parallel.attn_dp.DPRequestRouter on the rank that owns the HTTP front-end
@@ -445,6 +446,8 @@ class LLMEngine:
             tb = time.perf_counter()
         else:
             with self._phase("ForwardingLayers", nb, nt):
+                if self.before_forward is not None:
+                    self.before_forward(plan)  # prefill / decode disaggregation: KV leaves layer by layer
                 hidden = self.runner.forward(meta, refit)
                 self._run_probes(plan, meta, hidden)
             tb = time.perf_counter()

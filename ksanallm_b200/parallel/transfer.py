@@ -41,6 +41,11 @@ class LayerProgressTracker:
     def register_callback(self, fn: Callable[[int], None]) -> None:
         self._callbacks.append(fn)
 
+    def set_callbacks(self, fns: Sequence[Callable[[int], None]]) -> None:
+        """Replaces the callbacks (one forward pass = one set: the blocks to ship differ from step to step)."""
+        with self._lock:
+            self._callbacks = list(fns)
+
     def reset(self) -> None:
         with self._lock:
             self._events.clear()
@@ -200,25 +205,59 @@ class TransferEngine:
             self.cache.free_seq(tmp)
         return n_blocks
 
-    def import_request(self, peer: int) -> Tuple[List[int], List[int], int]:
+    # ---- layer-by-layer export: header + tokens first, each layer when the device has finished it, the tokens
+    # generated so far last (they do not exist yet while the layers leave) -------------------------------------------
+    def begin_export(self, tokens: Sequence[int], blocks: Sequence[int], peer: int) -> None:
+        toks = [int(t) for t in tokens]
+        h = self._hdr()
+        h[0], h[1], h[2], h[3] = len(toks), len(blocks), -1, len(self.kv)  # -1: the generated tokens follow the layers
+        self.tr.send(h, peer)
+        self.tr.send(torch.tensor(toks, dtype=torch.int32), peer)
+        self._lw_idx = torch.tensor(list(blocks), dtype=torch.long, device=self.kv[0].device) if blocks else None
+
+    def send_layer(self, layer: int, peer: int) -> None:
+        if self._lw_idx is not None:
+            self.tr.send(self.kv[layer].index_select(0, self._lw_idx), peer)
+
+    def finish_export(self, first_tokens: Sequence[int], peer: int) -> None:
+        t = torch.tensor([len(first_tokens)] + [int(x) for x in first_tokens], dtype=torch.int32)
+        self.tr.send(torch.tensor([t.numel()], dtype=torch.int64), peer)
+        self.tr.send(t, peer)
+        self.sent_blocks += 0 if self._lw_idx is None else int(self._lw_idx.numel())
+
+    def import_request(self, peer: int, lock=None, after_commit=None) -> Tuple[List[int], List[int], int]:
         """Receives one exported request. Returns (prompt tokens, tokens already generated, blocks placed in the
-        prefix tree)."""
+        prefix tree). ``lock``: held only while the cache manager is touched (block reservation before the layers
+        arrive, commit after them), not while the layers are in flight: a layer-by-layer export lasts as long as the
+        sender's forward pass. ``after_commit(first_block_kept, blocks)`` runs under the same hold as the commit."""
+        import contextlib
+        guard = lock if lock is not None else contextlib.nullcontext()
         h = self._hdr()
         self.last_import = (0, [])
         self.tr.recv(h, peer)
         n_tok, n_blocks, n_first, n_layers = (int(x) for x in h)
         assert n_layers == len(self.kv), "both instances must hold the same layers"
-        tt = torch.zeros(n_tok + n_first, dtype=torch.int32)
+        trailer = n_first < 0  # layer-by-layer export: the generated tokens arrive after the layers
+        tt = torch.zeros(n_tok + max(n_first, 0), dtype=torch.int32)
         self.tr.recv(tt, peer)
         toks, first = tt[:n_tok].tolist(), tt[n_tok:].tolist()
+
+        def read_trailer():
+            n = torch.zeros(1, dtype=torch.int64)
+            self.tr.recv(n, peer)
+            t = torch.zeros(int(n[0]), dtype=torch.int32)
+            self.tr.recv(t, peer)
+            return t[1:1 + int(t[0])].tolist()
+
         if n_blocks == 0:
-            return toks, first, 0
+            return toks, (read_trailer() if trailer else first), 0
         tmp = next(self._tmp_ids)
         covered = n_blocks * self.block_size
-        hit = self.cache.create_seq(tmp, toks[:covered] + [0])
-        have = hit // self.block_size
-        ok = self.cache.ensure_capacity(tmp, covered)
-        table = list(self.cache.block_table(tmp)) if ok else []
+        with guard:
+            hit = self.cache.create_seq(tmp, toks[:covered] + [0])
+            have = hit // self.block_size
+            ok = self.cache.ensure_capacity(tmp, covered)
+            table = list(self.cache.block_table(tmp)) if ok else []
         dev = self.kv[0].device
         for l in range(n_layers):
             buf = torch.empty((n_blocks,) + tuple(self.kv[l].shape[1:]), dtype=self.kv[l].dtype, device=dev)
@@ -226,12 +265,17 @@ class TransferEngine:
             if ok and have < n_blocks:
                 idx = torch.tensor(table[have:n_blocks], dtype=torch.long, device=dev)
                 self.kv[l].index_copy_(0, idx, buf[have:])
+        if trailer:
+            first = read_trailer()
         placed = 0
-        if ok:
-            self.cache.commit_filled(tmp, toks[:covered] + [0], covered)
-            placed = n_blocks - have
-        self.last_import = (have, table[have:n_blocks] if ok else [])  # which received blocks went where
-        self.cache.free_seq(tmp)
+        with guard:
+            if ok:
+                self.cache.commit_filled(tmp, toks[:covered] + [0], covered)
+                placed = n_blocks - have
+            self.last_import = (have, table[have:n_blocks] if ok else [])  # which received blocks went where
+            self.cache.free_seq(tmp)
+            if after_commit is not None:
+                after_commit(*self.last_import)
         self.recv_blocks += placed
         return toks, first, placed
 

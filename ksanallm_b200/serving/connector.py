@@ -15,6 +15,7 @@ TaskManager / TaskDispatcher and NCCL / ZMQ / TCP communicators plus a router cl
 from __future__ import annotations
 
 import json
+import os
 import socket
 import struct
 import threading
@@ -71,6 +72,12 @@ class PDConnector:
         self._threads: List[threading.Thread] = []
         self._srv: Optional[socket.socket] = None
         self.exported = self.imported = 0
+        # layer-by-layer hand-over (prefill side): request id -> session; see expect_export
+        self._sessions: Dict[int, "_LayerwiseExport"] = {}
+        self._by_rid: Dict[str, "_LayerwiseExport"] = {}
+        self._tracker = None
+        self.layerwise_exports = 0
+        self.layerwise = os.environ.get("KSANA_PD_LAYERWISE", "1") != "0"
 
     # ---- lifecycle ---------------------------------------------------------------------------------------------------
     def start(self) -> None:
@@ -142,7 +149,63 @@ class PDConnector:
         raise ConnectionError(f"no decode instance with a transfer listener for group key {group_key!r}")
 
     # ---- prefill side -------------------------------------------------------------------------------------------------
+    def expect_export(self, req, request_id: str, group_key: str) -> None:
+        """Announces that ``req`` will be handed over: the connection to the decode instance is opened now (off the
+        step thread), and when the scheduler plans the prompt's last chunk the KV blocks leave layer by layer while
+        the forward pass is still running (``LayerProgressTracker`` events), instead of all at once after the first
+        token. Used when the engine steps synchronously through the per-layer Python path on a single rank; anything
+        else keeps the one-piece export (the native executor reports its layers together, and tensor-parallel shards
+        travel after the step). Reference: the prefill side's layer-wise sends in
+        src/ksana_llm/transfer/transfer_engine.h:63-190."""
+        if not self.layerwise or self.llm.tp.size > 1 or getattr(self.llm, "async_mode", False):
+            return
+        sess = _LayerwiseExport(self, req, request_id, group_key)
+        self._by_rid[request_id] = sess
+        for s_ in req.seqs:
+            self._sessions[s_.seq_id] = sess
+        self.llm.before_forward = self._on_plan
+        threading.Thread(target=sess.connect, daemon=True).start()
+
+    def _on_plan(self, plan) -> None:
+        """Engine hook, step thread, right before the forward pass of ``plan``."""
+        model = self.llm.runner.model
+        armed = []
+        for e in plan.entries:
+            sess = self._sessions.get(e.seq_id)
+            if sess is not None and e.num_logits > 0 and not sess.armed:
+                if sess.arm(e.seq_id):
+                    armed.append(sess)
+                else:
+                    self._drop(sess)
+        if not armed:
+            if model.progress is not None and not any(s_.armed and not s_.layers_done.is_set()
+                                                      for s_ in self._by_rid.values()):
+                model.progress = None
+            return
+        from ..parallel.transfer import LayerProgressTracker
+        if self._tracker is None:
+            self._tracker = LayerProgressTracker(len(self.llm.runner.kv_caches), self.llm.runner.device)
+        self._tracker.reset()
+        self._tracker.set_callbacks([s_.on_layer for s_ in armed])
+        model.progress = self._tracker
+
+    def _drop(self, sess) -> None:
+        self._by_rid.pop(sess.request_id, None)
+        for k in [k for k, v in self._sessions.items() if v is sess]:
+            self._sessions.pop(k, None)
+        sess.close()
+
     def export(self, request_id: str, group_key: str, prompt_tokens: List[int], first_tokens: List[int]) -> int:
+        sess = self._by_rid.get(request_id)
+        if sess is not None:
+            try:
+                if sess.armed and sess.finish(first_tokens):
+                    self.exported += 1
+                    self.layerwise_exports += 1
+                    return sess.n_blocks
+            finally:
+                self._drop(sess)
+            # the session never started (connection not ready in time, request pre-empted, ...): one-piece export
         host, port = self._decode_transfer_addr(group_key)
         sock = _connect(host, port)
         try:
@@ -181,13 +244,22 @@ class PDConnector:
             conn.settimeout(60)
             rid = _recv_str(conn)
             te = TransferEngine(self.llm.runner.kv_caches, self.llm.cache, TcpTransport(conn), self.llm.block_size)
-            with self.llm.lock:  # the scheduler thread uses the same cache manager
-                toks, first, placed = te.import_request(0)
-                have, blocks = te.last_import
+            evs = []
+
+            def committed(have, blocks):
                 # the other ranks of a tensor-parallel instance place their shard into the same blocks; enqueued
-                # under the lock: no step that could read those blocks is planned before the message went out
-                ev = self.llm.enqueue_control({"op": "pd_import", "rid": rid, "skip": have, "blocks": list(blocks)})
-            ev.wait(60.0)
+                # under the lock that covers the commit: no step that could read those blocks is planned before
+                # the message went out
+                evs.append(self.llm.enqueue_control({"op": "pd_import", "rid": rid, "skip": have,
+                                                     "blocks": list(blocks)}))
+
+            # the engine's lock (the scheduler thread uses the same cache manager) is taken for the reservation and
+            # for the commit only: a layer-by-layer export keeps this connection busy for a whole forward pass
+            toks, first, placed = te.import_request(0, lock=self.llm.lock, after_commit=committed)
+            if not evs:
+                with self.llm.lock:
+                    committed(*te.last_import)
+            evs[0].wait(60.0)
             conn.sendall(b"\x01")
             with self._cv:
                 self._imports[rid] = (toks, first, placed)
@@ -209,6 +281,79 @@ class PDConnector:
             return self._imports.pop(request_id)
 
 
+class _LayerwiseExport:
+    """One request leaving the prefill instance layer by layer."""
+
+    def __init__(self, conn: PDConnector, req, request_id: str, group_key: str):
+        self.c, self.req, self.request_id, self.group_key = conn, req, request_id, group_key
+        self.sock: Optional[socket.socket] = None
+        self.ready = threading.Event()
+        self.layers_done = threading.Event()
+        self.armed = False
+        self.failed = False
+        self.te: Optional[TransferEngine] = None
+        self.n_blocks = 0
+
+    def connect(self) -> None:
+        try:
+            host, port = self.c._decode_transfer_addr(self.group_key)
+            self.sock = _connect(host, port)
+            _send_str(self.sock, self.request_id)
+        except (OSError, ConnectionError):
+            self.failed = True
+        self.ready.set()
+
+    def arm(self, seq_id: int) -> bool:
+        """Step thread, the prompt's last chunk is about to run: header + tokens go out now, the layers follow from
+        the tracker's callbacks. False: not possible (no connection yet), the caller falls back."""
+        # the connection is opened when the request arrives; a short wait here (step thread) is cheaper than losing
+        # the overlap when the very first step already runs the prompt's last chunk
+        self.ready.wait(float(os.environ.get("KSANA_PD_LAYERWISE_WAIT_MS", "20")) / 1000.0)
+        if not self.ready.is_set() or self.failed or self.sock is None:
+            return False
+        llm = self.c.llm
+        toks = list(self.req.prompt_tokens)
+        n_full = len(toks) // llm.block_size
+        with llm.lock:
+            blocks = list(llm.cache.block_table(seq_id))[:n_full]
+        self.n_blocks = len(blocks)
+        try:
+            self.te = TransferEngine(llm.runner.kv_caches, llm.cache, TcpTransport(self.sock), llm.block_size)
+            self.te.begin_export(toks, blocks, 0)
+        except (OSError, ConnectionError):
+            self.failed = True
+            return False
+        self.armed = True
+        return True
+
+    def on_layer(self, layer: int) -> None:
+        if self.failed:
+            return
+        try:
+            self.te.send_layer(layer, 0)
+        except (OSError, ConnectionError):
+            self.failed = True
+        if layer == len(self.te.kv) - 1:
+            self.layers_done.set()
+
+    def finish(self, first_tokens: List[int]) -> bool:
+        if not self.layers_done.wait(60.0) or self.failed:
+            return False
+        try:
+            self.te.finish_export(first_tokens, 0)
+            _recv_exact(self.sock, 1)  # the decode side acknowledges after committing the blocks
+            return True
+        except (OSError, ConnectionError):
+            return False
+
+    def close(self) -> None:
+        if self.sock is not None:
+            try:
+                self.sock.close()
+            except OSError:
+                pass
+
+
 class PDShardWorker:
     """Ranks > 0 of a tensor-parallel prefill / decode instance. The driving rank owns the request bookkeeping and
     the block tables; these ranks only move their shard of the KV blocks it names (control messages ``pd_export`` /
@@ -223,6 +368,12 @@ class PDShardWorker:
         self._stop = threading.Event()
         self._srv: Optional[socket.socket] = None
         self.exported = self.imported = 0
+        # layer-by-layer hand-over (prefill side): request id -> session; see expect_export
+        self._sessions: Dict[int, "_LayerwiseExport"] = {}
+        self._by_rid: Dict[str, "_LayerwiseExport"] = {}
+        self._tracker = None
+        self.layerwise_exports = 0
+        self.layerwise = os.environ.get("KSANA_PD_LAYERWISE", "1") != "0"
         llm.on_control = self.handle
 
     def start(self) -> None:

@@ -524,6 +524,8 @@ class KsanaLLMEngine:
                 sp = _dc.replace(sp, max_new_tokens=1)
             req = self.llm.add_request(tokens, sp, refit=refit, grammar=grammar, mrope_positions=mrope)
             req.ctx = req_ctx or {}
+            if pd_rid and self.connector.role == "prefill" and refit is None:
+                self.connector.expect_export(req, pd_rid, (req_ctx or {}).get("kv-comm-group-key", ""))
             req.pd_first = pd_first
             req.pd_prompt_len = len(tokens) - len(pd_first)
         except EngineError as ex:

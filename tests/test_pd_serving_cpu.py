@@ -136,3 +136,38 @@ def test_lookup_through_router(want):
         prefill.shutdown()
         server.should_exit = True
         th.join(timeout=5)
+
+
+def test_kv_leaves_layer_by_layer_during_the_last_prefill_chunk(want, monkeypatch):
+    """Synchronous stepping through the per-layer path: the prefill instance ships each layer's blocks from the
+    layer tracker's callbacks while its forward pass runs (chunked prefill: the blocks of earlier chunks go with
+    the first layers of the last chunk), the first token follows as a trailer."""
+    monkeypatch.setenv("KSANA_PD_LAYERWISE_WAIT_MS", "5000")
+    decode = _make("decode")
+    prefill = _make("prefill", peer_transfer_addr="%s:%d" % decode.connector.transfer_addr)
+    order = []
+    try:
+        prefill.llm.async_mode = False
+        from ksanallm_b200.parallel import transfer
+        real = transfer.TransferEngine.send_layer
+
+        def spy(self, layer, peer):
+            order.append(("layer", layer, prefill.llm.step_count))
+            return real(self, layer, peer)
+        monkeypatch.setattr(transfer.TransferEngine, "send_layer", spy)
+        real_fin = transfer.TransferEngine.finish_export
+        monkeypatch.setattr(transfer.TransferEngine, "finish_export",
+                            lambda self, first, peer: (order.append(("trailer", list(first))), real_fin(self, first, peer))[1])
+        (pst, pout), (dst, dout) = _run_pair(prefill, decode, {"kv-comm-request-id": "lw1"}, BODY)
+        assert pst.OK() and dst.OK()
+        assert dout.output_tokens == want.output_tokens and dout.input_tokens == want.input_tokens
+        assert prefill.connector.layerwise_exports == 1 and decode.connector.imported == 1
+        n_layers = len(prefill.llm.runner.kv_caches)
+        assert [o[:2] for o in order[:n_layers]] == [("layer", l) for l in range(n_layers)]
+        assert len({o[2] for o in order[:n_layers]}) == 1        # all within one step of the prefill instance
+        assert order[n_layers] == ("trailer", want.output_tokens[0][:1])
+        assert decode.llm.cache.stats.prefix_hit_tokens >= 32
+        assert prefill.llm.runner.model.progress is None or not prefill.connector._sessions
+    finally:
+        decode.shutdown()
+        prefill.shutdown()
