@@ -307,9 +307,308 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   }
 }
 
+// ---- the transposed form for small groups: at most 16 query rows (group x new tokens) ---------------------------------
+// With 8 query heads and one new token only 8 of the 128 rows above are real, yet every thread scans 128 score columns
+// twice: the softmax, not the memory system, sets the pace. Here the roles are swapped: S^T = K Q^T puts the 128 KV
+// tokens of a tile on the MMA rows (one per thread) and the <= 16 query rows on the columns, so a thread handles 16
+// scores per tile; the column maxima / sums go across threads (redux + shared memory), O^T = V^T P^T accumulates
+// 128 head dims x 16 query rows in 16 TMEM columns, and rescaling the accumulator touches 16 values per thread. One
+// CTA needs 73 KB of shared memory (one K tile, one V tile, Q, P) and 32 TMEM columns, so three CTAs share an SM and
+// overlap each other's loads, MMAs and softmax; inside a CTA the next K tile is requested as soon as S is out and the
+// next V tile as soon as O has been updated.
+//   warps 0-3  thread t = KV token t of the tile (S^T row) and head dim t (O^T row)
+//   warp 4     lane 0: TMA producer
+constexpr int DT_N = 16;
+constexpr int DT_Q_BYTES = DT_N * DG_D * 2;     // 4 KB: two 64-dim halves of [16 rows x 128 B]
+constexpr int DT_P_BYTES = DT_N * DG_BKV * 2;   // 4 KB: two 64-token halves of [16 rows x 128 B]
+constexpr int DT_OFF_K = 0;
+constexpr int DT_OFF_V = DT_OFF_K + DG_KV_BYTES;
+constexpr int DT_OFF_Q = DT_OFF_V + DG_KV_BYTES;
+constexpr int DT_OFF_P = DT_OFF_Q + DT_Q_BYTES;
+constexpr int DT_OFF_RED = DT_OFF_P + DT_P_BYTES;          // [4 warps][16] floats, twice (max, sum)
+constexpr int DT_OFF_BAR = DT_OFF_RED + 2 * 4 * DT_N * 4;
+constexpr int DT_SMEM = DT_OFF_BAR + 128 + 1024;
+
+// order-preserving float <-> int so that redux.sync.max can reduce floats
+__device__ __forceinline__ int dt_key(float f) {
+  const int b = __float_as_int(f);
+  return b ^ ((b >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float dt_unkey(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
+
+__global__ void __launch_bounds__(160, 3)
+paged_decode_gqa_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV,
+                          const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
+                          const int* __restrict__ kv_lens, int seq_base, int h, int hk, int q_box, float scale_log2,
+                          __nv_bfloat16* __restrict__ out, int ldo, float* __restrict__ part_o,
+                          float* __restrict__ part_lse, int splits, int tiles_per_split, int max_rows,
+                          unsigned int* err) {
+  const int bi = blockIdx.x;
+  const int b = bi + seq_base;
+  const int kh = blockIdx.y;
+  const int split = blockIdx.z;
+  const int G = h / hk;
+  const int q0 = cu_q[b];
+  const int q_len = cu_q[b + 1] - q0;
+  const int L = kv_lens[b];
+  const int q_start = L - q_len;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int rows = q_len * G;  // real query rows, <= 16
+  const int n_tiles_all = (L + DG_BKV - 1) / DG_BKV;
+  const int t0 = split * tiles_per_split;
+  const int t1 = min(n_tiles_all, t0 + tiles_per_split);
+  if (t0 >= t1) {
+    // this split holds no tokens of this (shorter) sequence: its rows must not count in the merge
+    if (tid < rows && splits > 1) {
+      const int qi = tid / G, head = kh * G + tid - qi * G;
+      part_lse[(static_cast<size_t>(bi) * max_rows + (static_cast<size_t>(qi) * h + head)) * splits + split] = -INFINITY;
+    }
+    return;
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + DT_OFF_K;
+  uint8_t* sV = smem + DT_OFF_V;
+  uint8_t* sQ = smem + DT_OFF_Q;
+  uint8_t* sP = smem + DT_OFF_P;
+  float* red_max = reinterpret_cast<float*>(smem + DT_OFF_RED);  // [4][16]
+  float* red_sum = red_max + 4 * DT_N;
+  uint64_t* q_bar = reinterpret_cast<uint64_t*>(smem + DT_OFF_BAR);
+  uint64_t* k_full = q_bar + 1;
+  uint64_t* v_full = k_full + 1;
+  uint64_t* k_free = v_full + 1;  // S^T is out: the K tile may be overwritten
+  uint64_t* v_free = k_free + 1;  // O^T is updated: the V tile (and P) may be overwritten
+  uint64_t* s_done = v_free + 1;
+  uint64_t* o_done = s_done + 1;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  if (tid == 0) {
+    mbar_init(q_bar, 1);
+    mbar_init(k_full, 1);
+    mbar_init(v_full, 1);
+    mbar_init(k_free, 1);
+    mbar_init(v_free, 1);
+    mbar_init(s_done, 1);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_holder, 32);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + DT_N;
+
+  if (warp == 4) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmKV);
+      const int n_pages = (L + DG_PAGE - 1) / DG_PAGE;
+      const int* bt = block_tables + static_cast<size_t>(b) * max_blocks;
+      mbar_expect_tx(q_bar, static_cast<uint32_t>(q_box) * G * DG_D * 2);
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) tma_load_3d(sQ + hf * (DT_N * 128), &tmQ, q_bar, hf * 64, kh * G, q0);
+      bool ok = true;
+      for (int kt = t0; kt < t1 && ok; ++kt) {
+        const int it = kt - t0;
+        for (int which = 0; which < 2 && ok; ++which) {  // 0: K, 1: V
+          uint64_t* freeb = which ? v_free : k_free;
+          uint64_t* fullb = which ? v_full : k_full;
+          uint8_t* dst = which ? sV : sK;
+          if (it > 0 && !mbar_wait_bounded(freeb, (it - 1) & 1, abort_flag, err)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(fullb, DG_KV_BYTES);
+          for (int p = 0; p < DG_BKV / DG_PAGE; ++p) {
+            int pg = kt * (DG_BKV / DG_PAGE) + p;
+            if (pg >= n_pages) pg = n_pages - 1;  // finite filler; those tokens are masked
+            const int row = ((bt[pg] * 2 + which) * hk + kh) * DG_PAGE;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+              tma_load_2d(dst + hf * (DG_BKV * 128) + p * (DG_PAGE * 128), &tmKV, fullb, hf * 64, row);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- MMA issue (thread 0) + softmax (128 threads) ----------------
+    float m_ref[DT_N], l_part[DT_N];
+#pragma unroll
+    for (int n = 0; n < DT_N; ++n) {
+      m_ref[n] = -INFINITY;
+      l_part[n] = 0.f;
+    }
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    int bad = 0;
+    if (!mbar_wait_bounded(q_bar, 0, abort_flag, err)) bad = 1;
+    for (int kt = t0; kt < t1; ++kt) {
+      const int it = kt - t0;
+      const uint32_t ph = it & 1;
+      if (tid == 0 && !bad) {
+        if (mbar_wait_bounded(k_full, ph, abort_flag, err)) {
+          tc_fence_after();
+          constexpr uint32_t idesc = umma_idesc(128, DT_N, 1, 1);
+#pragma unroll
+          for (int k = 0; k < DG_D / 16; ++k)
+            umma_f16(tmem_S, umma_desc_k128(smem_u32(sK) + (k >> 2) * (DG_BKV * 128) + (k & 3) * 32),
+                     umma_desc_k128(smem_u32(sQ) + (k >> 2) * (DT_N * 128) + (k & 3) * 32), idesc, k > 0 ? 1u : 0u);
+          umma_commit(k_free);
+          umma_commit(s_done);
+        } else {
+          bad = 1;
+        }
+      }
+      if (!bad && !mbar_wait_bounded(s_done, ph, abort_flag, err)) bad = 1;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abort_flag) {
+        bad = 1;
+        break;
+      }
+      tc_fence_after();
+
+      // scores of KV token kv0 + tid against the 16 query rows
+      uint32_t r[DT_N];
+      tmem_ld16(tmem_S + lane_off, r);
+      tmem_wait_ld();
+      const int kpos = kt * DG_BKV + tid;
+      float s[DT_N];
+#pragma unroll
+      for (int n = 0; n < DT_N; ++n) {
+        const int q_pos = q_start + n / G;
+        s[n] = (n >= rows || kpos >= L || kpos > q_pos) ? -INFINITY : __uint_as_float(r[n]) * scale_log2;
+      }
+      // column maxima over the 128 tokens: redux inside the warp, shared memory across the four warps
+#pragma unroll
+      for (int n = 0; n < DT_N; ++n) {
+        const int k = __reduce_max_sync(0xffffffffu, dt_key(s[n]));
+        if (lane == 0) red_max[warp * DT_N + n] = dt_unkey(k);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      float alpha[DT_N];
+      bool any_scale = false;
+#pragma unroll
+      for (int n = 0; n < DT_N; ++n) {
+        const float mt = fmaxf(fmaxf(red_max[n], red_max[DT_N + n]), fmaxf(red_max[2 * DT_N + n], red_max[3 * DT_N + n]));
+        const float m_new = fmaxf(m_ref[n], mt);
+        alpha[n] = (m_new > m_ref[n] && m_ref[n] != -INFINITY) ? exp2f(m_ref[n] - m_new) : 1.f;
+        any_scale |= alpha[n] != 1.f;
+        m_ref[n] = m_new;
+        l_part[n] *= alpha[n];
+      }
+      // probabilities first (this overlaps the previous tile's PV product) ...
+      float pr[DT_N];
+#pragma unroll
+      for (int n = 0; n < DT_N; ++n) {
+        pr[n] = (s[n] == -INFINITY) ? 0.f : exp2f(s[n] - m_ref[n]);
+        l_part[n] += pr[n];
+      }
+      // ... then the previous PV product must be in: it reads P, and O^T is rescaled below
+      if (it > 0) {
+        if (!bad && !mbar_wait_bounded(o_done, (it - 1) & 1, abort_flag, err)) bad = 1;
+        tc_fence_after();
+        if (any_scale && !bad) {  // the maxima are the same in every thread: a uniform branch
+          uint32_t o[DT_N];
+          tmem_ld16(tmem_O + lane_off, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int n = 0; n < DT_N; ++n) o[n] = __float_as_uint(__uint_as_float(o[n]) * alpha[n]);
+          tmem_st16(tmem_O + lane_off, o);
+          tmem_wait_st();
+        }
+      }
+      // P^T: thread = token (column of P), 16 query rows; bf16 into the K-major, 128-byte-swizzled B operand
+      {
+        uint8_t* base = sP + (tid >> 6) * (DT_N * 128) + (tid & 7) * 2;
+        const int chunk = (tid & 63) >> 3;
+#pragma unroll
+        for (int n = 0; n < DT_N; ++n)
+          *reinterpret_cast<__nv_bfloat16*>(base + n * 128 + ((chunk ^ (n & 7)) << 4)) = __float2bfloat16(pr[n]);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abort_flag) {
+        bad = 1;
+        break;
+      }
+      if (tid == 0) {
+        if (mbar_wait_bounded(v_full, ph, abort_flag, err)) {
+          tc_fence_after();
+          // O^T[dim, row] += V^T[dim, token] P^T[token, row]: A = V tile read MN-major (dims contiguous), B = P
+          constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) |
+                                     (static_cast<uint32_t>(DT_N >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+#pragma unroll
+          for (int k = 0; k < DG_BKV / 16; ++k)
+            umma_f16(tmem_O, dg_desc_mn128(smem_u32(sV) + k * (16 * 128), DG_BKV * 128),
+                     umma_desc_k128(smem_u32(sP) + (k >> 2) * (DT_N * 128) + (k & 3) * 32), idesc,
+                     (it > 0 || k > 0) ? 1u : 0u);
+          umma_commit(v_free);
+          umma_commit(o_done);
+        } else {
+          bad = 1;
+        }
+      }
+    }
+    const int n_it = t1 - t0;
+    if (!bad && !mbar_wait_bounded(o_done, (n_it - 1) & 1, abort_flag, err)) bad = 1;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (*abort_flag) bad = 1;
+    tc_fence_after();
+    if (!bad) {
+      // row sums over the 128 token-threads
+#pragma unroll
+      for (int n = 0; n < DT_N; ++n) {
+        float v = l_part[n];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) red_sum[warp * DT_N + n] = v;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      uint32_t o[DT_N];
+      tmem_ld16(tmem_O + lane_off, o);  // thread = head dim tid, 16 query rows
+      tmem_wait_ld();
+#pragma unroll
+      for (int n = 0; n < DT_N; ++n) {
+        if (n < rows) {
+          const float l = red_sum[n] + red_sum[DT_N + n] + red_sum[2 * DT_N + n] + red_sum[3 * DT_N + n];
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          const int qi = n / G, head = kh * G + n - qi * G;
+          const float v = __uint_as_float(o[n]) * inv;
+          if (splits == 1) {
+            out[static_cast<size_t>(q0 + qi) * ldo + head * DG_D + tid] = __float2bfloat16(v);
+          } else {
+            const size_t prow = (static_cast<size_t>(bi) * max_rows + (static_cast<size_t>(qi) * h + head)) * splits + split;
+            part_o[prow * DG_D + tid] = v;
+            if (tid == 0) part_lse[prow] = l > 0.f ? m_ref[n] + log2f(l) : -INFINITY;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 32);
+  }
+}
+
 }  // namespace ksana
 
 using namespace ksana;
+
+// 0: the transposed kernel for at most 16 query rows, the row kernel otherwise; 1: always the row kernel (tests, timing)
+static int g_gqa_variant = 0;
+KSANA_API void ksana_paged_decode_gqa_set_variant(int v) { g_gqa_variant = v; }
 
 // Decode attention for grouped-query models: sequences [seq_base, seq_base + num_seqs) of the step, each with at most
 // max_q_len new tokens; (h / hk) * max_q_len <= 128, d == 128, 16-token pages, bf16 cache
@@ -341,7 +640,10 @@ KSANA_API int ksana_paged_decode_gqa(const void* q, int ldq, int total_tokens, c
   const int sms = sm_count();
   const int n_tiles = (max_kv_len + DG_BKV - 1) / DG_BKV;
   const int base = num_seqs * hk;
-  int splits = base >= sms ? 1 : (sms + base - 1) / base;
+  // at most 16 query rows: the transposed kernel, three CTAs per SM
+  const bool transposed = G * max_q_len <= DT_N && g_gqa_variant != 1;
+  const int want_ctas = transposed ? 3 * sms : sms;
+  int splits = base >= want_ctas ? 1 : (want_ctas + base - 1) / base;
   if (splits > n_tiles) splits = n_tiles;
   if (splits < 1) splits = 1;
   int tiles_per_split = (n_tiles + splits - 1) / splits;
@@ -357,8 +659,18 @@ KSANA_API int ksana_paged_decode_gqa(const void* q, int ldq, int total_tokens, c
     part_o = workspace;
     part_lse = workspace + rows * d;
   }
-  if (KSANA_SMEM_ONCE(paged_decode_gqa_kernel, DG_SMEM) != 0) return -4;
   dim3 grid(num_seqs, hk, splits);
+  if (transposed) {
+    if (KSANA_SMEM_ONCE(paged_decode_gqa_t_kernel, DT_SMEM) != 0) return -4;
+    paged_decode_gqa_t_kernel<<<grid, 160, DT_SMEM, stream>>>(
+        tmQ, tmKV, block_tables, max_blocks, cu_q, kv_lens, seq_base, h, hk, max_q_len, scale * 1.4426950408889634f,
+        reinterpret_cast<__nv_bfloat16*>(out), ldo, part_o, part_lse, splits, tiles_per_split, max_rows, error_word());
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (splits > 1)
+      return launch_decode_combine(part_o, part_lse, cu_q, seq_base, h, splits, max_rows, num_seqs, out, ldo, stream);
+    return 0;
+  }
+  if (KSANA_SMEM_ONCE(paged_decode_gqa_kernel, DG_SMEM) != 0) return -4;
   paged_decode_gqa_kernel<<<grid, 128, DG_SMEM, stream>>>(
       tmQ, tmKV, block_tables, max_blocks, cu_q, kv_lens, seq_base, h, hk, max_q_len, scale * 1.4426950408889634f,
       reinterpret_cast<__nv_bfloat16*>(out), ldo, part_o, part_lse, splits, tiles_per_split, max_rows, error_word());

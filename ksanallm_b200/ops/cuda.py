@@ -68,6 +68,7 @@ class _Sig:
     ksana_paged_decode = ([P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, F, P, F, F, P, I, P, LL, P], I)
     ksana_paged_prefill = ([P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I, F, P, P, I, P], I)
     ksana_paged_decode_gqa = ([P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, F, P, I, P, LL, P], I)
+    ksana_paged_decode_gqa_set_variant = ([I], None)
     ksana_argmax = ([P, I, I, I, P, P], I)
     ksana_sample = ([P, I, I, I, P, P, P, P, P, P], I)
     ksana_gemm_bf16_batched = ([P, LL, LL, P, P, LL, LL, I, I, I, I, P], I)

@@ -57,14 +57,27 @@ def test_decode_multi_token_queries():
     _run([3, 1], [130, 64], h=4, hk=4, num_prefill=0)
 
 
-def test_decode_gqa_tensor_core_kernel_cases():
+@pytest.mark.parametrize("variant", [0, 1])
+def test_decode_gqa_tensor_core_kernel_cases(variant):
     """Group sizes 4 / 8 / 16, ragged lengths (short sequences leave KV splits empty), several new tokens per sequence
-    (speculative drafts), many sequences (no split) and one long one (many splits)."""
+    (speculative drafts), many sequences (no split) and one long one (many splits). Variant 0: up to 16 query rows
+    take the transposed kernel (KV tokens on the MMA rows), more the row kernel; variant 1: always the row kernel."""
+    from ksanallm_b200.ops import cuda
+    cuda.lib().ksana_paged_decode_gqa_set_variant(variant)
+    try:
+        _gqa_cases()
+    finally:
+        cuda.lib().ksana_paged_decode_gqa_set_variant(0)
+
+
+def _gqa_cases():
     _run([1] * 5, [1, 129, 4000, 16, 700], h=8, hk=2, num_prefill=0, seed=1)
     _run([1] * 3, [5000, 3, 260], h=32, hk=2, num_prefill=0, seed=2)
     _run([4, 2, 3], [900, 131, 4], h=8, hk=1, num_prefill=0, seed=3)
     _run([1] * 200, [37 + 11 * i for i in range(200)], h=8, hk=1, num_prefill=0, seed=4)
     _run([2], [9000], h=16, hk=2, num_prefill=0, seed=5)
+    _run([2, 1, 2, 1], [128, 128, 257, 1], h=16, hk=2, num_prefill=0, seed=6)  # tile-boundary lengths
+    _run([1] * 64, [2048] * 64, h=64, hk=8, num_prefill=0, seed=7)
 
 
 def test_decode_long_context_split_kv():
