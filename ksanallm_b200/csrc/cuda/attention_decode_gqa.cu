@@ -642,8 +642,12 @@ KSANA_API int ksana_paged_decode_gqa(const void* q, int ldq, int total_tokens, c
   const int base = num_seqs * hk;
   // at most 16 query rows: the transposed kernel, three CTAs per SM
   const bool transposed = G * max_q_len <= DT_N && g_gqa_variant != 1;
-  const int want_ctas = transposed ? 3 * sms : sms;
+  // The transposed kernel keeps three CTAs per SM: with only a few more CTAs than the 3 x SMs slots the last wave
+  // runs mostly empty (512 CTAs on 444 slots cost 40 %), so the KV range is cut until there are about four waves of
+  // CTAs of at least two tiles each; the hardware then balances them as slots free up.
+  const int want_ctas = transposed ? 12 * sms : sms;
   int splits = base >= want_ctas ? 1 : (want_ctas + base - 1) / base;
+  if (transposed && splits > (n_tiles + 1) / 2) splits = (n_tiles + 1) / 2;
   if (splits > n_tiles) splits = n_tiles;
   if (splits < 1) splits = 1;
   int tiles_per_split = (n_tiles + splits - 1) / splits;
