@@ -80,6 +80,15 @@ class HiddenChannel:
 
     def __init__(self, topo: StageTopology, hidden: int, dtype: torch.dtype, device: torch.device, group=None):
         self.topo, self.hidden, self.dtype, self.device, self.group = topo, hidden, dtype, device, group
+        # On GPUs the activations travel over NCCL, whose point-to-point operations run in issue order on one stream
+        # per communicator. The results' way back (last stage -> driver) crosses that order as soon as two
+        # micro-batches are in flight: the driver's second send waits for the last stage's second receive, which is
+        # queued behind its send of the first results, which waits for a receive the driver has queued behind that
+        # second send. So the (small) results go back over a host-side group of their own; every rank creates it here,
+        # in the same order. Found on two GPUs: the first NCCL run of the two-stage test stopped exactly there.
+        self.back_group = None
+        if torch.device(device).type == "cuda" and dist.is_initialized() and dist.get_world_size() > 1:
+            self.back_group = dist.new_group(backend="gloo")
 
     def send_hidden(self, x: torch.Tensor) -> None:
         dist.send(x.contiguous(), dst=self.topo.peer(self.topo.stage + 1), group=self.group)
@@ -93,27 +102,36 @@ class HiddenChannel:
         """Non-blocking: with several micro-batches in flight the driver only posts the matching receive after it
         has launched the next micro-batch, so a blocking send here could dead-lock against its plan broadcast."""
         buf = toks.to(torch.int32).contiguous()
+        self._isend_back(buf, dst_rank)
+
+    def _isend_back(self, buf: torch.Tensor, dst_rank: int) -> None:
+        grp = self.group
+        if self.back_group is not None:
+            buf, grp = buf.cpu(), self.back_group
         self._pending_sends = [(w, b) for w, b in getattr(self, "_pending_sends", []) if not w.is_completed()]
-        self._pending_sends.append((dist.isend(buf, dst=dst_rank, group=self.group), buf))
+        self._pending_sends.append((dist.isend(buf, dst=dst_rank, group=grp), buf))
+
+    def _recv_back(self, shape, dtype, src_rank: int) -> torch.Tensor:
+        if self.back_group is not None:
+            buf = torch.empty(shape, dtype=dtype)
+            dist.recv(buf, src=src_rank, group=self.back_group)
+            return buf.to(self.device)
+        buf = torch.empty(shape, dtype=dtype, device=self.device)
+        dist.recv(buf, src=src_rank, group=self.group)
+        return buf
 
     def send_logits(self, logits: torch.Tensor, dst_rank: int = 0) -> None:
         """Rows that are not sampled greedily: the sampling state (penalties, generators, grammar masks) lives on the
         driver, so the last stage returns the fp32 logits of those rows instead of tokens (non-blocking, see
         send_tokens). The reference returns the hidden states to the chief node, which owns lm_head + sampler
         (runtime/llm_runtime.cpp:76-110); here lm_head stays with the last stage."""
-        buf = logits.float().contiguous()
-        self._pending_sends = [(w, b) for w, b in getattr(self, "_pending_sends", []) if not w.is_completed()]
-        self._pending_sends.append((dist.isend(buf, dst=dst_rank, group=self.group), buf))
+        self._isend_back(logits.float().contiguous(), dst_rank)
 
     def recv_logits(self, count: int, vocab: int, src_rank: int) -> torch.Tensor:
-        buf = torch.empty(count, vocab, dtype=torch.float32, device=self.device)
-        dist.recv(buf, src=src_rank, group=self.group)
-        return buf
+        return self._recv_back((count, vocab), torch.float32, src_rank)
 
     def recv_tokens(self, count: int, src_rank: int) -> torch.Tensor:
-        buf = torch.empty(count, dtype=torch.int32, device=self.device)
-        dist.recv(buf, src=src_rank, group=self.group)
-        return buf
+        return self._recv_back((count,), torch.int32, src_rank)
 
 
 class BatchState(Enum):
