@@ -461,9 +461,18 @@ def tiny_moe_config() -> ModelConfig:
         max_position_embeddings=2048, torch_dtype="float32", eos_token_id=2, bos_token_id=1))
 
 
+def tiny_moe_128_config() -> ModelConfig:
+    """A small MoE whose shapes the CUDA kernels take (head_dim 128, hidden and expert widths multiples of 128)."""
+    return model_config_from_dict(dict(
+        model_type="mixtral", hidden_size=256, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=2,
+        head_dim=128, intermediate_size=128, num_local_experts=4, num_experts_per_tok=2, vocab_size=32000,
+        rms_norm_eps=1e-6, max_position_embeddings=2048, torch_dtype="bfloat16", eos_token_id=2, bos_token_id=1))
+
+
 NAMED_CONFIGS = {
     "tiny-llama": tiny_llama_config,
     "tiny-moe": tiny_moe_config,
+    "tiny-moe-128": tiny_moe_128_config,
     "llama-2-7b": llama2_7b_config,
     "llama-3-70b": llama3_70b_config,
     "qwen3-32b-fp8": qwen3_32b_config,

@@ -282,8 +282,12 @@ class KsanaLLMEngine:
                 ep_rank, ep_size = dp_world.rank, dp_world.size
                 tp.ep_rank, tp.ep_size = ep_rank, ep_size
                 plain_experts = cfg.quant.method in ("none", "", None) and not quantize
+                # the grouped expert GEMM behind the peer-memory exchange takes hidden and 2 x expert widths that are
+                # multiples of 128; other shapes (and quantised experts) go through the collective exchange
+                inter = cfg.moe_intermediate_size or cfg.intermediate_size
+                grouped_ok = cfg.hidden_size % 128 == 0 and (2 * inter) % 128 == 0 and inter % 8 == 0
                 if device.type == "cuda" and 2 <= dp_world.size <= 8 and cfg.num_experts % dp_world.size == 0 \
-                        and plain_experts:  # (quantised experts go through the collective exchange)
+                        and plain_experts and grouped_ok:
                     from ..parallel.ep import EPExchange
                     tp.ep = EPExchange(dp_world.group, dp_world.rank, dp_world.size, device, cfg.hidden_size,
                                        cfg.num_experts_per_tok, cfg.num_experts, bs.max_step_tokens)
