@@ -117,15 +117,20 @@ def iter_checkpoint(model_dir: str) -> Iterator[Tuple[str, torch.Tensor]]:
 
 
 def synthetic_checkpoint(cfg: ModelConfig, seed: int = 0, std: float = 0.02, device="cpu",
-                         dtype: Optional[torch.dtype] = None) -> Iterator[Tuple[str, torch.Tensor]]:
+                         dtype: Optional[torch.dtype] = None,
+                         expert_filter=None) -> Iterator[Tuple[str, torch.Tensor]]:
     """Random-init N(0, std) weights under plain HF Llama-style names (norm weights = 1). Every rank
-    that iterates with the same seed sees identical tensors, so TP slices are consistent."""
+    that iterates with the same seed sees identical tensors, so TP slices are consistent. Routed experts draw from a
+    generator of their own per (layer, expert), so ``expert_filter(layer index, expert) -> bool`` can leave out the
+    experts another rank owns without changing any other tensor: an expert-parallel rank of a 256-expert model
+    generates 1/ep_size of the expert weights instead of all of them."""
     dtype = dtype or getattr(torch, cfg.torch_dtype, torch.bfloat16)
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
+    cur = [gen]
 
     def rnd(*shape):
-        return (torch.randn(*shape, generator=gen, device=device, dtype=torch.float32) * std).to(dtype)
+        return (torch.randn(*shape, generator=cur[0], device=device, dtype=torch.float32) * std).to(dtype)
 
     def ones(n):
         return torch.ones(n, device=device, dtype=dtype)
@@ -175,9 +180,15 @@ def synthetic_checkpoint(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dev
             if cfg.topk_method == "noaux_tc":
                 yield m + ".gate.e_score_correction_bias", torch.zeros(cfg.num_experts, device=device, dtype=torch.float32)
             for e in range(cfg.num_experts):
+                if expert_filter is not None and not expert_filter(i, e):
+                    continue
+                ge = torch.Generator(device=device)
+                ge.manual_seed((seed * 1000003 + i * 65537 + e + 1) & 0x7FFFFFFFFFFF)
+                cur[0] = ge
                 yield f"{m}.experts.{e}.gate_proj.weight", rnd(I, H)
                 yield f"{m}.experts.{e}.up_proj.weight", rnd(I, H)
                 yield f"{m}.experts.{e}.down_proj.weight", rnd(H, I)
+                cur[0] = gen
             if cfg.num_shared_experts:
                 S = cfg.shared_expert_intermediate_size
                 yield m + ".shared_expert.gate_proj.weight", rnd(S, H)
@@ -410,6 +421,17 @@ class WeightLoader:
             self.out[prefix + ".zeros"] = z.to(self.dtype).contiguous()
             return
         self._put(prefix + ".weight", w)
+
+    def owns_expert(self, layer_idx: int, logical_expert: int) -> bool:
+        """Whether this rank keeps routed expert ``logical_expert`` of layer ``layer_idx`` (expert parallelism)."""
+        if self.ep_size <= 1:
+            return True
+        if self.layer_range is not None and layer_idx not in self.layer_range and layer_idx < self.cfg.num_layers:
+            return False
+        perm = self._perm_of(f"model.layers.{layer_idx}")
+        e = perm[logical_expert] if perm else logical_expert
+        per = max(self.cfg.num_experts // self.ep_size, 1)
+        return self.ep_rank * per <= e < (self.ep_rank + 1) * per
 
     def _perm_of(self, layer_name: str) -> Optional[List[int]]:
         """Logical -> physical expert permutation of ``model.layers.N`` (None: identity); also leaves the map in the
@@ -875,7 +897,8 @@ def load_model_weights(cfg: ModelConfig, model_dir: str = "", tp_rank: int = 0, 
     loader = WeightLoader(cfg, tp_rank, tp_size, device, dtype, quantize, ep_rank=ep_rank, ep_size=ep_size,
                           model_dir=model_dir, layer_range=layer_range)
     if synthetic_seed is not None or not model_dir:
-        src = synthetic_checkpoint(cfg, synthetic_seed or 0, synthetic_std, device=device, dtype=dtype)
+        src = synthetic_checkpoint(cfg, synthetic_seed or 0, synthetic_std, device=device, dtype=dtype,
+                                   expert_filter=loader.owns_expert if loader.ep_size > 1 else None)
         return loader.load(src)
     # ENABLE_MODEL_CACHE=1: the processed (sliced, fused, quantised) tensors of this rank are kept as one
     # safetensors file and reloaded at the next start instead of running the loader again
