@@ -520,6 +520,11 @@ static int fill_ctx(LlCtx* ctx, int rank, int ws, void* const* recv, long long r
 
 using namespace ksana;
 
+// The kernels are instantiated for up to 2, 4 and 8 ranks (register array sizes, loads in flight). With fewer GPUs than
+// 8 at hand, a test can ask for a larger instantiation than the rank count needs: the 8-rank code then runs on 2 or 4.
+static int g_ll_kernel_ranks = 0;
+KSANA_API void ksana_ll_set_kernel_ranks(int ranks) { g_ll_kernel_ranks = ranks; }
+
 // y = AllGather(RMSNorm(residual_slice += ReduceScatter(A * W^T)) * norm_w) in one launch, for small M.
 // A: [M, K] bf16 (pitch lda), W: [N, K] bf16 (pitch ldw); hbuf: this rank's activation buffer [>= M][N] bf16.
 // Per-rank symmetric buffers of 8-byte words, zero-initialised once (arrays indexed by rank):
@@ -544,11 +549,12 @@ KSANA_API int ksana_gemm_ll_reduce_norm(const void* A, const void* W, int M, int
     return -2;
   if (make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, LL_BN, LL_BK, CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
-  auto kern = ws <= 2 ? gemm_ll_reduce_norm_kernel<2, 6> : ws <= 4 ? gemm_ll_reduce_norm_kernel<4, 3>
-                                                                   : gemm_ll_reduce_norm_kernel<8, 2>;
-  if (ws <= 2) {
+  const int kws = g_ll_kernel_ranks > ws ? g_ll_kernel_ranks : ws;  // which instantiation (tests: see the setter)
+  auto kern = kws <= 2 ? gemm_ll_reduce_norm_kernel<2, 6> : kws <= 4 ? gemm_ll_reduce_norm_kernel<4, 3>
+                                                                     : gemm_ll_reduce_norm_kernel<8, 2>;
+  if (kws <= 2) {
     if (KSANA_SMEM_ONCE((gemm_ll_reduce_norm_kernel<2, 6>), LL_SMEM) != 0) return -4;
-  } else if (ws <= 4) {
+  } else if (kws <= 4) {
     if (KSANA_SMEM_ONCE((gemm_ll_reduce_norm_kernel<4, 3>), LL_SMEM) != 0) return -4;
   } else {
     if (KSANA_SMEM_ONCE((gemm_ll_reduce_norm_kernel<8, 2>), LL_SMEM) != 0) return -4;
@@ -608,7 +614,8 @@ KSANA_API int ksana_ll_reduce_norm(const void* partial, int ldp, int M, int H, i
                                                                              : (M * (H >> 2) + LL_THREADS - 1) / LL_THREADS;
   if (grid > want) grid = want;
   if (grid < 1) grid = 1;
-  auto kern = ws <= 2 ? ll_reduce_norm_kernel<2, 6> : ws <= 4 ? ll_reduce_norm_kernel<4, 3> : ll_reduce_norm_kernel<8, 2>;
+  const int kws = g_ll_kernel_ranks > ws ? g_ll_kernel_ranks : ws;
+  auto kern = kws <= 2 ? ll_reduce_norm_kernel<2, 6> : kws <= 4 ? ll_reduce_norm_kernel<4, 3> : ll_reduce_norm_kernel<8, 2>;
   kern<<<grid, LL_THREADS, 0, stream>>>(ctx, reinterpret_cast<const __nv_bfloat16*>(partial), ldp, M, H,
                                         reinterpret_cast<__nv_bfloat16*>(residual),
                                         reinterpret_cast<const __nv_bfloat16*>(norm_w), eps, epoch, mode, error_word());

@@ -1,5 +1,6 @@
 """Multi-GPU tests (2, 4 or 8 ranks, one process per GPU): fused reduce + residual + RMSNorm + gather kernel over
 symmetric memory, with and without the NVLS multicast path, and a tensor-parallel model forward."""
+import ctypes
 import os
 import socket
 
@@ -81,6 +82,30 @@ def _worker(rank, world, port, use_mc, q):
         out2 = fc.gemm_ll_reduce_add_norm(xs[rank], wsl[rank], res0.clone(), w, 1e-6).clone()
         torch.cuda.synchronize()
         llerrs.append((T, K, 0.0 if torch.equal(out, out2) else 1.0, 0.0))  # deterministic
+    # the instantiation for up to 8 ranks (other register array sizes and load batching), run on this many ranks:
+    # same sums in the same order, so the same bits
+    if ll_default:
+        lib = cuda.lib()
+        lib.ksana_ll_set_kernel_ranks.argtypes, lib.ksana_ll_set_kernel_ranks.restype = [ctypes.c_int], None
+        for T, K in ((64, 512), (256, 384)):
+            g = torch.Generator(device=dev).manual_seed(11 * T + K)
+            xs = [(torch.randn(T, K, device=dev, generator=g) * 0.5).to(torch.bfloat16) for _ in range(world)]
+            wsl = [(torch.randn(H, K, device=dev, generator=g) * 0.05).to(torch.bfloat16) for _ in range(world)]
+            res0 = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+            w = (1 + 0.1 * torch.randn(H, device=dev, generator=g)).to(torch.bfloat16)
+            base = fc.gemm_ll_reduce_add_norm(xs[rank], wsl[rank], res0.clone(), w, 1e-6).clone()
+            r_base = fc.reduce_add_norm((xs[rank].float() @ wsl[rank].float().t()).to(torch.bfloat16), res0.clone(), w,
+                                        1e-6).clone()
+            torch.cuda.synchronize()
+            dist.barrier()
+            lib.ksana_ll_set_kernel_ranks(8)
+            wide = fc.gemm_ll_reduce_add_norm(xs[rank], wsl[rank], res0.clone(), w, 1e-6).clone()
+            r_wide = fc.reduce_add_norm((xs[rank].float() @ wsl[rank].float().t()).to(torch.bfloat16), res0.clone(), w,
+                                        1e-6).clone()
+            torch.cuda.synchronize()
+            dist.barrier()
+            lib.ksana_ll_set_kernel_ranks(0)
+            llerrs.append((T, K, 0.0 if torch.equal(base, wide) else 1.0, 0.0 if torch.equal(r_base, r_wide) else 1.0))
     report["llerrs"] = llerrs
     # single-kernel GEMM + reduce-scatter + norm + all-gather vs (local GEMMs summed in fp32 -> reference norm)
     ferrs = []
