@@ -449,7 +449,49 @@ class WeightLoader:
         return int(m.group(1)) if m else None
 
     # ---- main entry -------------------------------------------------------------------------------
+    def _fp8_scalar_scales(self, tensors: Iterable[Tuple[str, torch.Tensor]]) -> Iterator[Tuple[str, torch.Tensor]]:
+        """fp8 checkpoints with ONE scale per weight (``quant_method: fp8`` without ``weight_block_size``, and the
+        compressed-tensors / FBGEMM layouts: ``X.weight`` e4m3 + ``X.weight_scale`` scalar, or one scale per output
+        row, + an optional static ``X.input_scale``) are re-expressed for the rest of the loader: a per-tensor scale
+        becomes a block-scale array holding that value in every 128 x 128 block, so the weight stays e4m3 and runs on
+        the block-scaled GEMMs; row-wise scales do not fit the block grid and are folded into a 16-bit weight.
+        Activations are quantised dynamically here, so ``input_scale`` is dropped. The reference's per-tensor path is
+        src/ksana_llm/layers/nvidia/fp8_matmul_layer.cpp."""
+        held: Dict[str, Dict[str, torch.Tensor]] = defaultdict(dict)
+
+        def ready(stem):
+            w, sc = held[stem]["weight"], held.pop(stem)["weight_scale"].float().reshape(-1)
+            if sc.numel() == 1:
+                n, k = w.shape[-2], w.shape[-1]
+                blocks = torch.full(((n + 127) // 128, (k + 127) // 128), float(sc.item()), dtype=torch.float32)
+                if w.dim() == 3:
+                    blocks = blocks.unsqueeze(0).expand(w.shape[0], -1, -1).contiguous()
+                yield stem + ".weight", w
+                yield stem + ".weight_scale_inv", blocks
+            else:
+                yield stem + ".weight", (w.float() * sc.to(w.device).view(-1, 1)).to(self.dtype)
+
+        for name, t in tensors:
+            if name.endswith(".input_scale") or name.endswith(".activation_scale"):
+                continue
+            if name.endswith(".weight_scale") and not name.endswith("weight_scale_inv"):
+                stem = name[:-len(".weight_scale")]
+                held[stem]["weight_scale"] = t
+            elif name.endswith(".weight") and self._fp8(t) and t.dim() >= 2:
+                stem = name[:-len(".weight")]
+                held[stem]["weight"] = t
+            else:
+                yield name, t
+                continue
+            if {"weight", "weight_scale"} <= set(held[stem]):
+                yield from ready(stem)
+        for stem, parts in held.items():
+            if "weight" in parts:
+                raise ValueError(f"fp8 weight {stem}.weight has no weight_scale in the checkpoint")
+
     def load(self, tensors: Iterable[Tuple[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
+        if self.cfg.quant.method in ("fp8", "compressed-tensors", "fbgemm_fp8"):
+            tensors = self._fp8_scalar_scales(tensors)
         for raw_name, t in tensors:
             if re.match(r"(model\.)?(visual|vision_tower|vision_model|vit|multi_modal_projector|mlp1)\.", raw_name):
                 continue  # vision towers belong to the serving plugin, not to the language model

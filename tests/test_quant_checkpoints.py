@@ -240,3 +240,42 @@ def test_w4a8_awq_checkpoint_runs_on_its_four_bit_grid(moe, tmp_path):
         p = "model.layers.1.self_attn.o_proj"
         deq = ref.dequant_int4_group(wq[p + ".qweight"], wq[p + ".scales"].float(), wq[p + ".zeros"].float(), GROUP)
         assert torch.allclose(deq * wq[p + ".pre_quant_scale"].float(), wd[p + ".weight"], atol=1e-5)
+
+
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_fp8_checkpoint_with_one_scale_per_weight(per_channel):
+    """``quant_method: fp8`` without block sizes: e4m3 weights with a scalar ``weight_scale`` (kept e4m3, the scale
+    spread over the 128 x 128 block grid) or one scale per output row (folded into a dense weight); static
+    ``input_scale`` entries are ignored."""
+    cfg = model_config_from_dict(BASE)
+    qcfg = model_config_from_dict(dict(BASE, quantization_config=dict(quant_method="fp8", activation_scheme="static")))
+    dense, quant = [], []
+    for name, w in synthetic_checkpoint(cfg, seed=7, dtype=torch.float32):
+        if not name.endswith("_proj.weight"):
+            dense.append((name, w))
+            quant.append((name, w))
+            continue
+        amax = w.abs().amax(dim=1, keepdim=True) if per_channel else w.abs().amax()
+        scale = (amax / 448.0).clamp_min(1e-8)
+        q = (w / scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+        dense.append((name, q.float() * scale))
+        stem = name[:-len(".weight")]
+        quant += [(stem + ".input_scale", torch.tensor(0.02)), (name, q),
+                  (stem + ".weight_scale", scale.reshape(-1) if per_channel else scale.reshape(()))]
+    want, _ = _hidden(cfg, dense)
+    got, w = _hidden(qcfg, quant)
+    k = "model.layers.0.mlp.down_proj"
+    if per_channel:
+        assert w[k + ".weight"].dtype == torch.float32 and (k + ".weight_scale_inv") not in w
+        assert (got - want).abs().max().item() < 1e-5
+    else:
+        assert w[k + ".weight"].dtype == torch.float8_e4m3fn and w[k + ".weight_scale_inv"].shape == (1, 2)
+        # the weights are the checkpoint's (re-rounded once onto power-of-two block scales); activations are
+        # quantised per token and 128 channels at run time, which the dense reference is not
+        assert (got - want).abs().max().item() < 0.15 * want.abs().max().item()
+        assert (got - want).abs().mean().item() < 0.02 * want.abs().max().item()
+    # tensor-parallel slices load too (this tiny model's shards are narrower than a 128-wide scale block, so only
+    # the row-wise form, which ends up dense, can be cut here)
+    if per_channel:
+        for rank in range(2):
+            WeightLoader(qcfg, tp_rank=rank, tp_size=2, dtype=torch.float32).load(quant)
