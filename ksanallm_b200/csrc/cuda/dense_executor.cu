@@ -58,6 +58,8 @@ int ksana_silu_mul_quant_ue8m0(const void* x, int ldx, void* q, int ldq, float* 
                                cudaStream_t stream);
 int ksana_gemm_mxf8(const void* A8, const void* sfa, const void* W8, const void* sfb, void* C, const void* bias, int M,
                     int N, int K, int lda, int ldw, int ldc, int variant, cudaStream_t stream);
+int ksana_gemm_bf16_swiglu(const void* A, const void* W_interleaved, void* C, int M, int N, int K, int lda, int ldw,
+                           int ldc, cudaStream_t stream);
 void ksana_gemm_set_lane(int lane);
 }
 
@@ -287,10 +289,20 @@ struct Exec {
   bool mlp(const KsanaDenseLayer& w, Range& g, bool whole_step, char* gu, char* act, char* res) {
     const int T = g.rows, H = m->hidden, I = m->inter;
     cudaStream_t st = g.stream;
-    if (!step(7, linear(g, g.h2, w.wgu, w.sgu, w.fgu, gu, nullptr, 2 * I, H, 2 * I, whole_step))) return false;
+    // bf16, prefill-sized (the CTA-pair GEMM's range) and an interleaved weight copy at hand: the activation is the
+    // GEMM's epilogue
+    const bool fused_act = w.wgu_il != nullptr && w.sgu == nullptr && w.sdown == nullptr && T >= 384;
+    if (fused_act) {
+      if (!step(7, ksana_gemm_bf16_swiglu(g.h2, w.wgu_il, act, T, 2 * I, H, H, H, I, st))) return false;
+    } else if (!step(7, linear(g, g.h2, w.wgu, w.sgu, w.fgu, gu, nullptr, 2 * I, H, 2 * I, whole_step))) {
+      return false;
+    }
     // fp8 down projection: SiLU * up is written once, already quantised
     int c8;
-    if (w.sdown == nullptr) {
+    if (fused_act) {
+      c8 = 0;
+      --(*launches);
+    } else if (w.sdown == nullptr) {
       c8 = ksana_silu_mul(gu, 2 * I, act, I, T, I, st);
     } else if (m->fp8_pow2 == 0) {
       c8 = ksana_silu_mul_quant_fp8(gu, 2 * I, a8(g), I, sa(g), T, I, st);

@@ -27,6 +27,9 @@ struct KsanaDenseLayer {
   const void* fo;
   const void* fgu;
   const void* fdown;
+  // optional copy of wgu with gate / up rows interleaved in groups of 16: prefill-sized steps then run the gated FFN's
+  // first GEMM with the SiLU-mul epilogue (ksana_gemm_bf16_swiglu) instead of GEMM + activation kernel
+  const void* wgu_il;
 };
 
 struct KsanaDenseModel {

@@ -328,6 +328,19 @@ void gemm_pair_set_lane(int lane);
 // a lane owns its own parking space for partial tiles. Default lane 0.
 KSANA_API void ksana_gemm_set_lane(int lane) { ksana::gemm_pair_set_lane(lane); }
 
+// Gated FFN in one kernel: C[M, N / 2] = SiLU(A Wg^T) * (A Wu^T), for a weight whose gate and up rows are interleaved
+// in groups of 16 (rows [32 b, 32 b + 16) = gate rows of features 16 b .. 16 b + 15, the next 16 rows their up rows),
+// so every 32 accumulator columns of the CTA-pair GEMM hold 16 (gate, up) pairs and the activation never goes through
+// memory as a [M, N] intermediate. N = 2 x features, N % 32 == 0; otherwise the rules of ksana_gemm_bf16. The
+// reference's counterpart is its fused gated GEMM (3rdparty/LLM_kernels/csrc/kernels/nvidia/asymmetric_gemm/
+// fused_gated_gemm/).
+KSANA_API int ksana_gemm_bf16_swiglu(const void* A, const void* W_interleaved, void* C, int M, int N, int K, int lda,
+                                     int ldw, int ldc, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N & 31) || (K & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return -1;
+  return ksana::gemm_bf16_pair(A, W_interleaved, C, nullptr, M, N, K, lda, ldw, ldc, 0, 256, 1, stream);
+}
+
 static unsigned long long* g_gemm_trace = nullptr;
 // Debug aid: device buffer of 8 uint64 that receives the timeline of CTA 0 of subsequent GEMM launches (nullptr: off).
 KSANA_API void ksana_gemm_set_trace(void* buf) { g_gemm_trace = reinterpret_cast<unsigned long long*>(buf); }

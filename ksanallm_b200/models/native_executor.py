@@ -21,7 +21,7 @@ P, I, F, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 
 class _Layer(ctypes.Structure):
     _fields_ = [(n, P) for n in ("wqkv", "bqkv", "wo", "ln2", "wgu", "wdown", "next_ln", "q_norm", "k_norm",
-                                 "kv_cache", "sqkv", "so", "sgu", "sdown", "fqkv", "fo", "fgu", "fdown")]
+                                 "kv_cache", "sqkv", "so", "sgu", "sdown", "fqkv", "fo", "fgu", "fdown", "wgu_il")]
 
 
 class _Model(ctypes.Structure):
@@ -121,6 +121,16 @@ class DenseExecutor:
                     L.fqkv, L.fo = _p(layer.attn.qkv.sfb()), _p(layer.attn.o_proj.sfb())
                     L.fgu, L.fdown = _p(layer.ffn.up.sfb()), _p(layer.ffn.down.sfb())
         self.fp8 = model.layers[0].attn.qkv.kind == "fp8_block"
+        # KSANA_FUSED_SWIGLU=1: keep a second copy of every gate_up weight with gate / up rows interleaved in groups of
+        # 16, so prefill-sized steps run SiLU-mul as the GEMM's epilogue (costs the memory of the gate_up weights again)
+        self._wgu_il = []
+        if os.environ.get("KSANA_FUSED_SWIGLU", "0") == "1" and not self.fp8 and self.inter % 16 == 0:
+            for i, layer in enumerate(model.layers):
+                w = layer.ffn.up.weight
+                I_ = w.shape[0] // 2
+                il = torch.stack((w[:I_].view(I_ // 16, 16, -1), w[I_:].view(I_ // 16, 16, -1)), 1).reshape(w.shape)
+                self._wgu_il.append(il.contiguous())
+                self._layers[i].wgu_il = self._wgu_il[-1].data_ptr()
         m = self._m = _Model()
         m.hidden, m.heads, m.kv_heads, m.head_dim, m.inter, m.n_layers = self.H, self.h, self.hk, self.d, self.inter, n
         m.eps = float(cfg.rms_norm_eps)

@@ -43,6 +43,7 @@ class _Sig:
     ksana_read_error = ([I], ctypes.c_uint)
     ksana_sm_count = ([], I)
     ksana_gemm_bf16 = ([P, P, P, P, I, I, I, I, I, I, I, I, I, P, LL, P, I, P], I)
+    ksana_gemm_bf16_swiglu = ([P, P, P, I, I, I, I, I, I, P], I)
     ksana_gemm_fp8_block = ([P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, LL, P, I, P], I)
     ksana_moe_route = ([P, I, P, I, I, I, I, I, I, I, F, P, P, P], I)
     ksana_moe_permute = ([P, I, P, I, I, I, I, I, P, P, P, P, P], I)
@@ -173,6 +174,22 @@ def gemm_fp8_block(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws_inv:
                                       1 if out.dtype == torch.float32 else 0, splits, _ptr(w.gemm_ws),
                                       w.gemm_ws.numel(), _ptr(w.gemm_counters), w.gemm_counters.numel(), _stream())
     _check(code, f"gemm_fp8_block M={M} N={N} K={K}")
+    return out
+
+
+def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
+    """[2 I, K] (gate rows, then up rows) -> the same rows interleaved in groups of 16, the layout of gemm_bf16_swiglu."""
+    I_ = w.shape[0] // 2
+    return torch.stack((w[:I_].view(I_ // 16, 16, -1), w[I_:].view(I_ // 16, 16, -1)), 1).reshape(w.shape).contiguous()
+
+
+def gemm_bf16_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+    """SiLU(x Wg^T) * (x Wu^T) in one kernel: x [M, K] bf16, w_interleaved [2 I, K] from interleave_gate_up -> [M, I]."""
+    M, K = x.shape
+    N = w_interleaved.shape[0]
+    out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=x.device)
+    _check(lib().ksana_gemm_bf16_swiglu(_ptr(x), _ptr(w_interleaved), _ptr(out), M, N, K, x.stride(0),
+                                        w_interleaved.stride(0), out.stride(0), _stream()), "gemm_bf16_swiglu")
     return out
 
 

@@ -85,3 +85,19 @@ def test_gemm_deterministic(bn):
     b = cuda.gemm_bf16(x, w, bn=bn)
     torch.cuda.synchronize()
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("M,I,K", [(512, 1408, 1024), (400, 688, 512), (2048, 5504, 4096)])
+def test_gemm_with_silu_mul_epilogue(M, I, K):
+    """Gated FFN front half in one kernel (gate / up rows interleaved in groups of 16) against fp32 math."""
+    from ksanallm_b200.ops import cuda
+    torch.manual_seed(M + I)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device="cuda") * 0.05).to(torch.bfloat16)
+    out = cuda.gemm_bf16_swiglu(x, cuda.interleave_gate_up(w))
+    torch.cuda.synchronize()
+    assert cuda.read_error() == 0
+    y = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(y[:, :I]) * y[:, I:]
+    assert out.shape == (M, I)
+    assert (out.float() - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())

@@ -99,3 +99,26 @@ def test_native_rebinds_a_new_cache_at_the_old_address():
     for a, b in zip(kv_2, kv_3):
         assert torch.equal(a, b)
     del spacer, first_ptr
+
+
+def test_native_with_fused_silu_mul_gemm(monkeypatch):
+    """KSANA_FUSED_SWIGLU=1: prefill-sized steps run the gated FFN's first GEMM with the activation as its epilogue
+    (fp32 SiLU-mul on the accumulators instead of on the bf16-rounded GEMM output: close, not bit-equal)."""
+    from ksanallm_b200.engine.step_input import make_step_input
+    from ksanallm_b200.ops import cuda
+    monkeypatch.setenv("KSANA_FUSED_SWIGLU", "1")
+    m = _build("llama")
+    T = 450
+    nb = (T + 15) // 16
+    bt = torch.arange(nb, dtype=torch.int32).view(1, nb)
+    meta = make_step_input([(7 * i + 3) % 1000 for i in range(T)], list(range(T)), list(range(T)), [0, T], [T], bt,
+                           num_prefill=1, device="cuda")
+    ex = m._native_executor()
+    assert ex is not None and len(ex._wgu_il) == len(m.layers)
+    out_fused = m.forward(meta, m.allocate_kv_cache(nb + 1, 16)).clone()
+    m._native = None
+    out_python = m.forward(meta, m.allocate_kv_cache(nb + 1, 16)).clone()
+    torch.cuda.synchronize()
+    assert cuda.read_error() == 0
+    err = (out_fused.float() - out_python.float()).abs().max().item()
+    assert err <= 3e-2 * out_python.float().abs().max().item(), err
