@@ -54,6 +54,8 @@ class LinearW:
         self.zeros = weights.get(prefix + ".zeros")
         self.group = 128
         self.sz = None
+        # act-order GPTQ: the 4-bit columns are stored group by group; the input is gathered the same way
+        self.perm = weights.get(prefix + ".perm")
         # AWQ smoothing factor of W4A8 checkpoints: y = (x * pre) @ W^T. Folded into a dense weight once; a weight
         # that kept its 4-bit grid gets its input scaled at run time.
         self.pre = weights.get(prefix + ".pre_quant_scale")
@@ -107,6 +109,8 @@ class LinearW:
         b = self.bias if add_bias else None
         if self.pre is not None:
             x = x * self.pre.to(x.dtype)
+        if self.perm is not None and self.kind == "int4":
+            x = x.index_select(-1, self.perm.to(x.device))
         if self.kind == "dense":
             return ops.linear(x, self.weight, b)
         if self.kind == "fp8_block":

@@ -220,12 +220,18 @@ class QuantW:
     """A 4-bit group-quantised linear weight travelling through the loader in place of a dense tensor:
     ``q`` [N, K] uint8 values 0..15, ``scales`` / ``zeros`` [N, K / group] fp32, w = (q - zero) * scale.
     Supports exactly the operations the loader applies to weights (row / column slices, row concatenation), so
-    tensor-parallel slicing and projection fusing keep the checkpoint's quantisation grid bit for bit."""
+    tensor-parallel slicing and projection fusing keep the checkpoint's quantisation grid bit for bit.
+
+    ``perm`` (act-order GPTQ): the stored columns are input channels ``perm[0], perm[1], ...`` (sorted by group, so
+    groups are contiguous again); the layer then gathers its input the same way, y = W[:, perm] x[perm]. Row slices
+    and concatenation of weights with the same permutation keep it; a K slice (row-parallel shards) cannot, because
+    a rank's channels no longer form whole groups, and returns the dense weight."""
 
     dtype = torch.uint8
 
-    def __init__(self, q: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group: int):
-        self.q, self.scales, self.zeros, self.group = q, scales, zeros, group
+    def __init__(self, q: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group: int,
+                 perm: Optional[torch.Tensor] = None):
+        self.q, self.scales, self.zeros, self.group, self.perm = q, scales, zeros, group, perm
 
     @property
     def shape(self):
@@ -235,23 +241,38 @@ class QuantW:
         return 2
 
     def rows(self, a: int, b: int) -> "QuantW":
-        return QuantW(self.q[a:b], self.scales[a:b], self.zeros[a:b], self.group)
+        return QuantW(self.q[a:b], self.scales[a:b], self.zeros[a:b], self.group, self.perm)
 
-    def cols(self, a: int, b: int) -> "QuantW":
+    def cols(self, a: int, b: int):
+        if a == 0 and b == self.q.shape[1]:
+            return self
+        if self.perm is not None:
+            return self.dequant()[:, a:b]
         g = self.group
         if a % g or b % g:
             raise ValueError(f"a K slice [{a}, {b}) must fall on group boundaries (group {g})")
         return QuantW(self.q[:, a:b], self.scales[:, a // g:b // g], self.zeros[:, a // g:b // g], g)
 
     @staticmethod
-    def cat0(parts) -> "QuantW":
+    def cat0(parts):
+        perms = [p.perm for p in parts]
+        same = all(x is None for x in perms) or (all(x is not None for x in perms) and
+                                                 all(torch.equal(perms[0], x) for x in perms[1:]))
+        if not same:  # projections quantised with different channel orders cannot share one input gather
+            return torch.cat([p.dequant() for p in parts], 0)
         return QuantW(torch.cat([p.q for p in parts], 0), torch.cat([p.scales for p in parts], 0),
-                      torch.cat([p.zeros for p in parts], 0), parts[0].group)
+                      torch.cat([p.zeros for p in parts], 0), parts[0].group, perms[0])
 
     def dequant(self) -> torch.Tensor:
+        """The dense weight in the checkpoint's own input-channel order."""
         N, K = self.q.shape
         qf = self.q.float().view(N, K // self.group, self.group)
-        return ((qf - self.zeros.unsqueeze(-1)) * self.scales.unsqueeze(-1)).view(N, K)
+        w = ((qf - self.zeros.unsqueeze(-1)) * self.scales.unsqueeze(-1)).view(N, K)
+        if self.perm is None:
+            return w
+        out = torch.empty_like(w)
+        out[:, self.perm.long()] = w
+        return out
 
 
 _AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)  # nibble i of an AutoAWQ word holds column 8 * word + _AWQ_ORDER[i]
@@ -274,8 +295,10 @@ def _unpack_nibbles(packed: torch.Tensor, dim: int, order=None) -> torch.Tensor:
 
 def unpack_gptq(qweight, qzeros, scales, g_idx, group: int, v1_zero_offset: bool):
     """AutoGPTQ layout: qweight [K/8, N] (packed along K), qzeros [K/g, N/8] (packed along N; the v1 format stores
-    zero - 1), scales [K/g, N], g_idx [K]. Returns (QuantW or None, dense fp32 weight or None): act-order
-    checkpoints (groups not contiguous in K) are returned dense."""
+    zero - 1), scales [K/g, N], g_idx [K]. Returns (QuantW or None, dense fp32 weight or None). Act-order checkpoints
+    (``g_idx`` not ascending: channels were quantised in order of importance) keep their grid with the columns
+    gathered group by group and the gather recorded in ``QuantW.perm``; only a ``g_idx`` whose groups are not all of
+    the nominal size is returned dense."""
     q = _unpack_nibbles(qweight, 0).t().contiguous()                 # [N, K]
     z = _unpack_nibbles(qzeros, 1).t().contiguous().float()          # [N, K/g]
     if v1_zero_offset:
@@ -286,6 +309,9 @@ def unpack_gptq(qweight, qzeros, scales, g_idx, group: int, v1_zero_offset: bool
         gi = g_idx.to(torch.int64)
         trivial = torch.equal(gi, torch.arange(K, device=gi.device) // group)
         if not trivial:
+            perm = torch.argsort(gi, stable=True)
+            if torch.equal(gi[perm], torch.arange(K, device=gi.device) // group):
+                return QuantW(q[:, perm].contiguous(), sc, z, group, perm.to(torch.int32)), None
             w = (q.float() - z[:, gi]) * sc[:, gi]
             return None, w
     return QuantW(q, sc, z, group), None
@@ -401,6 +427,8 @@ class WeightLoader:
             self.out[prefix + ".qweight"] = self._own(ref.pack_int4(w.q.to(torch.int32)))
             self.out[prefix + ".scales"] = self._own(w.scales.to(self.dtype))
             self.out[prefix + ".zeros"] = self._own(w.zeros.to(self.dtype))
+            if w.perm is not None:
+                self.out[prefix + ".perm"] = self._own(w.perm.to(torch.int32))
             return
         if scale_inv is not None:
             if FP8_POW2_SCALES and w.dim() == 2 and w.dtype == torch.float8_e4m3fn:
@@ -665,7 +693,9 @@ class WeightLoader:
                      re.fullmatch(r"(shared_expert\.)?(q_proj|k_proj|v_proj|o_proj|gate_proj|up_proj|down_proj)", stem)
                      and (qw is not None) and qw.shape[1] % 128 == 0 and g % 64 == 0)
         # routed experts keep their 4-bit grid too (also under MLA): they are most of a MoE checkpoint's bytes
+        # (not act-order ones: the stacked expert kernels have no per-expert input gather)
         keep_grid = keep_grid or (block == "mlp" and (qw is not None) and g % 64 == 0 and qw.shape[1] % g == 0 and
+                                  qw.perm is None and
                                   bool(re.fullmatch(r"experts\.\d+\.(gate_proj|up_proj|down_proj)", stem)))
         value = qw if keep_grid else (dense if dense is not None else qw.dequant())
         if not isinstance(value, QuantW):

@@ -81,12 +81,37 @@ def test_quantised_checkpoint_keeps_its_grid(fmt):
     assert (got - want).abs().max().item() < 1e-5
 
 
-def test_gptq_act_order_falls_back_to_dense():
+def test_gptq_act_order_keeps_its_four_bit_grid():
+    """Act-order: input channels quantised in a shuffled order (``g_idx`` not ascending). The columns are stored group
+    by group, the layer gathers its input the same way (``.perm``), the 4-bit grid survives bit for bit."""
     cfg, dense, qcfg, quant = _quantised_checkpoint("gptq", act_order=True)
     want, _ = _hidden(cfg, dense)
     got, w = _hidden(qcfg, quant)
-    assert "model.layers.0.self_attn.query_key_value.weight" in w  # permuted groups: stored dequantised
+    for stem in ("self_attn.query_key_value", "self_attn.o_proj", "mlp.gate_up_proj", "mlp.down_proj"):
+        p = f"model.layers.0.{stem}"
+        assert p + ".qweight" in w and p + ".perm" in w and p + ".weight" not in w
+        perm = w[p + ".perm"].long()
+        assert torch.equal(torch.sort(perm).values, torch.arange(perm.numel()))
     assert (got - want).abs().max().item() < 1e-5
+
+
+def test_gptq_act_order_tensor_parallel():
+    """Column-parallel projections keep the grid (their K is whole); a row-parallel shard holds scattered members
+    of every group and is stored dense."""
+    cfg, dense, qcfg, quant = _quantised_checkpoint("gptq", act_order=True)
+    for rank in range(2):
+        wd = WeightLoader(cfg, tp_rank=rank, tp_size=2, dtype=torch.float32).load(dense)
+        wq = WeightLoader(qcfg, tp_rank=rank, tp_size=2, dtype=torch.float32).load(quant)
+        for stem in ("self_attn.query_key_value", "mlp.gate_up_proj"):
+            p = f"model.layers.1.{stem}"
+            deq = ref.dequant_int4_group(wq[p + ".qweight"], wq[p + ".scales"].float(), wq[p + ".zeros"].float(), GROUP)
+            full = torch.empty_like(deq)
+            full[:, wq[p + ".perm"].long()] = deq
+            assert (full - wd[p + ".weight"]).abs().max().item() < 1e-6, (rank, stem)
+        for stem in ("self_attn.o_proj", "mlp.down_proj"):
+            p = f"model.layers.1.{stem}"
+            assert p + ".qweight" not in wq
+            assert (wq[p + ".weight"] - wd[p + ".weight"]).abs().max().item() < 1e-6, (rank, stem)
 
 
 @pytest.mark.parametrize("fmt", ["gptq", "awq"])
