@@ -489,15 +489,18 @@ class WeightLoader:
 
         def ready(stem):
             w, sc = held[stem]["weight"], held.pop(stem)["weight_scale"].float().reshape(-1)
-            if sc.numel() == 1:
-                n, k = w.shape[-2], w.shape[-1]
-                blocks = torch.full(((n + 127) // 128, (k + 127) // 128), float(sc.item()), dtype=torch.float32)
+            n, k = w.shape[-2], w.shape[-1]
+            per_matrix = sc.numel() == 1 or (w.dim() == 3 and sc.numel() == w.shape[0])  # one scale per (expert) matrix
+            if per_matrix:
+                nb, kb = (n + 127) // 128, (k + 127) // 128
                 if w.dim() == 3:
-                    blocks = blocks.unsqueeze(0).expand(w.shape[0], -1, -1).contiguous()
+                    blocks = sc.expand(w.shape[0]).reshape(-1, 1, 1).expand(-1, nb, kb).contiguous()
+                else:
+                    blocks = torch.full((nb, kb), float(sc.item()), dtype=torch.float32)
                 yield stem + ".weight", w
                 yield stem + ".weight_scale_inv", blocks
-            else:
-                yield stem + ".weight", (w.float() * sc.to(w.device).view(-1, 1)).to(self.dtype)
+            else:  # one scale per output row (of every expert)
+                yield stem + ".weight", (w.float() * sc.to(w.device).reshape(*w.shape[:-1], 1)).to(self.dtype)
 
         for name, t in tensors:
             if name.endswith(".input_scale") or name.endswith(".activation_scale"):

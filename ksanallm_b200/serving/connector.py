@@ -189,6 +189,12 @@ class PDConnector:
         self._tracker.set_callbacks([s_.on_layer for s_ in armed])
         model.progress = self._tracker
 
+    def cancel_export(self, request_id: str) -> None:
+        """The request ended without a hand-over (error, abort): close its session, if any."""
+        sess = self._by_rid.get(request_id)
+        if sess is not None:
+            self._drop(sess)
+
     def _drop(self, sess) -> None:
         self._by_rid.pop(sess.request_id, None)
         for k in [k for k, v in self._sessions.items() if v is sess]:

@@ -548,6 +548,8 @@ class KsanaLLMEngine:
             # hand the request over: KV of the prompt's full blocks + the first token
             await loop.run_in_executor(self.pool, self.connector.export, pd_rid, (req_ctx or {}).get("kv-comm-group-key", ""),
                                        list(req.prompt_tokens), list(req.seqs[0].output_tokens))
+        elif pd_rid and self.connector.role == "prefill":
+            self.connector.cancel_export(pd_rid)
         if self.plugin is not None:
             self.plugin.postprocess(request_dict, out)
         if streamer:  # a prefill instance answers a streaming request with its single item
