@@ -72,7 +72,9 @@ class PluginHost:
             fn(ksana_python_input=None, ksana_python_output=output, request_dict=request_dict)
 
 
-BUNDLED = {"qwen2_vl": "qwen2_vl", "qwen2_5_vl": "qwen2_vl", "internvl": "internvl", "internvl_chat": "internvl"}
+BUNDLED = {"qwen2_vl": "qwen2_vl", "qwen2_5_vl": "qwen2_vl", "internvl": "internvl", "internvl_chat": "internvl",
+           "qwen_vl": "qwen_vl", "qwenvl": "qwen_vl", "internlmxcomposer2": "internlmxcomposer2",
+           "internlm_xcomposer2": "internlmxcomposer2"}
 
 
 def search_plugin_path(model_dir: str, plugin_cfg: Dict[str, Any]) -> Optional[str]:
