@@ -1073,9 +1073,11 @@ class LLMEngine:
                 return
 
     # ---- attention data parallelism ------------------------------------------------------------------------------
-    def attach_dp(self, coordinator) -> None:
+    def attach_dp(self, coordinator, balance_coordinator=None) -> None:
         """This engine is one DP rank: its own requests, scheduler and KV cache; MoE blocks exchange tokens with the
-        other ranks, so every rank steps in lock-step (``run_dp``)."""
+        other ranks, so every rank steps in lock-step (``run_dp``). ``balance_coordinator``: for DP groups with tensor
+        parallelism inside, a coordinator over the groups' leaders only (None on followers): the prefill balancer's
+        per-step agreement is between the ranks that schedule."""
         self.dp = coordinator
         self.async_mode = False
         self.tp.ep_dp = True
@@ -1083,10 +1085,10 @@ class LLMEngine:
         # in every pass: one draft per step under attention data parallelism
         self.mtp_steps = min(self.mtp_steps, 1)
         lb = self.serving.setting.batch_scheduler.attention_dp_lb_config
-        if lb.enable_balance and self.tp.size == 1:  # (its collective is not part of the followers' step protocol)
+        bc = coordinator if self.tp.size == 1 else balance_coordinator
+        if lb.enable_balance and bc is not None:
             from ..parallel.attn_dp import ADPBalance
-            self.adp_balance = ADPBalance(coordinator, lb.max_waiting_steps, lb.max_waiting_time_in_ms,
-                                          lb.min_qps_for_waiting)
+            self.adp_balance = ADPBalance(bc, lb.max_waiting_steps, lb.max_waiting_time_in_ms, lb.min_qps_for_waiting)
 
     def run_dp(self, max_steps: int = 1 << 30) -> int:
         """Steps until NO rank has unfinished work (a rank whose own requests are done keeps running mock steps)."""

@@ -318,7 +318,14 @@ class KsanaLLMEngine:
         if dp_world is not None:
             import torch.distributed as dist
             from ..parallel.attn_dp import DPCoordinator, DPRequestRouter, DPRequestWorker
-            self.llm.attach_dp(DPCoordinator(dp_world.group, device if device.type == "cuda" else None))
+            balance = None
+            if attn_tp > 1 and self.serving.setting.batch_scheduler.attention_dp_lb_config.enable_balance:
+                # the prefill balancer's agreement runs between the DP groups' leaders (the ranks that schedule);
+                # every rank creates the group, only leaders use it
+                leaders = dist.new_group(ranks=[gi * attn_tp for gi in range(g.attn_data_para_size)], backend="gloo")
+                if dp_tp_rank == 0:
+                    balance = DPCoordinator(leaders)
+            self.llm.attach_dp(DPCoordinator(dp_world.group, device if device.type == "cuda" else None), balance)
             if dp_ctl is not None:
                 self.llm.attach_control_group(dp_ctl, src=dp_group_id * attn_tp)
                 self.llm.is_driver = dp_tp_rank == 0

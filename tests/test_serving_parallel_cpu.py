@@ -16,9 +16,12 @@ BODY = {"input_tokens": [(7 * i + 3) % 200 + 3 for i in range(23)], "stream": Fa
 
 
 def _serving(**glob):
-    return parse_serving_config({"setting": {"global": glob, "batch_scheduler": {
-        "max_batch_size": 4, "max_step_tokens": 64, "max_token_len": 128, "max_pp_batch_num": 2},
-        "block_manager": {"block_token_num": 16}}})
+    sched = {"max_batch_size": 4, "max_step_tokens": 64, "max_token_len": 128, "max_pp_batch_num": 2}
+    if glob.pop("balance", False):
+        sched["attention_dp_lb_config"] = {"enable_balance": True, "max_waiting_steps": 3,
+                                           "max_waiting_time_in_ms": 600000}
+    return parse_serving_config({"setting": {"global": glob, "batch_scheduler": sched,
+                                             "block_manager": {"block_token_num": 16}}})
 
 
 def _engine(model="tiny-llama", **glob):
@@ -114,6 +117,16 @@ def test_attention_dp_groups_with_tensor_parallel_inside():
     schedules its own requests, its follower hears about every step (also the empty ones) and joins the exchange."""
     want = _single("tiny-moe", 4)
     got, placed = _spawn(4, dict(tensor_para_size=4, attn_data_para_size=2, expert_para_size=4), "tiny-moe", 4)
+    assert got == want
+    assert placed == [2, 2]
+
+
+def test_prefill_balancer_between_the_leaders_of_tensor_parallel_dp_groups():
+    """attention_dp_lb_config.enable_balance with tensor parallelism inside the DP groups: the leaders agree per step
+    on holding new prompts back (a group of their own), the followers just execute; same tokens as without."""
+    want = _single("tiny-moe", 4)
+    got, placed = _spawn(4, dict(tensor_para_size=4, attn_data_para_size=2, expert_para_size=4, balance=True),
+                         "tiny-moe", 4)
     assert got == want
     assert placed == [2, 2]
 
