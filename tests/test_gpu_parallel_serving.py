@@ -63,11 +63,31 @@ def _worker(rank, world, port, out, glob, model, n):
         dist.destroy_process_group()
 
 
+def _free_port() -> int:
+    """A rendezvous port below the ephemeral range whose derived ports (+17 request router, +23 control channel) are
+    free too (a port from bind(0) has neighbours that outgoing connections may be using)."""
+    import random
+    import time
+    rng = random.Random(os.getpid() * 7919 + int(time.time() * 1000) % 100003)
+    for _ in range(200):
+        base = rng.randrange(20000, 30000)
+        socks = []
+        try:
+            for off in (0, 17, 23):
+                s = socket.socket()
+                s.bind(("127.0.0.1", base + off))
+                socks.append(s)
+            return base
+        except OSError:
+            continue
+        finally:
+            for s in socks:
+                s.close()
+    raise RuntimeError("no free port found")
+
+
 def _spawn(world, glob, model, n):
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    port = s.getsockname()[1]
-    s.close()
+    port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, world, port, q, glob, model, n)) for r in range(world)]

@@ -11,6 +11,29 @@ import torch.multiprocessing as mp
 from ksanallm_b200.config.schema import parse_serving_config
 from ksanallm_b200.serving.ksana_engine import EngineArgs, KsanaLLMEngine
 
+def _free_port() -> int:
+    """A rendezvous port below the ephemeral range whose derived ports (+17 request router, +23 control channel) are
+    free too: ports handed out by bind(0) sit in the range the kernel also uses for outgoing connections, so a derived
+    port could already be some connection's source port."""
+    import random
+    rng = random.Random(os.getpid() * 7919 + int(time.time() * 1000) % 100003)
+    for _ in range(200):
+        base = rng.randrange(20000, 30000)
+        socks = []
+        try:
+            for off in (0, 17, 23):
+                s = socket.socket()
+                s.bind(("127.0.0.1", base + off))
+                socks.append(s)
+            return base
+        except OSError:
+            continue
+        finally:
+            for s in socks:
+                s.close()
+    raise RuntimeError("no free port found")
+
+
 BODY = {"input_tokens": [(7 * i + 3) % 200 + 3 for i in range(23)], "stream": False,
         "sampling_config": {"max_new_tokens": 8, "topk": 1, "ignore_eos": True}}
 
@@ -61,10 +84,7 @@ def _worker(rank, world, port, out, glob, model="tiny-llama", n=3):
 
 
 def _spawn(world, glob, model="tiny-llama", n=3):
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    port = s.getsockname()[1]
-    s.close()
+    port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, world, port, q, glob, model, n)) for r in range(world)]
@@ -173,11 +193,10 @@ def test_prefill_decode_disaggregation_between_tensor_parallel_instances():
     eng.shutdown()
     want = o.output_tokens[0]
     ports = []
-    for _ in range(3):
-        s = socket.socket()
-        s.bind(("127.0.0.1", 0))
-        ports.append(s.getsockname()[1])
-        s.close()
+    while len(ports) < 3:
+        c = _free_port()
+        if all(abs(c - o) > 64 for o in ports):
+            ports.append(c)
     tport = ports[2]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -225,10 +244,7 @@ def _hb_worker(rank, world, port, out):
 
 
 def test_a_silent_rank_is_detected_and_new_requests_are_refused():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    port = s.getsockname()[1]
-    s.close()
+    port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_hb_worker, args=(r, 2, port, q)) for r in range(2)]
@@ -268,10 +284,7 @@ def _fault_worker(rank, world, port, out):
 
 
 def test_a_set_device_status_word_fails_what_is_in_flight_and_refuses_new_requests():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    port = s.getsockname()[1]
-    s.close()
+    port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_fault_worker, args=(r, 2, port, q)) for r in range(2)]
