@@ -298,7 +298,9 @@ def unpack_gptq(qweight, qzeros, scales, g_idx, group: int, v1_zero_offset: bool
     zero - 1), scales [K/g, N], g_idx [K]. Returns (QuantW or None, dense fp32 weight or None). Act-order checkpoints
     (``g_idx`` not ascending: channels were quantised in order of importance) keep their grid with the columns
     gathered group by group and the gather recorded in ``QuantW.perm``; only a ``g_idx`` whose groups are not all of
-    the nominal size is returned dense."""
+    the nominal size is returned dense. Reference: the g_idx handling of src/ksana_llm/models/quant/quant_weight.cpp
+    and the act-order path of 3rdparty/LLM_kernels/csrc/kernels/nvidia/gptq_marlin/marlin_template.h:54-110, which
+    permutes the activations on the way into the kernel; here the layer gathers them before the 4-bit GEMM."""
     q = _unpack_nibbles(qweight, 0).t().contiguous()                 # [N, K]
     z = _unpack_nibbles(qzeros, 1).t().contiguous().float()          # [N, K/g]
     if v1_zero_offset:
