@@ -417,6 +417,7 @@ class LLMEngine:
                 if plan.empty():
                     if stride > 0:
                         self.runner.mock_forward(bool(self.mtp_steps))
+                        self._mtp_idle_passes(self.mtp_steps - 1)
                         self.stats["mock_steps"] = self.stats.get("mock_steps", 0) + 1
                     self.tracer.record("Schedule", "E", self.step_count)
                     return 0
@@ -806,6 +807,7 @@ class LLMEngine:
                 dist.broadcast(rows.cpu(), src=self._ctl_src, group=self._ctl)
         drafts = self._mtp_forward(mtp, nxt, rows, meta, hidden)
         if drafts is None:
+            self._mtp_idle_passes(self.mtp_steps - 1)
             return
         chains = [[int(d)] for d in drafts.tolist()]
         if self.mtp_steps > 1:
@@ -836,6 +838,7 @@ class LLMEngine:
             if any(p // bs >= len(t) for p, t in zip(pos, tables)):
                 if peers:
                     dist.broadcast(torch.zeros(2, dtype=torch.int32), src=self._ctl_src, group=self._ctl)
+                self._mtp_idle_passes(self.mtp_steps - k)
                 return  # no reserved slot (end of the length budget): shorter chains for everybody
             slots = [t[p // bs] * bs + p % bs for p, t in zip(pos, tables)]
             width = max(len(t) for t in tables)
@@ -852,6 +855,14 @@ class LLMEngine:
             nxt = model.greedy_tokens(h, meta.logits_idx).tolist()
             for c, d in zip(chains, nxt):
                 c.append(int(d))
+
+    @torch.inference_mode()
+    def _mtp_idle_passes(self, n: int) -> None:
+        """Attention data parallelism: the other ranks may be running ``n`` more passes of the draft module, each of
+        which exchanges tokens with every rank's experts; join them with empty passes."""
+        if n <= 0 or self.dp is None or not getattr(self, "_dp_mtp_lockstep", False):
+            return
+        self.runner.mock_mtp_passes(n)
 
     @torch.inference_mode()
     def _mtp_forward(self, mtp, nxt, rows, meta, hidden):
@@ -1081,9 +1092,12 @@ class LLMEngine:
         self.dp = coordinator
         self.async_mode = False
         self.tp.ep_dp = True
-        # further draft passes run on the ranks that have drafts only, while the experts' exchange needs every rank
-        # in every pass: one draft per step under attention data parallelism
-        self.mtp_steps = min(self.mtp_steps, 1)
+        # Every pass of the draft module goes through the experts' exchange, which needs every DP rank: single-rank DP
+        # groups all run the same number of passes per step (a rank without drafts joins with empty passes, see
+        # _mtp_idle_passes); with tensor parallelism inside the groups the followers' protocol carries one draft
+        self._dp_mtp_lockstep = self.tp.size == 1
+        if not self._dp_mtp_lockstep:
+            self.mtp_steps = min(self.mtp_steps, 1)
         lb = self.serving.setting.batch_scheduler.attention_dp_lb_config
         bc = coordinator if self.tp.size == 1 else balance_coordinator
         if lb.enable_balance and bc is not None:

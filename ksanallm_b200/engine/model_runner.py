@@ -167,6 +167,20 @@ class ModelRunner:
             mtp.forward(h.new_zeros(0, h.shape[-1]), h, meta, self.kv_caches[len(self.model.layers)])
 
     @torch.inference_mode()
+    def mock_mtp_passes(self, n: int) -> None:
+        """``n`` passes of the draft module over zero rows: only its expert exchange matters (see mock_forward)."""
+        if not self.model.mtp_layers:
+            return
+        from .step_input import make_step_input
+        meta = make_step_input([], [], [], [0], [], torch.zeros(0, 1, dtype=torch.int32), logits_idx=[],
+                               num_prefill=0, device=self.device)
+        mtp = self.model.mtp_layers[0]
+        H = self.model.cfg.hidden_size
+        empty = torch.zeros(0, H, dtype=self.model.dtype, device=self.device)
+        for _ in range(n):
+            mtp.forward(empty, empty, meta, self.kv_caches[len(self.model.layers)])
+
+    @torch.inference_mode()
     def sample(self, hidden: torch.Tensor, meta: StepInput, rows: Optional[Sequence[SampleRow]],
                greedy: Optional[bool] = None) -> SampleOutput:
         """rows is None on ranks that do not own the sampler: they still join the collectives of the

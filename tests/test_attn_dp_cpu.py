@@ -190,7 +190,7 @@ def test_expert_placement_permutation_and_routing_dump(tmp_path, monkeypatch):
     layers._EPLB_LAYERS.clear()
 
 
-def _mtp_dp_worker(rank, world, port, out):
+def _mtp_dp_worker(rank, world, port, out, drafts=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       EPLB_WEIGHT="")
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -200,9 +200,10 @@ def _mtp_dp_worker(rank, world, port, out):
     tp.ep_rank, tp.ep_size = rank, world
     tp.ep = GatherEPExchange(dist.group.WORLD, rank, world, cfg.num_experts_per_tok, cfg.num_experts)
     serving = parse_serving_config({"setting": {"batch_scheduler": {"max_batch_size": 4, "max_step_tokens": 64,
-                                                                     "max_token_len": 128, "mtp_step_num": 1}}})
+                                                                     "max_token_len": 128, "mtp_step_num": drafts}}})
     eng = LLMEngine(TransformerModel(cfg, w, tp), serving, tp, num_blocks=64, num_host_blocks=0)
     eng.attach_dp(DPCoordinator(dist.group.WORLD))
+    assert eng.mtp_steps == drafts
     reqs = [eng.add_request(p, SamplingParams(topk=1, max_new_tokens=NEW[rank], ignore_eos=True)) for p in PROMPTS[rank]]
     steps = eng.run_dp(max_steps=200)
     out.put((rank, [r.output_token_ids[0] for r in reqs], steps, eng.sched.stats.draft_proposed))
@@ -219,9 +220,11 @@ def _mtp_cfg():
         num_nextn_predict_layers=1, torch_dtype="float32", max_position_embeddings=256, eos_token_id=2))
 
 
-def test_mtp_drafts_under_attention_dp_keep_the_ranks_in_step():
-    """The draft pass goes through the expert exchange a second time per step; a rank that idles (mock steps) joins
-    that one too. Outputs equal single-process decoding without drafts."""
+@pytest.mark.parametrize("drafts", [1, 2, 3])
+def test_mtp_drafts_under_attention_dp_keep_the_ranks_in_step(drafts):
+    """Every pass of the draft module goes through the expert exchange once more per step; a rank that idles (mock
+    steps), has no draft rows or ran out of reserved slots joins the others' passes with empty ones. Outputs equal
+    single-process decoding without drafts."""
     cfg = _mtp_cfg()
     w = load_model_weights(cfg, synthetic_seed=4, dtype=torch.float32)
     want = {}
@@ -235,7 +238,7 @@ def test_mtp_drafts_under_attention_dp_keep_the_ranks_in_step():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_mtp_dp_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_mtp_dp_worker, args=(r, 2, port, q, drafts)) for r in range(2)]
     for p in procs:
         p.start()
     got = {}
