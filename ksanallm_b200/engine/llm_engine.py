@@ -194,6 +194,9 @@ class LLMEngine:
         # trusted. A multi-rank instance then refuses new requests (its ranks no longer agree on what they computed).
         self.device_fault: Optional[str] = None
         self.before_forward = None  # optional hook(plan), called on the step thread right before a forward pass
+        # optional hook(plan), called before a step's results reach the scheduler, i.e. before any sequence of the
+        # plan can finish and release its cache blocks
+        self.before_resolve = None
         self._ctl_ops: List[Tuple[Dict[str, Any], threading.Event]] = []  # control messages for the follower ranks
         self.on_control: Optional[Callable[[Dict[str, Any]], None]] = None   # follower side: handler of such messages
         self.dp_router = None       # parallel.attn_dp.DPRequestRouter on the rank that owns the HTTP front-end
@@ -499,6 +502,8 @@ class LLMEngine:
         plan, handle = inf
         toks = self.runner.wait_tokens(handle)
         n = len(toks)
+        if self.before_resolve is not None:
+            self.before_resolve(plan)
         with self.lock:
             results = self.sched.resolve(plan, toks)
             return self._apply_results(plan, SampleOutput(tokens=toks, logprobs=[None] * n, chosen_logprob=[None] * n),
@@ -530,6 +535,8 @@ class LLMEngine:
             meta = self.runner.upload(layout)
             if fix:
                 self.runner.fixup_inputs(meta)
+            if self.before_forward is not None:
+                self.before_forward(plan)  # prefill / decode disaggregation: KV leaves layer by layer
             hidden = self.runner.forward(meta, None)
             handle = self.runner.sample_greedy_async(hidden, meta)
         tb = time.perf_counter()
@@ -609,6 +616,8 @@ class LLMEngine:
         sampled = out.tokens
         # beam search rewrites the sampled tokens from the top-2k log-probs before the scheduler sees them
         if results is None:
+            if self.before_resolve is not None:
+                self.before_resolve(plan)
             results = self.sched.update(plan, sampled, int(now * 1000))
         # reading the status word waits for the device: cheap after a synchronous step (it is idle), but under
         # asynchronous scheduling it would wait for the step in flight, so that path looks 16 times less often

@@ -153,17 +153,19 @@ class PDConnector:
         """Announces that ``req`` will be handed over: the connection to the decode instance is opened now (off the
         step thread), and when the scheduler plans the prompt's last chunk the KV blocks leave layer by layer while
         the forward pass is still running (``LayerProgressTracker`` events), instead of all at once after the first
-        token. Used when the engine steps synchronously through the per-layer Python path on a single rank; anything
-        else keeps the one-piece export (the native executor reports its layers together, and tensor-parallel shards
-        travel after the step). Reference: the prefill side's layer-wise sends in
+        token. Used on single-rank instances, with synchronous or asynchronous stepping (through the native executor
+        the layers report together at the end of the stack, so the transfer then overlaps the sampling and the next
+        step's scheduling only); tensor-parallel instances keep the one-piece export, their shards travel after the
+        step. Reference: the prefill side's layer-wise sends in
         src/ksana_llm/transfer/transfer_engine.h:63-190."""
-        if not self.layerwise or self.llm.tp.size > 1 or getattr(self.llm, "async_mode", False):
+        if not self.layerwise or self.llm.tp.size > 1:
             return
         sess = _LayerwiseExport(self, req, request_id, group_key)
         self._by_rid[request_id] = sess
         for s_ in req.seqs:
             self._sessions[s_.seq_id] = sess
         self.llm.before_forward = self._on_plan
+        self.llm.before_resolve = self._before_resolve
         threading.Thread(target=sess.connect, daemon=True).start()
 
     def _on_plan(self, plan) -> None:
@@ -194,6 +196,16 @@ class PDConnector:
         sess = self._by_rid.get(request_id)
         if sess is not None:
             self._drop(sess)
+
+    def _before_resolve(self, plan) -> None:
+        """Engine hook: the step's results are about to reach the scheduler, which may finish the request and return
+        its blocks to the pool. The layers of a session armed for this step are read from those blocks by the
+        tracker's thread: wait until the last one has been copied out (the device finished this forward pass before
+        its tokens could be read, so this is the copy time of the last layers at most)."""
+        for e in plan.entries:
+            sess = self._sessions.get(e.seq_id)
+            if sess is not None and sess.armed and not sess.failed:
+                sess.layers_done.wait(30.0)
 
     def _drop(self, sess) -> None:
         self._by_rid.pop(sess.request_id, None)
@@ -339,6 +351,7 @@ class _LayerwiseExport:
             self.te.send_layer(layer, 0)
         except (OSError, ConnectionError):
             self.failed = True
+            self.layers_done.set()  # nobody needs to wait for the rest
         if layer == len(self.te.kv) - 1:
             self.layers_done.set()
 

@@ -17,9 +17,11 @@ BODY = {"input_tokens": [(7 * i + 3) % 200 + 3 for i in range(40)], "stream": Fa
         "sampling_config": {"max_new_tokens": 6, "topk": 1, "ignore_eos": True}}
 
 
-def _make(role, router="", group="", **extra):
+def _make(role, router="", group="", enable_async=None, **extra):
     args = EngineArgs.from_config_file(os.path.join(ROOT, "examples", "tiny_cpu.yaml"), synthetic_model="tiny-llama",
                                        device="cpu")
+    if enable_async is not None:
+        args.serving.setting.batch_scheduler.enable_async = enable_async
     cs = args.serving.setting.connector
     cs.group_role, cs.router_addr, cs.group_name, cs.connector_waiting_sec = role, router, group, 30
     cs.heartbeat_interval_ms = 200
@@ -138,16 +140,17 @@ def test_lookup_through_router(want):
         th.join(timeout=5)
 
 
-def test_kv_leaves_layer_by_layer_during_the_last_prefill_chunk(want, monkeypatch):
-    """Synchronous stepping through the per-layer path: the prefill instance ships each layer's blocks from the
-    layer tracker's callbacks while its forward pass runs (chunked prefill: the blocks of earlier chunks go with
-    the first layers of the last chunk), the first token follows as a trailer."""
+@pytest.mark.parametrize("enable_async", [False, True])
+def test_kv_leaves_layer_by_layer_during_the_last_prefill_chunk(want, monkeypatch, enable_async):
+    """The prefill instance ships each layer's blocks from the layer tracker's callbacks while its forward pass runs
+    (chunked prefill: the blocks of earlier chunks go with the first layers of the last chunk), the first token
+    follows as a trailer; with synchronous and with asynchronous stepping."""
     monkeypatch.setenv("KSANA_PD_LAYERWISE_WAIT_MS", "5000")
     decode = _make("decode")
-    prefill = _make("prefill", peer_transfer_addr="%s:%d" % decode.connector.transfer_addr)
+    prefill = _make("prefill", enable_async=enable_async, peer_transfer_addr="%s:%d" % decode.connector.transfer_addr)
     order = []
     try:
-        prefill.llm.async_mode = False
+        assert prefill.llm.async_mode == enable_async
         from ksanallm_b200.parallel import transfer
         real = transfer.TransferEngine.send_layer
 
